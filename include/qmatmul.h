@@ -1,0 +1,143 @@
+/*
+ * qmatmul.h — C ABI of libqmatmul.so: fused dequantize-and-multiply over GGUF
+ * block-quantized weights on NVIDIA B200 (sm_100a).
+ *
+ * The library is meant to be bound without cgo (dlopen + dlsym, positional
+ * integer/pointer arguments, no variadics, no struct by value): the calling
+ * constraints of the reference's purego funnel (nvidia/internal/ffi/ffi.go:67-86).
+ * Every entry point returns an int32 status: 0 = success, negative = one of the
+ * QM_ERR_* codes below, positive = a CUresult of the CUDA driver, passed
+ * through unchanged (the convention of nvidia/driver/result.gen.go:207-212).
+ * No entry point aborts, traps or leaves a device-side wait unbounded.
+ *
+ * Kernels are sm_100a cubins that the library loads with cuModuleLoadData, the
+ * call behind the reference's cudakernel.Artifact.Load
+ * (nvidia/x/cudakernel/artifact.go:303-340). The same cubins and a JSON
+ * description of each kernel's parameters sit next to the library so that a Go
+ * caller may also load them directly through nvidia/driver.
+ *
+ * Threading: a qm_ctx binds one device's primary context and one stream. Each
+ * call makes that context current for its own duration (the discipline of
+ * nvidia/x/cuda/context.go:35-59), so calls may come from any OS thread, one at
+ * a time per qm_ctx.
+ */
+#ifndef QMATMUL_H
+#define QMATMUL_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QM_VERSION 100
+#define QM_API __attribute__((visibility("default")))
+
+/* Weight formats: the GGUF tensor type ids of gguf/gguf.go:273-282. */
+#define QM_FMT_Q4_0 2  /* lm/quant/quant.go:30-34  BlockQ4_0, 18 bytes / 32 elements  */
+#define QM_FMT_Q8_0 8  /* lm/quant/quant.go:36-40  BlockQ8_0, 34 bytes / 32 elements  */
+#define QM_FMT_Q2_K 10 /* lm/quant/kquant.go:29-34 BlockQ2_K, 84 bytes / 256 elements */
+#define QM_FMT_Q4_K 12 /* gguf/gguf.go:276         type 12, 144 bytes / 256 elements  */
+
+#define QM_OK 0
+#define QM_ERR_COUNT (-1)    /* element count negative or not a multiple of the block (quant.go:45) */
+#define QM_ERR_BUFFER (-2)   /* byte buffer shorter than the blocks need (quant.go:49)              */
+#define QM_ERR_FORMAT (-3)   /* unknown or unsupported weight format                                */
+#define QM_ERR_SHAPE (-4)    /* rows/cols/m/ld out of range for the operation                       */
+#define QM_ERR_ARG (-5)      /* NULL pointer or invalid handle                                      */
+#define QM_ERR_NO_DRIVER (-6)/* libcuda could not be loaded or lacks a required symbol              */
+#define QM_ERR_NO_KERNEL (-7)/* a kernel image failed to load: the library cannot run               */
+#define QM_ERR_TIMEOUT (-8)  /* a bounded device-side wait expired; see qm_last_status              */
+#define QM_ERR_NOMEM (-9)    /* host allocation failed                                              */
+#define QM_ERR_STATE (-10)   /* call not valid in the object's current state                        */
+#define QM_ERR_LIMIT (-11)   /* size beyond a documented fixed maximum                              */
+
+/* Input transforms applied to the activation vector while it is staged
+ * (qm_matvec flags, bits 0..3). */
+#define QM_XOP_NONE 0u
+#define QM_XOP_RMSNORM 1u     /* x * rsqrt(mean(x^2)+eps), the form of the reference's fused
+                                 RMSNorm+GEMV (nvidia/x/egraph/codegen.go:395-414), no gain    */
+#define QM_XOP_ADD_RMSNORM 2u /* rmsnorm(x + x2)                                               */
+#define QM_XOP_SWIGLU 3u      /* silu(x) * x2 (nvidia/x/egraph/codegen.go:328-374)             */
+#define QM_FLAG_PDL 0x100u    /* launch with programmatic stream serialization                 */
+
+typedef struct qm_ctx qm_ctx;
+typedef uint64_t qm_weight; /* opaque handle of one device-resident weight matrix */
+
+QM_API int32_t qm_version(void);
+/* Static, NUL-terminated description of a status code (driver codes included
+ * once a context exists). Mirrors cuGetErrorString as used by
+ * nvidia/driver/result.gen.go:21. */
+QM_API const char *qm_error_string(int32_t code);
+
+/* Context: loads libcuda, retains the primary context of `device`, loads the
+ * kernel images, creates a stream. Replaces the reference's
+ * cuda.NewDevice + nvrtcx Compile/Load chain (nvidia/x/cuda/device.go:22-41,
+ * nvidia/x/nvrtcx/load.go:26-71). */
+QM_API int32_t qm_init(int32_t device, qm_ctx **out);
+QM_API int32_t qm_destroy(qm_ctx *ctx);
+/* Use the caller's CUstream (0 = the library's own stream) for all later work. */
+QM_API int32_t qm_set_stream(qm_ctx *ctx, uint64_t cu_stream);
+QM_API int32_t qm_sync(qm_ctx *ctx);
+/* Device status word of the most recent launches (0 = clean); cleared on read. */
+QM_API int32_t qm_last_status(qm_ctx *ctx, uint32_t *status);
+/* Number of kernel launches issued through this context since qm_init. The
+ * counter the reference keeps in cudalaunch.TotalLaunches
+ * (nvidia/x/cudalaunch/launch.go:46-48). */
+QM_API int64_t qm_launch_count(qm_ctx *ctx);
+
+/* Plain device memory for callers without an allocator of their own
+ * (driver.MemAllocBytes / DevicePtr.CopyFromHostPtr / CopyToHostPtr,
+ * nvidia/driver/funcs.gen.go:12837, device_ptr.gen.go:679,597). */
+QM_API int32_t qm_malloc(qm_ctx *ctx, int64_t bytes, uint64_t *dptr);
+QM_API int32_t qm_free(qm_ctx *ctx, uint64_t dptr);
+QM_API int32_t qm_memcpy_h2d(qm_ctx *ctx, uint64_t dst, const void *src, int64_t bytes);
+QM_API int32_t qm_memcpy_d2h(qm_ctx *ctx, void *dst, uint64_t src, int64_t bytes);
+
+/* Weight store. `host_bytes` are the tensor's bytes exactly as the GGUF file
+ * holds them at DataOffset+Tensor.Offset (gguf/gguf.go:108-113,285-306):
+ * `rows` rows of `cols` elements, row-major blocks. `cols` is
+ * Tensor.Dimensions[0] and must be block aligned (gguf.go:290-292). Only rows
+ * [row_lo,row_hi) are kept on the device (tensor-parallel row shard);
+ * pass 0,rows for all. The bytes are copied before the call returns; nothing
+ * is retained (nvidia/internal/ffi/call_funnel.go:100-126). */
+QM_API int32_t qm_store_upload(qm_ctx *ctx, int32_t fmt, int64_t rows, int64_t cols, const void *host_bytes,
+                        int64_t len, int64_t row_lo, int64_t row_hi, qm_weight *out);
+/* A store entry assembled from several tensors stacked by rows (q|k|v,
+ * gate|up): create with the total row count, then write row ranges. */
+QM_API int32_t qm_store_create(qm_ctx *ctx, int32_t fmt, int64_t rows, int64_t cols, qm_weight *out);
+QM_API int32_t qm_store_write_rows(qm_ctx *ctx, qm_weight w, int64_t row_offset, int64_t nrows,
+                            const void *host_bytes, int64_t len);
+/* Same, with the GGUF bytes already in device memory (not retained). */
+QM_API int32_t qm_store_write_rows_device(qm_ctx *ctx, qm_weight w, int64_t row_offset, int64_t nrows,
+                                   uint64_t dev_bytes, int64_t len);
+QM_API int32_t qm_store_free(qm_ctx *ctx, qm_weight w);
+/* info[0]=fmt, [1]=rows, [2]=cols, [3]=device bytes held, [4]=GGUF bytes represented */
+QM_API int32_t qm_store_info(qm_ctx *ctx, qm_weight w, int64_t *info5);
+
+/* Dequantize a stored matrix to float32 [rows][cols] in device memory.
+ * Bit-exact with quant.DequantizeQ4_0/Q8_0/Q2_K (lm/quant/quant.go:44,72,
+ * lm/quant/kquant.go:49). */
+QM_API int32_t qm_dequantize(qm_ctx *ctx, qm_weight w, uint64_t out_f32_dev);
+/* quant.Dequantize*(data []byte, numElements int) ([]float32, error) on the
+ * GPU with host buffers: same validation order and error cases
+ * (lm/quant/quant.go:44-91, kquant.go:49-77). */
+QM_API int32_t qm_dequantize_host(qm_ctx *ctx, int32_t fmt, const void *data, int64_t len, int64_t num_elements,
+                           float *out_host);
+
+/* y[j][r] = sum_c x[j][c] * W[r][c] for j < m (1 <= m <= 8), float32 in and
+ * out, device pointers; x rows are ldx floats apart, y rows ldy floats apart.
+ * `x2_dev` is the second operand of QM_XOP_ADD_RMSNORM / QM_XOP_SWIGLU (0
+ * otherwise). Supersedes the reference's one-warp-per-row kernels
+ * (nvidia/x/egraph/codegen.go:443-482, 674-735). */
+QM_API int32_t qm_matvec(qm_ctx *ctx, qm_weight w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,
+                  uint64_t y_dev, int64_t ldy, uint32_t flags);
+/* Same through host buffers: x is copied to the device, y copied back and the
+ * stream synchronized before the call returns. */
+QM_API int32_t qm_matvec_host(qm_ctx *ctx, qm_weight w, const float *x_host, int32_t m, int64_t ldx,
+                       float *y_host, int64_t ldy, uint32_t flags);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QMATMUL_H */

@@ -1,0 +1,184 @@
+"""ctypes binding of include/qmatmul.h. Every call goes through the C ABI."""
+import ctypes
+import os
+import re
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.environ.get("QMATMUL_LIB", os.path.join(_HERE, "libqmatmul.so"))
+_HEADER = os.path.join(_HERE, "..", "include", "qmatmul.h")
+
+Q4_0, Q8_0, Q2_K, Q4_K = 2, 8, 10, 12
+XOP_NONE, XOP_RMSNORM, XOP_ADD_RMSNORM, XOP_SWIGLU = 0, 1, 2, 3
+FLAG_PDL = 0x100
+
+
+class QmError(RuntimeError):
+    def __init__(self, code, what=""):
+        self.code = code
+        msg = lib.qm_error_string(code).decode() if lib is not None else "status %d" % code
+        super().__init__("%s%s (status %d)" % (what + ": " if what else "", msg, code))
+
+
+def _load():
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            "libqmatmul.so is not built (%s); run `python -m lib_b200.build`. There is no "
+            "fallback implementation." % _LIB_PATH)
+    L = ctypes.CDLL(_LIB_PATH)
+    i32, i64, u32, u64, p = ctypes.c_int32, ctypes.c_int64, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
+    sig = {
+        "qm_version": (i32, []),
+        "qm_error_string": (ctypes.c_char_p, [i32]),
+        "qm_init": (i32, [i32, ctypes.POINTER(p)]),
+        "qm_destroy": (i32, [p]),
+        "qm_set_stream": (i32, [p, u64]),
+        "qm_sync": (i32, [p]),
+        "qm_last_status": (i32, [p, ctypes.POINTER(u32)]),
+        "qm_launch_count": (i64, [p]),
+        "qm_malloc": (i32, [p, i64, ctypes.POINTER(u64)]),
+        "qm_free": (i32, [p, u64]),
+        "qm_memcpy_h2d": (i32, [p, u64, p, i64]),
+        "qm_memcpy_d2h": (i32, [p, p, u64, i64]),
+        "qm_store_upload": (i32, [p, i32, i64, i64, p, i64, i64, i64, ctypes.POINTER(u64)]),
+        "qm_store_create": (i32, [p, i32, i64, i64, ctypes.POINTER(u64)]),
+        "qm_store_write_rows": (i32, [p, u64, i64, i64, p, i64]),
+        "qm_store_write_rows_device": (i32, [p, u64, i64, i64, u64, i64]),
+        "qm_store_free": (i32, [p, u64]),
+        "qm_store_info": (i32, [p, u64, ctypes.POINTER(i64)]),
+        "qm_dequantize": (i32, [p, u64, u64]),
+        "qm_dequantize_host": (i32, [p, i32, p, i64, i64, p]),
+        "qm_matvec": (i32, [p, u64, u64, u64, i32, i64, u64, i64, u32]),
+        "qm_matvec_host": (i32, [p, u64, p, i32, i64, p, i64, u32]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(L, name)
+        fn.restype, fn.argtypes = res, args
+    return L
+
+
+lib = _load()
+
+
+def declared_symbols():
+    """Names of every entry point include/qmatmul.h declares."""
+    return re.findall(r"QM_API\s+[\w \*]+?\b(qm_\w+)\(", open(_HEADER).read())
+
+
+def _check(rc, what=""):
+    if rc != 0:
+        raise QmError(rc, what)
+
+
+def _u8(data):
+    if isinstance(data, np.ndarray):
+        return np.ascontiguousarray(data.view(np.uint8).reshape(-1))
+    return np.frombuffer(bytes(data), dtype=np.uint8)
+
+
+class Weight:
+    """A device-resident weight matrix of the store (qm_weight)."""
+
+    def __init__(self, ctx, handle):
+        self.ctx, self.handle = ctx, handle
+        info = (ctypes.c_int64 * 5)()
+        _check(lib.qm_store_info(ctx._h, handle, info))
+        self.fmt, self.rows, self.cols, self.device_bytes, self.gguf_bytes = [int(v) for v in info]
+
+    def write_rows(self, row_offset, nrows, data):
+        a = _u8(data)
+        _check(lib.qm_store_write_rows(self.ctx._h, self.handle, row_offset, nrows, a.ctypes.data, a.size),
+               "store_write_rows")
+
+    def write_rows_device(self, row_offset, nrows, dev_ptr, nbytes):
+        _check(lib.qm_store_write_rows_device(self.ctx._h, self.handle, row_offset, nrows, dev_ptr, nbytes),
+               "store_write_rows_device")
+
+    def free(self):
+        if self.handle:
+            _check(lib.qm_store_free(self.ctx._h, self.handle))
+            self.handle = 0
+
+
+class Context:
+    """qm_ctx: one device, its kernels and a stream. Raises if the CUDA driver
+    or the sm_100a kernel images cannot be loaded — there is no other path."""
+
+    def __init__(self, device=0):
+        h = ctypes.c_void_p()
+        _check(lib.qm_init(device, ctypes.byref(h)), "qm_init")
+        self._h = h
+        self.device = device
+
+    def close(self):
+        if self._h:
+            lib.qm_destroy(self._h)
+            self._h = None
+
+    def set_stream(self, cu_stream):
+        _check(lib.qm_set_stream(self._h, int(cu_stream)))
+
+    def sync(self):
+        _check(lib.qm_sync(self._h), "qm_sync")
+
+    def last_status(self):
+        s = ctypes.c_uint32(0)
+        rc = lib.qm_last_status(self._h, ctypes.byref(s))
+        return rc, s.value
+
+    def launch_count(self):
+        return int(lib.qm_launch_count(self._h))
+
+    # -- memory -------------------------------------------------------------
+    def malloc(self, nbytes):
+        d = ctypes.c_uint64(0)
+        _check(lib.qm_malloc(self._h, nbytes, ctypes.byref(d)), "qm_malloc")
+        return d.value
+
+    def free(self, dptr):
+        _check(lib.qm_free(self._h, dptr))
+
+    def h2d(self, dptr, arr):
+        a = np.ascontiguousarray(arr)
+        _check(lib.qm_memcpy_h2d(self._h, dptr, a.ctypes.data, a.nbytes), "h2d")
+
+    def d2h(self, arr, dptr):
+        assert arr.flags["C_CONTIGUOUS"]
+        _check(lib.qm_memcpy_d2h(self._h, arr.ctypes.data, dptr, arr.nbytes), "d2h")
+
+    # -- store --------------------------------------------------------------
+    def store_upload(self, fmt, rows, cols, data, row_lo=0, row_hi=None):
+        a = _u8(data)
+        h = ctypes.c_uint64(0)
+        _check(lib.qm_store_upload(self._h, fmt, rows, cols, a.ctypes.data, a.size, row_lo,
+                                   rows if row_hi is None else row_hi, ctypes.byref(h)), "store_upload")
+        return Weight(self, h.value)
+
+    def store_create(self, fmt, rows, cols):
+        h = ctypes.c_uint64(0)
+        _check(lib.qm_store_create(self._h, fmt, rows, cols, ctypes.byref(h)), "store_create")
+        return Weight(self, h.value)
+
+    # -- operations -----------------------------------------------------------
+    def dequantize(self, w, out_dev):
+        _check(lib.qm_dequantize(self._h, w.handle, out_dev), "dequantize")
+
+    def dequantize_host(self, fmt, data, num_elements):
+        a = _u8(data)
+        out = np.empty(max(int(num_elements), 0), dtype=np.float32)
+        _check(lib.qm_dequantize_host(self._h, fmt, a.ctypes.data, a.size, int(num_elements),
+                                      out.ctypes.data), "dequantize")
+        return out
+
+    def matvec(self, w, x_dev, m, ldx, y_dev, ldy, flags=0, x2_dev=0):
+        _check(lib.qm_matvec(self._h, w.handle, x_dev, x2_dev, m, ldx, y_dev, ldy, flags), "matvec")
+
+    def matvec_host(self, w, x, flags=0, out=None):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        x2 = x.reshape(1, -1) if x.ndim == 1 else x
+        m = x2.shape[0]
+        y = out if out is not None else np.empty((m, w.rows), dtype=np.float32)
+        _check(lib.qm_matvec_host(self._h, w.handle, x2.ctypes.data, m, x2.shape[1], y.ctypes.data,
+                                  y.shape[-1], flags), "matvec")
+        return y[0] if (x.ndim == 1 and out is None) else y

@@ -1,0 +1,167 @@
+// qm_dequant.cu — bit-exact dequantization of stored weights to float32, and the
+// upload-time repack of Q4_0/Q8_0 GGUF blocks into the store's layout (sm_100a).
+//
+// The arithmetic is that of the reference's CPU decoders, one float32
+// operation at a time with no fused multiply-add:
+//   Q4_0  (nibble-8)*scale            lm/quant/quant.go:60-64
+//   Q8_0  int8*scale                  lm/quant/quant.go:87
+//   Q2_K  d*(sc&15)*q - dmin*(sc>>4)  lm/quant/kquant.go:66-73
+//   Q4_K  d*sc*q - dmin*m             same form; layout of GGUF type 12
+// fp16 scales go through an integer restatement of Float16ToFloat32
+// (lm/quant/quant.go:94-116) so that NaN payloads survive unchanged.
+#include <stdint.h>
+
+#include "qm_kernel_args.h"
+
+namespace {
+
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t h) {
+    const uint32_t sign = (h & 0x8000u) << 16;
+    uint32_t exp = (h & 0x7C00u) >> 10;
+    uint32_t mant = h & 0x03FFu;
+    if (exp == 0) {
+        if (mant == 0) return __uint_as_float(sign);
+        const int shift = __clz(mant) - 21;  // bring the leading one to bit 10
+        mant = (mant << shift) & 0x03FFu;
+        exp = (uint32_t)(1 - shift);
+    } else if (exp == 0x1F) {
+        return __uint_as_float(sign | 0x7F800000u | (mant << 13));
+    }
+    return __uint_as_float(sign | ((exp + 112u) << 23) | (mant << 13));
+}
+
+__device__ __forceinline__ float4 scale4(uint32_t bytes4, float t1, float t3) {
+    float4 o;
+    o.x = __fsub_rn(__fmul_rn(t1, (float)(bytes4 & 0xFF)), t3);
+    o.y = __fsub_rn(__fmul_rn(t1, (float)((bytes4 >> 8) & 0xFF)), t3);
+    o.z = __fsub_rn(__fmul_rn(t1, (float)((bytes4 >> 16) & 0xFF)), t3);
+    o.w = __fsub_rn(__fmul_rn(t1, (float)(bytes4 >> 24)), t3);
+    return o;
+}
+
+}  // namespace
+
+// One thread per four consecutive output columns.
+extern "C" __global__ void __launch_bounds__(256) qm_dequant_q4k(const __grid_constant__ QmDequantArgs a) {
+    const int64_t ngroups = a.rows * (int64_t)(a.cols / 4);
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < ngroups;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = idx / (a.cols / 4);
+        const int col = (int)(idx - row * (a.cols / 4)) * 4;
+        const int u = col >> 8, e = col & 255, j = e >> 5, i = e & 31;
+        const uint8_t *blk = a.wq + (row * a.units + u) * 144;
+        const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk);
+        const float d = f16_bits_to_f32(dd & 0xFFFFu), dmin = f16_bits_to_f32(dd >> 16);
+        const uint8_t *S = blk + 4;
+        int sc, m;
+        if (j < 4) {
+            sc = S[j] & 63;
+            m = S[j + 4] & 63;
+        } else {
+            sc = (S[j + 4] & 0x0F) | ((S[j - 4] >> 6) << 4);
+            m = (S[j + 4] >> 4) | ((S[j] >> 6) << 4);
+        }
+        uint32_t q4 = *reinterpret_cast<const uint32_t *>(blk + 16 + 32 * (j >> 1) + i);
+        q4 = (j & 1) ? ((q4 >> 4) & 0x0F0F0F0Fu) : (q4 & 0x0F0F0F0Fu);
+        const float t1 = __fmul_rn(d, (float)sc), t3 = __fmul_rn(dmin, (float)m);
+        *reinterpret_cast<float4 *>(a.out + row * a.cols + col) = scale4(q4, t1, t3);
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(256) qm_dequant_q2k(const __grid_constant__ QmDequantArgs a) {
+    const int64_t ngroups = a.rows * (int64_t)(a.cols / 4);
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < ngroups;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = idx / (a.cols / 4);
+        const int col = (int)(idx - row * (a.cols / 4)) * 4;
+        const int u = col >> 8, e = col & 255, group = e >> 4, l = e & 15;
+        const uint8_t *blk = a.wq + (row * a.units + u) * 84;
+        const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk + 80);
+        const float d = f16_bits_to_f32(dd & 0xFFFFu), dmin = f16_bits_to_f32(dd >> 16);
+        const int base = 32 * (group >> 3) + 16 * (group & 1);
+        const int shift = ((group >> 1) & 3) * 2;
+        const uint32_t q4 = (*reinterpret_cast<const uint32_t *>(blk + 16 + base + l) >> shift) & 0x03030303u;
+        const uint32_t sc = blk[group];
+        const float t1 = __fmul_rn(d, (float)(sc & 0x0F)), t3 = __fmul_rn(dmin, (float)(sc >> 4));
+        *reinterpret_cast<float4 *>(a.out + row * a.cols + col) = scale4(q4, t1, t3);
+    }
+}
+
+// Store layout of Q4_0: 4-block groups of 64 bytes, word t*4+i = word t of block 4G+i.
+extern "C" __global__ void __launch_bounds__(256) qm_dequant_q40(const __grid_constant__ QmDequantArgs a) {
+    const int64_t ngroups = a.rows * (int64_t)(a.cols / 4);
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < ngroups;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = idx / (a.cols / 4);
+        const int col = (int)(idx - row * (a.cols / 4)) * 4;
+        const int blk = col >> 5, i = col & 31, half = i >> 4, t = (i & 15) >> 2;
+        const int64_t b0 = row * a.units * 8;
+        const float d = f16_bits_to_f32(a.wd[b0 + blk]);
+        const uint32_t *words = reinterpret_cast<const uint32_t *>(a.wq + b0 * 16);
+        uint32_t q4 = words[(blk >> 2) * 16 + t * 4 + (blk & 3)];
+        q4 = half ? ((q4 >> 4) & 0x0F0F0F0Fu) : (q4 & 0x0F0F0F0Fu);
+        float4 o;
+        o.x = __fmul_rn((float)((int)(q4 & 0xFF) - 8), d);
+        o.y = __fmul_rn((float)((int)((q4 >> 8) & 0xFF) - 8), d);
+        o.z = __fmul_rn((float)((int)((q4 >> 16) & 0xFF) - 8), d);
+        o.w = __fmul_rn((float)((int)(q4 >> 24) - 8), d);
+        *reinterpret_cast<float4 *>(a.out + row * a.cols + col) = o;
+    }
+}
+
+// Store layout of Q8_0: 2-block groups of 64 bytes, word t*4+2*bi+hf = word 4*hf+t of block 2G+bi.
+extern "C" __global__ void __launch_bounds__(256) qm_dequant_q80(const __grid_constant__ QmDequantArgs a) {
+    const int64_t ngroups = a.rows * (int64_t)(a.cols / 4);
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < ngroups;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = idx / (a.cols / 4);
+        const int col = (int)(idx - row * (a.cols / 4)) * 4;
+        const int blk = col >> 5, w = (col & 31) >> 2, hf = w >> 2, t = w & 3;
+        const int64_t b0 = row * a.units * 8;
+        const float d = f16_bits_to_f32(a.wd[b0 + blk]);
+        const uint32_t *words = reinterpret_cast<const uint32_t *>(a.wq + b0 * 32);
+        const uint32_t q4 = words[(blk >> 1) * 16 + t * 4 + 2 * (blk & 1) + hf];
+        float4 o;
+        o.x = __fmul_rn((float)(int8_t)(q4 & 0xFF), d);
+        o.y = __fmul_rn((float)(int8_t)((q4 >> 8) & 0xFF), d);
+        o.z = __fmul_rn((float)(int8_t)((q4 >> 16) & 0xFF), d);
+        o.w = __fmul_rn((float)(int8_t)(q4 >> 24), d);
+        *reinterpret_cast<float4 *>(a.out + row * a.cols + col) = o;
+    }
+}
+
+// GGUF Q4_0 rows (18-byte blocks, 2-byte aligned) -> store layout. One thread per block.
+extern "C" __global__ void __launch_bounds__(256) qm_repack_q40(const __grid_constant__ QmRepackArgs a) {
+    const int nblk = a.cols / 32;
+    const int64_t total = a.nrows * nblk;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / nblk;
+        const int blk = (int)(idx - r * nblk);
+        const uint16_t *s = reinterpret_cast<const uint16_t *>(a.src + idx * 18);
+        const int64_t b0 = (a.row_offset + r) * a.units * 8;
+        a.wd[b0 + blk] = s[0];
+        uint32_t *words = reinterpret_cast<uint32_t *>(a.wq + b0 * 16);
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+            words[(blk >> 2) * 16 + t * 4 + (blk & 3)] = (uint32_t)s[1 + 2 * t] | ((uint32_t)s[2 + 2 * t] << 16);
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(256) qm_repack_q80(const __grid_constant__ QmRepackArgs a) {
+    const int nblk = a.cols / 32;
+    const int64_t total = a.nrows * nblk;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / nblk;
+        const int blk = (int)(idx - r * nblk);
+        const uint16_t *s = reinterpret_cast<const uint16_t *>(a.src + idx * 34);
+        const int64_t b0 = (a.row_offset + r) * a.units * 8;
+        a.wd[b0 + blk] = s[0];
+        uint32_t *words = reinterpret_cast<uint32_t *>(a.wq + b0 * 32);
+#pragma unroll
+        for (int w = 0; w < 8; w++)
+            words[(blk >> 1) * 16 + (w & 3) * 4 + 2 * (blk & 1) + (w >> 2)] =
+                (uint32_t)s[1 + 2 * w] | ((uint32_t)s[2 + 2 * w] << 16);
+    }
+}

@@ -1,0 +1,636 @@
+// qm_host.cpp — host side of libqmatmul.so: context, weight store, launch
+// planning and the C ABI of include/qmatmul.h, over the CUDA driver API.
+//
+// There is no CPU implementation of any operation in this library: if libcuda
+// or a kernel image cannot be loaded, qm_init fails and nothing else works.
+#include <dlfcn.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <mutex>
+#include <new>
+
+#include "../../include/qmatmul.h"
+#include "qm_driver.h"
+#include "qm_internal.h"
+
+// ---- driver binding --------------------------------------------------------------
+static QmDriver g_drv;
+static std::once_flag g_drv_once;
+static int g_drv_rc = QM_ERR_NO_DRIVER;
+
+int qm_driver_load(QmDriver **out) {
+    std::call_once(g_drv_once, [] {
+        const char *path = getenv("CUDA_LIB_PATH");  // same override as nvidia/driver/init.gen.go:190
+        void *h = nullptr;
+        if (path && *path) h = dlopen(path, RTLD_LAZY | RTLD_GLOBAL);
+        if (!h) h = dlopen("libcuda.so.1", RTLD_LAZY | RTLD_GLOBAL);
+        if (!h) h = dlopen("libcuda.so", RTLD_LAZY | RTLD_GLOBAL);
+        if (!h) return;
+        bool ok = true;
+#define X(name, ...)                                                          \
+    g_drv.name = reinterpret_cast<qm_fnptr<__VA_ARGS__>>(dlsym(h, #name));   \
+    if (!g_drv.name) ok = false;
+        QM_DRV_FUNCS(X)
+#undef X
+        g_drv.loaded = ok;
+        g_drv_rc = ok ? QM_OK : QM_ERR_NO_DRIVER;
+    });
+    *out = &g_drv;
+    return g_drv_rc;
+}
+
+// ---- embedded kernel images --------------------------------------------------------
+#define QM_STR2(x) #x
+#define QM_STR(x) QM_STR2(x)
+#define QM_INCBIN(sym, file)                                                               \
+    __asm__(".section .rodata\n.balign 16\n.global " #sym "\n" #sym ":\n.incbin \"" file   \
+            "\"\n.global " #sym "_end\n" #sym "_end:\n.byte 0\n.previous\n");              \
+    extern "C" const unsigned char sym[];                                                  \
+    extern "C" const unsigned char sym##_end[];
+
+QM_INCBIN(qm_cubin_gemv, QM_STR(QM_CUBIN_DIR) "/qm_gemv.sm_100a.cubin")
+QM_INCBIN(qm_cubin_dequant, QM_STR(QM_CUBIN_DIR) "/qm_dequant.sm_100a.cubin")
+
+struct KernelImage {
+    const unsigned char *begin;
+    const unsigned char *end;
+};
+static const KernelImage kImages[QM_MOD_COUNT] = {
+    {qm_cubin_gemv, qm_cubin_gemv_end},
+    {qm_cubin_dequant, qm_cubin_dequant_end},
+};
+struct KernelName {
+    int module;
+    const char *name;
+};
+static const KernelName kKernels[QM_K_COUNT] = {
+    {QM_MOD_GEMV, "qm_gemv_q4k_m4"},   {QM_MOD_GEMV, "qm_gemv_q4k_m8"},    {QM_MOD_GEMV, "qm_gemv_q40_m4"},
+    {QM_MOD_GEMV, "qm_gemv_q40_m8"},   {QM_MOD_GEMV, "qm_gemv_q80_m4"},    {QM_MOD_GEMV, "qm_gemv_q80_m8"},
+    {QM_MOD_DEQUANT, "qm_dequant_q4k"}, {QM_MOD_DEQUANT, "qm_dequant_q2k"}, {QM_MOD_DEQUANT, "qm_dequant_q40"},
+    {QM_MOD_DEQUANT, "qm_dequant_q80"}, {QM_MOD_DEQUANT, "qm_repack_q40"},  {QM_MOD_DEQUANT, "qm_repack_q80"},
+};
+
+// ---- errors --------------------------------------------------------------------------
+extern "C" int32_t qm_version(void) { return QM_VERSION; }
+
+extern "C" const char *qm_error_string(int32_t code) {
+    switch (code) {
+    case QM_OK: return "success";
+    case QM_ERR_COUNT: return "quant: element count is not a non-negative multiple of the block";
+    case QM_ERR_BUFFER: return "quant: buffer length insufficient for the blocks";
+    case QM_ERR_FORMAT: return "quant: unknown or unsupported weight format";
+    case QM_ERR_SHAPE: return "quant: shape out of range for the operation";
+    case QM_ERR_ARG: return "quant: null pointer or invalid handle";
+    case QM_ERR_NO_DRIVER: return "quant: CUDA driver library not available";
+    case QM_ERR_NO_KERNEL: return "quant: kernel image failed to load";
+    case QM_ERR_TIMEOUT: return "quant: bounded device wait expired";
+    case QM_ERR_NOMEM: return "quant: host allocation failed";
+    case QM_ERR_STATE: return "quant: call not valid in this state";
+    case QM_ERR_LIMIT: return "quant: size beyond the fixed maximum of this entry point";
+    }
+    if (code > 0 && g_drv.loaded) {
+        const char *s = nullptr;
+        if (g_drv.cuGetErrorString((CUresult)code, &s) == CUDA_SUCCESS && s) return s;
+    }
+    return "quant: unknown status";
+}
+
+// ---- context -----------------------------------------------------------------------------
+CtxGuard::CtxGuard(qm_ctx *c) : ctx(c) { rc = c->drv->cuCtxPushCurrent_v2(c->cuctx); }
+CtxGuard::~CtxGuard() {
+    if (rc == CUDA_SUCCESS) {
+        CUcontext old;
+        ctx->drv->cuCtxPopCurrent_v2(&old);
+    }
+}
+
+extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
+    if (!out) return QM_ERR_ARG;
+    *out = nullptr;
+    QmDriver *d;
+    int rc = qm_driver_load(&d);
+    if (rc) return rc;
+    DRV(d->cuInit(0));
+    qm_ctx *c = new (std::nothrow) qm_ctx();
+    if (!c) return QM_ERR_NOMEM;
+    c->magic = QM_CTX_MAGIC;
+    c->drv = d;
+    c->device = device;
+    CUresult r = d->cuDeviceGet(&c->cudev, device);
+    if (r == CUDA_SUCCESS) r = d->cuDevicePrimaryCtxRetain(&c->cuctx, c->cudev);
+    if (r != CUDA_SUCCESS) {
+        delete c;
+        return (int32_t)r;
+    }
+    c->have_ctx = true;
+    int32_t err = QM_OK;
+    {
+        CtxGuard g(c);
+        if (g.rc != CUDA_SUCCESS) err = (int32_t)g.rc;
+        int major = 0, minor = 0;
+        if (!err) {
+            d->cuDeviceGetAttribute(&major, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MAJOR, c->cudev);
+            d->cuDeviceGetAttribute(&minor, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MINOR, c->cudev);
+            d->cuDeviceGetAttribute(&c->sm_count, CU_DEVICE_ATTRIBUTE_MULTIPROCESSOR_COUNT, c->cudev);
+            d->cuDeviceGetAttribute(&c->l2_bytes, CU_DEVICE_ATTRIBUTE_L2_CACHE_SIZE, c->cudev);
+        }
+        for (int m = 0; m < QM_MOD_COUNT && !err; m++) {
+            // the images are sm_100a cubins: loading fails on any other device
+            r = d->cuModuleLoadData(&c->modules[m], kImages[m].begin);
+            if (r != CUDA_SUCCESS) {
+                fprintf(stderr, "qmatmul: kernel image %d failed to load on sm_%d%d: %s\n", m, major, minor,
+                        qm_error_string((int32_t)r));
+                err = QM_ERR_NO_KERNEL;
+            }
+        }
+        for (int k = 0; k < QM_K_COUNT && !err; k++) {
+            r = d->cuModuleGetFunction(&c->fn[k], c->modules[kKernels[k].module], kKernels[k].name);
+            if (r != CUDA_SUCCESS) err = QM_ERR_NO_KERNEL;
+        }
+        for (int k = QM_K_GEMV_Q4K_M4; k <= QM_K_GEMV_Q80_M8 && !err; k++) {
+            r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
+            if (r != CUDA_SUCCESS) err = (int32_t)r;
+        }
+        if (!err) {
+            r = d->cuStreamCreate(&c->own_stream, CU_STREAM_NON_BLOCKING);
+            if (r != CUDA_SUCCESS) err = (int32_t)r;
+            c->stream = c->own_stream;
+        }
+        if (!err) {
+            r = d->cuMemAlloc_v2(&c->status_dev, 256);
+            if (r == CUDA_SUCCESS) r = d->cuMemsetD8Async(c->status_dev, 0, 256, c->stream);
+            if (r == CUDA_SUCCESS) r = d->cuMemAlloc_v2(&c->tickets_dev, QM_TICKETS * sizeof(unsigned));
+            if (r == CUDA_SUCCESS) r = d->cuMemsetD8Async(c->tickets_dev, 0, QM_TICKETS * sizeof(unsigned), c->stream);
+            if (r == CUDA_SUCCESS) r = d->cuMemAlloc_v2(&c->partials_dev, QM_PARTIALS_BYTES);
+            if (r == CUDA_SUCCESS) r = d->cuStreamSynchronize(c->stream);
+            if (r != CUDA_SUCCESS) err = (int32_t)r;
+        }
+    }
+    if (err) {
+        qm_destroy(c);
+        return err;
+    }
+    *out = c;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_destroy(qm_ctx *c) {
+    if (!c || c->magic != QM_CTX_MAGIC) return QM_ERR_ARG;
+    QmDriver *d = c->drv;
+    if (c->have_ctx) {
+        CtxGuard g(c);
+        if (g.rc == CUDA_SUCCESS) {
+            if (c->own_stream) d->cuStreamSynchronize(c->own_stream);
+            if (c->status_dev) d->cuMemFree_v2(c->status_dev);
+            if (c->tickets_dev) d->cuMemFree_v2(c->tickets_dev);
+            if (c->partials_dev) d->cuMemFree_v2(c->partials_dev);
+            if (c->xstage_dev) d->cuMemFree_v2(c->xstage_dev);
+            if (c->upload_dev) d->cuMemFree_v2(c->upload_dev);
+            if (c->own_stream) d->cuStreamDestroy_v2(c->own_stream);
+            for (int m = 0; m < QM_MOD_COUNT; m++)
+                if (c->modules[m]) d->cuModuleUnload(c->modules[m]);
+        }
+    }
+    if (c->have_ctx) d->cuDevicePrimaryCtxRelease_v2(c->cudev);
+    c->magic = 0;
+    delete c;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_set_stream(qm_ctx *c, uint64_t s) {
+    CHECK_CTX(c);
+    c->stream = s ? (CUstream)(uintptr_t)s : c->own_stream;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_sync(qm_ctx *c) {
+    CHECK_CTX(c);
+    CtxGuard g(c);
+    DRV(g.rc);
+    DRV(c->drv->cuStreamSynchronize(c->stream));
+    return QM_OK;
+}
+
+extern "C" int32_t qm_last_status(qm_ctx *c, uint32_t *status) {
+    CHECK_CTX(c);
+    if (!status) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    DRV(c->drv->cuStreamSynchronize(c->stream));
+    DRV(c->drv->cuMemcpyDtoH_v2(status, c->status_dev, 4));
+    if (*status) DRV(c->drv->cuMemsetD8Async(c->status_dev, 0, 4, c->stream));
+    return (*status & QM_STATUS_TIMEOUT) ? QM_ERR_TIMEOUT : QM_OK;
+}
+
+extern "C" int64_t qm_launch_count(qm_ctx *c) {
+    if (!c || c->magic != QM_CTX_MAGIC) return -1;
+    return c->launches;
+}
+
+extern "C" int32_t qm_malloc(qm_ctx *c, int64_t bytes, uint64_t *dptr) {
+    CHECK_CTX(c);
+    if (!dptr || bytes < 0) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    CUdeviceptr p = 0;
+    DRV(c->drv->cuMemAlloc_v2(&p, bytes ? (size_t)bytes : 1));
+    *dptr = (uint64_t)p;
+    return QM_OK;
+}
+extern "C" int32_t qm_free(qm_ctx *c, uint64_t dptr) {
+    CHECK_CTX(c);
+    CtxGuard g(c);
+    DRV(g.rc);
+    if (dptr) DRV(c->drv->cuMemFree_v2((CUdeviceptr)dptr));
+    return QM_OK;
+}
+extern "C" int32_t qm_memcpy_h2d(qm_ctx *c, uint64_t dst, const void *src, int64_t bytes) {
+    CHECK_CTX(c);
+    if (bytes < 0 || (bytes && (!dst || !src))) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    if (bytes) {
+        DRV(c->drv->cuMemcpyHtoDAsync_v2((CUdeviceptr)dst, src, (size_t)bytes, c->stream));
+        DRV(c->drv->cuStreamSynchronize(c->stream));
+    }
+    return QM_OK;
+}
+extern "C" int32_t qm_memcpy_d2h(qm_ctx *c, void *dst, uint64_t src, int64_t bytes) {
+    CHECK_CTX(c);
+    if (bytes < 0 || (bytes && (!dst || !src))) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    if (bytes) {
+        DRV(c->drv->cuMemcpyDtoHAsync_v2(dst, (CUdeviceptr)src, (size_t)bytes, c->stream));
+        DRV(c->drv->cuStreamSynchronize(c->stream));
+    }
+    return QM_OK;
+}
+
+// ---- launch helper ----------------------------------------------------------------------
+int32_t qm_launch(qm_ctx *c, int kernel, unsigned gx, unsigned gy, unsigned block, unsigned smem, void *args,
+                  bool pdl) {
+    void *params[1] = {args};
+    CUlaunchConfig cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDimX = gx;
+    cfg.gridDimY = gy;
+    cfg.gridDimZ = 1;
+    cfg.blockDimX = block;
+    cfg.blockDimY = 1;
+    cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = smem;
+    cfg.hStream = c->stream;
+    CUlaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr[0].value.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    DRV(c->drv->cuLaunchKernelEx(&cfg, c->fn[kernel], params, nullptr));
+    c->launches++;
+    return QM_OK;
+}
+
+// ---- weight store -----------------------------------------------------------------------
+static bool fmt_geometry(int32_t fmt, int64_t *block, int64_t *bytes) {
+    switch (fmt) {
+    case QM_FMT_Q4_0: *block = 32; *bytes = 18; return true;
+    case QM_FMT_Q8_0: *block = 32; *bytes = 34; return true;
+    case QM_FMT_Q2_K: *block = 256; *bytes = 84; return true;
+    case QM_FMT_Q4_K: *block = 256; *bytes = 144; return true;
+    }
+    return false;
+}
+
+QmWeight *qm_weight_from_handle(qm_weight h) {
+    QmWeight *w = reinterpret_cast<QmWeight *>((uintptr_t)h);
+    if (!w || w->magic != QM_WEIGHT_MAGIC) return nullptr;
+    return w;
+}
+
+extern "C" int32_t qm_store_create(qm_ctx *c, int32_t fmt, int64_t rows, int64_t cols, qm_weight *out) {
+    CHECK_CTX(c);
+    if (!out) return QM_ERR_ARG;
+    *out = 0;
+    int64_t block, bbytes;
+    if (!fmt_geometry(fmt, &block, &bbytes)) return QM_ERR_FORMAT;
+    if (cols < 0 || cols % block != 0) return QM_ERR_COUNT;  // gguf/gguf.go:290-292
+    if (rows <= 0 || cols <= 0 || rows > (1 << 30) || cols > (1 << 24)) return QM_ERR_SHAPE;
+    QmWeight *w = new (std::nothrow) QmWeight();
+    if (!w) return QM_ERR_NOMEM;
+    w->magic = QM_WEIGHT_MAGIC;
+    w->fmt = fmt;
+    w->rows = rows;
+    w->cols = cols;
+    w->units = (int32_t)((cols + QM_K_UNIT - 1) / QM_K_UNIT);
+    w->gguf_row_bytes = cols / block * bbytes;
+    int64_t qbytes = 0, dbytes = 0;
+    if (fmt == QM_FMT_Q4_K || fmt == QM_FMT_Q2_K) qbytes = rows * w->units * bbytes;
+    if (fmt == QM_FMT_Q4_0) { qbytes = rows * w->units * 8 * 16; dbytes = rows * w->units * 8 * 2; }
+    if (fmt == QM_FMT_Q8_0) { qbytes = rows * w->units * 8 * 32; dbytes = rows * w->units * 8 * 2; }
+    w->qbytes = qbytes;
+    w->dbytes = dbytes;
+    CtxGuard g(c);
+    CUresult r = g.rc;
+    // 64 bytes of slack: rows past the last one are clamped, never read beyond
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&w->wq, (size_t)qbytes + 64);
+    if (r == CUDA_SUCCESS && dbytes) r = c->drv->cuMemAlloc_v2(&w->wd, (size_t)dbytes + 64);
+    // zero-scale padding blocks (Q4_0/Q8_0 rows that end inside a K unit) must read as zero
+    if (r == CUDA_SUCCESS && dbytes) r = c->drv->cuMemsetD8Async(w->wq, 0, (size_t)qbytes + 64, c->stream);
+    if (r == CUDA_SUCCESS && dbytes) r = c->drv->cuMemsetD8Async(w->wd, 0, (size_t)dbytes + 64, c->stream);
+    if (r != CUDA_SUCCESS) {
+        if (w->wq) c->drv->cuMemFree_v2(w->wq);
+        if (w->wd) c->drv->cuMemFree_v2(w->wd);
+        delete w;
+        return (int32_t)r;
+    }
+    *out = (qm_weight)(uintptr_t)w;
+    return QM_OK;
+}
+
+static int32_t store_write_dev(qm_ctx *c, QmWeight *w, int64_t row_offset, int64_t nrows, CUdeviceptr src) {
+    if (w->fmt == QM_FMT_Q4_K || w->fmt == QM_FMT_Q2_K) {
+        DRV(c->drv->cuMemcpyDtoDAsync_v2(w->wq + row_offset * w->gguf_row_bytes, src,
+                                         (size_t)(nrows * w->gguf_row_bytes), c->stream));
+        return QM_OK;
+    }
+    QmRepackArgs a;
+    a.src = (const uint8_t *)(uintptr_t)src;
+    a.wq = (uint8_t *)(uintptr_t)w->wq;
+    a.wd = (uint16_t *)(uintptr_t)w->wd;
+    a.row_offset = row_offset;
+    a.nrows = nrows;
+    a.cols = (int32_t)w->cols;
+    a.units = w->units;
+    const int64_t nblk = nrows * (w->cols / 32);
+    const unsigned grid = (unsigned)std::min<int64_t>((nblk + 255) / 256, 148 * 16);
+    return qm_launch(c, w->fmt == QM_FMT_Q4_0 ? QM_K_REPACK_Q40 : QM_K_REPACK_Q80, grid, 1, 256, 0, &a, false);
+}
+
+extern "C" int32_t qm_store_write_rows_device(qm_ctx *c, qm_weight h, int64_t row_offset, int64_t nrows,
+                                              uint64_t dev_bytes, int64_t len) {
+    CHECK_CTX(c);
+    QmWeight *w = qm_weight_from_handle(h);
+    if (!w || !dev_bytes) return QM_ERR_ARG;
+    if (row_offset < 0 || nrows < 0 || row_offset + nrows > w->rows) return QM_ERR_SHAPE;
+    if (len < nrows * w->gguf_row_bytes) return QM_ERR_BUFFER;
+    if ((dev_bytes & 1) != 0) return QM_ERR_ARG;
+    if (nrows == 0) return QM_OK;
+    CtxGuard g(c);
+    DRV(g.rc);
+    return store_write_dev(c, w, row_offset, nrows, (CUdeviceptr)dev_bytes);
+}
+
+extern "C" int32_t qm_store_write_rows(qm_ctx *c, qm_weight h, int64_t row_offset, int64_t nrows,
+                                       const void *host_bytes, int64_t len) {
+    CHECK_CTX(c);
+    QmWeight *w = qm_weight_from_handle(h);
+    if (!w || !host_bytes) return QM_ERR_ARG;
+    if (row_offset < 0 || nrows < 0 || row_offset + nrows > w->rows) return QM_ERR_SHAPE;
+    if (len < nrows * w->gguf_row_bytes) return QM_ERR_BUFFER;
+    if (nrows == 0) return QM_OK;
+    CtxGuard g(c);
+    DRV(g.rc);
+    const int64_t bytes = nrows * w->gguf_row_bytes;
+    if (w->fmt == QM_FMT_Q4_K || w->fmt == QM_FMT_Q2_K) {
+        // GGUF bytes are the device layout: copy straight into place
+        DRV(c->drv->cuMemcpyHtoDAsync_v2(w->wq + row_offset * w->gguf_row_bytes, host_bytes, (size_t)bytes,
+                                         c->stream));
+        DRV(c->drv->cuStreamSynchronize(c->stream));
+        return QM_OK;
+    }
+    // stage the GGUF bytes on the device, then permute them into the store layout
+    const int64_t chunk_rows = std::max<int64_t>(1, QM_UPLOAD_CHUNK / w->gguf_row_bytes);
+    if (!c->upload_dev) DRV(c->drv->cuMemAlloc_v2(&c->upload_dev, QM_UPLOAD_CHUNK + w->gguf_row_bytes));
+    if (w->gguf_row_bytes > QM_UPLOAD_CHUNK) return QM_ERR_SHAPE;
+    for (int64_t r0 = 0; r0 < nrows; r0 += chunk_rows) {
+        const int64_t nr = std::min(chunk_rows, nrows - r0);
+        DRV(c->drv->cuMemcpyHtoDAsync_v2(c->upload_dev, (const uint8_t *)host_bytes + r0 * w->gguf_row_bytes,
+                                         (size_t)(nr * w->gguf_row_bytes), c->stream));
+        int32_t rc = store_write_dev(c, w, row_offset + r0, nr, c->upload_dev);
+        if (rc) return rc;
+        DRV(c->drv->cuStreamSynchronize(c->stream));  // the staging buffer is reused
+    }
+    return QM_OK;
+}
+
+extern "C" int32_t qm_store_upload(qm_ctx *c, int32_t fmt, int64_t rows, int64_t cols, const void *host_bytes,
+                                   int64_t len, int64_t row_lo, int64_t row_hi, qm_weight *out) {
+    CHECK_CTX(c);
+    if (!out) return QM_ERR_ARG;
+    *out = 0;
+    int64_t block, bbytes;
+    if (!fmt_geometry(fmt, &block, &bbytes)) return QM_ERR_FORMAT;
+    if (rows < 0 || cols < 0 || cols % block != 0) return QM_ERR_COUNT;
+    if (!host_bytes) return QM_ERR_ARG;
+    if (row_lo < 0 || row_hi > rows || row_lo >= row_hi) return QM_ERR_SHAPE;
+    const int64_t row_bytes = cols / block * bbytes;
+    if (len < rows * row_bytes) return QM_ERR_BUFFER;  // trailing bytes are accepted (lm/quant/quant.go:49)
+    qm_weight h = 0;
+    int32_t rc = qm_store_create(c, fmt, row_hi - row_lo, cols, &h);
+    if (rc) return rc;
+    rc = qm_store_write_rows(c, h, 0, row_hi - row_lo, (const uint8_t *)host_bytes + row_lo * row_bytes,
+                             (row_hi - row_lo) * row_bytes);
+    if (rc) {
+        qm_store_free(c, h);
+        return rc;
+    }
+    *out = h;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_store_free(qm_ctx *c, qm_weight h) {
+    CHECK_CTX(c);
+    QmWeight *w = qm_weight_from_handle(h);
+    if (!w) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    c->drv->cuStreamSynchronize(c->stream);
+    if (w->wq) c->drv->cuMemFree_v2(w->wq);
+    if (w->wd) c->drv->cuMemFree_v2(w->wd);
+    w->magic = 0;
+    delete w;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_store_info(qm_ctx *c, qm_weight h, int64_t *info5) {
+    CHECK_CTX(c);
+    QmWeight *w = qm_weight_from_handle(h);
+    if (!w || !info5) return QM_ERR_ARG;
+    info5[0] = w->fmt;
+    info5[1] = w->rows;
+    info5[2] = w->cols;
+    info5[3] = w->qbytes + w->dbytes;
+    info5[4] = w->rows * w->gguf_row_bytes;
+    return QM_OK;
+}
+
+// ---- dequantize ---------------------------------------------------------------------------
+extern "C" int32_t qm_dequantize(qm_ctx *c, qm_weight h, uint64_t out_dev) {
+    CHECK_CTX(c);
+    QmWeight *w = qm_weight_from_handle(h);
+    if (!w || !out_dev || (out_dev & 15)) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    QmDequantArgs a;
+    a.wq = (const uint8_t *)(uintptr_t)w->wq;
+    a.wd = (const uint16_t *)(uintptr_t)w->wd;
+    a.out = (float *)(uintptr_t)out_dev;
+    a.rows = w->rows;
+    a.cols = (int32_t)w->cols;
+    a.units = w->units;
+    int k = w->fmt == QM_FMT_Q4_K ? QM_K_DEQUANT_Q4K : w->fmt == QM_FMT_Q2_K ? QM_K_DEQUANT_Q2K
+          : w->fmt == QM_FMT_Q4_0 ? QM_K_DEQUANT_Q40 : QM_K_DEQUANT_Q80;
+    const int64_t groups = w->rows * (w->cols / 4);
+    const unsigned grid = (unsigned)std::min<int64_t>((groups + 255) / 256, (int64_t)c->sm_count * 32);
+    return qm_launch(c, k, grid, 1, 256, 0, &a, false);
+}
+
+extern "C" int32_t qm_dequantize_host(qm_ctx *c, int32_t fmt, const void *data, int64_t len, int64_t n,
+                                      float *out_host) {
+    CHECK_CTX(c);
+    int64_t block, bbytes;
+    if (!fmt_geometry(fmt, &block, &bbytes)) return QM_ERR_FORMAT;
+    // validation order of lm/quant/quant.go:45-51
+    if (n < 0 || n % block != 0) return QM_ERR_COUNT;
+    if (len < 0 || len < n / block * bbytes) return QM_ERR_BUFFER;
+    if (n == 0) return QM_OK;
+    if (!data || !out_host) return QM_ERR_ARG;
+    // one logical row of n elements, cut into rows of at most 2^20 elements for the store
+    const int64_t row_elems = (n % (1 << 20) == 0) ? (1 << 20) : (n <= (1 << 24) ? n : block);
+    const int64_t rows = n / row_elems;
+    qm_weight h = 0;
+    int32_t rc = qm_store_upload(c, fmt, rows, row_elems, data, len, 0, rows, &h);
+    if (rc) return rc;
+    uint64_t out_dev = 0;
+    rc = qm_malloc(c, n * 4, &out_dev);
+    if (!rc) rc = qm_dequantize(c, h, out_dev);
+    if (!rc) rc = qm_memcpy_d2h(c, out_host, out_dev, n * 4);
+    if (out_dev) qm_free(c, out_dev);
+    qm_store_free(c, h);
+    return rc;
+}
+
+// ---- matvec ---------------------------------------------------------------------------------
+static int env_int(const char *name, int dflt) {
+    const char *s = getenv(name);
+    return (s && *s) ? atoi(s) : dflt;
+}
+
+int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p) {
+    const int planes = 2 * m;
+    const int per_unit = planes * (512 + 16);
+    const int fixed = planes * 64 + 8 * 16 * 8 * 4 + 64;
+    const int budget = env_int("QM_GEMV_SMEM", 72 * 1024);  // three CTAs per SM
+    int max_units = (budget - fixed) / per_unit;
+    if (max_units < 1) max_units = 1;
+    int ksplit = (w->units + max_units - 1) / max_units;
+    const int tiles = (int)((w->rows + 15) / 16);
+    int T = 1;
+    const int target = c->sm_count * 3;
+    while (T < 8 && (tiles + 2 * T - 1) / (2 * T) * ksplit >= target && w->units / ksplit >= 8 / T) T *= 2;
+    T = env_int("QM_GEMV_T", T);
+    ksplit = std::max(ksplit, env_int("QM_GEMV_KSPLIT", 1));
+    if (T != 1 && T != 2 && T != 4 && T != 8) return QM_ERR_ARG;
+    if (ksplit > w->units) ksplit = w->units;
+    if (ksplit > QM_KSPLIT_MAX) return QM_ERR_SHAPE;
+    p->T = T;
+    p->ksplit = ksplit;
+    p->units_per_split = (w->units + ksplit - 1) / ksplit;
+    p->ksplit = (w->units + p->units_per_split - 1) / p->units_per_split;
+    p->grid_x = (tiles + T - 1) / T;
+    p->rows_pad = p->grid_x * T * 16;
+    p->smem = planes * (p->units_per_split * 512 + 64) + p->units_per_split * planes * 16 + 8 * 16 * 8 * 4 + 64;
+    if (p->smem > QM_GEMV_SMEM_MAX) return QM_ERR_SHAPE;
+    if (p->ksplit > 1) {
+        if (p->grid_x > QM_TICKETS) return QM_ERR_SHAPE;
+        if ((int64_t)p->ksplit * 8 * p->rows_pad * 4 > QM_PARTIALS_BYTES) return QM_ERR_SHAPE;
+    }
+    return QM_OK;
+}
+
+int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,
+                         uint64_t y_dev, int64_t ldy, uint32_t flags, CUdeviceptr partials, CUdeviceptr tickets) {
+    if (w->fmt != QM_FMT_Q4_K && w->fmt != QM_FMT_Q4_0 && w->fmt != QM_FMT_Q8_0) return QM_ERR_FORMAT;
+    if (m < 1 || m > 8 || ldx < w->cols || ldy < w->rows) return QM_ERR_SHAPE;
+    const uint32_t xop = flags & 0xFu;
+    if (xop > QM_XOP_SWIGLU) return QM_ERR_ARG;
+    if (!x_dev || !y_dev || (x_dev & 15) || (ldx & 3)) return QM_ERR_ARG;
+    if ((xop == QM_XOP_ADD_RMSNORM || xop == QM_XOP_SWIGLU) && (!x2_dev || (x2_dev & 15))) return QM_ERR_ARG;
+    QmGemvPlan p;
+    int32_t rc = qm_plan_gemv(c, w, m, &p);
+    if (rc) return rc;
+    QmGemvArgs a;
+    memset(&a, 0, sizeof a);
+    a.wq = (const uint8_t *)(uintptr_t)w->wq;
+    a.wd = (const uint16_t *)(uintptr_t)w->wd;
+    a.x = (const float *)(uintptr_t)x_dev;
+    a.x2 = (const float *)(uintptr_t)x2_dev;
+    a.y = (float *)(uintptr_t)y_dev;
+    a.partials = (float *)(uintptr_t)partials;
+    a.tickets = (unsigned int *)(uintptr_t)tickets;
+    a.status = (unsigned int *)(uintptr_t)c->status_dev;
+    a.ldx = ldx;
+    a.ldy = ldy;
+    a.rows = (int32_t)w->rows;
+    a.cols = (int32_t)w->cols;
+    a.units = w->units;
+    a.m = m;
+    a.tiles_per_cta = p.T;
+    a.ksplit = p.ksplit;
+    a.units_per_split = p.units_per_split;
+    a.xop = (int32_t)xop;
+    a.eps = 1e-6f;
+    a.rows_pad = p.rows_pad;
+    const int mode = m <= 4 ? 0 : 1;
+    const int k = (w->fmt == QM_FMT_Q4_K ? QM_K_GEMV_Q4K_M4 : w->fmt == QM_FMT_Q4_0 ? QM_K_GEMV_Q40_M4 : QM_K_GEMV_Q80_M4) + mode;
+    return qm_launch(c, k, (unsigned)p.grid_x, (unsigned)p.ksplit, QM_GEMV_THREADS, (unsigned)p.smem, &a,
+                     (flags & QM_FLAG_PDL) != 0);
+}
+
+extern "C" int32_t qm_matvec(qm_ctx *c, qm_weight h, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,
+                             uint64_t y_dev, int64_t ldy, uint32_t flags) {
+    CHECK_CTX(c);
+    QmWeight *w = qm_weight_from_handle(h);
+    if (!w) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    return qm_matvec_launch(c, w, x_dev, x2_dev, m, ldx, y_dev, ldy, flags, c->partials_dev, c->tickets_dev);
+}
+
+extern "C" int32_t qm_matvec_host(qm_ctx *c, qm_weight h, const float *x_host, int32_t m, int64_t ldx,
+                                  float *y_host, int64_t ldy, uint32_t flags) {
+    CHECK_CTX(c);
+    QmWeight *w = qm_weight_from_handle(h);
+    if (!w || !x_host || !y_host) return QM_ERR_ARG;
+    if (m < 1 || m > 8 || ldx < w->cols || ldy < w->rows) return QM_ERR_SHAPE;
+    if ((flags & 0xFu) > QM_XOP_RMSNORM) return QM_ERR_ARG;  // two-operand transforms need device buffers
+    CtxGuard g(c);
+    DRV(g.rc);
+    // device staging: x as [m][cols4] and y as [m][rows], reused across calls
+    const int64_t cols4 = (w->cols + 3) & ~(int64_t)3;
+    const int64_t need = (m * cols4 + m * w->rows) * 4 + 256;
+    if (need > c->xstage_bytes) {
+        DRV(c->drv->cuStreamSynchronize(c->stream));
+        if (c->xstage_dev) DRV(c->drv->cuMemFree_v2(c->xstage_dev));
+        c->xstage_dev = 0;
+        c->xstage_bytes = 0;
+        DRV(c->drv->cuMemAlloc_v2(&c->xstage_dev, (size_t)need * 2));
+        c->xstage_bytes = need * 2;
+    }
+    const CUdeviceptr xd = c->xstage_dev;
+    const CUdeviceptr yd = c->xstage_dev + (((m * cols4 * 4) + 255) & ~(int64_t)255);
+    for (int j = 0; j < m; j++)
+        DRV(c->drv->cuMemcpyHtoDAsync_v2(xd + j * cols4 * 4, x_host + j * ldx, (size_t)w->cols * 4, c->stream));
+    int32_t rc = qm_matvec_launch(c, w, xd, 0, m, cols4, yd, w->rows, flags, c->partials_dev, c->tickets_dev);
+    if (rc) return rc;
+    for (int j = 0; j < m; j++)
+        DRV(c->drv->cuMemcpyDtoHAsync_v2(y_host + j * ldy, yd + j * w->rows * 4, (size_t)w->rows * 4, c->stream));
+    DRV(c->drv->cuStreamSynchronize(c->stream));
+    return QM_OK;
+}

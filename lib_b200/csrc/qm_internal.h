@@ -1,0 +1,79 @@
+// Internal types of libqmatmul.so shared between its translation units.
+#pragma once
+#include <stdint.h>
+
+#include "../../include/qmatmul.h"
+#include "qm_driver.h"
+#include "qm_kernel_args.h"
+
+#define QM_CTX_MAGIC 0x514D4358u     // "QMCX"
+#define QM_WEIGHT_MAGIC 0x514D5754u  // "QMWT"
+
+enum { QM_MOD_GEMV = 0, QM_MOD_DEQUANT, QM_MOD_COUNT };
+enum {
+    QM_K_GEMV_Q4K_M4 = 0, QM_K_GEMV_Q4K_M8, QM_K_GEMV_Q40_M4, QM_K_GEMV_Q40_M8, QM_K_GEMV_Q80_M4,
+    QM_K_GEMV_Q80_M8, QM_K_DEQUANT_Q4K, QM_K_DEQUANT_Q2K, QM_K_DEQUANT_Q40, QM_K_DEQUANT_Q80,
+    QM_K_REPACK_Q40, QM_K_REPACK_Q80, QM_K_COUNT
+};
+
+#define QM_GEMV_SMEM_MAX (200 * 1024)
+#define QM_TICKETS 65536
+#define QM_KSPLIT_MAX 64
+#define QM_PARTIALS_BYTES (32ll << 20)
+#define QM_UPLOAD_CHUNK (64ll << 20)
+
+struct qm_ctx {
+    uint32_t magic;
+    QmDriver *drv;
+    int device;
+    CUdevice cudev;
+    CUcontext cuctx;
+    bool have_ctx;
+    int sm_count, l2_bytes;
+    CUmodule modules[QM_MOD_COUNT];
+    CUfunction fn[QM_K_COUNT];
+    CUstream own_stream, stream;
+    CUdeviceptr status_dev, tickets_dev, partials_dev;
+    CUdeviceptr xstage_dev;
+    int64_t xstage_bytes;
+    CUdeviceptr upload_dev;
+    int64_t launches;
+};
+
+struct QmWeight {
+    uint32_t magic;
+    int32_t fmt;
+    int64_t rows, cols;
+    int32_t units;
+    int64_t gguf_row_bytes;
+    int64_t qbytes, dbytes;
+    CUdeviceptr wq, wd;
+};
+
+struct QmGemvPlan {
+    int T, ksplit, units_per_split, grid_x, rows_pad, smem;
+};
+
+struct CtxGuard {
+    qm_ctx *ctx;
+    CUresult rc;
+    explicit CtxGuard(qm_ctx *c);
+    ~CtxGuard();
+};
+
+#define DRV(expr)                                       \
+    do {                                                \
+        CUresult _r = (expr);                           \
+        if (_r != CUDA_SUCCESS) return (int32_t)_r;     \
+    } while (0)
+#define CHECK_CTX(c)                                            \
+    do {                                                        \
+        if (!(c) || (c)->magic != QM_CTX_MAGIC) return QM_ERR_ARG; \
+    } while (0)
+
+QmWeight *qm_weight_from_handle(qm_weight h);
+int32_t qm_launch(qm_ctx *c, int kernel, unsigned gx, unsigned gy, unsigned block, unsigned smem, void *args,
+                  bool pdl);
+int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p);
+int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,
+                         uint64_t y_dev, int64_t ldy, uint32_t flags, CUdeviceptr partials, CUdeviceptr tickets);

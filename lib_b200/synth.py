@@ -1,0 +1,51 @@
+"""Seeded synthetic tensors with the shapes and value distributions of the
+benchmark configurations. They stand in for model weights: no model file or
+dataset is read anywhere.
+
+Distributions (all drawn from numpy's Philox generator keyed by `seed`):
+  Q8_0: d = fp16(|N(0,1)|*0.002) per 32 elements, int8 codes uniform [-127,127]
+  Q4_0: d = fp16(|N(0,1)|*0.004), 4-bit codes uniform [0,15]
+  Q4_K: d, dmin = fp16(|N(0,1)|*0.003) per 256 elements, 6-bit scales and mins
+        uniform [0,63], 4-bit codes uniform [0,15]
+Bytes are laid out exactly as a GGUF file stores the tensor (row-major blocks).
+"""
+import numpy as np
+
+Q4_0, Q8_0, Q4_K = 2, 8, 12
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144)}
+
+
+def _rng(seed):
+    return np.random.Generator(np.random.Philox(key=int(seed)))
+
+
+def gguf_bytes(fmt, rows, cols):
+    be, bb = BLOCK[fmt]
+    return rows * (cols // be) * bb
+
+
+def weights(fmt, rows, cols, seed):
+    """GGUF bytes (uint8 array) of a rows x cols tensor of format `fmt`."""
+    be, bb = BLOCK[fmt]
+    assert cols % be == 0
+    nb = rows * (cols // be)
+    g = _rng(seed)
+    out = np.empty((nb, bb), dtype=np.uint8)
+    if fmt == Q8_0:
+        d = (np.abs(g.standard_normal(nb, dtype=np.float32)) * np.float32(0.002)).astype(np.float16)
+        out[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+        out[:, 2:] = g.integers(-127, 128, size=(nb, 32), dtype=np.int8).view(np.uint8)
+    elif fmt == Q4_0:
+        d = (np.abs(g.standard_normal(nb, dtype=np.float32)) * np.float32(0.004)).astype(np.float16)
+        out[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+        out[:, 2:] = g.integers(0, 256, size=(nb, 16), dtype=np.uint8)  # two uniform nibbles per byte
+    else:
+        dd = (np.abs(g.standard_normal((nb, 2), dtype=np.float32)) * np.float32(0.003)).astype(np.float16)
+        out[:, 0:4] = dd.view(np.uint8).reshape(nb, 4)
+        # 12 uniform bytes = eight uniform 6-bit scales and eight uniform 6-bit mins, any packing
+        out[:, 4:] = g.integers(0, 256, size=(nb, 140), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+def activations(m, cols, seed, dtype=np.float32):
+    return _rng(seed).standard_normal((m, cols), dtype=np.float32).astype(dtype)

@@ -9,8 +9,10 @@
 // weights per second, more than the FP32 pipes can convert and multiply one at
 // a time, so the inner product runs on the tensor cores even at one
 // activation row:
-//   * each lane pulls 16-byte pieces of its rows straight from HBM
-//     (ld.global.nc, L1 no-allocate) — 4 lanes per row, 16 rows per warp;
+//   * every warp streams its own (16-row tile, K range) pieces from HBM into a
+//     private shared-memory ring with cp.async.bulk copies that complete on an
+//     mbarrier, so the bytes in flight do not depend on registers or occupancy;
+//     lanes then read 16-byte pieces of their rows (4 lanes per row);
 //   * nibbles/bytes become exact small integers in fp16 with one LOP3/PRMT and
 //     one half2 FMA per pair (magic-number trick: 0x6400|q == 1024+q);
 //     for Q4_K the 6-bit sub-block scale is folded in exactly (sc*q <= 945);
@@ -20,10 +22,13 @@
 //     block/super-block scales are applied in fp32 on the accumulators;
 //   * the Q4_K minimum term sum_j m_j * sum(x in sub-block j) is one extra mma
 //     per super-block against pre-reduced activation sums.
-// 8 warps of a CTA split a K range between them; results meet in shared
-// memory. Long K with many activation rows is split over CTAs as well, with
-// per-split partial sums in global scratch, summed in a fixed order by the
-// last CTA to arrive (deterministic, no floating-point atomics).
+// The grid is one persistent CTA per SM. The (tile, K unit) item space is cut
+// into equal contiguous shares, one per warp of the whole grid, so there is no
+// tail wave and the activations are staged once per CTA. A tile whose K range
+// is shared by several warps (or by several K slices, when the activations of
+// the whole K do not fit in shared memory) is finished through per-segment
+// partial sums in global scratch, added in a fixed order by the last segment
+// to arrive (deterministic, no floating-point atomics).
 #include <cuda_fp16.h>
 #include <stdint.h>
 
@@ -66,13 +71,6 @@ __device__ __forceinline__ float h2f_lo(uint32_t h2) {
 __device__ __forceinline__ float h2f_hi(uint32_t h2) {
     return __half2float(__ushort_as_half((unsigned short)(h2 >> 16)));
 }
-__device__ __forceinline__ uint4 ldg_stream(const void *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
 // D = A(16x16, row) * B(16x8, col) + C, fp16 inputs, fp32 accumulate.
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1, const float (&c)[4]) {
@@ -107,29 +105,72 @@ template <> struct UnitData<QM_FMT_Q8_0> {
     uint4 q[2][4];  // four 2-block groups, word 2*bi+hf = word 4*hf+t of block 2G+bi
 };
 
+// ---- bulk-copy pipeline primitives -------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(1000000u)  // the hardware may park the warp for up to ~1 ms per try
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after about two seconds of SM clock and reports it.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > 4000000000ll) return false;
+    }
+    return true;
+}
+
+// bytes of one row of one K unit in a stage, and the row strides of a stage
+template <int FMT> struct StageGeom;
+template <> struct StageGeom<QM_FMT_Q4_K> {
+    static constexpr int kQ = 144, kD = 0;
+};
+template <> struct StageGeom<QM_FMT_Q4_0> {
+    static constexpr int kQ = 128, kD = 16;
+};
+template <> struct StageGeom<QM_FMT_Q8_0> {
+    static constexpr int kQ = 256, kD = 16;
+};
+
+// One K unit of a lane's two rows, read from a landed stage.
 template <int FMT>
-__device__ __forceinline__ void load_unit(UnitData<FMT> &ud, const QmGemvArgs &a, int64_t rowA,
-                                          int64_t rowB, int u, int t) {
-    const int64_t rows2[2] = {rowA, rowB};
+__device__ __forceinline__ void read_unit(UnitData<FMT> &ud, const uint8_t *stage, int rsq, int rsd, int un,
+                                          int g, int t) {
 #pragma unroll
     for (int rh = 0; rh < 2; rh++) {
+        const uint8_t *row = stage + (g + 8 * rh) * rsq + un * StageGeom<FMT>::kQ;
         if constexpr (FMT == QM_FMT_Q4_K) {
-            const uint8_t *p = a.wq + (rows2[rh] * a.units + u) * 144;
-            ud.hdr[rh] = ldg_stream(p);
-            ud.q[rh][0] = ldg_stream(p + 16 + 32 * t);
-            ud.q[rh][1] = ldg_stream(p + 32 + 32 * t);
-        } else if constexpr (FMT == QM_FMT_Q4_0) {
-            const int64_t blk0 = (rows2[rh] * a.units + u) * 8;
-            ud.d[rh] = ldg_stream(a.wd + blk0);
-            const uint8_t *p = a.wq + blk0 * 16;
-            ud.q[rh][0] = ldg_stream(p + 16 * t);
-            ud.q[rh][1] = ldg_stream(p + 64 + 16 * t);
+            ud.hdr[rh] = *reinterpret_cast<const uint4 *>(row);
+            ud.q[rh][0] = *reinterpret_cast<const uint4 *>(row + 16 + 32 * t);
+            ud.q[rh][1] = *reinterpret_cast<const uint4 *>(row + 32 + 32 * t);
         } else {
-            const int64_t blk0 = (rows2[rh] * a.units + u) * 8;
-            ud.d[rh] = ldg_stream(a.wd + blk0);
-            const uint8_t *p = a.wq + blk0 * 32;
+            ud.d[rh] = *reinterpret_cast<const uint4 *>(stage + 16 * rsq + (g + 8 * rh) * rsd + un * 16);
+            if constexpr (FMT == QM_FMT_Q4_0) {
+                ud.q[rh][0] = *reinterpret_cast<const uint4 *>(row + 16 * t);
+                ud.q[rh][1] = *reinterpret_cast<const uint4 *>(row + 64 + 16 * t);
+            } else {
 #pragma unroll
-            for (int G = 0; G < 4; G++) ud.q[rh][G] = ldg_stream(p + 64 * G + 16 * t);
+                for (int G = 0; G < 4; G++) ud.q[rh][G] = *reinterpret_cast<const uint4 *>(row + 64 * G + 16 * t);
+            }
         }
     }
 }
@@ -275,53 +316,86 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 
 template <int FMT, int MODE>
 __device__ __forceinline__ void gemv_body(const QmGemvArgs &a) {
-    extern __shared__ __align__(16) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int T = a.tiles_per_cta;
-    const int tile = warp % T, kp = warp / T, nkp = (QM_GEMV_THREADS / 32) / T;
-    const int us0 = blockIdx.y * a.units_per_split;
-    const int us1 = min(us0 + a.units_per_split, a.units);
-    const int nun = us1 - us0;
-    // contiguous share of the CTA's K range for this warp
-    const int wu0 = us0 + (int)(((int64_t)nun * kp) / nkp);
-    const int wu1 = us0 + (int)(((int64_t)nun * (kp + 1)) / nkp);
-    const int row0 = (blockIdx.x * T + tile) * QM_GEMV_TILE_ROWS;
-    const int64_t rowA = min(row0 + g, a.rows - 1);
-    const int64_t rowB = min(row0 + g + 8, a.rows - 1);
+    const int C = a.consumers, D = a.depth, KC = a.kc;
+    const int nthreads = C * 32;
 
-    // Activation planes: MODE 0 plane 2j / 2j+1 = hi / lo of activation row j (mma column n);
-    // MODE 1 plane j = hi, plane m+j = lo.
+    // K slice and share of the (tile, unit) item space of this warp
+    const int slice = blockIdx.x / a.ctas_per_slice;
+    const int cta_in_slice = blockIdx.x - slice * a.ctas_per_slice;
+    const int us0 = slice * a.units_per_slice;
+    const int nun = min(a.units_per_slice, a.units - us0);
+    const int64_t Wt = (int64_t)a.ctas_per_slice * C;
+    const int64_t v = (int64_t)cta_in_slice * C + warp;
+    const int64_t I = (int64_t)a.tiles * nun;
+    const int64_t lo = v * I / Wt, hi = (v + 1) * I / Wt;
+
+    // shared memory carve-up (the host computes the same sizes)
     const int NPL = 2 * a.m;
-    const int plane_stride = nun * 512 + 64;
-    uint8_t *xs = smem;                                                                // [NPL][plane_stride]
-    uint32_t *xsum = reinterpret_cast<uint32_t *>(smem + (size_t)NPL * plane_stride);  // [nun][NPL][4]
-    float *red = reinterpret_cast<float *>(xsum + (size_t)nun * NPL * 4);              // [8][16][8]
-    float *s_scale = red + 8 * 16 * 8;                                                 // [8]
-    __shared__ unsigned int s_last;
+    const int plane_stride = a.units_per_slice * 512 + 64;
+    uint8_t *xs = smem;                                                                  // [NPL][plane_stride]
+    uint32_t *xsum = reinterpret_cast<uint32_t *>(smem + (size_t)NPL * plane_stride);    // [ups][NPL][4]
+    float *red = reinterpret_cast<float *>(xsum + (size_t)a.units_per_slice * NPL * 4);  // [32][8]
+    float *s_scale = red + 32 * 8;                                                       // [8]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_scale + 8);                          // [C][D]
+    const int rsq = KC * StageGeom<FMT>::kQ + 16;   // odd multiple of 16 bytes: conflict-free row reads
+    const int rsd = KC * StageGeom<FMT>::kD + 16;
+    const int stage_bytes = (16 * rsq + (StageGeom<FMT>::kD ? 16 * rsd : 0) + 127) & ~127;
+    uint8_t *stages = reinterpret_cast<uint8_t *>(
+        ((uintptr_t)(bars + (size_t)C * D) + 127) & ~(uintptr_t)127);                    // [C][D][stage_bytes]
+    uint8_t *my_stages = stages + (size_t)warp * D * stage_bytes;
+    const uint32_t my_bars = smem_u32(bars + (size_t)warp * D);
 
-    // Weights do not depend on the producer of x: start the first loads before
-    // waiting for it, and let the next kernel in the stream do the same.
     asm volatile("griddepcontrol.launch_dependents;");
-    UnitData<FMT> cur;
-    if (wu0 < wu1) load_unit<FMT>(cur, a, rowA, rowB, wu0, t);
+    if (lane == 0)
+        for (int d = 0; d < D; d++) mbar_init(my_bars + 8 * d, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+
+    // chunk cursors: a chunk is up to KC consecutive K units of one tile
+    int64_t ii = lo;
+    int itile = (int)(lo / nun), iu = (int)(lo - (int64_t)itile * nun), islot = 0;
+    auto issue = [&]() {
+        const int n = (int)min((int64_t)min(KC, nun - iu), hi - ii);
+        const uint32_t bar = my_bars + 8 * islot;
+        const uint32_t dst = smem_u32(my_stages + (size_t)islot * stage_bytes);
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)(16 * n * (StageGeom<FMT>::kQ + StageGeom<FMT>::kD)));
+        __syncwarp();
+        const int r = lane & 15;
+        const int64_t row = min(itile * 16 + r, a.rows - 1);
+        const int64_t unit = row * a.units + us0 + iu;
+        if (lane < 16) {
+            bulk_g2s(dst + r * rsq, a.wq + unit * StageGeom<FMT>::kQ, (uint32_t)(n * StageGeom<FMT>::kQ), bar);
+        } else if (StageGeom<FMT>::kD) {
+            bulk_g2s(dst + 16 * rsq + r * rsd, a.wd + unit * 8, (uint32_t)(n * StageGeom<FMT>::kD), bar);
+        }
+        ii += n;
+        iu += n;
+        if (iu == nun) { iu = 0; itile++; }
+        islot = islot + 1 == D ? 0 : islot + 1;
+    };
+    // Weights do not depend on the producer of x: fill the ring before waiting for it.
+    for (int d = 0; d < D && ii < hi; d++) issue();
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    // ---- stage the activations -------------------------------------------------
+    // ---- stage the activations of this K slice, once per CTA ---------------------------
     const bool norm = (a.xop == 1 || a.xop == 2);
     if (norm) {
         for (int j = 0; j < a.m; j++) {
             float s = 0.f;
             const float *xr = a.x + (int64_t)j * a.ldx;
             const float *x2r = a.x2 ? a.x2 + (int64_t)j * a.ldx : nullptr;
-            for (int c = tid * 4; c < a.cols; c += QM_GEMV_THREADS * 4) {
-                float4 v = *reinterpret_cast<const float4 *>(xr + c);
+            for (int c = tid * 4; c < a.cols; c += nthreads * 4) {
+                float4 v4 = *reinterpret_cast<const float4 *>(xr + c);
                 if (a.xop == 2) {
                     const float4 w = *reinterpret_cast<const float4 *>(x2r + c);
-                    v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+                    v4.x += w.x; v4.y += w.y; v4.z += w.z; v4.w += w.w;
                 }
-                s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s);
-                s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
+                s = fmaf(v4.x, v4.x, s); s = fmaf(v4.y, v4.y, s);
+                s = fmaf(v4.z, v4.z, s); s = fmaf(v4.w, v4.w, s);
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -330,7 +404,7 @@ __device__ __forceinline__ void gemv_body(const QmGemvArgs &a) {
         __syncthreads();
         if (tid < a.m) {
             float s = 0.f;
-            for (int w = 0; w < 8; w++) s += red[w * 8 + tid];
+            for (int w = 0; w < C; w++) s += red[w * 8 + tid];
             s_scale[tid] = rsqrtf(s / (float)a.cols + a.eps);
         }
         __syncthreads();
@@ -338,33 +412,33 @@ __device__ __forceinline__ void gemv_body(const QmGemvArgs &a) {
     {
         const int groups = nun * 64;
         const int total = groups * a.m;
-        for (int idx = tid; idx < total; idx += QM_GEMV_THREADS) {
+        for (int idx = tid; idx < total; idx += nthreads) {
             const int j = idx / groups;
             const int gi = idx - j * groups;
             const int ul = gi >> 6, cg = gi & 63;
             const int col = (us0 + ul) * QM_K_UNIT + cg * 4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
             if (col < a.cols) {
-                v = *reinterpret_cast<const float4 *>(a.x + (int64_t)j * a.ldx + col);
+                v4 = *reinterpret_cast<const float4 *>(a.x + (int64_t)j * a.ldx + col);
                 if (a.xop == 2) {
                     const float4 w = *reinterpret_cast<const float4 *>(a.x2 + (int64_t)j * a.ldx + col);
-                    v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+                    v4.x += w.x; v4.y += w.y; v4.z += w.z; v4.w += w.w;
                 } else if (a.xop == 3) {
                     const float4 w = *reinterpret_cast<const float4 *>(a.x2 + (int64_t)j * a.ldx + col);
-                    v.x = v.x / (1.f + __expf(-v.x)) * w.x;
-                    v.y = v.y / (1.f + __expf(-v.y)) * w.y;
-                    v.z = v.z / (1.f + __expf(-v.z)) * w.z;
-                    v.w = v.w / (1.f + __expf(-v.w)) * w.w;
+                    v4.x = v4.x / (1.f + __expf(-v4.x)) * w.x;
+                    v4.y = v4.y / (1.f + __expf(-v4.y)) * w.y;
+                    v4.z = v4.z / (1.f + __expf(-v4.z)) * w.z;
+                    v4.w = v4.w / (1.f + __expf(-v4.w)) * w.w;
                 }
                 if (norm) {
                     const float sc = s_scale[j];
-                    v.x *= sc; v.y *= sc; v.z *= sc; v.w *= sc;
+                    v4.x *= sc; v4.y *= sc; v4.z *= sc; v4.w *= sc;
                 }
             }
             // fragment order inside a group of four columns: (c0, c2 | c1, c3)
-            const uint32_t hA = pack_h2(v.x, v.z), hB = pack_h2(v.y, v.w);
-            const uint32_t lA = pack_h2(v.x - h2f_lo(hA), v.z - h2f_hi(hA));
-            const uint32_t lB = pack_h2(v.y - h2f_lo(hB), v.w - h2f_hi(hB));
+            const uint32_t hA = pack_h2(v4.x, v4.z), hB = pack_h2(v4.y, v4.w);
+            const uint32_t lA = pack_h2(v4.x - h2f_lo(hA), v4.z - h2f_hi(hA));
+            const uint32_t lB = pack_h2(v4.y - h2f_lo(hB), v4.w - h2f_hi(hB));
             int jp, tt, hs;
             if constexpr (FMT == QM_FMT_Q4_K) {
                 // column bits inside the unit: t(2) | nibble(1) | h(1) | k(2) | e(2)
@@ -379,7 +453,7 @@ __device__ __forceinline__ void gemv_body(const QmGemvArgs &a) {
             *reinterpret_cast<uint2 *>(xs + (size_t)plo * plane_stride + off) = make_uint2(lA, lB);
             if constexpr (FMT == QM_FMT_Q4_K) {
                 // sum of the 32 activations under each sub-block scale
-                float s = (v.x + v.y) + (v.z + v.w);
+                float s = (v4.x + v4.y) + (v4.z + v4.w);
                 s += __shfl_xor_sync(0xffffffffu, s, 1);
                 s += __shfl_xor_sync(0xffffffffu, s, 2);
                 s += __shfl_xor_sync(0xffffffffu, s, 4);
@@ -395,79 +469,118 @@ __device__ __forceinline__ void gemv_body(const QmGemvArgs &a) {
     }
     __syncthreads();
 
-    // ---- main loop over this warp's K units ---------------------------------------
+    // ---- stream this warp's chunks ----------------------------------------------------------
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const bool bact = MODE == 0 ? (g < 2 * a.m) : (g < a.m);
     const uint8_t *plane_hi = xs + (size_t)g * plane_stride;
     const uint8_t *plane_lo = xs + (size_t)(g + a.m) * plane_stride;
-    auto run = [&](const UnitData<FMT> &ud, int u) {
-        const int ul = u - us0;
-        compute_unit<FMT, MODE>(ud, acc, plane_hi, plane_lo, xsum + ((size_t)ul * NPL + g) * 4,
-                                xsum + ((size_t)ul * NPL + g + a.m) * 4, ul, t, bact);
-    };
-    // two register buffers, ping-pong: the next unit's loads are in flight while
-    // the current one is multiplied
-    for (int u = wu0; u < wu1; u += 2) {
-        UnitData<FMT> nxt;
-        const bool has1 = u + 1 < wu1;
-        if (has1) load_unit<FMT>(nxt, a, rowA, rowB, u + 1, t);
-        run(cur, u);
-        if (has1) {
-            if (u + 2 < wu1) load_unit<FMT>(cur, a, rowA, rowB, u + 2, t);
-            run(nxt, u + 1);
-        }
-    }
 
-    // ---- meet the other warps -------------------------------------------------------
-    {
-        float *r = red + (size_t)warp * 128;
-        *reinterpret_cast<float2 *>(r + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
-        *reinterpret_cast<float2 *>(r + (g + 8) * 8 + 2 * t) = make_float2(acc[2], acc[3]);
-    }
-    __syncthreads();
-    const int nout = T * 16 * a.m;
-    const int rbase = blockIdx.x * T * 16;
-    for (int o = tid; o < nout; o += QM_GEMV_THREADS) {
-        const int r = o & 15, tl = (o >> 4) % T, j = (o >> 4) / T;
-        float s = 0.f;
-        for (int p = 0; p < nkp; p++) {
-            const float *rr = red + (size_t)(p * T + tl) * 128 + r * 8;
-            s += MODE == 0 ? (rr[2 * j] + rr[2 * j + 1]) : rr[j];
-        }
-        const int row = rbase + tl * 16 + r;
-        if (a.ksplit == 1) {
-            if (row < a.rows) a.y[(int64_t)j * a.ldy + row] = s;
-        } else {
-            a.partials[((size_t)blockIdx.y * 8 + j) * a.rows_pad + row] = s;
-        }
-    }
-    if (a.ksplit > 1) {
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const unsigned int old = atomicAdd(a.tickets + blockIdx.x, 1u);
-            s_last = (old == (unsigned int)(a.ksplit - 1));
-        }
-        __syncthreads();
-        if (s_last) {
-            __threadfence();
-            for (int o = tid; o < nout; o += QM_GEMV_THREADS) {
-                const int r = o & 15, tl = (o >> 4) % T, j = (o >> 4) / T;
-                const int row = rbase + tl * 16 + r;
-                float s = 0.f;
-                for (int p = 0; p < a.ksplit; p++)
-                    s += __ldcg(a.partials + ((size_t)p * 8 + j) * a.rows_pad + row);
-                if (row < a.rows) a.y[(int64_t)j * a.ldy + row] = s;
+    // Writes the finished sums of one tile. A tile whose K range is shared with other warps
+    // (or other K slices) goes through per-segment partial sums; the last segment to arrive
+    // adds them in a fixed order.
+    auto flush = [&](int tile) {
+        float v0, v1, v2, v3;  // MODE 0: (row g, row g+8) of activation row t; MODE 1: rows x (2t, 2t+1)
+        if (MODE == 0) { v0 = acc[0] + acc[1]; v1 = acc[2] + acc[3]; v2 = v3 = 0.f; }
+        else { v0 = acc[0]; v1 = acc[1]; v2 = acc[2]; v3 = acc[3]; }
+        const int64_t i0 = (int64_t)tile * nun, i1 = i0 + nun - 1;
+        const int64_t vf = ((i0 + 1) * Wt - 1) / I, vl = ((i1 + 1) * Wt - 1) / I;
+        if (a.ksplit == 1 && vf == vl) {
+            const int rA = tile * 16 + g, rB = rA + 8;
+            if (MODE == 0) {
+                if (t < a.m) {
+                    if (rA < a.rows) a.y[(int64_t)t * a.ldy + rA] = v0;
+                    if (rB < a.rows) a.y[(int64_t)t * a.ldy + rB] = v1;
+                }
+            } else {
+                if (2 * t < a.m) {
+                    if (rA < a.rows) a.y[(int64_t)(2 * t) * a.ldy + rA] = v0;
+                    if (rB < a.rows) a.y[(int64_t)(2 * t) * a.ldy + rB] = v2;
+                }
+                if (2 * t + 1 < a.m) {
+                    if (rA < a.rows) a.y[(int64_t)(2 * t + 1) * a.ldy + rA] = v1;
+                    if (rB < a.rows) a.y[(int64_t)(2 * t + 1) * a.ldy + rB] = v3;
+                }
             }
-            if (tid == 0) a.tickets[blockIdx.x] = 0u;  // ready for the next launch
+            return;
         }
+        float *p = a.partials + (((size_t)slice * a.tiles + tile) * a.maxseg + (size_t)(v - vf)) * 128;
+        if (MODE == 0) {
+            if (t < a.m) { p[t * 16 + g] = v0; p[t * 16 + g + 8] = v1; }
+        } else {
+            if (2 * t < a.m) { p[2 * t * 16 + g] = v0; p[2 * t * 16 + g + 8] = v2; }
+            if (2 * t + 1 < a.m) { p[(2 * t + 1) * 16 + g] = v1; p[(2 * t + 1) * 16 + g + 8] = v3; }
+        }
+        // segments of this tile over all K slices
+        unsigned int expected = 0;
+        for (int s = 0; s < a.ksplit; s++) {
+            const int n_s = min(a.units_per_slice, a.units - s * a.units_per_slice);
+            const int64_t I_s = (int64_t)a.tiles * n_s, j0 = (int64_t)tile * n_s, j1 = j0 + n_s - 1;
+            expected += (unsigned int)(((j1 + 1) * Wt - 1) / I_s - ((j0 + 1) * Wt - 1) / I_s + 1);
+        }
+        __threadfence();
+        __syncwarp();
+        unsigned int old = 0;
+        if (lane == 0) old = atomicAdd(a.tickets + tile, 1u);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old != expected - 1) return;
+        __threadfence();
+        for (int o = lane; o < 16 * a.m; o += 32) {
+            const int j = o >> 4, r = o & 15;
+            float s = 0.f;
+            for (int sl = 0; sl < a.ksplit; sl++) {
+                const int n_s = min(a.units_per_slice, a.units - sl * a.units_per_slice);
+                const int64_t I_s = (int64_t)a.tiles * n_s, j0 = (int64_t)tile * n_s, j1 = j0 + n_s - 1;
+                const int nseg = (int)(((j1 + 1) * Wt - 1) / I_s - ((j0 + 1) * Wt - 1) / I_s + 1);
+                const float *q = a.partials + ((size_t)sl * a.tiles + tile) * a.maxseg * 128 + o;
+                for (int sg = 0; sg < nseg; sg++) s += __ldcg(q + (size_t)sg * 128);
+            }
+            if (tile * 16 + r < a.rows) a.y[(int64_t)j * a.ldy + tile * 16 + r] = s;
+        }
+        if (lane == 0) a.tickets[tile] = 0u;  // ready for the next launch
+    };
+
+    int64_t ci = lo;
+    int ctile = (int)(lo / nun), cu = (int)(lo - (int64_t)ctile * nun), cslot = 0;
+    uint32_t phases = 0;  // bit d = parity to wait for on slot d
+    int cur_tile = ctile;
+    bool alive = true;
+    while (ci < hi) {
+        const int n = (int)min((int64_t)min(KC, nun - cu), hi - ci);
+        if (ctile != cur_tile) {
+            flush(cur_tile);
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+            cur_tile = ctile;
+        }
+        if (!mbar_wait_bounded(my_bars + 8 * cslot, (phases >> cslot) & 1u)) {
+            if (lane == 0) atomicOr(a.status, QM_STATUS_TIMEOUT);
+            alive = false;
+            break;
+        }
+        phases ^= 1u << cslot;
+        const uint8_t *stage = my_stages + (size_t)cslot * stage_bytes;
+        for (int un = 0; un < n; un++) {
+            UnitData<FMT> ud;
+            read_unit<FMT>(ud, stage, rsq, rsd, un, g, t);
+            const int ul = cu + un;
+            compute_unit<FMT, MODE>(ud, acc, plane_hi, plane_lo, xsum + ((size_t)ul * NPL + g) * 4,
+                                    xsum + ((size_t)ul * NPL + g + a.m) * 4, ul, t, bact);
+        }
+        ci += n;
+        cu += n;
+        if (cu == nun) { cu = 0; ctile++; }
+        cslot = cslot + 1 == D ? 0 : cslot + 1;
+        // the slot just read is free again: every lane's reads of it have returned (their values
+        // were consumed above), so after the warp converges the next bulk copy may overwrite it
+        __syncwarp();
+        if (ii < hi) issue();
     }
+    if (alive && lo < hi) flush(cur_tile);
 }
 
 }  // namespace
 
 #define QM_GEMV_KERNEL(name, FMT, MODE)                                                         \
-    extern "C" __global__ void __launch_bounds__(QM_GEMV_THREADS, 2)                            \
+    extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)                        \
         name(const __grid_constant__ QmGemvArgs a) {                                            \
         gemv_body<FMT, MODE>(a);                                                                \
     }

@@ -523,34 +523,40 @@ static int env_int(const char *name, int dflt) {
 }
 
 int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p) {
+    // One persistent CTA per SM: `consumers` warps, each streaming its own share of the
+    // (16-row tile, K unit) items through a private ring of `depth` bulk-copy stages of `kc`
+    // units. The activations of the CTA's K slice live in shared memory next to the rings; when
+    // they do not fit, K is cut into slices and groups of CTAs take one slice each.
+    const int q = w->fmt == QM_FMT_Q4_K ? 144 : w->fmt == QM_FMT_Q4_0 ? 128 : 256;
+    const int dq = w->fmt == QM_FMT_Q4_K ? 0 : 16;
+    p->consumers = env_int("QM_GEMV_C", 16);
+    p->depth = env_int("QM_GEMV_D", 2);
+    p->kc = env_int("QM_GEMV_KC", w->fmt == QM_FMT_Q8_0 ? 1 : 2);
+    if (p->consumers < 1 || p->consumers > QM_GEMV_MAX_THREADS / 32 || p->depth < 1 || p->depth > 8 ||
+        p->kc < 1 || p->kc > 8)
+        return QM_ERR_ARG;
+    const int rsq = p->kc * q + 16, rsd = p->kc * dq + 16;
+    const int stage = (16 * rsq + (dq ? 16 * rsd : 0) + 127) & ~127;
+    const int rings = p->consumers * p->depth * stage;
+    const int fixed = 32 * 8 * 4 + 32 + p->consumers * p->depth * 8 + 128 + rings;
     const int planes = 2 * m;
-    const int per_unit = planes * (512 + 16);
-    const int fixed = planes * 64 + 8 * 16 * 8 * 4 + 64;
-    const int budget = env_int("QM_GEMV_SMEM", 72 * 1024);  // three CTAs per SM
-    int max_units = (budget - fixed) / per_unit;
-    if (max_units < 1) max_units = 1;
+    const int room = QM_GEMV_SMEM_MAX - fixed - planes * 64;
+    int max_units = room / (planes * 528);
+    if (max_units < 1) return QM_ERR_SHAPE;
     int ksplit = (w->units + max_units - 1) / max_units;
-    const int tiles = (int)((w->rows + 15) / 16);
-    int T = 1;
-    const int target = c->sm_count * 3;
-    while (T < 8 && (tiles + 2 * T - 1) / (2 * T) * ksplit >= target && w->units / ksplit >= 8 / T) T *= 2;
-    T = env_int("QM_GEMV_T", T);
     ksplit = std::max(ksplit, env_int("QM_GEMV_KSPLIT", 1));
-    if (T != 1 && T != 2 && T != 4 && T != 8) return QM_ERR_ARG;
-    if (ksplit > w->units) ksplit = w->units;
-    if (ksplit > QM_KSPLIT_MAX) return QM_ERR_SHAPE;
-    p->T = T;
-    p->ksplit = ksplit;
-    p->units_per_split = (w->units + ksplit - 1) / ksplit;
-    p->ksplit = (w->units + p->units_per_split - 1) / p->units_per_split;
-    p->grid_x = (tiles + T - 1) / T;
-    p->rows_pad = p->grid_x * T * 16;
-    p->smem = planes * (p->units_per_split * 512 + 64) + p->units_per_split * planes * 16 + 8 * 16 * 8 * 4 + 64;
-    if (p->smem > QM_GEMV_SMEM_MAX) return QM_ERR_SHAPE;
-    if (p->ksplit > 1) {
-        if (p->grid_x > QM_TICKETS) return QM_ERR_SHAPE;
-        if ((int64_t)p->ksplit * 8 * p->rows_pad * 4 > QM_PARTIALS_BYTES) return QM_ERR_SHAPE;
-    }
+    ksplit = std::min(ksplit, (int)w->units);
+    if (ksplit > c->sm_count) return QM_ERR_SHAPE;
+    p->units_per_slice = (w->units + ksplit - 1) / ksplit;
+    p->ksplit = (w->units + p->units_per_slice - 1) / p->units_per_slice;
+    p->ctas_per_slice = std::max(1, env_int("QM_GEMV_CTAS", c->sm_count) / p->ksplit);
+    p->tiles = (int)((w->rows + 15) / 16);
+    const int64_t Wt = (int64_t)p->ctas_per_slice * p->consumers;
+    const int n = p->units_per_slice;
+    p->maxseg = (int)std::min<int64_t>(n, (int64_t)(n - 1) * Wt / ((int64_t)p->tiles * n) + 2);
+    p->smem = planes * (p->units_per_slice * 528 + 64) + fixed;
+    if (p->tiles > QM_TICKETS) return QM_ERR_SHAPE;
+    if ((int64_t)p->ksplit * p->tiles * p->maxseg * 512 > QM_PARTIALS_BYTES) return QM_ERR_SHAPE;
     return QM_OK;
 }
 
@@ -581,16 +587,20 @@ int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t 
     a.cols = (int32_t)w->cols;
     a.units = w->units;
     a.m = m;
-    a.tiles_per_cta = p.T;
+    a.tiles = p.tiles;
     a.ksplit = p.ksplit;
-    a.units_per_split = p.units_per_split;
+    a.units_per_slice = p.units_per_slice;
+    a.ctas_per_slice = p.ctas_per_slice;
+    a.consumers = p.consumers;
+    a.depth = p.depth;
+    a.kc = p.kc;
+    a.maxseg = p.maxseg;
     a.xop = (int32_t)xop;
     a.eps = 1e-6f;
-    a.rows_pad = p.rows_pad;
     const int mode = m <= 4 ? 0 : 1;
     const int k = (w->fmt == QM_FMT_Q4_K ? QM_K_GEMV_Q4K_M4 : w->fmt == QM_FMT_Q4_0 ? QM_K_GEMV_Q40_M4 : QM_K_GEMV_Q80_M4) + mode;
-    return qm_launch(c, k, (unsigned)p.grid_x, (unsigned)p.ksplit, QM_GEMV_THREADS, (unsigned)p.smem, &a,
-                     (flags & QM_FLAG_PDL) != 0);
+    return qm_launch(c, k, (unsigned)(p.ksplit * p.ctas_per_slice), 1, (unsigned)p.consumers * 32, (unsigned)p.smem,
+                     &a, (flags & QM_FLAG_PDL) != 0);
 }
 
 extern "C" int32_t qm_matvec(qm_ctx *c, qm_weight h, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,

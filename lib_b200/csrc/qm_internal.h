@@ -16,10 +16,9 @@ enum {
     QM_K_REPACK_Q40, QM_K_REPACK_Q80, QM_K_COUNT
 };
 
-#define QM_GEMV_SMEM_MAX (200 * 1024)
+#define QM_GEMV_SMEM_MAX (227 * 1024)
 #define QM_TICKETS 65536
-#define QM_KSPLIT_MAX 64
-#define QM_PARTIALS_BYTES (32ll << 20)
+#define QM_PARTIALS_BYTES (64ll << 20)
 #define QM_UPLOAD_CHUNK (64ll << 20)
 
 struct qm_ctx {
@@ -51,7 +50,7 @@ struct QmWeight {
 };
 
 struct QmGemvPlan {
-    int T, ksplit, units_per_split, grid_x, rows_pad, smem;
+    int consumers, depth, kc, ksplit, units_per_slice, ctas_per_slice, tiles, maxseg, smem;
 };
 
 struct CtxGuard {

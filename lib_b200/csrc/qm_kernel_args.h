@@ -7,7 +7,7 @@
 #include <stdint.h>
 
 #define QM_K_UNIT 256          // columns covered by one K unit (one Q4_K super-block)
-#define QM_GEMV_THREADS 256    // 8 warps per CTA
+#define QM_GEMV_MAX_THREADS 512  // up to 16 warps per CTA
 #define QM_GEMV_TILE_ROWS 16   // rows of one mma tile
 #define QM_STATUS_TIMEOUT 1u
 #define QM_STATUS_BOUNDS 2u
@@ -25,19 +25,23 @@ struct QmGemvArgs {
     const float *x;          // activations [m][ldx]
     const float *x2;         // second activation operand or null
     float *y;                // outputs [m][ldy]
-    float *partials;         // split-K scratch [ksplit][m_pad][rows_pad]
-    unsigned int *tickets;   // split-K arrival counters, one per row-tile group, zero between launches
+    float *partials;         // scratch [ksplit][tiles][maxseg][8][16] partial sums
+    unsigned int *tickets;   // scratch [tiles] arrival counters, zero between launches
     unsigned int *status;    // device status word
     int64_t ldx, ldy;
     int32_t rows, cols;      // logical matrix shape (cols = K)
     int32_t units;           // K units per row (cols rounded up / 256)
     int32_t m;               // activation rows, 1..8
-    int32_t tiles_per_cta;   // 1, 2, 4 or 8 row tiles per CTA (8 warps split the rest over K)
-    int32_t ksplit;          // CTAs along K (gridDim.y)
-    int32_t units_per_split; // K units per CTA along K
+    int32_t tiles;           // 16-row tiles: ceil(rows / 16)
+    int32_t ksplit;          // K slices; CTAs [s*ctas_per_slice, (s+1)*ctas_per_slice) own slice s
+    int32_t units_per_slice; // K units per slice (the last slice may be shorter)
+    int32_t ctas_per_slice;
+    int32_t consumers;       // warps per CTA
+    int32_t depth;           // bulk-copy stages per warp
+    int32_t kc;              // K units per stage
+    int32_t maxseg;          // partial-sum slots per (slice, tile)
     int32_t xop;             // QM_XOP_*
     float eps;
-    int32_t rows_pad;        // rows rounded up to 16*tiles_per_cta
 };
 
 struct QmDequantArgs {

@@ -137,6 +137,33 @@ QM_API int32_t qm_matvec(qm_ctx *ctx, qm_weight w, uint64_t x_dev, uint64_t x2_d
 QM_API int32_t qm_matvec_host(qm_ctx *ctx, qm_weight w, const float *x_host, int32_t m, int64_t ldx,
                        float *y_host, int64_t ldy, uint32_t flags);
 
+/* Decode step over a stack of layers whose matrices are stored weights of one
+ * format: per layer q|k|v [hidden+2*kv_dim][hidden], o [hidden][hidden],
+ * gate|up [2*ffn][hidden] and down [hidden][ffn], each matvec reading the RMS
+ * normalised output of its producer (down reads rmsnorm(gate + up)). The
+ * launches are captured once per batch size and replayed as one graph with
+ * programmatic dependent launch. New API of this path (the reference has no
+ * model runner above lm/quant); shapes as in Llama-3-8B: 32 layers, hidden
+ * 4096, kv_dim 1024, ffn 14336. */
+typedef struct qm_stack qm_stack;
+QM_API int32_t qm_stack_create(qm_ctx *ctx, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
+                               int32_t m_max, qm_stack **out);
+QM_API int32_t qm_stack_destroy(qm_ctx *ctx, qm_stack *stack);
+QM_API int32_t qm_stack_set_layer(qm_ctx *ctx, qm_stack *stack, int32_t layer, qm_weight qkv, qm_weight o,
+                                  qm_weight gate_up, qm_weight down);
+/* x_dev [m][ldx] -> h_out_dev [m][ldh] (last down-projection output), asynchronous. */
+QM_API int32_t qm_stack_step(qm_ctx *ctx, qm_stack *stack, uint64_t x_dev, int32_t m, int64_t ldx,
+                             uint64_t h_out_dev, int64_t ldh);
+/* Host buffers: x [m][hidden] in; h [m][hidden] and, if kv_host is not NULL, every layer's k|v
+ * outputs [layers][m][2*kv_dim] out; returns after the stream has drained. */
+QM_API int32_t qm_stack_step_host(qm_ctx *ctx, qm_stack *stack, const float *x_host, int32_t m, float *h_host,
+                                  float *kv_host);
+/* Activation buffers for per-matvec checks: [0] input, [1] q|k|v of every layer, [2] o,
+ * [3] gate|up, [4] down (of the last layer run). */
+QM_API int32_t qm_stack_buffers(qm_ctx *ctx, qm_stack *stack, uint64_t *ptrs5);
+/* 0 = issue the launches one by one instead of replaying the captured graph. */
+QM_API int32_t qm_stack_use_graph(qm_ctx *ctx, qm_stack *stack, int32_t on);
+
 #ifdef __cplusplus
 }
 #endif

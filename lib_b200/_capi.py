@@ -24,7 +24,7 @@ class QmError(RuntimeError):
 def _load():
     if not os.path.exists(_LIB_PATH):
         raise ImportError(
-            "libqmatmul.so is not built (%s); run `python -m lib_b200.build`. There is no "
+            "libqmatmul.so is not built (%s); run `python lib_b200/build.py`. There is no "
             "fallback implementation." % _LIB_PATH)
     L = ctypes.CDLL(_LIB_PATH)
     i32, i64, u32, u64, p = ctypes.c_int32, ctypes.c_int64, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
@@ -51,6 +51,13 @@ def _load():
         "qm_dequantize_host": (i32, [p, i32, p, i64, i64, p]),
         "qm_matvec": (i32, [p, u64, u64, u64, i32, i64, u64, i64, u32]),
         "qm_matvec_host": (i32, [p, u64, p, i32, i64, p, i64, u32]),
+        "qm_stack_create": (i32, [p, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
+        "qm_stack_destroy": (i32, [p, p]),
+        "qm_stack_set_layer": (i32, [p, p, i32, u64, u64, u64, u64]),
+        "qm_stack_step": (i32, [p, p, u64, i32, i64, u64, i64]),
+        "qm_stack_step_host": (i32, [p, p, p, i32, p, p]),
+        "qm_stack_buffers": (i32, [p, p, ctypes.POINTER(u64)]),
+        "qm_stack_use_graph": (i32, [p, p, i32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -182,3 +189,46 @@ class Context:
         _check(lib.qm_matvec_host(self._h, w.handle, x2.ctypes.data, m, x2.shape[1], y.ctypes.data,
                                   y.shape[-1], flags), "matvec")
         return y[0] if (x.ndim == 1 and out is None) else y
+
+
+class Stack:
+    """qm_stack: a decode step over `layers` quantized transformer-shaped layers."""
+
+    def __init__(self, ctx, layers, hidden, kv_dim, ffn, m_max=8):
+        self.ctx, self.layers, self.hidden, self.kv_dim, self.ffn, self.m_max = ctx, layers, hidden, kv_dim, ffn, m_max
+        h = ctypes.c_void_p()
+        _check(lib.qm_stack_create(ctx._h, layers, hidden, kv_dim, ffn, m_max, ctypes.byref(h)), "stack_create")
+        self._h = h
+        self.weights = []
+
+    def set_layer(self, layer, qkv, o, gate_up, down):
+        _check(lib.qm_stack_set_layer(self.ctx._h, self._h, layer, qkv.handle, o.handle, gate_up.handle,
+                                      down.handle), "stack_set_layer")
+        self.weights.append((qkv, o, gate_up, down))
+
+    def use_graph(self, on):
+        _check(lib.qm_stack_use_graph(self.ctx._h, self._h, int(on)))
+
+    def step(self, x_dev, m, ldx, h_out_dev=0, ldh=0):
+        _check(lib.qm_stack_step(self.ctx._h, self._h, x_dev, m, ldx, h_out_dev, ldh), "stack_step")
+
+    def step_host(self, x, want_kv=False, h_out=None, kv_out=None):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        m = x.shape[0]
+        h = h_out if h_out is not None else np.empty((m, self.hidden), dtype=np.float32)
+        kv = kv_out
+        if want_kv and kv is None:
+            kv = np.empty((self.layers, m, 2 * self.kv_dim), dtype=np.float32)
+        _check(lib.qm_stack_step_host(self.ctx._h, self._h, x.ctypes.data, m, h.ctypes.data,
+                                      kv.ctypes.data if kv is not None else None), "stack_step_host")
+        return (h, kv) if want_kv else h
+
+    def buffers(self):
+        ptrs = (ctypes.c_uint64 * 5)()
+        _check(lib.qm_stack_buffers(self.ctx._h, self._h, ptrs))
+        return [int(v) for v in ptrs]
+
+    def close(self):
+        if self._h:
+            lib.qm_stack_destroy(self.ctx._h, self._h)
+            self._h = None

@@ -1,6 +1,6 @@
 """Builds the sm_100a cubins, libqmatmul.so and the kernel descriptions.
 
-Usage: python -m lib_b200.build [--force]
+Usage: python lib_b200/build.py [--force]
 nvcc cross-compiles for sm_100a, so this runs on a machine without a GPU.
 Outputs (all git-ignored, all next to the sources they come from):
   lib_b200/csrc/build/<name>.sm_100a.cubin   one per .cu file
@@ -20,7 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libqmatmul.so")
 KERNEL_SOURCES = ["qm_gemv.cu", "qm_dequant.cu"]
-HOST_SOURCES = ["qm_host.cpp"]
+HOST_SOURCES = ["qm_host.cpp", "qm_stack.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -327,10 +327,13 @@ __device__ __forceinline__ void gemv_body(const QmGemvArgs &a) {
     const int cta_in_slice = blockIdx.x - slice * a.ctas_per_slice;
     const int us0 = slice * a.units_per_slice;
     const int nun = min(a.units_per_slice, a.units - us0);
-    const int64_t Wt = (int64_t)a.ctas_per_slice * C;
-    const int64_t v = (int64_t)cta_in_slice * C + warp;
+    // Warps are numbered warp-major over the CTAs of the slice, so that when there are fewer
+    // items than warps the busy warps spread over all SMs; surplus warps stay idle. Every busy
+    // warp owns at least one item, so a tile's segments are exactly the warps vf..vl below.
     const int64_t I = (int64_t)a.tiles * nun;
-    const int64_t lo = v * I / Wt, hi = (v + 1) * I / Wt;
+    const int64_t Wt = min((int64_t)a.ctas_per_slice * C, I);
+    const int64_t v = (int64_t)warp * a.ctas_per_slice + cta_in_slice;
+    const int64_t lo = v < Wt ? v * I / Wt : 0, hi = v < Wt ? (v + 1) * I / Wt : 0;
 
     // shared memory carve-up (the host computes the same sizes)
     const int NPL = 2 * a.m;
@@ -515,7 +518,8 @@ __device__ __forceinline__ void gemv_body(const QmGemvArgs &a) {
         for (int s = 0; s < a.ksplit; s++) {
             const int n_s = min(a.units_per_slice, a.units - s * a.units_per_slice);
             const int64_t I_s = (int64_t)a.tiles * n_s, j0 = (int64_t)tile * n_s, j1 = j0 + n_s - 1;
-            expected += (unsigned int)(((j1 + 1) * Wt - 1) / I_s - ((j0 + 1) * Wt - 1) / I_s + 1);
+            const int64_t W_s = min((int64_t)a.ctas_per_slice * C, I_s);
+            expected += (unsigned int)(((j1 + 1) * W_s - 1) / I_s - ((j0 + 1) * W_s - 1) / I_s + 1);
         }
         __threadfence();
         __syncwarp();
@@ -530,7 +534,8 @@ __device__ __forceinline__ void gemv_body(const QmGemvArgs &a) {
             for (int sl = 0; sl < a.ksplit; sl++) {
                 const int n_s = min(a.units_per_slice, a.units - sl * a.units_per_slice);
                 const int64_t I_s = (int64_t)a.tiles * n_s, j0 = (int64_t)tile * n_s, j1 = j0 + n_s - 1;
-                const int nseg = (int)(((j1 + 1) * Wt - 1) / I_s - ((j0 + 1) * Wt - 1) / I_s + 1);
+                const int64_t W_s = min((int64_t)a.ctas_per_slice * C, I_s);
+                const int nseg = (int)(((j1 + 1) * W_s - 1) / I_s - ((j0 + 1) * W_s - 1) / I_s + 1);
                 const float *q = a.partials + ((size_t)sl * a.tiles + tile) * a.maxseg * 128 + o;
                 for (int sg = 0; sg < nseg; sg++) s += __ldcg(q + (size_t)sg * 128);
             }

@@ -551,8 +551,8 @@ int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p) {
     p->ksplit = (w->units + p->units_per_slice - 1) / p->units_per_slice;
     p->ctas_per_slice = std::max(1, env_int("QM_GEMV_CTAS", c->sm_count) / p->ksplit);
     p->tiles = (int)((w->rows + 15) / 16);
-    const int64_t Wt = (int64_t)p->ctas_per_slice * p->consumers;
     const int n = p->units_per_slice;
+    const int64_t Wt = std::min<int64_t>((int64_t)p->ctas_per_slice * p->consumers, (int64_t)p->tiles * n);
     p->maxseg = (int)std::min<int64_t>(n, (int64_t)(n - 1) * Wt / ((int64_t)p->tiles * n) + 2);
     p->smem = planes * (p->units_per_slice * 528 + 64) + fixed;
     if (p->tiles > QM_TICKETS) return QM_ERR_SHAPE;

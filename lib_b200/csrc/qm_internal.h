@@ -70,6 +70,7 @@ struct CtxGuard {
         if (!(c) || (c)->magic != QM_CTX_MAGIC) return QM_ERR_ARG; \
     } while (0)
 
+struct qm_stack;
 QmWeight *qm_weight_from_handle(qm_weight h);
 int32_t qm_launch(qm_ctx *c, int kernel, unsigned gx, unsigned gy, unsigned block, unsigned smem, void *args,
                   bool pdl);

@@ -1,0 +1,218 @@
+// qm_stack.cpp — a decode step over a stack of transformer-shaped layers whose
+// matrices are all block-quantized: per layer q|k|v, o, gate|up and down
+// matvecs, RMS normalisation fused into each consumer's activation staging.
+// The 4*layers launches are captured once per batch size into a CUDA graph with
+// programmatic dependent launch, the capture/replay path the reference exposes
+// as Stream.BeginCapture / Graph.Instantiate / GraphExec.Launch
+// (nvidia/driver/stream.gen.go:115, graph.gen.go:651, graph_exec.gen.go:354).
+#include <string.h>
+
+#include <new>
+#include <vector>
+
+#include "qm_internal.h"
+
+#define QM_STACK_MAGIC 0x514D534Bu  // "QMSK"
+
+struct QmLayer {
+    QmWeight *qkv, *o, *gu, *dn;
+};
+
+struct qm_stack {
+    uint32_t magic;
+    int layers, hidden, kv, ffn, m_max;
+    std::vector<QmLayer> layer;
+    CUdeviceptr h0, qkv_out, o_out, gu_out, dn_out;  // activations
+    CUgraphExec graph[9];
+    bool use_graph;
+};
+
+static qm_stack *stack_check(qm_stack *s) { return (s && s->magic == QM_STACK_MAGIC) ? s : nullptr; }
+
+extern "C" int32_t qm_stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
+                                   int32_t m_max, qm_stack **out) {
+    CHECK_CTX(c);
+    if (!out) return QM_ERR_ARG;
+    *out = nullptr;
+    if (layers < 1 || layers > 1024 || hidden < 32 || kv_dim < 0 || ffn < 32 || m_max < 1 || m_max > 8)
+        return QM_ERR_SHAPE;
+    if ((hidden & 3) || (kv_dim & 3) || (ffn & 3)) return QM_ERR_SHAPE;
+    qm_stack *s = new (std::nothrow) qm_stack();
+    if (!s) return QM_ERR_NOMEM;
+    s->magic = QM_STACK_MAGIC;
+    s->layers = layers;
+    s->hidden = hidden;
+    s->kv = kv_dim;
+    s->ffn = ffn;
+    s->m_max = m_max;
+    s->layer.resize(layers);
+    memset(s->layer.data(), 0, sizeof(QmLayer) * layers);
+    memset(s->graph, 0, sizeof s->graph);
+    s->use_graph = true;
+    CtxGuard g(c);
+    CUresult r = g.rc;
+    const size_t f = 4;
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->h0, (size_t)m_max * hidden * f);
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->qkv_out, (size_t)layers * m_max * (hidden + 2 * kv_dim) * f);
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->o_out, (size_t)m_max * hidden * f);
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->gu_out, (size_t)m_max * 2 * ffn * f);
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->dn_out, (size_t)m_max * hidden * f);
+    if (r != CUDA_SUCCESS) {
+        qm_stack_destroy(c, s);
+        return (int32_t)r;
+    }
+    *out = s;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_stack_destroy(qm_ctx *c, qm_stack *s) {
+    CHECK_CTX(c);
+    if (!stack_check(s)) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    c->drv->cuStreamSynchronize(c->stream);
+    for (int i = 0; i < 9; i++)
+        if (s->graph[i]) c->drv->cuGraphExecDestroy(s->graph[i]);
+    CUdeviceptr bufs[5] = {s->h0, s->qkv_out, s->o_out, s->gu_out, s->dn_out};
+    for (CUdeviceptr b : bufs)
+        if (b) c->drv->cuMemFree_v2(b);
+    s->magic = 0;
+    delete s;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_stack_set_layer(qm_ctx *c, qm_stack *s, int32_t layer, qm_weight qkv, qm_weight o,
+                                      qm_weight gate_up, qm_weight down) {
+    CHECK_CTX(c);
+    if (!stack_check(s) || layer < 0 || layer >= s->layers) return QM_ERR_ARG;
+    QmWeight *w[4] = {qm_weight_from_handle(qkv), qm_weight_from_handle(o), qm_weight_from_handle(gate_up),
+                      qm_weight_from_handle(down)};
+    for (QmWeight *p : w)
+        if (!p) return QM_ERR_ARG;
+    const int64_t want[4][2] = {{s->hidden + 2 * s->kv, s->hidden}, {s->hidden, s->hidden},
+                                {2 * s->ffn, s->hidden}, {s->hidden, s->ffn}};
+    for (int i = 0; i < 4; i++)
+        if (w[i]->rows != want[i][0] || w[i]->cols != want[i][1]) return QM_ERR_SHAPE;
+    s->layer[layer] = QmLayer{w[0], w[1], w[2], w[3]};
+    for (int i = 0; i < 9; i++)
+        if (s->graph[i]) {
+            CtxGuard g(c);
+            c->drv->cuGraphExecDestroy(s->graph[i]);
+            s->graph[i] = nullptr;
+        }
+    return QM_OK;
+}
+
+// Device pointers of the activation buffers, for per-matvec checks:
+// [0]=h0 [m][hidden], [1]=qkv_out [layers][m][hidden+2kv], [2]=o_out [m][hidden],
+// [3]=gu_out [m][2*ffn], [4]=dn_out [m][hidden] (rows are packed for the m of the last step).
+extern "C" int32_t qm_stack_buffers(qm_ctx *c, qm_stack *s, uint64_t *ptrs5) {
+    CHECK_CTX(c);
+    if (!stack_check(s) || !ptrs5) return QM_ERR_ARG;
+    ptrs5[0] = s->h0;
+    ptrs5[1] = s->qkv_out;
+    ptrs5[2] = s->o_out;
+    ptrs5[3] = s->gu_out;
+    ptrs5[4] = s->dn_out;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_stack_use_graph(qm_ctx *c, qm_stack *s, int32_t on) {
+    CHECK_CTX(c);
+    if (!stack_check(s)) return QM_ERR_ARG;
+    s->use_graph = on != 0;
+    return QM_OK;
+}
+
+// The launches of one step for batch m, in stream order.
+static int32_t enqueue_layers(qm_ctx *c, qm_stack *s, int m, int upto_layers) {
+    const int64_t qkv_ld = s->hidden + 2 * s->kv;
+    const uint32_t F = QM_FLAG_PDL;
+    for (int L = 0; L < upto_layers; L++) {
+        const QmLayer &ly = s->layer[L];
+        if (!ly.qkv) return QM_ERR_STATE;
+        const CUdeviceptr qkv = s->qkv_out + (size_t)L * m * qkv_ld * 4;
+        int32_t rc = qm_matvec_launch(c, ly.qkv, L == 0 ? s->h0 : s->dn_out, 0, m, s->hidden, qkv, qkv_ld,
+                                      QM_XOP_RMSNORM | F, c->partials_dev, c->tickets_dev);
+        if (!rc) rc = qm_matvec_launch(c, ly.o, qkv, 0, m, qkv_ld, s->o_out, s->hidden, QM_XOP_RMSNORM | F,
+                                       c->partials_dev, c->tickets_dev);
+        if (!rc) rc = qm_matvec_launch(c, ly.gu, s->o_out, 0, m, s->hidden, s->gu_out, 2 * s->ffn,
+                                       QM_XOP_RMSNORM | F, c->partials_dev, c->tickets_dev);
+        if (!rc) rc = qm_matvec_launch(c, ly.dn, s->gu_out, s->gu_out + (size_t)s->ffn * 4, m, 2 * s->ffn,
+                                       s->dn_out, s->hidden, QM_XOP_ADD_RMSNORM | F, c->partials_dev,
+                                       c->tickets_dev);
+        if (rc) return rc;
+    }
+    return QM_OK;
+}
+
+static int32_t step_device(qm_ctx *c, qm_stack *s, int m) {
+    if (!s->use_graph) return enqueue_layers(c, s, m, s->layers);
+    if (!s->graph[m]) {
+        QmDriver *d = c->drv;
+        DRV(d->cuStreamBeginCapture_v2(c->stream, CU_STREAM_CAPTURE_MODE_THREAD_LOCAL));
+        const int64_t before = c->launches;
+        int32_t rc = enqueue_layers(c, s, m, s->layers);
+        c->launches = before;  // captured, not launched
+        CUgraph graph = nullptr;
+        CUresult r = d->cuStreamEndCapture(c->stream, &graph);
+        if (rc) {
+            if (graph) d->cuGraphDestroy(graph);
+            return rc;
+        }
+        DRV(r);
+        r = d->cuGraphInstantiateWithFlags(&s->graph[m], graph, 0);
+        d->cuGraphDestroy(graph);
+        DRV(r);
+    }
+    DRV(c->drv->cuGraphLaunch(s->graph[m], c->stream));
+    c->launches += 4 * (int64_t)s->layers;
+    return QM_OK;
+}
+
+// x_dev [m][ldx] float32 -> h_out_dev [m][ldh] float32 (the last layer's down-projection
+// output). Asynchronous on the context's stream.
+extern "C" int32_t qm_stack_step(qm_ctx *c, qm_stack *s, uint64_t x_dev, int32_t m, int64_t ldx,
+                                 uint64_t h_out_dev, int64_t ldh) {
+    CHECK_CTX(c);
+    if (!stack_check(s) || !x_dev) return QM_ERR_ARG;
+    if (m < 1 || m > s->m_max || ldx < s->hidden || (h_out_dev && ldh < s->hidden)) return QM_ERR_SHAPE;
+    CtxGuard g(c);
+    DRV(g.rc);
+    for (int j = 0; j < m; j++)
+        DRV(c->drv->cuMemcpyDtoDAsync_v2(s->h0 + (size_t)j * s->hidden * 4, x_dev + (size_t)j * ldx * 4,
+                                         (size_t)s->hidden * 4, c->stream));
+    int32_t rc = step_device(c, s, m);
+    if (rc) return rc;
+    if (h_out_dev)
+        for (int j = 0; j < m; j++)
+            DRV(c->drv->cuMemcpyDtoDAsync_v2(h_out_dev + (size_t)j * ldh * 4, s->dn_out + (size_t)j * s->hidden * 4,
+                                             (size_t)s->hidden * 4, c->stream));
+    return QM_OK;
+}
+
+// Host-buffer form: copies x in, runs the step, copies h [m][hidden] and (when kv_host is not
+// null) every layer's k|v rows [layers][m][2*kv] back, and synchronizes.
+extern "C" int32_t qm_stack_step_host(qm_ctx *c, qm_stack *s, const float *x_host, int32_t m, float *h_host,
+                                      float *kv_host) {
+    CHECK_CTX(c);
+    if (!stack_check(s) || !x_host || !h_host) return QM_ERR_ARG;
+    if (m < 1 || m > s->m_max) return QM_ERR_SHAPE;
+    CtxGuard g(c);
+    DRV(g.rc);
+    QmDriver *d = c->drv;
+    DRV(d->cuMemcpyHtoDAsync_v2(s->h0, x_host, (size_t)m * s->hidden * 4, c->stream));
+    int32_t rc = step_device(c, s, m);
+    if (rc) return rc;
+    DRV(d->cuMemcpyDtoHAsync_v2(h_host, s->dn_out, (size_t)m * s->hidden * 4, c->stream));
+    if (kv_host && s->kv) {
+        const int64_t qkv_ld = s->hidden + 2 * s->kv;
+        for (int L = 0; L < s->layers; L++)
+            for (int j = 0; j < m; j++)
+                DRV(d->cuMemcpyDtoHAsync_v2(kv_host + ((size_t)L * m + j) * 2 * s->kv,
+                                            s->qkv_out + (((size_t)L * m + j) * qkv_ld + s->hidden) * 4,
+                                            (size_t)2 * s->kv * 4, c->stream));
+    }
+    DRV(d->cuStreamSynchronize(c->stream));
+    return QM_OK;
+}

@@ -24,26 +24,33 @@ def gguf_bytes(fmt, rows, cols):
     return rows * (cols // be) * bb
 
 
+def _random_bytes(g, shape):
+    n = int(np.prod(shape))
+    raw = g.bit_generator.random_raw((n + 7) // 8)  # uniform 64-bit words -> uniform bytes
+    return raw.view(np.uint8)[:n].reshape(shape)
+
+
 def weights(fmt, rows, cols, seed):
     """GGUF bytes (uint8 array) of a rows x cols tensor of format `fmt`."""
     be, bb = BLOCK[fmt]
     assert cols % be == 0
     nb = rows * (cols // be)
     g = _rng(seed)
-    out = np.empty((nb, bb), dtype=np.uint8)
+    # uniform bytes: uniform nibbles (4-bit codes), uniform 6-bit scale/min fields in any packing
+    out = _random_bytes(g, (nb, bb)).copy()
     if fmt == Q8_0:
-        d = (np.abs(g.standard_normal(nb, dtype=np.float32)) * np.float32(0.002)).astype(np.float16)
-        out[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
-        out[:, 2:] = g.integers(-127, 128, size=(nb, 32), dtype=np.int8).view(np.uint8)
+        # int8 codes uniform in [-127, 127]: redraw the (rare) -128 patterns
+        q = out[:, 2:]
+        bad = q == 0x80
+        q[bad] = g.integers(-127, 128, size=int(bad.sum()), dtype=np.int8).view(np.uint8)
+        scale = 0.002
     elif fmt == Q4_0:
-        d = (np.abs(g.standard_normal(nb, dtype=np.float32)) * np.float32(0.004)).astype(np.float16)
-        out[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
-        out[:, 2:] = g.integers(0, 256, size=(nb, 16), dtype=np.uint8)  # two uniform nibbles per byte
+        scale = 0.004
     else:
-        dd = (np.abs(g.standard_normal((nb, 2), dtype=np.float32)) * np.float32(0.003)).astype(np.float16)
-        out[:, 0:4] = dd.view(np.uint8).reshape(nb, 4)
-        # 12 uniform bytes = eight uniform 6-bit scales and eight uniform 6-bit mins, any packing
-        out[:, 4:] = g.integers(0, 256, size=(nb, 140), dtype=np.uint8)
+        scale = 0.003
+    nd = 1 if fmt != Q4_K else 2
+    d = (np.abs(g.standard_normal((nb, nd), dtype=np.float32)) * np.float32(scale)).astype(np.float16)
+    out[:, 0:2 * nd] = d.view(np.uint8).reshape(nb, 2 * nd)
     return out.reshape(-1)
 
 

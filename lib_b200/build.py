@@ -19,7 +19,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libqmatmul.so")
-KERNEL_SOURCES = ["qm_gemv.cu", "qm_dequant.cu"]
+KERNEL_SOURCES = ["qm_gemv.cu", "qm_dequant.cu", "qm_gemv_q4k.cu"]
 HOST_SOURCES = ["qm_host.cpp", "qm_stack.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -62,7 +62,7 @@ def _describe(src, cubin, ptxas_log):
 
 def build(force=False, verbose=False):
     os.makedirs(OUT, exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".h")]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(HERE, "..", "include", "qmatmul.h"))
     cubins = []
     for name in KERNEL_SOURCES:

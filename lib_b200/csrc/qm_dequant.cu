@@ -41,7 +41,8 @@ __device__ __forceinline__ float4 scale4(uint32_t bytes4, float t1, float t3) {
 
 }  // namespace
 
-// One thread per four consecutive output columns.
+// Q4_K store layout: item (tile, unit) = 16 headers of 16 bytes, then for each 32-byte quant
+// group p the 16 rows side by side. One thread per four consecutive output columns.
 extern "C" __global__ void __launch_bounds__(256) qm_dequant_q4k(const __grid_constant__ QmDequantArgs a) {
     const int64_t ngroups = a.rows * (int64_t)(a.cols / 4);
     for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < ngroups;
@@ -49,7 +50,9 @@ extern "C" __global__ void __launch_bounds__(256) qm_dequant_q4k(const __grid_co
         const int64_t row = idx / (a.cols / 4);
         const int col = (int)(idx - row * (a.cols / 4)) * 4;
         const int u = col >> 8, e = col & 255, j = e >> 5, i = e & 31;
-        const uint8_t *blk = a.wq + (row * a.units + u) * 144;
+        const int r = (int)(row & 15);
+        const uint8_t *item = a.wq + ((row >> 4) * a.units + u) * QM_Q4K_ITEM_BYTES;
+        const uint8_t *blk = item + 16 * r;
         const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk);
         const float d = f16_bits_to_f32(dd & 0xFFFFu), dmin = f16_bits_to_f32(dd >> 16);
         const uint8_t *S = blk + 4;
@@ -61,10 +64,31 @@ extern "C" __global__ void __launch_bounds__(256) qm_dequant_q4k(const __grid_co
             sc = (S[j + 4] & 0x0F) | ((S[j - 4] >> 6) << 4);
             m = (S[j + 4] >> 4) | ((S[j] >> 6) << 4);
         }
-        uint32_t q4 = *reinterpret_cast<const uint32_t *>(blk + 16 + 32 * (j >> 1) + i);
+        uint32_t q4 = *reinterpret_cast<const uint32_t *>(item + 256 + 512 * (j >> 1) + 32 * r + i);
         q4 = (j & 1) ? ((q4 >> 4) & 0x0F0F0F0Fu) : (q4 & 0x0F0F0F0Fu);
         const float t1 = __fmul_rn(d, (float)sc), t3 = __fmul_rn(dmin, (float)m);
         *reinterpret_cast<float4 *>(a.out + row * a.cols + col) = scale4(q4, t1, t3);
+    }
+}
+
+// GGUF Q4_K rows (144-byte super-blocks) -> store layout. One thread per super-block.
+extern "C" __global__ void __launch_bounds__(256) qm_repack_q4k(const __grid_constant__ QmRepackArgs a) {
+    const int nblk = a.cols / 256;
+    const int64_t total = a.nrows * nblk;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t rr = idx / nblk;
+        const int u = (int)(idx - rr * nblk);
+        const int64_t row = a.row_offset + rr;
+        const uint4 *s = reinterpret_cast<const uint4 *>(a.src + idx * 144);
+        uint8_t *item = a.wq + ((row >> 4) * a.units + u) * QM_Q4K_ITEM_BYTES;
+        const int r = (int)(row & 15);
+        *reinterpret_cast<uint4 *>(item + 16 * r) = s[0];
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            *reinterpret_cast<uint4 *>(item + 256 + 512 * p + 32 * r) = s[1 + 2 * p];
+            *reinterpret_cast<uint4 *>(item + 256 + 512 * p + 32 * r + 16) = s[2 + 2 * p];
+        }
     }
 }
 

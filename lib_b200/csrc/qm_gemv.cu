@@ -590,8 +590,6 @@ __device__ __forceinline__ void gemv_body(const QmGemvArgs &a) {
         gemv_body<FMT, MODE>(a);                                                                \
     }
 
-QM_GEMV_KERNEL(qm_gemv_q4k_m4, QM_FMT_Q4_K, 0)
-QM_GEMV_KERNEL(qm_gemv_q4k_m8, QM_FMT_Q4_K, 1)
 QM_GEMV_KERNEL(qm_gemv_q40_m4, QM_FMT_Q4_0, 0)
 QM_GEMV_KERNEL(qm_gemv_q40_m8, QM_FMT_Q4_0, 1)
 QM_GEMV_KERNEL(qm_gemv_q80_m4, QM_FMT_Q8_0, 0)

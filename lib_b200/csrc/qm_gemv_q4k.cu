@@ -1,0 +1,515 @@
+// qm_gemv_q4k.cu — decode GEMV (1..8 activation rows) over Q4_K weights for
+// sm_100a on the integer tensor-core path, one matvec or a fused sequence of
+// dependent matvecs (a whole decode step) in a single persistent launch.
+//
+// Supersedes the reference's one-warp-per-row k-quant matvec
+// (nvidia/x/egraph/codegen.go:674-735) and its persistent task kernel idea
+// (nvidia/x/cudamega/mega.go:36-71).
+//
+// Arithmetic. Q4_K stores value = d*sc_j*q - dmin*m_j with 4-bit q and 6-bit
+// integers sc_j, m_j per 32-element sub-block. At HBM rate a B200 delivers
+// ~11.6e12 such weights per second, so every instruction per weight counts:
+//   * activations are quantized once per CTA into signed 8-bit limbs per
+//     256-column unit: x = sx * (h + l1/128 [+ l2/16384]), sx = max|x|/127
+//     (three limbs = 21 bits for up to 2 activation rows, two limbs beyond);
+//   * four 4-bit codes become four u8 mma operands with ONE and-mask (low
+//     nibbles) or one and-mask that leaves them multiplied by 16 (high
+//     nibbles); mma.sync.m16n8k32.s32.u8.s8 (A = weights, B = limbs, one limb
+//     per column) gives exact integer sub-block sums;
+//   * the 6-bit sub-block scale multiplies the exact sums in integer
+//     (one IMAD per accumulator); d, sx and the limb weight are applied once
+//     per 256-column unit in fp32;
+//   * the minimum term sum_j m_j * sum(x in sub-block j) is one fp16 mma per
+//     unit against pre-reduced activation sums (fp16 hi+lo).
+// Everything up to the per-unit fp32 scaling is exact integer arithmetic.
+//
+// Data movement. One persistent CTA per SM; every warp streams its share of the
+// (16-row tile, K unit) items of an op through a private ring of shared-memory
+// stages filled by 16-byte cp.async copies (one commit group per stage), so the
+// bytes in flight are bounded by shared memory, not by registers.
+// Weights never depend on activations, so the rings run ahead across op
+// boundaries: while the CTAs meet at the grid barrier that separates two
+// dependent matvecs, the next matrix is already streaming in.
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "qm_kernel_args.h"
+#include "qm_pipe.cuh"
+
+using namespace qm;
+
+namespace {
+
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%6}, {%7,%6}, "
+        "{%8,%8,%8,%8};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(0u), "r"(b0), "f"(0.f));
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most n of this thread's most recent commit groups are still in flight.
+__device__ __forceinline__ void cp_async_wait(int n) {
+    switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+    }
+}
+
+constexpr int kRowTab = 64;     // bytes of one row of the per-warp scale table
+constexpr int kTabBytes = 16 * kRowTab;
+
+// A stage holds one item of the store: 16 headers of 16 bytes, then for each of the four
+// 32-byte quant groups p the 16 rows side by side — so the 8-byte reads of four rows at a
+// time cover 128 contiguous bytes and the copy from HBM is one contiguous 2304-byte run.
+constexpr int kStageBytes = QM_Q4K_ITEM_BYTES;
+constexpr int kCopiesPerLane = (kStageBytes / 16 + 31) / 32;   // 16-byte pieces of a stage per lane
+
+struct Cursor {   // walks the items of this warp, op after op
+    int op;
+    int64_t i, hi;        // current item and end of the warp's range in op
+    int tile, u, units;   // position and K units of the op's slice
+    const uint8_t *src;   // store address of the current item
+    int64_t tile_skip;    // bytes from the end of a tile's slice to the start of the next tile's
+};
+
+template <int NT>
+__device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int C = a.consumers, D = a.depth, M = a.m, CPM = a.cpm;
+    const int nthreads = C * 32;
+    const int NL = CPM == 4 ? 3 : 2;            // limbs per activation row
+    const int P = M * NL;                        // stored activation planes
+    const QmOp *ops = a.ops ? a.ops : a.inl;
+
+    // ---- shared memory carve-up (qm_plan_fused on the host computes the same sizes) -------
+    const int plane_stride = a.max_units * 256 + 64;
+    uint8_t *xs = smem;                                                             // [P][plane_stride]
+    uint32_t *xsum = reinterpret_cast<uint32_t *>(xs + (size_t)P * plane_stride);    // [units][8NT][4]
+    float *sxw = reinterpret_cast<float *>(xsum + (size_t)a.max_units * 8 * NT * 4); // [units][8NT]
+    uint8_t *tabs = reinterpret_cast<uint8_t *>(sxw + (size_t)a.max_units * 8 * NT); // [C][kTabBytes]
+    float *red = reinterpret_cast<float *>(tabs + (size_t)C * kTabBytes);            // [32][8]
+    float *s_scale = red + 32 * 8;                                                   // [8]
+    constexpr int stage_bytes = kStageBytes;
+    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(s_scale + 8) + 127) & ~(uintptr_t)127);  // [C][D]
+    uint8_t *my_stages = stages + (size_t)warp * D * stage_bytes;
+    uint8_t *my_tab = tabs + (size_t)warp * kTabBytes;
+
+    asm volatile("griddepcontrol.launch_dependents;");
+    // columns of absent activation rows and pad columns must read as zero
+    for (int i = tid; i < a.max_units * 8 * NT * 5; i += nthreads) xsum[i] = 0u;   // xsum and sxw are adjacent
+    __syncthreads();
+
+    // This warp's share of an op: warps are numbered warp-major over the CTAs so that a short
+    // op still spreads over all SMs; every busy warp owns at least one item.
+    const int64_t vwarp = (int64_t)warp * gridDim.x + blockIdx.x;
+    auto op_range = [&](const QmOp &op, int64_t &lo, int64_t &hi, int64_t &Wt, int64_t &I) {
+        I = (int64_t)op.tiles * op.units;
+        Wt = min((int64_t)gridDim.x * C, I);
+        lo = vwarp < Wt ? vwarp * I / Wt : 0;
+        hi = vwarp < Wt ? (vwarp + 1) * I / Wt : 0;
+    };
+    auto cursor_at = [&](Cursor &c, int op) {
+        c.op = op;
+        c.i = c.hi = 0;
+        c.tile = c.u = 0;
+        c.units = 1;
+        c.src = nullptr;
+        c.tile_skip = 0;
+        if (op < a.nops) {
+            const QmOp o = ops[op];   // by value: the fields live in registers from here on
+            int64_t lo, Wt, I;
+            op_range(o, lo, c.hi, Wt, I);
+            c.i = lo;
+            c.units = o.units;
+            c.tile = (int)(lo / o.units);
+            c.u = (int)(lo - (int64_t)c.tile * o.units);
+            c.src = o.wq + ((int64_t)c.tile * o.units_total + o.unit0 + c.u) * QM_Q4K_ITEM_BYTES;
+            c.tile_skip = (int64_t)(o.units_total - o.units) * QM_Q4K_ITEM_BYTES;
+        }
+    };
+    auto cursor_skip_empty = [&](Cursor &c) {
+        while (c.op < a.nops && c.i >= c.hi) cursor_at(c, c.op + 1);
+    };
+
+    // ---- producer side of the ring ----------------------------------------------------------
+    Cursor ic;
+    cursor_at(ic, 0);
+    cursor_skip_empty(ic);
+    int islot = 0;
+    // Starts the copy of the next item into ring slot `islot` and commits one group; commits an
+    // empty group when the warp has nothing left, so that group counting stays uniform.
+    auto issue = [&]() {
+        if (ic.op < a.nops) {
+            const uint32_t dst = smem_u32(my_stages + (size_t)islot * stage_bytes) + lane * 16;
+            const uint8_t *src = ic.src + lane * 16;
+            if (a.debug != 3) {
+#pragma unroll
+                for (int k = 0; k < kCopiesPerLane; k++)
+                    if (lane + 32 * k < kStageBytes / 16) cp_async16(dst + 512 * k, src + 512 * k);
+            }
+            ic.i += 1;
+            ic.u += 1;
+            ic.src += QM_Q4K_ITEM_BYTES;
+            if (ic.u == ic.units) { ic.u = 0; ic.tile++; ic.src += ic.tile_skip; }
+            cursor_skip_empty(ic);
+        }
+        cp_async_commit();
+        islot = islot + 1 == D ? 0 : islot + 1;
+    };
+    for (int d = 0; d < D; d++) issue();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- lane roles on the activation side ---------------------------------------------------
+    // mma column n = 8*nt + g holds limb (n % CPM) of activation row (n / CPM).
+    bool bact[NT], mact[NT];
+    const uint8_t *bplane[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int n = 8 * nt + g, j = n / CPM, l = n - j * CPM;
+        bact[nt] = j < M && l < NL;
+        mact[nt] = j < M && l < 2;
+        bplane[nt] = xs + (size_t)(bact[nt] ? j * NL + l : 0) * plane_stride + t * 16;
+    }
+
+    int cslot = 0;
+    unsigned int nbar = 0;
+    Cursor cc;
+    cursor_at(cc, 0);
+
+    for (int opi = 0; opi < a.nops; opi++) {
+        const QmOp op = ops[opi];   // by value: no reloads through the generic pointer
+        const int nun = op.units;
+        // ---- wait for the producers of x, and for this CTA's readers of the old planes --------
+        if (opi > 0) {
+            __syncthreads();
+            if (op.barrier) {
+                if (tid == 0) {
+                    __threadfence();
+                    atomicAdd(a.grid_bar, 1u);
+                    const unsigned int target = (nbar + 1) * gridDim.x;
+                    const long long t0 = clock64();
+                    while (ld_acquire(a.grid_bar) < target) {
+                        if (clock64() - t0 > 4000000000ll) {
+                            atomicOr(a.status, QM_STATUS_TIMEOUT);
+                            break;
+                        }
+                        __nanosleep(64);
+                    }
+                }
+                nbar++;
+                __syncthreads();
+            }
+        }
+        // ---- quantize the activations of this op into limbs, once per CTA ---------------------
+        const bool norm = (op.xop == 1 || op.xop == 2);
+        if (norm) {
+            for (int j = 0; j < M; j++) {
+                float s = 0.f;
+                const float *xr = op.x + (int64_t)j * op.ldx;
+                const float *x2r = op.x2 ? op.x2 + (int64_t)j * op.ldx : nullptr;
+                for (int c = tid * 4; c < op.cols; c += nthreads * 4) {
+                    float4 v4 = __ldcg(reinterpret_cast<const float4 *>(xr + c));
+                    if (op.xop == 2) {
+                        const float4 w = __ldcg(reinterpret_cast<const float4 *>(x2r + c));
+                        v4.x += w.x; v4.y += w.y; v4.z += w.z; v4.w += w.w;
+                    }
+                    s = fmaf(v4.x, v4.x, s); s = fmaf(v4.y, v4.y, s);
+                    s = fmaf(v4.z, v4.z, s); s = fmaf(v4.w, v4.w, s);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (lane == 0) red[warp * 8 + j] = s;
+            }
+            __syncthreads();
+            if (tid < M) {
+                float s = 0.f;
+                for (int w = 0; w < C; w++) s += red[w * 8 + tid];
+                s_scale[tid] = rsqrtf(s / (float)op.cols + op.eps);
+            }
+            __syncthreads();
+        }
+        for (int idx = warp; idx < M * nun; idx += C) {
+            const int j = idx / nun, ul = idx - j * nun;
+            const int col = (op.unit0 + ul) * QM_K_UNIT + lane * 8;
+            const float *xp = op.x + (int64_t)j * op.ldx + col;
+            float v[8];
+            {
+                const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(xp));
+                const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(xp + 4));
+                v[0] = p0.x; v[1] = p0.y; v[2] = p0.z; v[3] = p0.w;
+                v[4] = p1.x; v[5] = p1.y; v[6] = p1.z; v[7] = p1.w;
+            }
+            if (op.xop >= 2) {
+                const float *x2p = op.x2 + (int64_t)j * op.ldx + col;
+                const float4 q0 = __ldcg(reinterpret_cast<const float4 *>(x2p));
+                const float4 q1 = __ldcg(reinterpret_cast<const float4 *>(x2p + 4));
+                const float w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+                for (int e = 0; e < 8; e++)
+                    v[e] = op.xop == 2 ? v[e] + w[e] : v[e] / (1.f + __expf(-v[e])) * w[e];
+            }
+            if (norm) {
+                const float sc = s_scale[j];
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] *= sc;
+            }
+            float amax = 0.f, sum = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; e++) { amax = fmaxf(amax, fabsf(v[e])); sum += v[e]; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            const float sx = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
+            const float inv = amax > 0.f ? 127.f / amax : 0.f;
+            uint32_t w0[3] = {0, 0, 0}, w1[3] = {0, 0, 0};
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const float r = v[e] * inv;
+                const int h = __float2int_rn(r);
+                const float r1 = (r - (float)h) * 128.f;
+                const int l1 = __float2int_rn(r1);
+                const int l2 = __float2int_rn((r1 - (float)l1) * 128.f);
+                const int sh = (e & 3) * 8;
+                uint32_t *dstw = e < 4 ? w0 : w1;
+                dstw[0] |= ((uint32_t)h & 0xFFu) << sh;
+                dstw[1] |= ((uint32_t)l1 & 0xFFu) << sh;
+                dstw[2] |= ((uint32_t)l2 & 0xFFu) << sh;
+            }
+            // lane = 4*sub-block + t': this lane's 8 columns are the B fragment of lane t' for
+            // sub-block sb; the fragments of sub-blocks 2p and 2p+1 sit side by side
+            const int sb = lane >> 2, tq = lane & 3;
+            const int off = ((ul * 4 + (sb >> 1)) * 4 + tq) * 16 + (sb & 1) * 8;
+            for (int l = 0; l < NL; l++)
+                *reinterpret_cast<uint2 *>(xs + (size_t)(j * NL + l) * plane_stride + off) = make_uint2(w0[l], w1[l]);
+            const int n0 = j * CPM;   // first mma column of this activation row
+            if (tq == 0) {
+                const __half sh = __float2half_rn(sum);
+                const __half sl = __float2half_rn(sum - __half2float(sh));
+                __half *xh = reinterpret_cast<__half *>(xsum);
+                xh[((size_t)ul * 8 * NT + n0) * 8 + sb] = sh;
+                xh[((size_t)ul * 8 * NT + n0 + 1) * 8 + sb] = sl;
+            }
+            if (lane < CPM) {
+                const float lw = lane == 0 ? 1.f : lane == 1 ? (1.f / 128.f) : lane == 2 && NL == 3 ? (1.f / 16384.f) : 0.f;
+                sxw[(size_t)ul * 8 * NT + n0 + lane] = sx * lw;
+            }
+        }
+        __syncthreads();
+
+        // ---- stream this warp's chunks of the op ---------------------------------------------------
+        int64_t lo, hi, Wt, I;
+        op_range(op, lo, hi, Wt, I);
+        if (cc.op != opi) cursor_at(cc, opi);
+        float accF[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) accF[nt][0] = accF[nt][1] = accF[nt][2] = accF[nt][3] = 0.f;
+        int cur_tile = cc.tile;
+
+        auto flush = [&](int tile) {
+            // per activation row: sum of its CPM columns; lanes t hold columns 2t, 2t+1
+            float vA[NT], vB[NT];
+            int jrow[NT];
+            bool valid[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                vA[nt] = accF[nt][0] + accF[nt][1];
+                vB[nt] = accF[nt][2] + accF[nt][3];
+                if (CPM == 4) {
+                    vA[nt] += __shfl_xor_sync(0xffffffffu, vA[nt], 1);
+                    vB[nt] += __shfl_xor_sync(0xffffffffu, vB[nt], 1);
+                    jrow[nt] = 2 * nt + (t >> 1);
+                    valid[nt] = (t & 1) == 0 && jrow[nt] < M;
+                } else {
+                    jrow[nt] = 4 * nt + t;
+                    valid[nt] = jrow[nt] < M;
+                }
+            }
+            const int64_t i0 = (int64_t)tile * nun, i1 = i0 + nun - 1;
+            const int64_t vf = ((i0 + 1) * Wt - 1) / I, vl = ((i1 + 1) * Wt - 1) / I;
+            const int rA = tile * 16 + g, rB = rA + 8;
+            if (vf == vl) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+                    if (valid[nt]) {
+                        float *yA = op.y + (int64_t)jrow[nt] * op.ldy + rA, *yB = yA + 8;
+                        if (rA < op.rows) *yA = vA[nt] + (op.accumulate ? __ldcg(yA) : 0.f);
+                        if (rB < op.rows) *yB = vB[nt] + (op.accumulate ? __ldcg(yB) : 0.f);
+                    }
+                return;
+            }
+            float *p = a.partials + ((size_t)tile * op.maxseg + (size_t)(vwarp - vf)) * 128;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+                if (valid[nt]) { p[jrow[nt] * 16 + g] = vA[nt]; p[jrow[nt] * 16 + g + 8] = vB[nt]; }
+            const unsigned int expected = (unsigned int)(vl - vf + 1);
+            __threadfence();
+            __syncwarp();
+            unsigned int old = 0;
+            if (lane == 0) old = atomicAdd(a.tickets + tile, 1u);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old != expected - 1) return;
+            __threadfence();
+            const float *q = a.partials + (size_t)tile * op.maxseg * 128;
+            for (int o = lane; o < 16 * M; o += 32) {
+                float s = 0.f;
+                for (unsigned int sg = 0; sg < expected; sg++) s += __ldcg(q + (size_t)sg * 128 + o);
+                const int j = o >> 4, r = o & 15;
+                float *yp = op.y + (int64_t)j * op.ldy + tile * 16 + r;
+                if (tile * 16 + r < op.rows) *yp = s + (op.accumulate ? __ldcg(yp) : 0.f);
+            }
+            if (lane == 0) a.tickets[tile] = 0u;  // ready for the next op or launch
+        };
+
+        // per-warp scale table of unit `un` of the landed stage, built by all 32 lanes:
+        // lane = 2*row + half handles sub-blocks 4*half .. 4*half+3 of its row
+        auto build_table = [&](const uint8_t *stage, uint8_t *tab) {
+            const int row = lane >> 1, half = lane & 1;
+            const uint4 hdr = *reinterpret_cast<const uint4 *>(stage + row * 16);
+            const uint32_t S0 = hdr.y, S1 = hdr.z, S2 = hdr.w;
+            const uint32_t scv = half == 0 ? (S0 & 0x3F3F3F3Fu) : ((S2 & 0x0F0F0F0Fu) | ((S0 >> 2) & 0x30303030u));
+            const uint32_t mv = half == 0 ? (S1 & 0x3F3F3F3Fu) : (((S2 >> 4) & 0x0F0F0F0Fu) | ((S1 >> 2) & 0x30303030u));
+            uint8_t *r = tab + row * kRowTab;
+            *reinterpret_cast<uint4 *>(r + half * 16) =
+                make_uint4(scv & 0xFF, (scv >> 8) & 0xFF, (scv >> 16) & 0xFF, scv >> 24);
+            const uint32_t m01 = hsub2(prmt(mv, 0x64646464u, 0x4140u), 0x64006400u);
+            const uint32_t m23 = hsub2(prmt(mv, 0x64646464u, 0x4342u), 0x64006400u);
+            *reinterpret_cast<uint2 *>(r + 32 + half * 8) = make_uint2(m01, m23);
+            if (half == 0) {
+                const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+                const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+                *reinterpret_cast<float2 *>(r + 48) = make_float2(d, dmin);
+            }
+        };
+
+        while (cc.op == opi && cc.i < cc.hi) {
+            if (cc.tile != cur_tile) {
+                flush(cur_tile);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) accF[nt][0] = accF[nt][1] = accF[nt][2] = accF[nt][3] = 0.f;
+                cur_tile = cc.tile;
+            }
+            // the oldest of the D groups in flight is this unit; the copies of every lane are
+            // visible to the whole warp once all lanes have waited
+            cp_async_wait(D - 1);
+            __syncwarp();
+            const uint8_t *stage = my_stages + (size_t)cslot * stage_bytes;
+            if (a.debug == 0 || a.debug == 3) {
+                const uint8_t *tab = my_tab;
+                build_table(stage, my_tab);
+                __syncwarp();
+                const int ul = cc.u;
+                // scales of this lane's two rows
+                const uint4 sA0 = *reinterpret_cast<const uint4 *>(tab + g * kRowTab);
+                const uint4 sA1 = *reinterpret_cast<const uint4 *>(tab + g * kRowTab + 16);
+                const uint4 sB0 = *reinterpret_cast<const uint4 *>(tab + (g + 8) * kRowTab);
+                const uint4 sB1 = *reinterpret_cast<const uint4 *>(tab + (g + 8) * kRowTab + 16);
+                const int scA[8] = {(int)sA0.x, (int)sA0.y, (int)sA0.z, (int)sA0.w, (int)sA1.x, (int)sA1.y, (int)sA1.z, (int)sA1.w};
+                const int scB[8] = {(int)sB0.x, (int)sB0.y, (int)sB0.z, (int)sB0.w, (int)sB1.x, (int)sB1.y, (int)sB1.z, (int)sB1.w};
+                int accL[NT][4], accH[NT][4];
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) accL[nt][c] = accH[nt][c] = 0;
+                const uint8_t *rowA = stage + 256 + 32 * g + 8 * t;
+                const uint8_t *rowB = rowA + 256;
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    const uint2 wA = *reinterpret_cast<const uint2 *>(rowA + 512 * p);
+                    const uint2 wB = *reinterpret_cast<const uint2 *>(rowB + 512 * p);
+                    const uint32_t a0 = wA.x & 0x0F0F0F0Fu, a1 = wB.x & 0x0F0F0F0Fu;
+                    const uint32_t a2 = wA.y & 0x0F0F0F0Fu, a3 = wB.y & 0x0F0F0F0Fu;
+                    const uint32_t h0 = wA.x & 0xF0F0F0F0u, h1 = wB.x & 0xF0F0F0F0u;
+                    const uint32_t h2 = wA.y & 0xF0F0F0F0u, h3 = wB.y & 0xF0F0F0F0u;
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        uint4 b = make_uint4(0, 0, 0, 0);
+                        if (bact[nt]) b = *reinterpret_cast<const uint4 *>(bplane[nt] + (ul * 4 + p) * 64);
+                        int S[4];
+                        mma_u8s8(S, a0, a1, a2, a3, b.x, b.y);
+                        accL[nt][0] += scA[2 * p] * S[0];
+                        accL[nt][1] += scA[2 * p] * S[1];
+                        accL[nt][2] += scB[2 * p] * S[2];
+                        accL[nt][3] += scB[2 * p] * S[3];
+                        mma_u8s8(S, h0, h1, h2, h3, b.z, b.w);   // sixteen times the sub-block sums
+                        accH[nt][0] += scA[2 * p + 1] * S[0];
+                        accH[nt][1] += scA[2 * p + 1] * S[1];
+                        accH[nt][2] += scB[2 * p + 1] * S[2];
+                        accH[nt][3] += scB[2 * p + 1] * S[3];
+                    }
+                }
+                const uint32_t mpA = *reinterpret_cast<const uint32_t *>(tab + g * kRowTab + 32 + 4 * t);
+                const uint32_t mpB = *reinterpret_cast<const uint32_t *>(tab + (g + 8) * kRowTab + 32 + 4 * t);
+                const float2 ddA = *reinterpret_cast<const float2 *>(tab + g * kRowTab + 48);
+                const float2 ddB = *reinterpret_cast<const float2 *>(tab + (g + 8) * kRowTab + 48);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const float2 cw = *reinterpret_cast<const float2 *>(sxw + (size_t)ul * 8 * NT + 8 * nt + 2 * t);
+                    float accM[4];
+                    const uint32_t bm = mact[nt] ? xsum[((size_t)ul * 8 * NT + 8 * nt + g) * 4 + t] : 0u;
+                    mma_f16(accM, mpA, mpB, bm);
+                    const float f0 = (float)accL[nt][0] + (float)accH[nt][0] * 0.0625f;
+                    const float f1 = (float)accL[nt][1] + (float)accH[nt][1] * 0.0625f;
+                    const float f2 = (float)accL[nt][2] + (float)accH[nt][2] * 0.0625f;
+                    const float f3 = (float)accL[nt][3] + (float)accH[nt][3] * 0.0625f;
+                    accF[nt][0] = fmaf(ddA.x * cw.x, f0, fmaf(-ddA.y, accM[0], accF[nt][0]));
+                    accF[nt][1] = fmaf(ddA.x * cw.y, f1, fmaf(-ddA.y, accM[1], accF[nt][1]));
+                    accF[nt][2] = fmaf(ddB.x * cw.x, f2, fmaf(-ddB.y, accM[2], accF[nt][2]));
+                    accF[nt][3] = fmaf(ddB.x * cw.y, f3, fmaf(-ddB.y, accM[3], accF[nt][3]));
+                }
+                __syncwarp();   // all lanes are done with the table before it is rebuilt
+            }
+            cc.i += 1;
+            cc.u += 1;
+            if (cc.u == nun) { cc.u = 0; cc.tile++; }
+            cslot = cslot + 1 == D ? 0 : cslot + 1;
+            // every lane's reads of the slot have returned (their values were consumed above):
+            // after the warp converges the next copy may overwrite it
+            __syncwarp();
+            issue();
+        }
+        if (lo < hi) flush(cur_tile);
+    }
+}
+
+}  // namespace
+
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_nt1(const __grid_constant__ QmFusedArgs a) {
+    fused_body<1>(a);
+}
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_nt2(const __grid_constant__ QmFusedArgs a) {
+    fused_body<2>(a);
+}

@@ -53,6 +53,7 @@ int qm_driver_load(QmDriver **out) {
 
 QM_INCBIN(qm_cubin_gemv, QM_STR(QM_CUBIN_DIR) "/qm_gemv.sm_100a.cubin")
 QM_INCBIN(qm_cubin_dequant, QM_STR(QM_CUBIN_DIR) "/qm_dequant.sm_100a.cubin")
+QM_INCBIN(qm_cubin_q4k, QM_STR(QM_CUBIN_DIR) "/qm_gemv_q4k.sm_100a.cubin")
 
 struct KernelImage {
     const unsigned char *begin;
@@ -61,16 +62,19 @@ struct KernelImage {
 static const KernelImage kImages[QM_MOD_COUNT] = {
     {qm_cubin_gemv, qm_cubin_gemv_end},
     {qm_cubin_dequant, qm_cubin_dequant_end},
+    {qm_cubin_q4k, qm_cubin_q4k_end},
 };
 struct KernelName {
     int module;
     const char *name;
 };
 static const KernelName kKernels[QM_K_COUNT] = {
-    {QM_MOD_GEMV, "qm_gemv_q4k_m4"},   {QM_MOD_GEMV, "qm_gemv_q4k_m8"},    {QM_MOD_GEMV, "qm_gemv_q40_m4"},
+    {QM_MOD_GEMV, "qm_gemv_q40_m4"},
     {QM_MOD_GEMV, "qm_gemv_q40_m8"},   {QM_MOD_GEMV, "qm_gemv_q80_m4"},    {QM_MOD_GEMV, "qm_gemv_q80_m8"},
     {QM_MOD_DEQUANT, "qm_dequant_q4k"}, {QM_MOD_DEQUANT, "qm_dequant_q2k"}, {QM_MOD_DEQUANT, "qm_dequant_q40"},
     {QM_MOD_DEQUANT, "qm_dequant_q80"}, {QM_MOD_DEQUANT, "qm_repack_q40"},  {QM_MOD_DEQUANT, "qm_repack_q80"},
+    {QM_MOD_DEQUANT, "qm_repack_q4k"},
+    {QM_MOD_Q4K, "qm_fused_q4k_nt1"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2"},
 };
 
 // ---- errors --------------------------------------------------------------------------
@@ -150,7 +154,11 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             r = d->cuModuleGetFunction(&c->fn[k], c->modules[kKernels[k].module], kKernels[k].name);
             if (r != CUDA_SUCCESS) err = QM_ERR_NO_KERNEL;
         }
-        for (int k = QM_K_GEMV_Q4K_M4; k <= QM_K_GEMV_Q80_M8 && !err; k++) {
+        for (int k = QM_K_FUSED_Q4K_NT1; k <= QM_K_FUSED_Q4K_NT2 && !err; k++) {
+            r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
+            if (r != CUDA_SUCCESS) err = (int32_t)r;
+        }
+        for (int k = QM_K_GEMV_Q40_M4; k <= QM_K_GEMV_Q80_M8 && !err; k++) {
             r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
@@ -165,6 +173,8 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             if (r == CUDA_SUCCESS) r = d->cuMemAlloc_v2(&c->tickets_dev, QM_TICKETS * sizeof(unsigned));
             if (r == CUDA_SUCCESS) r = d->cuMemsetD8Async(c->tickets_dev, 0, QM_TICKETS * sizeof(unsigned), c->stream);
             if (r == CUDA_SUCCESS) r = d->cuMemAlloc_v2(&c->partials_dev, QM_PARTIALS_BYTES);
+            if (r == CUDA_SUCCESS) r = d->cuMemAlloc_v2(&c->gridbar_dev, 256);
+            if (r == CUDA_SUCCESS) r = d->cuMemsetD8Async(c->gridbar_dev, 0, 256, c->stream);
             if (r == CUDA_SUCCESS) r = d->cuStreamSynchronize(c->stream);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
@@ -187,6 +197,7 @@ extern "C" int32_t qm_destroy(qm_ctx *c) {
             if (c->status_dev) d->cuMemFree_v2(c->status_dev);
             if (c->tickets_dev) d->cuMemFree_v2(c->tickets_dev);
             if (c->partials_dev) d->cuMemFree_v2(c->partials_dev);
+            if (c->gridbar_dev) d->cuMemFree_v2(c->gridbar_dev);
             if (c->xstage_dev) d->cuMemFree_v2(c->xstage_dev);
             if (c->upload_dev) d->cuMemFree_v2(c->upload_dev);
             if (c->own_stream) d->cuStreamDestroy_v2(c->own_stream);
@@ -271,29 +282,42 @@ extern "C" int32_t qm_memcpy_d2h(qm_ctx *c, void *dst, uint64_t src, int64_t byt
 }
 
 // ---- launch helper ----------------------------------------------------------------------
-int32_t qm_launch(qm_ctx *c, int kernel, unsigned gx, unsigned gy, unsigned block, unsigned smem, void *args,
-                  bool pdl) {
+int32_t qm_launch_ex(qm_ctx *c, int kernel, unsigned gx, unsigned block, unsigned smem, void *args, bool pdl,
+                     bool cooperative) {
     void *params[1] = {args};
     CUlaunchConfig cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDimX = gx;
-    cfg.gridDimY = gy;
+    cfg.gridDimY = 1;
     cfg.gridDimZ = 1;
     cfg.blockDimX = block;
     cfg.blockDimY = 1;
     cfg.blockDimZ = 1;
     cfg.sharedMemBytes = smem;
     cfg.hStream = c->stream;
-    CUlaunchAttribute attr[1];
+    CUlaunchAttribute attr[2];
+    unsigned n = 0;
     if (pdl) {
-        attr[0].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
-        attr[0].value.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        attr[n].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr[n].value.programmaticStreamSerializationAllowed = 1;
+        n++;
     }
+    if (cooperative) {  // all CTAs co-resident: required by the grid barrier between fused ops
+        attr[n].id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE;
+        attr[n].value.cooperative = 1;
+        n++;
+    }
+    cfg.attrs = n ? attr : nullptr;
+    cfg.numAttrs = n;
     DRV(c->drv->cuLaunchKernelEx(&cfg, c->fn[kernel], params, nullptr));
     c->launches++;
     return QM_OK;
+}
+
+int32_t qm_launch(qm_ctx *c, int kernel, unsigned gx, unsigned gy, unsigned block, unsigned smem, void *args,
+                  bool pdl) {
+    (void)gy;
+    return qm_launch_ex(c, kernel, gx, block, smem, args, pdl, false);
 }
 
 // ---- weight store -----------------------------------------------------------------------
@@ -330,7 +354,8 @@ extern "C" int32_t qm_store_create(qm_ctx *c, int32_t fmt, int64_t rows, int64_t
     w->units = (int32_t)((cols + QM_K_UNIT - 1) / QM_K_UNIT);
     w->gguf_row_bytes = cols / block * bbytes;
     int64_t qbytes = 0, dbytes = 0;
-    if (fmt == QM_FMT_Q4_K || fmt == QM_FMT_Q2_K) qbytes = rows * w->units * bbytes;
+    if (fmt == QM_FMT_Q2_K) qbytes = rows * w->units * bbytes;
+    if (fmt == QM_FMT_Q4_K) qbytes = (rows + 15) / 16 * w->units * QM_Q4K_ITEM_BYTES;  // whole 16-row tiles
     if (fmt == QM_FMT_Q4_0) { qbytes = rows * w->units * 8 * 16; dbytes = rows * w->units * 8 * 2; }
     if (fmt == QM_FMT_Q8_0) { qbytes = rows * w->units * 8 * 32; dbytes = rows * w->units * 8 * 2; }
     w->qbytes = qbytes;
@@ -340,8 +365,9 @@ extern "C" int32_t qm_store_create(qm_ctx *c, int32_t fmt, int64_t rows, int64_t
     // 64 bytes of slack: rows past the last one are clamped, never read beyond
     if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&w->wq, (size_t)qbytes + 64);
     if (r == CUDA_SUCCESS && dbytes) r = c->drv->cuMemAlloc_v2(&w->wd, (size_t)dbytes + 64);
-    // zero-scale padding blocks (Q4_0/Q8_0 rows that end inside a K unit) must read as zero
-    if (r == CUDA_SUCCESS && dbytes) r = c->drv->cuMemsetD8Async(w->wq, 0, (size_t)qbytes + 64, c->stream);
+    // padding must read as zero: Q4_0/Q8_0 rows that end inside a K unit, Q4_K rows past the last
+    if (r == CUDA_SUCCESS && (dbytes || fmt == QM_FMT_Q4_K))
+        r = c->drv->cuMemsetD8Async(w->wq, 0, (size_t)qbytes + 64, c->stream);
     if (r == CUDA_SUCCESS && dbytes) r = c->drv->cuMemsetD8Async(w->wd, 0, (size_t)dbytes + 64, c->stream);
     if (r != CUDA_SUCCESS) {
         if (w->wq) c->drv->cuMemFree_v2(w->wq);
@@ -354,7 +380,7 @@ extern "C" int32_t qm_store_create(qm_ctx *c, int32_t fmt, int64_t rows, int64_t
 }
 
 static int32_t store_write_dev(qm_ctx *c, QmWeight *w, int64_t row_offset, int64_t nrows, CUdeviceptr src) {
-    if (w->fmt == QM_FMT_Q4_K || w->fmt == QM_FMT_Q2_K) {
+    if (w->fmt == QM_FMT_Q2_K) {
         DRV(c->drv->cuMemcpyDtoDAsync_v2(w->wq + row_offset * w->gguf_row_bytes, src,
                                          (size_t)(nrows * w->gguf_row_bytes), c->stream));
         return QM_OK;
@@ -367,9 +393,10 @@ static int32_t store_write_dev(qm_ctx *c, QmWeight *w, int64_t row_offset, int64
     a.nrows = nrows;
     a.cols = (int32_t)w->cols;
     a.units = w->units;
-    const int64_t nblk = nrows * (w->cols / 32);
+    const int64_t nblk = nrows * (w->cols / (w->fmt == QM_FMT_Q4_K ? 256 : 32));
     const unsigned grid = (unsigned)std::min<int64_t>((nblk + 255) / 256, 148 * 16);
-    return qm_launch(c, w->fmt == QM_FMT_Q4_0 ? QM_K_REPACK_Q40 : QM_K_REPACK_Q80, grid, 1, 256, 0, &a, false);
+    const int k = w->fmt == QM_FMT_Q4_0 ? QM_K_REPACK_Q40 : w->fmt == QM_FMT_Q8_0 ? QM_K_REPACK_Q80 : QM_K_REPACK_Q4K;
+    return qm_launch(c, k, grid, 1, 256, 0, &a, false);
 }
 
 extern "C" int32_t qm_store_write_rows_device(qm_ctx *c, qm_weight h, int64_t row_offset, int64_t nrows,
@@ -379,7 +406,7 @@ extern "C" int32_t qm_store_write_rows_device(qm_ctx *c, qm_weight h, int64_t ro
     if (!w || !dev_bytes) return QM_ERR_ARG;
     if (row_offset < 0 || nrows < 0 || row_offset + nrows > w->rows) return QM_ERR_SHAPE;
     if (len < nrows * w->gguf_row_bytes) return QM_ERR_BUFFER;
-    if ((dev_bytes & 1) != 0) return QM_ERR_ARG;
+    if ((dev_bytes & (w->fmt == QM_FMT_Q4_K ? 15 : 1)) != 0) return QM_ERR_ARG;
     if (nrows == 0) return QM_OK;
     CtxGuard g(c);
     DRV(g.rc);
@@ -397,7 +424,7 @@ extern "C" int32_t qm_store_write_rows(qm_ctx *c, qm_weight h, int64_t row_offse
     CtxGuard g(c);
     DRV(g.rc);
     const int64_t bytes = nrows * w->gguf_row_bytes;
-    if (w->fmt == QM_FMT_Q4_K || w->fmt == QM_FMT_Q2_K) {
+    if (w->fmt == QM_FMT_Q2_K) {
         // GGUF bytes are the device layout: copy straight into place
         DRV(c->drv->cuMemcpyHtoDAsync_v2(w->wq + row_offset * w->gguf_row_bytes, host_bytes, (size_t)bytes,
                                          c->stream));
@@ -527,8 +554,8 @@ int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p) {
     // (16-row tile, K unit) items through a private ring of `depth` bulk-copy stages of `kc`
     // units. The activations of the CTA's K slice live in shared memory next to the rings; when
     // they do not fit, K is cut into slices and groups of CTAs take one slice each.
-    const int q = w->fmt == QM_FMT_Q4_K ? 144 : w->fmt == QM_FMT_Q4_0 ? 128 : 256;
-    const int dq = w->fmt == QM_FMT_Q4_K ? 0 : 16;
+    const int q = w->fmt == QM_FMT_Q4_0 ? 128 : 256;
+    const int dq = 16;
     p->consumers = env_int("QM_GEMV_C", 16);
     p->depth = env_int("QM_GEMV_D", 2);
     p->kc = env_int("QM_GEMV_KC", w->fmt == QM_FMT_Q8_0 ? 1 : 2);
@@ -560,6 +587,90 @@ int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p) {
     return QM_OK;
 }
 
+int32_t qm_plan_fused(qm_ctx *c, int32_t m, int32_t units, bool allow_slices, QmFusedPlan *p) {
+    (void)c;
+    p->nt = m <= 4 ? 1 : 2;
+    p->cpm = m <= 2 ? 4 : 2;
+    const int planes = m * (p->cpm == 4 ? 3 : 2);
+    // ring shapes in order of preference: (warps, stages per warp)
+    static const int cand[][2] = {{16, 4}, {16, 3}, {16, 2}};
+    const int forced = env_int("QM_GEMV_C", 0);
+    for (int slices = 1; slices <= (allow_slices ? QM_MAX_INLINE_OPS : 1); slices++) {
+        const int ups = (units + slices - 1) / slices;
+        for (const auto &cd : cand) {
+            int C = cd[0], D = cd[1];
+            if (forced) { C = forced; D = env_int("QM_GEMV_D", 3); }
+            if (C < 1 || C > QM_GEMV_MAX_THREADS / 32 || D < 1 || D > 8) return QM_ERR_ARG;
+            const int smem = planes * (ups * 256 + 64) + ups * 160 * p->nt + C * 1024 + 32 * 8 * 4 + 32 + 128 +
+                             C * D * QM_Q4K_ITEM_BYTES;
+            if (smem <= QM_GEMV_SMEM_MAX) {
+                p->consumers = C;
+                p->depth = D;
+                p->smem = smem;
+                p->max_units = ups;
+                p->units_per_slice = ups;
+                p->slices = (units + ups - 1) / ups;
+                return QM_OK;
+            }
+            if (forced) break;
+        }
+    }
+    return QM_ERR_SHAPE;
+}
+
+void qm_fill_op(qm_ctx *c, const QmFusedPlan &p, const QmWeight *w, uint64_t x, uint64_t x2, int64_t ldx, uint64_t y,
+                int64_t ldy, uint32_t xop, int barrier, int unit0, int units, int accumulate, QmOp *op) {
+    memset(op, 0, sizeof *op);
+    op->wq = (const uint8_t *)(uintptr_t)w->wq;
+    op->x = (const float *)(uintptr_t)x;
+    op->x2 = (const float *)(uintptr_t)x2;
+    op->y = (float *)(uintptr_t)y;
+    op->ldx = ldx;
+    op->ldy = ldy;
+    op->rows = (int32_t)w->rows;
+    op->cols = (int32_t)w->cols;
+    op->units = units;
+    op->units_total = w->units;
+    op->unit0 = unit0;
+    op->accumulate = accumulate;
+    op->tiles = (int32_t)((w->rows + 15) / 16);
+    op->xop = (int32_t)xop;
+    op->barrier = barrier;
+    const int64_t I = (int64_t)op->tiles * op->units;
+    const int64_t Wt = std::min<int64_t>((int64_t)c->sm_count * p.consumers, I);
+    op->maxseg = (int32_t)std::min<int64_t>(op->units, (int64_t)(op->units - 1) * Wt / I + 2);
+    op->eps = 1e-6f;
+}
+
+static int32_t fused_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m,
+                                   int64_t ldx, uint64_t y_dev, int64_t ldy, uint32_t flags, const QmFusedPlan &p) {
+    QmFusedArgs a;
+    memset(&a, 0, sizeof a);
+    for (int s = 0; s < p.slices; s++) {
+        const int u0 = s * p.units_per_slice, n = std::min(p.units_per_slice, w->units - u0);
+        qm_fill_op(c, p, w, x_dev, x2_dev, ldx, y_dev, ldy, flags & 0xFu, s > 0, u0, n, s > 0, &a.inl[s]);
+        if (a.inl[s].tiles > QM_TICKETS || (int64_t)a.inl[s].tiles * a.inl[s].maxseg * 512 > QM_PARTIALS_BYTES)
+            return QM_ERR_SHAPE;
+    }
+    a.ops = nullptr;
+    a.partials = (float *)(uintptr_t)c->partials_dev;
+    a.tickets = (unsigned int *)(uintptr_t)c->tickets_dev;
+    a.status = (unsigned int *)(uintptr_t)c->status_dev;
+    a.grid_bar = (unsigned int *)(uintptr_t)c->gridbar_dev;
+    a.nops = p.slices;
+    a.m = m;
+    a.consumers = p.consumers;
+    a.depth = p.depth;
+    a.max_units = p.max_units;
+    a.cpm = p.cpm;
+    a.debug = env_int("QM_DEBUG_SKIP", 0);
+    const bool coop = p.slices > 1;  // K slices meet at a grid barrier: all CTAs must be co-resident
+    if (coop) DRV(c->drv->cuMemsetD32Async(c->gridbar_dev, 0, 1, c->stream));
+    return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2,
+                        (unsigned)std::max(1, env_int("QM_GEMV_CTAS", c->sm_count)), (unsigned)p.consumers * 32,
+                        (unsigned)p.smem, &a, (flags & QM_FLAG_PDL) != 0 && !coop, coop);
+}
+
 int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,
                          uint64_t y_dev, int64_t ldy, uint32_t flags, CUdeviceptr partials, CUdeviceptr tickets) {
     if (w->fmt != QM_FMT_Q4_K && w->fmt != QM_FMT_Q4_0 && w->fmt != QM_FMT_Q8_0) return QM_ERR_FORMAT;
@@ -568,6 +679,14 @@ int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t 
     if (xop > QM_XOP_SWIGLU) return QM_ERR_ARG;
     if (!x_dev || !y_dev || (x_dev & 15) || (ldx & 3)) return QM_ERR_ARG;
     if ((xop == QM_XOP_ADD_RMSNORM || xop == QM_XOP_SWIGLU) && (!x2_dev || (x2_dev & 15))) return QM_ERR_ARG;
+    if (w->fmt == QM_FMT_Q4_K) {
+        // integer tensor-core path; K is cut into slices when the activation planes of the
+        // whole K do not fit in shared memory (many rows times a long K)
+        QmFusedPlan fp;
+        int32_t frc = qm_plan_fused(c, m, w->units, true, &fp);
+        if (frc) return frc;
+        return fused_matvec_launch(c, w, x_dev, x2_dev, m, ldx, y_dev, ldy, flags, fp);
+    }
     QmGemvPlan p;
     int32_t rc = qm_plan_gemv(c, w, m, &p);
     if (rc) return rc;
@@ -598,7 +717,7 @@ int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t 
     a.xop = (int32_t)xop;
     a.eps = 1e-6f;
     const int mode = m <= 4 ? 0 : 1;
-    const int k = (w->fmt == QM_FMT_Q4_K ? QM_K_GEMV_Q4K_M4 : w->fmt == QM_FMT_Q4_0 ? QM_K_GEMV_Q40_M4 : QM_K_GEMV_Q80_M4) + mode;
+    const int k = (w->fmt == QM_FMT_Q4_0 ? QM_K_GEMV_Q40_M4 : QM_K_GEMV_Q80_M4) + mode;
     return qm_launch(c, k, (unsigned)(p.ksplit * p.ctas_per_slice), 1, (unsigned)p.consumers * 32, (unsigned)p.smem,
                      &a, (flags & QM_FLAG_PDL) != 0);
 }

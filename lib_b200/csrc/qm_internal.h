@@ -9,11 +9,11 @@
 #define QM_CTX_MAGIC 0x514D4358u     // "QMCX"
 #define QM_WEIGHT_MAGIC 0x514D5754u  // "QMWT"
 
-enum { QM_MOD_GEMV = 0, QM_MOD_DEQUANT, QM_MOD_COUNT };
+enum { QM_MOD_GEMV = 0, QM_MOD_DEQUANT, QM_MOD_Q4K, QM_MOD_COUNT };
 enum {
-    QM_K_GEMV_Q4K_M4 = 0, QM_K_GEMV_Q4K_M8, QM_K_GEMV_Q40_M4, QM_K_GEMV_Q40_M8, QM_K_GEMV_Q80_M4,
+    QM_K_GEMV_Q40_M4 = 0, QM_K_GEMV_Q40_M8, QM_K_GEMV_Q80_M4,
     QM_K_GEMV_Q80_M8, QM_K_DEQUANT_Q4K, QM_K_DEQUANT_Q2K, QM_K_DEQUANT_Q40, QM_K_DEQUANT_Q80,
-    QM_K_REPACK_Q40, QM_K_REPACK_Q80, QM_K_COUNT
+    QM_K_REPACK_Q40, QM_K_REPACK_Q80, QM_K_REPACK_Q4K, QM_K_FUSED_Q4K_NT1, QM_K_FUSED_Q4K_NT2, QM_K_COUNT
 };
 
 #define QM_GEMV_SMEM_MAX (227 * 1024)
@@ -32,7 +32,7 @@ struct qm_ctx {
     CUmodule modules[QM_MOD_COUNT];
     CUfunction fn[QM_K_COUNT];
     CUstream own_stream, stream;
-    CUdeviceptr status_dev, tickets_dev, partials_dev;
+    CUdeviceptr status_dev, tickets_dev, partials_dev, gridbar_dev;
     CUdeviceptr xstage_dev;
     int64_t xstage_bytes;
     CUdeviceptr upload_dev;
@@ -51,6 +51,11 @@ struct QmWeight {
 
 struct QmGemvPlan {
     int consumers, depth, kc, ksplit, units_per_slice, ctas_per_slice, tiles, maxseg, smem;
+};
+
+struct QmFusedPlan {
+    int consumers, depth, max_units, cpm, nt, smem;
+    int slices, units_per_slice;   // K slices of one matvec when its activations do not fit whole
 };
 
 struct CtxGuard {
@@ -74,6 +79,13 @@ struct qm_stack;
 QmWeight *qm_weight_from_handle(qm_weight h);
 int32_t qm_launch(qm_ctx *c, int kernel, unsigned gx, unsigned gy, unsigned block, unsigned smem, void *args,
                   bool pdl);
+int32_t qm_launch_ex(qm_ctx *c, int kernel, unsigned gx, unsigned block, unsigned smem, void *args, bool pdl,
+                     bool cooperative);
+// Integer tensor-core path for Q4_K: plan for activation rows m and the largest K (in units)
+// of the ops; QM_ERR_SHAPE when the activation planes do not fit in shared memory.
+int32_t qm_plan_fused(qm_ctx *c, int32_t m, int32_t units, bool allow_slices, QmFusedPlan *p);
+void qm_fill_op(qm_ctx *c, const QmFusedPlan &p, const QmWeight *w, uint64_t x, uint64_t x2, int64_t ldx, uint64_t y,
+                int64_t ldy, uint32_t xop, int barrier, int unit0, int units, int accumulate, QmOp *op);
 int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p);
 int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,
                          uint64_t y_dev, int64_t ldy, uint32_t flags, CUdeviceptr partials, CUdeviceptr tickets);

@@ -13,7 +13,10 @@
 #define QM_STATUS_BOUNDS 2u
 
 // Device layouts held by the weight store.
-//   Q4_K : the GGUF bytes unchanged, [rows][units][144].
+//   Q4_K : the GGUF super-blocks regrouped so that one (16-row tile, K unit) item is 2304
+//          contiguous bytes: [tiles][units][ 16 x 16-byte headers (d|dmin|scales) |
+//          4 groups p x 16 rows x 32 quant bytes ]. A pure permutation of the 144-byte
+//          blocks; rows past the last one are zero.
 //   Q2_K : the GGUF bytes unchanged, [rows][units][84].
 //   Q4_0 : quants [rows][units*8] x 16 bytes, scales [rows][units*8] fp16.
 //   Q8_0 : quants [rows][units*8] x 32 bytes, scales [rows][units*8] fp16.
@@ -42,6 +45,40 @@ struct QmGemvArgs {
     int32_t maxseg;          // partial-sum slots per (slice, tile)
     int32_t xop;             // QM_XOP_*
     float eps;
+};
+
+// One matvec of a fused sequence (Q4_K weights, integer tensor-core path).
+#define QM_Q4K_ITEM_BYTES 2304
+#define QM_MAX_INLINE_OPS 8
+
+struct QmOp {
+    const uint8_t *wq;   // tiled Q4_K store layout
+    const float *x;      // activations [m][ldx]
+    const float *x2;     // second operand of QM_XOP_ADD_RMSNORM / QM_XOP_SWIGLU, or null
+    float *y;            // outputs [m][ldy]
+    int64_t ldx, ldy;
+    int32_t rows, cols, units, tiles;   // units = K units of this op's K slice
+    int32_t units_total; // K units of a whole row of the matrix
+    int32_t unit0;       // first K unit of the slice
+    int32_t accumulate;  // 1: add to y instead of overwriting it (later K slices)
+    int32_t xop;         // QM_XOP_*
+    int32_t barrier;     // 1: every CTA must have finished the previous op before x is read
+    int32_t maxseg;      // partial-sum slots per tile
+    float eps;
+};
+
+struct QmFusedArgs {
+    QmOp inl[QM_MAX_INLINE_OPS];  // the ops of a single-matvec launch (used when ops is null)
+    const QmOp *ops;     // device array of nops ops, or null
+    float *partials;     // scratch [tiles][maxseg][8][16] partial sums (largest op)
+    unsigned int *tickets;   // scratch [tiles] arrival counters, zero between launches
+    unsigned int *status;    // device status word
+    unsigned int *grid_bar;  // grid barrier counter, zero at launch
+    int32_t nops, m;
+    int32_t consumers, depth;
+    int32_t max_units;   // largest K units over the ops: sizes the activation planes
+    int32_t cpm;         // mma columns per activation row: 4 (m <= 2) or 2 (m <= 4, or 8 with two column tiles)
+    int32_t debug;       // 0 in production
 };
 
 struct QmDequantArgs {

@@ -35,7 +35,7 @@ def test_null_arguments_are_errors_not_crashes():
 
 def test_kernel_images_and_descriptions_are_built():
     d = os.path.join(os.path.dirname(_capi._LIB_PATH), "csrc", "build")
-    for stem in ("qm_gemv", "qm_dequant"):
+    for stem in ("qm_gemv", "qm_dequant", "qm_gemv_q4k"):
         cubin = os.path.join(d, stem + ".sm_100a.cubin")
         assert os.path.getsize(cubin) > 1000
         assert open(cubin, "rb").read(4) == b"\x7fELF"

@@ -3,7 +3,9 @@ oracle's dequantize + float64 dot on the same seeded inputs.
 
 Tolerance: normwise relative error ||y - y_ref|| / ||y_ref|| <= 1e-3 (float32
 activations), the bound the benchmark specification states. The kernels keep
-activations to ~22 bits (fp16 hi+lo), so the tests also hold them to 2e-5."""
+activations to 21-22 bits (three 7-bit integer limbs, or fp16 hi+lo) for up to
+two activation rows and to 14 bits of each 256-column unit's maximum (two
+limbs) beyond, so the tests also hold them to 2e-5 and 3e-4 respectively."""
 import numpy as np
 import pytest
 
@@ -13,6 +15,10 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 SPEC_TOL = 1e-3
 TIGHT_TOL = 2e-5
+
+
+def tight(fmt, m):
+    return 3e-4 if (fmt == 12 and m > 2) else TIGHT_TOL
 
 
 def nre(got, want):
@@ -46,14 +52,14 @@ def test_benchmark_shapes(ctx, devbuf, fmt, rows, cols, m):
     raw, x, y = run_matvec(ctx, devbuf, fmt, rows, cols, m, seed=11 * fmt + m)
     want = oracle.MatVec(fmt, raw, rows, cols, x)
     e = nre(y, want)
-    assert e <= SPEC_TOL and e <= TIGHT_TOL, e
+    assert e <= SPEC_TOL and e <= tight(fmt, m), e
 
 
 @pytest.mark.parametrize("fmt", [2, 8, 12])
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 7, 8])
 def test_every_batch(ctx, devbuf, fmt, m):
     raw, x, y = run_matvec(ctx, devbuf, fmt, 256, 1024, m, seed=40 + m)
-    assert nre(y, oracle.MatVec(fmt, raw, 256, 1024, x)) <= TIGHT_TOL
+    assert nre(y, oracle.MatVec(fmt, raw, 256, 1024, x)) <= tight(fmt, m)
 
 
 @pytest.mark.parametrize("fmt,rows,cols", [
@@ -65,7 +71,7 @@ def test_ragged_shapes(ctx, devbuf, fmt, rows, cols):
     32-element formats, K that ends inside a 256-column unit."""
     for m in (1, 3, 8):
         raw, x, y = run_matvec(ctx, devbuf, fmt, rows, cols, m, seed=rows + cols + m)
-        assert nre(y, oracle.MatVec(fmt, raw, rows, cols, x)) <= TIGHT_TOL
+        assert nre(y, oracle.MatVec(fmt, raw, rows, cols, x)) <= tight(fmt, m)
 
 
 def test_split_k_path_and_repeat(ctx, devbuf):
@@ -82,7 +88,7 @@ def test_split_k_path_and_repeat(ctx, devbuf):
         ctx.sync()
         outs.append(yd.get((8, 4096)))
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
-    assert nre(outs[0], oracle.MatVec(12, raw, 4096, 14336, x)) <= TIGHT_TOL
+    assert nre(outs[0], oracle.MatVec(12, raw, 4096, 14336, x)) <= tight(12, 8)
     w.free()
 
 

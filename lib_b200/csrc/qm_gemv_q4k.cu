@@ -23,6 +23,12 @@
 //     unit against pre-reduced activation sums (fp16 hi+lo).
 // Everything up to the per-unit fp32 scaling is exact integer arithmetic.
 //
+// Work split. One persistent CTA per SM; an op's 16-row tiles are dealt to the CTAs in
+// contiguous runs, and inside a CTA the (tile, K unit) items of its run are dealt evenly to
+// the warps. A tile whose K range is shared by several warps is finished through
+// shared-memory partial sums added in warp order after one CTA barrier: no global scratch,
+// no atomics, bit-reproducible.
+//
 // Data movement. One persistent CTA per SM; every warp streams its share of the
 // (16-row tile, K unit) items of an op through a private ring of shared-memory
 // stages filled by 16-byte cp.async copies (one commit group per stage), so the
@@ -84,6 +90,17 @@ __device__ __forceinline__ void cp_async_wait(int n) {
     }
 }
 
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define QM_MARK(k)                                                                          \
+    do {                                                                                    \
+        if (a.debug == 9 && lane == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))  \
+            reinterpret_cast<unsigned long long *>(a.status + 16)[(((a.debug_slot & 3) * 2 + (blockIdx.x != 0)) * 16 + warp) * 8 + (k)] = gtime(); \
+    } while (0)
+
 constexpr int kRowTab = 64;     // bytes of one row of the per-warp scale table
 constexpr int kTabBytes = 16 * kRowTab;
 
@@ -95,7 +112,7 @@ constexpr int kCopiesPerLane = (kStageBytes / 16 + 31) / 32;   // 16-byte pieces
 
 struct Cursor {   // walks the items of this warp, op after op
     int op;
-    int64_t i, hi;        // current item and end of the warp's range in op
+    int i, hi;            // current item and end of the warp's range in op
     int tile, u, units;   // position and K units of the op's slice
     const uint8_t *src;   // store address of the current item
     int64_t tile_skip;    // bytes from the end of a tile's slice to the start of the next tile's
@@ -121,10 +138,13 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     float *red = reinterpret_cast<float *>(tabs + (size_t)C * kTabBytes);            // [32][8]
     float *s_scale = red + 32 * 8;                                                   // [8]
     constexpr int stage_bytes = kStageBytes;
-    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(s_scale + 8) + 127) & ~(uintptr_t)127);  // [C][D]
+    float *ssq = s_scale + 8;                                                        // [8][units]
+    float *slots = ssq + (size_t)8 * a.max_units;                                    // [C][2][M*16]
+    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(slots + (size_t)C * 2 * M * 16) + 127) & ~(uintptr_t)127);  // [C][D]
     uint8_t *my_stages = stages + (size_t)warp * D * stage_bytes;
     uint8_t *my_tab = tabs + (size_t)warp * kTabBytes;
 
+    QM_MARK(0);
     asm volatile("griddepcontrol.launch_dependents;");
     // columns of absent activation rows and pad columns must read as zero
     for (int i = tid; i < a.max_units * 8 * NT * 5; i += nthreads) xsum[i] = 0u;   // xsum and sxw are adjacent
@@ -132,12 +152,16 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
 
     // This warp's share of an op: warps are numbered warp-major over the CTAs so that a short
     // op still spreads over all SMs; every busy warp owns at least one item.
-    const int64_t vwarp = (int64_t)warp * gridDim.x + blockIdx.x;
-    auto op_range = [&](const QmOp &op, int64_t &lo, int64_t &hi, int64_t &Wt, int64_t &I) {
-        I = (int64_t)op.tiles * op.units;
-        Wt = min((int64_t)gridDim.x * C, I);
-        lo = vwarp < Wt ? vwarp * I / Wt : 0;
-        hi = vwarp < Wt ? (vwarp + 1) * I / Wt : 0;
+    // CTA-local item range [lo, hi) of this warp and first tile of the CTA's run
+    auto op_range = [&](const QmOp &op, int &lo, int &hi, int &tile0, int &wq, int &wrem) {
+        const int c = (int)blockIdx.x;
+        tile0 = c * op.q + min(c, op.rem);
+        const int ntc = op.q + (c < op.rem ? 1 : 0);
+        const unsigned int Ic = (unsigned int)ntc * (unsigned int)op.units;
+        wq = (int)(Ic / (unsigned int)C);
+        wrem = (int)(Ic - (unsigned int)wq * (unsigned int)C);
+        lo = warp * wq + min(warp, wrem);
+        hi = lo + wq + (warp < wrem ? 1 : 0);
     };
     auto cursor_at = [&](Cursor &c, int op) {
         c.op = op;
@@ -148,13 +172,14 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         c.tile_skip = 0;
         if (op < a.nops) {
             const QmOp o = ops[op];   // by value: the fields live in registers from here on
-            int64_t lo, Wt, I;
-            op_range(o, lo, c.hi, Wt, I);
+            int lo, hi, tile0, wq, wrem;
+            op_range(o, lo, hi, tile0, wq, wrem);
             c.i = lo;
+            c.hi = hi;
             c.units = o.units;
-            c.tile = (int)(lo / o.units);
-            c.u = (int)(lo - (int64_t)c.tile * o.units);
-            c.src = o.wq + ((int64_t)c.tile * o.units_total + o.unit0 + c.u) * QM_Q4K_ITEM_BYTES;
+            c.tile = (int)((unsigned)lo / (unsigned)o.units);   // CTA-local tile
+            c.u = lo - c.tile * o.units;
+            c.src = o.wq + ((int64_t)(tile0 + c.tile) * o.units_total + o.unit0 + c.u) * QM_Q4K_ITEM_BYTES;
             c.tile_skip = (int64_t)(o.units_total - o.units) * QM_Q4K_ITEM_BYTES;
         }
     };
@@ -188,7 +213,9 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         islot = islot + 1 == D ? 0 : islot + 1;
     };
     for (int d = 0; d < D; d++) issue();
+    QM_MARK(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    QM_MARK(2);
 
     // ---- lane roles on the activation side ---------------------------------------------------
     // mma column n = 8*nt + g holds limb (n % CPM) of activation row (n / CPM).
@@ -232,8 +259,13 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
             }
         }
         // ---- quantize the activations of this op into limbs, once per CTA ---------------------
+        // RMS normalisation is a scalar per activation row, so it commutes with the product:
+        // the raw activations are quantized and the scale is applied to the finished sums.
+        // The sum of squares is collected per K unit while staging (one pass over x); only an
+        // op that covers a slice of K needs a pass of its own over the whole row.
         const bool norm = (op.xop == 1 || op.xop == 2);
-        if (norm) {
+        const bool sliced = op.units != op.units_total;
+        if (norm && sliced) {
             for (int j = 0; j < M; j++) {
                 float s = 0.f;
                 const float *xr = op.x + (int64_t)j * op.ldx;
@@ -279,14 +311,14 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 for (int e = 0; e < 8; e++)
                     v[e] = op.xop == 2 ? v[e] + w[e] : v[e] / (1.f + __expf(-v[e])) * w[e];
             }
-            if (norm) {
-                const float sc = s_scale[j];
+            float amax = 0.f, sum = 0.f, sq = 0.f;
 #pragma unroll
-                for (int e = 0; e < 8; e++) v[e] *= sc;
+            for (int e = 0; e < 8; e++) { amax = fmaxf(amax, fabsf(v[e])); sum += v[e]; sq = fmaf(v[e], v[e], sq); }
+            if (norm && !sliced) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (lane == 0) ssq[j * a.max_units + ul] = sq;
             }
-            float amax = 0.f, sum = 0.f;
-#pragma unroll
-            for (int e = 0; e < 8; e++) { amax = fmaxf(amax, fabsf(v[e])); sum += v[e]; }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
@@ -328,10 +360,32 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         }
         __syncthreads();
 
+        float myscale[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) myscale[nt] = 1.f;
+        if (norm) {
+            for (int j = 0; j < M; j++) {
+                float sc;
+                if (sliced) {
+                    sc = s_scale[j];
+                } else {
+                    float sq = 0.f;
+                    for (int ul = lane; ul < nun; ul += 32) sq += ssq[j * a.max_units + ul];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                    sc = rsqrtf(sq / (float)op.cols + op.eps);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+                    if ((CPM == 4 ? 2 * nt + (t >> 1) : 4 * nt + t) == j) myscale[nt] = sc;
+            }
+        }
+        QM_MARK(3);
         // ---- stream this warp's chunks of the op ---------------------------------------------------
-        int64_t lo, hi, Wt, I;
-        op_range(op, lo, hi, Wt, I);
+        int lo, hi, tile0, wq, wrem;
+        op_range(op, lo, hi, tile0, wq, wrem);
         if (cc.op != opi) cursor_at(cc, opi);
+        int fin_tile = -1;   // CTA-local tile this warp finishes after the barrier
         float accF[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) accF[nt][0] = accF[nt][1] = accF[nt][2] = accF[nt][3] = 0.f;
@@ -355,11 +409,13 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                     jrow[nt] = 4 * nt + t;
                     valid[nt] = jrow[nt] < M;
                 }
+                vA[nt] *= myscale[nt];
+                vB[nt] *= myscale[nt];
             }
-            const int64_t i0 = (int64_t)tile * nun, i1 = i0 + nun - 1;
-            const int64_t vf = ((i0 + 1) * Wt - 1) / I, vl = ((i1 + 1) * Wt - 1) / I;
-            const int rA = tile * 16 + g, rB = rA + 8;
-            if (vf == vl) {
+            const int ts = tile * nun, te = ts + nun;   // CTA-local items of the tile
+            const bool from_start = lo <= ts, to_end = hi >= te;
+            if (from_start && to_end) {   // the whole K range of the tile was this warp's
+                const int rA = (tile0 + tile) * 16 + g, rB = rA + 8;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++)
                     if (valid[nt]) {
@@ -369,27 +425,13 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                     }
                 return;
             }
-            float *p = a.partials + ((size_t)tile * op.maxseg + (size_t)(vwarp - vf)) * 128;
+            // slot 1: this warp's range ends inside the tile; slot 0: it joined the tile late and
+            // reaches its end, so it adds up the tile after the barrier
+            float *p = slots + ((size_t)warp * 2 + (to_end ? 0 : 1)) * M * 16;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
                 if (valid[nt]) { p[jrow[nt] * 16 + g] = vA[nt]; p[jrow[nt] * 16 + g + 8] = vB[nt]; }
-            const unsigned int expected = (unsigned int)(vl - vf + 1);
-            __threadfence();
-            __syncwarp();
-            unsigned int old = 0;
-            if (lane == 0) old = atomicAdd(a.tickets + tile, 1u);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old != expected - 1) return;
-            __threadfence();
-            const float *q = a.partials + (size_t)tile * op.maxseg * 128;
-            for (int o = lane; o < 16 * M; o += 32) {
-                float s = 0.f;
-                for (unsigned int sg = 0; sg < expected; sg++) s += __ldcg(q + (size_t)sg * 128 + o);
-                const int j = o >> 4, r = o & 15;
-                float *yp = op.y + (int64_t)j * op.ldy + tile * 16 + r;
-                if (tile * 16 + r < op.rows) *yp = s + (op.accumulate ? __ldcg(yp) : 0.f);
-            }
-            if (lane == 0) a.tickets[tile] = 0u;  // ready for the next op or launch
+            if (to_end) fin_tile = tile;
         };
 
         // per-warp scale table of unit `un` of the landed stage, built by all 32 lanes:
@@ -500,6 +542,24 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
             issue();
         }
         if (lo < hi) flush(cur_tile);
+        QM_MARK(4);
+        __syncthreads();
+        QM_MARK(5);
+        if (fin_tile >= 0) {
+            // partial sums of the warps that worked on the tile before this one, in warp order
+            const unsigned int ts = (unsigned int)(fin_tile * nun), big = (unsigned int)wrem * (unsigned int)(wq + 1);
+            const int wf = wq == 0 ? (int)ts : ts < big ? (int)(ts / (unsigned int)(wq + 1))
+                                                         : wrem + (int)((ts - big) / (unsigned int)wq);
+            for (int o = lane; o < 16 * M; o += 32) {
+                float sum = 0.f;
+                for (int x = wf; x < warp; x++) sum += slots[((size_t)x * 2 + 1) * M * 16 + o];
+                sum += slots[(size_t)warp * 2 * M * 16 + o];
+                const int j = o >> 4, r = (tile0 + fin_tile) * 16 + (o & 15);
+                float *yp = op.y + (int64_t)j * op.ldy + r;
+                if (r < op.rows) *yp = sum + (op.accumulate ? __ldcg(yp) : 0.f);
+            }
+        }
+        QM_MARK(6);
     }
 }
 

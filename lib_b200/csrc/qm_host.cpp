@@ -168,8 +168,8 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             c->stream = c->own_stream;
         }
         if (!err) {
-            r = d->cuMemAlloc_v2(&c->status_dev, 256);
-            if (r == CUDA_SUCCESS) r = d->cuMemsetD8Async(c->status_dev, 0, 256, c->stream);
+            r = d->cuMemAlloc_v2(&c->status_dev, 32768);
+            if (r == CUDA_SUCCESS) r = d->cuMemsetD8Async(c->status_dev, 0, 32768, c->stream);
             if (r == CUDA_SUCCESS) r = d->cuMemAlloc_v2(&c->tickets_dev, QM_TICKETS * sizeof(unsigned));
             if (r == CUDA_SUCCESS) r = d->cuMemsetD8Async(c->tickets_dev, 0, QM_TICKETS * sizeof(unsigned), c->stream);
             if (r == CUDA_SUCCESS) r = d->cuMemAlloc_v2(&c->partials_dev, QM_PARTIALS_BYTES);
@@ -234,6 +234,16 @@ extern "C" int32_t qm_last_status(qm_ctx *c, uint32_t *status) {
     DRV(c->drv->cuMemcpyDtoH_v2(status, c->status_dev, 4));
     if (*status) DRV(c->drv->cuMemsetD8Async(c->status_dev, 0, 4, c->stream));
     return (*status & QM_STATUS_TIMEOUT) ? QM_ERR_TIMEOUT : QM_OK;
+}
+
+// Debug aid: raw copy of the device status block (status word + phase timestamps).
+extern "C" __attribute__((visibility("default"))) int32_t qm_debug_status(qm_ctx *c, void *out, int64_t bytes) {
+    CHECK_CTX(c);
+    CtxGuard g(c);
+    DRV(g.rc);
+    DRV(c->drv->cuStreamSynchronize(c->stream));
+    DRV(c->drv->cuMemcpyDtoH_v2(out, c->status_dev, (size_t)std::min<int64_t>(bytes, 32768)));
+    return QM_OK;
 }
 
 extern "C" int64_t qm_launch_count(qm_ctx *c) {
@@ -587,6 +597,8 @@ int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p) {
     return QM_OK;
 }
 
+int qm_fused_grid(qm_ctx *c) { return std::max(1, env_int("QM_GEMV_CTAS", c->sm_count)); }
+
 int32_t qm_plan_fused(qm_ctx *c, int32_t m, int32_t units, bool allow_slices, QmFusedPlan *p) {
     (void)c;
     p->nt = m <= 4 ? 1 : 2;
@@ -601,8 +613,8 @@ int32_t qm_plan_fused(qm_ctx *c, int32_t m, int32_t units, bool allow_slices, Qm
             int C = cd[0], D = cd[1];
             if (forced) { C = forced; D = env_int("QM_GEMV_D", 3); }
             if (C < 1 || C > QM_GEMV_MAX_THREADS / 32 || D < 1 || D > 8) return QM_ERR_ARG;
-            const int smem = planes * (ups * 256 + 64) + ups * 160 * p->nt + C * 1024 + 32 * 8 * 4 + 32 + 128 +
-                             C * D * QM_Q4K_ITEM_BYTES;
+            const int smem = planes * (ups * 256 + 64) + ups * 160 * p->nt + C * 1024 + 32 * 8 * 4 + 32 + ups * 32 +
+                             C * 2 * m * 64 + 128 + C * D * QM_Q4K_ITEM_BYTES;
             if (smem <= QM_GEMV_SMEM_MAX) {
                 p->consumers = C;
                 p->depth = D;
@@ -636,9 +648,10 @@ void qm_fill_op(qm_ctx *c, const QmFusedPlan &p, const QmWeight *w, uint64_t x, 
     op->tiles = (int32_t)((w->rows + 15) / 16);
     op->xop = (int32_t)xop;
     op->barrier = barrier;
-    const int64_t I = (int64_t)op->tiles * op->units;
-    const int64_t Wt = std::min<int64_t>((int64_t)c->sm_count * p.consumers, I);
-    op->maxseg = (int32_t)std::min<int64_t>(op->units, (int64_t)(op->units - 1) * Wt / I + 2);
+    const int grid = qm_fused_grid(c);
+    op->q = op->tiles / grid;
+    op->rem = op->tiles % grid;
+    (void)p;
     op->eps = 1e-6f;
 }
 
@@ -649,12 +662,10 @@ static int32_t fused_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev,
     for (int s = 0; s < p.slices; s++) {
         const int u0 = s * p.units_per_slice, n = std::min(p.units_per_slice, w->units - u0);
         qm_fill_op(c, p, w, x_dev, x2_dev, ldx, y_dev, ldy, flags & 0xFu, s > 0, u0, n, s > 0, &a.inl[s]);
-        if (a.inl[s].tiles > QM_TICKETS || (int64_t)a.inl[s].tiles * a.inl[s].maxseg * 512 > QM_PARTIALS_BYTES)
+        if ((int64_t)a.inl[s].tiles * a.inl[s].units >= (1ll << 31))
             return QM_ERR_SHAPE;
     }
     a.ops = nullptr;
-    a.partials = (float *)(uintptr_t)c->partials_dev;
-    a.tickets = (unsigned int *)(uintptr_t)c->tickets_dev;
     a.status = (unsigned int *)(uintptr_t)c->status_dev;
     a.grid_bar = (unsigned int *)(uintptr_t)c->gridbar_dev;
     a.nops = p.slices;
@@ -664,11 +675,12 @@ static int32_t fused_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev,
     a.max_units = p.max_units;
     a.cpm = p.cpm;
     a.debug = env_int("QM_DEBUG_SKIP", 0);
+    a.debug_slot = (int32_t)(c->launches & 3);
     const bool coop = p.slices > 1;  // K slices meet at a grid barrier: all CTAs must be co-resident
     if (coop) DRV(c->drv->cuMemsetD32Async(c->gridbar_dev, 0, 1, c->stream));
     return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2,
-                        (unsigned)std::max(1, env_int("QM_GEMV_CTAS", c->sm_count)), (unsigned)p.consumers * 32,
-                        (unsigned)p.smem, &a, (flags & QM_FLAG_PDL) != 0 && !coop, coop);
+                        (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32, (unsigned)p.smem, &a,
+                        (flags & QM_FLAG_PDL) != 0 && !coop, coop);
 }
 
 int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,

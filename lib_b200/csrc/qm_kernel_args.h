@@ -63,15 +63,15 @@ struct QmOp {
     int32_t accumulate;  // 1: add to y instead of overwriting it (later K slices)
     int32_t xop;         // QM_XOP_*
     int32_t barrier;     // 1: every CTA must have finished the previous op before x is read
-    int32_t maxseg;      // partial-sum slots per tile
     float eps;
+    // the tiles of the op are dealt to the CTAs in contiguous runs: CTA c owns q tiles, the first
+    // `rem` CTAs one more
+    int32_t q, rem;
 };
 
 struct QmFusedArgs {
     QmOp inl[QM_MAX_INLINE_OPS];  // the ops of a single-matvec launch (used when ops is null)
     const QmOp *ops;     // device array of nops ops, or null
-    float *partials;     // scratch [tiles][maxseg][8][16] partial sums (largest op)
-    unsigned int *tickets;   // scratch [tiles] arrival counters, zero between launches
     unsigned int *status;    // device status word
     unsigned int *grid_bar;  // grid barrier counter, zero at launch
     int32_t nops, m;
@@ -79,6 +79,7 @@ struct QmFusedArgs {
     int32_t max_units;   // largest K units over the ops: sizes the activation planes
     int32_t cpm;         // mma columns per activation row: 4 (m <= 2) or 2 (m <= 4, or 8 with two column tiles)
     int32_t debug;       // 0 in production
+    int32_t debug_slot, pad2;
 };
 
 struct QmDequantArgs {

@@ -7,6 +7,7 @@
 // (nvidia/driver/stream.gen.go:115, graph.gen.go:651, graph_exec.gen.go:354).
 #include <string.h>
 
+#include <algorithm>
 #include <new>
 #include <vector>
 
@@ -24,7 +25,9 @@ struct qm_stack {
     std::vector<QmLayer> layer;
     CUdeviceptr h0, qkv_out, o_out, gu_out, dn_out;  // activations
     CUgraphExec graph[9];
-    bool use_graph;
+    CUdeviceptr ops_dev[9];     // fused op lists, one per batch size
+    QmFusedPlan fused_plan[9];
+    bool use_graph, use_fused;
 };
 
 static qm_stack *stack_check(qm_stack *s) { return (s && s->magic == QM_STACK_MAGIC) ? s : nullptr; }
@@ -48,7 +51,9 @@ extern "C" int32_t qm_stack_create(qm_ctx *c, int32_t layers, int32_t hidden, in
     s->layer.resize(layers);
     memset(s->layer.data(), 0, sizeof(QmLayer) * layers);
     memset(s->graph, 0, sizeof s->graph);
+    memset(s->ops_dev, 0, sizeof s->ops_dev);
     s->use_graph = true;
+    s->use_fused = true;
     CtxGuard g(c);
     CUresult r = g.rc;
     const size_t f = 4;
@@ -71,8 +76,10 @@ extern "C" int32_t qm_stack_destroy(qm_ctx *c, qm_stack *s) {
     CtxGuard g(c);
     DRV(g.rc);
     c->drv->cuStreamSynchronize(c->stream);
-    for (int i = 0; i < 9; i++)
+    for (int i = 0; i < 9; i++) {
         if (s->graph[i]) c->drv->cuGraphExecDestroy(s->graph[i]);
+        if (s->ops_dev[i]) c->drv->cuMemFree_v2(s->ops_dev[i]);
+    }
     CUdeviceptr bufs[5] = {s->h0, s->qkv_out, s->o_out, s->gu_out, s->dn_out};
     for (CUdeviceptr b : bufs)
         if (b) c->drv->cuMemFree_v2(b);
@@ -94,12 +101,16 @@ extern "C" int32_t qm_stack_set_layer(qm_ctx *c, qm_stack *s, int32_t layer, qm_
     for (int i = 0; i < 4; i++)
         if (w[i]->rows != want[i][0] || w[i]->cols != want[i][1]) return QM_ERR_SHAPE;
     s->layer[layer] = QmLayer{w[0], w[1], w[2], w[3]};
-    for (int i = 0; i < 9; i++)
-        if (s->graph[i]) {
-            CtxGuard g(c);
-            c->drv->cuGraphExecDestroy(s->graph[i]);
-            s->graph[i] = nullptr;
+    for (int i = 0; i < 9; i++) {
+        CtxGuard g(c);
+        if (s->graph[i]) c->drv->cuGraphExecDestroy(s->graph[i]);
+        s->graph[i] = nullptr;
+        if (s->ops_dev[i]) {
+            c->drv->cuStreamSynchronize(c->stream);
+            c->drv->cuMemFree_v2(s->ops_dev[i]);
         }
+        s->ops_dev[i] = 0;
+    }
     return QM_OK;
 }
 
@@ -117,11 +128,77 @@ extern "C" int32_t qm_stack_buffers(qm_ctx *c, qm_stack *s, uint64_t *ptrs5) {
     return QM_OK;
 }
 
+// on: 0 = one launch per matvec, issued one by one; 1 = the same launches replayed as a
+// captured graph; 2 (default) = the whole step as ONE persistent launch where the format
+// and the shapes allow it (Q4_K, activations of the longest K fit in shared memory),
+// falling back to 1 otherwise.
 extern "C" int32_t qm_stack_use_graph(qm_ctx *c, qm_stack *s, int32_t on) {
     CHECK_CTX(c);
     if (!stack_check(s)) return QM_ERR_ARG;
     s->use_graph = on != 0;
+    s->use_fused = on == 2;
     return QM_OK;
+}
+
+// Builds the op list of a whole step for batch m; QM_ERR_SHAPE/FORMAT when the step cannot
+// run as one launch.
+static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
+    int max_units = 0;
+    for (int L = 0; L < s->layers; L++) {
+        const QmLayer &ly = s->layer[L];
+        if (!ly.qkv) return QM_ERR_STATE;
+        const QmWeight *ws[4] = {ly.qkv, ly.o, ly.gu, ly.dn};
+        for (const QmWeight *w : ws) {
+            if (w->fmt != QM_FMT_Q4_K) return QM_ERR_FORMAT;
+            max_units = std::max(max_units, (int)w->units);
+        }
+    }
+    QmFusedPlan p;
+    int32_t rc = qm_plan_fused(c, m, max_units, false, &p);
+    if (rc) return rc;
+    std::vector<QmOp> ops((size_t)4 * s->layers);
+    const int64_t qkv_ld = s->hidden + 2 * s->kv;
+    for (int L = 0; L < s->layers; L++) {
+        const QmLayer &ly = s->layer[L];
+        const CUdeviceptr qkv = s->qkv_out + (size_t)L * m * qkv_ld * 4;
+        QmOp *o = &ops[(size_t)4 * L];
+        qm_fill_op(c, p, ly.qkv, L == 0 ? s->h0 : s->dn_out, 0, s->hidden, qkv, qkv_ld, QM_XOP_RMSNORM, L > 0, 0,
+                   ly.qkv->units, 0, o + 0);
+        qm_fill_op(c, p, ly.o, qkv, 0, qkv_ld, s->o_out, s->hidden, QM_XOP_RMSNORM, 1, 0, ly.o->units, 0, o + 1);
+        qm_fill_op(c, p, ly.gu, s->o_out, 0, s->hidden, s->gu_out, 2 * s->ffn, QM_XOP_RMSNORM, 1, 0, ly.gu->units, 0,
+                   o + 2);
+        qm_fill_op(c, p, ly.dn, s->gu_out, s->gu_out + (size_t)s->ffn * 4, 2 * s->ffn, s->dn_out, s->hidden,
+                   QM_XOP_ADD_RMSNORM, 1, 0, ly.dn->units, 0, o + 3);
+    }
+    CUdeviceptr dev = 0;
+    DRV(c->drv->cuMemAlloc_v2(&dev, ops.size() * sizeof(QmOp)));
+    CUresult r = c->drv->cuMemcpyHtoD_v2(dev, ops.data(), ops.size() * sizeof(QmOp));
+    if (r != CUDA_SUCCESS) {
+        c->drv->cuMemFree_v2(dev);
+        return (int32_t)r;
+    }
+    s->ops_dev[m] = dev;
+    s->fused_plan[m] = p;
+    return QM_OK;
+}
+
+static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
+    const QmFusedPlan &p = s->fused_plan[m];
+    QmFusedArgs a;
+    memset(&a, 0, sizeof a);
+    a.ops = (const QmOp *)(uintptr_t)s->ops_dev[m];
+    a.status = (unsigned int *)(uintptr_t)c->status_dev;
+    a.grid_bar = (unsigned int *)(uintptr_t)c->gridbar_dev;
+    a.nops = 4 * s->layers;
+    a.m = m;
+    a.consumers = p.consumers;
+    a.depth = p.depth;
+    a.max_units = p.max_units;
+    a.cpm = p.cpm;
+    DRV(c->drv->cuMemsetD32Async(c->gridbar_dev, 0, 1, c->stream));
+    // cooperative: the grid barrier between dependent matvecs needs every CTA resident
+    return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2, (unsigned)qm_fused_grid(c),
+                        (unsigned)p.consumers * 32, (unsigned)p.smem, &a, false, true);
 }
 
 // The launches of one step for batch m, in stream order.
@@ -147,6 +224,11 @@ static int32_t enqueue_layers(qm_ctx *c, qm_stack *s, int m, int upto_layers) {
 }
 
 static int32_t step_device(qm_ctx *c, qm_stack *s, int m) {
+    if (s->use_graph && s->use_fused) {
+        int32_t rc = s->ops_dev[m] ? QM_OK : build_fused(c, s, m);
+        if (rc == QM_OK) return launch_fused(c, s, m);
+        if (rc != QM_ERR_SHAPE && rc != QM_ERR_FORMAT) return rc;
+    }
     if (!s->use_graph) return enqueue_layers(c, s, m, s->layers);
     if (!s->graph[m]) {
         QmDriver *d = c->drv;

@@ -54,6 +54,9 @@ class SingleGpuDecode:
             ws = [upload_rows(ctx, fmt, rows, cols, parts)
                   for rows, cols, parts in stacked(layer_tensors(fmt, hidden, kv, ffn, seed, L))]
             self.stack.set_layer(L, *ws)
+        import os
+        if os.environ.get("QM_STACK_MODE"):
+            self.stack.use_graph(int(os.environ["QM_STACK_MODE"]))
 
     def step_device(self, x_dev, m, h_dev):
         self.stack.step(x_dev.data_ptr(), m, self.hidden, h_dev.data_ptr(), self.hidden)

@@ -52,12 +52,14 @@ def test_small_stack_matches_oracle(ctx, fmt, m):
     want_h, want_kv, _ = oracle_chain(fmt, raws, x, hidden, kv, ffn)
     assert nre(h, want_h) <= TOL
     assert nre(kvs, want_kv) <= TOL
-    # replaying the graph gives the same bits; so does issuing the launches one by one
+    # the step runs as one persistent launch where it can (mode 2, the default); repeating it,
+    # replaying it as a graph of per-matvec launches (1) and issuing those one by one (0) all
+    # give the same bits
     h2 = st.step_host(x)
     assert np.array_equal(h, h2)
-    st.use_graph(False)
-    h3 = st.step_host(x)
-    assert np.array_equal(h, h3)
+    for mode in (1, 0, 2):
+        st.use_graph(mode)
+        assert np.array_equal(h, st.step_host(x)), mode
     st.close()
 
 

@@ -95,10 +95,12 @@ __device__ __forceinline__ unsigned long long gtime() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+// Debug aid (a.debug == 9): phase timestamps of op a.debug_slot for the first and last CTA.
 #define QM_MARK(k)                                                                          \
     do {                                                                                    \
-        if (a.debug == 9 && lane == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))  \
-            reinterpret_cast<unsigned long long *>(a.status + 16)[(((a.debug_slot & 3) * 2 + (blockIdx.x != 0)) * 16 + warp) * 8 + (k)] = gtime(); \
+        if (a.debug == 9 && lane == 0 && mark_op == a.debug_slot &&                        \
+            (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))                               \
+            reinterpret_cast<unsigned long long *>(a.status + 16)[((blockIdx.x != 0) * 16 + warp) * 8 + (k)] = gtime(); \
     } while (0)
 
 constexpr int kRowTab = 64;     // bytes of one row of the per-warp scale table
@@ -144,7 +146,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     uint8_t *my_stages = stages + (size_t)warp * D * stage_bytes;
     uint8_t *my_tab = tabs + (size_t)warp * kTabBytes;
 
-    QM_MARK(0);
+    int mark_op = -1;
     asm volatile("griddepcontrol.launch_dependents;");
     // columns of absent activation rows and pad columns must read as zero
     for (int i = tid; i < a.max_units * 8 * NT * 5; i += nthreads) xsum[i] = 0u;   // xsum and sxw are adjacent
@@ -213,9 +215,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         islot = islot + 1 == D ? 0 : islot + 1;
     };
     for (int d = 0; d < D; d++) issue();
-    QM_MARK(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    QM_MARK(2);
 
     // ---- lane roles on the activation side ---------------------------------------------------
     // mma column n = 8*nt + g holds limb (n % CPM) of activation row (n / CPM).
@@ -236,6 +236,8 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
 
     for (int opi = 0; opi < a.nops; opi++) {
         const QmOp op = ops[opi];   // by value: no reloads through the generic pointer
+        mark_op = opi;
+        QM_MARK(0);
         const int nun = op.units;
         // ---- wait for the producers of x, and for this CTA's readers of the old planes --------
         if (opi > 0) {
@@ -258,6 +260,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 __syncthreads();
             }
         }
+        QM_MARK(1);
         // ---- quantize the activations of this op into limbs, once per CTA ---------------------
         // RMS normalisation is a scalar per activation row, so it commutes with the product:
         // the raw activations are quantized and the scale is applied to the finished sums.
@@ -291,26 +294,33 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
             }
             __syncthreads();
         }
-        for (int idx = warp; idx < M * nun; idx += C) {
+        // the loads of the next (row, unit) pair are in flight while this one is quantized
+        auto load_raw = [&](int idx, float4 (&r)[4]) {
             const int j = idx / nun, ul = idx - j * nun;
             const int col = (op.unit0 + ul) * QM_K_UNIT + lane * 8;
             const float *xp = op.x + (int64_t)j * op.ldx + col;
-            float v[8];
-            {
-                const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(xp));
-                const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(xp + 4));
-                v[0] = p0.x; v[1] = p0.y; v[2] = p0.z; v[3] = p0.w;
-                v[4] = p1.x; v[5] = p1.y; v[6] = p1.z; v[7] = p1.w;
-            }
+            r[0] = __ldcg(reinterpret_cast<const float4 *>(xp));
+            r[1] = __ldcg(reinterpret_cast<const float4 *>(xp + 4));
             if (op.xop >= 2) {
                 const float *x2p = op.x2 + (int64_t)j * op.ldx + col;
-                const float4 q0 = __ldcg(reinterpret_cast<const float4 *>(x2p));
-                const float4 q1 = __ldcg(reinterpret_cast<const float4 *>(x2p + 4));
-                const float w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                r[2] = __ldcg(reinterpret_cast<const float4 *>(x2p));
+                r[3] = __ldcg(reinterpret_cast<const float4 *>(x2p + 4));
+            }
+        };
+        float4 raw[4], raw_next[4];
+        if (warp < M * nun) load_raw(warp, raw);
+        for (int idx = warp; idx < M * nun; idx += C) {
+            const int j = idx / nun, ul = idx - j * nun;
+            if (idx + C < M * nun) load_raw(idx + C, raw_next);
+            float v[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
+            if (op.xop >= 2) {
+                const float w[8] = {raw[2].x, raw[2].y, raw[2].z, raw[2].w, raw[3].x, raw[3].y, raw[3].z, raw[3].w};
 #pragma unroll
                 for (int e = 0; e < 8; e++)
                     v[e] = op.xop == 2 ? v[e] + w[e] : v[e] / (1.f + __expf(-v[e])) * w[e];
             }
+#pragma unroll
+            for (int e = 0; e < 4; e++) raw[e] = raw_next[e];
             float amax = 0.f, sum = 0.f, sq = 0.f;
 #pragma unroll
             for (int e = 0; e < 8; e++) { amax = fmaxf(amax, fabsf(v[e])); sum += v[e]; sq = fmaf(v[e], v[e], sq); }
@@ -325,20 +335,29 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             const float sx = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
             const float inv = amax > 0.f ? 127.f / amax : 0.f;
-            uint32_t w0[3] = {0, 0, 0}, w1[3] = {0, 0, 0};
+            // Limbs by magic-number rounding: adding 1.5*2^23 rounds to the nearest integer and
+            // leaves it (two's complement) in the low mantissa bits — no conversion instructions.
+            uint32_t hb[8], l1b[8], l2b[8];
+            constexpr float kMagicF = 12582912.f;
 #pragma unroll
             for (int e = 0; e < 8; e++) {
                 const float r = v[e] * inv;
-                const int h = __float2int_rn(r);
-                const float r1 = (r - (float)h) * 128.f;
-                const int l1 = __float2int_rn(r1);
-                const int l2 = __float2int_rn((r1 - (float)l1) * 128.f);
-                const int sh = (e & 3) * 8;
-                uint32_t *dstw = e < 4 ? w0 : w1;
-                dstw[0] |= ((uint32_t)h & 0xFFu) << sh;
-                dstw[1] |= ((uint32_t)l1 & 0xFFu) << sh;
-                dstw[2] |= ((uint32_t)l2 & 0xFFu) << sh;
+                const float t0 = r + kMagicF;
+                const float r1 = (r - (t0 - kMagicF)) * 128.f;
+                const float t1 = r1 + kMagicF;
+                const float r2 = (r1 - (t1 - kMagicF)) * 128.f;
+                const float t2 = r2 + kMagicF;
+                hb[e] = __float_as_uint(t0);
+                l1b[e] = __float_as_uint(t1);
+                l2b[e] = __float_as_uint(t2);
             }
+            auto pack4 = [](uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) -> uint32_t {
+                return prmt(prmt(b0, b1, 0x0040u), prmt(b2, b3, 0x0040u), 0x5410u);  // low bytes of the four
+            };
+            const uint32_t w0[3] = {pack4(hb[0], hb[1], hb[2], hb[3]), pack4(l1b[0], l1b[1], l1b[2], l1b[3]),
+                                    pack4(l2b[0], l2b[1], l2b[2], l2b[3])};
+            const uint32_t w1[3] = {pack4(hb[4], hb[5], hb[6], hb[7]), pack4(l1b[4], l1b[5], l1b[6], l1b[7]),
+                                    pack4(l2b[4], l2b[5], l2b[6], l2b[7])};
             // lane = 4*sub-block + t': this lane's 8 columns are the B fragment of lane t' for
             // sub-block sb; the fragments of sub-blocks 2p and 2p+1 sit side by side
             const int sb = lane >> 2, tq = lane & 3;
@@ -347,8 +366,11 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 *reinterpret_cast<uint2 *>(xs + (size_t)(j * NL + l) * plane_stride + off) = make_uint2(w0[l], w1[l]);
             const int n0 = j * CPM;   // first mma column of this activation row
             if (tq == 0) {
-                const __half sh = __float2half_rn(sum);
-                const __half sl = __float2half_rn(sum - __half2float(sh));
+                // sub-block sums in units of the unit's maximum (|.| <= 32): safe in fp16 whatever
+                // the magnitude of the activations; the factor comes back with the column weight
+                const float sn = sum * inv * (1.f / 127.f);
+                const __half sh = __float2half_rn(sn);
+                const __half sl = __float2half_rn(sn - __half2float(sh));
                 __half *xh = reinterpret_cast<__half *>(xsum);
                 xh[((size_t)ul * 8 * NT + n0) * 8 + sb] = sh;
                 xh[((size_t)ul * 8 * NT + n0 + 1) * 8 + sb] = sl;
@@ -380,7 +402,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                     if ((CPM == 4 ? 2 * nt + (t >> 1) : 4 * nt + t) == j) myscale[nt] = sc;
             }
         }
-        QM_MARK(3);
+        QM_MARK(2);
         // ---- stream this warp's chunks of the op ---------------------------------------------------
         int lo, hi, tile0, wq, wrem;
         op_range(op, lo, hi, tile0, wq, wrem);
@@ -443,8 +465,10 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
             const uint32_t scv = half == 0 ? (S0 & 0x3F3F3F3Fu) : ((S2 & 0x0F0F0F0Fu) | ((S0 >> 2) & 0x30303030u));
             const uint32_t mv = half == 0 ? (S1 & 0x3F3F3F3Fu) : (((S2 >> 4) & 0x0F0F0F0Fu) | ((S1 >> 2) & 0x30303030u));
             uint8_t *r = tab + row * kRowTab;
+            // even sub-blocks (low nibbles) carry a factor 16 so that they add up with the odd ones,
+            // whose nibbles stay in place and are sixteen times too large
             *reinterpret_cast<uint4 *>(r + half * 16) =
-                make_uint4(scv & 0xFF, (scv >> 8) & 0xFF, (scv >> 16) & 0xFF, scv >> 24);
+                make_uint4((scv & 0xFF) << 4, (scv >> 8) & 0xFF, ((scv >> 16) & 0xFF) << 4, scv >> 24);
             const uint32_t m01 = hsub2(prmt(mv, 0x64646464u, 0x4140u), 0x64006400u);
             const uint32_t m23 = hsub2(prmt(mv, 0x64646464u, 0x4342u), 0x64006400u);
             *reinterpret_cast<uint2 *>(r + 32 + half * 8) = make_uint2(m01, m23);
@@ -479,11 +503,11 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 const uint4 sB1 = *reinterpret_cast<const uint4 *>(tab + (g + 8) * kRowTab + 16);
                 const int scA[8] = {(int)sA0.x, (int)sA0.y, (int)sA0.z, (int)sA0.w, (int)sA1.x, (int)sA1.y, (int)sA1.z, (int)sA1.w};
                 const int scB[8] = {(int)sB0.x, (int)sB0.y, (int)sB0.z, (int)sB0.w, (int)sB1.x, (int)sB1.y, (int)sB1.z, (int)sB1.w};
-                int accL[NT][4], accH[NT][4];
+                int accI[NT][4];   // sixteen times the scaled integer sums: < 2^30
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-                    for (int c = 0; c < 4; c++) accL[nt][c] = accH[nt][c] = 0;
+                    for (int c = 0; c < 4; c++) accI[nt][c] = 0;
                 const uint8_t *rowA = stage + 256 + 32 * g + 8 * t;
                 const uint8_t *rowB = rowA + 256;
 #pragma unroll
@@ -500,15 +524,15 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                         if (bact[nt]) b = *reinterpret_cast<const uint4 *>(bplane[nt] + (ul * 4 + p) * 64);
                         int S[4];
                         mma_u8s8(S, a0, a1, a2, a3, b.x, b.y);
-                        accL[nt][0] += scA[2 * p] * S[0];
-                        accL[nt][1] += scA[2 * p] * S[1];
-                        accL[nt][2] += scB[2 * p] * S[2];
-                        accL[nt][3] += scB[2 * p] * S[3];
+                        accI[nt][0] += scA[2 * p] * S[0];
+                        accI[nt][1] += scA[2 * p] * S[1];
+                        accI[nt][2] += scB[2 * p] * S[2];
+                        accI[nt][3] += scB[2 * p] * S[3];
                         mma_u8s8(S, h0, h1, h2, h3, b.z, b.w);   // sixteen times the sub-block sums
-                        accH[nt][0] += scA[2 * p + 1] * S[0];
-                        accH[nt][1] += scA[2 * p + 1] * S[1];
-                        accH[nt][2] += scB[2 * p + 1] * S[2];
-                        accH[nt][3] += scB[2 * p + 1] * S[3];
+                        accI[nt][0] += scA[2 * p + 1] * S[0];
+                        accI[nt][1] += scA[2 * p + 1] * S[1];
+                        accI[nt][2] += scB[2 * p + 1] * S[2];
+                        accI[nt][3] += scB[2 * p + 1] * S[3];
                     }
                 }
                 const uint32_t mpA = *reinterpret_cast<const uint32_t *>(tab + g * kRowTab + 32 + 4 * t);
@@ -521,14 +545,15 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                     float accM[4];
                     const uint32_t bm = mact[nt] ? xsum[((size_t)ul * 8 * NT + 8 * nt + g) * 4 + t] : 0u;
                     mma_f16(accM, mpA, mpB, bm);
-                    const float f0 = (float)accL[nt][0] + (float)accH[nt][0] * 0.0625f;
-                    const float f1 = (float)accL[nt][1] + (float)accH[nt][1] * 0.0625f;
-                    const float f2 = (float)accL[nt][2] + (float)accH[nt][2] * 0.0625f;
-                    const float f3 = (float)accL[nt][3] + (float)accH[nt][3] * 0.0625f;
-                    accF[nt][0] = fmaf(ddA.x * cw.x, f0, fmaf(-ddA.y, accM[0], accF[nt][0]));
-                    accF[nt][1] = fmaf(ddA.x * cw.y, f1, fmaf(-ddA.y, accM[1], accF[nt][1]));
-                    accF[nt][2] = fmaf(ddB.x * cw.x, f2, fmaf(-ddB.y, accM[2], accF[nt][2]));
-                    accF[nt][3] = fmaf(ddB.x * cw.y, f3, fmaf(-ddB.y, accM[3], accF[nt][3]));
+                    const float f0 = (float)accI[nt][0] * 0.0625f, f1 = (float)accI[nt][1] * 0.0625f;
+                    const float f2 = (float)accI[nt][2] * 0.0625f, f3 = (float)accI[nt][3] * 0.0625f;
+                    // even column: first limb / high half of the sums, weight sx; odd column:
+                    // second limb / low half, weight sx/128; the sums are in units of 127*sx
+                    const float mx = 127.f * cw.x, my = 16256.f * cw.y;
+                    accF[nt][0] = fmaf(ddA.x * cw.x, f0, fmaf(-ddA.y * mx, accM[0], accF[nt][0]));
+                    accF[nt][1] = fmaf(ddA.x * cw.y, f1, fmaf(-ddA.y * my, accM[1], accF[nt][1]));
+                    accF[nt][2] = fmaf(ddB.x * cw.x, f2, fmaf(-ddB.y * mx, accM[2], accF[nt][2]));
+                    accF[nt][3] = fmaf(ddB.x * cw.y, f3, fmaf(-ddB.y * my, accM[3], accF[nt][3]));
                 }
                 __syncwarp();   // all lanes are done with the table before it is rebuilt
             }
@@ -542,9 +567,9 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
             issue();
         }
         if (lo < hi) flush(cur_tile);
-        QM_MARK(4);
+        QM_MARK(3);
         __syncthreads();
-        QM_MARK(5);
+        QM_MARK(4);
         if (fin_tile >= 0) {
             // partial sums of the warps that worked on the tile before this one, in warp order
             const unsigned int ts = (unsigned int)(fin_tile * nun), big = (unsigned int)wrem * (unsigned int)(wq + 1);
@@ -559,7 +584,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 if (r < op.rows) *yp = sum + (op.accumulate ? __ldcg(yp) : 0.f);
             }
         }
-        QM_MARK(6);
+        QM_MARK(5);
     }
 }
 

@@ -554,7 +554,9 @@ extern "C" int32_t qm_dequantize_host(qm_ctx *c, int32_t fmt, const void *data, 
 }
 
 // ---- matvec ---------------------------------------------------------------------------------
-static int env_int(const char *name, int dflt) {
+int qm_env_int(const char *name, int dflt);
+static int env_int(const char *name, int dflt) { return qm_env_int(name, dflt); }
+int qm_env_int(const char *name, int dflt) {
     const char *s = getenv(name);
     return (s && *s) ? atoi(s) : dflt;
 }
@@ -675,7 +677,7 @@ static int32_t fused_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev,
     a.max_units = p.max_units;
     a.cpm = p.cpm;
     a.debug = env_int("QM_DEBUG_SKIP", 0);
-    a.debug_slot = (int32_t)(c->launches & 3);
+    a.debug_slot = env_int("QM_DEBUG_OP", 0);
     const bool coop = p.slices > 1;  // K slices meet at a grid barrier: all CTAs must be co-resident
     if (coop) DRV(c->drv->cuMemsetD32Async(c->gridbar_dev, 0, 1, c->stream));
     return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2,

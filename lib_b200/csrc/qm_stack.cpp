@@ -195,6 +195,8 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
     a.depth = p.depth;
     a.max_units = p.max_units;
     a.cpm = p.cpm;
+    a.debug = qm_env_int("QM_DEBUG_SKIP", 0);
+    a.debug_slot = qm_env_int("QM_DEBUG_OP", 0);
     DRV(c->drv->cuMemsetD32Async(c->gridbar_dev, 0, 1, c->stream));
     // cooperative: the grid barrier between dependent matvecs needs every CTA resident
     return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2, (unsigned)qm_fused_grid(c),

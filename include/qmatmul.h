@@ -137,6 +137,27 @@ QM_API int32_t qm_matvec(qm_ctx *ctx, qm_weight w, uint64_t x_dev, uint64_t x2_d
 QM_API int32_t qm_matvec_host(qm_ctx *ctx, qm_weight w, const float *x_host, int32_t m, int64_t ldx,
                        float *y_host, int64_t ldy, uint32_t flags);
 
+/* No counterpart in the reference. The Q4_0 / Q8_0 matvec of qm_matvec for callers that may
+ * not allocate device memory at the point of the call: a server whose memory plan is frozen
+ * once it starts serving, a latency-critical loop where an allocation would stall the device,
+ * or a host framework that owns the allocator and forbids allocations by the libraries it
+ * calls. The split-K scratch (partial sums, arrival tickets, status word) lives in a fixed
+ * 4 MiB array inside the library image, held by every GPU that loads the library until the
+ * process exits; nothing is allocated or freed by this call, ever.
+ *   w        a stored Q4_0 or Q8_0 matrix (its device memory was allocated when it was stored)
+ *   x_dev    float32 [m][ldx], 16-byte aligned, ldx a multiple of 4; y_dev float32 [m][ldy]
+ *   m        1..8 activation rows
+ *   cu_stream  the CUstream to launch on (0 = the default stream); the call does not wait
+ * The pointers belong to the current device's primary context. Returns QM_ERR_LIMIT when the
+ * matrix needs more scratch than the array holds (scratch = 512 bytes per 16-row tile, per K
+ * slice, per warp group sharing a tile, plus 4 bytes per tile), QM_ERR_FORMAT for other
+ * formats. The first call on a device resolves the array's device address and raises the
+ * kernels' shared-memory limit: make it outside any stream capture. All calls on a device
+ * share the array; each clears the words it needs at zero, and calls whose kernels overlap on
+ * the GPU race on it — order them on one stream or with events. */
+QM_API int32_t qm_matvec_noalloc(qm_weight w, uint64_t x_dev, int32_t m, int64_t ldx, uint64_t y_dev,
+                                 int64_t ldy, uint64_t cu_stream);
+
 /* Decode step over a stack of layers whose matrices are stored weights of one
  * format: per layer q|k|v [hidden+2*kv_dim][hidden], o [hidden][hidden],
  * gate|up [2*ffn][hidden] and down [hidden][ffn], each matvec reading the RMS

@@ -51,6 +51,7 @@ def _load():
         "qm_dequantize_host": (i32, [p, i32, p, i64, i64, p]),
         "qm_matvec": (i32, [p, u64, u64, u64, i32, i64, u64, i64, u32]),
         "qm_matvec_host": (i32, [p, u64, p, i32, i64, p, i64, u32]),
+        "qm_matvec_noalloc": (i32, [u64, u64, i32, i64, u64, i64, u64]),
         "qm_stack_create": (i32, [p, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_stack_destroy": (i32, [p, p]),
         "qm_stack_set_layer": (i32, [p, p, i32, u64, u64, u64, u64]),
@@ -180,6 +181,10 @@ class Context:
 
     def matvec(self, w, x_dev, m, ldx, y_dev, ldy, flags=0, x2_dev=0):
         _check(lib.qm_matvec(self._h, w.handle, x_dev, x2_dev, m, ldx, y_dev, ldy, flags), "matvec")
+
+    def matvec_noalloc(self, w, x_dev, m, ldx, y_dev, ldy, cu_stream=0):
+        """qm_matvec_noalloc: Q4_0/Q8_0 matvec that allocates nothing (fixed scratch array)."""
+        _check(lib.qm_matvec_noalloc(w.handle, x_dev, m, ldx, y_dev, ldy, cu_stream), "matvec_noalloc")
 
     def matvec_host(self, w, x, flags=0, out=None):
         x = np.ascontiguousarray(x, dtype=np.float32)

@@ -21,6 +21,7 @@ OUT = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libqmatmul.so")
 KERNEL_SOURCES = ["qm_gemv.cu", "qm_dequant.cu", "qm_gemv_q4k.cu"]
 HOST_SOURCES = ["qm_host.cpp", "qm_stack.cpp"]
+RUNTIME_SOURCES = ["qm_noalloc.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
@@ -77,10 +78,19 @@ def build(force=False, verbose=False):
             with open(cubin[:-6] + ".json", "w") as f:
                 json.dump(_describe(src, cubin, log), f, indent=1)
     srcs = [os.path.join(CSRC, s) for s in HOST_SOURCES]
-    if force or _newer(LIB, srcs + headers + cubins):
+    # translation units that use the CUDA runtime (kernels launched with <<<>>>)
+    rt_objs = []
+    for name in RUNTIME_SOURCES:
+        src = os.path.join(CSRC, name)
+        obj = os.path.join(OUT, name[:-3] + ".o")
+        rt_objs.append(obj)
+        if force or _newer(obj, [src, os.path.join(CSRC, "qm_gemv.cu")] + headers):
+            _run([NVCC] + ARCH + ["-c", "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden",
+                                  "-o", obj, src])
+    if force or _newer(LIB, srcs + headers + cubins + rt_objs):
         _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-fvisibility=hidden",
-              "-DQM_CUBIN_DIR=" + OUT, "-I/usr/local/cuda/include", "-o", LIB] + srcs +
-             ["-ldl", "-lpthread"])
+              "-DQM_CUBIN_DIR=" + OUT, "-I/usr/local/cuda/include", "-o", LIB] + srcs + rt_objs +
+             ["-L/usr/local/cuda/lib64", "-lcudart_static", "-lrt", "-ldl", "-lpthread"])
     return LIB
 
 

@@ -140,8 +140,8 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     float *red = reinterpret_cast<float *>(tabs + (size_t)C * kTabBytes);            // [32][8]
     float *s_scale = red + 32 * 8;                                                   // [8]
     constexpr int stage_bytes = kStageBytes;
-    float *ssq = s_scale + 8;                                                        // [8][units]
-    float *slots = ssq + (size_t)8 * a.max_units;                                    // [C][2][M*16]
+    float *ssq = s_scale + 8;                                                        // [8][16]
+    float *slots = ssq + 8 * 16;                                    // [C][2][M*16]
     uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(slots + (size_t)C * 2 * M * 16) + 127) & ~(uintptr_t)127);  // [C][D]
     uint8_t *my_stages = stages + (size_t)warp * D * stage_bytes;
     uint8_t *my_tab = tabs + (size_t)warp * kTabBytes;
@@ -155,14 +155,25 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     // This warp's share of an op: warps are numbered warp-major over the CTAs so that a short
     // op still spreads over all SMs; every busy warp owns at least one item.
     // CTA-local item range [lo, hi) of this warp and first tile of the CTA's run
-    auto op_range = [&](const QmOp &op, int &lo, int &hi, int &tile0, int &wq, int &wrem) {
+    // This CTA's run of an op in global item coordinates: first item and item count.
+    auto cta_run = [&](const QmOp &op, unsigned int &cbase, unsigned int &Ic) {
         const int c = (int)blockIdx.x;
-        tile0 = c * op.q + min(c, op.rem);
-        const int ntc = op.q + (c < op.rem ? 1 : 0);
-        const unsigned int Ic = (unsigned int)ntc * (unsigned int)op.units;
+        const unsigned int first = (unsigned int)(c * op.q + min(c, op.rem));
+        const unsigned int count = (unsigned int)(op.q + (c < op.rem ? 1 : 0));
+        if (op.balanced) { cbase = first; Ic = count; }
+        else { cbase = first * (unsigned int)op.units; Ic = count * (unsigned int)op.units; }
+    };
+    // Item range [lo, hi) of this warp in coordinates that start at the first item of tile0 (the
+    // tile holding the CTA's first item): the CTA's own run is [off0, off0 + Ic).
+    auto op_range = [&](const QmOp &op, int &lo, int &hi, int &tile0, int &wq, int &wrem, int &off0, int &Ic_) {
+        unsigned int cbase, Ic;
+        cta_run(op, cbase, Ic);
+        tile0 = (int)(cbase / (unsigned int)op.units);
+        off0 = (int)(cbase - (unsigned int)tile0 * (unsigned int)op.units);
+        Ic_ = (int)Ic;
         wq = (int)(Ic / (unsigned int)C);
         wrem = (int)(Ic - (unsigned int)wq * (unsigned int)C);
-        lo = warp * wq + min(warp, wrem);
+        lo = off0 + warp * wq + min(warp, wrem);
         hi = lo + wq + (warp < wrem ? 1 : 0);
     };
     auto cursor_at = [&](Cursor &c, int op) {
@@ -174,8 +185,8 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         c.tile_skip = 0;
         if (op < a.nops) {
             const QmOp o = ops[op];   // by value: the fields live in registers from here on
-            int lo, hi, tile0, wq, wrem;
-            op_range(o, lo, hi, tile0, wq, wrem);
+            int lo, hi, tile0, wq, wrem, off0, Ic;
+            op_range(o, lo, hi, tile0, wq, wrem, off0, Ic);
             c.i = lo;
             c.hi = hi;
             c.units = o.units;
@@ -262,6 +273,22 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         }
         QM_MARK(1);
         // ---- quantize the activations of this op into limbs, once per CTA ---------------------
+        // Tiles of the NEXT op that this CTA will share with a neighbour are added to with
+        // red.global.add: zero them now, a whole grid barrier before anybody adds.
+        if (opi + 1 < a.nops) {
+            const QmOp nx = ops[opi + 1];
+            if (nx.balanced && tid < 2 * 16 * M) {
+                unsigned int cb, ic;
+                cta_run(nx, cb, ic);
+                const unsigned int un = (unsigned int)nx.units;
+                const unsigned int edge = (tid >= 16 * M) ? cb + ic : cb;   // tail, head
+                if (ic > 0 && edge % un != 0) {
+                    const int tl = (int)((tid >= 16 * M ? edge - 1 : edge) / un);
+                    const int o = tid % (16 * M), r = tl * 16 + (o & 15);
+                    if (r < nx.rows) nx.y[(int64_t)(o >> 4) * nx.ldy + r] = 0.f;
+                }
+            }
+        }
         // RMS normalisation is a scalar per activation row, so it commutes with the product:
         // the raw activations are quantized and the scale is applied to the finished sums.
         // The sum of squares is collected per K unit while staging (one pass over x); only an
@@ -308,6 +335,10 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
             }
         };
         float4 raw[4], raw_next[4];
+        float sq_run = 0.f;
+        int sq_j = -1;
+        if (norm && !sliced && lane < 8) ssq[lane * 16 + warp] = 0.f;
+        __syncwarp();
         if (warp < M * nun) load_raw(warp, raw);
         for (int idx = warp; idx < M * nun; idx += C) {
             const int j = idx / nun, ul = idx - j * nun;
@@ -324,10 +355,17 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
             float amax = 0.f, sum = 0.f, sq = 0.f;
 #pragma unroll
             for (int e = 0; e < 8; e++) { amax = fmaxf(amax, fabsf(v[e])); sum += v[e]; sq = fmaf(v[e], v[e], sq); }
-            if (norm && !sliced) {
+            if (norm && !sliced) {   // per-warp running sum of squares of activation row j
+                if (j != sq_j) {
+                    if (sq_j >= 0) {
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                if (lane == 0) ssq[j * a.max_units + ul] = sq;
+                        for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
+                        if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
+                    }
+                    sq_j = j;
+                    sq_run = 0.f;
+                }
+                sq_run += sq;
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -380,6 +418,11 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 sxw[(size_t)ul * 8 * NT + n0 + lane] = sx * lw;
             }
         }
+        if (sq_j >= 0) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
+            if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
+        }
         __syncthreads();
 
         float myscale[NT];
@@ -392,9 +435,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                     sc = s_scale[j];
                 } else {
                     float sq = 0.f;
-                    for (int ul = lane; ul < nun; ul += 32) sq += ssq[j * a.max_units + ul];
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                    for (int w = 0; w < C; w++) sq += ssq[j * 16 + w];   // fixed order
                     sc = rsqrtf(sq / (float)op.cols + op.eps);
                 }
 #pragma unroll
@@ -404,8 +445,8 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         }
         QM_MARK(2);
         // ---- stream this warp's chunks of the op ---------------------------------------------------
-        int lo, hi, tile0, wq, wrem;
-        op_range(op, lo, hi, tile0, wq, wrem);
+        int lo, hi, tile0, wq, wrem, off0, Ic;
+        op_range(op, lo, hi, tile0, wq, wrem, off0, Ic);
         if (cc.op != opi) cursor_at(cc, opi);
         int fin_tile = -1;   // CTA-local tile this warp finishes after the barrier
         float accF[NT][4];
@@ -434,16 +475,23 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 vA[nt] *= myscale[nt];
                 vB[nt] *= myscale[nt];
             }
-            const int ts = tile * nun, te = ts + nun;   // CTA-local items of the tile
+            // the part of the tile inside this CTA's run; `whole` when that is all of it
+            const int ts = max(tile * nun, off0), te = min(tile * nun + nun, off0 + Ic);
+            const bool whole = te - ts == nun;
             const bool from_start = lo <= ts, to_end = hi >= te;
-            if (from_start && to_end) {   // the whole K range of the tile was this warp's
+            if (from_start && to_end) {   // this warp had all of the CTA's part of the tile
                 const int rA = (tile0 + tile) * 16 + g, rB = rA + 8;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++)
                     if (valid[nt]) {
                         float *yA = op.y + (int64_t)jrow[nt] * op.ldy + rA, *yB = yA + 8;
-                        if (rA < op.rows) *yA = vA[nt] + (op.accumulate ? __ldcg(yA) : 0.f);
-                        if (rB < op.rows) *yB = vB[nt] + (op.accumulate ? __ldcg(yB) : 0.f);
+                        if (whole) {
+                            if (rA < op.rows) *yA = vA[nt] + (op.accumulate ? __ldcg(yA) : 0.f);
+                            if (rB < op.rows) *yB = vB[nt] + (op.accumulate ? __ldcg(yB) : 0.f);
+                        } else {   // the tile is shared with a neighbouring CTA
+                            if (rA < op.rows) atomicAdd(yA, vA[nt]);
+                            if (rB < op.rows) atomicAdd(yB, vB[nt]);
+                        }
                     }
                 return;
             }
@@ -572,7 +620,9 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         QM_MARK(4);
         if (fin_tile >= 0) {
             // partial sums of the warps that worked on the tile before this one, in warp order
-            const unsigned int ts = (unsigned int)(fin_tile * nun), big = (unsigned int)wrem * (unsigned int)(wq + 1);
+            const int tsf = max(fin_tile * nun, off0);
+            const bool whole = min(fin_tile * nun + nun, off0 + Ic) - tsf == nun;
+            const unsigned int ts = (unsigned int)(tsf - off0), big = (unsigned int)wrem * (unsigned int)(wq + 1);
             const int wf = wq == 0 ? (int)ts : ts < big ? (int)(ts / (unsigned int)(wq + 1))
                                                          : wrem + (int)((ts - big) / (unsigned int)wq);
             for (int o = lane; o < 16 * M; o += 32) {
@@ -581,7 +631,10 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 sum += slots[(size_t)warp * 2 * M * 16 + o];
                 const int j = o >> 4, r = (tile0 + fin_tile) * 16 + (o & 15);
                 float *yp = op.y + (int64_t)j * op.ldy + r;
-                if (r < op.rows) *yp = sum + (op.accumulate ? __ldcg(yp) : 0.f);
+                if (r < op.rows) {
+                    if (whole) *yp = sum + (op.accumulate ? __ldcg(yp) : 0.f);
+                    else atomicAdd(yp, sum);
+                }
             }
         }
         QM_MARK(5);

@@ -615,7 +615,7 @@ int32_t qm_plan_fused(qm_ctx *c, int32_t m, int32_t units, bool allow_slices, Qm
             int C = cd[0], D = cd[1];
             if (forced) { C = forced; D = env_int("QM_GEMV_D", 3); }
             if (C < 1 || C > QM_GEMV_MAX_THREADS / 32 || D < 1 || D > 8) return QM_ERR_ARG;
-            const int smem = planes * (ups * 256 + 64) + ups * 160 * p->nt + C * 1024 + 32 * 8 * 4 + 32 + ups * 32 +
+            const int smem = planes * (ups * 256 + 64) + ups * 160 * p->nt + C * 1024 + 32 * 8 * 4 + 32 + 512 +
                              C * 2 * m * 64 + 128 + C * D * QM_Q4K_ITEM_BYTES;
             if (smem <= QM_GEMV_SMEM_MAX) {
                 p->consumers = C;
@@ -630,6 +630,18 @@ int32_t qm_plan_fused(qm_ctx *c, int32_t m, int32_t units, bool allow_slices, Qm
         }
     }
     return QM_ERR_SHAPE;
+}
+
+// Deals the op's items, not its tiles, to the CTAs. Only valid inside a fused list, for an op
+// that is not the first, whose y is not touched by the op before it, and whose K units per
+// tile do not exceed a CTA's share (so that at most two CTAs meet in a tile).
+void qm_balance_op(qm_ctx *c, QmOp *op) {
+    const int grid = qm_fused_grid(c);
+    const int64_t I = (int64_t)op->tiles * op->units;
+    if (op->accumulate || I / grid < op->units || qm_env_int("QM_NO_BALANCE", 0)) return;
+    op->q = (int32_t)(I / grid);
+    op->rem = (int32_t)(I % grid);
+    op->balanced = 1;
 }
 
 void qm_fill_op(qm_ctx *c, const QmFusedPlan &p, const QmWeight *w, uint64_t x, uint64_t x2, int64_t ldx, uint64_t y,
@@ -653,6 +665,7 @@ void qm_fill_op(qm_ctx *c, const QmFusedPlan &p, const QmWeight *w, uint64_t x, 
     const int grid = qm_fused_grid(c);
     op->q = op->tiles / grid;
     op->rem = op->tiles % grid;
+    op->balanced = 0;
     (void)p;
     op->eps = 1e-6f;
 }

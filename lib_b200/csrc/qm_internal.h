@@ -84,6 +84,7 @@ int32_t qm_launch_ex(qm_ctx *c, int kernel, unsigned gx, unsigned block, unsigne
 // Integer tensor-core path for Q4_K: plan for activation rows m and the largest K (in units)
 // of the ops; QM_ERR_SHAPE when the activation planes do not fit in shared memory.
 int qm_fused_grid(qm_ctx *c);
+void qm_balance_op(qm_ctx *c, QmOp *op);
 int qm_env_int(const char *name, int dflt);
 int32_t qm_plan_fused(qm_ctx *c, int32_t m, int32_t units, bool allow_slices, QmFusedPlan *p);
 void qm_fill_op(qm_ctx *c, const QmFusedPlan &p, const QmWeight *w, uint64_t x, uint64_t x2, int64_t ldx, uint64_t y,

@@ -64,9 +64,12 @@ struct QmOp {
     int32_t xop;         // QM_XOP_*
     int32_t barrier;     // 1: every CTA must have finished the previous op before x is read
     float eps;
-    // the tiles of the op are dealt to the CTAs in contiguous runs: CTA c owns q tiles, the first
-    // `rem` CTAs one more
+    // balanced == 0: the tiles of the op are dealt to the CTAs in contiguous runs, CTA c owns q
+    // tiles, the first `rem` CTAs one more. balanced == 1: the (tile, unit) ITEMS are dealt that
+    // way, so two CTAs may share a tile; both add their part to y with red.global.add (two
+    // addends on a zero: order-independent), and y's shared tiles are zeroed during the op before
     int32_t q, rem;
+    int32_t balanced, pad;
 };
 
 struct QmFusedArgs {

@@ -170,6 +170,8 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
         qm_fill_op(c, p, ly.dn, s->gu_out, s->gu_out + (size_t)s->ffn * 4, 2 * s->ffn, s->dn_out, s->hidden,
                    QM_XOP_ADD_RMSNORM, 1, 0, ly.dn->units, 0, o + 3);
     }
+    // every op but the first writes a buffer that the op before it does not touch
+    for (size_t k = 1; k < ops.size(); k++) qm_balance_op(c, &ops[k]);
     CUdeviceptr dev = 0;
     DRV(c->drv->cuMemAlloc_v2(&dev, ops.size() * sizeof(QmOp)));
     CUresult r = c->drv->cuMemcpyHtoD_v2(dev, ops.data(), ops.size() * sizeof(QmOp));

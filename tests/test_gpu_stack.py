@@ -52,14 +52,19 @@ def test_small_stack_matches_oracle(ctx, fmt, m):
     want_h, want_kv, _ = oracle_chain(fmt, raws, x, hidden, kv, ffn)
     assert nre(h, want_h) <= TOL
     assert nre(kvs, want_kv) <= TOL
-    # the step runs as one persistent launch where it can (mode 2, the default); repeating it,
-    # replaying it as a graph of per-matvec launches (1) and issuing those one by one (0) all
-    # give the same bits
-    h2 = st.step_host(x)
-    assert np.array_equal(h, h2)
-    for mode in (1, 0, 2):
-        st.use_graph(mode)
-        assert np.array_equal(h, st.step_host(x)), mode
+    # the step runs as one persistent launch where it can (mode 2, the default); repeating it
+    # gives the same bits. Replaying it as a graph of per-matvec launches (1) and issuing those
+    # one by one (0) give the same bits as each other, and agree with mode 2 to rounding (the
+    # single launch balances work across CTAs, which changes the order of a few additions).
+    assert np.array_equal(h, st.step_host(x))
+    st.use_graph(1)
+    h1 = st.step_host(x)
+    assert np.array_equal(h1, st.step_host(x))
+    st.use_graph(0)
+    assert np.array_equal(h1, st.step_host(x))
+    assert nre(h1, h.astype(np.float64)) <= 1e-5
+    st.use_graph(2)
+    assert np.array_equal(h, st.step_host(x))
     st.close()
 
 

@@ -137,6 +137,14 @@ QM_API int32_t qm_matvec(qm_ctx *ctx, qm_weight w, uint64_t x_dev, uint64_t x2_d
 QM_API int32_t qm_matvec_host(qm_ctx *ctx, qm_weight w, const float *x_host, int32_t m, int64_t ldx,
                        float *y_host, int64_t ldy, uint32_t flags);
 
+/* Batched / prefill product over a stored Q4_K matrix on the tcgen05 tensor cores:
+ * c[j][r] = sum_k a[j][k] * W[r][k] for j < m, a bf16 [m][lda] (16-byte aligned, lda a multiple
+ * of 8), c float32 [m][ldc], device pointers. Weights are dequantized into shared memory as
+ * bf16, accumulation is fp32 in tensor memory. Supersedes the reference's fp16 wmma prefill
+ * GEMM (nvidia/x/cudamoe/prefill.go:97-121). Asynchronous on the context's stream. */
+QM_API int32_t qm_matmul_bf16(qm_ctx *ctx, qm_weight w, uint64_t a_dev, int32_t m, int64_t lda, uint64_t c_dev,
+                              int64_t ldc);
+
 /* No counterpart in the reference. The Q4_0 / Q8_0 matvec of qm_matvec for callers that may
  * not allocate device memory at the point of the call: a server whose memory plan is frozen
  * once it starts serving, a latency-critical loop where an allocation would stall the device,

@@ -51,6 +51,7 @@ def _load():
         "qm_dequantize_host": (i32, [p, i32, p, i64, i64, p]),
         "qm_matvec": (i32, [p, u64, u64, u64, i32, i64, u64, i64, u32]),
         "qm_matvec_host": (i32, [p, u64, p, i32, i64, p, i64, u32]),
+        "qm_matmul_bf16": (i32, [p, u64, u64, i32, i64, u64, i64]),
         "qm_matvec_noalloc": (i32, [u64, u64, i32, i64, u64, i64, u64]),
         "qm_stack_create": (i32, [p, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_stack_destroy": (i32, [p, p]),
@@ -181,6 +182,10 @@ class Context:
 
     def matvec(self, w, x_dev, m, ldx, y_dev, ldy, flags=0, x2_dev=0):
         _check(lib.qm_matvec(self._h, w.handle, x_dev, x2_dev, m, ldx, y_dev, ldy, flags), "matvec")
+
+    def matmul_bf16(self, w, a_dev, m, lda, c_dev, ldc):
+        """qm_matmul_bf16: c[m][rows] = a[m][cols] (bf16) x W^T on tcgen05, fp32 out."""
+        _check(lib.qm_matmul_bf16(self._h, w.handle, a_dev, m, lda, c_dev, ldc), "matmul_bf16")
 
     def matvec_noalloc(self, w, x_dev, m, ldx, y_dev, ldy, cu_stream=0):
         """qm_matvec_noalloc: Q4_0/Q8_0 matvec that allocates nothing (fixed scratch array)."""

@@ -54,6 +54,7 @@ int qm_driver_load(QmDriver **out) {
 QM_INCBIN(qm_cubin_gemv, QM_STR(QM_CUBIN_DIR) "/qm_gemv.sm_100a.cubin")
 QM_INCBIN(qm_cubin_dequant, QM_STR(QM_CUBIN_DIR) "/qm_dequant.sm_100a.cubin")
 QM_INCBIN(qm_cubin_q4k, QM_STR(QM_CUBIN_DIR) "/qm_gemv_q4k.sm_100a.cubin")
+QM_INCBIN(qm_cubin_gemm, QM_STR(QM_CUBIN_DIR) "/qm_gemm_q4k.sm_100a.cubin")
 
 struct KernelImage {
     const unsigned char *begin;
@@ -63,6 +64,7 @@ static const KernelImage kImages[QM_MOD_COUNT] = {
     {qm_cubin_gemv, qm_cubin_gemv_end},
     {qm_cubin_dequant, qm_cubin_dequant_end},
     {qm_cubin_q4k, qm_cubin_q4k_end},
+    {qm_cubin_gemm, qm_cubin_gemm_end},
 };
 struct KernelName {
     int module;
@@ -75,6 +77,7 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_DEQUANT, "qm_dequant_q80"}, {QM_MOD_DEQUANT, "qm_repack_q40"},  {QM_MOD_DEQUANT, "qm_repack_q80"},
     {QM_MOD_DEQUANT, "qm_repack_q4k"},
     {QM_MOD_Q4K, "qm_fused_q4k_nt1"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2"},
+    {QM_MOD_GEMM, "qm_gemm_q4k_bf16"},
 };
 
 // ---- errors --------------------------------------------------------------------------
@@ -156,6 +159,10 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
         }
         for (int k = QM_K_FUSED_Q4K_NT1; k <= QM_K_FUSED_Q4K_NT2 && !err; k++) {
             r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
+            if (r != CUDA_SUCCESS) err = (int32_t)r;
+        }
+        if (!err) {
+            r = d->cuFuncSetAttribute(c->fn[QM_K_GEMM_Q4K], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
         for (int k = QM_K_GEMV_Q40_M4; k <= QM_K_GEMV_Q80_M8 && !err; k++) {
@@ -788,5 +795,52 @@ extern "C" int32_t qm_matvec_host(qm_ctx *c, qm_weight h, const float *x_host, i
     for (int j = 0; j < m; j++)
         DRV(c->drv->cuMemcpyDtoHAsync_v2(y_host + j * ldy, yd + j * w->rows * 4, (size_t)w->rows * 4, c->stream));
     DRV(c->drv->cuStreamSynchronize(c->stream));
+    return QM_OK;
+}
+
+// ---- prefill matmul (tcgen05) ----------------------------------------------------------------
+extern "C" int32_t qm_matmul_bf16(qm_ctx *c, qm_weight h, uint64_t a_dev, int32_t m, int64_t lda, uint64_t c_dev,
+                                  int64_t ldc) {
+    CHECK_CTX(c);
+    QmWeight *w = qm_weight_from_handle(h);
+    if (!w || !a_dev || !c_dev) return QM_ERR_ARG;
+    if (w->fmt != QM_FMT_Q4_K) return QM_ERR_FORMAT;
+    if (m < 1 || m > (1 << 20) || lda < w->cols || ldc < w->rows) return QM_ERR_SHAPE;
+    // TMA: base 16-byte aligned, row pitch a multiple of 16 bytes
+    if ((a_dev & 15) || ((lda * 2) & 15)) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    QmGemmArgs a;
+    memset(&a, 0, sizeof a);
+    const int bn = m <= 64 ? 64 : m <= 128 ? 128 : 256;
+    const cuuint64_t dims[2] = {(cuuint64_t)w->cols, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)bn};
+    const cuuint32_t estr[2] = {1, 1};
+    DRV(c->drv->cuTensorMapEncodeTiled(&a.tmap_act, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)(uintptr_t)a_dev, dims,
+                                       strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+    a.wq = (const uint8_t *)(uintptr_t)w->wq;
+    a.c = (float *)(uintptr_t)c_dev;
+    a.status = (unsigned int *)(uintptr_t)c->status_dev;
+    a.ldc = ldc;
+    a.m = m;
+    a.n = (int32_t)w->rows;
+    a.units = w->units;
+    a.tiles16 = (int32_t)((w->rows + 15) / 16);
+    a.bn = bn;
+    const unsigned smem = 1024 + 4 * (128 * 64 * 2 + bn * 64 * 2) + 256;
+    void *params[1] = {&a};
+    CUlaunchConfig cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDimX = (unsigned)((w->rows + 127) / 128);
+    cfg.gridDimY = (unsigned)((m + bn - 1) / bn);
+    cfg.gridDimZ = 1;
+    cfg.blockDimX = 192;
+    cfg.blockDimY = cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = smem;
+    cfg.hStream = c->stream;
+    DRV(c->drv->cuLaunchKernelEx(&cfg, c->fn[QM_K_GEMM_Q4K], params, nullptr));
+    c->launches++;
     return QM_OK;
 }

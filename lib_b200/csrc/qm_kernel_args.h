@@ -4,6 +4,7 @@
 // kinds the reference's ABI schema can describe
 // (nvidia/x/cudakernel/abi.go:43-100).
 #pragma once
+#include <cuda.h>
 #include <stdint.h>
 
 #define QM_K_UNIT 256          // columns covered by one K unit (one Q4_K super-block)
@@ -83,6 +84,20 @@ struct QmFusedArgs {
     int32_t cpm;         // mma columns per activation row: 4 (m <= 2) or 2 (m <= 4, or 8 with two column tiles)
     int32_t debug;       // 0 in production
     int32_t debug_slot, pad2;
+};
+
+// Prefill GEMM over Q4_K weights (tcgen05): C[m][n] = sum_k A[m][k] * W[n][k].
+struct QmGemmArgs {
+    alignas(64) CUtensorMap tmap_act;  // activations [m][k] bf16, box 64 x bn, 128-byte swizzle
+    const uint8_t *wq;     // tiled Q4_K store
+    float *c;              // [m][ldc]
+    unsigned int *status;
+    int64_t ldc;
+    int32_t m, n;
+    int32_t units;         // K / 256
+    int32_t tiles16;       // 16-row tiles of the store
+    int32_t bn;            // tokens per CTA: 64, 128 or 256
+    int32_t pad;
 };
 
 struct QmDequantArgs {

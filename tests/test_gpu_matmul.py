@@ -1,0 +1,60 @@
+"""GPU parity of the tcgen05 prefill matmul over Q4_K weights (bf16 activations, fp32
+accumulation) against the oracle's dequantize + float64 dot on the same seeded inputs.
+
+Tolerance: normwise relative error <= 3e-3, the bound the benchmark specification states for
+bf16 activations on the tensor cores (the kernel also rounds the dequantized weights to bf16)."""
+import numpy as np
+import pytest
+
+from lib_b200 import synth
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 3e-3
+
+
+def to_bf16_bits(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(b):
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def nre(got, want):
+    return float(np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30))
+
+
+def run(ctx, devbuf, n, k, m, seed, check_rows=None):
+    raw = synth.weights(12, n, k, seed)
+    a16 = to_bf16_bits(synth.activations(m, k, seed + 1))
+    w = ctx.store_upload(12, n, k, raw)
+    ad = devbuf(a16)
+    cd = devbuf(np.full((m, n), np.nan, np.float32))
+    ctx.matmul_bf16(w, ad.ptr, m, k, cd.ptr, n)
+    ctx.sync()
+    rc, status = ctx.last_status()
+    assert rc == 0 and status == 0
+    c = cd.get((m, n))
+    w.free()
+    r0, r1 = check_rows if check_rows else (0, n)
+    be = k // 256 * 144
+    want = oracle.MatVec(12, raw[r0 * be:r1 * be], r1 - r0, k, bf16_to_f32(a16))
+    assert np.isfinite(c).all()
+    return nre(c[:, r0:r1], want)
+
+
+@pytest.mark.parametrize("n,k,m", [(256, 512, 64), (128, 256, 1), (384, 1024, 100), (200, 768, 130),
+                                   (1000, 512, 300)])
+def test_small_and_ragged(ctx, devbuf, n, k, m):
+    assert run(ctx, devbuf, n, k, m, seed=n + m) <= TOL
+
+
+@pytest.mark.parametrize("m", [64, 256])
+def test_config3_shapes(ctx, devbuf, m):
+    assert run(ctx, devbuf, 4096, 4096, m, seed=31 + m) <= TOL
+
+
+def test_config3_m2048_sampled_rows(ctx, devbuf):
+    assert run(ctx, devbuf, 4096, 4096, 2048, seed=77, check_rows=(1920, 2048)) <= TOL

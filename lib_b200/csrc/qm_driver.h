@@ -31,6 +31,7 @@
     X(cuMemcpyDtoDAsync_v2, CUresult (*)(CUdeviceptr, CUdeviceptr, size_t, CUstream))             \
     X(cuMemsetD8Async, CUresult (*)(CUdeviceptr, unsigned char, size_t, CUstream))                \
     X(cuMemsetD32Async, CUresult (*)(CUdeviceptr, unsigned int, size_t, CUstream))                \
+    X(cuMemsetD2D32Async, CUresult (*)(CUdeviceptr, size_t, unsigned int, size_t, size_t, CUstream)) \
     X(cuStreamCreate, CUresult (*)(CUstream *, unsigned int))                                     \
     X(cuStreamDestroy_v2, CUresult (*)(CUstream))                                                 \
     X(cuStreamSynchronize, CUresult (*)(CUstream))                                                \

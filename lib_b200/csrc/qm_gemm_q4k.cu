@@ -4,18 +4,19 @@
 // Supersedes the reference's fp16 wmma 256-row "prefill" GEMM
 // (nvidia/x/cudamoe/prefill.go:97-121), which is neither quantized nor tcgen05.
 //
-// One CTA computes a 128 (weight rows) x BN (tokens, 64/128/256) tile of C^T:
-//   * warps 2..5 (128 threads, one weight row each) read the row's 32 quant bytes of a
-//     64-column K chunk straight from the tiled weight store, turn the nibbles into exact
+// One CTA computes a 128 (weight rows) x BN (tokens, 64..512) tile of C^T:
+//   * warps 2..9 (256 threads, two per weight row: low nibbles / high nibbles) read the row's
+//     32 quant bytes of a 64-column K chunk from the tiled weight store, turn the nibbles into exact
 //     bf16 integers with the magic-number trick (0x4300|q = 128+q), apply the sub-block
 //     scale and minimum with one bf16x2 FMA per pair, and write the row into shared memory
 //     in the canonical K-major 128-byte-swizzled layout of tcgen05 (A operand);
 //   * warp 0 streams the matching 64 x BN activation chunk with a 2-D TMA tile copy
 //     (SWIZZLE_128B, no multicast) that completes on an mbarrier (B operand);
 //   * one elected thread of warp 1 issues four tcgen05.mma.kind::f16 (K = 16 each) per chunk
-//     into a TMEM accumulator of BN fp32 columns, and tcgen05.commit releases the stage;
-//   * after the last chunk warps 2..5 read the accumulator back with tcgen05.ld and store C.
-// A ring of kStages shared-memory stages decouples the three roles. Every mbarrier wait is
+//     and per 256 tokens into a TMEM accumulator of BN fp32 columns (BN = 512 uses the whole
+//     tensor memory: the dequantized tile then feeds two MMAs), tcgen05.commit frees the stage;
+//   * after the last chunk warps 2..9 read the accumulator back with tcgen05.ld and store C.
+// A ring of 2..4 shared-memory stages decouples the three roles. Every mbarrier wait is
 // bounded (qm_pipe.cuh); on expiry the status word gets QM_STATUS_TIMEOUT, the roles leave
 // their loops, TMEM is freed and the kernel returns.
 #include <cuda.h>
@@ -29,7 +30,7 @@ using namespace qm;
 
 namespace {
 
-constexpr int kStages = 4;
+constexpr int kMaxStages = 4;
 constexpr int kBM = 128;          // weight rows per CTA (tcgen05 M)
 constexpr int kBK = 64;           // K columns per stage: one 32-byte quant group, 128 bytes of bf16
 constexpr int kATile = kBM * kBK * 2;
@@ -79,25 +80,29 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 
 }  // namespace
 
-extern "C" __global__ void __launch_bounds__(192, 1) qm_gemm_q4k_bf16(const __grid_constant__ QmGemmArgs a) {
+extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16(const __grid_constant__ QmGemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int BN = a.bn;
+    const int BN = a.bn, kStages = a.stages;
     const int b_tile = BN * kBK * 2;
     const int stage_bytes = kATile + b_tile;
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)kStages * stage_bytes);
-    const uint32_t full_a = smem_u32(bars), full_b = full_a + 8 * kStages, empty = full_b + 8 * kStages;
-    const uint32_t tmem_full = empty + 8 * kStages;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kStages + 1);
+    const uint32_t full_a = smem_u32(bars), full_b = full_a + 8 * kMaxStages, empty = full_b + 8 * kMaxStages;
+    const uint32_t tmem_full = empty + 8 * kMaxStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kMaxStages + 1);
     const uint32_t smem_base = smem_u32(smem);
 
     const int n0 = blockIdx.x * kBM, m0 = blockIdx.y * BN;
-    const int nk = a.units * 4;   // 64-column chunks along K
+    // 64-column chunks along K; with split K (gridDim.z > 1) this CTA takes a contiguous share
+    // and adds its partial tile to C, which the host zeroed
+    const int nk_all = a.units * 4;
+    const int kc_lo = (int)((int64_t)nk_all * blockIdx.z / gridDim.z);
+    const int nk = (int)((int64_t)nk_all * (blockIdx.z + 1) / gridDim.z) - kc_lo;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) {
-            mbar_init(full_a + 8 * s, 128);
+            mbar_init(full_a + 8 * s, 256);
             mbar_init(full_b + 8 * s, 1);
             mbar_init(empty + 8 * s, 1);
         }
@@ -123,14 +128,17 @@ extern "C" __global__ void __launch_bounds__(192, 1) qm_gemm_q4k_bf16(const __gr
                 const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
                 if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); break; }
                 mbar_expect_tx(full_b + 8 * s, (uint32_t)b_tile);
-                tma_load_2d(smem_base + s * stage_bytes + kATile, &a.tmap_act, kc * kBK, m0, full_b + 8 * s);
+                for (int nb = 0; nb < BN; nb += 256)   // a TMA box has at most 256 rows
+                    tma_load_2d(smem_base + s * stage_bytes + kATile + nb * 128, &a.tmap_act, (kc_lo + kc) * kBK, m0 + nb,
+                                full_b + 8 * s);
             }
         }
     } else if (warp == 1) {
         // ---- MMA issue ----------------------------------------------------------------------------
         if (lane == 0) {
             // kind::f16, fp32 accumulate, A and B bf16, both K-major, N = BN, M = 128
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+            const int NI = min(BN, 256);   // tokens per MMA
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NI >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
             bool ok = true;
             for (int kc = 0; kc < nk && ok; kc++) {
                 const int s = kc % kStages;
@@ -140,64 +148,79 @@ extern "C" __global__ void __launch_bounds__(192, 1) qm_gemm_q4k_bf16(const __gr
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t adesc = smem_desc(smem_base + s * stage_bytes);
                 const uint64_t bdesc = smem_desc(smem_base + s * stage_bytes + kATile);
+                for (int nb = 0; nb < BN; nb += 256)
 #pragma unroll
-                for (int k16 = 0; k16 < kBK / 16; k16++)   // 16 bf16 = 32 bytes = 2 descriptor units
-                    umma_f16(tmem_base, adesc + 2 * k16, bdesc + 2 * k16, idesc, (kc | k16) != 0);
+                    for (int k16 = 0; k16 < kBK / 16; k16++)   // 16 bf16 = 32 bytes = 2 descriptor units
+                        umma_f16(tmem_base + (uint32_t)nb, adesc + 2 * k16, bdesc + (nb * 128 >> 4) + 2 * k16, idesc,
+                                 (kc | k16) != 0);
                 umma_commit(empty + 8 * s);   // frees the stage when these MMAs have read it
             }
             umma_commit(tmem_full);           // accumulator complete (or abandoned)
         }
     } else {
         // ---- dequantize weight rows into the A tile, then the epilogue --------------------------
-        const int r = tid - 64;                                   // row of the tile, 0..127
+        const int r = (tid - 64) & 127;      // row of the tile
+        const int hsel = (tid - 64) >> 7;    // 0: low nibbles (columns 0..31), 1: high nibbles (32..63)
         const int64_t tile16 = min((n0 + r) >> 4, a.tiles16 - 1);
         const int rr = (n0 + r) & 15;
         const uint8_t *row_items = a.wq + tile16 * a.units * QM_Q4K_ITEM_BYTES;
-        uint4 hdr = make_uint4(0, 0, 0, 0);
         bool ok = true;
+        // the quant bytes of the next three chunks and the header of the next unit are in flight
+        // while a chunk is converted
+        constexpr int kAhead = 3;
+        uint4 qa[kAhead + 1], qb[kAhead + 1], hdr_next = make_uint4(0, 0, 0, 0), hdr = hdr_next;
+        auto load_q = [&](int kcl, uint4 &x0, uint4 &x1) {
+            const int kc = kc_lo + kcl;
+            const uint8_t *item = row_items + (size_t)(kc >> 2) * QM_Q4K_ITEM_BYTES + 256 + 512 * (kc & 3) + 32 * rr;
+            x0 = __ldg(reinterpret_cast<const uint4 *>(item));
+            x1 = __ldg(reinterpret_cast<const uint4 *>(item + 16));
+        };
+        hdr_next = __ldg(reinterpret_cast<const uint4 *>(row_items + (size_t)(kc_lo >> 2) * QM_Q4K_ITEM_BYTES + 16 * rr));
+#pragma unroll
+        for (int i = 0; i < kAhead; i++)
+            if (i < nk) load_q(i, qa[i], qb[i]);
         for (int kc = 0; kc < nk; kc++) {
             const int s = kc % kStages;
             const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
-            const int u = kc >> 2, p = kc & 3;
-            const uint8_t *item = row_items + (size_t)u * QM_Q4K_ITEM_BYTES;
-            if (p == 0) hdr = __ldg(reinterpret_cast<const uint4 *>(item + 16 * rr));
-            const uint4 q0 = __ldg(reinterpret_cast<const uint4 *>(item + 256 + 512 * p + 32 * rr));
-            const uint4 q1 = __ldg(reinterpret_cast<const uint4 *>(item + 256 + 512 * p + 32 * rr + 16));
-            // scales and minima of sub-blocks 2p (low nibbles) and 2p+1 (high nibbles)
-            int sc[2], mn[2];
+            const int u = (kc_lo + kc) >> 2, p = (kc_lo + kc) & 3;
+            if (p == 0 || kc == 0) {
+                hdr = hdr_next;
+                if (u + 1 < a.units)
+                    hdr_next = __ldg(reinterpret_cast<const uint4 *>(row_items + (size_t)(u + 1) * QM_Q4K_ITEM_BYTES + 16 * rr));
+            }
+            if (kc + kAhead < nk) load_q(kc + kAhead, qa[kAhead], qb[kAhead]);
+            const uint4 q0 = qa[0], q1 = qb[0];
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int j = 2 * p + h;
-                if (j < 4) {
-                    sc[h] = (hdr.y >> (8 * j)) & 63;
-                    mn[h] = (hdr.z >> (8 * j)) & 63;
-                } else {
-                    const int jj = j - 4;
-                    sc[h] = ((hdr.w >> (8 * jj)) & 0xF) | (((hdr.y >> (8 * jj + 6)) & 3) << 4);
-                    mn[h] = ((hdr.w >> (8 * jj + 4)) & 0xF) | (((hdr.z >> (8 * jj + 6)) & 3) << 4);
-                }
+            for (int i = 0; i < kAhead; i++) { qa[i] = qa[i + 1]; qb[i] = qb[i + 1]; }
+            // scale and minimum of sub-block 2p (low nibbles) or 2p+1 (high nibbles)
+            const int j = 2 * p + hsel;
+            int sc, mn;
+            if (j < 4) {
+                sc = (hdr.y >> (8 * j)) & 63;
+                mn = (hdr.z >> (8 * j)) & 63;
+            } else {
+                const int jj = j - 4;
+                sc = ((hdr.w >> (8 * jj)) & 0xF) | (((hdr.y >> (8 * jj + 6)) & 3) << 4);
+                mn = ((hdr.w >> (8 * jj + 4)) & 0xF) | (((hdr.z >> (8 * jj + 6)) & 3) << 4);
             }
             const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
             const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-            const uint32_t aLo = bf2(d * (float)sc[0]), bLo = bf2(-dmin * (float)mn[0]);
-            const uint32_t aHi = bf2(d * (float)sc[1]), bHi = bf2(-dmin * (float)mn[1]);
+            const uint32_t av = bf2(d * (float)sc), bv = bf2(-dmin * (float)mn);
             const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-            uint32_t lo[16], hi[16];   // bf16x2 pairs: lo = columns 0..31, hi = columns 32..63 of the chunk
+            const int sh = 4 * hsel;
+            uint32_t o[16];   // bf16x2 pairs: 32 columns of the chunk
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-                const uint32_t p01 = prmt(w[i], 0u, 0x4140u), p23 = prmt(w[i], 0u, 0x4342u);   // bytes spread to 16-bit lanes
-                lo[2 * i] = bfma2(bsub2((p01 & 0x000F000Fu) | 0x43004300u, 0x43004300u), aLo, bLo);
-                lo[2 * i + 1] = bfma2(bsub2((p23 & 0x000F000Fu) | 0x43004300u, 0x43004300u), aLo, bLo);
-                hi[2 * i] = bfma2(bsub2(((p01 >> 4) & 0x000F000Fu) | 0x43004300u, 0x43004300u), aHi, bHi);
-                hi[2 * i + 1] = bfma2(bsub2(((p23 >> 4) & 0x000F000Fu) | 0x43004300u, 0x43004300u), aHi, bHi);
+                const uint32_t p01 = prmt(w[i], 0u, 0x4140u) >> sh, p23 = prmt(w[i], 0u, 0x4342u) >> sh;   // bytes in 16-bit lanes
+                o[2 * i] = bfma2(bsub2((p01 & 0x000F000Fu) | 0x43004300u, 0x43004300u), av, bv);
+                o[2 * i + 1] = bfma2(bsub2((p23 & 0x000F000Fu) | 0x43004300u, 0x43004300u), av, bv);
             }
             if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); ok = false; break; }
             uint8_t *arow = smem + (size_t)s * stage_bytes + r * 128;
 #pragma unroll
-            for (int c = 0; c < 4; c++) {   // 16-byte pieces, XOR-swizzled by the row inside its 8-row group
-                *reinterpret_cast<uint4 *>(arow + ((c ^ (r & 7)) << 4)) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
-                *reinterpret_cast<uint4 *>(arow + (((c + 4) ^ (r & 7)) << 4)) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-            }
+            for (int c = 0; c < 4; c++)   // 16-byte pieces, XOR-swizzled by the row inside its 8-row group
+                *reinterpret_cast<uint4 *>(arow + (((c + 4 * hsel) ^ (r & 7)) << 4)) =
+                    make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
             mbar_arrive(full_a + 8 * s);
         }
@@ -206,7 +229,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) qm_gemm_q4k_bf16(const __gr
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
             const int n = n0 + (warp & 3) * 32 + lane;   // TMEM lane quarter of this warp
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            const int cbeg = hsel * (BN / 2), cend = cbeg + BN / 2;   // the two warps of a quarter split the columns
+            for (int c0 = cbeg; c0 < cend; c0 += 32) {
                 uint32_t v[32];
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -223,7 +247,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) qm_gemm_q4k_bf16(const __gr
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int m = m0 + c0 + j;
-                        if (m < a.m) a.c[(int64_t)m * a.ldc + n] = __uint_as_float(v[j]);
+                        if (m < a.m) {
+                            if (gridDim.z == 1) a.c[(int64_t)m * a.ldc + n] = __uint_as_float(v[j]);
+                            else atomicAdd(a.c + (int64_t)m * a.ldc + n, __uint_as_float(v[j]));
+                        }
                     }
                 }
             }

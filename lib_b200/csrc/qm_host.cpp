@@ -812,10 +812,11 @@ extern "C" int32_t qm_matmul_bf16(qm_ctx *c, qm_weight h, uint64_t a_dev, int32_
     DRV(g.rc);
     QmGemmArgs a;
     memset(&a, 0, sizeof a);
-    const int bn = m <= 64 ? 64 : m <= 128 ? 128 : 256;
+    const int bn = m <= 64 ? 64 : m <= 128 ? 128 : m <= 256 ? 256 : 512;
+    const int stages = bn == 512 ? 2 : 4;
     const cuuint64_t dims[2] = {(cuuint64_t)w->cols, (cuuint64_t)m};
     const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)bn};
+    const cuuint32_t box[2] = {64, (cuuint32_t)std::min(bn, 256)};
     const cuuint32_t estr[2] = {1, 1};
     DRV(c->drv->cuTensorMapEncodeTiled(&a.tmap_act, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)(uintptr_t)a_dev, dims,
                                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -829,14 +830,22 @@ extern "C" int32_t qm_matmul_bf16(qm_ctx *c, qm_weight h, uint64_t a_dev, int32_
     a.units = w->units;
     a.tiles16 = (int32_t)((w->rows + 15) / 16);
     a.bn = bn;
-    const unsigned smem = 1024 + 4 * (128 * 64 * 2 + bn * 64 * 2) + 256;
+    a.stages = stages;
+    const unsigned smem = 1024 + stages * (128 * 64 * 2 + bn * 64 * 2) + 256;
     void *params[1] = {&a};
     CUlaunchConfig cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDimX = (unsigned)((w->rows + 127) / 128);
     cfg.gridDimY = (unsigned)((m + bn - 1) / bn);
-    cfg.gridDimZ = 1;
-    cfg.blockDimX = 192;
+    // few tokens: split K over CTAs until the SMs are covered; partial tiles are added into a
+    // zeroed C (float adds in arrival order: results may differ in the last bits between runs)
+    int splitk = 1;
+    while (splitk < 8 && (int)(cfg.gridDimX * cfg.gridDimY) * splitk * 2 <= c->sm_count && w->units * 4 / (splitk * 2) >= 8)
+        splitk *= 2;
+    splitk = env_int("QM_GEMM_SPLITK", splitk);
+    cfg.gridDimZ = (unsigned)splitk;
+    if (splitk > 1) DRV(c->drv->cuMemsetD2D32Async((CUdeviceptr)c_dev, (size_t)ldc * 4, 0, (size_t)w->rows, (size_t)m, c->stream));
+    cfg.blockDimX = 320;
     cfg.blockDimY = cfg.blockDimZ = 1;
     cfg.sharedMemBytes = smem;
     cfg.hStream = c->stream;

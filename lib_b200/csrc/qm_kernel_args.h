@@ -96,8 +96,8 @@ struct QmGemmArgs {
     int32_t m, n;
     int32_t units;         // K / 256
     int32_t tiles16;       // 16-row tiles of the store
-    int32_t bn;            // tokens per CTA: 64, 128 or 256
-    int32_t pad;
+    int32_t bn;            // tokens per CTA: 64, 128, 256 or 512
+    int32_t stages;        // shared-memory stages, 2..4
 };
 
 struct QmDequantArgs {

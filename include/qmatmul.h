@@ -145,6 +145,25 @@ QM_API int32_t qm_matvec_host(qm_ctx *ctx, qm_weight w, const float *x_host, int
 QM_API int32_t qm_matmul_bf16(qm_ctx *ctx, qm_weight w, uint64_t a_dev, int32_t m, int64_t lda, uint64_t c_dev,
                               int64_t ldc);
 
+/* GroupedTopKRouter.Route (lm/moe/moe.go:73-141) for `tokens` tokens at once: experts ranked by
+ * logit + bias (descending, ties to the lower index), weights = softmax over the selected
+ * experts' UNBIASED logits (exp in double, rounded to float32, float32 sum in selection order).
+ * logits float32 [tokens][ld], bias float32 [experts] or 0, ids int32 [tokens][topk],
+ * weights float32 [tokens][topk]; experts <= 64. Device pointers, asynchronous. */
+QM_API int32_t qm_moe_route(qm_ctx *ctx, uint64_t logits_dev, int32_t tokens, int64_t ld, int32_t experts,
+                            int32_t topk, uint64_t bias_dev, uint64_t ids_dev, uint64_t weights_dev);
+/* Grouped expert matmul over routed token lists (SwiGLU experts, Q4_K weights):
+ * out[t] = sum_s weights[t][s] * down_e( silu(gate_e x_t) * (up_e x_t) ), e = ids[t][s].
+ * gate_up[e] is a stored [2*ffn][hidden] matrix (gate rows, then up rows), down[e] a stored
+ * [hidden][ffn] matrix; x bf16 [tokens][ldx], out float32 [tokens][ldo]. Tokens are grouped per
+ * expert on the device, each expert runs the tcgen05 matmul over its list, and the combine
+ * adds a token's expert outputs in slot order. New API of this path: the reference's lm/moe
+ * routes and caches experts but has no matmul; its device gather is nvidia/x/cudamoe/moe.go:72-96.
+ * Reads the list lengths back to the host (one stream synchronization inside the call). */
+QM_API int32_t qm_moe_grouped(qm_ctx *ctx, const qm_weight *gate_up, const qm_weight *down, int32_t experts,
+                              uint64_t x_bf16_dev, int32_t tokens, int64_t ldx, uint64_t ids_dev,
+                              uint64_t weights_dev, int32_t topk, uint64_t out_dev, int64_t ldo);
+
 /* No counterpart in the reference. The Q4_0 / Q8_0 matvec of qm_matvec for callers that may
  * not allocate device memory at the point of the call: a server whose memory plan is frozen
  * once it starts serving, a latency-critical loop where an allocation would stall the device,

@@ -52,6 +52,8 @@ def _load():
         "qm_matvec": (i32, [p, u64, u64, u64, i32, i64, u64, i64, u32]),
         "qm_matvec_host": (i32, [p, u64, p, i32, i64, p, i64, u32]),
         "qm_matmul_bf16": (i32, [p, u64, u64, i32, i64, u64, i64]),
+        "qm_moe_route": (i32, [p, u64, i32, i64, i32, i32, u64, u64, u64]),
+        "qm_moe_grouped": (i32, [p, p, p, i32, u64, i32, i64, u64, u64, i32, u64, i64]),
         "qm_matvec_noalloc": (i32, [u64, u64, i32, i64, u64, i64, u64]),
         "qm_stack_create": (i32, [p, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_stack_destroy": (i32, [p, p]),
@@ -186,6 +188,17 @@ class Context:
     def matmul_bf16(self, w, a_dev, m, lda, c_dev, ldc):
         """qm_matmul_bf16: c[m][rows] = a[m][cols] (bf16) x W^T on tcgen05, fp32 out."""
         _check(lib.qm_matmul_bf16(self._h, w.handle, a_dev, m, lda, c_dev, ldc), "matmul_bf16")
+
+    def moe_route(self, logits_dev, tokens, ld, experts, topk, ids_dev, weights_dev, bias_dev=0):
+        _check(lib.qm_moe_route(self._h, logits_dev, tokens, ld, experts, topk, bias_dev, ids_dev, weights_dev),
+               "moe_route")
+
+    def moe_grouped(self, gate_up, down, x_dev, tokens, ldx, ids_dev, weights_dev, topk, out_dev, ldo):
+        n = len(gate_up)
+        ga = (ctypes.c_uint64 * n)(*[w.handle for w in gate_up])
+        da = (ctypes.c_uint64 * n)(*[w.handle for w in down])
+        _check(lib.qm_moe_grouped(self._h, ga, da, n, x_dev, tokens, ldx, ids_dev, weights_dev, topk, out_dev, ldo),
+               "moe_grouped")
 
     def matvec_noalloc(self, w, x_dev, m, ldx, y_dev, ldy, cu_stream=0):
         """qm_matvec_noalloc: Q4_0/Q8_0 matvec that allocates nothing (fixed scratch array)."""

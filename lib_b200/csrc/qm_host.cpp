@@ -55,6 +55,7 @@ QM_INCBIN(qm_cubin_gemv, QM_STR(QM_CUBIN_DIR) "/qm_gemv.sm_100a.cubin")
 QM_INCBIN(qm_cubin_dequant, QM_STR(QM_CUBIN_DIR) "/qm_dequant.sm_100a.cubin")
 QM_INCBIN(qm_cubin_q4k, QM_STR(QM_CUBIN_DIR) "/qm_gemv_q4k.sm_100a.cubin")
 QM_INCBIN(qm_cubin_gemm, QM_STR(QM_CUBIN_DIR) "/qm_gemm_q4k.sm_100a.cubin")
+QM_INCBIN(qm_cubin_moe, QM_STR(QM_CUBIN_DIR) "/qm_moe.sm_100a.cubin")
 
 struct KernelImage {
     const unsigned char *begin;
@@ -65,6 +66,7 @@ static const KernelImage kImages[QM_MOD_COUNT] = {
     {qm_cubin_dequant, qm_cubin_dequant_end},
     {qm_cubin_q4k, qm_cubin_q4k_end},
     {qm_cubin_gemm, qm_cubin_gemm_end},
+    {qm_cubin_moe, qm_cubin_moe_end},
 };
 struct KernelName {
     int module;
@@ -78,6 +80,8 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_DEQUANT, "qm_repack_q4k"},
     {QM_MOD_Q4K, "qm_fused_q4k_nt1"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2"},
     {QM_MOD_GEMM, "qm_gemm_q4k_bf16"},
+    {QM_MOD_MOE, "qm_moe_route"},      {QM_MOD_MOE, "qm_moe_lists"},      {QM_MOD_MOE, "qm_moe_gather"},
+    {QM_MOD_MOE, "qm_moe_swiglu"},     {QM_MOD_MOE, "qm_moe_combine"},
 };
 
 // ---- errors --------------------------------------------------------------------------
@@ -207,6 +211,7 @@ extern "C" int32_t qm_destroy(qm_ctx *c) {
             if (c->gridbar_dev) d->cuMemFree_v2(c->gridbar_dev);
             if (c->xstage_dev) d->cuMemFree_v2(c->xstage_dev);
             if (c->upload_dev) d->cuMemFree_v2(c->upload_dev);
+            if (c->moe_ws) d->cuMemFree_v2(c->moe_ws);
             if (c->own_stream) d->cuStreamDestroy_v2(c->own_stream);
             for (int m = 0; m < QM_MOD_COUNT; m++)
                 if (c->modules[m]) d->cuModuleUnload(c->modules[m]);

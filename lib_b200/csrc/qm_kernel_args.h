@@ -100,6 +100,45 @@ struct QmGemmArgs {
     int32_t stages;        // shared-memory stages, 2..4
 };
 
+// Mixture-of-experts helpers (qm_moe.cu).
+struct QmRouteArgs {
+    const float *logits;   // [tokens][ld]
+    const float *bias;     // [experts] or null
+    int32_t *ids;          // [tokens][topk]
+    float *weights;        // [tokens][topk]
+    int64_t ld;
+    int32_t tokens, experts, topk, pad;
+};
+struct QmListArgs {
+    const int32_t *ids;    // [tokens*topk]
+    int32_t *rank;         // scratch [tokens*topk]
+    int32_t *counts;       // [experts]
+    int32_t *offsets;      // [experts+1]
+    int32_t *list;         // [tokens*topk] pair indices grouped by expert
+    int32_t *pos;          // [tokens*topk] row of each pair in the grouping
+    int32_t tokens, experts, topk, pad;
+};
+struct QmGatherArgs {
+    const uint16_t *x;     // bf16 [tokens][ldx]
+    const int32_t *list;
+    uint16_t *out;         // bf16 [rows][hidden]
+    int64_t ldx;
+    int32_t rows, hidden, topk, pad;
+};
+struct QmSwigluArgs {
+    const float *gu;       // [rows][2*ffn]
+    uint16_t *h;           // bf16 [rows][ffn]
+    int32_t rows, ffn;
+};
+struct QmCombineArgs {
+    const float *y;        // [rows][hidden] expert outputs in grouped order
+    const int32_t *pos;
+    const float *weights;
+    float *out;            // [tokens][ldo]
+    int64_t ldo;
+    int32_t tokens, hidden, topk, pad;
+};
+
 struct QmDequantArgs {
     const uint8_t *wq;
     const uint16_t *wd;

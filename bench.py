@@ -65,7 +65,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -144,7 +144,7 @@ def workload_config(batch, gpus, where):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="b200")
@@ -195,14 +195,15 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident steps ---------------------------------------------------------
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)   # nvidia-smi needs a moment before its first sample
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
             runner.step_device(x_dev, m, h_dev)
         stream.synchronize()
         barrier()
-        sampler = ClockSampler(local)
-        if rank == 0:
-            sampler.start()
         launches0 = ctx.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
@@ -213,7 +214,6 @@ def main():
         barrier()
         ms = e0.elapsed_time(e1) / args.steps
         launches = ctx.launch_count() - launches0
-        clocks = sampler.stop() if rank == 0 else None
 
         # ---- end to end through host buffers ---------------------------------------------
         for _ in range(3):
@@ -226,14 +226,14 @@ def main():
         stream.synchronize()
         barrier()
         ms_e2e = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
 
     t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e = float(t[0]), float(t[1])
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        finish(dist)
         return
 
     pk, pk_kind = peaks()
@@ -251,14 +251,14 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {
-            "bound": "hbm", "kernel": "qm_gemv_q4k_m4" if m <= 4 else "qm_gemv_q4k_m8",
+            "bound": "hbm", "kernel": "qm_fused_q4k_nt1" if m <= 4 else "qm_fused_q4k_nt2",
             "achieved": achieved * world if world > 1 else achieved, "peak": pk["hbm_gbs"] * world, "unit": "GB/s",
             "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind + " (copy bandwidth, MEASURED_PEAKS.json)",
-            "per_launch": {"launches_per_step": n_launch, "avg_bytes": step_bytes / n_launch / world,
-                           "avg_us": ms * 1e3 / n_launch},
+            "per_launch": {"launches_per_step": max(1, round(launches / args.steps)), "matvecs_per_step": n_launch,
+                           "bytes_per_step": step_bytes / world, "us_per_step": ms * 1e3},
             "traffic": None,
             "note": "achieved = GGUF weight bytes + fp32 activation bytes of the step / CUDA-event time; the "
-                    "step is %d launches of this one kernel back to back" % n_launch,
+                    "step is %d matvecs run by this one kernel (one persistent launch per step on 1 GPU)" % n_launch,
         },
     }
     if world == 1 and not args.no_cpu_baseline:
@@ -272,9 +272,21 @@ def main():
     traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(traffic_file):
         line["roofline"]["traffic"] = json.load(open(traffic_file)).get("bytes_per_step_batch%d" % m)
-    print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    print(json.dumps(line), flush=True)
+    finish(dist)
+
+
+def finish(dist):
+    """Multi-rank runs leave through os._exit after a last barrier: tearing down CUDA graphs
+    that hold NCCL kernels together with the process group can block at interpreter exit."""
+    if dist is None:
+        return
+    import torch
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":

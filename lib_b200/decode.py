@@ -7,9 +7,18 @@ Weights are seeded synthetic tensors (lib_b200.synth); q, k, v and gate, up are
 generated as separate tensors and written into one store entry by rows, the way
 a loader would place a GGUF file's tensors.
 """
+import os
+import sys
+import time
+
 import numpy as np
 
 from . import _capi, synth
+
+
+def _trace(msg):
+    if os.environ.get("QM_TRACE"):
+        print("[rank %s %.1fs] %s" % (os.environ.get("RANK", "0"), time.perf_counter(), msg), file=sys.stderr, flush=True)
 
 
 def layer_tensors(fmt, hidden, kv, ffn, seed, layer):
@@ -33,16 +42,28 @@ def stacked(tensors):
     return out
 
 
-def upload_rows(ctx, fmt, rows, cols, parts, row_lo=0, row_hi=None):
-    """Store entry holding rows [row_lo, row_hi) of the row-stacked tensors `parts`."""
-    row_hi = rows if row_hi is None else row_hi
+def shard_slices(fmt, cols, parts, row_lo, row_hi):
+    """The pieces of the row-stacked tensors `parts` that fall in rows [row_lo, row_hi):
+    yields (row offset inside the shard, row count, GGUF bytes of those rows)."""
     be, bb = synth.BLOCK[fmt]
     row_bytes = cols // be * bb
-    w = ctx.store_create(fmt, row_hi - row_lo, cols)
     for off, nrows, data in parts:
         lo, hi = max(off, row_lo), min(off + nrows, row_hi)
         if lo < hi:
-            w.write_rows(lo - row_lo, hi - lo, data[(lo - off) * row_bytes:(hi - off) * row_bytes])
+            yield lo - row_lo, hi - lo, data[(lo - off) * row_bytes:(hi - off) * row_bytes]
+
+
+def shard_range(rows, rank, world):
+    """Rows [lo, hi) of a matrix that tensor-parallel rank `rank` of `world` holds."""
+    return rank * rows // world, (rank + 1) * rows // world
+
+
+def upload_rows(ctx, fmt, rows, cols, parts, row_lo=0, row_hi=None):
+    """Store entry holding rows [row_lo, row_hi) of the row-stacked tensors `parts`."""
+    row_hi = rows if row_hi is None else row_hi
+    w = ctx.store_create(fmt, row_hi - row_lo, cols)
+    for off, nrows, data in shard_slices(fmt, cols, parts, row_lo, row_hi):
+        w.write_rows(off, nrows, data)
     return w
 
 
@@ -83,9 +104,10 @@ class TensorParallelDecode:
         for L in range(layers):
             ws = []
             for rows, cols, parts in stacked(layer_tensors(fmt, hidden, kv, ffn, seed, L)):
-                lo, hi = rank * rows // world, (rank + 1) * rows // world
+                lo, hi = shard_range(rows, rank, world)
                 ws.append(upload_rows(ctx, fmt, rows, cols, parts, lo, hi))
             self.w.append(ws)
+        _trace("weights uploaded")
         self.graphs = {}
 
     def _buffers(self, m):
@@ -109,8 +131,9 @@ class TensorParallelDecode:
                 n = self.rows[i]
                 if i == 3:
                     x2 = x.data_ptr() + self.ffn * 4
+                # no programmatic dependent launch here: the neighbours in the stream are NCCL kernels
                 self.ctx.matvec(self.w[L][i], x.data_ptr(), m, ldx, b["shard"][i].data_ptr(), n // g,
-                                ops[i] | _capi.FLAG_PDL, x2 if i == 3 else 0)
+                                ops[i], x2 if i == 3 else 0)
                 full = b["qkv_all"][L] if i == 0 else b["full"][i]
                 if m == 1:
                     dist.all_gather_into_tensor(full.view(-1), b["shard"][i].view(-1))
@@ -126,19 +149,23 @@ class TensorParallelDecode:
             b = self._buffers(m)
             with t.cuda.stream(self.stream):
                 self.ctx.set_stream(self.stream.cuda_stream)
+                _trace("eager warm-up pass")
                 self._enqueue(b, m)  # warm-up outside capture (NCCL connection set-up)
                 self.stream.synchronize()
+                _trace("capturing")
                 graph = t.cuda.CUDAGraph()
                 with t.cuda.graph(graph, stream=self.stream):
                     self.ctx.set_stream(t.cuda.current_stream().cuda_stream)
                     out = self._enqueue(b, m)
                 self.ctx.set_stream(self.stream.cuda_stream)
+            _trace("captured")
             self.graphs[m] = (graph, b, out)
         return self.graphs[m]
 
     def step_device(self, x_dev, m, h_dev):
         graph, b, out = self._graph(m)
         b["x"].copy_(x_dev, non_blocking=True)
+        _trace("replay")
         graph.replay()
         h_dev.copy_(out, non_blocking=True)
 

@@ -35,6 +35,11 @@ NAMES = ["qkv", "o", "gate_up", "down"]
 SEED = 20240229
 
 
+# DRAM bytes per layer of the fused decode kernel at batch 1, from the ncu capture summarised in
+# profiles/qm_fused_q4k_nt1_two_layer_stack.md (245.46 MB read + 4.11 MB written for 2 layers).
+NCU_DRAM_BYTES_PER_LAYER_BATCH1 = (245.459712e6 + 4.109056e6) / 2
+
+
 def layer_bytes():
     from lib_b200 import synth
     return sum(synth.gguf_bytes(FMT, r, c) for r, c in SHAPES)
@@ -269,9 +274,10 @@ def main():
             "value": m / (t_layer * LAYERS), "unit": "tok/s", "cores": cores, "kind": "port",
             "sample": "1 of %d layers (4 matvecs, %.1f MB of Q4_K) repeated ~12 s, time x%d" % (
                 LAYERS, layer_bytes() / 1e6, LAYERS)}
-    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_file):
-        line["roofline"]["traffic"] = json.load(open(traffic_file)).get("bytes_per_step_batch%d" % m)
+    if world == 1 and m == 1:
+        line["roofline"]["traffic"] = NCU_DRAM_BYTES_PER_LAYER_BATCH1 * layers
+        line["roofline"]["traffic_note"] = ("dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
+                                            "kernel on a 2-layer stack, per layer x %d layers" % layers)
     print(json.dumps(line), flush=True)
     finish(dist)
 

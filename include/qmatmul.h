@@ -164,6 +164,24 @@ QM_API int32_t qm_moe_grouped(qm_ctx *ctx, const qm_weight *gate_up, const qm_we
                               uint64_t x_bf16_dev, int32_t tokens, int64_t ldx, uint64_t ids_dev,
                               uint64_t weights_dev, int32_t topk, uint64_t out_dev, int64_t ldo);
 
+/* The three stages of qm_moe_grouped, for expert-parallel runs where an exchange of rows
+ * between GPUs sits between them (token dispatch, nvidia/x/cudamoe/moe.go:72-96 gathers rows
+ * the same way; the exchange itself is the caller's NCCL all-to-all).
+ * qm_moe_dispatch: groups the (token, slot) pairs of ids[tokens][topk] by expert (ascending
+ *   token inside an expert), copies the bf16 row of each pair's token to rows[pairs][hidden] in
+ *   that order, writes pos[pair] = row of the pair in the grouping, and returns the list
+ *   lengths in counts_host[experts] (the call synchronizes the stream once to read them).
+ * qm_moe_experts: y[p] = down_e( silu(gate_e r_p) * (up_e r_p) ) over rows grouped by expert
+ *   (counts_host[e] consecutive rows per expert e, in order); y float32 [rows][hidden].
+ * qm_moe_combine: out[t] = sum_s weights[t][s] * y[pos[t*topk+s]], slots in order. */
+QM_API int32_t qm_moe_dispatch(qm_ctx *ctx, uint64_t ids_dev, int32_t tokens, int32_t topk, int32_t experts,
+                               uint64_t x_bf16_dev, int64_t ldx, int32_t hidden, uint64_t rows_dev,
+                               uint64_t pos_dev, int32_t *counts_host);
+QM_API int32_t qm_moe_experts(qm_ctx *ctx, const qm_weight *gate_up, const qm_weight *down, int32_t experts,
+                              uint64_t rows_bf16_dev, const int32_t *counts_host, uint64_t y_dev);
+QM_API int32_t qm_moe_combine(qm_ctx *ctx, uint64_t y_dev, uint64_t pos_dev, uint64_t weights_dev, int32_t tokens,
+                              int32_t topk, int32_t hidden, uint64_t out_dev, int64_t ldo);
+
 /* No counterpart in the reference. The Q4_0 / Q8_0 matvec of qm_matvec for callers that may
  * not allocate device memory at the point of the call: a server whose memory plan is frozen
  * once it starts serving, a latency-critical loop where an allocation would stall the device,

@@ -54,6 +54,9 @@ def _load():
         "qm_matmul_bf16": (i32, [p, u64, u64, i32, i64, u64, i64]),
         "qm_moe_route": (i32, [p, u64, i32, i64, i32, i32, u64, u64, u64]),
         "qm_moe_grouped": (i32, [p, p, p, i32, u64, i32, i64, u64, u64, i32, u64, i64]),
+        "qm_moe_dispatch": (i32, [p, u64, i32, i32, i32, u64, i64, i32, u64, u64, p]),
+        "qm_moe_experts": (i32, [p, p, p, i32, u64, p, u64]),
+        "qm_moe_combine": (i32, [p, u64, u64, u64, i32, i32, i32, u64, i64]),
         "qm_matvec_noalloc": (i32, [u64, u64, i32, i64, u64, i64, u64]),
         "qm_stack_create": (i32, [p, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_stack_destroy": (i32, [p, p]),
@@ -199,6 +202,24 @@ class Context:
         da = (ctypes.c_uint64 * n)(*[w.handle for w in down])
         _check(lib.qm_moe_grouped(self._h, ga, da, n, x_dev, tokens, ldx, ids_dev, weights_dev, topk, out_dev, ldo),
                "moe_grouped")
+
+    def moe_dispatch(self, ids_dev, tokens, topk, experts, x_dev, ldx, hidden, rows_dev, pos_dev):
+        """qm_moe_dispatch: rows grouped by expert + pos; returns the per-expert counts (list)."""
+        counts = (ctypes.c_int32 * experts)()
+        _check(lib.qm_moe_dispatch(self._h, ids_dev, tokens, topk, experts, x_dev, ldx, hidden, rows_dev, pos_dev,
+                                   counts), "moe_dispatch")
+        return list(counts)
+
+    def moe_experts(self, gate_up, down, rows_dev, counts, y_dev):
+        n = len(gate_up)
+        ga = (ctypes.c_uint64 * n)(*[w.handle for w in gate_up])
+        da = (ctypes.c_uint64 * n)(*[w.handle for w in down])
+        ca = (ctypes.c_int32 * n)(*[int(v) for v in counts])
+        _check(lib.qm_moe_experts(self._h, ga, da, n, rows_dev, ca, y_dev), "moe_experts")
+
+    def moe_combine(self, y_dev, pos_dev, weights_dev, tokens, topk, hidden, out_dev, ldo):
+        _check(lib.qm_moe_combine(self._h, y_dev, pos_dev, weights_dev, tokens, topk, hidden, out_dev, ldo),
+               "moe_combine")
 
     def matvec_noalloc(self, w, x_dev, m, ldx, y_dev, ldy, cu_stream=0):
         """qm_matvec_noalloc: Q4_0/Q8_0 matvec that allocates nothing (fixed scratch array)."""

@@ -212,6 +212,8 @@ extern "C" int32_t qm_destroy(qm_ctx *c) {
             if (c->xstage_dev) d->cuMemFree_v2(c->xstage_dev);
             if (c->upload_dev) d->cuMemFree_v2(c->upload_dev);
             if (c->moe_ws) d->cuMemFree_v2(c->moe_ws);
+            if (c->moe_ws2) d->cuMemFree_v2(c->moe_ws2);
+            if (c->moe_ws3) d->cuMemFree_v2(c->moe_ws3);
             if (c->own_stream) d->cuStreamDestroy_v2(c->own_stream);
             for (int m = 0; m < QM_MOD_COUNT; m++)
                 if (c->modules[m]) d->cuModuleUnload(c->modules[m]);

@@ -36,8 +36,8 @@ struct qm_ctx {
     CUdeviceptr xstage_dev;
     int64_t xstage_bytes;
     CUdeviceptr upload_dev;
-    CUdeviceptr moe_ws;
-    int64_t moe_ws_bytes;
+    CUdeviceptr moe_ws, moe_ws2, moe_ws3;   // scratch of the MoE stages (grown on demand)
+    int64_t moe_ws_bytes, moe_ws2_bytes, moe_ws3_bytes;
     int64_t launches;
 };
 

@@ -34,15 +34,171 @@ extern "C" int32_t qm_moe_route(qm_ctx *c, uint64_t logits_dev, int32_t tokens, 
     return qm_launch(c, QM_K_MOE_ROUTE, (unsigned)((tokens + 127) / 128), 1, 128, 0, &a, false);
 }
 
-static int32_t ensure_ws(qm_ctx *c, int64_t bytes) {
-    if (bytes <= c->moe_ws_bytes) return QM_OK;
+// Three growing scratch areas, one per stage, so that the stages can call one another:
+// the dispatch lists, the expert intermediates, and the grouped call's rows and outputs.
+static int32_t grow(qm_ctx *c, CUdeviceptr *p, int64_t *have, int64_t bytes) {
+    if (bytes <= *have) return QM_OK;
     DRV(c->drv->cuStreamSynchronize(c->stream));
-    if (c->moe_ws) DRV(c->drv->cuMemFree_v2(c->moe_ws));
-    c->moe_ws = 0;
-    c->moe_ws_bytes = 0;
-    DRV(c->drv->cuMemAlloc_v2(&c->moe_ws, (size_t)bytes));
-    c->moe_ws_bytes = bytes;
+    if (*p) DRV(c->drv->cuMemFree_v2(*p));
+    *p = 0;
+    *have = 0;
+    DRV(c->drv->cuMemAlloc_v2(p, (size_t)bytes));
+    *have = bytes;
     return QM_OK;
+}
+static int32_t ensure_ws(qm_ctx *c, int64_t bytes) { return grow(c, &c->moe_ws, &c->moe_ws_bytes, bytes); }
+static int32_t ensure_ws2(qm_ctx *c, int64_t bytes) { return grow(c, &c->moe_ws2, &c->moe_ws2_bytes, bytes); }
+static int32_t ensure_ws3(qm_ctx *c, int64_t bytes) { return grow(c, &c->moe_ws3, &c->moe_ws3_bytes, bytes); }
+
+static int32_t check_experts(const qm_weight *gate_up, const qm_weight *down, int32_t experts,
+                             std::vector<QmWeight *> &wg, std::vector<QmWeight *> &wd, int64_t *hidden, int64_t *ffn) {
+    if (!gate_up || !down) return QM_ERR_ARG;
+    if (experts < 1 || experts > 64) return QM_ERR_SHAPE;
+    wg.resize(experts);
+    wd.resize(experts);
+    for (int e = 0; e < experts; e++) {
+        wg[e] = qm_weight_from_handle(gate_up[e]);
+        wd[e] = qm_weight_from_handle(down[e]);
+        if (!wg[e] || !wd[e]) return QM_ERR_ARG;
+        if (wg[e]->fmt != QM_FMT_Q4_K || wd[e]->fmt != QM_FMT_Q4_K) return QM_ERR_FORMAT;
+    }
+    *hidden = wg[0]->cols;
+    *ffn = wd[0]->cols;
+    for (int e = 0; e < experts; e++)
+        if (wg[e]->cols != *hidden || wg[e]->rows != 2 * *ffn || wd[e]->rows != *hidden || wd[e]->cols != *ffn)
+            return QM_ERR_SHAPE;
+    if ((*hidden & 7) || (*ffn & 7)) return QM_ERR_SHAPE;
+    return QM_OK;
+}
+
+static inline int64_t up256(int64_t v) { return (v + 255) & ~(int64_t)255; }
+
+// Groups the (token, slot) pairs by expert and copies the bf16 rows of their tokens into that
+// order. Blocks until the list lengths are on the host: the caller sizes its launches (and, in
+// expert-parallel runs, its exchange) with them.
+extern "C" int32_t qm_moe_dispatch(qm_ctx *c, uint64_t ids_dev, int32_t tokens, int32_t topk, int32_t experts,
+                                   uint64_t x_bf16_dev, int64_t ldx, int32_t hidden, uint64_t rows_dev,
+                                   uint64_t pos_dev, int32_t *counts_host) {
+    CHECK_CTX(c);
+    if (!ids_dev || !x_bf16_dev || !rows_dev || !pos_dev || !counts_host) return QM_ERR_ARG;
+    if (experts < 1 || experts > 64 || tokens < 0 || topk < 1 || hidden < 8 || (hidden & 7) || ldx < hidden ||
+        (x_bf16_dev & 15) || (rows_dev & 15) || ((ldx * 2) & 15))
+        return QM_ERR_SHAPE;
+    for (int e = 0; e < experts; e++) counts_host[e] = 0;
+    if (tokens == 0) return QM_OK;
+    CtxGuard g(c);
+    DRV(g.rc);
+    const int64_t pairs = (int64_t)tokens * topk;
+    const int64_t o_rank = 0, o_counts = up256(pairs * 4), o_offsets = o_counts + 256, o_list = o_offsets + 512,
+                  total = o_list + up256(pairs * 4);
+    int32_t rc = ensure_ws(c, total);
+    if (rc) return rc;
+    const CUdeviceptr ws = c->moe_ws;
+    QmListArgs la;
+    memset(&la, 0, sizeof la);
+    la.ids = (const int32_t *)(uintptr_t)ids_dev;
+    la.rank = (int32_t *)(uintptr_t)(ws + o_rank);
+    la.counts = (int32_t *)(uintptr_t)(ws + o_counts);
+    la.offsets = (int32_t *)(uintptr_t)(ws + o_offsets);
+    la.list = (int32_t *)(uintptr_t)(ws + o_list);
+    la.pos = (int32_t *)(uintptr_t)pos_dev;
+    la.tokens = tokens;
+    la.experts = experts;
+    la.topk = topk;
+    rc = qm_launch(c, QM_K_MOE_LISTS, 1, 1, 1024, 0, &la, false);
+    if (rc) return rc;
+    int32_t offsets[65];
+    DRV(c->drv->cuMemcpyDtoHAsync_v2(offsets, ws + o_offsets, (size_t)(experts + 1) * 4, c->stream));
+    DRV(c->drv->cuStreamSynchronize(c->stream));
+    const int rows = offsets[experts];
+    if (rows < 0 || rows > pairs) return QM_ERR_STATE;
+    for (int e = 0; e < experts; e++) counts_host[e] = offsets[e + 1] - offsets[e];
+    if (rows == 0) return QM_OK;
+    QmGatherArgs ga;
+    memset(&ga, 0, sizeof ga);
+    ga.x = (const uint16_t *)(uintptr_t)x_bf16_dev;
+    ga.list = (const int32_t *)(uintptr_t)(ws + o_list);
+    ga.out = (uint16_t *)(uintptr_t)rows_dev;
+    ga.ldx = ldx;
+    ga.rows = rows;
+    ga.hidden = hidden;
+    ga.topk = topk;
+    return qm_launch(c, QM_K_MOE_GATHER, grid_for((int64_t)rows * hidden / 8, 256, c->sm_count * 8), 1, 256, 0, &ga, false);
+}
+
+// y[p][:] = down_e( silu(gate_e r_p) * (up_e r_p) ) for rows r grouped by expert: the first
+// counts[0] rows belong to expert 0, the next counts[1] to expert 1, and so on.
+extern "C" int32_t qm_moe_experts(qm_ctx *c, const qm_weight *gate_up, const qm_weight *down, int32_t experts,
+                                  uint64_t rows_bf16_dev, const int32_t *counts_host, uint64_t y_dev) {
+    CHECK_CTX(c);
+    if (!rows_bf16_dev || !counts_host || !y_dev) return QM_ERR_ARG;
+    std::vector<QmWeight *> wg, wd;
+    int64_t hidden = 0, ffn = 0;
+    int32_t rc = check_experts(gate_up, down, experts, wg, wd, &hidden, &ffn);
+    if (rc) return rc;
+    if (rows_bf16_dev & 15) return QM_ERR_SHAPE;
+    int64_t rows = 0;
+    for (int e = 0; e < experts; e++) {
+        if (counts_host[e] < 0) return QM_ERR_COUNT;
+        rows += counts_host[e];
+    }
+    if (rows == 0) return QM_OK;
+    if (rows >= (1 << 24)) return QM_ERR_SHAPE;
+    CtxGuard g(c);
+    DRV(g.rc);
+    // workspace behind the dispatch arrays: gate|up fp32, then the bf16 hidden activations
+    const int64_t o_gu = 0, o_h = o_gu + up256(rows * 2 * ffn * 4), total = o_h + up256(rows * ffn * 2);
+    rc = ensure_ws2(c, total);
+    if (rc) return rc;
+    const CUdeviceptr ws = c->moe_ws2;
+    int64_t off = 0;
+    for (int e = 0; e < experts; e++) {
+        const int n_e = counts_host[e];
+        if (n_e > 0) {
+            rc = qm_matmul_bf16(c, gate_up[e], rows_bf16_dev + off * hidden * 2, n_e, hidden, ws + o_gu + off * 2 * ffn * 4, 2 * ffn);
+            if (rc) return rc;
+        }
+        off += n_e;
+    }
+    QmSwigluArgs sa;
+    sa.gu = (const float *)(uintptr_t)(ws + o_gu);
+    sa.h = (uint16_t *)(uintptr_t)(ws + o_h);
+    sa.rows = (int32_t)rows;
+    sa.ffn = (int32_t)ffn;
+    rc = qm_launch(c, QM_K_MOE_SWIGLU, grid_for(rows * ffn / 2, 256, c->sm_count * 8), 1, 256, 0, &sa, false);
+    if (rc) return rc;
+    off = 0;
+    for (int e = 0; e < experts; e++) {
+        const int n_e = counts_host[e];
+        if (n_e > 0) {
+            rc = qm_matmul_bf16(c, down[e], ws + o_h + off * ffn * 2, n_e, ffn, y_dev + off * hidden * 4, hidden);
+            if (rc) return rc;
+        }
+        off += n_e;
+    }
+    return QM_OK;
+}
+
+// out[t][:] = sum_s weights[t][s] * y[pos[t*topk+s]][:], slots in order (deterministic).
+extern "C" int32_t qm_moe_combine(qm_ctx *c, uint64_t y_dev, uint64_t pos_dev, uint64_t weights_dev, int32_t tokens,
+                                  int32_t topk, int32_t hidden, uint64_t out_dev, int64_t ldo) {
+    CHECK_CTX(c);
+    if (!y_dev || !pos_dev || !weights_dev || !out_dev) return QM_ERR_ARG;
+    if (tokens < 0 || topk < 1 || hidden < 1 || ldo < hidden) return QM_ERR_SHAPE;
+    if (tokens == 0) return QM_OK;
+    CtxGuard g(c);
+    DRV(g.rc);
+    QmCombineArgs a;
+    memset(&a, 0, sizeof a);
+    a.y = (const float *)(uintptr_t)y_dev;
+    a.pos = (const int32_t *)(uintptr_t)pos_dev;
+    a.weights = (const float *)(uintptr_t)weights_dev;
+    a.out = (float *)(uintptr_t)out_dev;
+    a.ldo = ldo;
+    a.tokens = tokens;
+    a.hidden = hidden;
+    a.topk = topk;
+    return qm_launch(c, QM_K_MOE_COMBINE, grid_for((int64_t)tokens * hidden, 256, c->sm_count * 8), 1, 256, 0, &a, false);
 }
 
 // out[t][:] = sum_s weights[t][s] * down_e( silu(gate_e x_t) * (up_e x_t) ), e = ids[t][s].
@@ -51,100 +207,27 @@ extern "C" int32_t qm_moe_grouped(qm_ctx *c, const qm_weight *gate_up, const qm_
                                   uint64_t x_bf16_dev, int32_t tokens, int64_t ldx, uint64_t ids_dev,
                                   uint64_t weights_dev, int32_t topk, uint64_t out_dev, int64_t ldo) {
     CHECK_CTX(c);
-    if (!gate_up || !down || !x_bf16_dev || !ids_dev || !weights_dev || !out_dev) return QM_ERR_ARG;
-    if (experts < 1 || experts > 64 || tokens < 1 || topk < 1 || topk > experts) return QM_ERR_SHAPE;
-    std::vector<QmWeight *> wg(experts), wd(experts);
-    for (int e = 0; e < experts; e++) {
-        wg[e] = qm_weight_from_handle(gate_up[e]);
-        wd[e] = qm_weight_from_handle(down[e]);
-        if (!wg[e] || !wd[e]) return QM_ERR_ARG;
-        if (wg[e]->fmt != QM_FMT_Q4_K || wd[e]->fmt != QM_FMT_Q4_K) return QM_ERR_FORMAT;
-    }
-    const int64_t hidden = wg[0]->cols, ffn = wd[0]->cols;
-    for (int e = 0; e < experts; e++)
-        if (wg[e]->cols != hidden || wg[e]->rows != 2 * ffn || wd[e]->rows != hidden || wd[e]->cols != ffn) return QM_ERR_SHAPE;
-    if (ldx < hidden || ldo < hidden || (hidden & 7) || (ffn & 7) || (x_bf16_dev & 15) || ((ldx * 2) & 15)) return QM_ERR_SHAPE;
-    CtxGuard g(c);
-    DRV(g.rc);
-    const int64_t pairs = (int64_t)tokens * topk;
-    // workspace: int arrays, then gathered bf16, gate|up fp32, h bf16, expert outputs fp32
-    auto up256 = [](int64_t v) { return (v + 255) & ~(int64_t)255; };
-    const int64_t o_rank = 0, o_counts = up256(pairs * 4), o_offsets = o_counts + 256, o_list = o_offsets + 512,
-                  o_pos = o_list + up256(pairs * 4), o_gath = o_pos + up256(pairs * 4),
-                  o_gu = o_gath + up256(pairs * hidden * 2), o_h = o_gu + up256(pairs * 2 * ffn * 4),
-                  o_y = o_h + up256(pairs * ffn * 2), total = o_y + up256(pairs * hidden * 4);
-    int32_t rc = ensure_ws(c, total);
+    if (!x_bf16_dev || !ids_dev || !weights_dev || !out_dev) return QM_ERR_ARG;
+    if (tokens < 1 || topk < 1 || topk > experts) return QM_ERR_SHAPE;
+    std::vector<QmWeight *> wg, wd;
+    int64_t hidden = 0, ffn = 0;
+    int32_t rc = check_experts(gate_up, down, experts, wg, wd, &hidden, &ffn);
     if (rc) return rc;
-    const CUdeviceptr ws = c->moe_ws;
+    if (ldx < hidden || ldo < hidden) return QM_ERR_SHAPE;
+    const int64_t pairs = (int64_t)tokens * topk;
+    const int64_t o_rows = 0, o_pos = up256(pairs * hidden * 2), o_y = o_pos + up256(pairs * 4),
+                  total = o_y + up256(pairs * hidden * 4);
     {
-        QmListArgs a;
-        memset(&a, 0, sizeof a);
-        a.ids = (const int32_t *)(uintptr_t)ids_dev;
-        a.rank = (int32_t *)(uintptr_t)(ws + o_rank);
-        a.counts = (int32_t *)(uintptr_t)(ws + o_counts);
-        a.offsets = (int32_t *)(uintptr_t)(ws + o_offsets);
-        a.list = (int32_t *)(uintptr_t)(ws + o_list);
-        a.pos = (int32_t *)(uintptr_t)(ws + o_pos);
-        a.tokens = tokens;
-        a.experts = experts;
-        a.topk = topk;
-        rc = qm_launch(c, QM_K_MOE_LISTS, 1, 1, 1024, 0, &a, false);
+        CtxGuard g(c);
+        DRV(g.rc);
+        rc = ensure_ws3(c, total);
         if (rc) return rc;
     }
-    // the per-expert launches need the list lengths on the host
-    int32_t offsets[65];
-    DRV(c->drv->cuMemcpyDtoHAsync_v2(offsets, ws + o_offsets, (size_t)(experts + 1) * 4, c->stream));
-    DRV(c->drv->cuStreamSynchronize(c->stream));
-    const int rows = offsets[experts];
-    if (rows < 0 || rows > pairs) return QM_ERR_STATE;
-    {
-        QmGatherArgs a;
-        memset(&a, 0, sizeof a);
-        a.x = (const uint16_t *)(uintptr_t)x_bf16_dev;
-        a.list = (const int32_t *)(uintptr_t)(ws + o_list);
-        a.out = (uint16_t *)(uintptr_t)(ws + o_gath);
-        a.ldx = ldx;
-        a.rows = rows;
-        a.hidden = (int32_t)hidden;
-        a.topk = topk;
-        rc = qm_launch(c, QM_K_MOE_GATHER, grid_for((int64_t)rows * hidden / 8, 256, c->sm_count * 8), 1, 256, 0, &a, false);
-        if (rc) return rc;
-    }
-    for (int e = 0; e < experts; e++) {
-        const int n_e = offsets[e + 1] - offsets[e];
-        if (n_e <= 0) continue;
-        rc = qm_matmul_bf16(c, gate_up[e], ws + o_gath + (int64_t)offsets[e] * hidden * 2, n_e, hidden,
-                            ws + o_gu + (int64_t)offsets[e] * 2 * ffn * 4, 2 * ffn);
-        if (rc) return rc;
-    }
-    {
-        QmSwigluArgs a;
-        a.gu = (const float *)(uintptr_t)(ws + o_gu);
-        a.h = (uint16_t *)(uintptr_t)(ws + o_h);
-        a.rows = rows;
-        a.ffn = (int32_t)ffn;
-        rc = qm_launch(c, QM_K_MOE_SWIGLU, grid_for((int64_t)rows * ffn / 2, 256, c->sm_count * 8), 1, 256, 0, &a, false);
-        if (rc) return rc;
-    }
-    for (int e = 0; e < experts; e++) {
-        const int n_e = offsets[e + 1] - offsets[e];
-        if (n_e <= 0) continue;
-        rc = qm_matmul_bf16(c, down[e], ws + o_h + (int64_t)offsets[e] * ffn * 2, n_e, ffn,
-                            ws + o_y + (int64_t)offsets[e] * hidden * 4, hidden);
-        if (rc) return rc;
-    }
-    {
-        QmCombineArgs a;
-        memset(&a, 0, sizeof a);
-        a.y = (const float *)(uintptr_t)(ws + o_y);
-        a.pos = (const int32_t *)(uintptr_t)(ws + o_pos);
-        a.weights = (const float *)(uintptr_t)weights_dev;
-        a.out = (float *)(uintptr_t)out_dev;
-        a.ldo = ldo;
-        a.tokens = tokens;
-        a.hidden = (int32_t)hidden;
-        a.topk = topk;
-        rc = qm_launch(c, QM_K_MOE_COMBINE, grid_for((int64_t)tokens * hidden, 256, c->sm_count * 8), 1, 256, 0, &a, false);
-    }
-    return rc;
+    const CUdeviceptr ws = c->moe_ws3;
+    int32_t counts[64];
+    rc = qm_moe_dispatch(c, ids_dev, tokens, topk, experts, x_bf16_dev, ldx, (int32_t)hidden, ws + o_rows, ws + o_pos, counts);
+    if (rc) return rc;
+    rc = qm_moe_experts(c, gate_up, down, experts, ws + o_rows, counts, ws + o_y);
+    if (rc) return rc;
+    return qm_moe_combine(c, ws + o_y, ws + o_pos, weights_dev, tokens, topk, (int32_t)hidden, out_dev, ldo);
 }

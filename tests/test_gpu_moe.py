@@ -104,3 +104,27 @@ def test_mixtral_shape_sampled_tokens(ctx, devbuf):
     """Config 5: 8 experts, top-2, hidden 4096, ffn 14336, 512 tokens; three tokens checked
     against the oracle (all 512 go through the kernels)."""
     assert run_moe(ctx, devbuf, 8, 4096, 14336, 512, 2, 500, [0, 255, 511]) <= TOL
+
+
+def test_layer_stages_match_oracle(ctx):
+    """lib_b200.moe.MoELayer on one GPU (route -> dispatch -> experts -> combine through the
+    staged entry points) against the oracle chain."""
+    import torch
+    from lib_b200 import moe
+    experts, topk, hidden, ffn, tokens, seed = 4, 2, 512, 768, 45, 3
+    layer = moe.MoELayer(ctx, experts, topk, hidden, ffn, seed)
+    dev = torch.device("cuda:0")
+    x_bits = to_bf16_bits(synth.activations(tokens, hidden, 900))
+    lg = synth.activations(tokens, experts, 901)
+    x = torch.from_numpy(x_bits.view(np.int16)).to(dev).view(torch.bfloat16)
+    out = layer.forward(x, torch.from_numpy(lg).to(dev))
+    ids, wts = layer.route(torch.from_numpy(lg).to(dev))
+    torch.cuda.synchronize()
+    rc, status = ctx.last_status()
+    assert rc == 0 and status == 0
+    raws = [moe.expert_weights(hidden, ffn, e, seed) for e in range(experts)]
+    want = moe_oracle([r[0] for r in raws], [r[1] for r in raws], hidden, ffn, x_bits, ids.cpu().numpy(),
+                      wts.cpu().numpy(), list(range(tokens)))
+    got = out.cpu().numpy().astype(np.float64)
+    assert float(np.linalg.norm(got - want) / np.linalg.norm(want)) <= TOL
+    layer.close()

@@ -120,7 +120,95 @@ struct Cursor {   // walks the items of this warp, op after op
     int64_t tile_skip;    // bytes from the end of a tile's slice to the start of the next tile's
 };
 
+// Quantizes the 256 activations of row j, unit ul (eight per lane, v) into limbs and writes
+// them, their sub-block sums and the column weights in the layout the main loop reads; the
+// destination is shared memory or an activation image. Returns this lane's sum of squares.
 template <int NT>
+__device__ __forceinline__ float quantize_pair(const float (&v)[8], int j, int ul, int lane, int NL, int CPM,
+                                               uint8_t *xs_b, int pstride, uint32_t *xsum_b, float *sxw_b) {
+    float amax = 0.f, sum = 0.f, sq = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; e++) { amax = fmaxf(amax, fabsf(v[e])); sum += v[e]; sq = fmaf(v[e], v[e], sq); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    const float sx = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
+    const float inv = amax > 0.f ? 127.f / amax : 0.f;
+    // Limbs by magic-number rounding: adding 1.5*2^23 rounds to the nearest integer and
+    // leaves it (two's complement) in the low mantissa bits — no conversion instructions.
+    uint32_t hb[8], l1b[8], l2b[8];
+    constexpr float kMagicF = 12582912.f;
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const float r = v[e] * inv;
+        const float t0 = r + kMagicF;
+        const float r1 = (r - (t0 - kMagicF)) * 128.f;
+        const float t1 = r1 + kMagicF;
+        const float r2 = (r1 - (t1 - kMagicF)) * 128.f;
+        const float t2 = r2 + kMagicF;
+        hb[e] = __float_as_uint(t0);
+        l1b[e] = __float_as_uint(t1);
+        l2b[e] = __float_as_uint(t2);
+    }
+    auto pack4 = [](uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) -> uint32_t {
+        return prmt(prmt(b0, b1, 0x0040u), prmt(b2, b3, 0x0040u), 0x5410u);  // low bytes of the four
+    };
+    const uint32_t w0[3] = {pack4(hb[0], hb[1], hb[2], hb[3]), pack4(l1b[0], l1b[1], l1b[2], l1b[3]),
+                            pack4(l2b[0], l2b[1], l2b[2], l2b[3])};
+    const uint32_t w1[3] = {pack4(hb[4], hb[5], hb[6], hb[7]), pack4(l1b[4], l1b[5], l1b[6], l1b[7]),
+                            pack4(l2b[4], l2b[5], l2b[6], l2b[7])};
+    // lane = 4*sub-block + t': this lane's 8 columns are the B fragment of lane t' for
+    // sub-block sb; the fragments of sub-blocks 2p and 2p+1 sit side by side
+    const int sb = lane >> 2, tq = lane & 3;
+    const int off = ((ul * 4 + (sb >> 1)) * 4 + tq) * 16 + (sb & 1) * 8;
+    for (int l = 0; l < NL; l++)
+        *reinterpret_cast<uint2 *>(xs_b + (size_t)(j * NL + l) * pstride + off) = make_uint2(w0[l], w1[l]);
+    const int n0 = j * CPM;   // first mma column of this activation row
+    if (tq == 0) {
+        // sub-block sums in units of the unit's maximum (|.| <= 32): safe in fp16 whatever
+        // the magnitude of the activations; the factor comes back with the column weight
+        const float sn = sum * inv * (1.f / 127.f);
+        const __half sh = __float2half_rn(sn);
+        const __half sl = __float2half_rn(sn - __half2float(sh));
+        __half *xh = reinterpret_cast<__half *>(xsum_b);
+        xh[((size_t)ul * 8 * NT + n0) * 8 + sb] = sh;
+        xh[((size_t)ul * 8 * NT + n0 + 1) * 8 + sb] = sl;
+    }
+    if (lane < CPM) {
+        const float lw = lane == 0 ? 1.f : lane == 1 ? (1.f / 128.f) : lane == 2 && NL == 3 ? (1.f / 16384.f) : 0.f;
+        sxw_b[(size_t)ul * 8 * NT + n0 + lane] = sx * lw;
+    }
+    return sq;
+}
+
+// One warp writes activation row j of unit u of the next op's activation image:
+// x = y[u] (+ y[half + u] when the next op adds two halves of y). Called outside the streaming
+// loop only, so that it does not cost the loop its registers.
+template <int NT>
+__device__ __noinline__ void quantize_row(const float *y, int64_t ldy, int u, int j, int NL, int CPM, int halves,
+                                          int half_tiles, uint8_t *img, int img_plane_stride, size_t off_xsum,
+                                          size_t off_sxw, size_t off_ssq) {
+    const int lane = threadIdx.x & 31;
+    const float *xp = y + (int64_t)j * ldy + u * QM_K_UNIT + lane * 8;
+    const float4 r0 = __ldcg(reinterpret_cast<const float4 *>(xp));
+    const float4 r1 = __ldcg(reinterpret_cast<const float4 *>(xp + 4));
+    float v[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    if (halves == 2) {
+        const float *x2p = xp + (int64_t)half_tiles * 16;
+        const float4 s0 = __ldcg(reinterpret_cast<const float4 *>(x2p));
+        const float4 s1 = __ldcg(reinterpret_cast<const float4 *>(x2p + 4));
+        v[0] += s0.x; v[1] += s0.y; v[2] += s0.z; v[3] += s0.w;
+        v[4] += s1.x; v[5] += s1.y; v[6] += s1.z; v[7] += s1.w;
+    }
+    float sq = quantize_pair<NT>(v, j, u, lane, NL, CPM, img, img_plane_stride,
+                                 reinterpret_cast<uint32_t *>(img + off_xsum), reinterpret_cast<float *>(img + off_sxw));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if (lane == 0) reinterpret_cast<float *>(img + off_ssq)[u * 8 + j] = sq;
+}
+
+template <int NT, bool IMG>
 __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -245,6 +333,69 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     Cursor cc;
     cursor_at(cc, 0);
 
+    // Layout of an activation image in global memory: the limb planes with room for
+    // a.img_units units each, then the sub-block sums, the column weights and the sums of squares
+    // per (unit, activation row).
+    const int img_plane_stride = a.img_units * 256 + 64;
+    const size_t img_off_xsum = (size_t)P * img_plane_stride;
+    const size_t img_off_sxw = img_off_xsum + (size_t)a.img_units * 8 * NT * 16;
+    const size_t img_off_ssq = img_off_sxw + (size_t)a.img_units * 8 * NT * 4;
+
+    auto quant_pair = [&](const float (&v)[8], int j, int ul, uint8_t *xs_b, int pstride, uint32_t *xsum_b,
+                          float *sxw_b) -> float {
+        return quantize_pair<NT>(v, j, ul, lane, NL, CPM, xs_b, pstride, xsum_b, sxw_b);
+    };
+    // Producer side of the activation image: called by a warp after its final stores (or adds)
+    // to tile `gtile` of y. `add` is 2 when the warp completed the whole tile and 1 when it is
+    // one of the two CTAs that share it. The warp that brings a unit's counter to its full count
+    // quantizes the unit for every activation row.
+    // The image fields of an op are read where they are needed (once per finished tile), not
+    // kept in registers through the streaming loop.
+    auto arrive = [&](int opi, int gtile, unsigned int add) -> int {
+        if (!IMG) return -1;
+        const QmOp *po = ops + opi;
+        unsigned int *cnt = po->q_cnt;
+        if (!cnt) return -1;
+        const int half_tiles = po->q_half_tiles, halves = po->q_halves;
+        if (gtile >= half_tiles * halves) return -1;    // rows that the next op does not read
+        const int half = gtile >= half_tiles ? 1 : 0;
+        const int u = (gtile - half * half_tiles) >> 4;
+        const int tiles_in_unit = min(16, half_tiles - 16 * u);
+        const unsigned int full = 2u * (unsigned int)(tiles_in_unit * halves);
+        __threadfence();
+        __syncwarp();
+        unsigned int old = 0;
+        if (lane == 0) old = atomicAdd(cnt + u, add);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        return old + add == full ? u : -1;
+    };
+    // Units completed by this CTA's warps wait in a short shared list (the reduction scratch is
+    // free between staging and the next op); after the CTA's last stores all warps share the
+    // (unit, activation row) pairs, so the tail is one row per warp, not a unit per warp.
+    int *done = reinterpret_cast<int *>(red);
+    constexpr int kDoneCap = 31;
+    auto quantize_rows = [&](int opi, int u, int j0, int j1) {
+        const QmOp *po = ops + opi;
+        const float *y = po->y;
+        const int64_t ldy = po->ldy;
+        const int halves = po->q_halves, half_tiles = po->q_half_tiles;
+        uint8_t *img = po->q_img;
+        for (int j = j0; j < j1; j++)
+            quantize_row<NT>(y, ldy, u, j, NL, CPM, halves, half_tiles, img, img_plane_stride, img_off_xsum,
+                             img_off_sxw, img_off_ssq);
+    };
+    auto note_done = [&](int opi, int du) {
+        if (du < 0) return;
+        int slot = 0;
+        if (lane == 0) slot = atomicAdd(&done[0], 1);
+        slot = __shfl_sync(0xffffffffu, slot, 0);
+        if (slot < kDoneCap) {
+            if (lane == 0) done[1 + slot] = du;
+        } else {
+            quantize_rows(opi, du, 0, M);   // list full: this warp does the unit alone
+        }
+    };
+
     for (int opi = 0; opi < a.nops; opi++) {
         const QmOp op = ops[opi];   // by value: no reloads through the generic pointer
         mark_op = opi;
@@ -295,7 +446,9 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         // op that covers a slice of K needs a pass of its own over the whole row.
         const bool norm = (op.xop == 1 || op.xop == 2);
         const bool sliced = op.units != op.units_total;
-        if (norm && sliced) {
+        const uint8_t *op_img = IMG ? (ops + opi)->img : nullptr;
+        const bool pre = op_img != nullptr;
+        if (norm && sliced && !pre) {
             for (int j = 0; j < M; j++) {
                 float s = 0.f;
                 const float *xr = op.x + (int64_t)j * op.ldx;
@@ -334,95 +487,75 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 r[3] = __ldcg(reinterpret_cast<const float4 *>(x2p + 4));
             }
         };
-        float4 raw[4], raw_next[4];
-        float sq_run = 0.f;
-        int sq_j = -1;
-        if (norm && !sliced && lane < 8) ssq[lane * 16 + warp] = 0.f;
-        __syncwarp();
-        if (warp < M * nun) load_raw(warp, raw);
-        for (int idx = warp; idx < M * nun; idx += C) {
-            const int j = idx / nun, ul = idx - j * nun;
-            if (idx + C < M * nun) load_raw(idx + C, raw_next);
-            float v[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
-            if (op.xop >= 2) {
-                const float w[8] = {raw[2].x, raw[2].y, raw[2].z, raw[2].w, raw[3].x, raw[3].y, raw[3].z, raw[3].w};
+        if (!pre) {
+            float4 raw[4], raw_next[4];
+            float sq_run = 0.f;
+            int sq_j = -1;
+            if (norm && !sliced && lane < 8) ssq[lane * 16 + warp] = 0.f;
+            __syncwarp();
+            if (warp < M * nun) load_raw(warp, raw);
+            for (int idx = warp; idx < M * nun; idx += C) {
+                const int j = idx / nun, ul = idx - j * nun;
+                if (idx + C < M * nun) load_raw(idx + C, raw_next);
+                float v[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
+                if (op.xop >= 2) {
+                    const float w[8] = {raw[2].x, raw[2].y, raw[2].z, raw[2].w, raw[3].x, raw[3].y, raw[3].z, raw[3].w};
 #pragma unroll
-                for (int e = 0; e < 8; e++)
-                    v[e] = op.xop == 2 ? v[e] + w[e] : v[e] / (1.f + __expf(-v[e])) * w[e];
-            }
-#pragma unroll
-            for (int e = 0; e < 4; e++) raw[e] = raw_next[e];
-            float amax = 0.f, sum = 0.f, sq = 0.f;
-#pragma unroll
-            for (int e = 0; e < 8; e++) { amax = fmaxf(amax, fabsf(v[e])); sum += v[e]; sq = fmaf(v[e], v[e], sq); }
-            if (norm && !sliced) {   // per-warp running sum of squares of activation row j
-                if (j != sq_j) {
-                    if (sq_j >= 0) {
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
-                        if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
-                    }
-                    sq_j = j;
-                    sq_run = 0.f;
+                    for (int e = 0; e < 8; e++)
+                        v[e] = op.xop == 2 ? v[e] + w[e] : v[e] / (1.f + __expf(-v[e])) * w[e];
                 }
-                sq_run += sq;
-            }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            const float sx = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
-            const float inv = amax > 0.f ? 127.f / amax : 0.f;
-            // Limbs by magic-number rounding: adding 1.5*2^23 rounds to the nearest integer and
-            // leaves it (two's complement) in the low mantissa bits — no conversion instructions.
-            uint32_t hb[8], l1b[8], l2b[8];
-            constexpr float kMagicF = 12582912.f;
+                for (int e = 0; e < 4; e++) raw[e] = raw_next[e];
+                const float sq = quant_pair(v, j, ul, xs, plane_stride, xsum, sxw);
+                if (norm && !sliced) {   // per-warp running sum of squares of activation row j
+                    if (j != sq_j) {
+                        if (sq_j >= 0) {
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const float r = v[e] * inv;
-                const float t0 = r + kMagicF;
-                const float r1 = (r - (t0 - kMagicF)) * 128.f;
-                const float t1 = r1 + kMagicF;
-                const float r2 = (r1 - (t1 - kMagicF)) * 128.f;
-                const float t2 = r2 + kMagicF;
-                hb[e] = __float_as_uint(t0);
-                l1b[e] = __float_as_uint(t1);
-                l2b[e] = __float_as_uint(t2);
+                            for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
+                            if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
+                        }
+                        sq_j = j;
+                        sq_run = 0.f;
+                    }
+                    sq_run += sq;
+                }
             }
-            auto pack4 = [](uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) -> uint32_t {
-                return prmt(prmt(b0, b1, 0x0040u), prmt(b2, b3, 0x0040u), 0x5410u);  // low bytes of the four
-            };
-            const uint32_t w0[3] = {pack4(hb[0], hb[1], hb[2], hb[3]), pack4(l1b[0], l1b[1], l1b[2], l1b[3]),
-                                    pack4(l2b[0], l2b[1], l2b[2], l2b[3])};
-            const uint32_t w1[3] = {pack4(hb[4], hb[5], hb[6], hb[7]), pack4(l1b[4], l1b[5], l1b[6], l1b[7]),
-                                    pack4(l2b[4], l2b[5], l2b[6], l2b[7])};
-            // lane = 4*sub-block + t': this lane's 8 columns are the B fragment of lane t' for
-            // sub-block sb; the fragments of sub-blocks 2p and 2p+1 sit side by side
-            const int sb = lane >> 2, tq = lane & 3;
-            const int off = ((ul * 4 + (sb >> 1)) * 4 + tq) * 16 + (sb & 1) * 8;
-            for (int l = 0; l < NL; l++)
-                *reinterpret_cast<uint2 *>(xs + (size_t)(j * NL + l) * plane_stride + off) = make_uint2(w0[l], w1[l]);
-            const int n0 = j * CPM;   // first mma column of this activation row
-            if (tq == 0) {
-                // sub-block sums in units of the unit's maximum (|.| <= 32): safe in fp16 whatever
-                // the magnitude of the activations; the factor comes back with the column weight
-                const float sn = sum * inv * (1.f / 127.f);
-                const __half sh = __float2half_rn(sn);
-                const __half sl = __float2half_rn(sn - __half2float(sh));
-                __half *xh = reinterpret_cast<__half *>(xsum);
-                xh[((size_t)ul * 8 * NT + n0) * 8 + sb] = sh;
-                xh[((size_t)ul * 8 * NT + n0 + 1) * 8 + sb] = sl;
+            if (sq_j >= 0) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
+                if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
             }
-            if (lane < CPM) {
-                const float lw = lane == 0 ? 1.f : lane == 1 ? (1.f / 128.f) : lane == 2 && NL == 3 ? (1.f / 16384.f) : 0.f;
-                sxw[(size_t)ul * 8 * NT + n0 + lane] = sx * lw;
+        } else {
+            // ---- the previous op left the quantized x in global memory: copy this slice in -------
+            const uint8_t *img = op_img;
+            const int nplanes = M * NL;
+            const int per_plane = nun * 16;                       // 16-byte pieces of a plane's slice
+            const int n_xs = nplanes * per_plane, n_sum = nun * 8 * NT, n_w = nun * 2 * NT;
+            const uint4 *g_xsum = reinterpret_cast<const uint4 *>(img + img_off_xsum) + (size_t)op.unit0 * 8 * NT;
+            const uint4 *g_sxw = reinterpret_cast<const uint4 *>(img + img_off_sxw) + (size_t)op.unit0 * 2 * NT;
+            // sixteen-byte asynchronous copies: nothing is staged in registers. They form a commit
+            // group of their own behind the ring's groups; waiting for all groups costs nothing here,
+            // the ring's copies were started before the grid barrier.
+            const uint8_t *img_xs = img + (size_t)op.unit0 * 256;
+            for (int i = tid; i < n_xs; i += nthreads) {
+                const int pl = i / per_plane, kk = i - pl * per_plane;
+                cp_async16(smem_u32(xs + (size_t)pl * plane_stride + (size_t)kk * 16),
+                           img_xs + (size_t)pl * img_plane_stride + (size_t)kk * 16);
+            }
+            for (int i = tid; i < n_sum + n_w; i += nthreads) {
+                if (i < n_sum) cp_async16(smem_u32(reinterpret_cast<uint4 *>(xsum) + i), g_xsum + i);
+                else cp_async16(smem_u32(reinterpret_cast<uint4 *>(sxw) + (i - n_sum)), g_sxw + (i - n_sum));
+            }
+            cp_async_commit();
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            if (norm && tid < M) {   // sum of squares of row tid: the units' parts in unit order
+                const float *g_ssq = reinterpret_cast<const float *>(img + img_off_ssq);
+                float sq = 0.f;
+                for (int u = 0; u < op.units_total; u++) sq += __ldcg(g_ssq + u * 8 + tid);
+                s_scale[tid] = rsqrtf(sq / (float)op.cols + op.eps);
             }
         }
-        if (sq_j >= 0) {
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
-            if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
-        }
+        if (IMG && tid == 0) done[0] = 0;
         __syncthreads();
 
         float myscale[NT];
@@ -431,7 +564,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         if (norm) {
             for (int j = 0; j < M; j++) {
                 float sc;
-                if (sliced) {
+                if (sliced || pre) {
                     sc = s_scale[j];
                 } else {
                     float sq = 0.f;
@@ -493,6 +626,9 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                             if (rB < op.rows) atomicAdd(yB, vB[nt]);
                         }
                     }
+                // a unit that this store completed is quantized by the CTA after its last stores
+                const int du = arrive(opi, tile0 + tile, whole ? 2u : 1u);
+                note_done(opi, du);
                 return;
             }
             // slot 1: this warp's range ends inside the tile; slot 0: it joined the tile late and
@@ -636,6 +772,16 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                     else atomicAdd(yp, sum);
                 }
             }
+            const int du = arrive(opi, tile0 + fin_tile, whole ? 2u : 1u);
+            note_done(opi, du);
+        }
+        if (IMG && (ops + opi)->q_cnt) {
+            __syncthreads();
+            const int n = min(done[0], kDoneCap);
+            for (int idx = warp; idx < n * M; idx += C) {
+                const int k = idx / M, j = idx - k * M;
+                quantize_rows(opi, done[1 + k], j, j + 1);
+            }
         }
         QM_MARK(5);
     }
@@ -645,9 +791,18 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
 
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt1(const __grid_constant__ QmFusedArgs a) {
-    fused_body<1>(a);
+    fused_body<1, false>(a);
 }
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt2(const __grid_constant__ QmFusedArgs a) {
-    fused_body<2>(a);
+    fused_body<2, false>(a);
+}
+// The same with activation images between dependent ops (used from two activation rows on).
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_nt1_img(const __grid_constant__ QmFusedArgs a) {
+    fused_body<1, true>(a);
+}
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_nt2_img(const __grid_constant__ QmFusedArgs a) {
+    fused_body<2, true>(a);
 }

@@ -71,6 +71,15 @@ struct QmOp {
     // addends on a zero: order-independent), and y's shared tiles are zeroed during the op before
     int32_t q, rem;
     int32_t balanced, pad;
+    // Activation image: the quantized form of an op's x (limb planes, sub-block sums, column
+    // weights, sums of squares per unit) in global memory. An op whose x is the previous op's y
+    // can read it ready-made instead of every CTA quantizing all of x: the previous op builds
+    // it unit by unit, each unit by the warp whose store completes the unit's 256 outputs.
+    const uint8_t *img;       // consumer side: image of this op's x, or null (quantize in the CTA)
+    uint8_t *q_img;           // producer side: image of the NEXT op's x, or null
+    unsigned int *q_cnt;      // producer side: one completion counter per unit of the next op's x, zero at launch
+    int32_t q_half_tiles;     // 16-row tiles of y per operand of the next op (its cols / 16)
+    int32_t q_halves;         // 1, or 2 when the next op's x is the sum of two halves of y
 };
 
 struct QmFusedArgs {
@@ -83,7 +92,8 @@ struct QmFusedArgs {
     int32_t max_units;   // largest K units over the ops: sizes the activation planes
     int32_t cpm;         // mma columns per activation row: 4 (m <= 2) or 2 (m <= 4, or 8 with two column tiles)
     int32_t debug;       // 0 in production
-    int32_t debug_slot, pad2;
+    int32_t debug_slot;
+    int32_t img_units;   // K units an activation image has room for (>= units_total of every op that reads one)
 };
 
 // Prefill GEMM over Q4_K weights (tcgen05): C[m][n] = sum_k A[m][k] * W[n][k].

@@ -27,6 +27,12 @@ struct qm_stack {
     CUgraphExec graph[9];
     CUdeviceptr ops_dev[9];     // fused op lists, one per batch size
     QmFusedPlan fused_plan[9];
+    int fused_nops[9];          // ops in the list (a matrix whose K does not fit is several ops)
+    CUdeviceptr img_dev[9];     // two activation images per batch size, used alternately
+    CUdeviceptr sync_dev[9];    // grid barrier word (first 256 bytes), then the unit counters
+    size_t sync_bytes[9];
+    int img_units[9];
+    bool fused_img[9];          // the op list uses activation images
     bool use_graph, use_fused;
 };
 
@@ -52,6 +58,8 @@ extern "C" int32_t qm_stack_create(qm_ctx *c, int32_t layers, int32_t hidden, in
     memset(s->layer.data(), 0, sizeof(QmLayer) * layers);
     memset(s->graph, 0, sizeof s->graph);
     memset(s->ops_dev, 0, sizeof s->ops_dev);
+    memset(s->img_dev, 0, sizeof s->img_dev);
+    memset(s->sync_dev, 0, sizeof s->sync_dev);
     s->use_graph = true;
     s->use_fused = true;
     CtxGuard g(c);
@@ -79,6 +87,8 @@ extern "C" int32_t qm_stack_destroy(qm_ctx *c, qm_stack *s) {
     for (int i = 0; i < 9; i++) {
         if (s->graph[i]) c->drv->cuGraphExecDestroy(s->graph[i]);
         if (s->ops_dev[i]) c->drv->cuMemFree_v2(s->ops_dev[i]);
+        if (s->img_dev[i]) c->drv->cuMemFree_v2(s->img_dev[i]);
+        if (s->sync_dev[i]) c->drv->cuMemFree_v2(s->sync_dev[i]);
     }
     CUdeviceptr bufs[5] = {s->h0, s->qkv_out, s->o_out, s->gu_out, s->dn_out};
     for (CUdeviceptr b : bufs)
@@ -108,8 +118,12 @@ extern "C" int32_t qm_stack_set_layer(qm_ctx *c, qm_stack *s, int32_t layer, qm_
         if (s->ops_dev[i]) {
             c->drv->cuStreamSynchronize(c->stream);
             c->drv->cuMemFree_v2(s->ops_dev[i]);
+            if (s->img_dev[i]) c->drv->cuMemFree_v2(s->img_dev[i]);
+            if (s->sync_dev[i]) c->drv->cuMemFree_v2(s->sync_dev[i]);
         }
         s->ops_dev[i] = 0;
+        s->img_dev[i] = 0;
+        s->sync_dev[i] = 0;
     }
     return QM_OK;
 }
@@ -154,32 +168,92 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
         }
     }
     QmFusedPlan p;
-    int32_t rc = qm_plan_fused(c, m, max_units, false, &p);
+    int32_t rc = qm_plan_fused(c, m, max_units, true, &p);
     if (rc) return rc;
-    std::vector<QmOp> ops((size_t)4 * s->layers);
+    // One group of ops per matrix: a matrix whose K units exceed what a CTA can hold of the
+    // activations is cut into K slices, the later ones adding to y.
+    std::vector<QmOp> ops;
+    std::vector<int> group_first, group_last;
+    auto add_matvec = [&](const QmWeight *w, CUdeviceptr x, CUdeviceptr x2, int64_t ldx, CUdeviceptr y, int64_t ldy,
+                          uint32_t xop, bool first) {
+        const int nslices = (w->units + p.max_units - 1) / p.max_units;
+        const int ups = (w->units + nslices - 1) / nslices;
+        group_first.push_back((int)ops.size());
+        for (int sl = 0; sl < nslices; sl++) {
+            QmOp op;
+            const int u0 = sl * ups, n = std::min(ups, (int)w->units - u0);
+            qm_fill_op(c, p, w, x, x2, ldx, y, ldy, xop, !(first && sl == 0), u0, n, sl > 0, &op);
+            ops.push_back(op);
+        }
+        group_last.push_back((int)ops.size() - 1);
+    };
     const int64_t qkv_ld = s->hidden + 2 * s->kv;
     for (int L = 0; L < s->layers; L++) {
         const QmLayer &ly = s->layer[L];
         const CUdeviceptr qkv = s->qkv_out + (size_t)L * m * qkv_ld * 4;
-        QmOp *o = &ops[(size_t)4 * L];
-        qm_fill_op(c, p, ly.qkv, L == 0 ? s->h0 : s->dn_out, 0, s->hidden, qkv, qkv_ld, QM_XOP_RMSNORM, L > 0, 0,
-                   ly.qkv->units, 0, o + 0);
-        qm_fill_op(c, p, ly.o, qkv, 0, qkv_ld, s->o_out, s->hidden, QM_XOP_RMSNORM, 1, 0, ly.o->units, 0, o + 1);
-        qm_fill_op(c, p, ly.gu, s->o_out, 0, s->hidden, s->gu_out, 2 * s->ffn, QM_XOP_RMSNORM, 1, 0, ly.gu->units, 0,
-                   o + 2);
-        qm_fill_op(c, p, ly.dn, s->gu_out, s->gu_out + (size_t)s->ffn * 4, 2 * s->ffn, s->dn_out, s->hidden,
-                   QM_XOP_ADD_RMSNORM, 1, 0, ly.dn->units, 0, o + 3);
+        add_matvec(ly.qkv, L == 0 ? s->h0 : s->dn_out, 0, s->hidden, qkv, qkv_ld, QM_XOP_RMSNORM, L == 0);
+        add_matvec(ly.o, qkv, 0, qkv_ld, s->o_out, s->hidden, QM_XOP_RMSNORM, false);
+        add_matvec(ly.gu, s->o_out, 0, s->hidden, s->gu_out, 2 * s->ffn, QM_XOP_RMSNORM, false);
+        add_matvec(ly.dn, s->gu_out, s->gu_out + (size_t)s->ffn * 4, 2 * s->ffn, s->dn_out, s->hidden,
+                   QM_XOP_ADD_RMSNORM, false);
     }
-    // every op but the first writes a buffer that the op before it does not touch
-    for (size_t k = 1; k < ops.size(); k++) qm_balance_op(c, &ops[k]);
-    CUdeviceptr dev = 0;
-    DRV(c->drv->cuMemAlloc_v2(&dev, ops.size() * sizeof(QmOp)));
-    CUresult r = c->drv->cuMemcpyHtoD_v2(dev, ops.data(), ops.size() * sizeof(QmOp));
+    for (const QmOp &op : ops)
+        if ((int64_t)op.tiles * op.units >= (1ll << 31)) return QM_ERR_SHAPE;
+    // every unsliced op but the first writes a buffer that the op before it does not touch
+    for (size_t k = 1; k < ops.size(); k++)
+        if (ops[k].units == ops[k].units_total) qm_balance_op(c, &ops[k]);
+
+    // Activation images: the last op of a matrix quantizes the next matrix's x as its outputs
+    // complete, so that the CTAs of the next op copy the quantized form instead of each
+    // quantizing all of x. Two images alternate (the readers of one are a grid barrier away from
+    // its next writers); one completion counter per (matrix, unit), zeroed before each launch.
+    const int NT = p.nt, NL = p.cpm == 4 ? 3 : 2, P = m * NL;
+    const int img_units = max_units;
+    const size_t img_bytes = (size_t)P * (img_units * 256 + 64) + (size_t)img_units * 8 * NT * 20 + (size_t)img_units * 32;
+    const size_t img_stride = (img_bytes + 255) & ~(size_t)255;
+    const size_t ngroups = group_first.size();
+    const size_t sync_bytes = 256 + ngroups * (size_t)img_units * 4;
+    CUdeviceptr img = 0, sync = 0, dev = 0;
+    CUresult r = c->drv->cuMemAlloc_v2(&img, 2 * img_stride);
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&sync, sync_bytes);
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemsetD8Async(img, 0, 2 * img_stride, c->stream);
+    // With one or two activation rows the per-CTA quantization is cheaper than the producers'
+    // fences and counters (measured per step, batch 1: 1.83 ms against 2.30 ms; batch 2: 2.09 ms
+    // against 2.33 ms); beyond that the image wins (batch 4: 2.46 ms; batch 8: 3.52 ms against 5.93 ms).
+    bool uses_img = false;
+    const int min_m = qm_env_int("QM_IMAGE_MIN_M", 3), min_units = qm_env_int("QM_IMAGE_MIN_UNITS", 1 << 30);
+    if (r == CUDA_SUCCESS && !qm_env_int("QM_NO_IMAGE", 0)) {
+        for (size_t k = 0; k + 1 < ngroups; k++) {
+            QmOp &prod = ops[group_last[k]];
+            const QmOp &cons = ops[group_first[k + 1]];
+            const bool two = cons.xop == QM_XOP_ADD_RMSNORM;
+            if (m < min_m && cons.units_total < min_units) continue;
+            if (cons.xop > QM_XOP_ADD_RMSNORM || (cons.cols & 255) || cons.x != prod.y || cons.ldx != prod.ldy) continue;
+            if (two && cons.x2 != prod.y + cons.cols) continue;
+            if ((int64_t)cons.cols * (two ? 2 : 1) > prod.rows) continue;
+            prod.q_img = (uint8_t *)(uintptr_t)(img + ((k + 1) & 1) * img_stride);
+            prod.q_cnt = (unsigned int *)(uintptr_t)(sync + 256 + (k + 1) * (size_t)img_units * 4);
+            prod.q_half_tiles = cons.cols / 16;
+            prod.q_halves = two ? 2 : 1;
+            for (int o = group_first[k + 1]; o <= group_last[k + 1]; o++) ops[o].img = prod.q_img;
+            uses_img = true;
+        }
+    }
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&dev, ops.size() * sizeof(QmOp));
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemcpyHtoD_v2(dev, ops.data(), ops.size() * sizeof(QmOp));
     if (r != CUDA_SUCCESS) {
-        c->drv->cuMemFree_v2(dev);
+        if (dev) c->drv->cuMemFree_v2(dev);
+        if (img) c->drv->cuMemFree_v2(img);
+        if (sync) c->drv->cuMemFree_v2(sync);
         return (int32_t)r;
     }
     s->ops_dev[m] = dev;
+    s->img_dev[m] = img;
+    s->sync_dev[m] = sync;
+    s->sync_bytes[m] = sync_bytes;
+    s->img_units[m] = img_units;
+    s->fused_nops[m] = (int)ops.size();
+    s->fused_img[m] = uses_img;
     s->fused_plan[m] = p;
     return QM_OK;
 }
@@ -190,8 +264,9 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
     memset(&a, 0, sizeof a);
     a.ops = (const QmOp *)(uintptr_t)s->ops_dev[m];
     a.status = (unsigned int *)(uintptr_t)c->status_dev;
-    a.grid_bar = (unsigned int *)(uintptr_t)c->gridbar_dev;
-    a.nops = 4 * s->layers;
+    a.grid_bar = (unsigned int *)(uintptr_t)s->sync_dev[m];
+    a.nops = s->fused_nops[m];
+    a.img_units = s->img_units[m];
     a.m = m;
     a.consumers = p.consumers;
     a.depth = p.depth;
@@ -199,9 +274,11 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
     a.cpm = p.cpm;
     a.debug = qm_env_int("QM_DEBUG_SKIP", 0);
     a.debug_slot = qm_env_int("QM_DEBUG_OP", 0);
-    DRV(c->drv->cuMemsetD32Async(c->gridbar_dev, 0, 1, c->stream));
+    DRV(c->drv->cuMemsetD32Async(s->sync_dev[m], 0, s->sync_bytes[m] / 4, c->stream));
     // cooperative: the grid barrier between dependent matvecs needs every CTA resident
-    return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2, (unsigned)qm_fused_grid(c),
+    const int kern = s->fused_img[m] ? (p.nt == 1 ? QM_K_FUSED_Q4K_NT1_IMG : QM_K_FUSED_Q4K_NT2_IMG)
+                                     : (p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2);
+    return qm_launch_ex(c, kern, (unsigned)qm_fused_grid(c),
                         (unsigned)p.consumers * 32, (unsigned)p.smem, &a, false, true);
 }
 

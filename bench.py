@@ -186,7 +186,10 @@ def main():
         runner = decode.SingleGpuDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED)
     else:
         from lib_b200 import decode
-        runner = decode.TensorParallelDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED, rank, world, stream)
+        if os.environ.get("QM_TP_MODE", "peer") == "nccl":   # the plain NCCL all-gather arm, for comparison
+            runner = decode.TensorParallelDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED, rank, world, stream)
+        else:
+            runner = decode.PeerTensorParallelDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED, rank, world)
 
     x_host = torch.from_numpy(synth.activations(m, HIDDEN, SEED + 999)).pin_memory()
     x_dev = x_host.to("cuda", non_blocking=False)

@@ -227,8 +227,27 @@ QM_API int32_t qm_stack_step_host(qm_ctx *ctx, qm_stack *stack, const float *x_h
 /* Activation buffers for per-matvec checks: [0] input, [1] q|k|v of every layer, [2] o,
  * [3] gate|up, [4] down (of the last layer run). */
 QM_API int32_t qm_stack_buffers(qm_ctx *ctx, qm_stack *stack, uint64_t *ptrs5);
-/* 0 = issue the launches one by one instead of replaying the captured graph. */
+/* 0 = issue the launches one by one; 1 = replay them as a captured graph; 2 (default) = the
+ * whole step as one persistent launch where format and shapes allow it, else as 1. */
 QM_API int32_t qm_stack_use_graph(qm_ctx *ctx, qm_stack *stack, int32_t on);
+
+/* Tensor-parallel decode stack over the GPUs of one box, one process per GPU (config "row
+ * sharding at 1/2/4/8 GPUs"): rank `rank` of `world` (<= 8) holds rows
+ * [rank*R/world, (rank+1)*R/world) of every matrix (R/world a multiple of 16) and hands those
+ * slices to qm_stack_set_layer. The whole step is one persistent launch per GPU: a GPU's
+ * output slice is stored straight into every peer's activation buffers over NVLink (peer
+ * memory mapped through CUDA IPC) and the barrier between dependent matvecs spans the GPUs
+ * (arrival flags in peer memory, every wait bounded: QM_STATUS timeout in qm_last_status) —
+ * the all-gather of the reference's plan (nvidia/nccl AllGather, nvidia/nccl/nccl.gen.go)
+ * fused into the matvec kernel. Set-up: every rank creates its stack, exports
+ * qm_stack_ipc_handle (64 bytes), the handles are exchanged by the caller (any transport) and
+ * given to qm_stack_set_peers as world x 64 bytes in rank order. Steps must be issued by all
+ * ranks, the same number of times with the same m. qm_stack_step_host returns the full h on
+ * every rank and, in kv_host, only the k|v rows of the rank's own slice. */
+QM_API int32_t qm_stack_create_tp(qm_ctx *ctx, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
+                                  int32_t m_max, int32_t rank, int32_t world, qm_stack **out);
+QM_API int32_t qm_stack_ipc_handle(qm_ctx *ctx, qm_stack *stack, void *handle64);
+QM_API int32_t qm_stack_set_peers(qm_ctx *ctx, qm_stack *stack, const void *handles);
 
 #ifdef __cplusplus
 }

@@ -65,6 +65,9 @@ def _load():
         "qm_stack_step_host": (i32, [p, p, p, i32, p, p]),
         "qm_stack_buffers": (i32, [p, p, ctypes.POINTER(u64)]),
         "qm_stack_use_graph": (i32, [p, p, i32]),
+        "qm_stack_create_tp": (i32, [p, i32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
+        "qm_stack_ipc_handle": (i32, [p, p, p]),
+        "qm_stack_set_peers": (i32, [p, p, p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -238,12 +241,30 @@ class Context:
 class Stack:
     """qm_stack: a decode step over `layers` quantized transformer-shaped layers."""
 
-    def __init__(self, ctx, layers, hidden, kv_dim, ffn, m_max=8):
+    def __init__(self, ctx, layers, hidden, kv_dim, ffn, m_max=8, rank=0, world=1):
         self.ctx, self.layers, self.hidden, self.kv_dim, self.ffn, self.m_max = ctx, layers, hidden, kv_dim, ffn, m_max
+        self.rank, self.world = rank, world
         h = ctypes.c_void_p()
-        _check(lib.qm_stack_create(ctx._h, layers, hidden, kv_dim, ffn, m_max, ctypes.byref(h)), "stack_create")
+        if world == 1:
+            _check(lib.qm_stack_create(ctx._h, layers, hidden, kv_dim, ffn, m_max, ctypes.byref(h)), "stack_create")
+        else:
+            _check(lib.qm_stack_create_tp(ctx._h, layers, hidden, kv_dim, ffn, m_max, rank, world, ctypes.byref(h)),
+                   "stack_create_tp")
         self._h = h
         self.weights = []
+
+    def ipc_handle(self):
+        """64-byte CUDA IPC handle of the tensor-parallel activation arena."""
+        buf = (ctypes.c_ubyte * 64)()
+        _check(lib.qm_stack_ipc_handle(self.ctx._h, self._h, buf), "stack_ipc_handle")
+        return bytes(buf)
+
+    def set_peers(self, handles):
+        """handles: the `world` 64-byte handles in rank order."""
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.world
+        buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
+        _check(lib.qm_stack_set_peers(self.ctx._h, self._h, buf), "stack_set_peers")
 
     def set_layer(self, layer, qkv, o, gate_up, down):
         _check(lib.qm_stack_set_layer(self.ctx._h, self._h, layer, qkv.handle, o.handle, gate_up.handle,

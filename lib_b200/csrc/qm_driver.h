@@ -47,6 +47,9 @@
     X(cuEventElapsedTime, CUresult (*)(float *, CUevent, CUevent))                                \
     X(cuEventDestroy_v2, CUresult (*)(CUevent))                                                   \
     X(cuGetErrorString, CUresult (*)(CUresult, const char **))                                    \
+    X(cuIpcGetMemHandle, CUresult (*)(CUipcMemHandle *, CUdeviceptr))                             \
+    X(cuIpcOpenMemHandle_v2, CUresult (*)(CUdeviceptr *, CUipcMemHandle, unsigned int))           \
+    X(cuIpcCloseMemHandle, CUresult (*)(CUdeviceptr))                                             \
     X(cuTensorMapEncodeTiled,                                                                     \
       CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,    \
                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,                    \

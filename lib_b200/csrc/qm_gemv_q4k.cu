@@ -208,7 +208,7 @@ __device__ __noinline__ void quantize_row(const float *y, int64_t ldy, int u, in
     if (lane == 0) reinterpret_cast<float *>(img + off_ssq)[u * 8 + j] = sq;
 }
 
-template <int NT, bool IMG>
+template <int NT, bool IMG, bool TP>
 __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -396,6 +396,55 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         }
     };
 
+    // Barrier over all CTAs (and, tensor-parallel, over all GPUs). Every wait is bounded: after
+    // about two seconds the CTA records QM_STATUS_TIMEOUT, stops waiting at this and all later
+    // barriers, and runs to the end.
+    bool dead = false;   // meaningful in thread 0
+    auto grid_sync = [&]() {
+        if (tid == 0) {
+            if (TP) __threadfence_system(); else __threadfence();
+            const unsigned int target = (nbar + 1) * gridDim.x;
+            const unsigned int old = atomicAdd(a.grid_bar, 1u);
+            const unsigned int epoch = a.tp_epoch0 + nbar + 1;
+            if (TP && old + 1 == target) {   // this GPU's slice is complete: tell the peers
+                __threadfence_system();
+                for (int p = 0; p < a.tp_world; p++)
+                    if (p != a.tp_rank)
+                        st_release_sys(reinterpret_cast<unsigned int *>(
+                                           reinterpret_cast<char *>(a.tp_flags + a.tp_rank) + a.peer_delta[p]), epoch);
+            }
+            const long long t0 = clock64();
+            while (!dead && ld_acquire(a.grid_bar) < target) {
+                if (clock64() - t0 > 4000000000ll) {
+                    atomicOr(a.status, QM_STATUS_TIMEOUT);
+                    dead = true;
+                }
+                __nanosleep(64);
+            }
+            if (TP) {
+                for (int p = 0; p < a.tp_world; p++) {
+                    if (p == a.tp_rank) continue;
+                    while (!dead && (int)(ld_acquire_sys(a.tp_flags + p) - epoch) < 0) {
+                        if (clock64() - t0 > 4000000000ll) {
+                            atomicOr(a.status, QM_STATUS_TIMEOUT);
+                            dead = true;
+                        }
+                    }
+                }
+            }
+        }
+        nbar++;
+        __syncthreads();
+    };
+    // Stores a finished output, tensor-parallel also into every peer's arena.
+    auto store_y = [&](float *yp, float val) {
+        *yp = val;
+        if (TP) {
+            for (int p = 0; p < a.tp_world; p++)
+                if (p != a.tp_rank) *reinterpret_cast<float *>(reinterpret_cast<char *>(yp) + a.peer_delta[p]) = val;
+        }
+    };
+
     for (int opi = 0; opi < a.nops; opi++) {
         const QmOp op = ops[opi];   // by value: no reloads through the generic pointer
         mark_op = opi;
@@ -404,23 +453,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         // ---- wait for the producers of x, and for this CTA's readers of the old planes --------
         if (opi > 0) {
             __syncthreads();
-            if (op.barrier) {
-                if (tid == 0) {
-                    __threadfence();
-                    atomicAdd(a.grid_bar, 1u);
-                    const unsigned int target = (nbar + 1) * gridDim.x;
-                    const long long t0 = clock64();
-                    while (ld_acquire(a.grid_bar) < target) {
-                        if (clock64() - t0 > 4000000000ll) {
-                            atomicOr(a.status, QM_STATUS_TIMEOUT);
-                            break;
-                        }
-                        __nanosleep(64);
-                    }
-                }
-                nbar++;
-                __syncthreads();
-            }
+            if (op.barrier) grid_sync();
         }
         QM_MARK(1);
         // ---- quantize the activations of this op into limbs, once per CTA ---------------------
@@ -619,8 +652,8 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                     if (valid[nt]) {
                         float *yA = op.y + (int64_t)jrow[nt] * op.ldy + rA, *yB = yA + 8;
                         if (whole) {
-                            if (rA < op.rows) *yA = vA[nt] + (op.accumulate ? __ldcg(yA) : 0.f);
-                            if (rB < op.rows) *yB = vB[nt] + (op.accumulate ? __ldcg(yB) : 0.f);
+                            if (rA < op.rows) store_y(yA, vA[nt] + (op.accumulate ? __ldcg(yA) : 0.f));
+                            if (rB < op.rows) store_y(yB, vB[nt] + (op.accumulate ? __ldcg(yB) : 0.f));
                         } else {   // the tile is shared with a neighbouring CTA
                             if (rA < op.rows) atomicAdd(yA, vA[nt]);
                             if (rB < op.rows) atomicAdd(yB, vB[nt]);
@@ -768,7 +801,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 const int j = o >> 4, r = (tile0 + fin_tile) * 16 + (o & 15);
                 float *yp = op.y + (int64_t)j * op.ldy + r;
                 if (r < op.rows) {
-                    if (whole) *yp = sum + (op.accumulate ? __ldcg(yp) : 0.f);
+                    if (whole) store_y(yp, sum + (op.accumulate ? __ldcg(yp) : 0.f));
                     else atomicAdd(yp, sum);
                 }
             }
@@ -785,24 +818,39 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         }
         QM_MARK(5);
     }
+    // Tensor-parallel: the launch ends only when every GPU's last slice has arrived everywhere,
+    // so that the host may read the outputs and the next launch may overwrite the inputs.
+    if (TP) {
+        __syncthreads();
+        grid_sync();
+    }
 }
 
 }  // namespace
 
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt1(const __grid_constant__ QmFusedArgs a) {
-    fused_body<1, false>(a);
+    fused_body<1, false, false>(a);
 }
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt2(const __grid_constant__ QmFusedArgs a) {
-    fused_body<2, false>(a);
+    fused_body<2, false, false>(a);
 }
 // The same with activation images between dependent ops (used from two activation rows on).
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt1_img(const __grid_constant__ QmFusedArgs a) {
-    fused_body<1, true>(a);
+    fused_body<1, true, false>(a);
 }
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt2_img(const __grid_constant__ QmFusedArgs a) {
-    fused_body<2, true>(a);
+    fused_body<2, true, false>(a);
+}
+// Tensor-parallel variants: outputs go to every peer's arena, barriers span the GPUs.
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_nt1_tp(const __grid_constant__ QmFusedArgs a) {
+    fused_body<1, false, true>(a);
+}
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_nt2_tp(const __grid_constant__ QmFusedArgs a) {
+    fused_body<2, false, true>(a);
 }

@@ -51,6 +51,7 @@ struct QmGemvArgs {
 // One matvec of a fused sequence (Q4_K weights, integer tensor-core path).
 #define QM_Q4K_ITEM_BYTES 2304
 #define QM_MAX_INLINE_OPS 8
+#define QM_MAX_PEERS 8
 
 struct QmOp {
     const uint8_t *wq;   // tiled Q4_K store layout
@@ -94,6 +95,16 @@ struct QmFusedArgs {
     int32_t debug;       // 0 in production
     int32_t debug_slot;
     int32_t img_units;   // K units an activation image has room for (>= units_total of every op that reads one)
+    // Tensor-parallel launch (kernels *_tp): this GPU computes a row slice of every op and stores
+    // it into the same place of every peer's activation arena (its own address + peer_delta[p]);
+    // the barrier between dependent ops then spans the GPUs: the last CTA of a GPU to arrive
+    // writes the barrier's epoch into flag [tp_rank] of every peer, and every CTA waits for the
+    // flags of all peers in its own arena.
+    int32_t tp_world, tp_rank;       // tp_world <= 1: single GPU
+    unsigned int tp_epoch0;          // epoch of the launch's first barrier minus one; grows from launch to launch
+    unsigned int tp_pad;
+    unsigned int *tp_flags;          // [tp_world] in this GPU's arena, written by the peers
+    int64_t peer_delta[QM_MAX_PEERS];   // bytes from an address in this arena to the same place in peer p's
 };
 
 // Prefill GEMM over Q4_K weights (tcgen05): C[m][n] = sum_k A[m][k] * W[n][k].

@@ -33,19 +33,30 @@ struct qm_stack {
     size_t sync_bytes[9];
     int img_units[9];
     bool fused_img[9];          // the op list uses activation images
+    // tensor-parallel: one arena holds all activation buffers and the peers' arrival flags; the
+    // peers map it through CUDA IPC and this GPU stores its row slices into all of them
+    int tp_world, tp_rank;
+    CUdeviceptr arena;
+    size_t arena_bytes, flags_off;
+    CUdeviceptr peer_base[QM_MAX_PEERS];
+    bool peers_open;
+    unsigned int tp_epoch;
     bool use_graph, use_fused;
 };
 
 static qm_stack *stack_check(qm_stack *s) { return (s && s->magic == QM_STACK_MAGIC) ? s : nullptr; }
 
-extern "C" int32_t qm_stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
-                                   int32_t m_max, qm_stack **out) {
+static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn, int32_t m_max,
+                            int32_t rank, int32_t world, qm_stack **out) {
     CHECK_CTX(c);
     if (!out) return QM_ERR_ARG;
     *out = nullptr;
     if (layers < 1 || layers > 1024 || hidden < 32 || kv_dim < 0 || ffn < 32 || m_max < 1 || m_max > 8)
         return QM_ERR_SHAPE;
     if ((hidden & 3) || (kv_dim & 3) || (ffn & 3)) return QM_ERR_SHAPE;
+    if (world < 1 || world > QM_MAX_PEERS || rank < 0 || rank >= world) return QM_ERR_ARG;
+    if (world > 1 && (((hidden + 2 * kv_dim) % (16 * world)) || (hidden % (16 * world)) || ((2 * ffn) % (16 * world))))
+        return QM_ERR_SHAPE;   // every GPU's row slice must be whole 16-row tiles
     qm_stack *s = new (std::nothrow) qm_stack();
     if (!s) return QM_ERR_NOMEM;
     s->magic = QM_STACK_MAGIC;
@@ -54,6 +65,12 @@ extern "C" int32_t qm_stack_create(qm_ctx *c, int32_t layers, int32_t hidden, in
     s->kv = kv_dim;
     s->ffn = ffn;
     s->m_max = m_max;
+    s->tp_world = world;
+    s->tp_rank = rank;
+    s->arena = 0;
+    s->peers_open = false;
+    s->tp_epoch = 0;
+    memset(s->peer_base, 0, sizeof s->peer_base);
     s->layer.resize(layers);
     memset(s->layer.data(), 0, sizeof(QmLayer) * layers);
     memset(s->graph, 0, sizeof s->graph);
@@ -65,16 +82,84 @@ extern "C" int32_t qm_stack_create(qm_ctx *c, int32_t layers, int32_t hidden, in
     CtxGuard g(c);
     CUresult r = g.rc;
     const size_t f = 4;
-    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->h0, (size_t)m_max * hidden * f);
-    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->qkv_out, (size_t)layers * m_max * (hidden + 2 * kv_dim) * f);
-    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->o_out, (size_t)m_max * hidden * f);
-    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->gu_out, (size_t)m_max * 2 * ffn * f);
-    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->dn_out, (size_t)m_max * hidden * f);
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    const size_t b_h0 = up((size_t)m_max * hidden * f), b_qkv = up((size_t)layers * m_max * (hidden + 2 * kv_dim) * f),
+                 b_o = up((size_t)m_max * hidden * f), b_gu = up((size_t)m_max * 2 * ffn * f),
+                 b_dn = up((size_t)m_max * hidden * f);
+    if (world == 1) {
+        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->h0, b_h0);
+        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->qkv_out, b_qkv);
+        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->o_out, b_o);
+        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->gu_out, b_gu);
+        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->dn_out, b_dn);
+    } else {
+        s->flags_off = b_h0 + b_qkv + b_o + b_gu + b_dn;
+        s->arena_bytes = s->flags_off + 256;
+        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->arena, s->arena_bytes);
+        if (r == CUDA_SUCCESS) r = c->drv->cuMemsetD8Async(s->arena, 0, s->arena_bytes, c->stream);
+        if (r == CUDA_SUCCESS) r = c->drv->cuStreamSynchronize(c->stream);
+        s->h0 = s->arena;
+        s->qkv_out = s->h0 + b_h0;
+        s->o_out = s->qkv_out + b_qkv;
+        s->gu_out = s->o_out + b_o;
+        s->dn_out = s->gu_out + b_gu;
+    }
     if (r != CUDA_SUCCESS) {
         qm_stack_destroy(c, s);
         return (int32_t)r;
     }
     *out = s;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
+                                   int32_t m_max, qm_stack **out) {
+    return stack_create(c, layers, hidden, kv_dim, ffn, m_max, 0, 1, out);
+}
+
+// Tensor-parallel stack: rank `rank` of `world` GPUs of one box. Every matrix handed to
+// qm_stack_set_layer holds this rank's slice of the rows, rows [rank*R/world, (rank+1)*R/world).
+extern "C" int32_t qm_stack_create_tp(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
+                                      int32_t m_max, int32_t rank, int32_t world, qm_stack **out) {
+    return stack_create(c, layers, hidden, kv_dim, ffn, m_max, rank, world, out);
+}
+
+// The CUDA IPC handle (64 bytes) of this stack's activation arena, for the peers.
+extern "C" int32_t qm_stack_ipc_handle(qm_ctx *c, qm_stack *s, void *handle64) {
+    CHECK_CTX(c);
+    if (!stack_check(s) || !handle64 || s->tp_world < 2) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    CUipcMemHandle h;
+    DRV(c->drv->cuIpcGetMemHandle(&h, s->arena));
+    static_assert(sizeof(CUipcMemHandle) == 64, "IPC handle size");
+    memcpy(handle64, &h, 64);
+    return QM_OK;
+}
+
+// handles: world x 64 bytes, entry p = the handle of rank p's arena (entry tp_rank is ignored).
+// Maps every peer's arena into this process; a step can run afterwards.
+extern "C" int32_t qm_stack_set_peers(qm_ctx *c, qm_stack *s, const void *handles) {
+    CHECK_CTX(c);
+    if (!stack_check(s) || !handles || s->tp_world < 2 || s->peers_open) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    for (int p = 0; p < s->tp_world; p++) {
+        if (p == s->tp_rank) {
+            s->peer_base[p] = s->arena;
+            continue;
+        }
+        CUipcMemHandle h;
+        memcpy(&h, (const char *)handles + (size_t)p * 64, 64);
+        CUresult r = c->drv->cuIpcOpenMemHandle_v2(&s->peer_base[p], h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS);
+        if (r != CUDA_SUCCESS) {
+            for (int q = 0; q < p; q++)
+                if (q != s->tp_rank && s->peer_base[q]) c->drv->cuIpcCloseMemHandle(s->peer_base[q]);
+            memset(s->peer_base, 0, sizeof s->peer_base);
+            return (int32_t)r;
+        }
+    }
+    s->peers_open = true;
     return QM_OK;
 }
 
@@ -90,9 +175,16 @@ extern "C" int32_t qm_stack_destroy(qm_ctx *c, qm_stack *s) {
         if (s->img_dev[i]) c->drv->cuMemFree_v2(s->img_dev[i]);
         if (s->sync_dev[i]) c->drv->cuMemFree_v2(s->sync_dev[i]);
     }
-    CUdeviceptr bufs[5] = {s->h0, s->qkv_out, s->o_out, s->gu_out, s->dn_out};
-    for (CUdeviceptr b : bufs)
-        if (b) c->drv->cuMemFree_v2(b);
+    if (s->tp_world > 1) {
+        if (s->peers_open)
+            for (int p = 0; p < s->tp_world; p++)
+                if (p != s->tp_rank && s->peer_base[p]) c->drv->cuIpcCloseMemHandle(s->peer_base[p]);
+        if (s->arena) c->drv->cuMemFree_v2(s->arena);
+    } else {
+        CUdeviceptr bufs[5] = {s->h0, s->qkv_out, s->o_out, s->gu_out, s->dn_out};
+        for (CUdeviceptr b : bufs)
+            if (b) c->drv->cuMemFree_v2(b);
+    }
     s->magic = 0;
     delete s;
     return QM_OK;
@@ -106,8 +198,9 @@ extern "C" int32_t qm_stack_set_layer(qm_ctx *c, qm_stack *s, int32_t layer, qm_
                       qm_weight_from_handle(down)};
     for (QmWeight *p : w)
         if (!p) return QM_ERR_ARG;
-    const int64_t want[4][2] = {{s->hidden + 2 * s->kv, s->hidden}, {s->hidden, s->hidden},
-                                {2 * s->ffn, s->hidden}, {s->hidden, s->ffn}};
+    const int64_t W = s->tp_world;   // tensor-parallel: this rank's slice of the rows
+    const int64_t want[4][2] = {{(s->hidden + 2 * s->kv) / W, s->hidden}, {s->hidden / W, s->hidden},
+                                {2 * s->ffn / W, s->hidden}, {s->hidden / W, s->ffn}};
     for (int i = 0; i < 4; i++)
         if (w[i]->rows != want[i][0] || w[i]->cols != want[i][1]) return QM_ERR_SHAPE;
     s->layer[layer] = QmLayer{w[0], w[1], w[2], w[3]};
@@ -191,16 +284,20 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     for (int L = 0; L < s->layers; L++) {
         const QmLayer &ly = s->layer[L];
         const CUdeviceptr qkv = s->qkv_out + (size_t)L * m * qkv_ld * 4;
-        add_matvec(ly.qkv, L == 0 ? s->h0 : s->dn_out, 0, s->hidden, qkv, qkv_ld, QM_XOP_RMSNORM, L == 0);
-        add_matvec(ly.o, qkv, 0, qkv_ld, s->o_out, s->hidden, QM_XOP_RMSNORM, false);
-        add_matvec(ly.gu, s->o_out, 0, s->hidden, s->gu_out, 2 * s->ffn, QM_XOP_RMSNORM, false);
-        add_matvec(ly.dn, s->gu_out, s->gu_out + (size_t)s->ffn * 4, 2 * s->ffn, s->dn_out, s->hidden,
-                   QM_XOP_ADD_RMSNORM, false);
+        // tensor-parallel: y points at this rank's rows of the full-width output
+        const size_t R = (size_t)s->tp_rank * 4;
+        add_matvec(ly.qkv, L == 0 ? s->h0 : s->dn_out, 0, s->hidden, qkv + R * ly.qkv->rows, qkv_ld, QM_XOP_RMSNORM,
+                   L == 0);
+        add_matvec(ly.o, qkv, 0, qkv_ld, s->o_out + R * ly.o->rows, s->hidden, QM_XOP_RMSNORM, false);
+        add_matvec(ly.gu, s->o_out, 0, s->hidden, s->gu_out + R * ly.gu->rows, 2 * s->ffn, QM_XOP_RMSNORM, false);
+        add_matvec(ly.dn, s->gu_out, s->gu_out + (size_t)s->ffn * 4, 2 * s->ffn, s->dn_out + R * ly.dn->rows,
+                   s->hidden, QM_XOP_ADD_RMSNORM, false);
     }
     for (const QmOp &op : ops)
         if ((int64_t)op.tiles * op.units >= (1ll << 31)) return QM_ERR_SHAPE;
     // every unsliced op but the first writes a buffer that the op before it does not touch
-    for (size_t k = 1; k < ops.size(); k++)
+    // (tensor-parallel ops keep whole tiles per CTA: their outputs are plain stores to every GPU)
+    for (size_t k = 1; k < ops.size() && s->tp_world == 1; k++)
         if (ops[k].units == ops[k].units_total) qm_balance_op(c, &ops[k]);
 
     // Activation images: the last op of a matrix quantizes the next matrix's x as its outputs
@@ -222,7 +319,7 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     // against 2.33 ms); beyond that the image wins (batch 4: 2.46 ms; batch 8: 3.52 ms against 5.93 ms).
     bool uses_img = false;
     const int min_m = qm_env_int("QM_IMAGE_MIN_M", 3), min_units = qm_env_int("QM_IMAGE_MIN_UNITS", 1 << 30);
-    if (r == CUDA_SUCCESS && !qm_env_int("QM_NO_IMAGE", 0)) {
+    if (r == CUDA_SUCCESS && !qm_env_int("QM_NO_IMAGE", 0) && s->tp_world == 1) {
         for (size_t k = 0; k + 1 < ngroups; k++) {
             QmOp &prod = ops[group_last[k]];
             const QmOp &cons = ops[group_first[k + 1]];
@@ -276,6 +373,17 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
     a.debug_slot = qm_env_int("QM_DEBUG_OP", 0);
     DRV(c->drv->cuMemsetD32Async(s->sync_dev[m], 0, s->sync_bytes[m] / 4, c->stream));
     // cooperative: the grid barrier between dependent matvecs needs every CTA resident
+    if (s->tp_world > 1) {
+        if (!s->peers_open) return QM_ERR_STATE;
+        a.tp_world = s->tp_world;
+        a.tp_rank = s->tp_rank;
+        a.tp_epoch0 = s->tp_epoch;
+        s->tp_epoch += (unsigned int)a.nops;   // nops - 1 barriers between the ops and one at the end
+        a.tp_flags = (unsigned int *)(uintptr_t)(s->arena + s->flags_off);
+        for (int q = 0; q < s->tp_world; q++) a.peer_delta[q] = (int64_t)s->peer_base[q] - (int64_t)s->arena;
+        return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1_TP : QM_K_FUSED_Q4K_NT2_TP, (unsigned)qm_fused_grid(c),
+                            (unsigned)p.consumers * 32, (unsigned)p.smem, &a, false, true);
+    }
     const int kern = s->fused_img[m] ? (p.nt == 1 ? QM_K_FUSED_Q4K_NT1_IMG : QM_K_FUSED_Q4K_NT2_IMG)
                                      : (p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2);
     return qm_launch_ex(c, kern, (unsigned)qm_fused_grid(c),
@@ -305,6 +413,10 @@ static int32_t enqueue_layers(qm_ctx *c, qm_stack *s, int m, int upto_layers) {
 }
 
 static int32_t step_device(qm_ctx *c, qm_stack *s, int m) {
+    if (s->tp_world > 1) {   // tensor-parallel steps exist as the one fused launch only
+        int32_t rc = s->ops_dev[m] ? QM_OK : build_fused(c, s, m);
+        return rc ? rc : launch_fused(c, s, m);
+    }
     if (s->use_graph && s->use_fused) {
         int32_t rc = s->ops_dev[m] ? QM_OK : build_fused(c, s, m);
         if (rc == QM_OK) return launch_fused(c, s, m);
@@ -370,11 +482,15 @@ extern "C" int32_t qm_stack_step_host(qm_ctx *c, qm_stack *s, const float *x_hos
     DRV(d->cuMemcpyDtoHAsync_v2(h_host, s->dn_out, (size_t)m * s->hidden * 4, c->stream));
     if (kv_host && s->kv) {
         const int64_t qkv_ld = s->hidden + 2 * s->kv;
-        for (int L = 0; L < s->layers; L++)
+        // tensor-parallel: only the k|v rows of this rank's slice (a peer's next step may already
+        // be overwriting the others); the rest of kv_host is left untouched
+        const int64_t S = qkv_ld / s->tp_world;
+        const int64_t lo = std::max<int64_t>(s->hidden, s->tp_rank * S), hi = std::min<int64_t>(qkv_ld, (s->tp_rank + 1) * S);
+        for (int L = 0; L < s->layers && lo < hi; L++)
             for (int j = 0; j < m; j++)
-                DRV(d->cuMemcpyDtoHAsync_v2(kv_host + ((size_t)L * m + j) * 2 * s->kv,
-                                            s->qkv_out + (((size_t)L * m + j) * qkv_ld + s->hidden) * 4,
-                                            (size_t)2 * s->kv * 4, c->stream));
+                DRV(d->cuMemcpyDtoHAsync_v2(kv_host + ((size_t)L * m + j) * 2 * s->kv + (lo - s->hidden),
+                                            s->qkv_out + (((size_t)L * m + j) * qkv_ld + lo) * 4,
+                                            (size_t)(hi - lo) * 4, c->stream));
     }
     DRV(d->cuStreamSynchronize(c->stream));
     return QM_OK;

@@ -86,6 +86,35 @@ class SingleGpuDecode:
         self.stack.step_host(x, h_out=h, kv_out=kv)
 
 
+class PeerTensorParallelDecode:
+    """Row-sharded decode step as ONE persistent launch per GPU (qm_stack_create_tp): rank r
+    holds rows [r*N/g, (r+1)*N/g) of every stacked matrix and stores its slice of every
+    matvec straight into all peers' activation buffers over NVLink; the barrier between
+    dependent matvecs spans the GPUs. torch.distributed only carries the 64-byte IPC handles
+    at set-up."""
+
+    def __init__(self, ctx, layers, hidden, kv, ffn, fmt, seed, rank, world, m_max=8):
+        import torch.distributed as dist
+        self.ctx, self.hidden, self.rank, self.world = ctx, hidden, rank, world
+        self.stack = _capi.Stack(ctx, layers, hidden, kv, ffn, m_max, rank, world)
+        for L in range(layers):
+            ws = []
+            for rows, cols, parts in stacked(layer_tensors(fmt, hidden, kv, ffn, seed, L)):
+                lo, hi = shard_range(rows, rank, world)
+                ws.append(upload_rows(ctx, fmt, rows, cols, parts, lo, hi))
+            self.stack.set_layer(L, *ws)
+        handles = [None] * world
+        dist.all_gather_object(handles, self.stack.ipc_handle())
+        self.stack.set_peers(handles)
+        dist.barrier()   # every rank has mapped every arena before the first step
+
+    def step_device(self, x_dev, m, h_dev):
+        self.stack.step(x_dev.data_ptr(), m, self.hidden, h_dev.data_ptr(), self.hidden)
+
+    def step_host(self, x, h, kv):
+        self.stack.step_host(x, h_out=h, kv_out=kv)
+
+
 class TensorParallelDecode:
     """Row-sharded decode step: rank r holds rows [r*N/g, (r+1)*N/g) of every stacked matrix,
     computes its slice of each matvec and all-gathers the slices (NCCL) so that every rank

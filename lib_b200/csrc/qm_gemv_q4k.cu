@@ -419,7 +419,6 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                     atomicOr(a.status, QM_STATUS_TIMEOUT);
                     dead = true;
                 }
-                __nanosleep(64);
             }
             if (TP) {
                 for (int p = 0; p < a.tp_world; p++) {
@@ -600,8 +599,10 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 if (sliced || pre) {
                     sc = s_scale[j];
                 } else {
-                    float sq = 0.f;
-                    for (int w = 0; w < C; w++) sq += ssq[j * 16 + w];   // fixed order
+                    // the warps' parts, added as a fixed tree over sixteen lanes
+                    float sq = (lane & 15) < C ? ssq[j * 16 + (lane & 15)] : 0.f;
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
                     sc = rsqrtf(sq / (float)op.cols + op.eps);
                 }
 #pragma unroll

@@ -80,12 +80,16 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 
 }  // namespace
 
-extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16(const __grid_constant__ QmGemmArgs a) {
+// NSUB = 128-row sub-tiles of weight rows per CTA: 1 (128 x BN tile, BN up to 512) or 2
+// (256 x BN tile, BN up to 256: half the activation traffic per flop and room for a third stage).
+template <int NSUB>
+__device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int BN = a.bn, kStages = a.stages;
     const int b_tile = BN * kBK * 2;
-    const int stage_bytes = kATile + b_tile;
+    constexpr int a_tile = NSUB * kATile;
+    const int stage_bytes = a_tile + b_tile;
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)kStages * stage_bytes);
     const uint32_t full_a = smem_u32(bars), full_b = full_a + 8 * kMaxStages, empty = full_b + 8 * kMaxStages;
@@ -93,7 +97,7 @@ extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16(const __gr
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kMaxStages + 1);
     const uint32_t smem_base = smem_u32(smem);
 
-    const int n0 = blockIdx.x * kBM, m0 = blockIdx.y * BN;
+    const int n0 = blockIdx.x * kBM * NSUB, m0 = blockIdx.y * BN;
     // 64-column chunks along K; with split K (gridDim.z > 1) this CTA takes a contiguous share
     // and adds its partial tile to C, which the host zeroed
     const int nk_all = a.units * 4;
@@ -109,9 +113,9 @@ extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16(const __gr
         mbar_init(tmem_full, 1);
         fence_barrier_init();
     }
-    if (warp == 1) {   // TMEM accumulator: BN fp32 columns x 128 lanes
+    if (warp == 1) {   // TMEM accumulators: NSUB x BN fp32 columns x 128 lanes
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)BN)
+                     "r"((uint32_t)(NSUB * BN))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -129,7 +133,7 @@ extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16(const __gr
                 if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); break; }
                 mbar_expect_tx(full_b + 8 * s, (uint32_t)b_tile);
                 for (int nb = 0; nb < BN; nb += 256)   // a TMA box has at most 256 rows
-                    tma_load_2d(smem_base + s * stage_bytes + kATile + nb * 128, &a.tmap_act, (kc_lo + kc) * kBK, m0 + nb,
+                    tma_load_2d(smem_base + s * stage_bytes + a_tile + nb * 128, &a.tmap_act, (kc_lo + kc) * kBK, m0 + nb,
                                 full_b + 8 * s);
             }
         }
@@ -147,89 +151,108 @@ extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16(const __gr
                 if (!ok) { atomicOr(a.status, QM_STATUS_TIMEOUT); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t adesc = smem_desc(smem_base + s * stage_bytes);
-                const uint64_t bdesc = smem_desc(smem_base + s * stage_bytes + kATile);
-                for (int nb = 0; nb < BN; nb += 256)
+                const uint64_t bdesc = smem_desc(smem_base + s * stage_bytes + a_tile);
 #pragma unroll
-                    for (int k16 = 0; k16 < kBK / 16; k16++)   // 16 bf16 = 32 bytes = 2 descriptor units
-                        umma_f16(tmem_base + (uint32_t)nb, adesc + 2 * k16, bdesc + (nb * 128 >> 4) + 2 * k16, idesc,
-                                 (kc | k16) != 0);
+                for (int sub = 0; sub < NSUB; sub++)
+                    for (int nb = 0; nb < BN; nb += 256)
+#pragma unroll
+                        for (int k16 = 0; k16 < kBK / 16; k16++)   // 16 bf16 = 32 bytes = 2 descriptor units
+                            umma_f16(tmem_base + (uint32_t)(sub * BN + nb), adesc + sub * (kATile >> 4) + 2 * k16,
+                                     bdesc + (nb * 128 >> 4) + 2 * k16, idesc, (kc | k16) != 0);
                 umma_commit(empty + 8 * s);   // frees the stage when these MMAs have read it
             }
             umma_commit(tmem_full);           // accumulator complete (or abandoned)
         }
     } else {
         // ---- dequantize weight rows into the A tile, then the epilogue --------------------------
-        const int r = (tid - 64) & 127;      // row of the tile
+        const int r = (tid - 64) & 127;      // row of a 128-row sub-tile
         const int hsel = (tid - 64) >> 7;    // 0: low nibbles (columns 0..31), 1: high nibbles (32..63)
-        const int64_t tile16 = min((n0 + r) >> 4, a.tiles16 - 1);
         const int rr = (n0 + r) & 15;
-        const uint8_t *row_items = a.wq + tile16 * a.units * QM_Q4K_ITEM_BYTES;
+        const uint8_t *row_items[NSUB];
+#pragma unroll
+        for (int sub = 0; sub < NSUB; sub++) {
+            const int64_t tile16 = min((n0 + sub * kBM + r) >> 4, a.tiles16 - 1);
+            row_items[sub] = a.wq + tile16 * a.units * QM_Q4K_ITEM_BYTES;
+        }
         bool ok = true;
-        // the quant bytes of the next three chunks and the header of the next unit are in flight
-        // while a chunk is converted
-        constexpr int kAhead = 3;
-        uint4 qa[kAhead + 1], qb[kAhead + 1], hdr_next = make_uint4(0, 0, 0, 0), hdr = hdr_next;
-        auto load_q = [&](int kcl, uint4 &x0, uint4 &x1) {
+        // the quant bytes of the next chunks and the headers of the next unit are in flight while a
+        // chunk is converted
+        constexpr int kAhead = NSUB == 1 ? 3 : 2;
+        uint4 qa[NSUB][kAhead + 1], qb[NSUB][kAhead + 1], hdr_next[NSUB], hdr[NSUB];
+        auto load_q = [&](int sub, int kcl, uint4 &x0, uint4 &x1) {
             const int kc = kc_lo + kcl;
-            const uint8_t *item = row_items + (size_t)(kc >> 2) * QM_Q4K_ITEM_BYTES + 256 + 512 * (kc & 3) + 32 * rr;
+            const uint8_t *item = row_items[sub] + (size_t)(kc >> 2) * QM_Q4K_ITEM_BYTES + 256 + 512 * (kc & 3) + 32 * rr;
             x0 = __ldg(reinterpret_cast<const uint4 *>(item));
             x1 = __ldg(reinterpret_cast<const uint4 *>(item + 16));
         };
-        hdr_next = __ldg(reinterpret_cast<const uint4 *>(row_items + (size_t)(kc_lo >> 2) * QM_Q4K_ITEM_BYTES + 16 * rr));
 #pragma unroll
-        for (int i = 0; i < kAhead; i++)
-            if (i < nk) load_q(i, qa[i], qb[i]);
+        for (int sub = 0; sub < NSUB; sub++) {
+            hdr[sub] = make_uint4(0, 0, 0, 0);
+            hdr_next[sub] = __ldg(reinterpret_cast<const uint4 *>(row_items[sub] + (size_t)(kc_lo >> 2) * QM_Q4K_ITEM_BYTES + 16 * rr));
+#pragma unroll
+            for (int i = 0; i < kAhead; i++)
+                if (i < nk) load_q(sub, i, qa[sub][i], qb[sub][i]);
+        }
         for (int kc = 0; kc < nk; kc++) {
             const int s = kc % kStages;
             const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
             const int u = (kc_lo + kc) >> 2, p = (kc_lo + kc) & 3;
-            if (p == 0 || kc == 0) {
-                hdr = hdr_next;
-                if (u + 1 < a.units)
-                    hdr_next = __ldg(reinterpret_cast<const uint4 *>(row_items + (size_t)(u + 1) * QM_Q4K_ITEM_BYTES + 16 * rr));
-            }
-            if (kc + kAhead < nk) load_q(kc + kAhead, qa[kAhead], qb[kAhead]);
-            const uint4 q0 = qa[0], q1 = qb[0];
+            uint32_t o[NSUB][16];   // bf16x2 pairs: 32 columns of the chunk, per sub-tile row
 #pragma unroll
-            for (int i = 0; i < kAhead; i++) { qa[i] = qa[i + 1]; qb[i] = qb[i + 1]; }
-            // scale and minimum of sub-block 2p (low nibbles) or 2p+1 (high nibbles)
-            const int j = 2 * p + hsel;
-            int sc, mn;
-            if (j < 4) {
-                sc = (hdr.y >> (8 * j)) & 63;
-                mn = (hdr.z >> (8 * j)) & 63;
-            } else {
-                const int jj = j - 4;
-                sc = ((hdr.w >> (8 * jj)) & 0xF) | (((hdr.y >> (8 * jj + 6)) & 3) << 4);
-                mn = ((hdr.w >> (8 * jj + 4)) & 0xF) | (((hdr.z >> (8 * jj + 6)) & 3) << 4);
-            }
-            const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
-            const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-            const uint32_t av = bf2(d * (float)sc), bv = bf2(-dmin * (float)mn);
-            const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-            const int sh = 4 * hsel;
-            uint32_t o[16];   // bf16x2 pairs: 32 columns of the chunk
+            for (int sub = 0; sub < NSUB; sub++) {
+                if (p == 0 || kc == 0) {
+                    hdr[sub] = hdr_next[sub];
+                    if (u + 1 < a.units)
+                        hdr_next[sub] = __ldg(reinterpret_cast<const uint4 *>(row_items[sub] + (size_t)(u + 1) * QM_Q4K_ITEM_BYTES + 16 * rr));
+                }
+                if (kc + kAhead < nk) load_q(sub, kc + kAhead, qa[sub][kAhead], qb[sub][kAhead]);
+                const uint4 q0 = qa[sub][0], q1 = qb[sub][0];
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const uint32_t p01 = prmt(w[i], 0u, 0x4140u) >> sh, p23 = prmt(w[i], 0u, 0x4342u) >> sh;   // bytes in 16-bit lanes
-                o[2 * i] = bfma2(bsub2((p01 & 0x000F000Fu) | 0x43004300u, 0x43004300u), av, bv);
-                o[2 * i + 1] = bfma2(bsub2((p23 & 0x000F000Fu) | 0x43004300u, 0x43004300u), av, bv);
+                for (int i = 0; i < kAhead; i++) { qa[sub][i] = qa[sub][i + 1]; qb[sub][i] = qb[sub][i + 1]; }
+                // scale and minimum of sub-block 2p (low nibbles) or 2p+1 (high nibbles)
+                const uint4 hd = hdr[sub];
+                const int j = 2 * p + hsel;
+                int sc, mn;
+                if (j < 4) {
+                    sc = (hd.y >> (8 * j)) & 63;
+                    mn = (hd.z >> (8 * j)) & 63;
+                } else {
+                    const int jj = j - 4;
+                    sc = ((hd.w >> (8 * jj)) & 0xF) | (((hd.y >> (8 * jj + 6)) & 3) << 4);
+                    mn = ((hd.w >> (8 * jj + 4)) & 0xF) | (((hd.z >> (8 * jj + 6)) & 3) << 4);
+                }
+                const float d = __half2float(__ushort_as_half((unsigned short)(hd.x & 0xFFFFu)));
+                const float dmin = __half2float(__ushort_as_half((unsigned short)(hd.x >> 16)));
+                const uint32_t av = bf2(d * (float)sc), bv = bf2(-dmin * (float)mn);
+                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                const int sh = 4 * hsel;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint32_t p01 = prmt(w[i], 0u, 0x4140u) >> sh, p23 = prmt(w[i], 0u, 0x4342u) >> sh;   // bytes in 16-bit lanes
+                    o[sub][2 * i] = bfma2(bsub2((p01 & 0x000F000Fu) | 0x43004300u, 0x43004300u), av, bv);
+                    o[sub][2 * i + 1] = bfma2(bsub2((p23 & 0x000F000Fu) | 0x43004300u, 0x43004300u), av, bv);
+                }
             }
             if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); ok = false; break; }
-            uint8_t *arow = smem + (size_t)s * stage_bytes + r * 128;
 #pragma unroll
-            for (int c = 0; c < 4; c++)   // 16-byte pieces, XOR-swizzled by the row inside its 8-row group
-                *reinterpret_cast<uint4 *>(arow + (((c + 4 * hsel) ^ (r & 7)) << 4)) =
-                    make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+            for (int sub = 0; sub < NSUB; sub++) {
+                uint8_t *arow = smem + (size_t)s * stage_bytes + sub * kATile + r * 128;
+#pragma unroll
+                for (int c = 0; c < 4; c++)   // 16-byte pieces, XOR-swizzled by the row inside its 8-row group
+                    *reinterpret_cast<uint4 *>(arow + (((c + 4 * hsel) ^ (r & 7)) << 4)) =
+                        make_uint4(o[sub][4 * c], o[sub][4 * c + 1], o[sub][4 * c + 2], o[sub][4 * c + 3]);
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
             mbar_arrive(full_a + 8 * s);
         }
         // ---- epilogue: accumulator row r holds C[m0..m0+BN)[n0+r] -------------------------------------
         if (ok && mbar_wait_bounded(tmem_full, 0u)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-            const int n = n0 + (warp & 3) * 32 + lane;   // TMEM lane quarter of this warp
             const int cbeg = hsel * (BN / 2), cend = cbeg + BN / 2;   // the two warps of a quarter split the columns
+#pragma unroll 1
+            for (int sub = 0; sub < NSUB; sub++) {
+            const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(sub * BN);
+            const int n = n0 + sub * kBM + (warp & 3) * 32 + lane;   // TMEM lane quarter of this warp
             for (int c0 = cbeg; c0 < cend; c0 += 32) {
                 uint32_t v[32];
                 asm volatile(
@@ -254,6 +277,7 @@ extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16(const __gr
                     }
                 }
             }
+            }
         } else if (ok) {
             atomicOr(a.status, QM_STATUS_TIMEOUT);
         }
@@ -262,6 +286,13 @@ extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16(const __gr
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(NSUB * BN)) : "memory");
     }
+}
+
+extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16(const __grid_constant__ QmGemmArgs a) {
+    gemm_body<1>(a);
+}
+extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16_r256(const __grid_constant__ QmGemmArgs a) {
+    gemm_body<2>(a);
 }

@@ -81,7 +81,7 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_Q4K, "qm_fused_q4k_nt1"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2"},
     {QM_MOD_Q4K, "qm_fused_q4k_nt1_img"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2_img"},
     {QM_MOD_Q4K, "qm_fused_q4k_nt1_tp"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2_tp"},
-    {QM_MOD_GEMM, "qm_gemm_q4k_bf16"},
+    {QM_MOD_GEMM, "qm_gemm_q4k_bf16"}, {QM_MOD_GEMM, "qm_gemm_q4k_bf16_r256"},
     {QM_MOD_MOE, "qm_moe_route"},      {QM_MOD_MOE, "qm_moe_lists"},      {QM_MOD_MOE, "qm_moe_gather"},
     {QM_MOD_MOE, "qm_moe_swiglu"},     {QM_MOD_MOE, "qm_moe_combine"},
 };
@@ -169,6 +169,8 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
         }
         if (!err) {
             r = d->cuFuncSetAttribute(c->fn[QM_K_GEMM_Q4K], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
+            if (r == CUDA_SUCCESS)
+                r = d->cuFuncSetAttribute(c->fn[QM_K_GEMM_Q4K_R256], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
         for (int k = QM_K_GEMV_Q40_M4; k <= QM_K_GEMV_Q80_M8 && !err; k++) {
@@ -821,8 +823,14 @@ extern "C" int32_t qm_matmul_bf16(qm_ctx *c, qm_weight h, uint64_t a_dev, int32_
     DRV(g.rc);
     QmGemmArgs a;
     memset(&a, 0, sizeof a);
-    const int bn = m <= 64 ? 64 : m <= 128 ? 128 : m <= 256 ? 256 : 512;
-    const int stages = bn == 512 ? 2 : 4;
+    // Tile shapes: 128 weight rows x 64..512 tokens per CTA (four stages, two at 512 tokens). A
+    // 256 x 256 variant (two accumulators, three stages, half the activation bytes per flop) is
+    // kept behind QM_GEMM_R256=1: measured equal within noise (76.6 us against 74.0 us at
+    // 4096 x 4096 x 2048), so neither the stage count nor the activation traffic is the limit.
+    const bool r256 = env_int("QM_GEMM_R256", 0) != 0 && w->rows >= 256;
+    const int nsub = r256 ? 2 : 1;
+    const int bn = r256 ? 256 : m <= 64 ? 64 : m <= 128 ? 128 : m <= 256 ? 256 : 512;
+    const int stages = r256 ? 3 : bn == 512 ? 2 : 4;
     const cuuint64_t dims[2] = {(cuuint64_t)w->cols, (cuuint64_t)m};
     const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
     const cuuint32_t box[2] = {64, (cuuint32_t)std::min(bn, 256)};
@@ -840,11 +848,11 @@ extern "C" int32_t qm_matmul_bf16(qm_ctx *c, qm_weight h, uint64_t a_dev, int32_
     a.tiles16 = (int32_t)((w->rows + 15) / 16);
     a.bn = bn;
     a.stages = stages;
-    const unsigned smem = 1024 + stages * (128 * 64 * 2 + bn * 64 * 2) + 256;
+    const unsigned smem = 1024 + stages * (nsub * 128 * 64 * 2 + bn * 64 * 2) + 256;
     void *params[1] = {&a};
     CUlaunchConfig cfg;
     memset(&cfg, 0, sizeof cfg);
-    cfg.gridDimX = (unsigned)((w->rows + 127) / 128);
+    cfg.gridDimX = (unsigned)((w->rows + 128 * nsub - 1) / (128 * nsub));
     cfg.gridDimY = (unsigned)((m + bn - 1) / bn);
     // few tokens: split K over CTAs until the SMs are covered; partial tiles are added into a
     // zeroed C (float adds in arrival order: results may differ in the last bits between runs)
@@ -858,7 +866,7 @@ extern "C" int32_t qm_matmul_bf16(qm_ctx *c, qm_weight h, uint64_t a_dev, int32_
     cfg.blockDimY = cfg.blockDimZ = 1;
     cfg.sharedMemBytes = smem;
     cfg.hStream = c->stream;
-    DRV(c->drv->cuLaunchKernelEx(&cfg, c->fn[QM_K_GEMM_Q4K], params, nullptr));
+    DRV(c->drv->cuLaunchKernelEx(&cfg, c->fn[r256 ? QM_K_GEMM_Q4K_R256 : QM_K_GEMM_Q4K], params, nullptr));
     c->launches++;
     return QM_OK;
 }

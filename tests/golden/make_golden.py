@@ -1,7 +1,7 @@
 """Generates the committed fixtures of tests/golden/ from the reference checkout.
 
 Run in a container that has the reference mounted:
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py [path of the reference checkout]
 Writes
   ds4_superblocks.json  the two pseudorandom super-blocks and the 2x256 expected
                         values of lm/quant/testdata/ds4_golden.txt, after checking

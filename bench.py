@@ -186,10 +186,23 @@ def main():
         runner = decode.SingleGpuDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED)
     else:
         from lib_b200 import decode
-        if os.environ.get("QM_TP_MODE", "peer") == "nccl":   # the plain NCCL all-gather arm, for comparison
+        runner = None
+        if os.environ.get("QM_TP_MODE", "peer") != "nccl":
+            # one persistent launch per GPU with peer-memory stores; if any rank cannot map its
+            # peers' memory, all ranks agree to fall back to the NCCL all-gather arm
+            try:
+                runner = decode.PeerTensorParallelDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED, rank, world,
+                                                         barrier=False)
+            except Exception as exc:   # noqa: BLE001
+                print("rank %d: peer tensor parallelism unavailable (%s)" % (rank, exc), file=sys.stderr, flush=True)
+            flag = torch.tensor([1 if runner is not None else 0], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:
+                runner = None
+        tp_mode = "peer stores + cross-GPU barrier in one launch per GPU"
+        if runner is None:   # the plain NCCL all-gather arm
+            tp_mode = "matvec launches + NCCL all-gather (CUDA graph)"
             runner = decode.TensorParallelDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED, rank, world, stream)
-        else:
-            runner = decode.PeerTensorParallelDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED, rank, world)
 
     x_host = torch.from_numpy(synth.activations(m, HIDDEN, SEED + 999)).pin_memory()
     x_dev = x_host.to("cuda", non_blocking=False)
@@ -252,7 +265,7 @@ def main():
         "metric": "decode_tokens_per_s", "value": m / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(m, world, "B200"),
+        "config": dict(workload_config(m, world, "B200"), **({"exchange": tp_mode} if world > 1 else {})),
         "e2e": {"value": m / (ms_e2e * 1e-3), "unit": "tok/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(x_host.numel() * 4),
                 "d2h_bytes_per_step": int(h_host.numel() * 4 + kv_host.numel() * 4)},
@@ -261,7 +274,7 @@ def main():
         "roofline": {
             "bound": "hbm", "kernel": "qm_fused_q4k_nt1" if m <= 4 else "qm_fused_q4k_nt2",
             "achieved": achieved * world if world > 1 else achieved, "peak": pk["hbm_gbs"] * world, "unit": "GB/s",
-            "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind + " (copy bandwidth, MEASURED_PEAKS.json)",
+            "frac": achieved / pk["hbm_gbs"], "frac_of_8TBs_datasheet": achieved / 8000.0, "peak_kind": pk_kind + " (copy bandwidth, MEASURED_PEAKS.json)",
             "per_launch": {"launches_per_step": max(1, round(launches / args.steps)), "matvecs_per_step": n_launch,
                            "bytes_per_step": step_bytes / world, "us_per_step": ms * 1e3},
             "traffic": None,

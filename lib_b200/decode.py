@@ -93,7 +93,9 @@ class PeerTensorParallelDecode:
     dependent matvecs spans the GPUs. torch.distributed only carries the 64-byte IPC handles
     at set-up."""
 
-    def __init__(self, ctx, layers, hidden, kv, ffn, fmt, seed, rank, world, m_max=8):
+    def __init__(self, ctx, layers, hidden, kv, ffn, fmt, seed, rank, world, m_max=8, barrier=True):
+        """barrier=False: the caller runs a collective of its own on all ranks before the first
+        step (every rank must have mapped every arena before any rank stores into one)."""
         import torch.distributed as dist
         self.ctx, self.hidden, self.rank, self.world = ctx, hidden, rank, world
         self.stack = _capi.Stack(ctx, layers, hidden, kv, ffn, m_max, rank, world)
@@ -106,7 +108,8 @@ class PeerTensorParallelDecode:
         handles = [None] * world
         dist.all_gather_object(handles, self.stack.ipc_handle())
         self.stack.set_peers(handles)
-        dist.barrier()   # every rank has mapped every arena before the first step
+        if barrier:
+            dist.barrier()   # every rank has mapped every arena before the first step
 
     def step_device(self, x_dev, m, h_dev):
         self.stack.step(x_dev.data_ptr(), m, self.hidden, h_dev.data_ptr(), self.hidden)

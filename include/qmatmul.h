@@ -159,7 +159,8 @@ QM_API int32_t qm_moe_route(qm_ctx *ctx, uint64_t logits_dev, int32_t tokens, in
  * expert on the device, each expert runs the tcgen05 matmul over its list, and the combine
  * adds a token's expert outputs in slot order. New API of this path: the reference's lm/moe
  * routes and caches experts but has no matmul; its device gather is nvidia/x/cudamoe/moe.go:72-96.
- * Reads the list lengths back to the host (one stream synchronization inside the call). */
+ * Asynchronous: the lists stay on the device and all experts run in two grouped launches
+ * (gate|up with the SwiGLU in its epilogue, then down); ffn must be a multiple of 128. */
 QM_API int32_t qm_moe_grouped(qm_ctx *ctx, const qm_weight *gate_up, const qm_weight *down, int32_t experts,
                               uint64_t x_bf16_dev, int32_t tokens, int64_t ldx, uint64_t ids_dev,
                               uint64_t weights_dev, int32_t topk, uint64_t out_dev, int64_t ldo);
@@ -172,7 +173,8 @@ QM_API int32_t qm_moe_grouped(qm_ctx *ctx, const qm_weight *gate_up, const qm_we
  *   that order, writes pos[pair] = row of the pair in the grouping, and returns the list
  *   lengths in counts_host[experts] (the call synchronizes the stream once to read them).
  * qm_moe_experts: y[p] = down_e( silu(gate_e r_p) * (up_e r_p) ) over rows grouped by expert
- *   (counts_host[e] consecutive rows per expert e, in order); y float32 [rows][hidden].
+ *   (counts_host[e] consecutive rows per expert e, in order); y float32 [rows][hidden]. Two
+ *   grouped launches for all experts; asynchronous.
  * qm_moe_combine: out[t] = sum_s weights[t][s] * y[pos[t*topk+s]], slots in order. */
 QM_API int32_t qm_moe_dispatch(qm_ctx *ctx, uint64_t ids_dev, int32_t tokens, int32_t topk, int32_t experts,
                                uint64_t x_bf16_dev, int64_t ldx, int32_t hidden, uint64_t rows_dev,

@@ -5,17 +5,18 @@
 // (nvidia/x/cudamoe/prefill.go:97-121), which is neither quantized nor tcgen05.
 //
 // One CTA computes a 128 (weight rows) x BN (tokens, 64..512) tile of C^T:
-//   * warps 2..9 (256 threads, two per weight row: low nibbles / high nibbles) read the row's
-//     32 quant bytes of a 64-column K chunk from the tiled weight store, turn the nibbles into exact
-//     bf16 integers with the magic-number trick (0x4300|q = 128+q), apply the sub-block
-//     scale and minimum with one bf16x2 FMA per pair, and write the row into shared memory
-//     in the canonical K-major 128-byte-swizzled layout of tcgen05 (A operand);
+//   * warps 2..17 form four groups of 128 threads; group g handles the K chunks g, g+4, ...: one
+//     thread per weight row reads the row's 32 quant bytes of a 64-column K chunk from the tiled
+//     weight store, turns the nibbles into exact bf16 integers with the magic-number trick (byte
+//     0x43 beside the code = 128+q), applies the sub-block scale and minimum with one bf16x2 FMA
+//     per pair, and writes the row into shared memory in the canonical K-major 128-byte-swizzled
+//     layout of tcgen05 (A operand); four chunks in flight hide the latency of that chain;
 //   * warp 0 streams the matching 64 x BN activation chunk with a 2-D TMA tile copy
 //     (SWIZZLE_128B, no multicast) that completes on an mbarrier (B operand);
 //   * one elected thread of warp 1 issues four tcgen05.mma.kind::f16 (K = 16 each) per chunk
 //     and per 256 tokens into a TMEM accumulator of BN fp32 columns (BN = 512 uses the whole
 //     tensor memory: the dequantized tile then feeds two MMAs), tcgen05.commit frees the stage;
-//   * after the last chunk warps 2..9 read the accumulator back with tcgen05.ld and store C.
+//   * after the last chunk warps 2..17 read the accumulator back with tcgen05.ld and store C.
 // A ring of 2..4 shared-memory stages decouples the three roles. Every mbarrier wait is
 // bounded (qm_pipe.cuh); on expiry the status word gets QM_STATUS_TIMEOUT, the roles leave
 // their loops, TMEM is freed and the kernel returns.
@@ -97,16 +98,28 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kMaxStages + 1);
     const uint32_t smem_base = smem_u32(smem);
 
-    const int n0 = blockIdx.x * kBM * NSUB, m0 = blockIdx.y * BN;
-    // 64-column chunks along K; with split K (gridDim.z > 1) this CTA takes a contiguous share
+    const bool fuse_swiglu = NSUB == 2 && a.swiglu != 0;
+    const int n0 = blockIdx.x * kBM * (fuse_swiglu ? 1 : NSUB), m0 = blockIdx.y * BN;
+    // grouped launch: this CTA's expert, its rows of the gathered activations and its weights
+    int row_off = 0, m_cnt = a.m;
+    const uint8_t *wq = a.wq;
+    if (a.grouped) {
+        const int e = blockIdx.z;
+        row_off = a.offsets[e];
+        m_cnt = a.offsets[e + 1] - row_off;
+        if (m0 >= m_cnt) return;   // nothing routed here (uniform over the CTA, before any barrier)
+        wq = a.wq_list[e];
+    }
+    // 64-column chunks along K; with split K (splitk > 1) this CTA takes a contiguous share
     // and adds its partial tile to C, which the host zeroed
     const int nk_all = a.units * 4;
-    const int kc_lo = (int)((int64_t)nk_all * blockIdx.z / gridDim.z);
-    const int nk = (int)((int64_t)nk_all * (blockIdx.z + 1) / gridDim.z) - kc_lo;
+    const int zk = a.grouped ? 0 : (int)blockIdx.z;
+    const int kc_lo = (int)((int64_t)nk_all * zk / a.splitk);
+    const int nk = (int)((int64_t)nk_all * (zk + 1) / a.splitk) - kc_lo;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) {
-            mbar_init(full_a + 8 * s, 256);
+            mbar_init(full_a + 8 * s, kStages >= 4 ? 128 : 256);
             mbar_init(full_b + 8 * s, 1);
             mbar_init(empty + 8 * s, 1);
         }
@@ -133,7 +146,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                 if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); break; }
                 mbar_expect_tx(full_b + 8 * s, (uint32_t)b_tile);
                 for (int nb = 0; nb < BN; nb += 256)   // a TMA box has at most 256 rows
-                    tma_load_2d(smem_base + s * stage_bytes + a_tile + nb * 128, &a.tmap_act, (kc_lo + kc) * kBK, m0 + nb,
+                    tma_load_2d(smem_base + s * stage_bytes + a_tile + nb * 128, &a.tmap_act, (kc_lo + kc) * kBK, row_off + m0 + nb,
                                 full_b + 8 * s);
             }
         }
@@ -165,82 +178,93 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         }
     } else {
         // ---- dequantize weight rows into the A tile, then the epilogue --------------------------
-        const int r = (tid - 64) & 127;      // row of a 128-row sub-tile
-        const int hsel = (tid - 64) >> 7;    // 0: low nibbles (columns 0..31), 1: high nibbles (32..63)
+        // Sixteen producer warps in four groups of 128 threads. Group g converts the chunks
+        // kc = g, g+4, g+8, ...: one thread per weight row turns the row's 32 quant bytes of the
+        // chunk into its 64 bf16 columns. A thread's iteration is a chain of dependent steps (wait
+        // for the stage, convert, store, fence, arrive); four chunks in flight hide that latency.
+        // A group may be at most one phase ahead of a stage's "empty" barrier (a parity wait
+        // cannot tell phases two apart), so there are no more groups than stages: four groups with
+        // four stages, two groups (two threads per row, one per nibble half) with two or three.
+        const int kGroups = kStages >= 4 ? 4 : 2;
+        const int pt = tid - 64;
+        const int r = pt & 127;              // row of a 128-row sub-tile
+        const int grp = kGroups == 4 ? pt >> 7 : pt >> 8;   // warp-uniform
+        const int my_hs = kGroups == 4 ? -1 : (pt >> 7) & 1;   // the nibble half of this thread, or both
         const int rr = (n0 + r) & 15;
         const uint8_t *row_items[NSUB];
 #pragma unroll
         for (int sub = 0; sub < NSUB; sub++) {
-            const int64_t tile16 = min((n0 + sub * kBM + r) >> 4, a.tiles16 - 1);
-            row_items[sub] = a.wq + tile16 * a.units * QM_Q4K_ITEM_BYTES;
+            const int sub_row = fuse_swiglu ? sub * a.up_offset : sub * kBM;   // up rows sit up_offset below the gate rows
+            const int64_t tile16 = min((n0 + sub_row + r) >> 4, a.tiles16 - 1);
+            row_items[sub] = wq + tile16 * a.units * QM_Q4K_ITEM_BYTES;
         }
         bool ok = true;
-        // the quant bytes of the next chunks and the headers of the next unit are in flight while a
-        // chunk is converted
-        constexpr int kAhead = NSUB == 1 ? 3 : 2;
-        uint4 qa[NSUB][kAhead + 1], qb[NSUB][kAhead + 1], hdr_next[NSUB], hdr[NSUB];
-        auto load_q = [&](int sub, int kcl, uint4 &x0, uint4 &x1) {
+        // the quant bytes and the header of the group's next chunk are in flight while one is converted
+        uint4 qa[NSUB], qb[NSUB], hd[NSUB], qa_n[NSUB], qb_n[NSUB], hd_n[NSUB];
+        auto load_chunk = [&](int sub, int kcl, uint4 &x0, uint4 &x1, uint4 &h) {
             const int kc = kc_lo + kcl;
-            const uint8_t *item = row_items[sub] + (size_t)(kc >> 2) * QM_Q4K_ITEM_BYTES + 256 + 512 * (kc & 3) + 32 * rr;
-            x0 = __ldg(reinterpret_cast<const uint4 *>(item));
-            x1 = __ldg(reinterpret_cast<const uint4 *>(item + 16));
+            const uint8_t *item = row_items[sub] + (size_t)(kc >> 2) * QM_Q4K_ITEM_BYTES;
+            h = __ldg(reinterpret_cast<const uint4 *>(item + 16 * rr));
+            x0 = __ldg(reinterpret_cast<const uint4 *>(item + 256 + 512 * (kc & 3) + 32 * rr));
+            x1 = __ldg(reinterpret_cast<const uint4 *>(item + 256 + 512 * (kc & 3) + 32 * rr + 16));
         };
 #pragma unroll
-        for (int sub = 0; sub < NSUB; sub++) {
-            hdr[sub] = make_uint4(0, 0, 0, 0);
-            hdr_next[sub] = __ldg(reinterpret_cast<const uint4 *>(row_items[sub] + (size_t)(kc_lo >> 2) * QM_Q4K_ITEM_BYTES + 16 * rr));
-#pragma unroll
-            for (int i = 0; i < kAhead; i++)
-                if (i < nk) load_q(sub, i, qa[sub][i], qb[sub][i]);
-        }
-        for (int kc = 0; kc < nk; kc++) {
+        for (int sub = 0; sub < NSUB; sub++)
+            if (grp < nk) load_chunk(sub, grp, qa_n[sub], qb_n[sub], hd_n[sub]);
+        for (int kc = grp; kc < nk; kc += kGroups) {
             const int s = kc % kStages;
             const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
-            const int u = (kc_lo + kc) >> 2, p = (kc_lo + kc) & 3;
-            uint32_t o[NSUB][16];   // bf16x2 pairs: 32 columns of the chunk, per sub-tile row
+            const int p = (kc_lo + kc) & 3;
 #pragma unroll
             for (int sub = 0; sub < NSUB; sub++) {
-                if (p == 0 || kc == 0) {
-                    hdr[sub] = hdr_next[sub];
-                    if (u + 1 < a.units)
-                        hdr_next[sub] = __ldg(reinterpret_cast<const uint4 *>(row_items[sub] + (size_t)(u + 1) * QM_Q4K_ITEM_BYTES + 16 * rr));
-                }
-                if (kc + kAhead < nk) load_q(sub, kc + kAhead, qa[sub][kAhead], qb[sub][kAhead]);
-                const uint4 q0 = qa[sub][0], q1 = qb[sub][0];
-#pragma unroll
-                for (int i = 0; i < kAhead; i++) { qa[sub][i] = qa[sub][i + 1]; qb[sub][i] = qb[sub][i + 1]; }
-                // scale and minimum of sub-block 2p (low nibbles) or 2p+1 (high nibbles)
-                const uint4 hd = hdr[sub];
-                const int j = 2 * p + hsel;
-                int sc, mn;
-                if (j < 4) {
-                    sc = (hd.y >> (8 * j)) & 63;
-                    mn = (hd.z >> (8 * j)) & 63;
-                } else {
-                    const int jj = j - 4;
-                    sc = ((hd.w >> (8 * jj)) & 0xF) | (((hd.y >> (8 * jj + 6)) & 3) << 4);
-                    mn = ((hd.w >> (8 * jj + 4)) & 0xF) | (((hd.z >> (8 * jj + 6)) & 3) << 4);
-                }
-                const float d = __half2float(__ushort_as_half((unsigned short)(hd.x & 0xFFFFu)));
-                const float dmin = __half2float(__ushort_as_half((unsigned short)(hd.x >> 16)));
-                const uint32_t av = bf2(d * (float)sc), bv = bf2(-dmin * (float)mn);
-                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-                const int sh = 4 * hsel;
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const uint32_t p01 = prmt(w[i], 0u, 0x4140u) >> sh, p23 = prmt(w[i], 0u, 0x4342u) >> sh;   // bytes in 16-bit lanes
-                    o[sub][2 * i] = bfma2(bsub2((p01 & 0x000F000Fu) | 0x43004300u, 0x43004300u), av, bv);
-                    o[sub][2 * i + 1] = bfma2(bsub2((p23 & 0x000F000Fu) | 0x43004300u, 0x43004300u), av, bv);
-                }
+                qa[sub] = qa_n[sub];
+                qb[sub] = qb_n[sub];
+                hd[sub] = hd_n[sub];
+                if (kc + kGroups < nk) load_chunk(sub, kc + kGroups, qa_n[sub], qb_n[sub], hd_n[sub]);
             }
             if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); ok = false; break; }
 #pragma unroll
             for (int sub = 0; sub < NSUB; sub++) {
+                // scales and minima of sub-blocks 2p (low nibbles, columns 0..31) and 2p+1 (high, 32..63)
+                const uint4 h4 = hd[sub];
+                uint32_t av[2], bv[2];
+                const float d = __half2float(__ushort_as_half((unsigned short)(h4.x & 0xFFFFu)));
+                const float dmin = __half2float(__ushort_as_half((unsigned short)(h4.x >> 16)));
+#pragma unroll
+                for (int hs = 0; hs < 2; hs++) {
+                    const int j = 2 * p + hs;
+                    int sc, mn;
+                    if (j < 4) {
+                        sc = (h4.y >> (8 * j)) & 63;
+                        mn = (h4.z >> (8 * j)) & 63;
+                    } else {
+                        const int jj = j - 4;
+                        sc = ((h4.w >> (8 * jj)) & 0xF) | (((h4.y >> (8 * jj + 6)) & 3) << 4);
+                        mn = ((h4.w >> (8 * jj + 4)) & 0xF) | (((h4.z >> (8 * jj + 6)) & 3) << 4);
+                    }
+                    av[hs] = bf2(d * (float)sc);
+                    bv[hs] = bf2(-dmin * (float)mn);
+                }
+                const uint32_t w[8] = {qa[sub].x, qa[sub].y, qa[sub].z, qa[sub].w, qb[sub].x, qb[sub].y, qb[sub].z, qb[sub].w};
                 uint8_t *arow = smem + (size_t)s * stage_bytes + sub * kATile + r * 128;
 #pragma unroll
-                for (int c = 0; c < 4; c++)   // 16-byte pieces, XOR-swizzled by the row inside its 8-row group
-                    *reinterpret_cast<uint4 *>(arow + (((c + 4 * hsel) ^ (r & 7)) << 4)) =
-                        make_uint4(o[sub][4 * c], o[sub][4 * c + 1], o[sub][4 * c + 2], o[sub][4 * c + 3]);
+                for (int hs = 0; hs < 2; hs++) {
+                    if (my_hs >= 0 && hs != my_hs) continue;
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {   // 16-byte pieces (eight columns), XOR-swizzled by the row inside its 8-row group
+                        uint32_t o[4];
+#pragma unroll
+                        for (int i = 0; i < 2; i++) {
+                            // four codes of this nibble half, then each next to the byte 0x43: bf16 128+q
+                            const uint32_t wv = w[2 * c + i];
+                            const uint32_t nib = hs ? (wv >> 4) & 0x0F0F0F0Fu : wv & 0x0F0F0F0Fu;
+                            const uint32_t p01 = prmt(nib, 0x43434343u, 0x4140u), p23 = prmt(nib, 0x43434343u, 0x4342u);
+                            o[2 * i] = bfma2(bsub2(p01, 0x43004300u), av[hs], bv[hs]);
+                            o[2 * i + 1] = bfma2(bsub2(p23, 0x43004300u), av[hs], bv[hs]);
+                        }
+                        *reinterpret_cast<uint4 *>(arow + (((c + 4 * hs) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
             mbar_arrive(full_a + 8 * s);
@@ -248,13 +272,9 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         // ---- epilogue: accumulator row r holds C[m0..m0+BN)[n0+r] -------------------------------------
         if (ok && mbar_wait_bounded(tmem_full, 0u)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int cbeg = hsel * (BN / 2), cend = cbeg + BN / 2;   // the two warps of a quarter split the columns
-#pragma unroll 1
-            for (int sub = 0; sub < NSUB; sub++) {
-            const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(sub * BN);
-            const int n = n0 + sub * kBM + (warp & 3) * 32 + lane;   // TMEM lane quarter of this warp
-            for (int c0 = cbeg; c0 < cend; c0 += 32) {
-                uint32_t v[32];
+            // the four warps of a TMEM lane quarter split the token columns (at least 32 each)
+            const int cpart = max(32, BN / 4), cbeg = ((warp - 2) >> 2) * cpart, cend = min(BN, cbeg + cpart);
+            auto tmem_ld32 = [](uint32_t addr, uint32_t (&v)[32]) {
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
                     "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -263,20 +283,51 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                       "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
                       "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
                       "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                    : "r"(lane_base + (uint32_t)c0)
+                    : "r"(addr)
                     : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < a.n) {
+            };
+            const uint32_t quarter_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);   // TMEM lane quarter of this warp
+            if (fuse_swiglu) {
+                // gate in accumulator 0, the matching up rows in accumulator 1: h = silu(gate) * up
+                const int n = n0 + (warp & 3) * 32 + lane;
+                for (int c0 = cbeg; c0 < cend; c0 += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(quarter_base + (uint32_t)c0, g);
+                    tmem_ld32(quarter_base + (uint32_t)(BN + c0), u);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (n < a.n) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int m = m0 + c0 + j;
-                        if (m < a.m) {
-                            if (gridDim.z == 1) a.c[(int64_t)m * a.ldc + n] = __uint_as_float(v[j]);
-                            else atomicAdd(a.c + (int64_t)m * a.ldc + n, __uint_as_float(v[j]));
+                        for (int j = 0; j < 32; j++) {
+                            const int m = m0 + c0 + j;
+                            if (m < m_cnt) {
+                                const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+                                const __nv_bfloat16 hv = __float2bfloat16_rn(gv / (1.f + __expf(-gv)) * uv);
+                                a.h[(int64_t)(row_off + m) * a.ldh + n] = *reinterpret_cast<const uint16_t *>(&hv);
+                            }
                         }
                     }
                 }
-            }
+            } else {
+#pragma unroll 1
+                for (int sub = 0; sub < NSUB; sub++) {
+                    const int n = n0 + sub * kBM + (warp & 3) * 32 + lane;
+                    for (int c0 = cbeg; c0 < cend; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(quarter_base + (uint32_t)(sub * BN + c0), v);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (n < a.n) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const int m = m0 + c0 + j;
+                                if (m < m_cnt) {
+                                    float *cp = a.c + (int64_t)(row_off + m) * a.ldc + n;
+                                    if (a.splitk == 1) *cp = __uint_as_float(v[j]);
+                                    else atomicAdd(cp, __uint_as_float(v[j]));
+                                }
+                            }
+                        }
+                    }
+                }
             }
         } else if (ok) {
             atomicOr(a.status, QM_STATUS_TIMEOUT);
@@ -290,9 +341,9 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     }
 }
 
-extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16(const __grid_constant__ QmGemmArgs a) {
+extern "C" __global__ void __launch_bounds__(576, 1) qm_gemm_q4k_bf16(const __grid_constant__ QmGemmArgs a) {
     gemm_body<1>(a);
 }
-extern "C" __global__ void __launch_bounds__(320, 1) qm_gemm_q4k_bf16_r256(const __grid_constant__ QmGemmArgs a) {
+extern "C" __global__ void __launch_bounds__(576, 1) qm_gemm_q4k_bf16_r256(const __grid_constant__ QmGemmArgs a) {
     gemm_body<2>(a);
 }

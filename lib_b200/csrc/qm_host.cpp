@@ -810,6 +810,79 @@ extern "C" int32_t qm_matvec_host(qm_ctx *c, qm_weight h, const float *x_host, i
 }
 
 // ---- prefill matmul (tcgen05) ----------------------------------------------------------------
+// One launch of the tcgen05 matmul. Single matrix: g.experts == 0, weights w, activations
+// a_dev [m][lda]. Grouped over experts (g.experts > 0): blockIdx.z = expert, its activation rows
+// are [offsets[e], offsets[e+1]) of a_dev [rows_total][lda], its weights wq_list[e] (all experts
+// shaped like w); m = the longest expert list (sizes the grid). With g.swiglu the weights are
+// gate|up matrices [2*ffn][k] and the launch stores bf16 silu(gate)*up to g.h instead of C.
+int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, int64_t rows_total, int64_t lda,
+                       uint64_t c_dev, int64_t ldc, const QmGemmGroup &g) {
+    QmGemmArgs a;
+    memset(&a, 0, sizeof a);
+    const bool grouped = g.experts > 0;
+    // Tile shapes: 128 weight rows x 64..512 tokens per CTA (four stages, two at 512 tokens). A
+    // 256-row variant (two accumulators, three or four stages) serves the fused SwiGLU epilogue
+    // (gate rows in one accumulator, the matching up rows in the other); for plain matmuls it is
+    // kept behind QM_GEMM_R256=1: measured equal within noise (76.6 us against 74.0 us at
+    // 4096 x 4096 x 2048), so neither the stage count nor the activation traffic is the limit.
+    const bool r256 = g.swiglu || (env_int("QM_GEMM_R256", 0) != 0 && w->rows >= 256);
+    const int nsub = r256 ? 2 : 1;
+    const int mt = g.m_typical > 0 ? g.m_typical : m;
+    const int bn = mt <= 64 ? 64 : mt <= 128 ? 128 : (mt <= 256 || r256) ? 256 : 512;
+    const int stage_bytes = nsub * 128 * 64 * 2 + bn * 64 * 2;
+    const int stages = std::max(2, std::min(4, (QM_GEMV_SMEM_MAX - 2048) / stage_bytes));
+    const cuuint64_t dims[2] = {(cuuint64_t)w->cols, (cuuint64_t)rows_total};
+    const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)std::min(bn, 256)};
+    const cuuint32_t estr[2] = {1, 1};
+    DRV(c->drv->cuTensorMapEncodeTiled(&a.tmap_act, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)(uintptr_t)a_dev, dims,
+                                       strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+    const int64_t out_cols = g.swiglu ? w->rows / 2 : w->rows;   // columns of the output matrix
+    a.wq = (const uint8_t *)(uintptr_t)w->wq;
+    a.c = (float *)(uintptr_t)c_dev;
+    a.status = (unsigned int *)(uintptr_t)c->status_dev;
+    a.ldc = ldc;
+    a.m = m;
+    a.n = (int32_t)out_cols;
+    a.units = w->units;
+    a.tiles16 = (int32_t)((w->rows + 15) / 16);
+    a.bn = bn;
+    a.stages = stages;
+    a.grouped = grouped ? 1 : 0;
+    a.wq_list = (const uint8_t *const *)(uintptr_t)g.wq_list_dev;
+    a.offsets = (const int32_t *)(uintptr_t)g.offsets_dev;
+    a.swiglu = g.swiglu ? 1 : 0;
+    a.up_offset = (int32_t)(w->rows / 2);
+    a.h = (uint16_t *)(uintptr_t)g.h_dev;
+    a.ldh = g.ldh;
+    const unsigned smem = 1024 + stages * stage_bytes + 256;
+    void *params[1] = {&a};
+    CUlaunchConfig cfg;
+    memset(&cfg, 0, sizeof cfg);
+    const int rows_per_cta = g.swiglu ? 128 : 128 * nsub;
+    cfg.gridDimX = (unsigned)((out_cols + rows_per_cta - 1) / rows_per_cta);
+    cfg.gridDimY = (unsigned)((m + bn - 1) / bn);
+    // few tokens: split K over CTAs until the SMs are covered; partial tiles are added into a
+    // zeroed C (float adds in arrival order: results may differ in the last bits between runs)
+    int splitk = 1;
+    if (!grouped) {
+        while (splitk < 8 && (int)(cfg.gridDimX * cfg.gridDimY) * splitk * 2 <= c->sm_count && w->units * 4 / (splitk * 2) >= 8)
+            splitk *= 2;
+        splitk = env_int("QM_GEMM_SPLITK", splitk);
+    }
+    a.splitk = splitk;
+    cfg.gridDimZ = grouped ? (unsigned)g.experts : (unsigned)splitk;
+    if (splitk > 1) DRV(c->drv->cuMemsetD2D32Async((CUdeviceptr)c_dev, (size_t)ldc * 4, 0, (size_t)w->rows, (size_t)m, c->stream));
+    cfg.blockDimX = 576;   // TMA warp, MMA warp, sixteen dequantizing warps
+    cfg.blockDimY = cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = smem;
+    cfg.hStream = c->stream;
+    DRV(c->drv->cuLaunchKernelEx(&cfg, c->fn[r256 ? QM_K_GEMM_Q4K_R256 : QM_K_GEMM_Q4K], params, nullptr));
+    c->launches++;
+    return QM_OK;
+}
+
 extern "C" int32_t qm_matmul_bf16(qm_ctx *c, qm_weight h, uint64_t a_dev, int32_t m, int64_t lda, uint64_t c_dev,
                                   int64_t ldc) {
     CHECK_CTX(c);
@@ -821,52 +894,7 @@ extern "C" int32_t qm_matmul_bf16(qm_ctx *c, qm_weight h, uint64_t a_dev, int32_
     if ((a_dev & 15) || ((lda * 2) & 15)) return QM_ERR_ARG;
     CtxGuard g(c);
     DRV(g.rc);
-    QmGemmArgs a;
-    memset(&a, 0, sizeof a);
-    // Tile shapes: 128 weight rows x 64..512 tokens per CTA (four stages, two at 512 tokens). A
-    // 256 x 256 variant (two accumulators, three stages, half the activation bytes per flop) is
-    // kept behind QM_GEMM_R256=1: measured equal within noise (76.6 us against 74.0 us at
-    // 4096 x 4096 x 2048), so neither the stage count nor the activation traffic is the limit.
-    const bool r256 = env_int("QM_GEMM_R256", 0) != 0 && w->rows >= 256;
-    const int nsub = r256 ? 2 : 1;
-    const int bn = r256 ? 256 : m <= 64 ? 64 : m <= 128 ? 128 : m <= 256 ? 256 : 512;
-    const int stages = r256 ? 3 : bn == 512 ? 2 : 4;
-    const cuuint64_t dims[2] = {(cuuint64_t)w->cols, (cuuint64_t)m};
-    const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)std::min(bn, 256)};
-    const cuuint32_t estr[2] = {1, 1};
-    DRV(c->drv->cuTensorMapEncodeTiled(&a.tmap_act, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)(uintptr_t)a_dev, dims,
-                                       strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
-    a.wq = (const uint8_t *)(uintptr_t)w->wq;
-    a.c = (float *)(uintptr_t)c_dev;
-    a.status = (unsigned int *)(uintptr_t)c->status_dev;
-    a.ldc = ldc;
-    a.m = m;
-    a.n = (int32_t)w->rows;
-    a.units = w->units;
-    a.tiles16 = (int32_t)((w->rows + 15) / 16);
-    a.bn = bn;
-    a.stages = stages;
-    const unsigned smem = 1024 + stages * (nsub * 128 * 64 * 2 + bn * 64 * 2) + 256;
-    void *params[1] = {&a};
-    CUlaunchConfig cfg;
-    memset(&cfg, 0, sizeof cfg);
-    cfg.gridDimX = (unsigned)((w->rows + 128 * nsub - 1) / (128 * nsub));
-    cfg.gridDimY = (unsigned)((m + bn - 1) / bn);
-    // few tokens: split K over CTAs until the SMs are covered; partial tiles are added into a
-    // zeroed C (float adds in arrival order: results may differ in the last bits between runs)
-    int splitk = 1;
-    while (splitk < 8 && (int)(cfg.gridDimX * cfg.gridDimY) * splitk * 2 <= c->sm_count && w->units * 4 / (splitk * 2) >= 8)
-        splitk *= 2;
-    splitk = env_int("QM_GEMM_SPLITK", splitk);
-    cfg.gridDimZ = (unsigned)splitk;
-    if (splitk > 1) DRV(c->drv->cuMemsetD2D32Async((CUdeviceptr)c_dev, (size_t)ldc * 4, 0, (size_t)w->rows, (size_t)m, c->stream));
-    cfg.blockDimX = 320;
-    cfg.blockDimY = cfg.blockDimZ = 1;
-    cfg.sharedMemBytes = smem;
-    cfg.hStream = c->stream;
-    DRV(c->drv->cuLaunchKernelEx(&cfg, c->fn[r256 ? QM_K_GEMM_Q4K_R256 : QM_K_GEMM_Q4K], params, nullptr));
-    c->launches++;
-    return QM_OK;
+    QmGemmGroup none;
+    memset(&none, 0, sizeof none);
+    return qm_gemm_launch(c, w, a_dev, m, m, lda, c_dev, ldc, none);
 }

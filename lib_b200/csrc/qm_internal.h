@@ -87,6 +87,17 @@ int32_t qm_launch_ex(qm_ctx *c, int kernel, unsigned gx, unsigned block, unsigne
 // of the ops; QM_ERR_SHAPE when the activation planes do not fit in shared memory.
 int qm_fused_grid(qm_ctx *c);
 void qm_balance_op(qm_ctx *c, QmOp *op);
+struct QmGemmGroup {
+    int experts;               // 0: a single matmul
+    int m_typical;             // 0, or the list length to choose the token tile for (the grid still covers m)
+    CUdeviceptr wq_list_dev;   // device array of the experts' weight stores
+    CUdeviceptr offsets_dev;   // device array [experts + 1]: first activation row of each expert
+    bool swiglu;               // gate|up weights, output bf16 silu(gate)*up to h_dev
+    CUdeviceptr h_dev;
+    int64_t ldh;
+};
+int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, int64_t rows_total, int64_t lda,
+                       uint64_t c_dev, int64_t ldc, const QmGemmGroup &g);
 int qm_env_int(const char *name, int dflt);
 int32_t qm_plan_fused(qm_ctx *c, int32_t m, int32_t units, bool allow_slices, QmFusedPlan *p);
 void qm_fill_op(qm_ctx *c, const QmFusedPlan &p, const QmWeight *w, uint64_t x, uint64_t x2, int64_t ldx, uint64_t y,

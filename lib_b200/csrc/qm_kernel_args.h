@@ -119,6 +119,18 @@ struct QmGemmArgs {
     int32_t tiles16;       // 16-row tiles of the store
     int32_t bn;            // tokens per CTA: 64, 128, 256 or 512
     int32_t stages;        // shared-memory stages, 2..4
+    int32_t splitk;        // K shares (blockIdx.z) of a single matmul; 1 in grouped launches
+    // Grouped launch over the experts of a mixture-of-experts layer (blockIdx.z = expert): the
+    // activations are the rows [offsets[e], offsets[e+1]) of one gathered matrix, the weights
+    // of expert e start at wq_list[e]; CTAs beyond an expert's rows leave at once.
+    int32_t grouped;
+    const uint8_t *const *wq_list;   // device array of the experts' stores
+    const int32_t *offsets;          // device array [experts + 1]
+    // SwiGLU epilogue (256-row kernel only): sub-tile 0 holds gate rows n, sub-tile 1 the up rows
+    // n + up_offset; the CTA stores bf16 silu(gate) * up to h[row][n] instead of C.
+    int32_t swiglu, up_offset;
+    uint16_t *h;           // bf16 [rows][ldh]
+    int64_t ldh;
 };
 
 // Mixture-of-experts helpers (qm_moe.cu).

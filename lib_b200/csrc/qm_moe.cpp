@@ -76,15 +76,17 @@ static inline int64_t up256(int64_t v) { return (v + 255) & ~(int64_t)255; }
 // Groups the (token, slot) pairs by expert and copies the bf16 rows of their tokens into that
 // order. Blocks until the list lengths are on the host: the caller sizes its launches (and, in
 // expert-parallel runs, its exchange) with them.
-extern "C" int32_t qm_moe_dispatch(qm_ctx *c, uint64_t ids_dev, int32_t tokens, int32_t topk, int32_t experts,
-                                   uint64_t x_bf16_dev, int64_t ldx, int32_t hidden, uint64_t rows_dev,
-                                   uint64_t pos_dev, int32_t *counts_host) {
+// counts_host == nullptr: nothing is read back (no synchronization); the gather then covers all
+// pairs and *offsets_dev_out names the device array [experts + 1] of list starts.
+static int32_t dispatch_impl(qm_ctx *c, uint64_t ids_dev, int32_t tokens, int32_t topk, int32_t experts,
+                             uint64_t x_bf16_dev, int64_t ldx, int32_t hidden, uint64_t rows_dev, uint64_t pos_dev,
+                             int32_t *counts_host, CUdeviceptr *offsets_dev_out) {
     CHECK_CTX(c);
-    if (!ids_dev || !x_bf16_dev || !rows_dev || !pos_dev || !counts_host) return QM_ERR_ARG;
+    if (!ids_dev || !x_bf16_dev || !rows_dev || !pos_dev) return QM_ERR_ARG;
     if (experts < 1 || experts > 64 || tokens < 0 || topk < 1 || hidden < 8 || (hidden & 7) || ldx < hidden ||
         (x_bf16_dev & 15) || (rows_dev & 15) || ((ldx * 2) & 15))
         return QM_ERR_SHAPE;
-    for (int e = 0; e < experts; e++) counts_host[e] = 0;
+    for (int e = 0; e < experts && counts_host; e++) counts_host[e] = 0;
     if (tokens == 0) return QM_OK;
     CtxGuard g(c);
     DRV(g.rc);
@@ -107,13 +109,17 @@ extern "C" int32_t qm_moe_dispatch(qm_ctx *c, uint64_t ids_dev, int32_t tokens, 
     la.topk = topk;
     rc = qm_launch(c, QM_K_MOE_LISTS, 1, 1, 1024, 0, &la, false);
     if (rc) return rc;
-    int32_t offsets[65];
-    DRV(c->drv->cuMemcpyDtoHAsync_v2(offsets, ws + o_offsets, (size_t)(experts + 1) * 4, c->stream));
-    DRV(c->drv->cuStreamSynchronize(c->stream));
-    const int rows = offsets[experts];
-    if (rows < 0 || rows > pairs) return QM_ERR_STATE;
-    for (int e = 0; e < experts; e++) counts_host[e] = offsets[e + 1] - offsets[e];
-    if (rows == 0) return QM_OK;
+    if (offsets_dev_out) *offsets_dev_out = ws + o_offsets;
+    int rows = (int)pairs;   // every pair names an expert, so the lists hold all pairs
+    if (counts_host) {
+        int32_t offsets[65];
+        DRV(c->drv->cuMemcpyDtoHAsync_v2(offsets, ws + o_offsets, (size_t)(experts + 1) * 4, c->stream));
+        DRV(c->drv->cuStreamSynchronize(c->stream));
+        rows = offsets[experts];
+        if (rows < 0 || rows > pairs) return QM_ERR_STATE;
+        for (int e = 0; e < experts; e++) counts_host[e] = offsets[e + 1] - offsets[e];
+        if (rows == 0) return QM_OK;
+    }
     QmGatherArgs ga;
     memset(&ga, 0, sizeof ga);
     ga.x = (const uint16_t *)(uintptr_t)x_bf16_dev;
@@ -126,8 +132,51 @@ extern "C" int32_t qm_moe_dispatch(qm_ctx *c, uint64_t ids_dev, int32_t tokens, 
     return qm_launch(c, QM_K_MOE_GATHER, grid_for((int64_t)rows * hidden / 8, 256, c->sm_count * 8), 1, 256, 0, &ga, false);
 }
 
+extern "C" int32_t qm_moe_dispatch(qm_ctx *c, uint64_t ids_dev, int32_t tokens, int32_t topk, int32_t experts,
+                                   uint64_t x_bf16_dev, int64_t ldx, int32_t hidden, uint64_t rows_dev,
+                                   uint64_t pos_dev, int32_t *counts_host) {
+    if (!counts_host) return QM_ERR_ARG;
+    return dispatch_impl(c, ids_dev, tokens, topk, experts, x_bf16_dev, ldx, hidden, rows_dev, pos_dev, counts_host,
+                         nullptr);
+}
+
+// The two grouped launches over rows grouped by expert (list starts in offsets_dev): gate|up with
+// the SwiGLU in the epilogue (bf16 h in the stage's workspace), then down into y. `longest`
+// bounds the list lengths (sizes the grid), `typical` chooses the token tile.
+static int32_t experts_launch(qm_ctx *c, const std::vector<QmWeight *> &wg, const std::vector<QmWeight *> &wd,
+                              int32_t experts, uint64_t rows_bf16_dev, int64_t rows, int32_t longest, int32_t typical,
+                              CUdeviceptr offsets_dev, uint64_t y_dev, int64_t hidden, int64_t ffn) {
+    const int64_t o_h = 0, o_gl = up256(rows * ffn * 2) + 512, o_dl = o_gl + 512, total = o_dl + 512;
+    int32_t rc = ensure_ws2(c, total);
+    if (rc) return rc;
+    const CUdeviceptr ws = c->moe_ws2;
+    uint64_t lists[2][64];
+    for (int e = 0; e < experts; e++) {
+        lists[0][e] = (uint64_t)wg[e]->wq;
+        lists[1][e] = (uint64_t)wd[e]->wq;
+    }
+    DRV(c->drv->cuMemcpyHtoDAsync_v2(ws + o_gl, lists[0], (size_t)experts * 8, c->stream));
+    DRV(c->drv->cuMemcpyHtoDAsync_v2(ws + o_dl, lists[1], (size_t)experts * 8, c->stream));
+    QmGemmGroup grp;
+    memset(&grp, 0, sizeof grp);
+    grp.experts = experts;
+    grp.m_typical = typical;
+    grp.offsets_dev = offsets_dev;
+    grp.wq_list_dev = ws + o_gl;
+    grp.swiglu = true;
+    grp.h_dev = ws + o_h;
+    grp.ldh = ffn;
+    rc = qm_gemm_launch(c, wg[0], rows_bf16_dev, longest, rows, hidden, 0, 0, grp);
+    if (rc) return rc;
+    grp.wq_list_dev = ws + o_dl;
+    grp.swiglu = false;
+    grp.h_dev = 0;
+    return qm_gemm_launch(c, wd[0], ws + o_h, longest, rows, ffn, y_dev, hidden, grp);
+}
+
 // y[p][:] = down_e( silu(gate_e r_p) * (up_e r_p) ) for rows r grouped by expert: the first
-// counts[0] rows belong to expert 0, the next counts[1] to expert 1, and so on.
+// counts[0] rows belong to expert 0, the next counts[1] to expert 1, and so on. Two launches
+// for all experts together: gate|up with the SwiGLU in the epilogue (bf16 h), then down.
 extern "C" int32_t qm_moe_experts(qm_ctx *c, const qm_weight *gate_up, const qm_weight *down, int32_t experts,
                                   uint64_t rows_bf16_dev, const int32_t *counts_host, uint64_t y_dev) {
     CHECK_CTX(c);
@@ -136,47 +185,29 @@ extern "C" int32_t qm_moe_experts(qm_ctx *c, const qm_weight *gate_up, const qm_
     int64_t hidden = 0, ffn = 0;
     int32_t rc = check_experts(gate_up, down, experts, wg, wd, &hidden, &ffn);
     if (rc) return rc;
-    if (rows_bf16_dev & 15) return QM_ERR_SHAPE;
+    if ((rows_bf16_dev & 15) || (ffn & 127)) return QM_ERR_SHAPE;   // SwiGLU epilogue: whole 128-row tiles of gate rows
     int64_t rows = 0;
+    int32_t longest = 0;
+    int32_t offsets[65];
     for (int e = 0; e < experts; e++) {
         if (counts_host[e] < 0) return QM_ERR_COUNT;
+        offsets[e] = (int32_t)rows;
         rows += counts_host[e];
+        longest = std::max(longest, counts_host[e]);
     }
+    offsets[experts] = (int32_t)rows;
     if (rows == 0) return QM_OK;
     if (rows >= (1 << 24)) return QM_ERR_SHAPE;
     CtxGuard g(c);
     DRV(g.rc);
-    // workspace behind the dispatch arrays: gate|up fp32, then the bf16 hidden activations
-    const int64_t o_gu = 0, o_h = o_gu + up256(rows * 2 * ffn * 4), total = o_h + up256(rows * ffn * 2);
+    // workspace: the bf16 hidden activations, the offsets, then the two lists of weight stores
+    const int64_t o_off = up256(rows * ffn * 2), total = o_off + 3 * 512;
     rc = ensure_ws2(c, total);
     if (rc) return rc;
     const CUdeviceptr ws = c->moe_ws2;
-    int64_t off = 0;
-    for (int e = 0; e < experts; e++) {
-        const int n_e = counts_host[e];
-        if (n_e > 0) {
-            rc = qm_matmul_bf16(c, gate_up[e], rows_bf16_dev + off * hidden * 2, n_e, hidden, ws + o_gu + off * 2 * ffn * 4, 2 * ffn);
-            if (rc) return rc;
-        }
-        off += n_e;
-    }
-    QmSwigluArgs sa;
-    sa.gu = (const float *)(uintptr_t)(ws + o_gu);
-    sa.h = (uint16_t *)(uintptr_t)(ws + o_h);
-    sa.rows = (int32_t)rows;
-    sa.ffn = (int32_t)ffn;
-    rc = qm_launch(c, QM_K_MOE_SWIGLU, grid_for(rows * ffn / 2, 256, c->sm_count * 8), 1, 256, 0, &sa, false);
-    if (rc) return rc;
-    off = 0;
-    for (int e = 0; e < experts; e++) {
-        const int n_e = counts_host[e];
-        if (n_e > 0) {
-            rc = qm_matmul_bf16(c, down[e], ws + o_h + off * ffn * 2, n_e, ffn, y_dev + off * hidden * 4, hidden);
-            if (rc) return rc;
-        }
-        off += n_e;
-    }
-    return QM_OK;
+    // the offsets travel in stream order; the host copy is read before the call returns
+    DRV(c->drv->cuMemcpyHtoDAsync_v2(ws + o_off, offsets, (size_t)(experts + 1) * 4, c->stream));
+    return experts_launch(c, wg, wd, experts, rows_bf16_dev, rows, longest, longest, ws + o_off, y_dev, hidden, ffn);
 }
 
 // out[t][:] = sum_s weights[t][s] * y[pos[t*topk+s]][:], slots in order (deterministic).
@@ -224,10 +255,20 @@ extern "C" int32_t qm_moe_grouped(qm_ctx *c, const qm_weight *gate_up, const qm_
         if (rc) return rc;
     }
     const CUdeviceptr ws = c->moe_ws3;
-    int32_t counts[64];
-    rc = qm_moe_dispatch(c, ids_dev, tokens, topk, experts, x_bf16_dev, ldx, (int32_t)hidden, ws + o_rows, ws + o_pos, counts);
+    // nothing is read back to the host: the lists stay on the device, the grouped launches cover
+    // the longest possible list (all pairs) and CTAs beyond an expert's rows leave at once
+    if (ffn & 127) return QM_ERR_SHAPE;
+    CUdeviceptr offsets_dev = 0;
+    rc = dispatch_impl(c, ids_dev, tokens, topk, experts, x_bf16_dev, ldx, (int32_t)hidden, ws + o_rows, ws + o_pos,
+                       nullptr, &offsets_dev);
     if (rc) return rc;
-    rc = qm_moe_experts(c, gate_up, down, experts, ws + o_rows, counts, ws + o_y);
-    if (rc) return rc;
+    {
+        CtxGuard g(c);
+        DRV(g.rc);
+        const int32_t typical = (int32_t)std::max<int64_t>(1, (pairs + experts - 1) / experts);
+        rc = experts_launch(c, wg, wd, experts, ws + o_rows, pairs, (int32_t)pairs, typical, offsets_dev, ws + o_y, hidden,
+                            ffn);
+        if (rc) return rc;
+    }
     return qm_moe_combine(c, ws + o_y, ws + o_pos, weights_dev, tokens, topk, (int32_t)hidden, out_dev, ldo);
 }

@@ -99,12 +99,15 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     const uint32_t smem_base = smem_u32(smem);
 
     const bool fuse_swiglu = NSUB == 2 && a.swiglu != 0;
-    const int n0 = blockIdx.x * kBM * (fuse_swiglu ? 1 : NSUB), m0 = blockIdx.y * BN;
+    // grouped launches put the expert in blockIdx.y and the token tile in blockIdx.z: CTAs are
+    // handed out x-fastest, then y, then z, so every expert's first token tiles (the ones with
+    // work) start before the mostly empty later tiles
+    const int n0 = blockIdx.x * kBM * (fuse_swiglu ? 1 : NSUB), m0 = (a.grouped ? blockIdx.z : blockIdx.y) * BN;
     // grouped launch: this CTA's expert, its rows of the gathered activations and its weights
     int row_off = 0, m_cnt = a.m;
     const uint8_t *wq = a.wq;
     if (a.grouped) {
-        const int e = blockIdx.z;
+        const int e = blockIdx.y;
         row_off = a.offsets[e];
         m_cnt = a.offsets[e + 1] - row_off;
         if (m0 >= m_cnt) return;   // nothing routed here (uniform over the CTA, before any barrier)

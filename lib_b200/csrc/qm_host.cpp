@@ -872,7 +872,11 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
         splitk = env_int("QM_GEMM_SPLITK", splitk);
     }
     a.splitk = splitk;
-    cfg.gridDimZ = grouped ? (unsigned)g.experts : (unsigned)splitk;
+    cfg.gridDimZ = (unsigned)splitk;
+    if (grouped) {   // expert in y, token tile in z (see the kernel)
+        cfg.gridDimZ = cfg.gridDimY;
+        cfg.gridDimY = (unsigned)g.experts;
+    }
     if (splitk > 1) DRV(c->drv->cuMemsetD2D32Async((CUdeviceptr)c_dev, (size_t)ldc * 4, 0, (size_t)w->rows, (size_t)m, c->stream));
     cfg.blockDimX = 576;   // TMA warp, MMA warp, sixteen dequantizing warps
     cfg.blockDimY = cfg.blockDimZ = 1;

@@ -251,6 +251,23 @@ QM_API int32_t qm_stack_create_tp(qm_ctx *ctx, int32_t layers, int32_t hidden, i
 QM_API int32_t qm_stack_ipc_handle(qm_ctx *ctx, qm_stack *stack, void *handle64);
 QM_API int32_t qm_stack_set_peers(qm_ctx *ctx, qm_stack *stack, const void *handles);
 
+/* Host-side residency manager for expert weight blobs, the behaviour of moe.ExpertCacheManager
+ * (lm/moe/moe.go:143-287): at most max_hot experts stay in host memory, admitting one more
+ * spills the least recently used one (never the one just touched) to <dir>/expert_<id>.bin, a
+ * cold expert is read back on demand. dir NULL or "" = $TMPDIR/lm-expert-cache. max_hot <= 0 is
+ * refused (QM_ERR_ARG), an unknown expert is QM_ERR_ARG, file errors are QM_ERR_STATE.
+ * qm_expert_cache_get with out = NULL only returns the size (and pages the expert in); with a
+ * buffer it copies the bytes (QM_ERR_BUFFER if capacity is short). The bytes are what
+ * qm_store_upload takes. Thread-safe; no GPU involved. */
+typedef struct qm_expert_cache qm_expert_cache;
+QM_API int32_t qm_expert_cache_create(const char *dir, int32_t max_hot, qm_expert_cache **out);   /* NewExpertCacheManager */
+QM_API int32_t qm_expert_cache_register(qm_expert_cache *cache, int64_t expert, const void *bytes, int64_t n); /* RegisterExpert */
+QM_API int32_t qm_expert_cache_get(qm_expert_cache *cache, int64_t expert, void *out, int64_t capacity,
+                                   int64_t *size);                                               /* GetExpert */
+QM_API int32_t qm_expert_cache_hot(qm_expert_cache *cache);                                      /* HotExperts */
+QM_API int32_t qm_expert_cache_evict(qm_expert_cache *cache, int64_t expert);                    /* EvictColdExpert */
+QM_API int32_t qm_expert_cache_close(qm_expert_cache *cache);                                    /* Close */
+
 #ifdef __cplusplus
 }
 #endif

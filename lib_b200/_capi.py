@@ -68,6 +68,12 @@ def _load():
         "qm_stack_create_tp": (i32, [p, i32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_stack_ipc_handle": (i32, [p, p, p]),
         "qm_stack_set_peers": (i32, [p, p, p]),
+        "qm_expert_cache_create": (i32, [ctypes.c_char_p, i32, ctypes.POINTER(p)]),
+        "qm_expert_cache_register": (i32, [p, i64, p, i64]),
+        "qm_expert_cache_get": (i32, [p, i64, p, i64, ctypes.POINTER(i64)]),
+        "qm_expert_cache_hot": (i32, [p]),
+        "qm_expert_cache_evict": (i32, [p, i64]),
+        "qm_expert_cache_close": (i32, [p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

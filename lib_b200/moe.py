@@ -150,3 +150,41 @@ class MoELayer:
         for w in self.gate_up + self.down:
             w.free()
         self.gate_up, self.down = [], []
+
+
+class ExpertCacheManager:
+    """moe.ExpertCacheManager (lm/moe/moe.go:143-287) over the library's host-side cache: at most
+    max_hot expert blobs in memory, least recently used spilled to <dir>/expert_<id>.bin, cold
+    experts paged back in by get_expert. Method names follow the Go API."""
+
+    def __init__(self, directory, max_hot):
+        import ctypes
+        from ._capi import lib, _check
+        self._lib, self._check, self._ct = lib, _check, ctypes
+        h = ctypes.c_void_p()
+        _check(lib.qm_expert_cache_create((directory or "").encode(), int(max_hot), ctypes.byref(h)),
+               "NewExpertCacheManager")
+        self._h = h
+
+    def register_expert(self, expert_id, weights):
+        data = bytes(weights)
+        self._check(self._lib.qm_expert_cache_register(self._h, int(expert_id), data, len(data)), "RegisterExpert")
+
+    def get_expert(self, expert_id):
+        ct = self._ct
+        size = ct.c_int64()
+        self._check(self._lib.qm_expert_cache_get(self._h, int(expert_id), None, 0, ct.byref(size)), "GetExpert")
+        buf = (ct.c_ubyte * max(1, size.value))()
+        self._check(self._lib.qm_expert_cache_get(self._h, int(expert_id), buf, size.value, ct.byref(size)), "GetExpert")
+        return bytes(buf[:size.value])
+
+    def hot_experts(self):
+        return int(self._lib.qm_expert_cache_hot(self._h))
+
+    def evict_cold_expert(self, expert_id):
+        self._check(self._lib.qm_expert_cache_evict(self._h, int(expert_id)), "EvictColdExpert")
+
+    def close(self):
+        if self._h:
+            self._lib.qm_expert_cache_close(self._h)
+            self._h = None

@@ -17,7 +17,7 @@
 //     and per 256 tokens into a TMEM accumulator of BN fp32 columns (BN = 512 uses the whole
 //     tensor memory: the dequantized tile then feeds two MMAs), tcgen05.commit frees the stage;
 //   * after the last chunk warps 2..17 read the accumulator back with tcgen05.ld and store C.
-// A ring of 2..4 shared-memory stages decouples the three roles. Every mbarrier wait is
+// A ring of 2..8 shared-memory stages decouples the three roles. Every mbarrier wait is
 // bounded (qm_pipe.cuh); on expiry the status word gets QM_STATUS_TIMEOUT, the roles leave
 // their loops, TMEM is freed and the kernel returns.
 #include <cuda.h>
@@ -31,7 +31,7 @@ using namespace qm;
 
 namespace {
 
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 8;
 constexpr int kBM = 128;          // weight rows per CTA (tcgen05 M)
 constexpr int kBK = 64;           // K columns per stage: one 32-byte quant group, 128 bytes of bf16
 constexpr int kATile = kBM * kBK * 2;
@@ -122,7 +122,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
 
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) {
-            mbar_init(full_a + 8 * s, kStages >= 4 ? 128 : 256);
+            mbar_init(full_a + 8 * s, kStages >= 4 ? 4 : 8);   // warps of one producer group
             mbar_init(full_b + 8 * s, 1);
             mbar_init(empty + 8 * s, 1);
         }
@@ -147,6 +147,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                 const int s = kc % kStages;
                 const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
                 if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); break; }
+                if (a.debug & 2) { mbar_arrive(full_b + 8 * s); continue; }
                 mbar_expect_tx(full_b + 8 * s, (uint32_t)b_tile);
                 for (int nb = 0; nb < BN; nb += 256)   // a TMA box has at most 256 rows
                     tma_load_2d(smem_base + s * stage_bytes + a_tile + nb * 128, &a.tmap_act, (kc_lo + kc) * kBK, row_off + m0 + nb,
@@ -170,7 +171,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                 const uint64_t bdesc = smem_desc(smem_base + s * stage_bytes + a_tile);
 #pragma unroll
                 for (int sub = 0; sub < NSUB; sub++)
-                    for (int nb = 0; nb < BN; nb += 256)
+                    for (int nb = 0; nb < BN && !(a.debug & 4); nb += 256)
 #pragma unroll
                         for (int k16 = 0; k16 < kBK / 16; k16++)   // 16 bf16 = 32 bytes = 2 descriptor units
                             umma_f16(tmem_base + (uint32_t)(sub * BN + nb), adesc + sub * (kATile >> 4) + 2 * k16,
@@ -203,7 +204,10 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         }
         bool ok = true;
         // the quant bytes and the header of the group's next chunk are in flight while one is converted
-        uint4 qa[NSUB], qb[NSUB], hd[NSUB], qa_n[NSUB], qb_n[NSUB], hd_n[NSUB];
+        // (two chunks ahead in the 128-row kernel, one in the 256-row kernel, which has the registers
+        // for no more)
+        constexpr int kPre = NSUB == 1 ? 2 : 1;
+        uint4 qa[NSUB], qb[NSUB], hd[NSUB], qa_n[kPre][NSUB], qb_n[kPre][NSUB], hd_n[kPre][NSUB];
         auto load_chunk = [&](int sub, int kcl, uint4 &x0, uint4 &x1, uint4 &h) {
             const int kc = kc_lo + kcl;
             const uint8_t *item = row_items[sub] + (size_t)(kc >> 2) * QM_Q4K_ITEM_BYTES;
@@ -212,22 +216,32 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
             x1 = __ldg(reinterpret_cast<const uint4 *>(item + 256 + 512 * (kc & 3) + 32 * rr + 16));
         };
 #pragma unroll
-        for (int sub = 0; sub < NSUB; sub++)
-            if (grp < nk) load_chunk(sub, grp, qa_n[sub], qb_n[sub], hd_n[sub]);
+        for (int i = 0; i < kPre; i++)
+#pragma unroll
+            for (int sub = 0; sub < NSUB; sub++)
+                if (grp + i * kGroups < nk) load_chunk(sub, grp + i * kGroups, qa_n[i][sub], qb_n[i][sub], hd_n[i][sub]);
         for (int kc = grp; kc < nk; kc += kGroups) {
             const int s = kc % kStages;
             const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
             const int p = (kc_lo + kc) & 3;
 #pragma unroll
             for (int sub = 0; sub < NSUB; sub++) {
-                qa[sub] = qa_n[sub];
-                qb[sub] = qb_n[sub];
-                hd[sub] = hd_n[sub];
-                if (kc + kGroups < nk) load_chunk(sub, kc + kGroups, qa_n[sub], qb_n[sub], hd_n[sub]);
+                qa[sub] = qa_n[0][sub];
+                qb[sub] = qb_n[0][sub];
+                hd[sub] = hd_n[0][sub];
+#pragma unroll
+                for (int i = 0; i + 1 < kPre; i++) {
+                    qa_n[i][sub] = qa_n[i + 1][sub];
+                    qb_n[i][sub] = qb_n[i + 1][sub];
+                    hd_n[i][sub] = hd_n[i + 1][sub];
+                }
+                if (kc + kPre * kGroups < nk)
+                    load_chunk(sub, kc + kPre * kGroups, qa_n[kPre - 1][sub], qb_n[kPre - 1][sub], hd_n[kPre - 1][sub]);
             }
             if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); ok = false; break; }
 #pragma unroll
             for (int sub = 0; sub < NSUB; sub++) {
+                if (a.debug & 1) break;
                 // scales and minima of sub-blocks 2p (low nibbles, columns 0..31) and 2p+1 (high, 32..63)
                 const uint4 h4 = hd[sub];
                 uint32_t av[2], bv[2];
@@ -270,7 +284,8 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
-            mbar_arrive(full_a + 8 * s);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_a + 8 * s);   // one arrival per warp: 128 arrivals on one barrier serialize
         }
         // ---- epilogue: accumulator row r holds C[m0..m0+BN)[n0+r] -------------------------------------
         if (ok && mbar_wait_bounded(tmem_full, 0u)) {

@@ -830,7 +830,7 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     const int mt = g.m_typical > 0 ? g.m_typical : m;
     const int bn = mt <= 64 ? 64 : mt <= 128 ? 128 : (mt <= 256 || r256) ? 256 : 512;
     const int stage_bytes = nsub * 128 * 64 * 2 + bn * 64 * 2;
-    const int stages = std::max(2, std::min(4, (QM_GEMV_SMEM_MAX - 2048) / stage_bytes));
+    const int stages = std::max(2, std::min(8, (QM_GEMV_SMEM_MAX - 2048) / stage_bytes));
     const cuuint64_t dims[2] = {(cuuint64_t)w->cols, (cuuint64_t)rows_total};
     const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
     const cuuint32_t box[2] = {64, (cuuint32_t)std::min(bn, 256)};
@@ -856,6 +856,7 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     a.up_offset = (int32_t)(w->rows / 2);
     a.h = (uint16_t *)(uintptr_t)g.h_dev;
     a.ldh = g.ldh;
+    a.debug = env_int("QM_GEMM_DEBUG", 0);
     const unsigned smem = 1024 + stages * stage_bytes + 256;
     void *params[1] = {&a};
     CUlaunchConfig cfg;

@@ -118,7 +118,7 @@ struct QmGemmArgs {
     int32_t units;         // K / 256
     int32_t tiles16;       // 16-row tiles of the store
     int32_t bn;            // tokens per CTA: 64, 128, 256 or 512
-    int32_t stages;        // shared-memory stages, 2..4
+    int32_t stages;        // shared-memory stages, 2..8
     int32_t splitk;        // K shares (blockIdx.z) of a single matmul; 1 in grouped launches
     // Grouped launch over the experts of a mixture-of-experts layer (blockIdx.z = expert): the
     // activations are the rows [offsets[e], offsets[e+1]) of one gathered matrix, the weights
@@ -131,6 +131,7 @@ struct QmGemmArgs {
     int32_t swiglu, up_offset;
     uint16_t *h;           // bf16 [rows][ldh]
     int64_t ldh;
+    int32_t debug, pad;    // 0 in production; bits switch off pipeline roles for timing experiments (results are wrong)
 };
 
 // Mixture-of-experts helpers (qm_moe.cu).

@@ -159,8 +159,11 @@ QM_API int32_t qm_moe_route(qm_ctx *ctx, uint64_t logits_dev, int32_t tokens, in
  * expert on the device, each expert runs the tcgen05 matmul over its list, and the combine
  * adds a token's expert outputs in slot order. New API of this path: the reference's lm/moe
  * routes and caches experts but has no matmul; its device gather is nvidia/x/cudamoe/moe.go:72-96.
- * Asynchronous: the lists stay on the device and all experts run in two grouped launches
- * (gate|up with the SwiGLU in its epilogue, then down); ffn must be a multiple of 128. */
+ * All experts run in two grouped launches (gate|up with the SwiGLU in its epilogue, then
+ * down); ffn must be a multiple of 128. The list lengths are read back to the host once (one
+ * stream synchronization inside the call) to size those launches; with QM_MOE_NOSYNC=1 in the
+ * environment nothing is read back and the call is fully asynchronous (slower: the launches
+ * then cover the longest possible lists). */
 QM_API int32_t qm_moe_grouped(qm_ctx *ctx, const qm_weight *gate_up, const qm_weight *down, int32_t experts,
                               uint64_t x_bf16_dev, int32_t tokens, int64_t ldx, uint64_t ids_dev,
                               uint64_t weights_dev, int32_t topk, uint64_t out_dev, int64_t ldo);

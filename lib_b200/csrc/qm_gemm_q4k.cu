@@ -83,14 +83,18 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 
 // NSUB = 128-row sub-tiles of weight rows per CTA: 1 (128 x BN tile, BN up to 512) or 2
 // (256 x BN tile, BN up to 256: half the activation traffic per flop and room for a third stage).
-template <int NSUB>
+// KS = 64-column K chunks per pipeline stage: 1, or 2 for small token tiles, where the barrier
+// handshake of a stage (about 0.3 us, whatever the stage count) is longer than the MMAs of one
+// chunk: two chunks per handshake halve it.
+template <int NSUB, int KS>
 __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int BN = a.bn, kStages = a.stages;
-    const int b_tile = BN * kBK * 2;
-    constexpr int a_tile = NSUB * kATile;
-    const int stage_bytes = a_tile + b_tile;
+    const int b_tile = BN * kBK * 2;          // one 64-column chunk of the activations
+    constexpr int a_tile = NSUB * kATile;     // one 64-column chunk of the weights
+    const int a_bytes = KS * a_tile;
+    const int stage_bytes = a_bytes + KS * b_tile;
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)kStages * stage_bytes);
     const uint32_t full_a = smem_u32(bars), full_b = full_a + 8 * kMaxStages, empty = full_b + 8 * kMaxStages;
@@ -115,7 +119,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     }
     // 64-column chunks along K; with split K (splitk > 1) this CTA takes a contiguous share
     // and adds its partial tile to C, which the host zeroed
-    const int nk_all = a.units * 4;
+    const int nk_all = a.units * 4 / KS;      // stage chunks of KS x 64 columns
     const int zk = a.grouped ? 0 : (int)blockIdx.z;
     const int kc_lo = (int)((int64_t)nk_all * zk / a.splitk);
     const int nk = (int)((int64_t)nk_all * (zk + 1) / a.splitk) - kc_lo;
@@ -148,10 +152,12 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                 const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
                 if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); break; }
                 if (a.debug & 2) { mbar_arrive(full_b + 8 * s); continue; }
-                mbar_expect_tx(full_b + 8 * s, (uint32_t)b_tile);
-                for (int nb = 0; nb < BN; nb += 256)   // a TMA box has at most 256 rows
-                    tma_load_2d(smem_base + s * stage_bytes + a_tile + nb * 128, &a.tmap_act, (kc_lo + kc) * kBK, row_off + m0 + nb,
-                                full_b + 8 * s);
+                mbar_expect_tx(full_b + 8 * s, (uint32_t)(KS * b_tile));
+#pragma unroll
+                for (int j = 0; j < KS; j++)
+                    for (int nb = 0; nb < BN; nb += 256)   // a TMA box has at most 256 rows
+                        tma_load_2d(smem_base + s * stage_bytes + a_bytes + j * b_tile + nb * 128, &a.tmap_act,
+                                    ((kc_lo + kc) * KS + j) * kBK, row_off + m0 + nb, full_b + 8 * s);
             }
         }
     } else if (warp == 1) {
@@ -167,15 +173,18 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                 ok = mbar_wait_bounded(full_a + 8 * s, ph) && mbar_wait_bounded(full_b + 8 * s, ph);
                 if (!ok) { atomicOr(a.status, QM_STATUS_TIMEOUT); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = smem_desc(smem_base + s * stage_bytes);
-                const uint64_t bdesc = smem_desc(smem_base + s * stage_bytes + a_tile);
 #pragma unroll
-                for (int sub = 0; sub < NSUB; sub++)
-                    for (int nb = 0; nb < BN && !(a.debug & 4); nb += 256)
+                for (int j = 0; j < KS; j++) {
+                    const uint64_t adesc = smem_desc(smem_base + s * stage_bytes + j * a_tile);
+                    const uint64_t bdesc = smem_desc(smem_base + s * stage_bytes + a_bytes + j * b_tile);
 #pragma unroll
-                        for (int k16 = 0; k16 < kBK / 16; k16++)   // 16 bf16 = 32 bytes = 2 descriptor units
-                            umma_f16(tmem_base + (uint32_t)(sub * BN + nb), adesc + sub * (kATile >> 4) + 2 * k16,
-                                     bdesc + (nb * 128 >> 4) + 2 * k16, idesc, (kc | k16) != 0);
+                    for (int sub = 0; sub < NSUB; sub++)
+                        for (int nb = 0; nb < BN && !(a.debug & 4); nb += 256)
+#pragma unroll
+                            for (int k16 = 0; k16 < kBK / 16; k16++)   // 16 bf16 = 32 bytes = 2 descriptor units
+                                umma_f16(tmem_base + (uint32_t)(sub * BN + nb), adesc + sub * (kATile >> 4) + 2 * k16,
+                                         bdesc + (nb * 128 >> 4) + 2 * k16, idesc, (kc | j | k16) != 0);
+                }
                 umma_commit(empty + 8 * s);   // frees the stage when these MMAs have read it
             }
             umma_commit(tmem_full);           // accumulator complete (or abandoned)
@@ -203,89 +212,81 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
             row_items[sub] = wq + tile16 * a.units * QM_Q4K_ITEM_BYTES;
         }
         bool ok = true;
-        // the quant bytes and the header of the group's next chunk are in flight while one is converted
-        // (two chunks ahead in the 128-row kernel, one in the 256-row kernel, which has the registers
-        // for no more)
-        constexpr int kPre = NSUB == 1 ? 2 : 1;
-        uint4 qa[NSUB], qb[NSUB], hd[NSUB], qa_n[kPre][NSUB], qb_n[kPre][NSUB], hd_n[kPre][NSUB];
-        auto load_chunk = [&](int sub, int kcl, uint4 &x0, uint4 &x1, uint4 &h) {
-            const int kc = kc_lo + kcl;
-            const uint8_t *item = row_items[sub] + (size_t)(kc >> 2) * QM_Q4K_ITEM_BYTES;
-            h = __ldg(reinterpret_cast<const uint4 *>(item + 16 * rr));
-            x0 = __ldg(reinterpret_cast<const uint4 *>(item + 256 + 512 * (kc & 3) + 32 * rr));
-            x1 = __ldg(reinterpret_cast<const uint4 *>(item + 256 + 512 * (kc & 3) + 32 * rr + 16));
+        // The quant bytes and headers of the group's next stage chunk are loaded right after the
+        // current one has been handed over, into the same registers: the other groups' turns lie
+        // between the loads and their use.
+        uint4 qa[KS][NSUB], qb[KS][NSUB], hd[KS][NSUB];
+        auto load_stage = [&](int kcl) {
+#pragma unroll
+            for (int j = 0; j < KS; j++) {
+                const int c64 = (kc_lo + kcl) * KS + j;   // 64-column chunk along K
+#pragma unroll
+                for (int sub = 0; sub < NSUB; sub++) {
+                    const uint8_t *item = row_items[sub] + (size_t)(c64 >> 2) * QM_Q4K_ITEM_BYTES;
+                    hd[j][sub] = __ldg(reinterpret_cast<const uint4 *>(item + 16 * rr));
+                    qa[j][sub] = __ldg(reinterpret_cast<const uint4 *>(item + 256 + 512 * (c64 & 3) + 32 * rr));
+                    qb[j][sub] = __ldg(reinterpret_cast<const uint4 *>(item + 256 + 512 * (c64 & 3) + 32 * rr + 16));
+                }
+            }
         };
-#pragma unroll
-        for (int i = 0; i < kPre; i++)
-#pragma unroll
-            for (int sub = 0; sub < NSUB; sub++)
-                if (grp + i * kGroups < nk) load_chunk(sub, grp + i * kGroups, qa_n[i][sub], qb_n[i][sub], hd_n[i][sub]);
+        if (grp < nk) load_stage(grp);
         for (int kc = grp; kc < nk; kc += kGroups) {
             const int s = kc % kStages;
             const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
-            const int p = (kc_lo + kc) & 3;
-#pragma unroll
-            for (int sub = 0; sub < NSUB; sub++) {
-                qa[sub] = qa_n[0][sub];
-                qb[sub] = qb_n[0][sub];
-                hd[sub] = hd_n[0][sub];
-#pragma unroll
-                for (int i = 0; i + 1 < kPre; i++) {
-                    qa_n[i][sub] = qa_n[i + 1][sub];
-                    qb_n[i][sub] = qb_n[i + 1][sub];
-                    hd_n[i][sub] = hd_n[i + 1][sub];
-                }
-                if (kc + kPre * kGroups < nk)
-                    load_chunk(sub, kc + kPre * kGroups, qa_n[kPre - 1][sub], qb_n[kPre - 1][sub], hd_n[kPre - 1][sub]);
-            }
             if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); ok = false; break; }
 #pragma unroll
-            for (int sub = 0; sub < NSUB; sub++) {
-                if (a.debug & 1) break;
-                // scales and minima of sub-blocks 2p (low nibbles, columns 0..31) and 2p+1 (high, 32..63)
-                const uint4 h4 = hd[sub];
-                uint32_t av[2], bv[2];
-                const float d = __half2float(__ushort_as_half((unsigned short)(h4.x & 0xFFFFu)));
-                const float dmin = __half2float(__ushort_as_half((unsigned short)(h4.x >> 16)));
+            for (int j = 0; j < KS; j++) {
+                const int p = ((kc_lo + kc) * KS + j) & 3;
 #pragma unroll
-                for (int hs = 0; hs < 2; hs++) {
-                    const int j = 2 * p + hs;
-                    int sc, mn;
-                    if (j < 4) {
-                        sc = (h4.y >> (8 * j)) & 63;
-                        mn = (h4.z >> (8 * j)) & 63;
-                    } else {
-                        const int jj = j - 4;
-                        sc = ((h4.w >> (8 * jj)) & 0xF) | (((h4.y >> (8 * jj + 6)) & 3) << 4);
-                        mn = ((h4.w >> (8 * jj + 4)) & 0xF) | (((h4.z >> (8 * jj + 6)) & 3) << 4);
-                    }
-                    av[hs] = bf2(d * (float)sc);
-                    bv[hs] = bf2(-dmin * (float)mn);
-                }
-                const uint32_t w[8] = {qa[sub].x, qa[sub].y, qa[sub].z, qa[sub].w, qb[sub].x, qb[sub].y, qb[sub].z, qb[sub].w};
-                uint8_t *arow = smem + (size_t)s * stage_bytes + sub * kATile + r * 128;
+                for (int sub = 0; sub < NSUB; sub++) {
+                    if (a.debug & 1) break;
+                    // scales and minima of sub-blocks 2p (low nibbles, columns 0..31) and 2p+1 (high, 32..63)
+                    const uint4 h4 = hd[j][sub];
+                    uint32_t av[2], bv[2];
+                    const float d = __half2float(__ushort_as_half((unsigned short)(h4.x & 0xFFFFu)));
+                    const float dmin = __half2float(__ushort_as_half((unsigned short)(h4.x >> 16)));
 #pragma unroll
-                for (int hs = 0; hs < 2; hs++) {
-                    if (my_hs >= 0 && hs != my_hs) continue;
-#pragma unroll
-                    for (int c = 0; c < 4; c++) {   // 16-byte pieces (eight columns), XOR-swizzled by the row inside its 8-row group
-                        uint32_t o[4];
-#pragma unroll
-                        for (int i = 0; i < 2; i++) {
-                            // four codes of this nibble half, then each next to the byte 0x43: bf16 128+q
-                            const uint32_t wv = w[2 * c + i];
-                            const uint32_t nib = hs ? (wv >> 4) & 0x0F0F0F0Fu : wv & 0x0F0F0F0Fu;
-                            const uint32_t p01 = prmt(nib, 0x43434343u, 0x4140u), p23 = prmt(nib, 0x43434343u, 0x4342u);
-                            o[2 * i] = bfma2(bsub2(p01, 0x43004300u), av[hs], bv[hs]);
-                            o[2 * i + 1] = bfma2(bsub2(p23, 0x43004300u), av[hs], bv[hs]);
+                    for (int hs = 0; hs < 2; hs++) {
+                        const int jj4 = 2 * p + hs;
+                        int sc, mn;
+                        if (jj4 < 4) {
+                            sc = (h4.y >> (8 * jj4)) & 63;
+                            mn = (h4.z >> (8 * jj4)) & 63;
+                        } else {
+                            const int jj = jj4 - 4;
+                            sc = ((h4.w >> (8 * jj)) & 0xF) | (((h4.y >> (8 * jj + 6)) & 3) << 4);
+                            mn = ((h4.w >> (8 * jj + 4)) & 0xF) | (((h4.z >> (8 * jj + 6)) & 3) << 4);
                         }
-                        *reinterpret_cast<uint4 *>(arow + (((c + 4 * hs) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        av[hs] = bf2(d * (float)sc);
+                        bv[hs] = bf2(-dmin * (float)mn);
+                    }
+                    const uint32_t w[8] = {qa[j][sub].x, qa[j][sub].y, qa[j][sub].z, qa[j][sub].w,
+                                           qb[j][sub].x, qb[j][sub].y, qb[j][sub].z, qb[j][sub].w};
+                    uint8_t *arow = smem + (size_t)s * stage_bytes + j * a_tile + sub * kATile + r * 128;
+#pragma unroll
+                    for (int hs = 0; hs < 2; hs++) {
+                        if (my_hs >= 0 && hs != my_hs) continue;
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {   // 16-byte pieces (eight columns), XOR-swizzled by the row inside its 8-row group
+                            uint32_t o[4];
+#pragma unroll
+                            for (int i = 0; i < 2; i++) {
+                                // four codes of this nibble half, then each next to the byte 0x43: bf16 128+q
+                                const uint32_t wv = w[2 * c + i];
+                                const uint32_t nib = hs ? (wv >> 4) & 0x0F0F0F0Fu : wv & 0x0F0F0F0Fu;
+                                const uint32_t p01 = prmt(nib, 0x43434343u, 0x4140u), p23 = prmt(nib, 0x43434343u, 0x4342u);
+                                o[2 * i] = bfma2(bsub2(p01, 0x43004300u), av[hs], bv[hs]);
+                                o[2 * i + 1] = bfma2(bsub2(p23, 0x43004300u), av[hs], bv[hs]);
+                            }
+                            *reinterpret_cast<uint4 *>(arow + (((c + 4 * hs) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
                     }
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
             __syncwarp();
             if (lane == 0) mbar_arrive(full_a + 8 * s);   // one arrival per warp: 128 arrivals on one barrier serialize
+            if (kc + kGroups < nk) load_stage(kc + kGroups);
         }
         // ---- epilogue: accumulator row r holds C[m0..m0+BN)[n0+r] -------------------------------------
         if (ok && mbar_wait_bounded(tmem_full, 0u)) {
@@ -360,8 +361,15 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
 }
 
 extern "C" __global__ void __launch_bounds__(576, 1) qm_gemm_q4k_bf16(const __grid_constant__ QmGemmArgs a) {
-    gemm_body<1>(a);
+    gemm_body<1, 1>(a);
 }
 extern "C" __global__ void __launch_bounds__(576, 1) qm_gemm_q4k_bf16_r256(const __grid_constant__ QmGemmArgs a) {
-    gemm_body<2>(a);
+    gemm_body<2, 1>(a);
+}
+// Two 64-column chunks per stage (small token tiles).
+extern "C" __global__ void __launch_bounds__(576, 1) qm_gemm_q4k_bf16_k128(const __grid_constant__ QmGemmArgs a) {
+    gemm_body<1, 2>(a);
+}
+extern "C" __global__ void __launch_bounds__(576, 1) qm_gemm_q4k_bf16_r256_k128(const __grid_constant__ QmGemmArgs a) {
+    gemm_body<2, 2>(a);
 }

@@ -82,6 +82,7 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_Q4K, "qm_fused_q4k_nt1_img"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2_img"},
     {QM_MOD_Q4K, "qm_fused_q4k_nt1_tp"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2_tp"},
     {QM_MOD_GEMM, "qm_gemm_q4k_bf16"}, {QM_MOD_GEMM, "qm_gemm_q4k_bf16_r256"},
+    {QM_MOD_GEMM, "qm_gemm_q4k_bf16_k128"}, {QM_MOD_GEMM, "qm_gemm_q4k_bf16_r256_k128"},
     {QM_MOD_MOE, "qm_moe_route"},      {QM_MOD_MOE, "qm_moe_lists"},      {QM_MOD_MOE, "qm_moe_gather"},
     {QM_MOD_MOE, "qm_moe_swiglu"},     {QM_MOD_MOE, "qm_moe_combine"},
 };
@@ -169,8 +170,8 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
         }
         if (!err) {
             r = d->cuFuncSetAttribute(c->fn[QM_K_GEMM_Q4K], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
-            if (r == CUDA_SUCCESS)
-                r = d->cuFuncSetAttribute(c->fn[QM_K_GEMM_Q4K_R256], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
+            for (int k = QM_K_GEMM_Q4K_R256; k <= QM_K_GEMM_Q4K_R256_K128 && r == CUDA_SUCCESS; k++)
+                r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
         for (int k = QM_K_GEMV_Q40_M4; k <= QM_K_GEMV_Q80_M8 && !err; k++) {
@@ -829,8 +830,13 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     const int nsub = r256 ? 2 : 1;
     const int mt = g.m_typical > 0 ? g.m_typical : m;
     const int bn = mt <= 64 ? 64 : mt <= 128 ? 128 : (mt <= 256 || r256) ? 256 : 512;
-    const int stage_bytes = nsub * 128 * 64 * 2 + bn * 64 * 2;
+    // Two 64-column chunks per stage where at least two such stages fit and the token tile is
+    // small: the handshake of a stage costs ~0.3 us, more than the MMAs of one small chunk.
+    const int chunk_bytes = nsub * 128 * 64 * 2 + bn * 64 * 2;
+    const int ks = env_int("QM_GEMM_KS", (bn <= 256 && (QM_GEMV_SMEM_MAX - 2048) / (2 * chunk_bytes) >= 2) ? 2 : 1) == 2 ? 2 : 1;
+    const int stage_bytes = ks * chunk_bytes;
     const int stages = std::max(2, std::min(8, (QM_GEMV_SMEM_MAX - 2048) / stage_bytes));
+    if (stages * stage_bytes + 2048 > QM_GEMV_SMEM_MAX) return QM_ERR_SHAPE;
     const cuuint64_t dims[2] = {(cuuint64_t)w->cols, (cuuint64_t)rows_total};
     const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
     const cuuint32_t box[2] = {64, (cuuint32_t)std::min(bn, 256)};
@@ -883,7 +889,8 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     cfg.blockDimY = cfg.blockDimZ = 1;
     cfg.sharedMemBytes = smem;
     cfg.hStream = c->stream;
-    DRV(c->drv->cuLaunchKernelEx(&cfg, c->fn[r256 ? QM_K_GEMM_Q4K_R256 : QM_K_GEMM_Q4K], params, nullptr));
+    const int kern = ks == 2 ? (r256 ? QM_K_GEMM_Q4K_R256_K128 : QM_K_GEMM_Q4K_K128) : (r256 ? QM_K_GEMM_Q4K_R256 : QM_K_GEMM_Q4K);
+    DRV(c->drv->cuLaunchKernelEx(&cfg, c->fn[kern], params, nullptr));
     c->launches++;
     return QM_OK;
 }

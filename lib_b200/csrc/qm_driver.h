@@ -50,6 +50,8 @@
     X(cuIpcGetMemHandle, CUresult (*)(CUipcMemHandle *, CUdeviceptr))                             \
     X(cuIpcOpenMemHandle_v2, CUresult (*)(CUdeviceptr *, CUipcMemHandle, unsigned int))           \
     X(cuIpcCloseMemHandle, CUresult (*)(CUdeviceptr))                                             \
+    X(cuPointerGetAttribute, CUresult (*)(void *, CUpointer_attribute, CUdeviceptr))              \
+    X(cuDeviceGetP2PAttribute, CUresult (*)(int *, CUdevice_P2PAttribute, CUdevice, CUdevice))    \
     X(cuTensorMapEncodeTiled,                                                                     \
       CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,    \
                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,                    \

@@ -401,6 +401,28 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     // barriers, and runs to the end.
     bool dead = false;   // meaningful in thread 0
     auto grid_sync = [&]() {
+        if (TP && a.tp_counter) {
+            // Counter form: every CTA adds its arrival to the counter word of every GPU's arena
+            // (its own included) and waits until its own counter has seen all CTAs of all GPUs.
+            // The count grows from launch to launch; the comparison is wrap-safe.
+            if (tid == 0) {
+                __threadfence_system();
+                unsigned int *cnt = a.tp_flags + 32;
+                for (int p = 0; p < a.tp_world; p++)
+                    red_add_release_sys(reinterpret_cast<unsigned int *>(reinterpret_cast<char *>(cnt) + a.peer_delta[p]), 1u);
+                const unsigned int target = a.tp_epoch0 + (nbar + 1) * gridDim.x * (unsigned int)a.tp_world;
+                const long long t0 = clock64();
+                while (!dead && (int)(ld_acquire_sys(cnt) - target) < 0) {
+                    if (clock64() - t0 > 4000000000ll) {
+                        atomicOr(a.status, QM_STATUS_TIMEOUT);
+                        dead = true;
+                    }
+                }
+            }
+            nbar++;
+            __syncthreads();
+            return;
+        }
         if (tid == 0) {
             if (TP) __threadfence_system(); else __threadfence();
             const unsigned int target = (nbar + 1) * gridDim.x;

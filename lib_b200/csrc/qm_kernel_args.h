@@ -102,7 +102,7 @@ struct QmFusedArgs {
     // flags of all peers in its own arena.
     int32_t tp_world, tp_rank;       // tp_world <= 1: single GPU
     unsigned int tp_epoch0;          // epoch of the launch's first barrier minus one; grows from launch to launch
-    unsigned int tp_pad;
+    unsigned int tp_counter;         // 1: every CTA adds its arrival to a counter in every arena (NVLink atomics); 0: flags
     unsigned int *tp_flags;          // [tp_world] in this GPU's arena, written by the peers
     int64_t peer_delta[QM_MAX_PEERS];   // bytes from an address in this arena to the same place in peer p's
 };

@@ -58,4 +58,8 @@ __device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) 
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ void red_add_release_sys(unsigned int *p, unsigned int v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 }  // namespace qm

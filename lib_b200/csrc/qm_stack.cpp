@@ -40,6 +40,7 @@ struct qm_stack {
     size_t arena_bytes, flags_off;
     CUdeviceptr peer_base[QM_MAX_PEERS];
     bool peers_open;
+    bool tp_counter;            // peers reachable with native NVLink atomics: counter barrier
     unsigned int tp_epoch;
     bool use_graph, use_fused;
 };
@@ -158,6 +159,20 @@ extern "C" int32_t qm_stack_set_peers(qm_ctx *c, qm_stack *s, const void *handle
             memset(s->peer_base, 0, sizeof s->peer_base);
             return (int32_t)r;
         }
+    }
+    // Counter barrier if every peer takes native atomics from this GPU (NVLink), else flags.
+    s->tp_counter = qm_env_int("QM_TP_BARRIER_FLAGS", 0) == 0;
+    CUdevice me = 0;
+    if (c->drv->cuDeviceGet(&me, c->device) != CUDA_SUCCESS) s->tp_counter = false;
+    for (int p = 0; p < s->tp_world && s->tp_counter; p++) {
+        if (p == s->tp_rank) continue;
+        int ordinal = -1, native = 0;
+        CUdevice peer = 0;
+        if (c->drv->cuPointerGetAttribute(&ordinal, CU_POINTER_ATTRIBUTE_DEVICE_ORDINAL, s->peer_base[p]) != CUDA_SUCCESS ||
+            c->drv->cuDeviceGet(&peer, ordinal) != CUDA_SUCCESS ||
+            c->drv->cuDeviceGetP2PAttribute(&native, CU_DEVICE_P2P_ATTRIBUTE_NATIVE_ATOMIC_SUPPORTED, me, peer) != CUDA_SUCCESS ||
+            !native)
+            s->tp_counter = false;
     }
     s->peers_open = true;
     return QM_OK;
@@ -378,7 +393,9 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
         a.tp_world = s->tp_world;
         a.tp_rank = s->tp_rank;
         a.tp_epoch0 = s->tp_epoch;
-        s->tp_epoch += (unsigned int)a.nops;   // nops - 1 barriers between the ops and one at the end
+        a.tp_counter = s->tp_counter ? 1u : 0u;
+        // nops - 1 barriers between the ops and one at the end; the counter form counts CTA arrivals
+        s->tp_epoch += (unsigned int)a.nops * (s->tp_counter ? (unsigned int)(qm_fused_grid(c) * s->tp_world) : 1u);
         a.tp_flags = (unsigned int *)(uintptr_t)(s->arena + s->flags_off);
         for (int q = 0; q < s->tp_world; q++) a.peer_delta[q] = (int64_t)s->peer_base[q] - (int64_t)s->arena;
         return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1_TP : QM_K_FUSED_Q4K_NT2_TP, (unsigned)qm_fused_grid(c),

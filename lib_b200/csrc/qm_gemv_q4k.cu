@@ -400,8 +400,9 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     // about two seconds the CTA records QM_STATUS_TIMEOUT, stops waiting at this and all later
     // barriers, and runs to the end.
     bool dead = false;   // meaningful in thread 0
-    auto grid_sync = [&]() {
-        if (TP && a.tp_counter) {
+    unsigned int nloc = 0, ncross = 0;   // barriers so far on the local counter / over all GPUs
+    auto grid_sync = [&](bool cross) {
+        if (TP && cross && a.tp_counter) {
             // Counter form: every CTA adds its arrival to the counter word of every GPU's arena
             // (its own included) and waits until its own counter has seen all CTAs of all GPUs.
             // The count grows from launch to launch; the comparison is wrap-safe.
@@ -410,7 +411,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 unsigned int *cnt = a.tp_flags + 32;
                 for (int p = 0; p < a.tp_world; p++)
                     red_add_release_sys(reinterpret_cast<unsigned int *>(reinterpret_cast<char *>(cnt) + a.peer_delta[p]), 1u);
-                const unsigned int target = a.tp_epoch0 + (nbar + 1) * gridDim.x * (unsigned int)a.tp_world;
+                const unsigned int target = a.tp_epoch0 + (ncross + 1) * gridDim.x * (unsigned int)a.tp_world;
                 const long long t0 = clock64();
                 while (!dead && (int)(ld_acquire_sys(cnt) - target) < 0) {
                     if (clock64() - t0 > 4000000000ll) {
@@ -419,16 +420,16 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                     }
                 }
             }
-            nbar++;
+            ncross++;
             __syncthreads();
             return;
         }
         if (tid == 0) {
-            if (TP) __threadfence_system(); else __threadfence();
-            const unsigned int target = (nbar + 1) * gridDim.x;
+            if (TP && cross) __threadfence_system(); else __threadfence();
+            const unsigned int target = (nloc + 1) * gridDim.x;
             const unsigned int old = atomicAdd(a.grid_bar, 1u);
-            const unsigned int epoch = a.tp_epoch0 + nbar + 1;
-            if (TP && old + 1 == target) {   // this GPU's slice is complete: tell the peers
+            const unsigned int epoch = a.tp_epoch0 + ncross + 1;
+            if (TP && cross && old + 1 == target) {   // this GPU's slice is complete: tell the peers
                 __threadfence_system();
                 for (int p = 0; p < a.tp_world; p++)
                     if (p != a.tp_rank)
@@ -442,7 +443,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                     dead = true;
                 }
             }
-            if (TP) {
+            if (TP && cross) {
                 for (int p = 0; p < a.tp_world; p++) {
                     if (p == a.tp_rank) continue;
                     while (!dead && (int)(ld_acquire_sys(a.tp_flags + p) - epoch) < 0) {
@@ -454,13 +455,15 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 }
             }
         }
-        nbar++;
+        nloc++;
+        if (TP && cross) ncross++;
         __syncthreads();
     };
-    // Stores a finished output, tensor-parallel also into every peer's arena.
+    // Stores a finished output; for an op that is shared between the GPUs also into every peer's arena.
+    bool share_cur = false;
     auto store_y = [&](float *yp, float val) {
         *yp = val;
-        if (TP) {
+        if (TP && share_cur) {
             for (int p = 0; p < a.tp_world; p++)
                 if (p != a.tp_rank) *reinterpret_cast<float *>(reinterpret_cast<char *>(yp) + a.peer_delta[p]) = val;
         }
@@ -474,8 +477,10 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         // ---- wait for the producers of x, and for this CTA's readers of the old planes --------
         if (opi > 0) {
             __syncthreads();
-            if (op.barrier) grid_sync();
+            // the barrier spans the GPUs when the op before this one was shared between them
+            if (op.barrier) grid_sync(TP && (ops + opi - 1)->tp_shared != 0);
         }
+        share_cur = TP && op.tp_shared != 0;
         QM_MARK(1);
         // ---- quantize the activations of this op into limbs, once per CTA ---------------------
         // Tiles of the NEXT op that this CTA will share with a neighbour are added to with
@@ -845,7 +850,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     // so that the host may read the outputs and the next launch may overwrite the inputs.
     if (TP) {
         __syncthreads();
-        grid_sync();
+        grid_sync(true);
     }
 }
 

@@ -71,7 +71,9 @@ struct QmOp {
     // way, so two CTAs may share a tile; both add their part to y with red.global.add (two
     // addends on a zero: order-independent), and y's shared tiles are zeroed during the op before
     int32_t q, rem;
-    int32_t balanced, pad;
+    int32_t balanced;
+    int32_t tp_shared;   // tensor-parallel launch: 1 = this op computes a row slice and stores it into every GPU's arena
+                         // (a barrier over all GPUs follows); 0 = every GPU computes the whole op for itself
     // Activation image: the quantized form of an op's x (limb planes, sub-block sums, column
     // weights, sums of squares per unit) in global memory. An op whose x is the previous op's y
     // can read it ready-made instead of every CTA quantizing all of x: the previous op builds

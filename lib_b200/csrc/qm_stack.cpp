@@ -28,6 +28,7 @@ struct qm_stack {
     CUdeviceptr ops_dev[9];     // fused op lists, one per batch size
     QmFusedPlan fused_plan[9];
     int fused_nops[9];          // ops in the list (a matrix whose K does not fit is several ops)
+    int fused_ncross[9];        // barriers over all GPUs in one tensor-parallel launch
     CUdeviceptr img_dev[9];     // two activation images per batch size, used alternately
     CUdeviceptr sync_dev[9];    // grid barrier word (first 256 bytes), then the unit counters
     size_t sync_bytes[9];
@@ -56,7 +57,7 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
         return QM_ERR_SHAPE;
     if ((hidden & 3) || (kv_dim & 3) || (ffn & 3)) return QM_ERR_SHAPE;
     if (world < 1 || world > QM_MAX_PEERS || rank < 0 || rank >= world) return QM_ERR_ARG;
-    if (world > 1 && (((hidden + 2 * kv_dim) % (16 * world)) || (hidden % (16 * world)) || ((2 * ffn) % (16 * world))))
+    if (world > 1 && ((hidden % (16 * world)) || ((2 * ffn) % (16 * world))))
         return QM_ERR_SHAPE;   // every GPU's row slice must be whole 16-row tiles
     qm_stack *s = new (std::nothrow) qm_stack();
     if (!s) return QM_ERR_NOMEM;
@@ -118,8 +119,9 @@ extern "C" int32_t qm_stack_create(qm_ctx *c, int32_t layers, int32_t hidden, in
     return stack_create(c, layers, hidden, kv_dim, ffn, m_max, 0, 1, out);
 }
 
-// Tensor-parallel stack: rank `rank` of `world` GPUs of one box. Every matrix handed to
-// qm_stack_set_layer holds this rank's slice of the rows, rows [rank*R/world, (rank+1)*R/world).
+// Tensor-parallel stack: rank `rank` of `world` GPUs of one box. The gate|up and down matrices
+// handed to qm_stack_set_layer hold this rank's slice of the rows, rows
+// [rank*R/world, (rank+1)*R/world); q|k|v and o are whole on every rank.
 extern "C" int32_t qm_stack_create_tp(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
                                       int32_t m_max, int32_t rank, int32_t world, qm_stack **out) {
     return stack_create(c, layers, hidden, kv_dim, ffn, m_max, rank, world, out);
@@ -213,8 +215,9 @@ extern "C" int32_t qm_stack_set_layer(qm_ctx *c, qm_stack *s, int32_t layer, qm_
                       qm_weight_from_handle(down)};
     for (QmWeight *p : w)
         if (!p) return QM_ERR_ARG;
-    const int64_t W = s->tp_world;   // tensor-parallel: this rank's slice of the rows
-    const int64_t want[4][2] = {{(s->hidden + 2 * s->kv) / W, s->hidden}, {s->hidden / W, s->hidden},
+    // tensor-parallel: q|k|v and o whole on every rank, gate|up and down this rank's slice of the rows
+    const int64_t W = s->tp_world;
+    const int64_t want[4][2] = {{s->hidden + 2 * s->kv, s->hidden}, {s->hidden, s->hidden},
                                 {2 * s->ffn / W, s->hidden}, {s->hidden / W, s->ffn}};
     for (int i = 0; i < 4; i++)
         if (w[i]->rows != want[i][0] || w[i]->cols != want[i][1]) return QM_ERR_SHAPE;
@@ -283,7 +286,7 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     std::vector<QmOp> ops;
     std::vector<int> group_first, group_last;
     auto add_matvec = [&](const QmWeight *w, CUdeviceptr x, CUdeviceptr x2, int64_t ldx, CUdeviceptr y, int64_t ldy,
-                          uint32_t xop, bool first) {
+                          uint32_t xop, bool first, bool shared) {
         const int nslices = (w->units + p.max_units - 1) / p.max_units;
         const int ups = (w->units + nslices - 1) / nslices;
         group_first.push_back((int)ops.size());
@@ -291,6 +294,7 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
             QmOp op;
             const int u0 = sl * ups, n = std::min(ups, (int)w->units - u0);
             qm_fill_op(c, p, w, x, x2, ldx, y, ldy, xop, !(first && sl == 0), u0, n, sl > 0, &op);
+            op.tp_shared = shared ? 1 : 0;
             ops.push_back(op);
         }
         group_last.push_back((int)ops.size() - 1);
@@ -299,21 +303,26 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     for (int L = 0; L < s->layers; L++) {
         const QmLayer &ly = s->layer[L];
         const CUdeviceptr qkv = s->qkv_out + (size_t)L * m * qkv_ld * 4;
-        // tensor-parallel: y points at this rank's rows of the full-width output
+        // Tensor-parallel: the two large matrices (gate|up, down: 81 % of the bytes) are shared — y
+        // points at this rank's rows of the full-width output; q|k|v and o are computed whole by
+        // every GPU, which costs less than the barrier over the GPUs that sharing them would add.
+        const bool tp = s->tp_world > 1;
         const size_t R = (size_t)s->tp_rank * 4;
-        add_matvec(ly.qkv, L == 0 ? s->h0 : s->dn_out, 0, s->hidden, qkv + R * ly.qkv->rows, qkv_ld, QM_XOP_RMSNORM,
-                   L == 0);
-        add_matvec(ly.o, qkv, 0, qkv_ld, s->o_out + R * ly.o->rows, s->hidden, QM_XOP_RMSNORM, false);
-        add_matvec(ly.gu, s->o_out, 0, s->hidden, s->gu_out + R * ly.gu->rows, 2 * s->ffn, QM_XOP_RMSNORM, false);
+        add_matvec(ly.qkv, L == 0 ? s->h0 : s->dn_out, 0, s->hidden, qkv, qkv_ld, QM_XOP_RMSNORM, L == 0, false);
+        add_matvec(ly.o, qkv, 0, qkv_ld, s->o_out, s->hidden, QM_XOP_RMSNORM, false, false);
+        add_matvec(ly.gu, s->o_out, 0, s->hidden, s->gu_out + R * ly.gu->rows, 2 * s->ffn, QM_XOP_RMSNORM, false, tp);
         add_matvec(ly.dn, s->gu_out, s->gu_out + (size_t)s->ffn * 4, 2 * s->ffn, s->dn_out + R * ly.dn->rows,
-                   s->hidden, QM_XOP_ADD_RMSNORM, false);
+                   s->hidden, QM_XOP_ADD_RMSNORM, false, tp);
     }
     for (const QmOp &op : ops)
         if ((int64_t)op.tiles * op.units >= (1ll << 31)) return QM_ERR_SHAPE;
     // every unsliced op but the first writes a buffer that the op before it does not touch
-    // (tensor-parallel ops keep whole tiles per CTA: their outputs are plain stores to every GPU)
-    for (size_t k = 1; k < ops.size() && s->tp_world == 1; k++)
-        if (ops[k].units == ops[k].units_total) qm_balance_op(c, &ops[k]);
+    // (ops shared between GPUs keep whole tiles per CTA: their outputs are plain stores to every GPU)
+    for (size_t k = 1; k < ops.size(); k++)
+        if (ops[k].units == ops[k].units_total && !ops[k].tp_shared) qm_balance_op(c, &ops[k]);
+    // barriers over all GPUs in one launch: after every shared op, and the one that ends the launch
+    int ncross = 1;
+    for (size_t k = 1; k < ops.size(); k++) ncross += ops[k - 1].tp_shared && ops[k].barrier ? 1 : 0;
 
     // Activation images: the last op of a matrix quantizes the next matrix's x as its outputs
     // complete, so that the CTAs of the next op copy the quantized form instead of each
@@ -365,6 +374,7 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     s->sync_bytes[m] = sync_bytes;
     s->img_units[m] = img_units;
     s->fused_nops[m] = (int)ops.size();
+    s->fused_ncross[m] = ncross;
     s->fused_img[m] = uses_img;
     s->fused_plan[m] = p;
     return QM_OK;
@@ -394,8 +404,8 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
         a.tp_rank = s->tp_rank;
         a.tp_epoch0 = s->tp_epoch;
         a.tp_counter = s->tp_counter ? 1u : 0u;
-        // nops - 1 barriers between the ops and one at the end; the counter form counts CTA arrivals
-        s->tp_epoch += (unsigned int)a.nops * (s->tp_counter ? (unsigned int)(qm_fused_grid(c) * s->tp_world) : 1u);
+        // the epoch counts the launch's barriers over all GPUs; the counter form counts CTA arrivals
+        s->tp_epoch += (unsigned int)s->fused_ncross[m] * (s->tp_counter ? (unsigned int)(qm_fused_grid(c) * s->tp_world) : 1u);
         a.tp_flags = (unsigned int *)(uintptr_t)(s->arena + s->flags_off);
         for (int q = 0; q < s->tp_world; q++) a.peer_delta[q] = (int64_t)s->peer_base[q] - (int64_t)s->arena;
         return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1_TP : QM_K_FUSED_Q4K_NT2_TP, (unsigned)qm_fused_grid(c),
@@ -499,15 +509,12 @@ extern "C" int32_t qm_stack_step_host(qm_ctx *c, qm_stack *s, const float *x_hos
     DRV(d->cuMemcpyDtoHAsync_v2(h_host, s->dn_out, (size_t)m * s->hidden * 4, c->stream));
     if (kv_host && s->kv) {
         const int64_t qkv_ld = s->hidden + 2 * s->kv;
-        // tensor-parallel: only the k|v rows of this rank's slice (a peer's next step may already
-        // be overwriting the others); the rest of kv_host is left untouched
-        const int64_t S = qkv_ld / s->tp_world;
-        const int64_t lo = std::max<int64_t>(s->hidden, s->tp_rank * S), hi = std::min<int64_t>(qkv_ld, (s->tp_rank + 1) * S);
-        for (int L = 0; L < s->layers && lo < hi; L++)
+        // (tensor-parallel: q|k|v is computed whole by every GPU, so all rows are local)
+        for (int L = 0; L < s->layers; L++)
             for (int j = 0; j < m; j++)
-                DRV(d->cuMemcpyDtoHAsync_v2(kv_host + ((size_t)L * m + j) * 2 * s->kv + (lo - s->hidden),
-                                            s->qkv_out + (((size_t)L * m + j) * qkv_ld + lo) * 4,
-                                            (size_t)(hi - lo) * 4, c->stream));
+                DRV(d->cuMemcpyDtoHAsync_v2(kv_host + ((size_t)L * m + j) * 2 * s->kv,
+                                            s->qkv_out + (((size_t)L * m + j) * qkv_ld + s->hidden) * 4,
+                                            (size_t)2 * s->kv * 4, c->stream));
     }
     DRV(d->cuStreamSynchronize(c->stream));
     return QM_OK;

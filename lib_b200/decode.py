@@ -88,9 +88,9 @@ class SingleGpuDecode:
 
 class PeerTensorParallelDecode:
     """Row-sharded decode step as ONE persistent launch per GPU (qm_stack_create_tp): rank r
-    holds rows [r*N/g, (r+1)*N/g) of every stacked matrix and stores its slice of every
-    matvec straight into all peers' activation buffers over NVLink; the barrier between
-    dependent matvecs spans the GPUs. torch.distributed only carries the 64-byte IPC handles
+    holds rows [r*N/g, (r+1)*N/g) of gate|up and down (q|k|v and o whole) and stores its slice
+    of those matvecs straight into all peers' activation buffers over NVLink; the barrier after
+    a shared matvec spans the GPUs. torch.distributed only carries the 64-byte IPC handles
     at set-up."""
 
     def __init__(self, ctx, layers, hidden, kv, ffn, fmt, seed, rank, world, m_max=8, barrier=True):
@@ -101,8 +101,9 @@ class PeerTensorParallelDecode:
         self.stack = _capi.Stack(ctx, layers, hidden, kv, ffn, m_max, rank, world)
         for L in range(layers):
             ws = []
-            for rows, cols, parts in stacked(layer_tensors(fmt, hidden, kv, ffn, seed, L)):
-                lo, hi = shard_range(rows, rank, world)
+            for i, (rows, cols, parts) in enumerate(stacked(layer_tensors(fmt, hidden, kv, ffn, seed, L))):
+                # q|k|v and o whole on every rank; gate|up and down sliced by rows
+                lo, hi = (0, rows) if i < 2 else shard_range(rows, rank, world)
                 ws.append(upload_rows(ctx, fmt, rows, cols, parts, lo, hi))
             self.stack.set_layer(L, *ws)
         handles = [None] * world

@@ -338,11 +338,12 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     CUresult r = c->drv->cuMemAlloc_v2(&img, 2 * img_stride);
     if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&sync, sync_bytes);
     if (r == CUDA_SUCCESS) r = c->drv->cuMemsetD8Async(img, 0, 2 * img_stride, c->stream);
-    // With one or two activation rows the per-CTA quantization is cheaper than the producers'
-    // fences and counters (measured per step, batch 1: 1.83 ms against 2.30 ms; batch 2: 2.09 ms
-    // against 2.33 ms); beyond that the image wins (batch 4: 2.46 ms; batch 8: 3.52 ms against 5.93 ms).
+    // With up to three activation rows the per-CTA quantization is as cheap as or cheaper than the
+    // producers' fences and counters (measured per step, batch 1: 1.83 ms against 2.30 ms; batch 2:
+    // 2.09 against 2.33; batch 3: 2.34 against 2.37); from four rows on the image wins (batch 4:
+    // 2.46 ms against 2.63 ms; batch 8: 3.52 ms against 5.93 ms).
     bool uses_img = false;
-    const int min_m = qm_env_int("QM_IMAGE_MIN_M", 3), min_units = qm_env_int("QM_IMAGE_MIN_UNITS", 1 << 30);
+    const int min_m = qm_env_int("QM_IMAGE_MIN_M", 4), min_units = qm_env_int("QM_IMAGE_MIN_UNITS", 1 << 30);
     if (r == CUDA_SUCCESS && !qm_env_int("QM_NO_IMAGE", 0) && s->tp_world == 1) {
         for (size_t k = 0; k + 1 < ngroups; k++) {
             QmOp &prod = ops[group_last[k]];

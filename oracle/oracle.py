@@ -14,8 +14,8 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libqm_oracle.so")
 
-Q4_0, Q8_0, Q2_K, Q4_K = 2, 8, 10, 12
-BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q2_K: (256, 84), Q4_K: (256, 144)}
+Q4_0, Q8_0, Q2_K, Q4_K, IQ2_XXS = 2, 8, 10, 12, 16
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q2_K: (256, 84), Q4_K: (256, 144), IQ2_XXS: (256, 66)}
 
 
 class OracleError(ValueError):
@@ -23,8 +23,8 @@ class OracleError(ValueError):
 
 
 def _load():
-    if not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(
-            os.path.join(_HERE, "qm_oracle.c")):
+    if not os.path.exists(_SO) or os.path.getmtime(_SO) < max(
+            os.path.getmtime(os.path.join(_HERE, f)) for f in ("qm_oracle.c", "iq2xxs_grid.h")):
         subprocess.check_call(["make", "-C", _HERE, "libqm_oracle.so"],
                               stdout=subprocess.DEVNULL)
     lib = ctypes.CDLL(_SO)
@@ -89,6 +89,11 @@ def DequantizeQ2_K(data, n):
 
 def DequantizeQ4_K(data, n):
     return Dequantize(Q4_K, data, n)
+
+
+def DequantizeIQ2_XXS(data, n):
+    """lm/quant/kquant.go:87."""
+    return Dequantize(IQ2_XXS, data, n)
 
 
 def TensorBytes(type_id, dims):

@@ -44,6 +44,7 @@ def ds4_golden():
         "q2k_raw": bytes.fromhex(g["q2k_raw"]),
         "iq2_raw": bytes.fromhex(g["iq2_raw"]),
         "q2k": np.array([np.float32(v) for v in g["q2k"]], dtype=np.float32),
+        "iq2": np.array([np.float32(v) for v in g["iq2"]], dtype=np.float32),
     }
 
 

@@ -1,7 +1,7 @@
 """Generates the committed fixtures of tests/golden/ from the reference checkout.
 
 Run in a container that has the reference mounted:
-    python tests/golden/make_golden.py [path of the reference checkout]
+    python tests/golden/make_golden.py <path of the reference checkout>
 Writes
   ds4_superblocks.json  the two pseudorandom super-blocks and the 2x256 expected
                         values of lm/quant/testdata/ds4_golden.txt, after checking
@@ -38,10 +38,13 @@ def parse(text):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit(__doc__)
+    ref = sys.argv[1]
     txt = open(os.path.join(ref, "lm/quant/testdata/ds4_golden.txt")).read()
     gold = parse(txt)
-    subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "ref"], stdout=subprocess.DEVNULL)
+    subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "ref", "REFERENCE=" + ref],
+                          stdout=subprocess.DEVNULL)
     regenerated = subprocess.check_output([os.path.join(ROOT, "oracle/_ref/ds4_golden")], text=True)
     assert parse(regenerated) == gold, "the reference generator no longer reproduces its golden file"
     gold["source"] = "lm/quant/testdata/ds4_golden.txt (values as decimal strings, parsed as float32)"

@@ -71,11 +71,11 @@ def test_q2_k_layout():
 
 
 @pytest.mark.parametrize("fn,blk,n_partial", [
-    (quant.DequantizeQ2_K, 84, 128), (quant.DequantizeQ4_K, 144, 128),
+    (quant.DequantizeQ2_K, 84, 128), (quant.DequantizeQ4_K, 144, 128), (quant.DequantizeIQ2_XXS, 66, 128),
     (quant.DequantizeQ4_0, 18, 16), (quant.DequantizeQ8_0, 34, 16)])
 def test_error_paths(fn, blk, n_partial):
     # lm/quant/kquant_test.go:181-202
-    full = 256 if blk in (84, 144) else 32
+    full = 256 if blk in (84, 144, 66) else 32
     with pytest.raises(quant.OracleError):
         fn(bytes(blk), n_partial)
     with pytest.raises(quant.OracleError):
@@ -103,8 +103,79 @@ def test_float16_known_values_and_exhaustive():
     assert np.all(np.isnan(got[np.isnan(ref)]))
 
 
+def test_iq2_xxs_golden(ds4_golden):
+    # lm/quant/kquant_test.go:95-108 (tolerance 1e-6*(1+|want|) there; the values agree bit for bit)
+    got = quant.DequantizeIQ2_XXS(ds4_golden["iq2_raw"], 256)
+    want = ds4_golden["iq2"]
+    assert np.all(np.abs(got.astype(np.float64) - want) <= 1e-6 * (1 + np.abs(want.astype(np.float64))))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_iq2_xxs_layout():
+    # lm/quant/kquant_test.go:151-179
+    block = bytearray(66)
+    block[0:2] = b"\x00\x3c"
+    plain = quant.DequantizeIQ2_XXS(block, 256)
+    assert np.all(plain == np.float32(0.125 * 8))
+    block[2 + 7] = 0xF0
+    got = quant.DequantizeIQ2_XXS(block, 256)
+    assert got[0] == np.float32(0.125 * 31 * 8)
+    assert got[32] == np.float32(0.125 * 8)
+    # sign index 1 negates element 0 and, through the parity bit, element 7
+    block = bytearray(66)
+    block[0:2] = b"\x00\x3c"
+    block[2 + 4] = 0x01
+    got = quant.DequantizeIQ2_XXS(block, 256)
+    assert list(got[:8]) == [-1.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0, -1.0]
+
+
+GGUFPY = {"Q4_0": (2, 32, 18), "Q8_0": (8, 32, 34), "Q2_K": (10, 256, 84), "Q4_K": (12, 256, 144),
+          "IQ2_XXS": (16, 256, 66)}
+
+
+def _same_bits(a, b):
+    return bool(((a.view(np.uint32) == b.view(np.uint32)) | (np.isnan(a) & np.isnan(b))).all())
+
+
+@pytest.mark.parametrize("name", sorted(GGUFPY))
+def test_oracle_matches_ggufpy_fixture(name):
+    """The committed vectors of the GGUF format's upstream Python decoder (gguf-py): this is what
+    pins Q4_K, for which the reference holds no vector. Bit for bit (NaNs as NaNs)."""
+    fmt, be, bb = GGUFPY[name]
+    fx = json.load(open(os.path.join(ROOT, "tests/golden/ggufpy_vectors.json")))["formats"][name]
+    assert fx
+    for case, v in fx.items():
+        raw = bytes.fromhex(v["raw"])
+        want = np.array(v["bits"], dtype=np.uint32).view(np.float32)
+        with np.errstate(all="ignore"):
+            got = quant.Dequantize(fmt, raw, len(raw) // bb * be)
+        assert _same_bits(got, want), (name, case)
+
+
+@pytest.mark.parametrize("name", sorted(GGUFPY))
+def test_oracle_matches_ggufpy_live(name):
+    """Same comparison against the installed package, on more data: random bytes, the benchmark's
+    seeded tensors (config 3: 4096-wide Q4_K rows) and a patterned block."""
+    gguf = pytest.importorskip("gguf", reason="gguf-py is not installed; the committed fixture still pins the oracle")
+    from gguf import quants
+    from lib_b200 import synth
+    fmt, be, bb = GGUFPY[name]
+    qtype = getattr(gguf.GGMLQuantizationType, name)
+    g = np.random.Generator(np.random.Philox(key=31))
+    raws = [g.integers(0, 256, bb * 256, dtype=np.uint8), (np.arange(bb * 3, dtype=np.uint32) * 37 + 11).astype(np.uint8)]
+    if fmt in synth.BLOCK:
+        raws.append(synth.weights(fmt, 16, 4096, seed=3))
+    for raw in raws:
+        n = raw.size // bb * be
+        with np.errstate(all="ignore"):
+            want = quants.dequantize(raw.reshape(1, -1), qtype).reshape(-1)
+            got = quant.Dequantize(fmt, raw, n)
+        assert _same_bits(got, want), name
+
+
 def test_q4_k_two_decoders_agree():
-    # no reference vector exists for GGUF type 12; two independent decoders must agree bit for bit
+    # a second, independently written numpy decoder must agree bit for bit (the pin itself is the
+    # gguf-py comparison above)
     g = np.random.Generator(np.random.Philox(key=7))
     raw = g.integers(0, 256, 144 * 512, dtype=np.uint8)
     a = quant.DequantizeQ4_K(raw, 256 * 512)

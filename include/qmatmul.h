@@ -38,6 +38,7 @@ extern "C" {
 #define QM_FMT_Q8_0 8  /* lm/quant/quant.go:36-40  BlockQ8_0, 34 bytes / 32 elements  */
 #define QM_FMT_Q2_K 10 /* lm/quant/kquant.go:29-34 BlockQ2_K, 84 bytes / 256 elements */
 #define QM_FMT_Q4_K 12 /* gguf/gguf.go:276         type 12, 144 bytes / 256 elements  */
+#define QM_FMT_IQ2_XXS 16 /* lm/quant/kquant.go:36-40 BlockIQ2_XXS, 66 bytes / 256 elements */
 
 #define QM_OK 0
 #define QM_ERR_COUNT (-1)    /* element count negative or not a multiple of the block (quant.go:45) */
@@ -198,7 +199,8 @@ QM_API int32_t qm_moe_combine(qm_ctx *ctx, uint64_t y_dev, uint64_t pos_dev, uin
  *   x_dev    float32 [m][ldx], 16-byte aligned, ldx a multiple of 4; y_dev float32 [m][ldy]
  *   m        1..8 activation rows
  *   cu_stream  the CUstream to launch on (0 = the default stream); the call does not wait
- * The pointers belong to the current device's primary context. Returns QM_ERR_LIMIT when the
+ * The pointers belong to the current device's primary context, and the current device must be
+ * the one the weights were stored on (QM_ERR_ARG otherwise). Returns QM_ERR_LIMIT when the
  * matrix needs more scratch than the array holds (scratch = 512 bytes per 16-row tile, per K
  * slice, per warp group sharing a tile, plus 4 bytes per tile), QM_ERR_FORMAT for other
  * formats. The first call on a device resolves the array's device address and raises the
@@ -207,6 +209,13 @@ QM_API int32_t qm_moe_combine(qm_ctx *ctx, uint64_t y_dev, uint64_t pos_dev, uin
  * the GPU race on it — order them on one stream or with events. */
 QM_API int32_t qm_matvec_noalloc(qm_weight w, uint64_t x_dev, int32_t m, int64_t ldx, uint64_t y_dev,
                                  int64_t ldy, uint64_t cu_stream);
+/* Status word of the most recent qm_matvec_noalloc on the current device: 0 = clean,
+ * bit 0 = a bounded wait inside the kernel ran out (y is then incomplete; the call returns
+ * QM_ERR_TIMEOUT). The word sits in the same fixed array, so reading it allocates nothing (a
+ * 4-byte device-to-host copy). Synchronize the matvec's stream first, and read before the next
+ * qm_matvec_noalloc on the device, which clears the word. Like qm_matvec_noalloc it has no
+ * counterpart in the reference. */
+QM_API int32_t qm_noalloc_status(uint32_t *status);
 
 /* Decode step over a stack of layers whose matrices are stored weights of one
  * format: per layer q|k|v [hidden+2*kv_dim][hidden], o [hidden][hidden],

@@ -9,7 +9,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.environ.get("QMATMUL_LIB", os.path.join(_HERE, "libqmatmul.so"))
 _HEADER = os.path.join(_HERE, "..", "include", "qmatmul.h")
 
-Q4_0, Q8_0, Q2_K, Q4_K = 2, 8, 10, 12
+Q4_0, Q8_0, Q2_K, Q4_K, IQ2_XXS = 2, 8, 10, 12, 16
 XOP_NONE, XOP_RMSNORM, XOP_ADD_RMSNORM, XOP_SWIGLU = 0, 1, 2, 3
 FLAG_PDL = 0x100
 
@@ -58,6 +58,7 @@ def _load():
         "qm_moe_experts": (i32, [p, p, p, i32, u64, p, u64]),
         "qm_moe_combine": (i32, [p, u64, u64, u64, i32, i32, i32, u64, i64]),
         "qm_matvec_noalloc": (i32, [u64, u64, i32, i64, u64, i64, u64]),
+        "qm_noalloc_status": (i32, [ctypes.POINTER(u32)]),
         "qm_stack_create": (i32, [p, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_stack_destroy": (i32, [p, p]),
         "qm_stack_set_layer": (i32, [p, p, i32, u64, u64, u64, u64]),
@@ -233,6 +234,12 @@ class Context:
     def matvec_noalloc(self, w, x_dev, m, ldx, y_dev, ldy, cu_stream=0):
         """qm_matvec_noalloc: Q4_0/Q8_0 matvec that allocates nothing (fixed scratch array)."""
         _check(lib.qm_matvec_noalloc(w.handle, x_dev, m, ldx, y_dev, ldy, cu_stream), "matvec_noalloc")
+
+    def noalloc_status(self):
+        """qm_noalloc_status: (return code, status word) of the last qm_matvec_noalloc on this device."""
+        s = ctypes.c_uint32(0)
+        rc = lib.qm_noalloc_status(ctypes.byref(s))
+        return rc, s.value
 
     def matvec_host(self, w, x, flags=0, out=None):
         x = np.ascontiguousarray(x, dtype=np.float32)

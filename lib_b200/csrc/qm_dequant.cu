@@ -7,10 +7,13 @@
 //   Q8_0  int8*scale                  lm/quant/quant.go:87
 //   Q2_K  d*(sc&15)*q - dmin*(sc>>4)  lm/quant/kquant.go:66-73
 //   Q4_K  d*sc*q - dmin*m             same form; layout of GGUF type 12
+//   IQ2_XXS (0.125*d*(2s+1))*(+-code) lm/quant/kquant.go:103-118
 // fp16 scales go through an integer restatement of Float16ToFloat32
 // (lm/quant/quant.go:94-116) so that NaN payloads survive unchanged.
 #include <stdint.h>
 
+#define QM_GRID_QUALIFIER __device__ __constant__
+#include "qm_iq2xxs_grid.h"
 #include "qm_kernel_args.h"
 
 namespace {
@@ -108,6 +111,35 @@ extern "C" __global__ void __launch_bounds__(256) qm_dequant_q2k(const __grid_co
         const uint32_t sc = blk[group];
         const float t1 = __fmul_rn(d, (float)(sc & 0x0F)), t3 = __fmul_rn(dmin, (float)(sc >> 4));
         *reinterpret_cast<float4 *>(a.out + row * a.cols + col) = scale4(q4, t1, t3);
+    }
+}
+
+// IQ2_XXS: GGUF bytes unchanged, 66-byte super-blocks (2-byte aligned): d, then eight groups of
+// two little-endian words (four codebook indices | four 7-bit sign indices and the 4-bit scale).
+// Sign index i stands for the byte i | parity(i) << 7; bit j set negates element j.
+extern "C" __global__ void __launch_bounds__(256) qm_dequant_iq2xxs(const __grid_constant__ QmDequantArgs a) {
+    const int64_t ngroups = a.rows * (int64_t)(a.cols / 4);
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < ngroups;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = idx / (a.cols / 4);
+        const int col = (int)(idx - row * (a.cols / 4)) * 4;
+        const int u = col >> 8, e = col & 255, group = e >> 5, l = (e >> 3) & 3, j0 = e & 7;
+        const uint8_t *blk = a.wq + (row * a.units + u) * 66;
+        const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk));
+        const uint16_t *g16 = reinterpret_cast<const uint16_t *>(blk + 2 + 8 * group);
+        const uint32_t indices = (uint32_t)g16[0] | ((uint32_t)g16[1] << 16);
+        const uint32_t aux = (uint32_t)g16[2] | ((uint32_t)g16[3] << 16);
+        const float scale = __fmul_rn(__fmul_rn(0.125f, d), (float)(2u * (aux >> 28) + 1u));
+        const unsigned long long code = QM_IQ2XXS_GRID_INIT[(indices >> (8 * l)) & 0xFFu];
+        const uint32_t si = (aux >> (7 * l)) & 127u;
+        const uint32_t signs = si | ((uint32_t)(__popc(si) & 1) << 7);
+        float o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float v = (float)(uint32_t)((code >> (8 * (j0 + j))) & 0xFFull);
+            o[j] = __fmul_rn(scale, ((signs >> (j0 + j)) & 1u) ? -v : v);
+        }
+        *reinterpret_cast<float4 *>(a.out + row * a.cols + col) = make_float4(o[0], o[1], o[2], o[3]);
     }
 }
 

@@ -90,18 +90,27 @@ __device__ __forceinline__ void cp_async_wait(int n) {
     }
 }
 
+#ifdef QM_DEBUG
 __device__ __forceinline__ unsigned long long gtime() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Debug aid (a.debug == 9): phase timestamps of op a.debug_slot for the first and last CTA.
+#endif
+// Debug builds only (-DQM_DEBUG, a.debug == 9): phase timestamps of op a.debug_slot for the
+// first and last CTA.
+#ifdef QM_DEBUG
 #define QM_MARK(k)                                                                          \
     do {                                                                                    \
         if (a.debug == 9 && lane == 0 && mark_op == a.debug_slot &&                        \
             (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))                               \
             reinterpret_cast<unsigned long long *>(a.status + 16)[((blockIdx.x != 0) * 16 + warp) * 8 + (k)] = gtime(); \
     } while (0)
+#define QM_DEBUG_IS(v) (a.debug == (v))
+#else
+#define QM_MARK(k) do { } while (0)
+#define QM_DEBUG_IS(v) false
+#endif
 
 constexpr int kRowTab = 64;     // bytes of one row of the per-warp scale table
 constexpr int kTabBytes = 16 * kRowTab;
@@ -234,7 +243,9 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     uint8_t *my_stages = stages + (size_t)warp * D * stage_bytes;
     uint8_t *my_tab = tabs + (size_t)warp * kTabBytes;
 
+#ifdef QM_DEBUG
     int mark_op = -1;
+#endif
     asm volatile("griddepcontrol.launch_dependents;");
     // columns of absent activation rows and pad columns must read as zero
     for (int i = tid; i < a.max_units * 8 * NT * 5; i += nthreads) xsum[i] = 0u;   // xsum and sxw are adjacent
@@ -299,7 +310,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
         if (ic.op < a.nops) {
             const uint32_t dst = smem_u32(my_stages + (size_t)islot * stage_bytes) + lane * 16;
             const uint8_t *src = ic.src + lane * 16;
-            if (a.debug != 3) {
+            if (!QM_DEBUG_IS(3)) {
 #pragma unroll
                 for (int k = 0; k < kCopiesPerLane; k++)
                     if (lane + 32 * k < kStageBytes / 16) cp_async16(dst + 512 * k, src + 512 * k);
@@ -329,7 +340,6 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     }
 
     int cslot = 0;
-    unsigned int nbar = 0;
     Cursor cc;
     cursor_at(cc, 0);
 
@@ -414,7 +424,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 const unsigned int target = a.tp_epoch0 + (ncross + 1) * gridDim.x * (unsigned int)a.tp_world;
                 const long long t0 = clock64();
                 while (!dead && (int)(ld_acquire_sys(cnt) - target) < 0) {
-                    if (clock64() - t0 > 4000000000ll) {
+                    if (clock64() - t0 > a.wait_cycles) {
                         atomicOr(a.status, QM_STATUS_TIMEOUT);
                         dead = true;
                     }
@@ -438,7 +448,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
             }
             const long long t0 = clock64();
             while (!dead && ld_acquire(a.grid_bar) < target) {
-                if (clock64() - t0 > 4000000000ll) {
+                if (clock64() - t0 > a.wait_cycles) {
                     atomicOr(a.status, QM_STATUS_TIMEOUT);
                     dead = true;
                 }
@@ -447,7 +457,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
                 for (int p = 0; p < a.tp_world; p++) {
                     if (p == a.tp_rank) continue;
                     while (!dead && (int)(ld_acquire_sys(a.tp_flags + p) - epoch) < 0) {
-                        if (clock64() - t0 > 4000000000ll) {
+                        if (clock64() - t0 > a.wait_cycles) {
                             atomicOr(a.status, QM_STATUS_TIMEOUT);
                             dead = true;
                         }
@@ -471,7 +481,9 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
 
     for (int opi = 0; opi < a.nops; opi++) {
         const QmOp op = ops[opi];   // by value: no reloads through the generic pointer
+#ifdef QM_DEBUG
         mark_op = opi;
+#endif
         QM_MARK(0);
         const int nun = op.units;
         // ---- wait for the producers of x, and for this CTA's readers of the old planes --------
@@ -736,7 +748,7 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
             cp_async_wait(D - 1);
             __syncwarp();
             const uint8_t *stage = my_stages + (size_t)cslot * stage_bytes;
-            if (a.debug == 0 || a.debug == 3) {
+            if (!QM_DEBUG_IS(1)) {   // debug builds: 1 = copies only, no arithmetic
                 const uint8_t *tab = my_tab;
                 build_table(stage, my_tab);
                 __syncwarp();
@@ -854,6 +866,378 @@ __device__ __forceinline__ void fused_body(const QmFusedArgs &a) {
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Data-driven decode step for up to four activation rows (kernels qm_fused_q4k_dd*).
+//
+// Dependent matvecs are not separated by a grid barrier. Every output buffer of the launch
+// holds the "not yet written" pattern when the launch starts (the host fills them), a consumer
+// staging x polls the very words it needs until none of them holds the pattern, and a producer
+// simply stores its results: a value that has arrived is its own flag. The chain
+// store -> fence -> counter -> poll -> load of a barrier becomes store -> load. It needs whole
+// tiles per CTA (no adds from two CTAs into one output), no K slices, and an output buffer of
+// its own for every op.
+//
+// The body is specialised at compile time (sixteen warps, D ring stages, CPM mma columns per
+// activation row) and keeps the per-item instruction count low, because at batch 1 the
+// streaming loop is bound by instruction issue, not by HBM: the scales of a lane's two rows are
+// unpacked in registers (no shared table, no extra warp barriers), sub-blocks in the high
+// nibbles accumulate separately and are divided by 16 once per unit, every lane reads a valid
+// activation plane (columns without an activation row carry a zero column weight instead of a
+// predicate), and the producer side is a pointer and a count.
+// ---------------------------------------------------------------------------------------------
+// Accesses of the hand-over: strong (gpu scope) relaxed loads and stores that go to L2, where
+// every SM sees them.
+__device__ __forceinline__ float4 ld_relaxed_v4(const float *p) {
+    float4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_f32(float *p, float v) {
+    asm volatile("st.relaxed.gpu.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+// "Not yet written": a NaN that no arithmetic here produces (sums of products give the canonical
+// quiet NaN; fp16 scales widen to NaNs whose low 13 bits are zero).
+constexpr uint32_t kUnwritten = 0xFFFFFFFFu;
+__device__ __forceinline__ bool written4(const float4 &v) {
+    return (__float_as_uint(v.x) != kUnwritten) & (__float_as_uint(v.y) != kUnwritten) &
+           (__float_as_uint(v.z) != kUnwritten) & (__float_as_uint(v.w) != kUnwritten);
+}
+template <typename T>
+__device__ __forceinline__ T *ldg_ptr(T *const *p) {   // read-only load of a pointer field
+    return reinterpret_cast<T *>(__ldg(reinterpret_cast<const unsigned long long *>(p)));
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait_n() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int CPM, int D>
+__device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
+    constexpr int C = 16;                       // warps per CTA
+    constexpr int NL = CPM == 4 ? 3 : 2;        // limbs per activation row
+    constexpr int NT = 1;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int M = a.m, P = M * NL;
+    const QmOp *ops = a.ops;   // a device array (this kernel runs op lists, not single matvecs)
+
+    // ---- shared memory (qm_plan_fused computes an upper bound of this) -------------------------
+    const int plane_stride = a.max_units * 256 + 64;
+    uint8_t *xs = smem;                                                            // [P][plane_stride]
+    uint32_t *xsum = reinterpret_cast<uint32_t *>(xs + (size_t)P * plane_stride);   // [units][8][4] f16 pairs
+    float *sxw = reinterpret_cast<float *>(xsum + (size_t)a.max_units * 8 * 4);     // [units][8] column weights
+    float *ssq = sxw + (size_t)a.max_units * 8;                                     // [8][16]
+    float *slots = ssq + 8 * 16;                                                    // [C][2][M*16]
+    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(slots + (size_t)C * 2 * M * 16) + 127) & ~(uintptr_t)127);
+    uint8_t *my_stages = stages + (size_t)warp * D * kStageBytes;
+
+    // columns of absent activation rows and pad columns must read as zero weights and sums
+    for (int i = tid; i < a.max_units * 8 * 5; i += C * 32) xsum[i] = 0u;   // xsum and sxw are adjacent
+    __syncthreads();
+
+    // This warp's items of op `o`: the CTA owns a run of whole tiles, its items are dealt evenly to
+    // the warps in order. Returns the first item and the count in CTA-local coordinates.
+    auto warp_range = [&](int q, int rem, int units, int &tile0, int &lo, int &n, int &wq, int &wrem) {
+        const int c = (int)blockIdx.x;
+        tile0 = c * q + min(c, rem);
+        const int Ic = (q + (c < rem ? 1 : 0)) * units;
+        wq = Ic / C;
+        wrem = Ic - wq * C;
+        lo = warp * wq + min(warp, wrem);
+        n = wq + (warp < wrem ? 1 : 0);
+    };
+
+    // ---- producer side of the ring: a pointer and a count per op -------------------------------
+    int p_op = -1, p_n = 0;
+    const uint8_t *p_src = nullptr;
+    auto p_next_op = [&]() {
+        p_n = 0;
+        for (p_op++; p_op < a.nops; p_op++) {
+            const QmOp *po = ops + p_op;
+            int tile0, lo, n, wq, wrem;
+            const int units = __ldg(&po->units);
+            warp_range(__ldg(&po->q), __ldg(&po->rem), units, tile0, lo, n, wq, wrem);
+            if (n > 0) {
+                p_n = n;
+                p_src = ldg_ptr(&po->wq) + ((int64_t)tile0 * units + lo) * QM_Q4K_ITEM_BYTES + lane * 16;
+                break;
+            }
+        }
+    };
+    const uint32_t ring0 = smem_u32(my_stages) + lane * 16;
+    uint32_t p_dst = ring0;
+    auto issue = [&]() {
+        if (p_n > 0) {
+            cp_async16(p_dst, p_src);
+            cp_async16(p_dst + 512, p_src + 512);
+            cp_async16(p_dst + 1024, p_src + 1024);
+            cp_async16(p_dst + 1536, p_src + 1536);
+            if (lane < 16) cp_async16(p_dst + 2048, p_src + 2048);
+            p_src += QM_Q4K_ITEM_BYTES;
+            if (--p_n == 0) p_next_op();
+        }
+        cp_async_commit();
+        p_dst = p_dst + kStageBytes == ring0 + D * kStageBytes ? ring0 : p_dst + kStageBytes;
+    };
+    p_next_op();
+#pragma unroll
+    for (int d = 0; d < D; d++) issue();
+
+    // mma column n = g holds limb (n % CPM) of activation row (n / CPM); lanes whose column has no
+    // row read plane 0 (their column weight is zero)
+    const int col_row = g / CPM, col_limb = g - col_row * CPM;
+    const bool col_on = col_row < M && col_limb < NL;
+    const uint8_t *bplane = xs + (size_t)(col_on ? col_row * NL + col_limb : 0) * plane_stride + t * 16;
+    // byte selector that brings the minima of sub-blocks 2t and 2t+1 (of the eight in two words)
+    // to the low half of a word
+    const uint32_t min_sel = (uint32_t)(2 * t) | ((uint32_t)(2 * t + 1) << 4) | 0x4400u;
+
+    const uint8_t *c_stage = my_stages;   // consumer slot
+    bool dead = false;
+
+    for (int opi = 0; opi < a.nops; opi++) {
+        const QmOp *po = ops + opi;
+        const int nun = __ldg(&po->units);
+        const int xop = __ldg(&po->xop);
+        const float *opx = ldg_ptr(&po->x), *opx2 = ldg_ptr(&po->x2);
+        const int64_t ldx = __ldg(&po->ldx);
+        const bool norm = xop == 1 || xop == 2;
+        // every warp has finished with the activation planes and the partial sums of the op before
+        if (opi > 0) __syncthreads();
+
+        // ---- stage x: poll until written, quantize into limbs -------------------------------------
+        {
+            constexpr int kRounds = 2;   // (row, unit) pairs of a warp in flight at once
+            const int total = M * nun;
+            const bool poll = __ldg(&po->barrier) != 0;   // x is an earlier op's output
+            float sq_run = 0.f;
+            int sq_j = -1;
+            if (norm && lane < 8) ssq[lane * 16 + warp] = 0.f;
+            __syncwarp();
+            auto load_x = [&](int idx, float4 (&r)[4]) {
+                const int j = idx / nun, ul = idx - j * nun;
+                const float *xp = opx + (int64_t)j * ldx + ul * QM_K_UNIT + lane * 8;
+                r[0] = ld_relaxed_v4(xp);
+                r[1] = ld_relaxed_v4(xp + 4);
+                if (xop >= 2) {
+                    const float *x2p = opx2 + (int64_t)j * ldx + ul * QM_K_UNIT + lane * 8;
+                    r[2] = ld_relaxed_v4(x2p);
+                    r[3] = ld_relaxed_v4(x2p + 4);
+                }
+            };
+            for (int base = warp; base < total; base += kRounds * C) {
+                float4 raw[kRounds][4];
+#pragma unroll
+                for (int r = 0; r < kRounds; r++)
+                    if (base + r * C < total) load_x(base + r * C, raw[r]);
+#pragma unroll
+                for (int r = 0; r < kRounds; r++) {
+                    const int idx = base + r * C;
+                    if (idx >= total) break;
+                    if (poll) {
+                        long long t0 = 0;
+                        for (;;) {
+                            bool ok = written4(raw[r][0]) & written4(raw[r][1]);
+                            if (xop >= 2) ok = ok & written4(raw[r][2]) & written4(raw[r][3]);
+                            if (__all_sync(0xffffffffu, ok || dead)) break;
+                            if (t0 == 0) t0 = clock64();
+                            else if (clock64() - t0 > a.wait_cycles) {
+                                if (lane == 0) atomicOr(a.status, QM_STATUS_TIMEOUT);
+                                dead = true;   // this and every later wait of the thread give up at once
+                            }
+                            load_x(idx, raw[r]);
+                        }
+                    }
+                    const int j = idx / nun, ul = idx - j * nun;
+                    float v[8] = {raw[r][0].x, raw[r][0].y, raw[r][0].z, raw[r][0].w,
+                                  raw[r][1].x, raw[r][1].y, raw[r][1].z, raw[r][1].w};
+                    if (xop >= 2) {
+                        const float w[8] = {raw[r][2].x, raw[r][2].y, raw[r][2].z, raw[r][2].w,
+                                            raw[r][3].x, raw[r][3].y, raw[r][3].z, raw[r][3].w};
+#pragma unroll
+                        for (int e = 0; e < 8; e++)
+                            v[e] = xop == 2 ? v[e] + w[e] : v[e] / (1.f + __expf(-v[e])) * w[e];
+                    }
+                    const float sq = quantize_pair<NT>(v, j, ul, lane, NL, CPM, xs, plane_stride, xsum, sxw);
+                    if (norm) {   // per-warp running sum of squares of activation row j
+                        if (j != sq_j) {
+                            if (sq_j >= 0) {
+#pragma unroll
+                                for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
+                                if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
+                            }
+                            sq_j = j;
+                            sq_run = 0.f;
+                        }
+                        sq_run += sq;
+                    }
+                }
+            }
+            if (sq_j >= 0) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
+                if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
+            }
+        }
+        __syncthreads();
+
+        // RMS normalisation is a scalar per activation row: it multiplies the finished sums
+        float myscale = 1.f;
+        if (norm) {
+            const float inv_cols = 1.f / (float)__ldg(&po->cols), eps = __ldg(&po->eps);
+            for (int j = 0; j < M; j++) {
+                float sq = ssq[j * 16 + (lane & 15)];   // the warps' parts, added as a fixed tree
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                const float sc = rsqrtf(sq * inv_cols + eps);
+                if ((CPM == 4 ? (t >> 1) : t) == j) myscale = sc;
+            }
+        }
+
+        // ---- stream this warp's items of the op ---------------------------------------------------
+        int tile0, lo, n, wq, wrem;
+        warp_range(__ldg(&po->q), __ldg(&po->rem), nun, tile0, lo, n, wq, wrem);
+        float *opy = ldg_ptr(&po->y);
+        const int64_t ldy = __ldg(&po->ldy);
+        const int rows = __ldg(&po->rows);
+        const int hi = lo + n;
+        int fin_tile = -1;   // CTA-local tile this warp adds up after the CTA barrier
+
+        auto store_y = [&](float *yp, float val) {   // a result must never look like "not yet written"
+            if (__float_as_uint(val) == kUnwritten) val = __uint_as_float(0x7FC00000u);
+            st_relaxed_f32(yp, val);
+        };
+        // Ends a tile's segment [s0, s1) of this warp: stores the outputs if the warp had the whole
+        // tile, else leaves its partial sums for the warp that reaches the tile's end.
+        auto flush = [&](int tile, int s0, int s1, const float (&accF)[4]) {
+            float vA = accF[0] + accF[1], vB = accF[2] + accF[3];
+            int jrow;
+            bool valid;
+            if (CPM == 4) {
+                vA += __shfl_xor_sync(0xffffffffu, vA, 1);
+                vB += __shfl_xor_sync(0xffffffffu, vB, 1);
+                jrow = t >> 1;
+                valid = (t & 1) == 0 && jrow < M;
+            } else {
+                jrow = t;
+                valid = jrow < M;
+            }
+            vA *= myscale;
+            vB *= myscale;
+            const bool from_start = s0 == tile * nun, to_end = s1 == tile * nun + nun;
+            if (from_start && to_end) {
+                const int rA = (tile0 + tile) * 16 + g, rB = rA + 8;
+                if (valid) {
+                    float *yA = opy + (int64_t)jrow * ldy + rA;
+                    if (rA < rows) store_y(yA, vA);
+                    if (rB < rows) store_y(yA + 8, vB);
+                }
+                return;
+            }
+            // slot 1: the segment ends inside the tile; slot 0: it joined the tile late and reaches
+            // its end, so this warp adds the tile up after the barrier
+            float *p = slots + ((size_t)warp * 2 + (to_end ? 0 : 1)) * M * 16;
+            if (valid) { p[jrow * 16 + g] = vA; p[jrow * 16 + g + 8] = vB; }
+            if (to_end) fin_tile = tile;
+        };
+
+        const uint8_t *bp = bplane;                 // activation limbs of the current unit
+        const float *cwp = sxw + 2 * t;             // column weights of the current unit
+        const uint32_t *bmp = xsum + g * 4 + t;     // sub-block sums of the current unit
+        for (int i = lo; i < hi;) {
+            const int tile = i / nun, u0 = i - tile * nun;
+            const int seg_end = min(hi, (tile + 1) * nun);
+            float accF[4] = {0.f, 0.f, 0.f, 0.f};
+            bp = bplane + (size_t)u0 * 256;
+            cwp = sxw + (size_t)u0 * 8 + 2 * t;
+            bmp = xsum + (size_t)u0 * 32 + g * 4 + t;
+            for (int k = i; k < seg_end; k++) {
+                cp_async_wait_n<D - 1>();   // the oldest of the D groups in flight is this item
+                __syncwarp();               // ... and every lane's copies of it have landed
+                const uint8_t *stage = c_stage;
+                // ---- scales of this lane's rows g and g+8 -------------------------------------------
+                const uint4 hA = *reinterpret_cast<const uint4 *>(stage + 16 * g);
+                const uint4 hB = *reinterpret_cast<const uint4 *>(stage + 16 * g + 128);
+                const uint32_t scA0 = hA.y & 0x3F3F3F3Fu, scA1 = (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u);
+                const uint32_t scB0 = hB.y & 0x3F3F3F3Fu, scB1 = (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u);
+                const uint32_t mnA0 = hA.z & 0x3F3F3F3Fu, mnA1 = ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u);
+                const uint32_t mnB0 = hB.z & 0x3F3F3F3Fu, mnB1 = ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u);
+                int accL[4] = {0, 0, 0, 0}, accH[4] = {0, 0, 0, 0};   // low-nibble / high-nibble sub-blocks
+                const uint8_t *rowA = stage + 256 + 32 * g + 8 * t;
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    const uint2 wA = *reinterpret_cast<const uint2 *>(rowA + 512 * p);
+                    const uint2 wB = *reinterpret_cast<const uint2 *>(rowA + 512 * p + 256);
+                    const uint4 b = *reinterpret_cast<const uint4 *>(bp + 64 * p);
+                    // sub-block 2p in the low nibbles, 2p+1 in the high ones (left in place: x16)
+                    const int sAl = (int)__byte_perm(p < 2 ? scA0 : scA1, 0, 0x4440 + ((2 * p) & 3));
+                    const int sAh = (int)__byte_perm(p < 2 ? scA0 : scA1, 0, 0x4440 + ((2 * p + 1) & 3));
+                    const int sBl = (int)__byte_perm(p < 2 ? scB0 : scB1, 0, 0x4440 + ((2 * p) & 3));
+                    const int sBh = (int)__byte_perm(p < 2 ? scB0 : scB1, 0, 0x4440 + ((2 * p + 1) & 3));
+                    int S[4];
+                    mma_u8s8(S, wA.x & 0x0F0F0F0Fu, wB.x & 0x0F0F0F0Fu, wA.y & 0x0F0F0F0Fu, wB.y & 0x0F0F0F0Fu, b.x, b.y);
+                    accL[0] += sAl * S[0];
+                    accL[1] += sAl * S[1];
+                    accL[2] += sBl * S[2];
+                    accL[3] += sBl * S[3];
+                    mma_u8s8(S, wA.x & 0xF0F0F0F0u, wB.x & 0xF0F0F0F0u, wA.y & 0xF0F0F0F0u, wB.y & 0xF0F0F0F0u, b.z, b.w);
+                    accH[0] += sAh * S[0];
+                    accH[1] += sAh * S[1];
+                    accH[2] += sBh * S[2];
+                    accH[3] += sBh * S[3];
+                }
+                // ---- minima: one f16 mma against the sub-block sums of the activations -----------------
+                const uint32_t mpA = hsub2(__byte_perm(__byte_perm(mnA0, mnA1, min_sel), 0x64646464u, 0x4140), 0x64006400u);
+                const uint32_t mpB = hsub2(__byte_perm(__byte_perm(mnB0, mnB1, min_sel), 0x64646464u, 0x4140), 0x64006400u);
+                float accM[4];
+                mma_f16(accM, mpA, mpB, *bmp);
+                // ---- per-unit float32 scaling -------------------------------------------------------
+                const float2 ddA = __half22float2(*reinterpret_cast<const __half2 *>(&hA.x));   // d, dmin of row g
+                const float2 ddB = __half22float2(*reinterpret_cast<const __half2 *>(&hB.x));
+                const float2 cw = *reinterpret_cast<const float2 *>(cwp);
+                // even column: first limb / high half of the sums, weight sx; odd column: second limb /
+                // low half, weight sx/128; the sums are in units of 127*sx
+                const float mx = 127.f * cw.x, my = 16256.f * cw.y;
+                const float f0 = fmaf((float)accH[0], 0.0625f, (float)accL[0]), f1 = fmaf((float)accH[1], 0.0625f, (float)accL[1]);
+                const float f2 = fmaf((float)accH[2], 0.0625f, (float)accL[2]), f3 = fmaf((float)accH[3], 0.0625f, (float)accL[3]);
+                accF[0] = fmaf(ddA.x * cw.x, f0, fmaf(-ddA.y * mx, accM[0], accF[0]));
+                accF[1] = fmaf(ddA.x * cw.y, f1, fmaf(-ddA.y * my, accM[1], accF[1]));
+                accF[2] = fmaf(ddB.x * cw.x, f2, fmaf(-ddB.y * mx, accM[2], accF[2]));
+                accF[3] = fmaf(ddB.x * cw.y, f3, fmaf(-ddB.y * my, accM[3], accF[3]));
+                bp += 256;
+                cwp += 8;
+                bmp += 32;
+                c_stage = c_stage + kStageBytes == my_stages + D * kStageBytes ? my_stages : c_stage + kStageBytes;
+                // every lane's reads of the slot have returned (their values were consumed above):
+                // after the warp converges the next copy may overwrite it
+                __syncwarp();
+                issue();
+            }
+            flush(tile, i, seg_end, accF);
+            i = seg_end;
+        }
+        __syncthreads();
+        if (fin_tile >= 0) {
+            // partial sums of the warps that worked on the tile before this one, in warp order
+            const unsigned int ts = (unsigned int)(fin_tile * nun), big = (unsigned int)wrem * (unsigned int)(wq + 1);
+            const int wf = wq == 0 ? (int)ts : ts < big ? (int)(ts / (unsigned int)(wq + 1))
+                                                         : wrem + (int)((ts - big) / (unsigned int)wq);
+            for (int o = lane; o < 16 * M; o += 32) {
+                float sum = 0.f;
+                for (int x = wf; x < warp; x++) sum += slots[((size_t)x * 2 + 1) * M * 16 + o];
+                sum += slots[(size_t)warp * 2 * M * 16 + o];
+                const int j = o >> 4, r = (tile0 + fin_tile) * 16 + (o & 15);
+                if (r < rows) store_y(opy + (int64_t)j * ldy + r, sum);
+            }
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
@@ -872,6 +1256,24 @@ extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt2_img(const __grid_constant__ QmFusedArgs a) {
     fused_body<2, true, false>(a);
+}
+// Data-driven variants (no grid barrier between dependent ops): up to two activation rows with
+// three limbs (four ring stages at one row, three at two), three or four rows with two limbs.
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_dd_c4d4(const __grid_constant__ QmFusedArgs a) {
+    dd_body<4, 4>(a);
+}
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_dd_c4d3(const __grid_constant__ QmFusedArgs a) {
+    dd_body<4, 3>(a);
+}
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_dd_c2d3(const __grid_constant__ QmFusedArgs a) {
+    dd_body<2, 3>(a);
+}
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_dd_c2d2(const __grid_constant__ QmFusedArgs a) {
+    dd_body<2, 2>(a);
 }
 // Tensor-parallel variants: outputs go to every peer's arena, barriers span the GPUs.
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)

@@ -56,6 +56,7 @@ QM_INCBIN(qm_cubin_dequant, QM_STR(QM_CUBIN_DIR) "/qm_dequant.sm_100a.cubin")
 QM_INCBIN(qm_cubin_q4k, QM_STR(QM_CUBIN_DIR) "/qm_gemv_q4k.sm_100a.cubin")
 QM_INCBIN(qm_cubin_gemm, QM_STR(QM_CUBIN_DIR) "/qm_gemm_q4k.sm_100a.cubin")
 QM_INCBIN(qm_cubin_moe, QM_STR(QM_CUBIN_DIR) "/qm_moe.sm_100a.cubin")
+QM_INCBIN(qm_cubin_kq, QM_STR(QM_CUBIN_DIR) "/qm_gemv_kq.sm_100a.cubin")
 
 struct KernelImage {
     const unsigned char *begin;
@@ -67,6 +68,7 @@ static const KernelImage kImages[QM_MOD_COUNT] = {
     {qm_cubin_q4k, qm_cubin_q4k_end},
     {qm_cubin_gemm, qm_cubin_gemm_end},
     {qm_cubin_moe, qm_cubin_moe_end},
+    {qm_cubin_kq, qm_cubin_kq_end},
 };
 struct KernelName {
     int module;
@@ -81,10 +83,16 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_Q4K, "qm_fused_q4k_nt1"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2"},
     {QM_MOD_Q4K, "qm_fused_q4k_nt1_img"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2_img"},
     {QM_MOD_Q4K, "qm_fused_q4k_nt1_tp"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2_tp"},
+    {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d4"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d3"},
+    {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d3"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d2"},
     {QM_MOD_GEMM, "qm_gemm_q4k_bf16"}, {QM_MOD_GEMM, "qm_gemm_q4k_bf16_r256"},
     {QM_MOD_GEMM, "qm_gemm_q4k_bf16_k128"}, {QM_MOD_GEMM, "qm_gemm_q4k_bf16_r256_k128"},
     {QM_MOD_MOE, "qm_moe_route"},      {QM_MOD_MOE, "qm_moe_lists"},      {QM_MOD_MOE, "qm_moe_gather"},
-    {QM_MOD_MOE, "qm_moe_swiglu"},     {QM_MOD_MOE, "qm_moe_combine"},
+    {QM_MOD_MOE, "qm_moe_combine"},
+    {QM_MOD_DEQUANT, "qm_dequant_iq2xxs"},
+    {QM_MOD_KQ, "qm_gemv_q2k_m1"},     {QM_MOD_KQ, "qm_gemv_q2k_m2"},     {QM_MOD_KQ, "qm_gemv_q2k_m4"},
+    {QM_MOD_KQ, "qm_gemv_q2k_m8"},     {QM_MOD_KQ, "qm_gemv_iq2xxs_m1"},  {QM_MOD_KQ, "qm_gemv_iq2xxs_m2"},
+    {QM_MOD_KQ, "qm_gemv_iq2xxs_m4"},  {QM_MOD_KQ, "qm_gemv_iq2xxs_m8"},
 };
 
 // ---- errors --------------------------------------------------------------------------
@@ -164,7 +172,7 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             r = d->cuModuleGetFunction(&c->fn[k], c->modules[kKernels[k].module], kKernels[k].name);
             if (r != CUDA_SUCCESS) err = QM_ERR_NO_KERNEL;
         }
-        for (int k = QM_K_FUSED_Q4K_NT1; k <= QM_K_FUSED_Q4K_NT2_TP && !err; k++) {
+        for (int k = QM_K_FUSED_Q4K_NT1; k <= QM_K_FUSED_Q4K_DD_C2D2 && !err; k++) {
             r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
@@ -356,6 +364,7 @@ static bool fmt_geometry(int32_t fmt, int64_t *block, int64_t *bytes) {
     case QM_FMT_Q8_0: *block = 32; *bytes = 34; return true;
     case QM_FMT_Q2_K: *block = 256; *bytes = 84; return true;
     case QM_FMT_Q4_K: *block = 256; *bytes = 144; return true;
+    case QM_FMT_IQ2_XXS: *block = 256; *bytes = 66; return true;
     }
     return false;
 }
@@ -378,12 +387,13 @@ extern "C" int32_t qm_store_create(qm_ctx *c, int32_t fmt, int64_t rows, int64_t
     if (!w) return QM_ERR_NOMEM;
     w->magic = QM_WEIGHT_MAGIC;
     w->fmt = fmt;
+    w->device = c->device;
     w->rows = rows;
     w->cols = cols;
     w->units = (int32_t)((cols + QM_K_UNIT - 1) / QM_K_UNIT);
     w->gguf_row_bytes = cols / block * bbytes;
     int64_t qbytes = 0, dbytes = 0;
-    if (fmt == QM_FMT_Q2_K) qbytes = rows * w->units * bbytes;
+    if (fmt == QM_FMT_Q2_K || fmt == QM_FMT_IQ2_XXS) qbytes = rows * w->units * bbytes;
     if (fmt == QM_FMT_Q4_K) qbytes = (rows + 15) / 16 * w->units * QM_Q4K_ITEM_BYTES;  // whole 16-row tiles
     if (fmt == QM_FMT_Q4_0) { qbytes = rows * w->units * 8 * 16; dbytes = rows * w->units * 8 * 2; }
     if (fmt == QM_FMT_Q8_0) { qbytes = rows * w->units * 8 * 32; dbytes = rows * w->units * 8 * 2; }
@@ -409,7 +419,7 @@ extern "C" int32_t qm_store_create(qm_ctx *c, int32_t fmt, int64_t rows, int64_t
 }
 
 static int32_t store_write_dev(qm_ctx *c, QmWeight *w, int64_t row_offset, int64_t nrows, CUdeviceptr src) {
-    if (w->fmt == QM_FMT_Q2_K) {
+    if (w->fmt == QM_FMT_Q2_K || w->fmt == QM_FMT_IQ2_XXS) {
         DRV(c->drv->cuMemcpyDtoDAsync_v2(w->wq + row_offset * w->gguf_row_bytes, src,
                                          (size_t)(nrows * w->gguf_row_bytes), c->stream));
         return QM_OK;
@@ -453,7 +463,7 @@ extern "C" int32_t qm_store_write_rows(qm_ctx *c, qm_weight h, int64_t row_offse
     CtxGuard g(c);
     DRV(g.rc);
     const int64_t bytes = nrows * w->gguf_row_bytes;
-    if (w->fmt == QM_FMT_Q2_K) {
+    if (w->fmt == QM_FMT_Q2_K || w->fmt == QM_FMT_IQ2_XXS) {
         // GGUF bytes are the device layout: copy straight into place
         DRV(c->drv->cuMemcpyHtoDAsync_v2(w->wq + row_offset * w->gguf_row_bytes, host_bytes, (size_t)bytes,
                                          c->stream));
@@ -541,6 +551,7 @@ extern "C" int32_t qm_dequantize(qm_ctx *c, qm_weight h, uint64_t out_dev) {
     a.cols = (int32_t)w->cols;
     a.units = w->units;
     int k = w->fmt == QM_FMT_Q4_K ? QM_K_DEQUANT_Q4K : w->fmt == QM_FMT_Q2_K ? QM_K_DEQUANT_Q2K
+          : w->fmt == QM_FMT_IQ2_XXS ? QM_K_DEQUANT_IQ2XXS
           : w->fmt == QM_FMT_Q4_0 ? QM_K_DEQUANT_Q40 : QM_K_DEQUANT_Q80;
     const int64_t groups = w->rows * (w->cols / 4);
     const unsigned grid = (unsigned)std::min<int64_t>((groups + 255) / 256, (int64_t)c->sm_count * 32);
@@ -581,6 +592,10 @@ int qm_env_int(const char *name, int dflt) {
 }
 
 int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p) {
+    return qm_plan_gemv_sms(c->sm_count, w, m, p);
+}
+
+int32_t qm_plan_gemv_sms(int sm_count, const QmWeight *w, int32_t m, QmGemvPlan *p) {
     // One persistent CTA per SM: `consumers` warps, each streaming its own share of the
     // (16-row tile, K unit) items through a private ring of `depth` bulk-copy stages of `kc`
     // units. The activations of the CTA's K slice live in shared memory next to the rings; when
@@ -604,10 +619,10 @@ int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p) {
     int ksplit = (w->units + max_units - 1) / max_units;
     ksplit = std::max(ksplit, env_int("QM_GEMV_KSPLIT", 1));
     ksplit = std::min(ksplit, (int)w->units);
-    if (ksplit > c->sm_count) return QM_ERR_SHAPE;
+    if (ksplit > sm_count) return QM_ERR_SHAPE;
     p->units_per_slice = (w->units + ksplit - 1) / ksplit;
     p->ksplit = (w->units + p->units_per_slice - 1) / p->units_per_slice;
-    p->ctas_per_slice = std::max(1, env_int("QM_GEMV_CTAS", c->sm_count) / p->ksplit);
+    p->ctas_per_slice = std::max(1, env_int("QM_GEMV_CTAS", sm_count) / p->ksplit);
     p->tiles = (int)((w->rows + 15) / 16);
     const int n = p->units_per_slice;
     const int64_t Wt = std::min<int64_t>((int64_t)p->ctas_per_slice * p->consumers, (int64_t)p->tiles * n);
@@ -616,6 +631,14 @@ int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p) {
     if (p->tiles > QM_TICKETS) return QM_ERR_SHAPE;
     if ((int64_t)p->ksplit * p->tiles * p->maxseg * 512 > QM_PARTIALS_BYTES) return QM_ERR_SHAPE;
     return QM_OK;
+}
+
+// Bound of every device-side wait in SM clock cycles: about two seconds by default,
+// QM_WAIT_LIMIT (cycles) overrides it (tests use a short bound to see a wait run out).
+int64_t qm_wait_cycles() {
+    const char *s = getenv("QM_WAIT_LIMIT");
+    const long long v = (s && *s) ? atoll(s) : 0;
+    return v > 0 ? (int64_t)v : 4000000000ll;
 }
 
 int qm_fused_grid(qm_ctx *c) { return std::max(1, env_int("QM_GEMV_CTAS", c->sm_count)); }
@@ -710,6 +733,7 @@ static int32_t fused_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev,
     a.cpm = p.cpm;
     a.debug = env_int("QM_DEBUG_SKIP", 0);
     a.debug_slot = env_int("QM_DEBUG_OP", 0);
+    a.wait_cycles = qm_wait_cycles();
     const bool coop = p.slices > 1;  // K slices meet at a grid barrier: all CTAs must be co-resident
     if (coop) DRV(c->drv->cuMemsetD32Async(c->gridbar_dev, 0, 1, c->stream));
     return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2,
@@ -719,12 +743,34 @@ static int32_t fused_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev,
 
 int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,
                          uint64_t y_dev, int64_t ldy, uint32_t flags, CUdeviceptr partials, CUdeviceptr tickets) {
-    if (w->fmt != QM_FMT_Q4_K && w->fmt != QM_FMT_Q4_0 && w->fmt != QM_FMT_Q8_0) return QM_ERR_FORMAT;
+    if (w->fmt != QM_FMT_Q4_K && w->fmt != QM_FMT_Q4_0 && w->fmt != QM_FMT_Q8_0 && w->fmt != QM_FMT_Q2_K &&
+        w->fmt != QM_FMT_IQ2_XXS)
+        return QM_ERR_FORMAT;
     if (m < 1 || m > 8 || ldx < w->cols || ldy < w->rows) return QM_ERR_SHAPE;
     const uint32_t xop = flags & 0xFu;
     if (xop > QM_XOP_SWIGLU) return QM_ERR_ARG;
     if (!x_dev || !y_dev || (x_dev & 15) || (ldx & 3)) return QM_ERR_ARG;
     if ((xop == QM_XOP_ADD_RMSNORM || xop == QM_XOP_SWIGLU) && (!x2_dev || (x2_dev & 15))) return QM_ERR_ARG;
+    if (w->fmt == QM_FMT_Q2_K || w->fmt == QM_FMT_IQ2_XXS) {
+        // warp-per-row kernels over the GGUF bytes; plain products only (no fused input transform)
+        if (xop != QM_XOP_NONE) return QM_ERR_ARG;
+        QmKqArgs ka;
+        memset(&ka, 0, sizeof ka);
+        ka.wq = (const uint8_t *)(uintptr_t)w->wq;
+        ka.x = (const float *)(uintptr_t)x_dev;
+        ka.y = (float *)(uintptr_t)y_dev;
+        ka.ldx = ldx;
+        ka.ldy = ldy;
+        ka.rows = w->rows;
+        ka.units = w->units;
+        ka.m = m;
+        const int mi = m <= 1 ? 0 : m <= 2 ? 1 : m <= 4 ? 2 : 3;
+        const int k = (w->fmt == QM_FMT_Q2_K ? QM_K_GEMV_Q2K_M1 : QM_K_GEMV_IQ2XXS_M1) + mi;
+        // eight warps per CTA, one row per warp at a time; enough CTAs to fill every SM eight deep
+        const int64_t want = (w->rows + 7) / 8;
+        const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)c->sm_count * 8));
+        return qm_launch(c, k, grid, 1, 256, 0, &ka, (flags & QM_FLAG_PDL) != 0);
+    }
     if (w->fmt == QM_FMT_Q4_K) {
         // integer tensor-core path; K is cut into slices when the activation planes of the
         // whole K do not fit in shared memory (many rows times a long K)

@@ -9,11 +9,13 @@
 #define QM_CTX_MAGIC 0x514D4358u     // "QMCX"
 #define QM_WEIGHT_MAGIC 0x514D5754u  // "QMWT"
 
-enum { QM_MOD_GEMV = 0, QM_MOD_DEQUANT, QM_MOD_Q4K, QM_MOD_GEMM, QM_MOD_MOE, QM_MOD_COUNT };
+enum { QM_MOD_GEMV = 0, QM_MOD_DEQUANT, QM_MOD_Q4K, QM_MOD_GEMM, QM_MOD_MOE, QM_MOD_KQ, QM_MOD_COUNT };
 enum {
     QM_K_GEMV_Q40_M4 = 0, QM_K_GEMV_Q40_M8, QM_K_GEMV_Q80_M4,
     QM_K_GEMV_Q80_M8, QM_K_DEQUANT_Q4K, QM_K_DEQUANT_Q2K, QM_K_DEQUANT_Q40, QM_K_DEQUANT_Q80,
-    QM_K_REPACK_Q40, QM_K_REPACK_Q80, QM_K_REPACK_Q4K, QM_K_FUSED_Q4K_NT1, QM_K_FUSED_Q4K_NT2, QM_K_FUSED_Q4K_NT1_IMG, QM_K_FUSED_Q4K_NT2_IMG, QM_K_FUSED_Q4K_NT1_TP, QM_K_FUSED_Q4K_NT2_TP, QM_K_GEMM_Q4K, QM_K_GEMM_Q4K_R256, QM_K_GEMM_Q4K_K128, QM_K_GEMM_Q4K_R256_K128, QM_K_MOE_ROUTE, QM_K_MOE_LISTS, QM_K_MOE_GATHER, QM_K_MOE_SWIGLU, QM_K_MOE_COMBINE, QM_K_COUNT
+    QM_K_REPACK_Q40, QM_K_REPACK_Q80, QM_K_REPACK_Q4K, QM_K_FUSED_Q4K_NT1, QM_K_FUSED_Q4K_NT2, QM_K_FUSED_Q4K_NT1_IMG, QM_K_FUSED_Q4K_NT2_IMG, QM_K_FUSED_Q4K_NT1_TP, QM_K_FUSED_Q4K_NT2_TP, QM_K_FUSED_Q4K_DD_C4D4, QM_K_FUSED_Q4K_DD_C4D3, QM_K_FUSED_Q4K_DD_C2D3, QM_K_FUSED_Q4K_DD_C2D2, QM_K_GEMM_Q4K, QM_K_GEMM_Q4K_R256, QM_K_GEMM_Q4K_K128, QM_K_GEMM_Q4K_R256_K128, QM_K_MOE_ROUTE, QM_K_MOE_LISTS, QM_K_MOE_GATHER, QM_K_MOE_COMBINE,
+    QM_K_DEQUANT_IQ2XXS, QM_K_GEMV_Q2K_M1, QM_K_GEMV_Q2K_M2, QM_K_GEMV_Q2K_M4, QM_K_GEMV_Q2K_M8,
+    QM_K_GEMV_IQ2XXS_M1, QM_K_GEMV_IQ2XXS_M2, QM_K_GEMV_IQ2XXS_M4, QM_K_GEMV_IQ2XXS_M8, QM_K_COUNT
 };
 
 #define QM_GEMV_SMEM_MAX (227 * 1024)
@@ -44,6 +46,7 @@ struct qm_ctx {
 struct QmWeight {
     uint32_t magic;
     int32_t fmt;
+    int32_t device;   // ordinal of the GPU that holds the bytes
     int64_t rows, cols;
     int32_t units;
     int64_t gguf_row_bytes;
@@ -86,6 +89,7 @@ int32_t qm_launch_ex(qm_ctx *c, int kernel, unsigned gx, unsigned block, unsigne
 // Integer tensor-core path for Q4_K: plan for activation rows m and the largest K (in units)
 // of the ops; QM_ERR_SHAPE when the activation planes do not fit in shared memory.
 int qm_fused_grid(qm_ctx *c);
+int64_t qm_wait_cycles();
 void qm_balance_op(qm_ctx *c, QmOp *op);
 struct QmGemmGroup {
     int experts;               // 0: a single matmul
@@ -103,5 +107,7 @@ int32_t qm_plan_fused(qm_ctx *c, int32_t m, int32_t units, bool allow_slices, Qm
 void qm_fill_op(qm_ctx *c, const QmFusedPlan &p, const QmWeight *w, uint64_t x, uint64_t x2, int64_t ldx, uint64_t y,
                 int64_t ldy, uint32_t xop, int barrier, int unit0, int units, int accumulate, QmOp *op);
 int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p);
+// The same plan for a device with `sm_count` SMs (no context needed).
+int32_t qm_plan_gemv_sms(int sm_count, const QmWeight *w, int32_t m, QmGemvPlan *p);
 int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,
                          uint64_t y_dev, int64_t ldy, uint32_t flags, CUdeviceptr partials, CUdeviceptr tickets);

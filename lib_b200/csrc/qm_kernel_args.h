@@ -97,6 +97,8 @@ struct QmFusedArgs {
     int32_t debug;       // 0 in production
     int32_t debug_slot;
     int32_t img_units;   // K units an activation image has room for (>= units_total of every op that reads one)
+    int32_t pad0;
+    int64_t wait_cycles; // SM clock cycles after which a device-side wait gives up and sets QM_STATUS_TIMEOUT
     // Tensor-parallel launch (kernels *_tp): this GPU computes a row slice of every op and stores
     // it into the same place of every peer's activation arena (its own address + peer_delta[p]);
     // the barrier between dependent ops then spans the GPUs: the last CTA of a GPU to arrive
@@ -161,11 +163,6 @@ struct QmGatherArgs {
     int64_t ldx;
     int32_t rows, hidden, topk, pad;
 };
-struct QmSwigluArgs {
-    const float *gu;       // [rows][2*ffn]
-    uint16_t *h;           // bf16 [rows][ffn]
-    int32_t rows, ffn;
-};
 struct QmCombineArgs {
     const float *y;        // [rows][hidden] expert outputs in grouped order
     const int32_t *pos;
@@ -173,6 +170,16 @@ struct QmCombineArgs {
     float *out;            // [tokens][ldo]
     int64_t ldo;
     int32_t tokens, hidden, topk, pad;
+};
+
+// GEMV over Q2_K / IQ2_XXS weights kept in their GGUF byte layout (qm_gemv_kq.cu).
+struct QmKqArgs {
+    const uint8_t *wq;       // [rows][units] super-blocks of 84 (Q2_K) or 66 (IQ2_XXS) bytes
+    const float *x;          // activations [m][ldx]
+    float *y;                // outputs [m][ldy]
+    int64_t ldx, ldy;
+    int64_t rows;
+    int32_t units, m;
 };
 
 struct QmDequantArgs {

@@ -99,18 +99,6 @@ extern "C" __global__ void __launch_bounds__(256) qm_moe_gather(const __grid_con
     }
 }
 
-// h[p][j] = bf16( silu(gu[p][j]) * gu[p][ffn + j] ), gu float32 [rows][2*ffn].
-extern "C" __global__ void __launch_bounds__(256) qm_moe_swiglu(const __grid_constant__ QmSwigluArgs a) {
-    const int64_t total = (int64_t)a.rows * (a.ffn / 2);
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int p = (int)(i / (a.ffn / 2)), j = (int)(i - (int64_t)p * (a.ffn / 2)) * 2;
-        const float2 g = *reinterpret_cast<const float2 *>(a.gu + (int64_t)p * 2 * a.ffn + j);
-        const float2 u = *reinterpret_cast<const float2 *>(a.gu + (int64_t)p * 2 * a.ffn + a.ffn + j);
-        const float h0 = g.x / (1.f + __expf(-g.x)) * u.x, h1 = g.y / (1.f + __expf(-g.y)) * u.y;
-        *reinterpret_cast<__nv_bfloat162 *>(a.h + (int64_t)p * a.ffn + j) = __floats2bfloat162_rn(h0, h1);
-    }
-}
-
 // out[tok][:] = sum_s weights[tok][s] * y[pos[tok*topk+s]][:] in slot order (deterministic).
 extern "C" __global__ void __launch_bounds__(256) qm_moe_combine(const __grid_constant__ QmCombineArgs a) {
     const int64_t total = (int64_t)a.tokens * a.hidden;

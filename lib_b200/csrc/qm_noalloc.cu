@@ -74,7 +74,8 @@ int32_t setup_device(int dev, DeviceSetup **out) {
 
 // y[j][r] = sum_c x[j][c] * W[r][c], j < m <= 8, for a stored Q4_0 or Q8_0 matrix; x and y are
 // float32 device pointers in the current device's primary context, the launch goes to
-// `cu_stream` (0 = the default stream) and the call returns without waiting for it.
+// `cu_stream` (0 = the default stream) and the call returns without waiting for it. The current
+// device must be the one that holds the weights (QM_ERR_ARG otherwise).
 extern "C" __attribute__((visibility("default"))) int32_t qm_matvec_noalloc(qm_weight h, uint64_t x_dev, int32_t m,
                                                                               int64_t ldx, uint64_t y_dev,
                                                                               int64_t ldy, uint64_t cu_stream) {
@@ -85,28 +86,16 @@ extern "C" __attribute__((visibility("default"))) int32_t qm_matvec_noalloc(qm_w
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int32_t)e;
+    if (dev != w->device) return QM_ERR_ARG;   // the weights live on another GPU than the current one
     DeviceSetup *ds = nullptr;
     int32_t rc = setup_device(dev, &ds);
     if (rc) return rc;
 
-    // launch shape: 16 warps per CTA, one CTA per SM, K cut into slices until the activation
-    // planes of a slice fit in shared memory next to the copy rings
-    const int C = 16, D = 2, KC = w->fmt == QM_FMT_Q8_0 ? 1 : 2;
-    const int q = w->fmt == QM_FMT_Q4_0 ? 128 : 256;
-    const int stage = (16 * (KC * q + 16) + 16 * (KC * 16 + 16) + 127) & ~127;
-    const int fixed = 32 * 8 * 4 + 32 + C * D * 8 + 128 + C * D * stage;
-    const int planes = 2 * m;
-    const int max_units = (QM_GEMV_SMEM_MAX - fixed - planes * 64) / (planes * 528);
-    if (max_units < 1) return QM_ERR_LIMIT;
-    int ksplit = std::min((int)w->units, (w->units + max_units - 1) / max_units);
-    if (ksplit > ds->sm_count) return QM_ERR_LIMIT;
-    const int ups = (w->units + ksplit - 1) / ksplit;
-    ksplit = (w->units + ups - 1) / ups;
-    const int ctas = std::max(1, ds->sm_count / ksplit);
-    const int tiles = (int)((w->rows + 15) / 16);
-    const int64_t Wt = std::min<int64_t>((int64_t)ctas * C, (int64_t)tiles * ups);
-    const int maxseg = (int)std::min<int64_t>(ups, (int64_t)(ups - 1) * Wt / ((int64_t)tiles * ups) + 2);
-    const int smem = planes * (ups * 528 + 64) + fixed;
+    // the launch shape is the one qm_matvec uses (same planner)
+    QmGemvPlan p;
+    rc = qm_plan_gemv_sms(ds->sm_count, w, m, &p);
+    if (rc) return rc == QM_ERR_SHAPE ? QM_ERR_LIMIT : rc;
+    const int tiles = p.tiles, ksplit = p.ksplit, maxseg = p.maxseg, smem = p.smem;
 
     // scratch layout: [status 256 B][tickets: tiles x 4 B, rounded to 256][partial sums]
     const size_t tickets_bytes = ((size_t)tiles * 4 + 255) & ~(size_t)255;
@@ -135,15 +124,15 @@ extern "C" __attribute__((visibility("default"))) int32_t qm_matvec_noalloc(qm_w
     a.m = m;
     a.tiles = tiles;
     a.ksplit = ksplit;
-    a.units_per_slice = ups;
-    a.ctas_per_slice = ctas;
-    a.consumers = C;
-    a.depth = D;
-    a.kc = KC;
+    a.units_per_slice = p.units_per_slice;
+    a.ctas_per_slice = p.ctas_per_slice;
+    a.consumers = p.consumers;
+    a.depth = p.depth;
+    a.kc = p.kc;
     a.maxseg = maxseg;
     a.xop = 0;
     a.eps = 1e-6f;
-    const dim3 grid((unsigned)(ksplit * ctas)), block((unsigned)C * 32);
+    const dim3 grid((unsigned)(ksplit * p.ctas_per_slice)), block((unsigned)p.consumers * 32);
     if (w->fmt == QM_FMT_Q4_0) {
         if (m <= 4) qm_gemv_q40_m4<<<grid, block, smem, stream>>>(a);
         else qm_gemv_q40_m8<<<grid, block, smem, stream>>>(a);
@@ -153,4 +142,23 @@ extern "C" __attribute__((visibility("default"))) int32_t qm_matvec_noalloc(qm_w
     }
     e = cudaGetLastError();
     return e == cudaSuccess ? QM_OK : (int32_t)e;
+}
+
+// The status word of the most recent qm_matvec_noalloc on the current device (0 = clean,
+// QM_STATUS_TIMEOUT = a bounded wait inside the kernel ran out and y is incomplete). The word
+// lives in the fixed array, so reading it allocates nothing: a 4-byte copy that waits for the
+// device. Call it after the stream of the matvec has been synchronized, and before the next
+// qm_matvec_noalloc on this device, which clears the word. Returns QM_ERR_TIMEOUT when the
+// timeout bit is set.
+extern "C" __attribute__((visibility("default"))) int32_t qm_noalloc_status(uint32_t *status) {
+    if (!status) return QM_ERR_ARG;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int32_t)e;
+    DeviceSetup *ds = nullptr;
+    int32_t rc = setup_device(dev, &ds);
+    if (rc) return rc;
+    e = cudaMemcpy(status, ds->scratch, 4, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return (int32_t)e;
+    return (*status & QM_STATUS_TIMEOUT) ? QM_ERR_TIMEOUT : QM_OK;
 }

@@ -23,7 +23,12 @@ struct qm_stack {
     uint32_t magic;
     int layers, hidden, kv, ffn, m_max;
     std::vector<QmLayer> layer;
-    CUdeviceptr h0, qkv_out, o_out, gu_out, dn_out;  // activations
+    // Activations: the step's input h0 [m][hidden], then one block per layer holding that layer's
+    // q|k|v, o, gate|up and down outputs (rows packed for the batch m of the step). Every
+    // matvec has an output buffer of its own, which lets dependent matvecs hand over through
+    // the data itself (see build_fused).
+    CUdeviceptr h0, act;
+    size_t act_bytes;
     CUgraphExec graph[9];
     CUdeviceptr ops_dev[9];     // fused op lists, one per batch size
     QmFusedPlan fused_plan[9];
@@ -34,6 +39,8 @@ struct qm_stack {
     size_t sync_bytes[9];
     int img_units[9];
     bool fused_img[9];          // the op list uses activation images
+    bool fused_dd[9];           // the op list hands over through the data (no grid barriers)
+    int fused_dd_kernel[9];
     // tensor-parallel: one arena holds all activation buffers and the peers' arrival flags; the
     // peers map it through CUDA IPC and this GPU stores its row slices into all of them
     int tp_world, tp_rank;
@@ -44,7 +51,23 @@ struct qm_stack {
     bool tp_counter;            // peers reachable with native NVLink atomics: counter barrier
     unsigned int tp_epoch;
     bool use_graph, use_fused;
+    int last_m;                 // batch of the most recent step
 };
+
+// Device addresses of layer L's output buffers in a step of batch m.
+struct LayerBufs {
+    CUdeviceptr qkv, o, gu, dn;
+};
+static LayerBufs layer_bufs(const qm_stack *s, int L, int m) {
+    const size_t qkv_ld = (size_t)s->hidden + 2 * s->kv;
+    const size_t per_row = qkv_ld + (size_t)s->hidden + 2 * (size_t)s->ffn + (size_t)s->hidden;
+    LayerBufs b;
+    b.qkv = s->act + (size_t)L * m * per_row * 4;
+    b.o = b.qkv + (size_t)m * qkv_ld * 4;
+    b.gu = b.o + (size_t)m * s->hidden * 4;
+    b.dn = b.gu + (size_t)m * 2 * s->ffn * 4;
+    return b;
+}
 
 static qm_stack *stack_check(qm_stack *s) { return (s && s->magic == QM_STACK_MAGIC) ? s : nullptr; }
 
@@ -81,30 +104,24 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
     memset(s->sync_dev, 0, sizeof s->sync_dev);
     s->use_graph = true;
     s->use_fused = true;
+    s->last_m = 0;
+    s->h0 = s->act = 0;
     CtxGuard g(c);
     CUresult r = g.rc;
-    const size_t f = 4;
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
-    const size_t b_h0 = up((size_t)m_max * hidden * f), b_qkv = up((size_t)layers * m_max * (hidden + 2 * kv_dim) * f),
-                 b_o = up((size_t)m_max * hidden * f), b_gu = up((size_t)m_max * 2 * ffn * f),
-                 b_dn = up((size_t)m_max * hidden * f);
+    const size_t b_h0 = up((size_t)m_max * hidden * 4);
+    s->act_bytes = up((size_t)layers * m_max * (2 * (size_t)hidden + 2 * kv_dim + hidden + 2 * (size_t)ffn) * 4);
     if (world == 1) {
         if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->h0, b_h0);
-        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->qkv_out, b_qkv);
-        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->o_out, b_o);
-        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->gu_out, b_gu);
-        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->dn_out, b_dn);
+        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->act, s->act_bytes);
     } else {
-        s->flags_off = b_h0 + b_qkv + b_o + b_gu + b_dn;
+        s->flags_off = b_h0 + s->act_bytes;
         s->arena_bytes = s->flags_off + 256;
         if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->arena, s->arena_bytes);
         if (r == CUDA_SUCCESS) r = c->drv->cuMemsetD8Async(s->arena, 0, s->arena_bytes, c->stream);
         if (r == CUDA_SUCCESS) r = c->drv->cuStreamSynchronize(c->stream);
         s->h0 = s->arena;
-        s->qkv_out = s->h0 + b_h0;
-        s->o_out = s->qkv_out + b_qkv;
-        s->gu_out = s->o_out + b_o;
-        s->dn_out = s->gu_out + b_gu;
+        s->act = s->h0 + b_h0;
     }
     if (r != CUDA_SUCCESS) {
         qm_stack_destroy(c, s);
@@ -198,9 +215,8 @@ extern "C" int32_t qm_stack_destroy(qm_ctx *c, qm_stack *s) {
                 if (p != s->tp_rank && s->peer_base[p]) c->drv->cuIpcCloseMemHandle(s->peer_base[p]);
         if (s->arena) c->drv->cuMemFree_v2(s->arena);
     } else {
-        CUdeviceptr bufs[5] = {s->h0, s->qkv_out, s->o_out, s->gu_out, s->dn_out};
-        for (CUdeviceptr b : bufs)
-            if (b) c->drv->cuMemFree_v2(b);
+        if (s->h0) c->drv->cuMemFree_v2(s->h0);
+        if (s->act) c->drv->cuMemFree_v2(s->act);
     }
     s->magic = 0;
     delete s;
@@ -239,17 +255,20 @@ extern "C" int32_t qm_stack_set_layer(qm_ctx *c, qm_stack *s, int32_t layer, qm_
     return QM_OK;
 }
 
-// Device pointers of the activation buffers, for per-matvec checks:
-// [0]=h0 [m][hidden], [1]=qkv_out [layers][m][hidden+2kv], [2]=o_out [m][hidden],
-// [3]=gu_out [m][2*ffn], [4]=dn_out [m][hidden] (rows are packed for the m of the last step).
+// Device pointers of the activation buffers as the last step (of batch m) left them, for
+// per-matvec checks: [0]=h0 [m][hidden], [1]=q|k|v outputs of layer 0 [m][hidden+2kv] (layer L's
+// follow at a stride of m*(3*hidden+2*kv+2*ffn) floats, like the other three), and of the LAST
+// layer [2]=o output [m][hidden], [3]=gate|up output [m][2*ffn], [4]=down output [m][hidden].
 extern "C" int32_t qm_stack_buffers(qm_ctx *c, qm_stack *s, uint64_t *ptrs5) {
     CHECK_CTX(c);
     if (!stack_check(s) || !ptrs5) return QM_ERR_ARG;
+    const int m = s->last_m > 0 ? s->last_m : 1;
+    const LayerBufs last = layer_bufs(s, s->layers - 1, m);
     ptrs5[0] = s->h0;
-    ptrs5[1] = s->qkv_out;
-    ptrs5[2] = s->o_out;
-    ptrs5[3] = s->gu_out;
-    ptrs5[4] = s->dn_out;
+    ptrs5[1] = layer_bufs(s, 0, m).qkv;
+    ptrs5[2] = last.o;
+    ptrs5[3] = last.gu;
+    ptrs5[4] = last.dn;
     return QM_OK;
 }
 
@@ -302,23 +321,35 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     const int64_t qkv_ld = s->hidden + 2 * s->kv;
     for (int L = 0; L < s->layers; L++) {
         const QmLayer &ly = s->layer[L];
-        const CUdeviceptr qkv = s->qkv_out + (size_t)L * m * qkv_ld * 4;
+        const LayerBufs b = layer_bufs(s, L, m);
+        const CUdeviceptr x0 = L == 0 ? s->h0 : layer_bufs(s, L - 1, m).dn;
         // Tensor-parallel: the two large matrices (gate|up, down: 81 % of the bytes) are shared — y
         // points at this rank's rows of the full-width output; q|k|v and o are computed whole by
         // every GPU, which costs less than the barrier over the GPUs that sharing them would add.
         const bool tp = s->tp_world > 1;
         const size_t R = (size_t)s->tp_rank * 4;
-        add_matvec(ly.qkv, L == 0 ? s->h0 : s->dn_out, 0, s->hidden, qkv, qkv_ld, QM_XOP_RMSNORM, L == 0, false);
-        add_matvec(ly.o, qkv, 0, qkv_ld, s->o_out, s->hidden, QM_XOP_RMSNORM, false, false);
-        add_matvec(ly.gu, s->o_out, 0, s->hidden, s->gu_out + R * ly.gu->rows, 2 * s->ffn, QM_XOP_RMSNORM, false, tp);
-        add_matvec(ly.dn, s->gu_out, s->gu_out + (size_t)s->ffn * 4, 2 * s->ffn, s->dn_out + R * ly.dn->rows,
+        add_matvec(ly.qkv, x0, 0, s->hidden, b.qkv, qkv_ld, QM_XOP_RMSNORM, L == 0, false);
+        add_matvec(ly.o, b.qkv, 0, qkv_ld, b.o, s->hidden, QM_XOP_RMSNORM, false, false);
+        add_matvec(ly.gu, b.o, 0, s->hidden, b.gu + R * ly.gu->rows, 2 * s->ffn, QM_XOP_RMSNORM, false, tp);
+        add_matvec(ly.dn, b.gu, b.gu + (size_t)s->ffn * 4, 2 * s->ffn, b.dn + R * ly.dn->rows,
                    s->hidden, QM_XOP_ADD_RMSNORM, false, tp);
     }
     for (const QmOp &op : ops)
         if ((int64_t)op.tiles * op.units >= (1ll << 31)) return QM_ERR_SHAPE;
     // every unsliced op but the first writes a buffer that the op before it does not touch
     // (ops shared between GPUs keep whole tiles per CTA: their outputs are plain stores to every GPU)
-    for (size_t k = 1; k < ops.size(); k++)
+    // Data-driven hand-over (kernels qm_fused_q4k_dd_*): every output buffer is filled with the
+    // "not yet written" pattern before the launch and consumers poll the words they read, so the
+    // grid barrier between dependent matvecs goes away. Needs whole tiles per CTA, no K slices
+    // and one row tile of mma columns; used below the batch from which activation images win.
+    const int min_m = qm_env_int("QM_IMAGE_MIN_M", 4);
+    const int dd_kernel = p.cpm == 4 ? (p.depth == 4 ? QM_K_FUSED_Q4K_DD_C4D4 : p.depth == 3 ? QM_K_FUSED_Q4K_DD_C4D3 : -1)
+                                     : (p.depth == 3 ? QM_K_FUSED_Q4K_DD_C2D3 : p.depth == 2 ? QM_K_FUSED_Q4K_DD_C2D2 : -1);
+    bool dd = s->tp_world == 1 && p.nt == 1 && p.consumers == 16 && dd_kernel >= 0 && m < min_m &&
+              qm_env_int("QM_DD", 1) != 0;
+    for (const QmOp &op : ops)
+        if (op.units != op.units_total || op.accumulate) dd = false;
+    for (size_t k = 1; k < ops.size() && !dd; k++)
         if (ops[k].units == ops[k].units_total && !ops[k].tp_shared) qm_balance_op(c, &ops[k]);
     // barriers over all GPUs in one launch: after every shared op, and the one that ends the launch
     int ncross = 1;
@@ -343,8 +374,8 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     // 2.09 against 2.33; batch 3: 2.34 against 2.37); from four rows on the image wins (batch 4:
     // 2.46 ms against 2.63 ms; batch 8: 3.52 ms against 5.93 ms).
     bool uses_img = false;
-    const int min_m = qm_env_int("QM_IMAGE_MIN_M", 4), min_units = qm_env_int("QM_IMAGE_MIN_UNITS", 1 << 30);
-    if (r == CUDA_SUCCESS && !qm_env_int("QM_NO_IMAGE", 0) && s->tp_world == 1) {
+    const int min_units = qm_env_int("QM_IMAGE_MIN_UNITS", 1 << 30);
+    if (r == CUDA_SUCCESS && !qm_env_int("QM_NO_IMAGE", 0) && s->tp_world == 1 && !dd) {
         for (size_t k = 0; k + 1 < ngroups; k++) {
             QmOp &prod = ops[group_last[k]];
             const QmOp &cons = ops[group_first[k + 1]];
@@ -377,6 +408,8 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     s->fused_nops[m] = (int)ops.size();
     s->fused_ncross[m] = ncross;
     s->fused_img[m] = uses_img;
+    s->fused_dd[m] = dd;
+    s->fused_dd_kernel[m] = dd_kernel;
     s->fused_plan[m] = p;
     return QM_OK;
 }
@@ -397,7 +430,15 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
     a.cpm = p.cpm;
     a.debug = qm_env_int("QM_DEBUG_SKIP", 0);
     a.debug_slot = qm_env_int("QM_DEBUG_OP", 0);
+    a.wait_cycles = qm_wait_cycles();
     DRV(c->drv->cuMemsetD32Async(s->sync_dev[m], 0, s->sync_bytes[m] / 4, c->stream));
+    if (s->fused_dd[m]) {
+        // every output word of the step starts as "not yet written" (all ones)
+        const size_t bytes = (size_t)(layer_bufs(s, s->layers, m).qkv - s->act);
+        DRV(c->drv->cuMemsetD8Async(s->act, 0xFF, bytes, c->stream));
+        return qm_launch_ex(c, s->fused_dd_kernel[m], (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32,
+                            (unsigned)p.smem, &a, false, true);
+    }
     // cooperative: the grid barrier between dependent matvecs needs every CTA resident
     if (s->tp_world > 1) {
         if (!s->peers_open) return QM_ERR_STATE;
@@ -425,15 +466,16 @@ static int32_t enqueue_layers(qm_ctx *c, qm_stack *s, int m, int upto_layers) {
     for (int L = 0; L < upto_layers; L++) {
         const QmLayer &ly = s->layer[L];
         if (!ly.qkv) return QM_ERR_STATE;
-        const CUdeviceptr qkv = s->qkv_out + (size_t)L * m * qkv_ld * 4;
-        int32_t rc = qm_matvec_launch(c, ly.qkv, L == 0 ? s->h0 : s->dn_out, 0, m, s->hidden, qkv, qkv_ld,
+        const LayerBufs b = layer_bufs(s, L, m);
+        const CUdeviceptr x0 = L == 0 ? s->h0 : layer_bufs(s, L - 1, m).dn;
+        int32_t rc = qm_matvec_launch(c, ly.qkv, x0, 0, m, s->hidden, b.qkv, qkv_ld,
                                       QM_XOP_RMSNORM | F, c->partials_dev, c->tickets_dev);
-        if (!rc) rc = qm_matvec_launch(c, ly.o, qkv, 0, m, qkv_ld, s->o_out, s->hidden, QM_XOP_RMSNORM | F,
+        if (!rc) rc = qm_matvec_launch(c, ly.o, b.qkv, 0, m, qkv_ld, b.o, s->hidden, QM_XOP_RMSNORM | F,
                                        c->partials_dev, c->tickets_dev);
-        if (!rc) rc = qm_matvec_launch(c, ly.gu, s->o_out, 0, m, s->hidden, s->gu_out, 2 * s->ffn,
+        if (!rc) rc = qm_matvec_launch(c, ly.gu, b.o, 0, m, s->hidden, b.gu, 2 * s->ffn,
                                        QM_XOP_RMSNORM | F, c->partials_dev, c->tickets_dev);
-        if (!rc) rc = qm_matvec_launch(c, ly.dn, s->gu_out, s->gu_out + (size_t)s->ffn * 4, m, 2 * s->ffn,
-                                       s->dn_out, s->hidden, QM_XOP_ADD_RMSNORM | F, c->partials_dev,
+        if (!rc) rc = qm_matvec_launch(c, ly.dn, b.gu, b.gu + (size_t)s->ffn * 4, m, 2 * s->ffn,
+                                       b.dn, s->hidden, QM_XOP_ADD_RMSNORM | F, c->partials_dev,
                                        c->tickets_dev);
         if (rc) return rc;
     }
@@ -441,6 +483,7 @@ static int32_t enqueue_layers(qm_ctx *c, qm_stack *s, int m, int upto_layers) {
 }
 
 static int32_t step_device(qm_ctx *c, qm_stack *s, int m) {
+    s->last_m = m;
     if (s->tp_world > 1) {   // tensor-parallel steps exist as the one fused launch only
         int32_t rc = s->ops_dev[m] ? QM_OK : build_fused(c, s, m);
         return rc ? rc : launch_fused(c, s, m);
@@ -489,7 +532,7 @@ extern "C" int32_t qm_stack_step(qm_ctx *c, qm_stack *s, uint64_t x_dev, int32_t
     if (rc) return rc;
     if (h_out_dev)
         for (int j = 0; j < m; j++)
-            DRV(c->drv->cuMemcpyDtoDAsync_v2(h_out_dev + (size_t)j * ldh * 4, s->dn_out + (size_t)j * s->hidden * 4,
+            DRV(c->drv->cuMemcpyDtoDAsync_v2(h_out_dev + (size_t)j * ldh * 4, layer_bufs(s, s->layers - 1, m).dn + (size_t)j * s->hidden * 4,
                                              (size_t)s->hidden * 4, c->stream));
     return QM_OK;
 }
@@ -507,14 +550,14 @@ extern "C" int32_t qm_stack_step_host(qm_ctx *c, qm_stack *s, const float *x_hos
     DRV(d->cuMemcpyHtoDAsync_v2(s->h0, x_host, (size_t)m * s->hidden * 4, c->stream));
     int32_t rc = step_device(c, s, m);
     if (rc) return rc;
-    DRV(d->cuMemcpyDtoHAsync_v2(h_host, s->dn_out, (size_t)m * s->hidden * 4, c->stream));
+    DRV(d->cuMemcpyDtoHAsync_v2(h_host, layer_bufs(s, s->layers - 1, m).dn, (size_t)m * s->hidden * 4, c->stream));
     if (kv_host && s->kv) {
         const int64_t qkv_ld = s->hidden + 2 * s->kv;
         // (tensor-parallel: q|k|v is computed whole by every GPU, so all rows are local)
         for (int L = 0; L < s->layers; L++)
             for (int j = 0; j < m; j++)
                 DRV(d->cuMemcpyDtoHAsync_v2(kv_host + ((size_t)L * m + j) * 2 * s->kv,
-                                            s->qkv_out + (((size_t)L * m + j) * qkv_ld + s->hidden) * 4,
+                                            layer_bufs(s, L, m).qkv + ((size_t)j * qkv_ld + s->hidden) * 4,
                                             (size_t)2 * s->kv * 4, c->stream));
     }
     DRV(d->cuStreamSynchronize(c->stream));

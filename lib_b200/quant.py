@@ -8,12 +8,12 @@ keeps the package's voice: GGUF block bytes in, float32 out, `quant:` errors.
 import numpy as np
 
 from . import _capi
-from ._capi import Q4_0, Q8_0, Q2_K, Q4_K, QmError  # noqa: F401
+from ._capi import Q4_0, Q8_0, Q2_K, Q4_K, IQ2_XXS, QmError  # noqa: F401
 
 BlockSize = 32          # lm/quant/quant.go:12
 SuperBlockSize = 256    # lm/quant/kquant.go:12
-FormatQ4_0, FormatQ8_0, FormatQ2_K, FormatQ4_K = "Q4_0", "Q8_0", "Q2_K", "Q4_K"
-_FMT = {FormatQ4_0: Q4_0, FormatQ8_0: Q8_0, FormatQ2_K: Q2_K, FormatQ4_K: Q4_K}
+FormatQ4_0, FormatQ8_0, FormatQ2_K, FormatQ4_K, FormatIQ2_XXS = "Q4_0", "Q8_0", "Q2_K", "Q4_K", "IQ2_XXS"
+_FMT = {FormatQ4_0: Q4_0, FormatQ8_0: Q8_0, FormatQ2_K: Q2_K, FormatQ4_K: Q4_K, FormatIQ2_XXS: IQ2_XXS}
 
 _default_ctx = None
 
@@ -38,6 +38,11 @@ def DequantizeQ8_0(data, numElements, ctx=None):
 def DequantizeQ2_K(data, numElements, ctx=None):
     """quant.DequantizeQ2_K (lm/quant/kquant.go:49)."""
     return (ctx or default_context()).dequantize_host(Q2_K, data, numElements)
+
+
+def DequantizeIQ2_XXS(data, numElements, ctx=None):
+    """quant.DequantizeIQ2_XXS (lm/quant/kquant.go:87)."""
+    return (ctx or default_context()).dequantize_host(IQ2_XXS, data, numElements)
 
 
 def DequantizeQ4_K(data, numElements, ctx=None):

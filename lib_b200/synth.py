@@ -7,12 +7,16 @@ Distributions (all drawn from numpy's Philox generator keyed by `seed`):
   Q4_0: d = fp16(|N(0,1)|*0.004), 4-bit codes uniform [0,15]
   Q4_K: d, dmin = fp16(|N(0,1)|*0.003) per 256 elements, 6-bit scales and mins
         uniform [0,63], 4-bit codes uniform [0,15]
+  Q2_K: d, dmin = fp16(|N(0,1)|*0.01) per 256 elements (bytes 80..83), 4-bit scales and
+        mins and 2-bit codes uniform
+  IQ2_XXS: d = fp16(|N(0,1)|*0.01) per 256 elements, codebook indices, sign indices and
+        4-bit group scales uniform
 Bytes are laid out exactly as a GGUF file stores the tensor (row-major blocks).
 """
 import numpy as np
 
-Q4_0, Q8_0, Q4_K = 2, 8, 12
-BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144)}
+Q4_0, Q8_0, Q2_K, Q4_K, IQ2_XXS = 2, 8, 10, 12, 16
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q2_K: (256, 84), IQ2_XXS: (256, 66)}
 
 
 def _rng(seed):
@@ -46,11 +50,14 @@ def weights(fmt, rows, cols, seed):
         scale = 0.002
     elif fmt == Q4_0:
         scale = 0.004
-    else:
+    elif fmt == Q4_K:
         scale = 0.003
-    nd = 1 if fmt != Q4_K else 2
+    else:
+        scale = 0.01
+    nd = 2 if fmt in (Q4_K, Q2_K) else 1
+    at = 80 if fmt == Q2_K else 0   # Q2_K keeps d | dmin at the end of the block
     d = (np.abs(g.standard_normal((nb, nd), dtype=np.float32)) * np.float32(scale)).astype(np.float16)
-    out[:, 0:2 * nd] = d.view(np.uint8).reshape(nb, 2 * nd)
+    out[:, at:at + 2 * nd] = d.view(np.uint8).reshape(nb, 2 * nd)
     return out.reshape(-1)
 
 

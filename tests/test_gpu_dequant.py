@@ -9,7 +9,7 @@ from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-FMTS = {2: (32, 18), 8: (32, 34), 10: (256, 84), 12: (256, 144)}
+FMTS = {2: (32, 18), 8: (32, 34), 10: (256, 84), 12: (256, 144), 16: (256, 66)}
 
 
 def _same_bits(a, b):
@@ -31,9 +31,18 @@ def test_known_answers(ctx, ds4_golden):
     assert gq.DequantizeQ8_0(d, 32, ctx)[0] == 65504.0
     got = gq.DequantizeQ2_K(ds4_golden["q2k_raw"], 256, ctx)
     assert np.array_equal(got.view(np.uint32), ds4_golden["q2k"].view(np.uint32))
+    # lm/quant/kquant_test.go:95-108 (1e-6 there; the device values are bit-equal) and :151-179
+    got = gq.DequantizeIQ2_XXS(ds4_golden["iq2_raw"], 256, ctx)
+    assert np.array_equal(got.view(np.uint32), ds4_golden["iq2"].view(np.uint32))
+    blk = bytearray(66)
+    blk[0:2] = b"\x00\x3c"
+    assert np.all(gq.DequantizeIQ2_XXS(blk, 256, ctx) == np.float32(1.0))
+    blk[2 + 7] = 0xF0
+    got = gq.DequantizeIQ2_XXS(blk, 256, ctx)
+    assert got[0] == np.float32(0.125 * 31 * 8) and got[32] == np.float32(1.0)
 
 
-@pytest.mark.parametrize("fmt", [2, 8, 10, 12])
+@pytest.mark.parametrize("fmt", [2, 8, 10, 12, 16])
 def test_random_bytes_bit_exact(ctx, fmt):
     """Uniform random bytes reach every scale pattern: subnormal, inf and NaN
     fp16 scales included."""
@@ -70,7 +79,7 @@ def test_store_dequantize_matrix(ctx, devbuf, fmt):
     ws.free()
 
 
-@pytest.mark.parametrize("fmt", [2, 8, 10, 12])
+@pytest.mark.parametrize("fmt", [2, 8, 10, 12, 16])
 def test_error_paths(ctx, fmt):
     be, bb = FMTS[fmt]
     for data, n, code in [(bytes(bb), be // 2, -1), (bytes(bb), -be, -1), (bytes(bb - 1), be, -2)]:
@@ -82,6 +91,22 @@ def test_error_paths(ctx, fmt):
     with pytest.raises(lib_b200.QmError) as e:
         ctx.dequantize_host(99, bytes(64), 32)
     assert e.value.code == -3
+
+
+def test_ggufpy_vectors_on_device(ctx):
+    """The committed vectors of the GGUF format's upstream Python decoder, decoded on the device."""
+    import json
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    fx = json.load(open(os.path.join(root, "tests/golden/ggufpy_vectors.json")))["formats"]
+    ids = {"Q4_0": 2, "Q8_0": 8, "Q2_K": 10, "Q4_K": 12, "IQ2_XXS": 16}
+    for name, cases in fx.items():
+        be, bb = FMTS[ids[name]]
+        for case, v in cases.items():
+            raw = bytes.fromhex(v["raw"])
+            want = np.array(v["bits"], dtype=np.uint32).view(np.float32)
+            got = ctx.dequantize_host(ids[name], raw, len(raw) // bb * be)
+            assert _same_bits(got, want), (name, case)
 
 
 def test_full_size_q8_0_bit_exact(ctx):

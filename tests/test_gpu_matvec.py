@@ -160,7 +160,51 @@ def test_argument_errors(ctx, devbuf):
         ctx.matvec(w, 0, 1, 256, yd.ptr, 16)
     w2 = ctx.store_upload(10, 16, 256, bytes(16 * 84))
     with pytest.raises(lib_b200.QmError) as e:
-        ctx.matvec(w2, xd.ptr, 1, 256, yd.ptr, 16)
-    assert e.value.code == -3  # Q2_K is stored and dequantized, not multiplied
+        ctx.matvec(w2, xd.ptr, 1, 256, yd.ptr, 16, _capi.XOP_RMSNORM)
+    assert e.value.code == -5  # the Q2_K / IQ2_XXS kernels take plain products only
     w.free()
     w2.free()
+
+
+def q2k_test_blocks(nblocks):
+    """The deterministic blocks of nvidia/x/egraph/q2k_cuda_test.go:98-125: both nibbles of every
+    scale byte non-zero, quant bytes that differ across the interleaved byte groups."""
+    scale_bits = [0x3800, 0x3400, 0x3C00, 0x3000]
+    min_bits = [0x3000, 0x2C00, 0x3400, 0x2800]
+    out = np.zeros((nblocks, 84), dtype=np.uint8)
+    for b in range(nblocks):
+        for g in range(16):
+            out[b, g] = ((1 + (g * 5 + b) % 15) << 4) | (1 + (g * 3 + b) % 15)
+        for i in range(64):
+            out[b, 16 + i] = (i * 37 + b * 11) & 0xFF
+        out[b, 80:82] = np.array([scale_bits[b % 4]], dtype=np.uint16).view(np.uint8)
+        out[b, 82:84] = np.array([min_bits[b % 4]], dtype=np.uint16).view(np.uint8)
+    return out.reshape(-1)
+
+
+def test_q2k_reference_device_case(ctx, devbuf):
+    """nvidia/x/egraph/q2k_cuda_test.go:142-213: 4 rows x 512 columns of the patterned blocks,
+    x[i] = ((13 i) mod 17 - 8) / 4, every row within 1e-4*max(1,|want|) of the float64 sum."""
+    rows, cols = 4, 512
+    raw = q2k_test_blocks(rows * cols // 256)
+    x = (((np.arange(cols) * 13) % 17 - 8) / 4).astype(np.float32).reshape(1, cols)
+    w = ctx.store_upload(10, rows, cols, raw)
+    xd, yd = devbuf(x), devbuf(nbytes=rows * 4)
+    ctx.matvec(w, xd.ptr, 1, cols, yd.ptr, rows)
+    ctx.sync()
+    y = yd.get((1, rows))
+    want = oracle.MatVec(10, raw, rows, cols, x)
+    assert np.all(np.abs(y.astype(np.float64) - want) <= 1e-4 * np.maximum(1, np.abs(want)))
+    w.free()
+
+
+@pytest.mark.parametrize("fmt", [10, 16])
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
+def test_q2k_iq2xxs_matvec(ctx, devbuf, fmt, m):
+    """The two low-bit super-block formats: ragged row counts, several K lengths, every batch
+    bucket of the kernels; float32 accumulation against the float64 oracle."""
+    for rows, cols in [(37, 256), (300, 1024), (1024, 4096)]:
+        raw, x, y = run_matvec(ctx, devbuf, fmt, rows, cols, m, seed=17 * fmt + m)
+        want = oracle.MatVec(fmt, raw, rows, cols, x)
+        e = nre(y, want)
+        assert e <= TIGHT_TOL, (fmt, m, rows, cols, e)

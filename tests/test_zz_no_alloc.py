@@ -41,6 +41,7 @@ def test_noalloc_matches_matvec_twice(ctx, devbuf, fmt, rows, cols, m):
         ctx.sync()
         ctx.matvec_noalloc(w, xd.ptr, m, cols, y_new.ptr, rows)
         device_sync()
+        assert ctx.noalloc_status() == (0, 0)   # no bounded wait of the kernel ran out
         want, got = y_ref.get((m, rows)), y_new.get((m, rows))
         assert np.isfinite(got).all()
         assert nre(got, want) <= TOL

@@ -24,6 +24,9 @@ HOST_SOURCES = ["qm_host.cpp", "qm_stack.cpp", "qm_moe.cpp", "qm_expert_cache.cp
 RUNTIME_SOURCES = ["qm_noalloc.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+# QM_DEBUG_BUILD=1 compiles the timing experiments in (phase time stamps, switches that turn
+# pipeline roles off and give wrong results). The shipped build leaves it unset.
+DEBUG = ["-DQM_DEBUG"] if os.environ.get("QM_DEBUG_BUILD") else []
 
 
 def _newer(target, deps):
@@ -71,7 +74,7 @@ def build(force=False, verbose=False):
         cubin = os.path.join(OUT, name[:-3] + ".sm_100a.cubin")
         cubins.append(cubin)
         if force or _newer(cubin, [src] + headers):
-            log = _run([NVCC] + ARCH + ["-cubin", "-O3", "-lineinfo", "-std=c++17", "-Xptxas", "-v",
+            log = _run([NVCC] + ARCH + DEBUG + ["-cubin", "-O3", "-lineinfo", "-std=c++17", "-Xptxas", "-v",
                                         "-o", cubin, src])
             if verbose:
                 print(log)
@@ -85,10 +88,10 @@ def build(force=False, verbose=False):
         obj = os.path.join(OUT, name[:-3] + ".o")
         rt_objs.append(obj)
         if force or _newer(obj, [src, os.path.join(CSRC, "qm_gemv.cu")] + headers):
-            _run([NVCC] + ARCH + ["-c", "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden",
+            _run([NVCC] + ARCH + DEBUG + ["-c", "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden",
                                   "-o", obj, src])
     if force or _newer(LIB, srcs + headers + cubins + rt_objs):
-        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-fvisibility=hidden",
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-fvisibility=hidden"] + DEBUG + [
               "-DQM_CUBIN_DIR=" + OUT, "-I/usr/local/cuda/include", "-o", LIB] + srcs + rt_objs +
              ["-L/usr/local/cuda/lib64", "-lcudart_static", "-lrt", "-ldl", "-lpthread"])
     return LIB

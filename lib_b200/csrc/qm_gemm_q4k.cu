@@ -27,6 +27,14 @@
 #include "qm_kernel_args.h"
 #include "qm_pipe.cuh"
 
+// Debug builds (-DQM_DEBUG) can switch pipeline roles off for timing experiments; the results are
+// then wrong. The shipped build compiles the switches out.
+#ifdef QM_DEBUG
+#define QM_GEMM_DEBUG_BIT(b) ((a.debug & (b)) != 0)
+#else
+#define QM_GEMM_DEBUG_BIT(b) false
+#endif
+
 using namespace qm;
 
 namespace {
@@ -151,7 +159,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                 const int s = kc % kStages;
                 const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
                 if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); break; }
-                if (a.debug & 2) { mbar_arrive(full_b + 8 * s); continue; }
+                if (QM_GEMM_DEBUG_BIT(2)) { mbar_arrive(full_b + 8 * s); continue; }
                 mbar_expect_tx(full_b + 8 * s, (uint32_t)(KS * b_tile));
 #pragma unroll
                 for (int j = 0; j < KS; j++)
@@ -179,7 +187,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                     const uint64_t bdesc = smem_desc(smem_base + s * stage_bytes + a_bytes + j * b_tile);
 #pragma unroll
                     for (int sub = 0; sub < NSUB; sub++)
-                        for (int nb = 0; nb < BN && !(a.debug & 4); nb += 256)
+                        for (int nb = 0; nb < BN && !QM_GEMM_DEBUG_BIT(4); nb += 256)
 #pragma unroll
                             for (int k16 = 0; k16 < kBK / 16; k16++)   // 16 bf16 = 32 bytes = 2 descriptor units
                                 umma_f16(tmem_base + (uint32_t)(sub * BN + nb), adesc + sub * (kATile >> 4) + 2 * k16,
@@ -239,7 +247,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                 const int p = ((kc_lo + kc) * KS + j) & 3;
 #pragma unroll
                 for (int sub = 0; sub < NSUB; sub++) {
-                    if (a.debug & 1) break;
+                    if (QM_GEMM_DEBUG_BIT(1)) break;
                     // scales and minima of sub-blocks 2p (low nibbles, columns 0..31) and 2p+1 (high, 32..63)
                     const uint4 h4 = hd[j][sub];
                     uint32_t av[2], bv[2];

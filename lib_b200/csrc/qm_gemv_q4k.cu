@@ -999,9 +999,20 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
 
     const uint8_t *c_stage = my_stages;   // consumer slot
     bool dead = false;
+#ifdef QM_DEBUG
+    // debug builds, a.debug == 9: time stamps of every op's phases as seen by thread 0 of the first and last CTA
+#define QM_DD_MARK(k)                                                                                             \
+    do {                                                                                                          \
+        if (a.debug == 9 && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && opi < 480)            \
+            reinterpret_cast<unsigned long long *>(a.status + 16)[(opi * 2 + (blockIdx.x != 0)) * 4 + (k)] = gtime(); \
+    } while (0)
+#else
+#define QM_DD_MARK(k) do { } while (0)
+#endif
 
     for (int opi = 0; opi < a.nops; opi++) {
         const QmOp *po = ops + opi;
+        QM_DD_MARK(0);
         const int nun = __ldg(&po->units);
         const int xop = __ldg(&po->xop);
         const float *opx = ldg_ptr(&po->x), *opx2 = ldg_ptr(&po->x2);
@@ -1085,6 +1096,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             }
         }
         __syncthreads();
+        QM_DD_MARK(1);
 
         // RMS normalisation is a scalar per activation row: it multiplies the finished sums
         float myscale = 1.f;
@@ -1221,6 +1233,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             flush(tile, i, seg_end, accF);
             i = seg_end;
         }
+        QM_DD_MARK(2);
         __syncthreads();
         if (fin_tile >= 0) {
             // partial sums of the warps that worked on the tile before this one, in warp order
@@ -1235,6 +1248,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                 if (r < rows) store_y(opy + (int64_t)j * ldy + r, sum);
             }
         }
+        QM_DD_MARK(3);
     }
 }
 

@@ -263,7 +263,8 @@ extern "C" int32_t qm_last_status(qm_ctx *c, uint32_t *status) {
     return (*status & QM_STATUS_TIMEOUT) ? QM_ERR_TIMEOUT : QM_OK;
 }
 
-// Debug aid: raw copy of the device status block (status word + phase timestamps).
+#ifdef QM_DEBUG
+// Debug builds only: raw copy of the device status block (status word + phase timestamps).
 extern "C" __attribute__((visibility("default"))) int32_t qm_debug_status(qm_ctx *c, void *out, int64_t bytes) {
     CHECK_CTX(c);
     CtxGuard g(c);
@@ -272,6 +273,7 @@ extern "C" __attribute__((visibility("default"))) int32_t qm_debug_status(qm_ctx
     DRV(c->drv->cuMemcpyDtoH_v2(out, c->status_dev, (size_t)std::min<int64_t>(bytes, 32768)));
     return QM_OK;
 }
+#endif
 
 extern "C" int64_t qm_launch_count(qm_ctx *c) {
     if (!c || c->magic != QM_CTX_MAGIC) return -1;
@@ -731,8 +733,10 @@ static int32_t fused_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev,
     a.depth = p.depth;
     a.max_units = p.max_units;
     a.cpm = p.cpm;
+#ifdef QM_DEBUG
     a.debug = env_int("QM_DEBUG_SKIP", 0);
     a.debug_slot = env_int("QM_DEBUG_OP", 0);
+#endif
     a.wait_cycles = qm_wait_cycles();
     const bool coop = p.slices > 1;  // K slices meet at a grid barrier: all CTAs must be co-resident
     if (coop) DRV(c->drv->cuMemsetD32Async(c->gridbar_dev, 0, 1, c->stream));
@@ -908,7 +912,9 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     a.up_offset = (int32_t)(w->rows / 2);
     a.h = (uint16_t *)(uintptr_t)g.h_dev;
     a.ldh = g.ldh;
+#ifdef QM_DEBUG
     a.debug = env_int("QM_GEMM_DEBUG", 0);
+#endif
     const unsigned smem = 1024 + stages * stage_bytes + 256;
     void *params[1] = {&a};
     CUlaunchConfig cfg;

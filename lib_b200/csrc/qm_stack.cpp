@@ -428,8 +428,10 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
     a.depth = p.depth;
     a.max_units = p.max_units;
     a.cpm = p.cpm;
+#ifdef QM_DEBUG
     a.debug = qm_env_int("QM_DEBUG_SKIP", 0);
     a.debug_slot = qm_env_int("QM_DEBUG_OP", 0);
+#endif
     a.wait_cycles = qm_wait_cycles();
     DRV(c->drv->cuMemsetD32Async(s->sync_dev[m], 0, s->sync_bytes[m] / 4, c->stream));
     if (s->fused_dd[m]) {

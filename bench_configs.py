@@ -8,11 +8,12 @@
      over the N GPUs and the tokens exchanged by NCCL all-to-all)
   7  Q4_K decode GEMV at the Llama-3-8B matrix shapes, one matrix at a time, batch 1 and 8
 
-Run as `python lib_b200/bench_configs.py --config 3 [--m 2048] [--copies 4] [--iters 10]`.
+Run as `python bench_configs.py --config 3 [--m 2048] [--copies 4] [--iters 10]`; bench.py runs
+short versions of the same cases for its `other_configs` block.
 Each case prints one JSON line.  Every case cycles through enough copies of the weights to
 exceed the 126 MB L2 (or `--copies`), records the launches in a CUDA graph, and is timed with
 CUDA events on the launching stream after three warm-up replays.  Rooflines are against the
-measured peaks in MEASURED_PEAKS.json beside this package (fallback 6650 GB/s, 1590 TFLOP/s)."""
+measured peaks in MEASURED_PEAKS.json beside this file (fallback 6650 GB/s, 1590 TFLOP/s)."""
 import argparse
 import json
 import os
@@ -20,7 +21,7 @@ import sys
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
@@ -29,6 +30,7 @@ import lib_b200  # noqa: E402
 from lib_b200 import _capi, synth  # noqa: E402
 
 Q4_0, Q8_0, Q4_K = 2, 8, 12
+PDL = _capi.FLAG_PDL
 
 
 def peaks():
@@ -82,7 +84,7 @@ def timed_eager(ctx, enqueue, iters):
 
 
 def gemv_case(ctx, fmt, rows, cols, m, copies, iters, flags):
-    dev = torch.device("cuda:0")
+    dev = torch.device("cuda", torch.cuda.current_device())
     nbytes = synth.gguf_bytes(fmt, rows, cols)
     copies = copies or max(2, int(400e6 // nbytes))
     raw = synth.weights(fmt, rows, cols, 1)
@@ -105,7 +107,7 @@ def gemv_case(ctx, fmt, rows, cols, m, copies, iters, flags):
 
 
 def gemm_case(ctx, m, copies, iters, n=4096, k=4096):
-    dev = torch.device("cuda:0")
+    dev = torch.device("cuda", torch.cuda.current_device())
     copies = copies or 16
     raw = synth.weights(Q4_K, n, k, 1)
     ws = [ctx.store_upload(Q4_K, n, k, raw) for _ in range(copies)]
@@ -119,14 +121,19 @@ def gemm_case(ctx, m, copies, iters, n=4096, k=4096):
     ms = timed_graph(ctx, enqueue, iters) / copies
     for w in ws:
         w.free()
-    _, tf, which = peaks()
+    hbm, tf, which = peaks()
     tflops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-    return {"op": "matmul_bf16", "format": "Q4_K", "n": n, "k": k, "m": m, "us": round(ms * 1e3, 2),
-            "TFLOPs": round(tflops, 1), "frac_tensor": round(tflops / tf, 3), "peak": which, "copies": copies}
+    gbs = (synth.gguf_bytes(Q4_K, n, k) + 2.0 * m * k + 4.0 * m * n) / (ms * 1e-3) / 1e9
+    out = {"op": "matmul_bf16", "format": "Q4_K", "n": n, "k": k, "m": m, "us": round(ms * 1e3, 2),
+           "TFLOPs": round(tflops, 1), "frac_tensor": round(tflops / tf, 3), "GBps": round(gbs, 1),
+           "frac_hbm": round(gbs / hbm, 3), "peak": which, "copies": copies}
+    # below the ridge (peak flops / peak bytes per second) a case is bound by HBM, above it by the tensor cores
+    out["bound"] = "hbm" if 2.0 * m * n * k / (synth.gguf_bytes(Q4_K, n, k) + 2.0 * m * k + 4.0 * m * n) < tf * 1e3 / hbm else "tensor"
+    return out
 
 
 def moe_case(ctx, tokens, iters, hidden=4096, ffn=14336, experts=8, topk=2):
-    dev = torch.device("cuda:0")
+    dev = torch.device("cuda", torch.cuda.current_device())
     gu = [ctx.store_upload(Q4_K, 2 * ffn, hidden, synth.weights(Q4_K, 2 * ffn, hidden, 10 + e)) for e in range(experts)]
     dn = [ctx.store_upload(Q4_K, hidden, ffn, synth.weights(Q4_K, hidden, ffn, 30 + e)) for e in range(experts)]
     x = torch.randn(tokens, hidden, device=dev).to(torch.bfloat16)
@@ -140,6 +147,8 @@ def moe_case(ctx, tokens, iters, hidden=4096, ffn=14336, experts=8, topk=2):
         ctx.moe_grouped(gu, dn, x.data_ptr(), tokens, hidden, ids.data_ptr(), wts.data_ptr(), topk, out.data_ptr(), hidden)
 
     ms = timed_eager(ctx, enqueue, iters)
+    for w in gu + dn:
+        w.free()
     _, tf, which = peaks()
     flops = 2.0 * tokens * topk * 3 * hidden * ffn
     tflops = flops / (ms * 1e-3) / 1e12

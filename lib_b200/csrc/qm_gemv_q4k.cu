@@ -899,6 +899,18 @@ __device__ __forceinline__ float4 ld_relaxed_v4(const float *p) {
 __device__ __forceinline__ void st_relaxed_f32(float *p, float v) {
     asm volatile("st.relaxed.gpu.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
 }
+// System scope: the other party is another GPU (tensor-parallel launches).
+__device__ __forceinline__ float4 ld_relaxed_sys_v4(const float *p) {
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_f32(float *p, float v) {
+    asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
 // "Not yet written": a NaN that no arithmetic here produces (sums of products give the canonical
 // quiet NaN; fp16 scales widen to NaNs whose low 13 bits are zero).
 constexpr uint32_t kUnwritten = 0xFFFFFFFFu;
@@ -915,7 +927,12 @@ __device__ __forceinline__ void cp_async_wait_n() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int CPM, int D>
+// TP (tensor parallel): this GPU computes a row slice of every op and stores each result into
+// the same place of every GPU's activation arena (plain peer stores over NVLink); consumers
+// poll their own arena only, so no barrier crosses the GPUs inside a step. One barrier over the
+// GPUs ends the launch: when it returns, every slice of the step has arrived everywhere, which
+// is what lets the host refill the other arena half with the "not yet written" pattern.
+template <int CPM, int D, bool TP>
 __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     constexpr int C = 16;                       // warps per CTA
     constexpr int NL = CPM == 4 ? 3 : 2;        // limbs per activation row
@@ -1033,12 +1050,12 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             auto load_x = [&](int idx, float4 (&r)[4]) {
                 const int j = idx / nun, ul = idx - j * nun;
                 const float *xp = opx + (int64_t)j * ldx + ul * QM_K_UNIT + lane * 8;
-                r[0] = ld_relaxed_v4(xp);
-                r[1] = ld_relaxed_v4(xp + 4);
+                r[0] = TP ? ld_relaxed_sys_v4(xp) : ld_relaxed_v4(xp);
+                r[1] = TP ? ld_relaxed_sys_v4(xp + 4) : ld_relaxed_v4(xp + 4);
                 if (xop >= 2) {
                     const float *x2p = opx2 + (int64_t)j * ldx + ul * QM_K_UNIT + lane * 8;
-                    r[2] = ld_relaxed_v4(x2p);
-                    r[3] = ld_relaxed_v4(x2p + 4);
+                    r[2] = TP ? ld_relaxed_sys_v4(x2p) : ld_relaxed_v4(x2p);
+                    r[3] = TP ? ld_relaxed_sys_v4(x2p + 4) : ld_relaxed_v4(x2p + 4);
                 }
             };
             for (int base = warp; base < total; base += kRounds * C) {
@@ -1122,7 +1139,12 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
 
         auto store_y = [&](float *yp, float val) {   // a result must never look like "not yet written"
             if (__float_as_uint(val) == kUnwritten) val = __uint_as_float(0x7FC00000u);
-            st_relaxed_f32(yp, val);
+            if (TP) {
+                for (int p = 0; p < a.tp_world; p++)   // the same place of every GPU's arena, this one included
+                    st_relaxed_sys_f32(reinterpret_cast<float *>(reinterpret_cast<char *>(yp) + a.peer_delta[p]), val);
+            } else {
+                st_relaxed_f32(yp, val);
+            }
         };
         // Ends a tile's segment [s0, s1) of this warp: stores the outputs if the warp had the whole
         // tile, else leaves its partial sums for the warp that reaches the tile's end.
@@ -1250,6 +1272,34 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         }
         QM_DD_MARK(3);
     }
+    if (TP) {
+        // The launch ends only when every GPU's stores of this step have been performed everywhere:
+        // each CTA fences at system scope and arrives at the local counter; the last one tells the
+        // peers (its GPU's flag in their arenas takes the launch's epoch) and waits, bounded, for theirs.
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence_system();
+            const unsigned int old = atomicAdd(a.grid_bar, 1u);
+            if (old + 1 == gridDim.x) {
+                __threadfence_system();
+                const unsigned int epoch = a.tp_epoch0 + 1;
+                for (int p = 0; p < a.tp_world; p++)
+                    if (p != a.tp_rank)
+                        st_release_sys(reinterpret_cast<unsigned int *>(
+                                           reinterpret_cast<char *>(a.tp_flags + a.tp_rank) + a.peer_delta[p]), epoch);
+                const long long t0 = clock64();
+                for (int p = 0; p < a.tp_world; p++) {
+                    if (p == a.tp_rank) continue;
+                    while (!dead && (int)(ld_acquire_sys(a.tp_flags + p) - epoch) < 0) {
+                        if (clock64() - t0 > a.wait_cycles) {
+                            atomicOr(a.status, QM_STATUS_TIMEOUT);
+                            dead = true;
+                        }
+                    }
+                }
+            }
+        }
+    }
 }
 
 }  // namespace
@@ -1275,21 +1325,39 @@ extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
 // three limbs (four ring stages at one row, three at two), three or four rows with two limbs.
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_dd_c4d4(const __grid_constant__ QmFusedArgs a) {
-    dd_body<4, 4>(a);
+    dd_body<4, 4, false>(a);
 }
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_dd_c4d3(const __grid_constant__ QmFusedArgs a) {
-    dd_body<4, 3>(a);
+    dd_body<4, 3, false>(a);
 }
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_dd_c2d3(const __grid_constant__ QmFusedArgs a) {
-    dd_body<2, 3>(a);
+    dd_body<2, 3, false>(a);
 }
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_dd_c2d2(const __grid_constant__ QmFusedArgs a) {
-    dd_body<2, 2>(a);
+    dd_body<2, 2, false>(a);
 }
-// Tensor-parallel variants: outputs go to every peer's arena, barriers span the GPUs.
+// The same, tensor parallel: results are stored into every GPU's arena, one barrier over the
+// GPUs ends the launch.
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_dd_c4d4_tp(const __grid_constant__ QmFusedArgs a) {
+    dd_body<4, 4, true>(a);
+}
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_dd_c4d3_tp(const __grid_constant__ QmFusedArgs a) {
+    dd_body<4, 3, true>(a);
+}
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_dd_c2d3_tp(const __grid_constant__ QmFusedArgs a) {
+    dd_body<2, 3, true>(a);
+}
+extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
+    qm_fused_q4k_dd_c2d2_tp(const __grid_constant__ QmFusedArgs a) {
+    dd_body<2, 2, true>(a);
+}
+// Tensor-parallel variants with barriers: outputs go to every peer's arena, barriers span the GPUs.
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt1_tp(const __grid_constant__ QmFusedArgs a) {
     fused_body<1, false, true>(a);

@@ -27,7 +27,13 @@ struct qm_stack {
     // q|k|v, o, gate|up and down outputs (rows packed for the batch m of the step). Every
     // matvec has an output buffer of its own, which lets dependent matvecs hand over through
     // the data itself (see build_fused).
-    CUdeviceptr h0, act;
+    // Tensor-parallel stacks hold two such halves and alternate between them from step to step:
+    // while a step runs in one half, the other is refilled with the "not yet written" pattern
+    // for the next step (a peer may start that step, and store into this GPU's arena, before this
+    // GPU has left the current one). `act` is the half of the most recent step.
+    CUdeviceptr h0, act, act_half[2];
+    int cur_half;
+    int half_m[2];              // batch of the last step run in each half (0: the half is all "not yet written")
     size_t act_bytes;
     CUgraphExec graph[9];
     CUdeviceptr ops_dev[9];     // fused op lists, one per batch size
@@ -41,6 +47,7 @@ struct qm_stack {
     bool fused_img[9];          // the op list uses activation images
     bool fused_dd[9];           // the op list hands over through the data (no grid barriers)
     int fused_dd_kernel[9];
+    int fused_half0[9];         // tensor-parallel: arena half that the first copy of the op list addresses
     // tensor-parallel: one arena holds all activation buffers and the peers' arrival flags; the
     // peers map it through CUDA IPC and this GPU stores its row slices into all of them
     int tp_world, tp_rank;
@@ -80,7 +87,7 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
         return QM_ERR_SHAPE;
     if ((hidden & 3) || (kv_dim & 3) || (ffn & 3)) return QM_ERR_SHAPE;
     if (world < 1 || world > QM_MAX_PEERS || rank < 0 || rank >= world) return QM_ERR_ARG;
-    if (world > 1 && ((hidden % (16 * world)) || ((2 * ffn) % (16 * world))))
+    if (world > 1 && ((hidden % (16 * world)) || ((2 * ffn) % (16 * world)) || ((hidden + 2 * kv_dim) % (16 * world))))
         return QM_ERR_SHAPE;   // every GPU's row slice must be whole 16-row tiles
     qm_stack *s = new (std::nothrow) qm_stack();
     if (!s) return QM_ERR_NOMEM;
@@ -106,6 +113,9 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
     s->use_fused = true;
     s->last_m = 0;
     s->h0 = s->act = 0;
+    s->act_half[0] = s->act_half[1] = 0;
+    s->cur_half = 0;
+    s->half_m[0] = s->half_m[1] = 0;
     CtxGuard g(c);
     CUresult r = g.rc;
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
@@ -114,14 +124,19 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
     if (world == 1) {
         if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->h0, b_h0);
         if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->act, s->act_bytes);
+        s->act_half[0] = s->act_half[1] = s->act;
     } else {
-        s->flags_off = b_h0 + s->act_bytes;
+        s->flags_off = b_h0 + 2 * s->act_bytes;
         s->arena_bytes = s->flags_off + 256;
         if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->arena, s->arena_bytes);
         if (r == CUDA_SUCCESS) r = c->drv->cuMemsetD8Async(s->arena, 0, s->arena_bytes, c->stream);
-        if (r == CUDA_SUCCESS) r = c->drv->cuStreamSynchronize(c->stream);
         s->h0 = s->arena;
-        s->act = s->h0 + b_h0;
+        s->act_half[0] = s->h0 + b_h0;
+        s->act_half[1] = s->act_half[0] + s->act_bytes;
+        s->act = s->act_half[0];
+        // both halves start as "not yet written" (all ones)
+        if (r == CUDA_SUCCESS) r = c->drv->cuMemsetD8Async(s->act_half[0], 0xFF, 2 * s->act_bytes, c->stream);
+        if (r == CUDA_SUCCESS) r = c->drv->cuStreamSynchronize(c->stream);
     }
     if (r != CUDA_SUCCESS) {
         qm_stack_destroy(c, s);
@@ -231,9 +246,9 @@ extern "C" int32_t qm_stack_set_layer(qm_ctx *c, qm_stack *s, int32_t layer, qm_
                       qm_weight_from_handle(down)};
     for (QmWeight *p : w)
         if (!p) return QM_ERR_ARG;
-    // tensor-parallel: q|k|v and o whole on every rank, gate|up and down this rank's slice of the rows
+    // tensor-parallel: every matrix is this rank's slice of the rows
     const int64_t W = s->tp_world;
-    const int64_t want[4][2] = {{s->hidden + 2 * s->kv, s->hidden}, {s->hidden, s->hidden},
+    const int64_t want[4][2] = {{(s->hidden + 2 * s->kv) / W, s->hidden}, {s->hidden / W, s->hidden},
                                 {2 * s->ffn / W, s->hidden}, {s->hidden / W, s->ffn}};
     for (int i = 0; i < 4; i++)
         if (w[i]->rows != want[i][0] || w[i]->cols != want[i][1]) return QM_ERR_SHAPE;
@@ -323,13 +338,12 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
         const QmLayer &ly = s->layer[L];
         const LayerBufs b = layer_bufs(s, L, m);
         const CUdeviceptr x0 = L == 0 ? s->h0 : layer_bufs(s, L - 1, m).dn;
-        // Tensor-parallel: the two large matrices (gate|up, down: 81 % of the bytes) are shared — y
-        // points at this rank's rows of the full-width output; q|k|v and o are computed whole by
-        // every GPU, which costs less than the barrier over the GPUs that sharing them would add.
+        // Tensor-parallel: every matrix is sliced by rows (GPU r of g holds rows [r*N/g, (r+1)*N/g));
+        // y points at this rank's rows of the full-width output and the results go to every GPU's arena.
         const bool tp = s->tp_world > 1;
         const size_t R = (size_t)s->tp_rank * 4;
-        add_matvec(ly.qkv, x0, 0, s->hidden, b.qkv, qkv_ld, QM_XOP_RMSNORM, L == 0, false);
-        add_matvec(ly.o, b.qkv, 0, qkv_ld, b.o, s->hidden, QM_XOP_RMSNORM, false, false);
+        add_matvec(ly.qkv, x0, 0, s->hidden, b.qkv + R * ly.qkv->rows, qkv_ld, QM_XOP_RMSNORM, L == 0, tp);
+        add_matvec(ly.o, b.qkv, 0, qkv_ld, b.o + R * ly.o->rows, s->hidden, QM_XOP_RMSNORM, false, tp);
         add_matvec(ly.gu, b.o, 0, s->hidden, b.gu + R * ly.gu->rows, 2 * s->ffn, QM_XOP_RMSNORM, false, tp);
         add_matvec(ly.dn, b.gu, b.gu + (size_t)s->ffn * 4, 2 * s->ffn, b.dn + R * ly.dn->rows,
                    s->hidden, QM_XOP_ADD_RMSNORM, false, tp);
@@ -345,8 +359,7 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     const int min_m = qm_env_int("QM_IMAGE_MIN_M", 4);
     const int dd_kernel = p.cpm == 4 ? (p.depth == 4 ? QM_K_FUSED_Q4K_DD_C4D4 : p.depth == 3 ? QM_K_FUSED_Q4K_DD_C4D3 : -1)
                                      : (p.depth == 3 ? QM_K_FUSED_Q4K_DD_C2D3 : p.depth == 2 ? QM_K_FUSED_Q4K_DD_C2D2 : -1);
-    bool dd = s->tp_world == 1 && p.nt == 1 && p.consumers == 16 && dd_kernel >= 0 && m < min_m &&
-              qm_env_int("QM_DD", 1) != 0;
+    bool dd = p.nt == 1 && p.consumers == 16 && dd_kernel >= 0 && m < min_m && qm_env_int("QM_DD", 1) != 0;
     for (const QmOp &op : ops)
         if (op.units != op.units_total || op.accumulate) dd = false;
     for (size_t k = 1; k < ops.size() && !dd; k++)
@@ -392,6 +405,23 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
             uses_img = true;
         }
     }
+    // tensor-parallel: a second copy of the list for the other arena half
+    const size_t nops = ops.size();
+    if (s->tp_world > 1) {
+        const CUdeviceptr lo = s->act, other = s->act_half[s->act == s->act_half[0] ? 1 : 0];
+        auto moved = [&](const void *ptr) -> uintptr_t {
+            const CUdeviceptr a0 = (CUdeviceptr)(uintptr_t)ptr;
+            return (uintptr_t)((a0 >= lo && a0 < lo + s->act_bytes) ? a0 - lo + other : a0);
+        };
+        for (size_t k = 0; k < nops; k++) {
+            QmOp op = ops[k];
+            op.x = (const float *)moved(op.x);
+            op.x2 = (const float *)moved(op.x2);
+            op.y = (float *)moved(op.y);
+            ops.push_back(op);
+        }
+        s->fused_half0[m] = s->act == s->act_half[0] ? 0 : 1;   // which half the first copy addresses
+    }
     if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&dev, ops.size() * sizeof(QmOp));
     if (r == CUDA_SUCCESS) r = c->drv->cuMemcpyHtoD_v2(dev, ops.data(), ops.size() * sizeof(QmOp));
     if (r != CUDA_SUCCESS) {
@@ -405,7 +435,7 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     s->sync_dev[m] = sync;
     s->sync_bytes[m] = sync_bytes;
     s->img_units[m] = img_units;
-    s->fused_nops[m] = (int)ops.size();
+    s->fused_nops[m] = (int)nops;
     s->fused_ncross[m] = ncross;
     s->fused_img[m] = uses_img;
     s->fused_dd[m] = dd;
@@ -434,26 +464,46 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
 #endif
     a.wait_cycles = qm_wait_cycles();
     DRV(c->drv->cuMemsetD32Async(s->sync_dev[m], 0, s->sync_bytes[m] / 4, c->stream));
+    // cooperative: every CTA must be resident (grid barriers, or CTAs polling each other's outputs)
+    if (s->tp_world > 1) {
+        if (!s->peers_open) return QM_ERR_STATE;
+        const bool second = (s->act == s->act_half[0] ? 0 : 1) != s->fused_half0[m];
+        a.ops = (const QmOp *)(uintptr_t)(s->ops_dev[m] + (second ? (size_t)a.nops * sizeof(QmOp) : 0));
+        a.tp_world = s->tp_world;
+        a.tp_rank = s->tp_rank;
+        a.tp_epoch0 = s->tp_epoch;
+        a.tp_flags = (unsigned int *)(uintptr_t)(s->arena + s->flags_off);
+        for (int q = 0; q < s->tp_world; q++) a.peer_delta[q] = (int64_t)s->peer_base[q] - (int64_t)s->arena;
+        // the half this step does not use is refilled for the next step; its last readers and writers
+        // finished with the step before this one (every launch ends with a barrier over the GPUs)
+        // (only the part the last step in that half wrote: a step of batch m touches the first
+        // layers*m rows' worth of the half)
+        const int cur = s->act == s->act_half[0] ? 0 : 1, other = cur ^ 1;
+        if (s->half_m[other] > 0) {
+            const size_t per_row = 3 * (size_t)s->hidden + 2 * (size_t)s->kv + 2 * (size_t)s->ffn;
+            DRV(c->drv->cuMemsetD8Async(s->act_half[other], 0xFF, (size_t)s->layers * s->half_m[other] * per_row * 4,
+                                        c->stream));
+            s->half_m[other] = 0;
+        }
+        s->half_m[cur] = m;
+        if (s->fused_dd[m]) {
+            a.tp_counter = 0;
+            s->tp_epoch += 1;   // one barrier over the GPUs per launch
+            return qm_launch_ex(c, s->fused_dd_kernel[m] + (QM_K_FUSED_Q4K_DD_C4D4_TP - QM_K_FUSED_Q4K_DD_C4D4),
+                                (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32, (unsigned)p.smem, &a, false, true);
+        }
+        a.tp_counter = s->tp_counter ? 1u : 0u;
+        // the epoch counts the launch's barriers over all GPUs; the counter form counts CTA arrivals
+        s->tp_epoch += (unsigned int)s->fused_ncross[m] * (s->tp_counter ? (unsigned int)(qm_fused_grid(c) * s->tp_world) : 1u);
+        return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1_TP : QM_K_FUSED_Q4K_NT2_TP, (unsigned)qm_fused_grid(c),
+                            (unsigned)p.consumers * 32, (unsigned)p.smem, &a, false, true);
+    }
     if (s->fused_dd[m]) {
         // every output word of the step starts as "not yet written" (all ones)
         const size_t bytes = (size_t)(layer_bufs(s, s->layers, m).qkv - s->act);
         DRV(c->drv->cuMemsetD8Async(s->act, 0xFF, bytes, c->stream));
         return qm_launch_ex(c, s->fused_dd_kernel[m], (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32,
                             (unsigned)p.smem, &a, false, true);
-    }
-    // cooperative: the grid barrier between dependent matvecs needs every CTA resident
-    if (s->tp_world > 1) {
-        if (!s->peers_open) return QM_ERR_STATE;
-        a.tp_world = s->tp_world;
-        a.tp_rank = s->tp_rank;
-        a.tp_epoch0 = s->tp_epoch;
-        a.tp_counter = s->tp_counter ? 1u : 0u;
-        // the epoch counts the launch's barriers over all GPUs; the counter form counts CTA arrivals
-        s->tp_epoch += (unsigned int)s->fused_ncross[m] * (s->tp_counter ? (unsigned int)(qm_fused_grid(c) * s->tp_world) : 1u);
-        a.tp_flags = (unsigned int *)(uintptr_t)(s->arena + s->flags_off);
-        for (int q = 0; q < s->tp_world; q++) a.peer_delta[q] = (int64_t)s->peer_base[q] - (int64_t)s->arena;
-        return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1_TP : QM_K_FUSED_Q4K_NT2_TP, (unsigned)qm_fused_grid(c),
-                            (unsigned)p.consumers * 32, (unsigned)p.smem, &a, false, true);
     }
     const int kern = s->fused_img[m] ? (p.nt == 1 ? QM_K_FUSED_Q4K_NT1_IMG : QM_K_FUSED_Q4K_NT2_IMG)
                                      : (p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2);
@@ -488,7 +538,10 @@ static int32_t step_device(qm_ctx *c, qm_stack *s, int m) {
     s->last_m = m;
     if (s->tp_world > 1) {   // tensor-parallel steps exist as the one fused launch only
         int32_t rc = s->ops_dev[m] ? QM_OK : build_fused(c, s, m);
-        return rc ? rc : launch_fused(c, s, m);
+        if (rc) return rc;
+        s->cur_half ^= 1;    // this step's half: the one refilled during the step before
+        s->act = s->act_half[s->cur_half];
+        return launch_fused(c, s, m);
     }
     if (s->use_graph && s->use_fused) {
         int32_t rc = s->ops_dev[m] ? QM_OK : build_fused(c, s, m);
@@ -555,7 +608,7 @@ extern "C" int32_t qm_stack_step_host(qm_ctx *c, qm_stack *s, const float *x_hos
     DRV(d->cuMemcpyDtoHAsync_v2(h_host, layer_bufs(s, s->layers - 1, m).dn, (size_t)m * s->hidden * 4, c->stream));
     if (kv_host && s->kv) {
         const int64_t qkv_ld = s->hidden + 2 * s->kv;
-        // (tensor-parallel: q|k|v is computed whole by every GPU, so all rows are local)
+        // (tensor-parallel: every GPU's slice of q|k|v has been stored into this arena)
         for (int L = 0; L < s->layers; L++)
             for (int j = 0; j < m; j++)
                 DRV(d->cuMemcpyDtoHAsync_v2(kv_host + ((size_t)L * m + j) * 2 * s->kv,

@@ -85,13 +85,20 @@ class SingleGpuDecode:
     def step_host(self, x, h, kv):
         self.stack.step_host(x, h_out=h, kv_out=kv)
 
+    def close(self):
+        """Frees the stack and its weights."""
+        weights = [w for layer in self.stack.weights for w in layer]
+        self.stack.close()
+        for w in weights:
+            w.free()
+
 
 class PeerTensorParallelDecode:
     """Row-sharded decode step as ONE persistent launch per GPU (qm_stack_create_tp): rank r
-    holds rows [r*N/g, (r+1)*N/g) of gate|up and down (q|k|v and o whole) and stores its slice
-    of those matvecs straight into all peers' activation buffers over NVLink; the barrier after
-    a shared matvec spans the GPUs. torch.distributed only carries the 64-byte IPC handles
-    at set-up."""
+    holds rows [r*N/g, (r+1)*N/g) of every matrix and stores its slice of each matvec straight
+    into all peers' activation buffers over NVLink; consumers poll their own arena for the words
+    they read, so no barrier crosses the GPUs inside a step (one ends it). torch.distributed only
+    carries the 64-byte IPC handles at set-up."""
 
     def __init__(self, ctx, layers, hidden, kv, ffn, fmt, seed, rank, world, m_max=8, barrier=True):
         """barrier=False: the caller runs a collective of its own on all ranks before the first
@@ -102,8 +109,7 @@ class PeerTensorParallelDecode:
         for L in range(layers):
             ws = []
             for i, (rows, cols, parts) in enumerate(stacked(layer_tensors(fmt, hidden, kv, ffn, seed, L))):
-                # q|k|v and o whole on every rank; gate|up and down sliced by rows
-                lo, hi = (0, rows) if i < 2 else shard_range(rows, rank, world)
+                lo, hi = shard_range(rows, rank, world)   # every matrix sliced by rows
                 ws.append(upload_rows(ctx, fmt, rows, cols, parts, lo, hi))
             self.stack.set_layer(L, *ws)
         handles = [None] * world

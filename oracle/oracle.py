@@ -36,6 +36,7 @@ def _load():
     lib.qo_route.argtypes = [p, i32, i32, i32, p, p, p]
     lib.qo_matvec.argtypes = [i32, p, i64, i64, i64, p, i32, i64, p, i64]
     lib.qo_matvec_f32_threaded.argtypes = [i32, p, i64, i64, i64, p, i32, i64, p, i64, i32]
+    lib.qo_matvec_faithful.argtypes = [i32, p, i64, i64, i64, p, i32, i64, p, i64]
     lib.qo_rmsnorm.argtypes = [p, i64, ctypes.c_float, p]
     lib.qo_rmsnorm.restype = None
     return lib
@@ -131,6 +132,17 @@ def MatVec(fmt, data, rows, cols, x, threads=0):
         rc = _lib.qo_matvec(fmt, a.ctypes.data, a.size, rows, cols, x2.ctypes.data, m,
                             x2.shape[1], y.ctypes.data, rows)
     _raise(rc)
+    return y[0] if x.ndim == 1 else y
+
+
+def MatVecFaithful(fmt, data, rows, cols, x):
+    """Timed single-thread baseline: dequantize the whole matrix to float32, then dot in float32."""
+    a = _u8(data)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    x2 = x.reshape(1, -1) if x.ndim == 1 else x
+    y = np.empty((x2.shape[0], rows), dtype=np.float32)
+    _raise(_lib.qo_matvec_faithful(fmt, a.ctypes.data, a.size, rows, cols, x2.ctypes.data, x2.shape[0],
+                                   x2.shape[1], y.ctypes.data, rows))
     return y[0] if x.ndim == 1 else y
 
 

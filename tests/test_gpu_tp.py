@@ -1,6 +1,6 @@
-"""Tensor-parallel decode stack on two GPUs (one persistent launch per GPU, output slices
-stored into the peer's buffers over NVLink, barriers spanning the GPUs) against the same stack
-on one GPU. Needs two visible GPUs; skipped otherwise. The ranks run as child processes and
+"""Tensor-parallel decode stack on two GPUs (every matrix sliced by rows, one persistent launch
+per GPU, output slices stored into the peer's buffers over NVLink and polled there) against the
+same stack on one GPU. Needs two visible GPUs; skipped otherwise. The ranks run as child processes and
 exchange the 64-byte IPC handles over a gloo group."""
 import os
 import socket
@@ -30,19 +30,15 @@ one = decode.SingleGpuDecode(ctx, layers, hidden, kv, ffn, fmt, seed)
 ok = True
 for m in (1, 3, 8):
     x = synth.activations(m, hidden, 300 + m)
-    for rep in range(3):                       # several steps: the barrier epochs keep growing
+    for rep in range(3):                       # several steps: the arena halves alternate, the epochs grow
         h = np.full((m, hidden), np.nan, np.float32)
         kvb = np.full((layers, m, 2 * kv), np.nan, np.float32)
         tp.step_host(x, h, kvb)
     want, want_kv = one.stack.step_host(x, want_kv=True)
     rc, status = ctx.last_status()
     err = float(np.linalg.norm(h.astype(np.float64) - want) / np.linalg.norm(want))
-    S = (hidden + 2 * kv) // world
-    lo, hi = max(hidden, rank * S), min(hidden + 2 * kv, (rank + 1) * S)
-    kv_ok = True
-    if lo < hi:
-        a, b = kvb[:, :, lo - hidden:hi - hidden], want_kv[:, :, lo - hidden:hi - hidden]
-        kv_ok = bool(np.isfinite(a).all()) and float(np.linalg.norm(a - b) / np.linalg.norm(b)) <= 1e-4
+    # every rank holds all k|v rows: each GPU's slice was stored into every arena
+    kv_ok = bool(np.isfinite(kvb).all()) and float(np.linalg.norm(kvb - want_kv) / np.linalg.norm(want_kv)) <= 1e-4
     good = rc == 0 and status == 0 and bool(np.isfinite(h).all()) and err <= 1e-4 and kv_ok
     print("rank", rank, "m", m, "err", err, "status", rc, status, "kv", kv_ok, "ok", good, flush=True)
     ok = ok and good

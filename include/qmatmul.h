@@ -241,6 +241,9 @@ QM_API int32_t qm_stack_step_host(qm_ctx *ctx, qm_stack *stack, const float *x_h
 /* Activation buffers for per-matvec checks: [0] input, [1] q|k|v of every layer, [2] o,
  * [3] gate|up, [4] down (of the last layer run). */
 QM_API int32_t qm_stack_buffers(qm_ctx *ctx, qm_stack *stack, uint64_t *ptrs5);
+/* info2[0] = K parts the most recent step cut the o projection into (1 = whole), info2[1] = floats
+ * between its partial vectors: ptrs5[2] of qm_stack_buffers then holds partial sums. */
+QM_API int32_t qm_stack_parts(qm_ctx *ctx, qm_stack *stack, int64_t *info2);
 /* 0 = issue the launches one by one; 1 = replay them as a captured graph; 2 (default) = the
  * whole step as one persistent launch where format and shapes allow it, else as 1. */
 QM_API int32_t qm_stack_use_graph(qm_ctx *ctx, qm_stack *stack, int32_t on);

@@ -65,6 +65,7 @@ def _load():
         "qm_stack_step": (i32, [p, p, u64, i32, i64, u64, i64]),
         "qm_stack_step_host": (i32, [p, p, p, i32, p, p]),
         "qm_stack_buffers": (i32, [p, p, ctypes.POINTER(u64)]),
+        "qm_stack_parts": (i32, [p, p, ctypes.POINTER(i64)]),
         "qm_stack_use_graph": (i32, [p, p, i32]),
         "qm_stack_create_tp": (i32, [p, i32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_stack_ipc_handle": (i32, [p, p, p]),
@@ -305,6 +306,12 @@ class Stack:
         ptrs = (ctypes.c_uint64 * 5)()
         _check(lib.qm_stack_buffers(self.ctx._h, self._h, ptrs))
         return [int(v) for v in ptrs]
+
+    def parts(self):
+        """(K parts of the o projection in the most recent step, floats between its partial vectors)."""
+        info = (ctypes.c_int64 * 2)()
+        _check(lib.qm_stack_parts(self.ctx._h, self._h, info))
+        return int(info[0]), int(info[1])
 
     def close(self):
         if self._h:

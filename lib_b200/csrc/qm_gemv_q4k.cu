@@ -959,8 +959,9 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
 
     // This warp's items of op `o`: the CTA owns a run of whole tiles, its items are dealt evenly to
     // the warps in order. Returns the first item and the count in CTA-local coordinates.
-    auto warp_range = [&](int q, int rem, int units, int &tile0, int &lo, int &n, int &wq, int &wrem) {
-        const int c = (int)blockIdx.x;
+    // An op cut into K parts splits the CTAs into as many groups; `c` is then the CTA's index within
+    // its group (q and rem are computed for the group's size).
+    auto warp_range = [&](int q, int rem, int units, int c, int &tile0, int &lo, int &n, int &wq, int &wrem) {
         tile0 = c * q + min(c, rem);
         const int Ic = (q + (c < rem ? 1 : 0)) * units;
         wq = Ic / C;
@@ -970,18 +971,26 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     };
 
     // ---- producer side of the ring: a pointer and a count per op -------------------------------
-    int p_op = -1, p_n = 0;
+    // (the items of a tile's K part are contiguous in the store; the next tile's part follows
+    // p_skip bytes later)
+    int p_op = -1, p_n = 0, p_u = 0, p_units = 1;
+    int64_t p_skip = 0;
     const uint8_t *p_src = nullptr;
     auto p_next_op = [&]() {
         p_n = 0;
         for (p_op++; p_op < a.nops; p_op++) {
             const QmOp *po = ops + p_op;
             int tile0, lo, n, wq, wrem;
-            const int units = __ldg(&po->units);
-            warp_range(__ldg(&po->q), __ldg(&po->rem), units, tile0, lo, n, wq, wrem);
+            const int units = __ldg(&po->units), parts = __ldg(&po->parts), total = __ldg(&po->units_total);
+            const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G;
+            warp_range(__ldg(&po->q), __ldg(&po->rem), units, (int)blockIdx.x - grp * G, tile0, lo, n, wq, wrem);
             if (n > 0) {
+                const int tile = lo / units, u = lo - tile * units;
                 p_n = n;
-                p_src = ldg_ptr(&po->wq) + ((int64_t)tile0 * units + lo) * QM_Q4K_ITEM_BYTES + lane * 16;
+                p_units = units;
+                p_u = units - u;
+                p_skip = (int64_t)(total - units) * QM_Q4K_ITEM_BYTES;
+                p_src = ldg_ptr(&po->wq) + ((int64_t)(tile0 + tile) * total + grp * units + u) * QM_Q4K_ITEM_BYTES + lane * 16;
                 break;
             }
         }
@@ -996,6 +1005,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             cp_async16(p_dst + 1536, p_src + 1536);
             if (lane < 16) cp_async16(p_dst + 2048, p_src + 2048);
             p_src += QM_Q4K_ITEM_BYTES;
+            if (--p_u == 0) { p_src += p_skip; p_u = p_units; }
             if (--p_n == 0) p_next_op();
         }
         cp_async_commit();
@@ -1035,6 +1045,10 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         const float *opx = ldg_ptr(&po->x), *opx2 = ldg_ptr(&po->x2);
         const int64_t ldx = __ldg(&po->ldx);
         const bool norm = xop == 1 || xop == 2;
+        const int parts = __ldg(&po->parts), x_parts = __ldg(&po->x_parts);
+        const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G, cta_in_grp = (int)blockIdx.x - grp * G;
+        const int col0 = grp * nun * QM_K_UNIT;   // first column of this group's K part
+        const int64_t xps = __ldg(&po->x_part_stride);
         // every warp has finished with the activation planes and the partial sums of the op before
         if (opi > 0) __syncthreads();
 
@@ -1049,15 +1063,63 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             __syncwarp();
             auto load_x = [&](int idx, float4 (&r)[4]) {
                 const int j = idx / nun, ul = idx - j * nun;
-                const float *xp = opx + (int64_t)j * ldx + ul * QM_K_UNIT + lane * 8;
+                const float *xp = opx + (int64_t)j * ldx + col0 + ul * QM_K_UNIT + lane * 8;
                 r[0] = TP ? ld_relaxed_sys_v4(xp) : ld_relaxed_v4(xp);
                 r[1] = TP ? ld_relaxed_sys_v4(xp + 4) : ld_relaxed_v4(xp + 4);
                 if (xop >= 2) {
-                    const float *x2p = opx2 + (int64_t)j * ldx + ul * QM_K_UNIT + lane * 8;
+                    const float *x2p = opx2 + (int64_t)j * ldx + col0 + ul * QM_K_UNIT + lane * 8;
                     r[2] = TP ? ld_relaxed_sys_v4(x2p) : ld_relaxed_v4(x2p);
                     r[3] = TP ? ld_relaxed_sys_v4(x2p + 4) : ld_relaxed_v4(x2p + 4);
                 }
             };
+            // x given as several partial vectors (the producer was cut into K parts): all of them are
+            // in flight at once, one (row, unit) pair per warp and round
+            if (x_parts > 1) {
+                for (int idx = warp; idx < total; idx += C) {
+                    const int j = idx / nun, ul = idx - j * nun;
+                    const float *xp = opx + (int64_t)j * ldx + col0 + ul * QM_K_UNIT + lane * 8;
+                    float4 r[8];
+                    long long t0 = 0;
+                    for (;;) {
+                        bool ok = true;
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            if (k < x_parts) {
+                                r[2 * k] = TP ? ld_relaxed_sys_v4(xp + k * xps) : ld_relaxed_v4(xp + k * xps);
+                                r[2 * k + 1] = TP ? ld_relaxed_sys_v4(xp + k * xps + 4) : ld_relaxed_v4(xp + k * xps + 4);
+                            }
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            if (k < x_parts) ok = ok & written4(r[2 * k]) & written4(r[2 * k + 1]);
+                        if (__all_sync(0xffffffffu, ok || dead)) break;
+                        if (t0 == 0) t0 = clock64();
+                        else if (clock64() - t0 > a.wait_cycles) {
+                            if (lane == 0) atomicOr(a.status, QM_STATUS_TIMEOUT);
+                            dead = true;
+                        }
+                    }
+                    float v[8] = {r[0].x, r[0].y, r[0].z, r[0].w, r[1].x, r[1].y, r[1].z, r[1].w};
+#pragma unroll
+                    for (int k = 1; k < 4; k++)
+                        if (k < x_parts) {   // the parts in order: the same sum on every CTA and GPU
+                            v[0] += r[2 * k].x; v[1] += r[2 * k].y; v[2] += r[2 * k].z; v[3] += r[2 * k].w;
+                            v[4] += r[2 * k + 1].x; v[5] += r[2 * k + 1].y; v[6] += r[2 * k + 1].z; v[7] += r[2 * k + 1].w;
+                        }
+                    const float sq = quantize_pair<NT>(v, j, ul, lane, NL, CPM, xs, plane_stride, xsum, sxw);
+                    if (norm) {
+                        if (j != sq_j) {
+                            if (sq_j >= 0) {
+#pragma unroll
+                                for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
+                                if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
+                            }
+                            sq_j = j;
+                            sq_run = 0.f;
+                        }
+                        sq_run += sq;
+                    }
+                }
+            } else
             for (int base = warp; base < total; base += kRounds * C) {
                 float4 raw[kRounds][4];
 #pragma unroll
@@ -1118,11 +1180,40 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         // RMS normalisation is a scalar per activation row: it multiplies the finished sums
         float myscale = 1.f;
         if (norm) {
-            const float inv_cols = 1.f / (float)__ldg(&po->cols), eps = __ldg(&po->eps);
+            const float inv_cols = 1.f / (float)__ldg(&po->cols);
+            const float *ssq_in = ldg_ptr(&po->ssq_in);
+            float *ssq_out = ldg_ptr(&po->ssq_out);
             for (int j = 0; j < M; j++) {
                 float sq = ssq[j * 16 + (lane & 15)];   // the warps' parts, added as a fixed tree
 #pragma unroll
                 for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (parts > 1) {
+                    // a K part leaves its products unscaled; the consumer scales the sum. One CTA of the
+                    // group publishes the part's sum of squares.
+                    if (cta_in_grp == 0 && tid == 0) st_relaxed_f32(ssq_out + grp * 8 + j, sq);
+                    continue;
+                }
+                float eps = __ldg(&po->eps);
+                if (ssq_in) {
+                    // x is c times the sum that was staged, c = rsqrt(ms + eps') of the producer's input:
+                    // normalising c*v with eps equals normalising v with eps / c^2
+                    float ms = 0.f;
+                    long long t0 = 0;
+                    for (int k = 0; k < x_parts; k++) {
+                        float part;
+                        for (;;) {
+                            asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + j) : "memory");
+                            if (__float_as_uint(part) != kUnwritten || dead) break;
+                            if (t0 == 0) t0 = clock64();
+                            else if (clock64() - t0 > a.wait_cycles) {
+                                atomicOr(a.status, QM_STATUS_TIMEOUT);
+                                dead = true;
+                            }
+                        }
+                        ms += part;
+                    }
+                    eps *= ms * __ldg(&po->ssq_in_inv_cols) + __ldg(&po->ssq_in_eps);
+                }
                 const float sc = rsqrtf(sq * inv_cols + eps);
                 if ((CPM == 4 ? (t >> 1) : t) == j) myscale = sc;
             }
@@ -1130,8 +1221,8 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
 
         // ---- stream this warp's items of the op ---------------------------------------------------
         int tile0, lo, n, wq, wrem;
-        warp_range(__ldg(&po->q), __ldg(&po->rem), nun, tile0, lo, n, wq, wrem);
-        float *opy = ldg_ptr(&po->y);
+        warp_range(__ldg(&po->q), __ldg(&po->rem), nun, cta_in_grp, tile0, lo, n, wq, wrem);
+        float *opy = ldg_ptr(&po->y) + (int64_t)grp * __ldg(&po->y_part_stride);
         const int64_t ldy = __ldg(&po->ldy);
         const int rows = __ldg(&po->rows);
         const int hi = lo + n;
@@ -1321,42 +1412,42 @@ extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt2_img(const __grid_constant__ QmFusedArgs a) {
     fused_body<2, true, false>(a);
 }
-// Data-driven variants (no grid barrier between dependent ops): up to two activation rows with
-// three limbs (four ring stages at one row, three at two), three or four rows with two limbs.
-extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
-    qm_fused_q4k_dd_c4d4(const __grid_constant__ QmFusedArgs a) {
-    dd_body<4, 4, false>(a);
+// Data-driven variants (no grid barrier between dependent ops): CPM = 4 mma columns per
+// activation row (up to two rows, three limbs) or 2 (up to four rows, two limbs), D ring stages
+// per warp as shared memory allows; _tp: tensor parallel, results stored into every GPU's arena
+// and one barrier over the GPUs at the end of the launch.
+#define QM_DD_KERNEL(name, cpm, d, tp)                                                       \
+    extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)                     \
+        name(const __grid_constant__ QmFusedArgs a) {                                        \
+        dd_body<cpm, d, tp>(a);                                                              \
+    }
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d2, 4, 2, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d3, 4, 3, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d4, 4, 4, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d2, 2, 2, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d3, 2, 3, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d4, 2, 4, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d2_tp, 4, 2, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d3_tp, 4, 3, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d4_tp, 4, 4, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d2_tp, 2, 2, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d3_tp, 2, 3, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d4_tp, 2, 4, true)
+
+// h = c * (sum of the K parts of the step's last matvec), see QmSumPartsArgs.
+extern "C" __global__ void __launch_bounds__(256) qm_sum_parts(const __grid_constant__ QmSumPartsArgs a) {
+    const int total = a.m * a.n;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const int j = idx / a.n, r = idx - j * a.n;
+        float sum = 0.f, sq = 0.f;
+        for (int k = 0; k < a.nparts; k++) {
+            sum += a.parts[k * a.part_stride + (int64_t)j * a.ld_in + r];
+            sq += a.ssq[k * 8 + j];
+        }
+        a.out[(int64_t)j * a.ld_out + r] = sum * rsqrtf(sq * a.inv_cols + a.eps);
+    }
 }
-extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
-    qm_fused_q4k_dd_c4d3(const __grid_constant__ QmFusedArgs a) {
-    dd_body<4, 3, false>(a);
-}
-extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
-    qm_fused_q4k_dd_c2d3(const __grid_constant__ QmFusedArgs a) {
-    dd_body<2, 3, false>(a);
-}
-extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
-    qm_fused_q4k_dd_c2d2(const __grid_constant__ QmFusedArgs a) {
-    dd_body<2, 2, false>(a);
-}
-// The same, tensor parallel: results are stored into every GPU's arena, one barrier over the
-// GPUs ends the launch.
-extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
-    qm_fused_q4k_dd_c4d4_tp(const __grid_constant__ QmFusedArgs a) {
-    dd_body<4, 4, true>(a);
-}
-extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
-    qm_fused_q4k_dd_c4d3_tp(const __grid_constant__ QmFusedArgs a) {
-    dd_body<4, 3, true>(a);
-}
-extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
-    qm_fused_q4k_dd_c2d3_tp(const __grid_constant__ QmFusedArgs a) {
-    dd_body<2, 3, true>(a);
-}
-extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
-    qm_fused_q4k_dd_c2d2_tp(const __grid_constant__ QmFusedArgs a) {
-    dd_body<2, 2, true>(a);
-}
+
 // Tensor-parallel variants with barriers: outputs go to every peer's arena, barriers span the GPUs.
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt1_tp(const __grid_constant__ QmFusedArgs a) {

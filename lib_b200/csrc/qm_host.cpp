@@ -83,10 +83,11 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_Q4K, "qm_fused_q4k_nt1"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2"},
     {QM_MOD_Q4K, "qm_fused_q4k_nt1_img"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2_img"},
     {QM_MOD_Q4K, "qm_fused_q4k_nt1_tp"},  {QM_MOD_Q4K, "qm_fused_q4k_nt2_tp"},
-    {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d4"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d3"},
-    {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d3"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d2"},
-    {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d4_tp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d3_tp"},
-    {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d3_tp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d2_tp"},
+    {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d2"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d3"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d4"},
+    {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d2"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d3"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d4"},
+    {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d2_tp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d3_tp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d4_tp"},
+    {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d2_tp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d3_tp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d4_tp"},
+    {QM_MOD_Q4K, "qm_sum_parts"},
     {QM_MOD_GEMM, "qm_gemm_q4k_bf16"}, {QM_MOD_GEMM, "qm_gemm_q4k_bf16_r256"},
     {QM_MOD_GEMM, "qm_gemm_q4k_bf16_k128"}, {QM_MOD_GEMM, "qm_gemm_q4k_bf16_r256_k128"},
     {QM_MOD_MOE, "qm_moe_route"},      {QM_MOD_MOE, "qm_moe_lists"},      {QM_MOD_MOE, "qm_moe_gather"},
@@ -174,7 +175,7 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             r = d->cuModuleGetFunction(&c->fn[k], c->modules[kKernels[k].module], kKernels[k].name);
             if (r != CUDA_SUCCESS) err = QM_ERR_NO_KERNEL;
         }
-        for (int k = QM_K_FUSED_Q4K_NT1; k <= QM_K_FUSED_Q4K_DD_C2D2_TP && !err; k++) {
+        for (int k = QM_K_FUSED_Q4K_NT1; k <= QM_K_FUSED_Q4K_DD_C2D4_TP && !err; k++) {
             r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }

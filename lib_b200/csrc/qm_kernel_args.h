@@ -83,6 +83,22 @@ struct QmOp {
     unsigned int *q_cnt;      // producer side: one completion counter per unit of the next op's x, zero at launch
     int32_t q_half_tiles;     // 16-row tiles of y per operand of the next op (its cols / 16)
     int32_t q_halves;         // 1, or 2 when the next op's x is the sum of two halves of y
+    // K parts (data-driven kernels only). An op with parts = S > 1 is cut into S column ranges of
+    // `units` K units each; the CTAs form S groups, group s computes the partial products of range s
+    // over all tiles and stores them, WITHOUT the RMS scale of its input, to y + s*y_part_stride. A
+    // group stages only its range of x, and the tiles spread over S times as many (tile, range)
+    // pieces. The consumer (x_parts = S) adds the S partial vectors while it stages them; it
+    // normalises that sum itself, and to make the result equal to normalising the scaled sum it
+    // needs the producer's input mean square: group s leaves the sum of squares of its range per
+    // activation row in ssq_out[s*8 + row], the consumer reads all S from ssq_in.
+    int32_t parts;            // producer side: K parts of this op (1 = whole K per CTA)
+    int32_t x_parts;          // consumer side: partial vectors that add up to x (1 = x is one vector)
+    int64_t y_part_stride;    // floats between the partial output vectors
+    int64_t x_part_stride;    // floats between the partial input vectors
+    float *ssq_out;           // producer side: [parts][8] sums of squares of x per K part and activation row
+    const float *ssq_in;      // consumer side: the same words of the op that produced x
+    float ssq_in_inv_cols;    // 1 / K of the op that produced x
+    float ssq_in_eps;         // its epsilon
 };
 
 struct QmFusedArgs {
@@ -180,6 +196,17 @@ struct QmKqArgs {
     int64_t ldx, ldy;
     int64_t rows;
     int32_t units, m;
+};
+
+// h[j][r] = c_j * sum over parts of parts[k*part_stride + j*ld_in + r], c_j = rsqrt(mean square + eps)
+// from the per-part sums of squares ssq[k*8 + j] (qm_sum_parts: the last matvec of a step that ran in K parts).
+struct QmSumPartsArgs {
+    const float *parts;
+    const float *ssq;
+    float *out;
+    int64_t part_stride, ld_in, ld_out;
+    int32_t nparts, m, n;
+    float inv_cols, eps;
 };
 
 struct QmDequantArgs {

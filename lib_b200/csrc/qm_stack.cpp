@@ -32,6 +32,7 @@ struct qm_stack {
     // for the next step (a peer may start that step, and store into this GPU's arena, before this
     // GPU has left the current one). `act` is the half of the most recent step.
     CUdeviceptr h0, act, act_half[2];
+    CUdeviceptr h_sum;          // [m][hidden]: the last down projection summed over its K parts
     int cur_half;
     int half_m[2];              // batch of the last step run in each half (0: the half is all "not yet written")
     size_t act_bytes;
@@ -48,6 +49,7 @@ struct qm_stack {
     bool fused_dd[9];           // the op list hands over through the data (no grid barriers)
     int fused_dd_kernel[9];
     int fused_half0[9];         // tensor-parallel: arena half that the first copy of the op list addresses
+    int fused_parts_o[9], fused_parts_dn[9];   // K parts of the o / down projections in the op list (1 = whole)
     // tensor-parallel: one arena holds all activation buffers and the peers' arrival flags; the
     // peers map it through CUDA IPC and this GPU stores its row slices into all of them
     int tp_world, tp_rank;
@@ -59,24 +61,37 @@ struct qm_stack {
     unsigned int tp_epoch;
     bool use_graph, use_fused;
     int last_m;                 // batch of the most recent step
+    bool last_dd;               // the most recent step ran in the data-driven form
 };
 
-// Device addresses of layer L's output buffers in a step of batch m.
+// Device addresses of layer L's output buffers in a step of batch m. The o and down projections
+// have room for QM_MAX_PARTS partial output vectors each (see QmOp::parts; steps that do not cut
+// them into K parts use the first), followed by the words their K parts publish.
+#define QM_MAX_PARTS 4
 struct LayerBufs {
     CUdeviceptr qkv, o, gu, dn;
+    CUdeviceptr ssq_o, ssq_dn;   // [QM_MAX_PARTS][8] floats each
+    int64_t part_stride;         // floats between the partial vectors of o (and of dn)
 };
+static size_t layer_floats(const qm_stack *s, int m) {
+    const size_t qkv_ld = (size_t)s->hidden + 2 * s->kv;
+    return (size_t)m * (qkv_ld + 2 * (size_t)s->ffn + 2 * QM_MAX_PARTS * (size_t)s->hidden) + 2 * QM_MAX_PARTS * 8;
+}
 static LayerBufs layer_bufs(const qm_stack *s, int L, int m) {
     const size_t qkv_ld = (size_t)s->hidden + 2 * s->kv;
-    const size_t per_row = qkv_ld + (size_t)s->hidden + 2 * (size_t)s->ffn + (size_t)s->hidden;
     LayerBufs b;
-    b.qkv = s->act + (size_t)L * m * per_row * 4;
+    b.part_stride = (int64_t)m * s->hidden;
+    b.qkv = s->act + (size_t)L * layer_floats(s, m) * 4;
     b.o = b.qkv + (size_t)m * qkv_ld * 4;
-    b.gu = b.o + (size_t)m * s->hidden * 4;
+    b.gu = b.o + (size_t)QM_MAX_PARTS * m * s->hidden * 4;
     b.dn = b.gu + (size_t)m * 2 * s->ffn * 4;
+    b.ssq_o = b.dn + (size_t)QM_MAX_PARTS * m * s->hidden * 4;
+    b.ssq_dn = b.ssq_o + QM_MAX_PARTS * 8 * 4;
     return b;
 }
 
 static qm_stack *stack_check(qm_stack *s) { return (s && s->magic == QM_STACK_MAGIC) ? s : nullptr; }
+static CUdeviceptr h_source(const qm_stack *s, int m);
 
 static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn, int32_t m_max,
                             int32_t rank, int32_t world, qm_stack **out) {
@@ -112,6 +127,7 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
     s->use_graph = true;
     s->use_fused = true;
     s->last_m = 0;
+    s->last_dd = false;
     s->h0 = s->act = 0;
     s->act_half[0] = s->act_half[1] = 0;
     s->cur_half = 0;
@@ -120,18 +136,20 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
     CUresult r = g.rc;
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
     const size_t b_h0 = up((size_t)m_max * hidden * 4);
-    s->act_bytes = up((size_t)layers * m_max * (2 * (size_t)hidden + 2 * kv_dim + hidden + 2 * (size_t)ffn) * 4);
+    s->act_bytes = up((size_t)layers * layer_floats(s, m_max) * 4);
     if (world == 1) {
-        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->h0, b_h0);
+        if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->h0, 2 * b_h0);
+        s->h_sum = s->h0 + b_h0;
         if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->act, s->act_bytes);
         s->act_half[0] = s->act_half[1] = s->act;
     } else {
-        s->flags_off = b_h0 + 2 * s->act_bytes;
+        s->flags_off = 2 * b_h0 + 2 * s->act_bytes;
         s->arena_bytes = s->flags_off + 256;
         if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&s->arena, s->arena_bytes);
         if (r == CUDA_SUCCESS) r = c->drv->cuMemsetD8Async(s->arena, 0, s->arena_bytes, c->stream);
         s->h0 = s->arena;
-        s->act_half[0] = s->h0 + b_h0;
+        s->h_sum = s->h0 + b_h0;
+        s->act_half[0] = s->h_sum + b_h0;
         s->act_half[1] = s->act_half[0] + s->act_bytes;
         s->act = s->act_half[0];
         // both halves start as "not yet written" (all ones)
@@ -271,9 +289,11 @@ extern "C" int32_t qm_stack_set_layer(qm_ctx *c, qm_stack *s, int32_t layer, qm_
 }
 
 // Device pointers of the activation buffers as the last step (of batch m) left them, for
-// per-matvec checks: [0]=h0 [m][hidden], [1]=q|k|v outputs of layer 0 [m][hidden+2kv] (layer L's
-// follow at a stride of m*(3*hidden+2*kv+2*ffn) floats, like the other three), and of the LAST
-// layer [2]=o output [m][hidden], [3]=gate|up output [m][2*ffn], [4]=down output [m][hidden].
+// per-matvec checks: [0]=h0 [m][hidden], [1]=q|k|v outputs of layer 0 [m][hidden+2kv], and of the
+// LAST layer [2]=o output, [3]=gate|up output [m][2*ffn], [4]=h [m][hidden]. When the step cut
+// the o projection into K parts (qm_stack_parts), [2] is the first of `parts` partial vectors
+// [m][hidden], `stride` floats apart, whose sum times the RMS scale of the o projection's input
+// is the o output.
 extern "C" int32_t qm_stack_buffers(qm_ctx *c, qm_stack *s, uint64_t *ptrs5) {
     CHECK_CTX(c);
     if (!stack_check(s) || !ptrs5) return QM_ERR_ARG;
@@ -283,7 +303,18 @@ extern "C" int32_t qm_stack_buffers(qm_ctx *c, qm_stack *s, uint64_t *ptrs5) {
     ptrs5[1] = layer_bufs(s, 0, m).qkv;
     ptrs5[2] = last.o;
     ptrs5[3] = last.gu;
-    ptrs5[4] = last.dn;
+    ptrs5[4] = h_source(s, m);
+    return QM_OK;
+}
+
+// info2[0] = K parts of the o projection in the most recent step (1 = whole), info2[1] = floats
+// between its partial vectors.
+extern "C" int32_t qm_stack_parts(qm_ctx *c, qm_stack *s, int64_t *info2) {
+    CHECK_CTX(c);
+    if (!stack_check(s) || !info2) return QM_ERR_ARG;
+    const int m = s->last_m > 0 ? s->last_m : 1;
+    info2[0] = s->last_dd ? s->fused_parts_o[m] : 1;
+    info2[1] = layer_bufs(s, s->layers - 1, m).part_stride;
     return QM_OK;
 }
 
@@ -296,6 +327,140 @@ extern "C" int32_t qm_stack_use_graph(qm_ctx *c, qm_stack *s, int32_t on) {
     if (!stack_check(s)) return QM_ERR_ARG;
     s->use_graph = on != 0;
     s->use_fused = on == 2;
+    return QM_OK;
+}
+
+// Uploads an op list; tensor-parallel stacks get a second copy that addresses the other arena half.
+static int32_t upload_ops(qm_ctx *c, qm_stack *s, int m, std::vector<QmOp> &ops) {
+    const size_t nops = ops.size();
+    if (s->tp_world > 1) {
+        const CUdeviceptr lo = s->act, other = s->act_half[s->act == s->act_half[0] ? 1 : 0];
+        auto moved = [&](const void *ptr) -> uintptr_t {
+            const CUdeviceptr a0 = (CUdeviceptr)(uintptr_t)ptr;
+            return (uintptr_t)((a0 >= lo && a0 < lo + s->act_bytes) ? a0 - lo + other : a0);
+        };
+        for (size_t k = 0; k < nops; k++) {
+            QmOp op = ops[k];
+            op.x = (const float *)moved(op.x);
+            op.x2 = (const float *)moved(op.x2);
+            op.y = (float *)moved(op.y);
+            op.ssq_out = (float *)moved(op.ssq_out);
+            op.ssq_in = (const float *)moved(op.ssq_in);
+            ops.push_back(op);
+        }
+        s->fused_half0[m] = s->act == s->act_half[0] ? 0 : 1;   // which half the first copy addresses
+    }
+    CUdeviceptr dev = 0;
+    DRV(c->drv->cuMemAlloc_v2(&dev, ops.size() * sizeof(QmOp)));
+    CUresult r = c->drv->cuMemcpyHtoD_v2(dev, ops.data(), ops.size() * sizeof(QmOp));
+    if (r != CUDA_SUCCESS) {
+        c->drv->cuMemFree_v2(dev);
+        return (int32_t)r;
+    }
+    s->ops_dev[m] = dev;
+    s->fused_nops[m] = (int)nops;
+    return QM_OK;
+}
+
+// The op list of a step for the data-driven kernels (qm_fused_q4k_dd_*): every output buffer is
+// filled with the "not yet written" pattern before the launch and consumers poll the words they
+// read, so no grid barrier separates dependent matvecs. Needs whole tiles per CTA, no K slices
+// and one row tile of mma columns; used below the batch from which activation images win.
+// The o and down projections are cut into K parts (QmOp::parts): their CTAs stage a quarter of x
+// each and spread over four times as many (tile, part) pieces; the consumer adds the parts up
+// while it stages them. QM_ERR_SHAPE when the step does not qualify (the caller then builds the
+// barrier form).
+static int32_t build_fused_dd(qm_ctx *c, qm_stack *s, int m) {
+    if (m >= qm_env_int("QM_IMAGE_MIN_M", 4) || qm_env_int("QM_DD", 1) == 0) return QM_ERR_SHAPE;
+    const int grid = qm_fused_grid(c);
+    const int want_parts = qm_env_int("QM_PARTS", QM_MAX_PARTS);
+    auto parts_for = [&](const QmWeight *w) {
+        for (int k = QM_MAX_PARTS; k > 1; k >>= 1)
+            if (k <= want_parts && w->units % k == 0 && grid % k == 0) return k;
+        return 1;
+    };
+    int max_units = 0, So = QM_MAX_PARTS, Sd = QM_MAX_PARTS;
+    for (int L = 0; L < s->layers; L++) {
+        const QmLayer &ly = s->layer[L];
+        if (!ly.qkv) return QM_ERR_STATE;
+        const QmWeight *ws[4] = {ly.qkv, ly.o, ly.gu, ly.dn};
+        for (const QmWeight *w : ws)
+            if (w->fmt != QM_FMT_Q4_K) return QM_ERR_FORMAT;
+        So = std::min(So, parts_for(ly.o));
+        Sd = std::min(Sd, parts_for(ly.dn));
+    }
+    for (int L = 0; L < s->layers; L++) {
+        const QmLayer &ly = s->layer[L];
+        max_units = std::max({max_units, (int)ly.qkv->units, (int)ly.gu->units, (int)ly.o->units / So, (int)ly.dn->units / Sd});
+    }
+    QmFusedPlan p;
+    if (qm_plan_fused(c, m, max_units, false, &p) != QM_OK) return QM_ERR_SHAPE;
+    int kernel = -1;
+    if (p.nt == 1 && p.consumers == 16 && p.depth >= 2 && p.depth <= 4)
+        kernel = (p.cpm == 4 ? QM_K_FUSED_Q4K_DD_C4D2 : QM_K_FUSED_Q4K_DD_C2D2) + (p.depth - 2);
+    if (kernel < 0) return QM_ERR_SHAPE;
+
+    std::vector<QmOp> ops;
+    const int64_t qkv_ld = s->hidden + 2 * s->kv;
+    const bool tp = s->tp_world > 1;
+    const size_t R = (size_t)s->tp_rank * 4;
+    // Tensor-parallel: every matrix is sliced by rows (GPU r of g holds rows [r*N/g, (r+1)*N/g)); y points
+    // at this rank's rows of the full-width output and the results go to every GPU's arena.
+    auto add = [&](const QmWeight *w, CUdeviceptr x, CUdeviceptr x2, int64_t ldx, CUdeviceptr y, int64_t ldy, uint32_t xop,
+                   bool first, int parts, int64_t y_part_stride, CUdeviceptr ssq_out) -> QmOp & {
+        QmOp op;
+        qm_fill_op(c, p, w, x, x2, ldx, y + R * w->rows, ldy, xop, !first, 0, w->units / parts, 0, &op);
+        const int G = grid / parts;
+        op.q = op.tiles / G;
+        op.rem = op.tiles % G;
+        op.parts = parts;
+        op.y_part_stride = y_part_stride;
+        op.ssq_out = parts > 1 ? (float *)(uintptr_t)ssq_out : nullptr;
+        op.tp_shared = tp ? 1 : 0;
+        ops.push_back(op);
+        return ops.back();
+    };
+    auto consumes = [&](QmOp &op, int parts, int64_t stride, CUdeviceptr ssq, const QmWeight *producer) {
+        op.x_parts = parts;
+        op.x_part_stride = stride;
+        if (parts > 1) {
+            op.ssq_in = (const float *)(uintptr_t)ssq;
+            op.ssq_in_inv_cols = 1.f / (float)producer->cols;
+            op.ssq_in_eps = 1e-6f;
+        }
+    };
+    for (int L = 0; L < s->layers; L++) {
+        const QmLayer &ly = s->layer[L];
+        const LayerBufs b = layer_bufs(s, L, m);
+        QmOp &qkv = add(ly.qkv, L == 0 ? s->h0 : layer_bufs(s, L - 1, m).dn, 0, s->hidden, b.qkv, qkv_ld, QM_XOP_RMSNORM,
+                        L == 0, 1, 0, 0);
+        if (L > 0) consumes(qkv, Sd, b.part_stride, layer_bufs(s, L - 1, m).ssq_dn, s->layer[L - 1].dn);
+        add(ly.o, b.qkv, 0, qkv_ld, b.o, s->hidden, QM_XOP_RMSNORM, false, So, b.part_stride, b.ssq_o);
+        QmOp &gu = add(ly.gu, b.o, 0, s->hidden, b.gu, 2 * s->ffn, QM_XOP_RMSNORM, false, 1, 0, 0);
+        consumes(gu, So, b.part_stride, b.ssq_o, ly.o);
+        add(ly.dn, b.gu, b.gu + (size_t)s->ffn * 4, 2 * s->ffn, b.dn, s->hidden, QM_XOP_ADD_RMSNORM, false, Sd,
+            b.part_stride, b.ssq_dn);
+    }
+    for (const QmOp &op : ops)
+        if ((int64_t)op.tiles * op.units >= (1ll << 31)) return QM_ERR_SHAPE;
+    CUdeviceptr sync = 0;
+    DRV(c->drv->cuMemAlloc_v2(&sync, 256));
+    int32_t rc = upload_ops(c, s, m, ops);
+    if (rc) {
+        c->drv->cuMemFree_v2(sync);
+        return rc;
+    }
+    s->img_dev[m] = 0;
+    s->sync_dev[m] = sync;
+    s->sync_bytes[m] = 256;
+    s->img_units[m] = max_units;
+    s->fused_ncross[m] = 1;
+    s->fused_img[m] = false;
+    s->fused_dd[m] = true;
+    s->fused_dd_kernel[m] = kernel;
+    s->fused_parts_o[m] = So;
+    s->fused_parts_dn[m] = Sd;
+    s->fused_plan[m] = p;
     return QM_OK;
 }
 
@@ -352,17 +517,8 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
         if ((int64_t)op.tiles * op.units >= (1ll << 31)) return QM_ERR_SHAPE;
     // every unsliced op but the first writes a buffer that the op before it does not touch
     // (ops shared between GPUs keep whole tiles per CTA: their outputs are plain stores to every GPU)
-    // Data-driven hand-over (kernels qm_fused_q4k_dd_*): every output buffer is filled with the
-    // "not yet written" pattern before the launch and consumers poll the words they read, so the
-    // grid barrier between dependent matvecs goes away. Needs whole tiles per CTA, no K slices
-    // and one row tile of mma columns; used below the batch from which activation images win.
-    const int min_m = qm_env_int("QM_IMAGE_MIN_M", 4);
-    const int dd_kernel = p.cpm == 4 ? (p.depth == 4 ? QM_K_FUSED_Q4K_DD_C4D4 : p.depth == 3 ? QM_K_FUSED_Q4K_DD_C4D3 : -1)
-                                     : (p.depth == 3 ? QM_K_FUSED_Q4K_DD_C2D3 : p.depth == 2 ? QM_K_FUSED_Q4K_DD_C2D2 : -1);
-    bool dd = p.nt == 1 && p.consumers == 16 && dd_kernel >= 0 && m < min_m && qm_env_int("QM_DD", 1) != 0;
-    for (const QmOp &op : ops)
-        if (op.units != op.units_total || op.accumulate) dd = false;
-    for (size_t k = 1; k < ops.size() && !dd; k++)
+    for (QmOp &op : ops) op.parts = op.x_parts = 1;
+    for (size_t k = 1; k < ops.size(); k++)
         if (ops[k].units == ops[k].units_total && !ops[k].tp_shared) qm_balance_op(c, &ops[k]);
     // barriers over all GPUs in one launch: after every shared op, and the one that ends the launch
     int ncross = 1;
@@ -378,7 +534,7 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     const size_t img_stride = (img_bytes + 255) & ~(size_t)255;
     const size_t ngroups = group_first.size();
     const size_t sync_bytes = 256 + ngroups * (size_t)img_units * 4;
-    CUdeviceptr img = 0, sync = 0, dev = 0;
+    CUdeviceptr img = 0, sync = 0;
     CUresult r = c->drv->cuMemAlloc_v2(&img, 2 * img_stride);
     if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&sync, sync_bytes);
     if (r == CUDA_SUCCESS) r = c->drv->cuMemsetD8Async(img, 0, 2 * img_stride, c->stream);
@@ -387,8 +543,8 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     // 2.09 against 2.33; batch 3: 2.34 against 2.37); from four rows on the image wins (batch 4:
     // 2.46 ms against 2.63 ms; batch 8: 3.52 ms against 5.93 ms).
     bool uses_img = false;
-    const int min_units = qm_env_int("QM_IMAGE_MIN_UNITS", 1 << 30);
-    if (r == CUDA_SUCCESS && !qm_env_int("QM_NO_IMAGE", 0) && s->tp_world == 1 && !dd) {
+    const int min_m = qm_env_int("QM_IMAGE_MIN_M", 4), min_units = qm_env_int("QM_IMAGE_MIN_UNITS", 1 << 30);
+    if (r == CUDA_SUCCESS && !qm_env_int("QM_NO_IMAGE", 0) && s->tp_world == 1) {
         for (size_t k = 0; k + 1 < ngroups; k++) {
             QmOp &prod = ops[group_last[k]];
             const QmOp &cons = ops[group_first[k + 1]];
@@ -405,43 +561,55 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
             uses_img = true;
         }
     }
-    // tensor-parallel: a second copy of the list for the other arena half
-    const size_t nops = ops.size();
-    if (s->tp_world > 1) {
-        const CUdeviceptr lo = s->act, other = s->act_half[s->act == s->act_half[0] ? 1 : 0];
-        auto moved = [&](const void *ptr) -> uintptr_t {
-            const CUdeviceptr a0 = (CUdeviceptr)(uintptr_t)ptr;
-            return (uintptr_t)((a0 >= lo && a0 < lo + s->act_bytes) ? a0 - lo + other : a0);
-        };
-        for (size_t k = 0; k < nops; k++) {
-            QmOp op = ops[k];
-            op.x = (const float *)moved(op.x);
-            op.x2 = (const float *)moved(op.x2);
-            op.y = (float *)moved(op.y);
-            ops.push_back(op);
-        }
-        s->fused_half0[m] = s->act == s->act_half[0] ? 0 : 1;   // which half the first copy addresses
-    }
-    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&dev, ops.size() * sizeof(QmOp));
-    if (r == CUDA_SUCCESS) r = c->drv->cuMemcpyHtoD_v2(dev, ops.data(), ops.size() * sizeof(QmOp));
     if (r != CUDA_SUCCESS) {
-        if (dev) c->drv->cuMemFree_v2(dev);
         if (img) c->drv->cuMemFree_v2(img);
         if (sync) c->drv->cuMemFree_v2(sync);
         return (int32_t)r;
     }
-    s->ops_dev[m] = dev;
+    rc = upload_ops(c, s, m, ops);
+    if (rc) {
+        c->drv->cuMemFree_v2(img);
+        c->drv->cuMemFree_v2(sync);
+        return rc;
+    }
     s->img_dev[m] = img;
     s->sync_dev[m] = sync;
     s->sync_bytes[m] = sync_bytes;
     s->img_units[m] = img_units;
-    s->fused_nops[m] = (int)nops;
     s->fused_ncross[m] = ncross;
     s->fused_img[m] = uses_img;
-    s->fused_dd[m] = dd;
-    s->fused_dd_kernel[m] = dd_kernel;
+    s->fused_dd[m] = false;
+    s->fused_dd_kernel[m] = -1;
+    s->fused_parts_o[m] = s->fused_parts_dn[m] = 1;
     s->fused_plan[m] = p;
     return QM_OK;
+}
+
+// The last layer's down projection, when it ran in K parts: h = c * (sum of the partial vectors), c the RMS
+// scale of its input, into s->h_sum.
+static int32_t sum_last_parts(qm_ctx *c, qm_stack *s, int m) {
+    if (s->fused_parts_dn[m] <= 1) return QM_OK;
+    const LayerBufs b = layer_bufs(s, s->layers - 1, m);
+    QmSumPartsArgs a;
+    memset(&a, 0, sizeof a);
+    a.parts = (const float *)(uintptr_t)b.dn;
+    a.ssq = (const float *)(uintptr_t)b.ssq_dn;
+    a.out = (float *)(uintptr_t)s->h_sum;
+    a.part_stride = b.part_stride;
+    a.ld_in = s->hidden;
+    a.ld_out = s->hidden;
+    a.nparts = s->fused_parts_dn[m];
+    a.m = m;
+    a.n = s->hidden;
+    a.inv_cols = 1.f / (float)s->ffn;
+    a.eps = 1e-6f;
+    return qm_launch(c, QM_K_SUM_PARTS, (unsigned)std::min(148, (m * s->hidden + 255) / 256), 1, 256, 0, &a, false);
+}
+
+// Where the most recent step left h [m][hidden].
+static CUdeviceptr h_source(const qm_stack *s, int m) {
+    if (s->last_dd && s->fused_parts_dn[m] > 1) return s->h_sum;
+    return layer_bufs(s, s->layers - 1, m).dn;
 }
 
 static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
@@ -480,17 +648,17 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
         // layers*m rows' worth of the half)
         const int cur = s->act == s->act_half[0] ? 0 : 1, other = cur ^ 1;
         if (s->half_m[other] > 0) {
-            const size_t per_row = 3 * (size_t)s->hidden + 2 * (size_t)s->kv + 2 * (size_t)s->ffn;
-            DRV(c->drv->cuMemsetD8Async(s->act_half[other], 0xFF, (size_t)s->layers * s->half_m[other] * per_row * 4,
-                                        c->stream));
+            DRV(c->drv->cuMemsetD8Async(s->act_half[other], 0xFF,
+                                        (size_t)s->layers * layer_floats(s, s->half_m[other]) * 4, c->stream));
             s->half_m[other] = 0;
         }
         s->half_m[cur] = m;
         if (s->fused_dd[m]) {
             a.tp_counter = 0;
             s->tp_epoch += 1;   // one barrier over the GPUs per launch
-            return qm_launch_ex(c, s->fused_dd_kernel[m] + (QM_K_FUSED_Q4K_DD_C4D4_TP - QM_K_FUSED_Q4K_DD_C4D4),
-                                (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32, (unsigned)p.smem, &a, false, true);
+            int32_t rc = qm_launch_ex(c, s->fused_dd_kernel[m] + (QM_K_FUSED_Q4K_DD_C4D2_TP - QM_K_FUSED_Q4K_DD_C4D2),
+                                      (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32, (unsigned)p.smem, &a, false, true);
+            return rc ? rc : sum_last_parts(c, s, m);
         }
         a.tp_counter = s->tp_counter ? 1u : 0u;
         // the epoch counts the launch's barriers over all GPUs; the counter form counts CTA arrivals
@@ -502,8 +670,9 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
         // every output word of the step starts as "not yet written" (all ones)
         const size_t bytes = (size_t)(layer_bufs(s, s->layers, m).qkv - s->act);
         DRV(c->drv->cuMemsetD8Async(s->act, 0xFF, bytes, c->stream));
-        return qm_launch_ex(c, s->fused_dd_kernel[m], (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32,
-                            (unsigned)p.smem, &a, false, true);
+        int32_t rc = qm_launch_ex(c, s->fused_dd_kernel[m], (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32,
+                                  (unsigned)p.smem, &a, false, true);
+        return rc ? rc : sum_last_parts(c, s, m);
     }
     const int kern = s->fused_img[m] ? (p.nt == 1 ? QM_K_FUSED_Q4K_NT1_IMG : QM_K_FUSED_Q4K_NT2_IMG)
                                      : (p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2);
@@ -534,18 +703,30 @@ static int32_t enqueue_layers(qm_ctx *c, qm_stack *s, int m, int upto_layers) {
     return QM_OK;
 }
 
+// The data-driven form where the step qualifies, else the form with grid barriers.
+static int32_t build_any(qm_ctx *c, qm_stack *s, int m) {
+    int32_t rc = build_fused_dd(c, s, m);
+    if (rc == QM_ERR_SHAPE) rc = build_fused(c, s, m);
+    return rc;
+}
+
 static int32_t step_device(qm_ctx *c, qm_stack *s, int m) {
     s->last_m = m;
+    s->last_dd = false;
     if (s->tp_world > 1) {   // tensor-parallel steps exist as the one fused launch only
-        int32_t rc = s->ops_dev[m] ? QM_OK : build_fused(c, s, m);
+        int32_t rc = s->ops_dev[m] ? QM_OK : build_any(c, s, m);
         if (rc) return rc;
+        s->last_dd = s->fused_dd[m];
         s->cur_half ^= 1;    // this step's half: the one refilled during the step before
         s->act = s->act_half[s->cur_half];
         return launch_fused(c, s, m);
     }
     if (s->use_graph && s->use_fused) {
-        int32_t rc = s->ops_dev[m] ? QM_OK : build_fused(c, s, m);
-        if (rc == QM_OK) return launch_fused(c, s, m);
+        int32_t rc = s->ops_dev[m] ? QM_OK : build_any(c, s, m);
+        if (rc == QM_OK) {
+            s->last_dd = s->fused_dd[m];
+            return launch_fused(c, s, m);
+        }
         if (rc != QM_ERR_SHAPE && rc != QM_ERR_FORMAT) return rc;
     }
     if (!s->use_graph) return enqueue_layers(c, s, m, s->layers);
@@ -587,7 +768,7 @@ extern "C" int32_t qm_stack_step(qm_ctx *c, qm_stack *s, uint64_t x_dev, int32_t
     if (rc) return rc;
     if (h_out_dev)
         for (int j = 0; j < m; j++)
-            DRV(c->drv->cuMemcpyDtoDAsync_v2(h_out_dev + (size_t)j * ldh * 4, layer_bufs(s, s->layers - 1, m).dn + (size_t)j * s->hidden * 4,
+            DRV(c->drv->cuMemcpyDtoDAsync_v2(h_out_dev + (size_t)j * ldh * 4, h_source(s, m) + (size_t)j * s->hidden * 4,
                                              (size_t)s->hidden * 4, c->stream));
     return QM_OK;
 }
@@ -605,7 +786,7 @@ extern "C" int32_t qm_stack_step_host(qm_ctx *c, qm_stack *s, const float *x_hos
     DRV(d->cuMemcpyHtoDAsync_v2(s->h0, x_host, (size_t)m * s->hidden * 4, c->stream));
     int32_t rc = step_device(c, s, m);
     if (rc) return rc;
-    DRV(d->cuMemcpyDtoHAsync_v2(h_host, layer_bufs(s, s->layers - 1, m).dn, (size_t)m * s->hidden * 4, c->stream));
+    DRV(d->cuMemcpyDtoHAsync_v2(h_host, h_source(s, m), (size_t)m * s->hidden * 4, c->stream));
     if (kv_host && s->kv) {
         const int64_t qkv_ld = s->hidden + 2 * s->kv;
         // (tensor-parallel: every GPU's slice of q|k|v has been stored into this arena)

@@ -267,6 +267,12 @@ QM_API int32_t qm_stack_create_tp(qm_ctx *ctx, int32_t layers, int32_t hidden, i
                                   int32_t m_max, int32_t rank, int32_t world, qm_stack **out);
 QM_API int32_t qm_stack_ipc_handle(qm_ctx *ctx, qm_stack *stack, void *handle64);
 QM_API int32_t qm_stack_set_peers(qm_ctx *ctx, qm_stack *stack, const void *handles);
+/* The same for a caller that drives all GPUs from one process (the reference's nccltest model,
+ * nvidia/x/nccltest/run.go:375-391, with Context.EnablePeerAccess, nvidia/driver/context.gen.go:98):
+ * qm_stack_arena returns this rank's arena, qm_stack_set_peer_pointers takes the `world` arena
+ * base addresses as this process addresses them (entry `rank` ignored). */
+QM_API int32_t qm_stack_arena(qm_ctx *ctx, qm_stack *stack, uint64_t *base, int64_t *bytes);
+QM_API int32_t qm_stack_set_peer_pointers(qm_ctx *ctx, qm_stack *stack, const uint64_t *bases);
 
 /* Host-side residency manager for expert weight blobs, the behaviour of moe.ExpertCacheManager
  * (lm/moe/moe.go:143-287): at most max_hot experts stay in host memory, admitting one more

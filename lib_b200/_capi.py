@@ -70,6 +70,8 @@ def _load():
         "qm_stack_create_tp": (i32, [p, i32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_stack_ipc_handle": (i32, [p, p, p]),
         "qm_stack_set_peers": (i32, [p, p, p]),
+        "qm_stack_arena": (i32, [p, p, ctypes.POINTER(u64), ctypes.POINTER(i64)]),
+        "qm_stack_set_peer_pointers": (i32, [p, p, ctypes.POINTER(u64)]),
         "qm_expert_cache_create": (i32, [ctypes.c_char_p, i32, ctypes.POINTER(p)]),
         "qm_expert_cache_register": (i32, [p, i64, p, i64]),
         "qm_expert_cache_get": (i32, [p, i64, p, i64, ctypes.POINTER(i64)]),
@@ -279,6 +281,17 @@ class Stack:
         assert len(blob) == 64 * self.world
         buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
         _check(lib.qm_stack_set_peers(self.ctx._h, self._h, buf), "stack_set_peers")
+
+    def arena(self):
+        """(base device address, bytes) of the tensor-parallel activation arena."""
+        base, nbytes = ctypes.c_uint64(0), ctypes.c_int64(0)
+        _check(lib.qm_stack_arena(self.ctx._h, self._h, ctypes.byref(base), ctypes.byref(nbytes)), "stack_arena")
+        return base.value, nbytes.value
+
+    def set_peer_pointers(self, bases):
+        """bases: the `world` arena base addresses as this process addresses them."""
+        arr = (ctypes.c_uint64 * self.world)(*[int(b) for b in bases])
+        _check(lib.qm_stack_set_peer_pointers(self.ctx._h, self._h, arr), "stack_set_peer_pointers")
 
     def set_layer(self, layer, qkv, o, gate_up, down):
         _check(lib.qm_stack_set_layer(self.ctx._h, self._h, layer, qkv.handle, o.handle, gate_up.handle,

@@ -927,136 +927,29 @@ __device__ __forceinline__ void cp_async_wait_n() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// TP (tensor parallel): this GPU computes a row slice of every op and stores each result into
-// the same place of every GPU's activation arena (plain peer stores over NVLink); consumers
-// poll their own arena only, so no barrier crosses the GPUs inside a step. One barrier over the
-// GPUs ends the launch: when it returns, every slice of the step has arrived everywhere, which
-// is what lets the host refill the other arena half with the "not yet written" pattern.
-template <int CPM, int D, bool TP>
-__device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
-    constexpr int C = 16;                       // warps per CTA
-    constexpr int NL = CPM == 4 ? 3 : 2;        // limbs per activation row
-    constexpr int NT = 1;
-    extern __shared__ __align__(128) uint8_t smem[];
+// Stages the x of one op for this CTA: polls the words until the producers have written them,
+// adds the partial vectors of a producer that ran in K parts, applies the input transform and
+// quantizes into limb planes, sub-block sums and column weights; leaves each warp's part of the
+// sums of squares in ssq. Returns the thread's "gave up waiting" flag.
+template <int CPM, bool TP>
+__device__ __noinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, uint8_t *xs, int plane_stride,
+                                      uint32_t *xsum, float *sxw, float *ssq, bool dead) {
+    const QmFusedArgs &a = *ap;
+    constexpr int C = 16, NL = CPM == 4 ? 3 : 2, NT = 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int M = a.m, P = M * NL;
-    const QmOp *ops = a.ops;   // a device array (this kernel runs op lists, not single matvecs)
-
-    // ---- shared memory (qm_plan_fused computes an upper bound of this) -------------------------
-    const int plane_stride = a.max_units * 256 + 64;
-    uint8_t *xs = smem;                                                            // [P][plane_stride]
-    uint32_t *xsum = reinterpret_cast<uint32_t *>(xs + (size_t)P * plane_stride);   // [units][8][4] f16 pairs
-    float *sxw = reinterpret_cast<float *>(xsum + (size_t)a.max_units * 8 * 4);     // [units][8] column weights
-    float *ssq = sxw + (size_t)a.max_units * 8;                                     // [8][16]
-    float *slots = ssq + 8 * 16;                                                    // [C][2][M*16]
-    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(slots + (size_t)C * 2 * M * 16) + 127) & ~(uintptr_t)127);
-    uint8_t *my_stages = stages + (size_t)warp * D * kStageBytes;
-
-    // columns of absent activation rows and pad columns must read as zero weights and sums
-    for (int i = tid; i < a.max_units * 8 * 5; i += C * 32) xsum[i] = 0u;   // xsum and sxw are adjacent
-    __syncthreads();
-
-    // This warp's items of op `o`: the CTA owns a run of whole tiles, its items are dealt evenly to
-    // the warps in order. Returns the first item and the count in CTA-local coordinates.
-    // An op cut into K parts splits the CTAs into as many groups; `c` is then the CTA's index within
-    // its group (q and rem are computed for the group's size).
-    auto warp_range = [&](int q, int rem, int units, int c, int &tile0, int &lo, int &n, int &wq, int &wrem) {
-        tile0 = c * q + min(c, rem);
-        const int Ic = (q + (c < rem ? 1 : 0)) * units;
-        wq = Ic / C;
-        wrem = Ic - wq * C;
-        lo = warp * wq + min(warp, wrem);
-        n = wq + (warp < wrem ? 1 : 0);
-    };
-
-    // ---- producer side of the ring: a pointer and a count per op -------------------------------
-    // (the items of a tile's K part are contiguous in the store; the next tile's part follows
-    // p_skip bytes later)
-    int p_op = -1, p_n = 0, p_u = 0, p_units = 1;
-    int64_t p_skip = 0;
-    const uint8_t *p_src = nullptr;
-    auto p_next_op = [&]() {
-        p_n = 0;
-        for (p_op++; p_op < a.nops; p_op++) {
-            const QmOp *po = ops + p_op;
-            int tile0, lo, n, wq, wrem;
-            const int units = __ldg(&po->units), parts = __ldg(&po->parts), total = __ldg(&po->units_total);
-            const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G;
-            warp_range(__ldg(&po->q), __ldg(&po->rem), units, (int)blockIdx.x - grp * G, tile0, lo, n, wq, wrem);
-            if (n > 0) {
-                const int tile = lo / units, u = lo - tile * units;
-                p_n = n;
-                p_units = units;
-                p_u = units - u;
-                p_skip = (int64_t)(total - units) * QM_Q4K_ITEM_BYTES;
-                p_src = ldg_ptr(&po->wq) + ((int64_t)(tile0 + tile) * total + grp * units + u) * QM_Q4K_ITEM_BYTES + lane * 16;
-                break;
-            }
-        }
-    };
-    const uint32_t ring0 = smem_u32(my_stages) + lane * 16;
-    uint32_t p_dst = ring0;
-    auto issue = [&]() {
-        if (p_n > 0) {
-            cp_async16(p_dst, p_src);
-            cp_async16(p_dst + 512, p_src + 512);
-            cp_async16(p_dst + 1024, p_src + 1024);
-            cp_async16(p_dst + 1536, p_src + 1536);
-            if (lane < 16) cp_async16(p_dst + 2048, p_src + 2048);
-            p_src += QM_Q4K_ITEM_BYTES;
-            if (--p_u == 0) { p_src += p_skip; p_u = p_units; }
-            if (--p_n == 0) p_next_op();
-        }
-        cp_async_commit();
-        p_dst = p_dst + kStageBytes == ring0 + D * kStageBytes ? ring0 : p_dst + kStageBytes;
-    };
-    p_next_op();
-#pragma unroll
-    for (int d = 0; d < D; d++) issue();
-
-    // mma column n = g holds limb (n % CPM) of activation row (n / CPM); lanes whose column has no
-    // row read plane 0 (their column weight is zero)
-    const int col_row = g / CPM, col_limb = g - col_row * CPM;
-    const bool col_on = col_row < M && col_limb < NL;
-    const uint8_t *bplane = xs + (size_t)(col_on ? col_row * NL + col_limb : 0) * plane_stride + t * 16;
-    // byte selector that brings the minima of sub-blocks 2t and 2t+1 (of the eight in two words)
-    // to the low half of a word
-    const uint32_t min_sel = (uint32_t)(2 * t) | ((uint32_t)(2 * t + 1) << 4) | 0x4400u;
-
-    const uint8_t *c_stage = my_stages;   // consumer slot
-    bool dead = false;
-#ifdef QM_DEBUG
-    // debug builds, a.debug == 9: time stamps of every op's phases as seen by thread 0 of the first and last CTA
-#define QM_DD_MARK(k)                                                                                             \
-    do {                                                                                                          \
-        if (a.debug == 9 && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && opi < 480)            \
-            reinterpret_cast<unsigned long long *>(a.status + 16)[(opi * 2 + (blockIdx.x != 0)) * 4 + (k)] = gtime(); \
-    } while (0)
-#else
-#define QM_DD_MARK(k) do { } while (0)
-#endif
-
-    for (int opi = 0; opi < a.nops; opi++) {
-        const QmOp *po = ops + opi;
-        QM_DD_MARK(0);
-        const int nun = __ldg(&po->units);
-        const int xop = __ldg(&po->xop);
-        const float *opx = ldg_ptr(&po->x), *opx2 = ldg_ptr(&po->x2);
-        const int64_t ldx = __ldg(&po->ldx);
-        const bool norm = xop == 1 || xop == 2;
-        const int parts = __ldg(&po->parts), x_parts = __ldg(&po->x_parts);
-        const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G, cta_in_grp = (int)blockIdx.x - grp * G;
-        const int col0 = grp * nun * QM_K_UNIT;   // first column of this group's K part
-        const int64_t xps = __ldg(&po->x_part_stride);
-        // every warp has finished with the activation planes and the partial sums of the op before
-        if (opi > 0) __syncthreads();
-
-        // ---- stage x: poll until written, quantize into limbs -------------------------------------
-        {
+    const int M = a.m;
+    const int nun = po->units, xop = po->xop;
+    const float *opx = po->x, *opx2 = po->x2;
+    const int64_t ldx = po->ldx;
+    const bool norm = xop == 1 || xop == 2;
+    const int parts = po->parts, x_parts = po->x_parts;
+    const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G;
+    const int col0 = grp * nun * QM_K_UNIT;   // first column of this group's K part
+    const int64_t xps = po->x_part_stride;
+    {
             constexpr int kRounds = 2;   // (row, unit) pairs of a warp in flight at once
             const int total = M * nun;
-            const bool poll = __ldg(&po->barrier) != 0;   // x is an earlier op's output
+            const bool poll = po->barrier != 0;   // x is an earlier op's output
             float sq_run = 0.f;
             int sq_j = -1;
             if (norm && lane < 8) ssq[lane * 16 + warp] = 0.f;
@@ -1173,16 +1066,153 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                 for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
                 if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
             }
+    }
+    return dead;
+}
+
+// TP (tensor parallel): this GPU computes a row slice of every op and stores each result into
+// the same place of every GPU's activation arena (plain peer stores over NVLink); consumers
+// poll their own arena only, so no barrier crosses the GPUs inside a step. One barrier over the
+// GPUs ends the launch: when it returns, every slice of the step has arrived everywhere, which
+// is what lets the host refill the other arena half with the "not yet written" pattern.
+template <int CPM, int D, bool TP>
+__device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
+    constexpr int C = 16;                       // warps per CTA
+    constexpr int NL = CPM == 4 ? 3 : 2;        // limbs per activation row
+    constexpr int NT = 1;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int M = a.m, P = M * NL;
+    const QmOp *ops = a.ops;   // a device array (this kernel runs op lists, not single matvecs)
+
+    // ---- shared memory (qm_plan_fused computes an upper bound of this) -------------------------
+    const int plane_stride = a.max_units * 256 + 64;
+    uint8_t *xs = smem;                                                            // [P][plane_stride]
+    uint32_t *xsum = reinterpret_cast<uint32_t *>(xs + (size_t)P * plane_stride);   // [units][8][4] f16 pairs
+    float *sxw = reinterpret_cast<float *>(xsum + (size_t)a.max_units * 8 * 4);     // [units][8] column weights
+    float *ssq = sxw + (size_t)a.max_units * 8;                                     // [8][16]
+    float *slots = ssq + 8 * 16;                                                    // [C][2][M*16]
+    QmOp *sop = reinterpret_cast<QmOp *>(((uintptr_t)(slots + (size_t)C * 2 * M * 16) + 15) & ~(uintptr_t)15);   // [2]
+    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(sop + 2) + 127) & ~(uintptr_t)127);
+    uint8_t *my_stages = stages + (size_t)warp * D * kStageBytes;
+
+    // columns of absent activation rows and pad columns must read as zero weights and sums
+    for (int i = tid; i < a.max_units * 8 * 5; i += C * 32) xsum[i] = 0u;   // xsum and sxw are adjacent
+    __syncthreads();
+
+    // This warp's items of op `o`: the CTA owns a run of whole tiles, its items are dealt evenly to
+    // the warps in order. Returns the first item and the count in CTA-local coordinates.
+    // An op cut into K parts splits the CTAs into as many groups; `c` is then the CTA's index within
+    // its group (q and rem are computed for the group's size).
+    auto warp_range = [&](int q, int rem, int units, int c, int &tile0, int &lo, int &n, int &wq, int &wrem) {
+        tile0 = c * q + min(c, rem);
+        const int Ic = (q + (c < rem ? 1 : 0)) * units;
+        wq = Ic / C;
+        wrem = Ic - wq * C;
+        lo = warp * wq + min(warp, wrem);
+        n = wq + (warp < wrem ? 1 : 0);
+    };
+
+    // ---- producer side of the ring: a pointer and a count per op -------------------------------
+    // (the items of a tile's K part are contiguous in the store; the next tile's part follows
+    // p_skip bytes later)
+    int p_op = -1, p_n = 0, p_u = 0;
+    const uint8_t *p_src = nullptr;
+    auto p_next_op = [&]() {
+        p_n = 0;
+        for (p_op++; p_op < a.nops; p_op++) {
+            const QmOp *po = ops + p_op;
+            int tile0, lo, n, wq, wrem;
+            const int units = __ldg(&po->units), parts = __ldg(&po->parts), total = __ldg(&po->units_total);
+            const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G;
+            warp_range(__ldg(&po->q), __ldg(&po->rem), units, (int)blockIdx.x - grp * G, tile0, lo, n, wq, wrem);
+            if (n > 0) {
+                const int tile = lo / units, u = lo - tile * units;
+                p_n = n;
+                p_u = units - u;
+                p_src = ldg_ptr(&po->wq) + ((int64_t)(tile0 + tile) * total + grp * units + u) * QM_Q4K_ITEM_BYTES + lane * 16;
+                break;
+            }
         }
+    };
+    const uint32_t ring0 = smem_u32(my_stages) + lane * 16;
+    uint32_t p_dst = ring0;
+    auto issue = [&]() {
+        if (p_n > 0) {
+            cp_async16(p_dst, p_src);
+            cp_async16(p_dst + 512, p_src + 512);
+            cp_async16(p_dst + 1024, p_src + 1024);
+            cp_async16(p_dst + 1536, p_src + 1536);
+            if (lane < 16) cp_async16(p_dst + 2048, p_src + 2048);
+            p_src += QM_Q4K_ITEM_BYTES;
+            if (--p_u == 0) {   // end of a tile's K part (the op's fields are re-read here, not kept in registers)
+                const QmOp *po = ops + p_op;
+                p_u = __ldg(&po->units);
+                p_src += (int64_t)(__ldg(&po->units_total) - p_u) * QM_Q4K_ITEM_BYTES;
+            }
+            if (--p_n == 0) p_next_op();
+        }
+        cp_async_commit();
+        p_dst = p_dst + kStageBytes == ring0 + D * kStageBytes ? ring0 : p_dst + kStageBytes;
+    };
+    p_next_op();
+#pragma unroll
+    for (int d = 0; d < D; d++) issue();
+
+    // mma column n = g holds limb (n % CPM) of activation row (n / CPM); lanes whose column has no
+    // row read plane 0 (their column weight is zero)
+    const int col_row = g / CPM, col_limb = g - col_row * CPM;
+    const bool col_on = col_row < M && col_limb < NL;
+    const uint8_t *bplane = xs + (size_t)(col_on ? col_row * NL + col_limb : 0) * plane_stride + t * 16;
+    // byte selector that brings the minima of sub-blocks 2t and 2t+1 (of the eight in two words)
+    // to the low half of a word
+    const uint32_t min_sel = (uint32_t)(2 * t) | ((uint32_t)(2 * t + 1) << 4) | 0x4400u;
+
+    const uint8_t *c_stage = my_stages;   // consumer slot
+    bool dead = false;
+#ifdef QM_DEBUG
+    // debug builds, a.debug == 9: time stamps of every op's phases as seen by thread 0 of the first and last CTA
+#define QM_DD_MARK(k)                                                                                             \
+    do {                                                                                                          \
+        if (a.debug == 9 && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && opi < 480)            \
+            reinterpret_cast<unsigned long long *>(a.status + 16)[(opi * 2 + (blockIdx.x != 0)) * 4 + (k)] = gtime(); \
+    } while (0)
+#else
+#define QM_DD_MARK(k) do { } while (0)
+#endif
+
+    // The descriptor of the current op is read from shared memory; a warp copies the next op's
+    // there while the current one streams.
+    static_assert(sizeof(QmOp) % 16 == 0, "QmOp is copied in 16-byte pieces");
+    if (warp == 0 && lane < (int)(sizeof(QmOp) / 16))
+        reinterpret_cast<uint4 *>(&sop[0])[lane] = __ldg(reinterpret_cast<const uint4 *>(ops) + lane);
+
+    for (int opi = 0; opi < a.nops; opi++) {
+        const QmOp *po = &sop[opi & 1];
+        QM_DD_MARK(0);
+        // every warp has finished with the activation planes and the partial sums of the op before
+        __syncthreads();
+        const int nun = po->units;
+        const int xop = po->xop;
+        const bool norm = xop == 1 || xop == 2;
+        const int parts = po->parts, x_parts = po->x_parts;
+        const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G, cta_in_grp = (int)blockIdx.x - grp * G;
+
+        // ---- stage x: poll until written, quantize into limbs (a call, so that its registers do
+        // not weigh on the streaming loop) ------------------------------------------------------------
+        dead = dd_stage<CPM, TP>(&a, po, xs, plane_stride, xsum, sxw, ssq, dead);
         __syncthreads();
         QM_DD_MARK(1);
+        if (warp == C - 1 && opi + 1 < a.nops && lane < (int)(sizeof(QmOp) / 16))
+            reinterpret_cast<uint4 *>(&sop[(opi + 1) & 1])[lane] = __ldg(reinterpret_cast<const uint4 *>(ops + opi + 1) + lane);
 
         // RMS normalisation is a scalar per activation row: it multiplies the finished sums
         float myscale = 1.f;
         if (norm) {
-            const float inv_cols = 1.f / (float)__ldg(&po->cols);
-            const float *ssq_in = ldg_ptr(&po->ssq_in);
-            float *ssq_out = ldg_ptr(&po->ssq_out);
+            const float inv_cols = 1.f / (float)po->cols;
+            const float *ssq_in = po->ssq_in;
+            float *ssq_out = po->ssq_out;
             for (int j = 0; j < M; j++) {
                 float sq = ssq[j * 16 + (lane & 15)];   // the warps' parts, added as a fixed tree
 #pragma unroll
@@ -1193,7 +1223,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                     if (cta_in_grp == 0 && tid == 0) st_relaxed_f32(ssq_out + grp * 8 + j, sq);
                     continue;
                 }
-                float eps = __ldg(&po->eps);
+                float eps = po->eps;
                 if (ssq_in) {
                     // x is c times the sum that was staged, c = rsqrt(ms + eps') of the producer's input:
                     // normalising c*v with eps equals normalising v with eps / c^2
@@ -1212,7 +1242,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                         }
                         ms += part;
                     }
-                    eps *= ms * __ldg(&po->ssq_in_inv_cols) + __ldg(&po->ssq_in_eps);
+                    eps *= ms * po->ssq_in_inv_cols + po->ssq_in_eps;
                 }
                 const float sc = rsqrtf(sq * inv_cols + eps);
                 if ((CPM == 4 ? (t >> 1) : t) == j) myscale = sc;
@@ -1220,11 +1250,14 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         }
 
         // ---- stream this warp's items of the op ---------------------------------------------------
-        int tile0, lo, n, wq, wrem;
-        warp_range(__ldg(&po->q), __ldg(&po->rem), nun, cta_in_grp, tile0, lo, n, wq, wrem);
-        float *opy = ldg_ptr(&po->y) + (int64_t)grp * __ldg(&po->y_part_stride);
-        const int64_t ldy = __ldg(&po->ldy);
-        const int rows = __ldg(&po->rows);
+        int tile0, lo, n;
+        {
+            int wq_, wrem_;
+            warp_range(po->q, po->rem, nun, cta_in_grp, tile0, lo, n, wq_, wrem_);
+        }
+        float *opy = po->y + (int64_t)grp * po->y_part_stride;
+        const int64_t ldy = po->ldy;
+        const int rows = po->rows;
         const int hi = lo + n;
         int fin_tile = -1;   // CTA-local tile this warp adds up after the CTA barrier
 
@@ -1350,6 +1383,11 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         __syncthreads();
         if (fin_tile >= 0) {
             // partial sums of the warps that worked on the tile before this one, in warp order
+            int t0_, lo_, n_, wq, wrem;
+            {
+                const int parts_ = po->parts, G_ = (int)gridDim.x / parts_;
+                warp_range(po->q, po->rem, nun, (int)blockIdx.x % G_, t0_, lo_, n_, wq, wrem);
+            }
             const unsigned int ts = (unsigned int)(fin_tile * nun), big = (unsigned int)wrem * (unsigned int)(wq + 1);
             const int wf = wq == 0 ? (int)ts : ts < big ? (int)(ts / (unsigned int)(wq + 1))
                                                          : wrem + (int)((ts - big) / (unsigned int)wq);

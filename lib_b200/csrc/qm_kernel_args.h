@@ -53,7 +53,7 @@ struct QmGemvArgs {
 #define QM_MAX_INLINE_OPS 8
 #define QM_MAX_PEERS 8
 
-struct QmOp {
+struct alignas(16) QmOp {   // a multiple of 16 bytes: the kernels copy descriptors in 16-byte pieces
     const uint8_t *wq;   // tiled Q4_K store layout
     const float *x;      // activations [m][ldx]
     const float *x2;     // second operand of QM_XOP_ADD_RMSNORM / QM_XOP_SWIGLU, or null

@@ -57,6 +57,7 @@ struct qm_stack {
     size_t arena_bytes, flags_off;
     CUdeviceptr peer_base[QM_MAX_PEERS];
     bool peers_open;
+    bool peers_ipc;             // the peers' arenas were opened from IPC handles (closed again at destroy)
     bool tp_counter;            // peers reachable with native NVLink atomics: counter barrier
     unsigned int tp_epoch;
     bool use_graph, use_fused;
@@ -116,6 +117,7 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
     s->tp_rank = rank;
     s->arena = 0;
     s->peers_open = false;
+    s->peers_ipc = false;
     s->tp_epoch = 0;
     memset(s->peer_base, 0, sizeof s->peer_base);
     s->layer.resize(layers);
@@ -227,6 +229,33 @@ extern "C" int32_t qm_stack_set_peers(qm_ctx *c, qm_stack *s, const void *handle
             s->tp_counter = false;
     }
     s->peers_open = true;
+    s->peers_ipc = true;
+    return QM_OK;
+}
+
+// Base address and size of the tensor-parallel activation arena, for callers that drive all GPUs from
+// one process and hand the peers' arenas over as plain device pointers (qm_stack_set_peer_pointers).
+extern "C" int32_t qm_stack_arena(qm_ctx *c, qm_stack *s, uint64_t *base, int64_t *bytes) {
+    CHECK_CTX(c);
+    if (!stack_check(s) || !base || !bytes || s->tp_world < 2) return QM_ERR_ARG;
+    *base = (uint64_t)s->arena;
+    *bytes = (int64_t)s->arena_bytes;
+    return QM_OK;
+}
+
+// Single-process form of qm_stack_set_peers: bases[p] = the arena of rank p as this process addresses
+// it (peer access between the devices enabled by the caller, the reference's
+// Context.EnablePeerAccess, nvidia/driver/context.gen.go:98). Entry tp_rank is ignored.
+extern "C" int32_t qm_stack_set_peer_pointers(qm_ctx *c, qm_stack *s, const uint64_t *bases) {
+    CHECK_CTX(c);
+    if (!stack_check(s) || !bases || s->tp_world < 2 || s->peers_open) return QM_ERR_ARG;
+    for (int p = 0; p < s->tp_world; p++) {
+        s->peer_base[p] = p == s->tp_rank ? s->arena : (CUdeviceptr)bases[p];
+        if (!s->peer_base[p]) return QM_ERR_ARG;
+    }
+    s->tp_counter = false;
+    s->peers_open = true;
+    s->peers_ipc = false;
     return QM_OK;
 }
 
@@ -243,7 +272,7 @@ extern "C" int32_t qm_stack_destroy(qm_ctx *c, qm_stack *s) {
         if (s->sync_dev[i]) c->drv->cuMemFree_v2(s->sync_dev[i]);
     }
     if (s->tp_world > 1) {
-        if (s->peers_open)
+        if (s->peers_open && s->peers_ipc)
             for (int p = 0; p < s->tp_world; p++)
                 if (p != s->tp_rank && s->peer_base[p]) c->drv->cuIpcCloseMemHandle(s->peer_base[p]);
         if (s->arena) c->drv->cuMemFree_v2(s->arena);
@@ -648,8 +677,8 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
         // layers*m rows' worth of the half)
         const int cur = s->act == s->act_half[0] ? 0 : 1, other = cur ^ 1;
         if (s->half_m[other] > 0) {
-            DRV(c->drv->cuMemsetD8Async(s->act_half[other], 0xFF,
-                                        (size_t)s->layers * layer_floats(s, s->half_m[other]) * 4, c->stream));
+            DRV(c->drv->cuMemsetD32Async(s->act_half[other], 0xFFFFFFFFu,
+                                         (size_t)s->layers * layer_floats(s, s->half_m[other]), c->stream));
             s->half_m[other] = 0;
         }
         s->half_m[cur] = m;
@@ -669,7 +698,7 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
     if (s->fused_dd[m]) {
         // every output word of the step starts as "not yet written" (all ones)
         const size_t bytes = (size_t)(layer_bufs(s, s->layers, m).qkv - s->act);
-        DRV(c->drv->cuMemsetD8Async(s->act, 0xFF, bytes, c->stream));
+        DRV(c->drv->cuMemsetD32Async(s->act, 0xFFFFFFFFu, bytes / 4, c->stream));
         int32_t rc = qm_launch_ex(c, s->fused_dd_kernel[m], (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32,
                                   (unsigned)p.smem, &a, false, true);
         return rc ? rc : sum_last_parts(c, s, m);

@@ -931,8 +931,8 @@ __device__ __forceinline__ void cp_async_wait_n() {
 // adds the partial vectors of a producer that ran in K parts, applies the input transform and
 // quantizes into limb planes, sub-block sums and column weights; leaves each warp's part of the
 // sums of squares in ssq. Returns the thread's "gave up waiting" flag.
-template <int CPM, bool TP>
-__device__ __noinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, uint8_t *xs, int plane_stride,
+template <int CPM, bool TP, bool PARTS>
+__device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, uint8_t *xs, int plane_stride,
                                       uint32_t *xsum, float *sxw, float *ssq, bool dead) {
     const QmFusedArgs &a = *ap;
     constexpr int C = 16, NL = CPM == 4 ? 3 : 2, NT = 1;
@@ -942,7 +942,7 @@ __device__ __noinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, uin
     const float *opx = po->x, *opx2 = po->x2;
     const int64_t ldx = po->ldx;
     const bool norm = xop == 1 || xop == 2;
-    const int parts = po->parts, x_parts = po->x_parts;
+    const int parts = PARTS ? po->parts : 1, x_parts = PARTS ? po->x_parts : 1;
     const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G;
     const int col0 = grp * nun * QM_K_UNIT;   // first column of this group's K part
     const int64_t xps = po->x_part_stride;
@@ -1075,7 +1075,9 @@ __device__ __noinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, uin
 // poll their own arena only, so no barrier crosses the GPUs inside a step. One barrier over the
 // GPUs ends the launch: when it returns, every slice of the step has arrived everywhere, which
 // is what lets the host refill the other arena half with the "not yet written" pattern.
-template <int CPM, int D, bool TP>
+// PARTS: the op list may hold ops cut into K parts (QmOp::parts); compiled out otherwise, because
+// the streaming loop has no register to spare for it.
+template <int CPM, int D, bool TP, bool PARTS>
 __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     constexpr int C = 16;                       // warps per CTA
     constexpr int NL = CPM == 4 ? 3 : 2;        // limbs per activation row
@@ -1124,7 +1126,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         for (p_op++; p_op < a.nops; p_op++) {
             const QmOp *po = ops + p_op;
             int tile0, lo, n, wq, wrem;
-            const int units = __ldg(&po->units), parts = __ldg(&po->parts), total = __ldg(&po->units_total);
+            const int units = __ldg(&po->units), parts = PARTS ? __ldg(&po->parts) : 1, total = __ldg(&po->units_total);
             const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G;
             warp_range(__ldg(&po->q), __ldg(&po->rem), units, (int)blockIdx.x - grp * G, tile0, lo, n, wq, wrem);
             if (n > 0) {
@@ -1146,7 +1148,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             cp_async16(p_dst + 1536, p_src + 1536);
             if (lane < 16) cp_async16(p_dst + 2048, p_src + 2048);
             p_src += QM_Q4K_ITEM_BYTES;
-            if (--p_u == 0) {   // end of a tile's K part (the op's fields are re-read here, not kept in registers)
+            if (PARTS && --p_u == 0) {   // end of a tile's K part (the op's fields are re-read here, not kept in registers)
                 const QmOp *po = ops + p_op;
                 p_u = __ldg(&po->units);
                 p_src += (int64_t)(__ldg(&po->units_total) - p_u) * QM_Q4K_ITEM_BYTES;
@@ -1196,12 +1198,11 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         const int nun = po->units;
         const int xop = po->xop;
         const bool norm = xop == 1 || xop == 2;
-        const int parts = po->parts, x_parts = po->x_parts;
+        const int parts = PARTS ? po->parts : 1, x_parts = PARTS ? po->x_parts : 1;
         const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G, cta_in_grp = (int)blockIdx.x - grp * G;
 
-        // ---- stage x: poll until written, quantize into limbs (a call, so that its registers do
-        // not weigh on the streaming loop) ------------------------------------------------------------
-        dead = dd_stage<CPM, TP>(&a, po, xs, plane_stride, xsum, sxw, ssq, dead);
+        // ---- stage x: poll until written, quantize into limbs --------------------------------------
+        dead = dd_stage<CPM, TP, PARTS>(&a, po, xs, plane_stride, xsum, sxw, ssq, dead);
         __syncthreads();
         QM_DD_MARK(1);
         if (warp == C - 1 && opi + 1 < a.nops && lane < (int)(sizeof(QmOp) / 16))
@@ -1385,7 +1386,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             // partial sums of the warps that worked on the tile before this one, in warp order
             int t0_, lo_, n_, wq, wrem;
             {
-                const int parts_ = po->parts, G_ = (int)gridDim.x / parts_;
+                const int parts_ = PARTS ? po->parts : 1, G_ = (int)gridDim.x / parts_;
                 warp_range(po->q, po->rem, nun, (int)blockIdx.x % G_, t0_, lo_, n_, wq, wrem);
             }
             const unsigned int ts = (unsigned int)(fin_tile * nun), big = (unsigned int)wrem * (unsigned int)(wq + 1);
@@ -1453,24 +1454,31 @@ extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
 // Data-driven variants (no grid barrier between dependent ops): CPM = 4 mma columns per
 // activation row (up to two rows, three limbs) or 2 (up to four rows, two limbs), D ring stages
 // per warp as shared memory allows; _tp: tensor parallel, results stored into every GPU's arena
-// and one barrier over the GPUs at the end of the launch.
-#define QM_DD_KERNEL(name, cpm, d, tp)                                                       \
+// and one barrier over the GPUs at the end of the launch; _tpp: tensor parallel and op lists
+// with ops cut into K parts (each GPU holds few tiles of an op; the parts spread them over more CTAs).
+#define QM_DD_KERNEL(name, cpm, d, tp, parts)                                                \
     extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)                     \
         name(const __grid_constant__ QmFusedArgs a) {                                        \
-        dd_body<cpm, d, tp>(a);                                                              \
+        dd_body<cpm, d, tp, parts>(a);                                                       \
     }
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d2, 4, 2, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d3, 4, 3, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d4, 4, 4, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d2, 2, 2, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d3, 2, 3, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d4, 2, 4, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d2_tp, 4, 2, true)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d3_tp, 4, 3, true)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d4_tp, 4, 4, true)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d2_tp, 2, 2, true)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d3_tp, 2, 3, true)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d4_tp, 2, 4, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d2, 4, 2, false, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d3, 4, 3, false, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d4, 4, 4, false, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d2, 2, 2, false, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d3, 2, 3, false, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d4, 2, 4, false, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d2_tp, 4, 2, true, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d3_tp, 4, 3, true, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d4_tp, 4, 4, true, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d2_tp, 2, 2, true, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d3_tp, 2, 3, true, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d4_tp, 2, 4, true, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d2_tpp, 4, 2, true, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d3_tpp, 4, 3, true, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d4_tpp, 4, 4, true, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d2_tpp, 2, 2, true, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d3_tpp, 2, 3, true, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d4_tpp, 2, 4, true, true)
 
 // h = c * (sum of the K parts of the step's last matvec), see QmSumPartsArgs.
 extern "C" __global__ void __launch_bounds__(256) qm_sum_parts(const __grid_constant__ QmSumPartsArgs a) {

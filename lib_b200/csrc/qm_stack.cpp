@@ -402,12 +402,22 @@ static int32_t upload_ops(qm_ctx *c, qm_stack *s, int m, std::vector<QmOp> &ops)
 static int32_t build_fused_dd(qm_ctx *c, qm_stack *s, int m) {
     if (m >= qm_env_int("QM_IMAGE_MIN_M", 4) || qm_env_int("QM_DD", 1) == 0) return QM_ERR_SHAPE;
     const int grid = qm_fused_grid(c);
-    const int want_parts = qm_env_int("QM_PARTS", QM_MAX_PARTS);
-    auto parts_for = [&](const QmWeight *w) {
+    // The down projection (long K: its CTAs would each stage all of x) runs in four K parts. The o
+    // projection stays whole by default: its x is short, and every part adds a vector that each CTA of
+    // the consumer polls and loads.
+    auto parts_for = [&](const QmWeight *w, int want) {
         for (int k = QM_MAX_PARTS; k > 1; k >>= 1)
-            if (k <= want_parts && w->units % k == 0 && grid % k == 0) return k;
+            if (k <= want && w->units % k == 0 && grid % k == 0) return k;
         return 1;
     };
+    // On one GPU every op stays whole: the kernels without K parts keep their streaming loop free of
+    // the extra state, which is worth more there than the shorter staging.
+    // With few GPUs the same holds (2 GPUs measured: 1.04 ms per step whole against 1.05 with the down
+    // projection in two parts); from four GPUs on a GPU's slice of the down projection is 64 tiles
+    // or fewer, which fills under half of the CTAs unless it is cut.
+    const bool tp_parts = s->tp_world > 1;
+    const int want_o = tp_parts ? qm_env_int("QM_PARTS_O", 1) : 1;
+    const int want_dn = tp_parts ? qm_env_int("QM_PARTS_DN", s->tp_world >= 4 ? QM_MAX_PARTS : 1) : 1;
     int max_units = 0, So = QM_MAX_PARTS, Sd = QM_MAX_PARTS;
     for (int L = 0; L < s->layers; L++) {
         const QmLayer &ly = s->layer[L];
@@ -415,8 +425,8 @@ static int32_t build_fused_dd(qm_ctx *c, qm_stack *s, int m) {
         const QmWeight *ws[4] = {ly.qkv, ly.o, ly.gu, ly.dn};
         for (const QmWeight *w : ws)
             if (w->fmt != QM_FMT_Q4_K) return QM_ERR_FORMAT;
-        So = std::min(So, parts_for(ly.o));
-        Sd = std::min(Sd, parts_for(ly.dn));
+        So = std::min(So, parts_for(ly.o, want_o));
+        Sd = std::min(Sd, parts_for(ly.dn, want_dn));
     }
     for (int L = 0; L < s->layers; L++) {
         const QmLayer &ly = s->layer[L];
@@ -685,7 +695,8 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
         if (s->fused_dd[m]) {
             a.tp_counter = 0;
             s->tp_epoch += 1;   // one barrier over the GPUs per launch
-            int32_t rc = qm_launch_ex(c, s->fused_dd_kernel[m] + (QM_K_FUSED_Q4K_DD_C4D2_TP - QM_K_FUSED_Q4K_DD_C4D2),
+            const bool with_parts = s->fused_parts_o[m] > 1 || s->fused_parts_dn[m] > 1;
+            int32_t rc = qm_launch_ex(c, s->fused_dd_kernel[m] + ((with_parts ? QM_K_FUSED_Q4K_DD_C4D2_TPP : QM_K_FUSED_Q4K_DD_C4D2_TP) - QM_K_FUSED_Q4K_DD_C4D2),
                                       (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32, (unsigned)p.smem, &a, false, true);
             return rc ? rc : sum_last_parts(c, s, m);
         }

@@ -134,7 +134,8 @@ struct Cursor {   // walks the items of this warp, op after op
 // destination is shared memory or an activation image. Returns this lane's sum of squares.
 template <int NT>
 __device__ __forceinline__ float quantize_pair(const float (&v)[8], int j, int ul, int lane, int NL, int CPM,
-                                               uint8_t *xs_b, int pstride, uint32_t *xsum_b, float *sxw_b) {
+                                               uint8_t *xs_b, int pstride, uint32_t *xsum_b, float *sxw_b,
+                                               float wmul = 1.f) {
     float amax = 0.f, sum = 0.f, sq = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; e++) { amax = fmaxf(amax, fabsf(v[e])); sum += v[e]; sq = fmaf(v[e], v[e], sq); }
@@ -186,7 +187,7 @@ __device__ __forceinline__ float quantize_pair(const float (&v)[8], int j, int u
     }
     if (lane < CPM) {
         const float lw = lane == 0 ? 1.f : lane == 1 ? (1.f / 128.f) : lane == 2 && NL == 3 ? (1.f / 16384.f) : 0.f;
-        sxw_b[(size_t)ul * 8 * NT + n0 + lane] = sx * lw;
+        sxw_b[(size_t)ul * 8 * NT + n0 + lane] = sx * lw * wmul;   // wmul: a constant the consumer folds into the column weight
     }
     return sq;
 }
@@ -998,7 +999,7 @@ __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, 
                             v[0] += r[2 * k].x; v[1] += r[2 * k].y; v[2] += r[2 * k].z; v[3] += r[2 * k].w;
                             v[4] += r[2 * k + 1].x; v[5] += r[2 * k + 1].y; v[6] += r[2 * k + 1].z; v[7] += r[2 * k + 1].w;
                         }
-                    const float sq = quantize_pair<NT>(v, j, ul, lane, NL, CPM, xs, plane_stride, xsum, sxw);
+                    const float sq = quantize_pair<NT>(v, j, ul, lane, NL, CPM, xs, plane_stride, xsum, sxw, 0.0625f);
                     if (norm) {
                         if (j != sq_j) {
                             if (sq_j >= 0) {
@@ -1046,7 +1047,7 @@ __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, 
                         for (int e = 0; e < 8; e++)
                             v[e] = xop == 2 ? v[e] + w[e] : v[e] / (1.f + __expf(-v[e])) * w[e];
                     }
-                    const float sq = quantize_pair<NT>(v, j, ul, lane, NL, CPM, xs, plane_stride, xsum, sxw);
+                    const float sq = quantize_pair<NT>(v, j, ul, lane, NL, CPM, xs, plane_stride, xsum, sxw, 0.0625f);
                     if (norm) {   // per-warp running sum of squares of activation row j
                         if (j != sq_j) {
                             if (sq_j >= 0) {
@@ -1086,7 +1087,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int M = a.m, P = M * NL;
-    const QmOp *ops = a.ops;   // a device array (this kernel runs op lists, not single matvecs)
+    const bool inl = a.ops == nullptr;   // a single matvec: its few ops travel in the launch parameters
 
     // ---- shared memory (qm_plan_fused computes an upper bound of this) -------------------------
     const int plane_stride = a.max_units * 256 + 64;
@@ -1095,13 +1096,19 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     float *sxw = reinterpret_cast<float *>(xsum + (size_t)a.max_units * 8 * 4);     // [units][8] column weights
     float *ssq = sxw + (size_t)a.max_units * 8;                                     // [8][16]
     float *slots = ssq + 8 * 16;                                                    // [C][2][M*16]
-    QmOp *sop = reinterpret_cast<QmOp *>(((uintptr_t)(slots + (size_t)C * 2 * M * 16) + 15) & ~(uintptr_t)15);   // [2]
-    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(sop + 2) + 127) & ~(uintptr_t)127);
+    QmOp *sop = reinterpret_cast<QmOp *>(((uintptr_t)(slots + (size_t)C * 2 * M * 16) + 15) & ~(uintptr_t)15);   // [2], or [nops] inline
+    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(sop + (inl ? QM_MAX_INLINE_OPS : 2)) + 127) & ~(uintptr_t)127);
     uint8_t *my_stages = stages + (size_t)warp * D * kStageBytes;
 
+    asm volatile("griddepcontrol.launch_dependents;");
     // columns of absent activation rows and pad columns must read as zero weights and sums
     for (int i = tid; i < a.max_units * 8 * 5; i += C * 32) xsum[i] = 0u;   // xsum and sxw are adjacent
+    // inline ops: all of them into shared memory, where the producer side reads ahead too
+    if (inl)
+        for (int i = tid; i < a.nops * (int)(sizeof(QmOp) / 16); i += C * 32)
+            reinterpret_cast<uint4 *>(sop)[i] = reinterpret_cast<const uint4 *>(a.inl)[i];
     __syncthreads();
+    const QmOp *ops = inl ? sop : a.ops;
 
     // This warp's items of op `o`: the CTA owns a run of whole tiles, its items are dealt evenly to
     // the warps in order. Returns the first item and the count in CTA-local coordinates.
@@ -1126,14 +1133,14 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         for (p_op++; p_op < a.nops; p_op++) {
             const QmOp *po = ops + p_op;
             int tile0, lo, n, wq, wrem;
-            const int units = __ldg(&po->units), parts = PARTS ? __ldg(&po->parts) : 1, total = __ldg(&po->units_total);
+            const int units = po->units, parts = PARTS ? po->parts : 1, total = po->units_total;
             const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G;
-            warp_range(__ldg(&po->q), __ldg(&po->rem), units, (int)blockIdx.x - grp * G, tile0, lo, n, wq, wrem);
+            warp_range(po->q, po->rem, units, (int)blockIdx.x - grp * G, tile0, lo, n, wq, wrem);
             if (n > 0) {
                 const int tile = lo / units, u = lo - tile * units;
                 p_n = n;
                 p_u = units - u;
-                p_src = ldg_ptr(&po->wq) + ((int64_t)(tile0 + tile) * total + grp * units + u) * QM_Q4K_ITEM_BYTES + lane * 16;
+                p_src = po->wq + ((int64_t)(tile0 + tile) * total + grp * units + u) * QM_Q4K_ITEM_BYTES + lane * 16;
                 break;
             }
         }
@@ -1150,8 +1157,8 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             p_src += QM_Q4K_ITEM_BYTES;
             if (PARTS && --p_u == 0) {   // end of a tile's K part (the op's fields are re-read here, not kept in registers)
                 const QmOp *po = ops + p_op;
-                p_u = __ldg(&po->units);
-                p_src += (int64_t)(__ldg(&po->units_total) - p_u) * QM_Q4K_ITEM_BYTES;
+                p_u = po->units;
+                p_src += (int64_t)(po->units_total - p_u) * QM_Q4K_ITEM_BYTES;
             }
             if (--p_n == 0) p_next_op();
         }
@@ -1187,11 +1194,13 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     // The descriptor of the current op is read from shared memory; a warp copies the next op's
     // there while the current one streams.
     static_assert(sizeof(QmOp) % 16 == 0, "QmOp is copied in 16-byte pieces");
-    if (warp == 0 && lane < (int)(sizeof(QmOp) / 16))
+    if (!inl && warp == 0 && lane < (int)(sizeof(QmOp) / 16))
         reinterpret_cast<uint4 *>(&sop[0])[lane] = __ldg(reinterpret_cast<const uint4 *>(ops) + lane);
+    // the activations of a launch's first op may come from the launch before it in the stream
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     for (int opi = 0; opi < a.nops; opi++) {
-        const QmOp *po = &sop[opi & 1];
+        const QmOp *po = inl ? &sop[opi] : &sop[opi & 1];
         QM_DD_MARK(0);
         // every warp has finished with the activation planes and the partial sums of the op before
         __syncthreads();
@@ -1205,7 +1214,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         dead = dd_stage<CPM, TP, PARTS>(&a, po, xs, plane_stride, xsum, sxw, ssq, dead);
         __syncthreads();
         QM_DD_MARK(1);
-        if (warp == C - 1 && opi + 1 < a.nops && lane < (int)(sizeof(QmOp) / 16))
+        if (!inl && warp == C - 1 && opi + 1 < a.nops && lane < (int)(sizeof(QmOp) / 16))
             reinterpret_cast<uint4 *>(&sop[(opi + 1) & 1])[lane] = __ldg(reinterpret_cast<const uint4 *>(ops + opi + 1) + lane);
 
         // RMS normalisation is a scalar per activation row: it multiplies the finished sums
@@ -1360,10 +1369,11 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                 const float2 ddB = __half22float2(*reinterpret_cast<const __half2 *>(&hB.x));
                 const float2 cw = *reinterpret_cast<const float2 *>(cwp);
                 // even column: first limb / high half of the sums, weight sx; odd column: second limb /
-                // low half, weight sx/128; the sums are in units of 127*sx
-                const float mx = 127.f * cw.x, my = 16256.f * cw.y;
-                const float f0 = fmaf((float)accH[0], 0.0625f, (float)accL[0]), f1 = fmaf((float)accH[1], 0.0625f, (float)accL[1]);
-                const float f2 = fmaf((float)accH[2], 0.0625f, (float)accL[2]), f3 = fmaf((float)accH[3], 0.0625f, (float)accL[3]);
+                // low half, weight sx/128; the sums are in units of 127*sx. The column weights come
+                // divided by 16: the integer sums are taken as 16*low + high (below 2^29).
+                const float mx = 2032.f * cw.x, my = 260096.f * cw.y;
+                const float f0 = (float)(accL[0] * 16 + accH[0]), f1 = (float)(accL[1] * 16 + accH[1]);
+                const float f2 = (float)(accL[2] * 16 + accH[2]), f3 = (float)(accL[3] * 16 + accH[3]);
                 accF[0] = fmaf(ddA.x * cw.x, f0, fmaf(-ddA.y * mx, accM[0], accF[0]));
                 accF[1] = fmaf(ddA.x * cw.y, f1, fmaf(-ddA.y * my, accM[1], accF[1]));
                 accF[2] = fmaf(ddB.x * cw.x, f2, fmaf(-ddB.y * mx, accM[2], accF[2]));

@@ -715,6 +715,7 @@ void qm_fill_op(qm_ctx *c, const QmFusedPlan &p, const QmWeight *w, uint64_t x, 
     op->q = op->tiles / grid;
     op->rem = op->tiles % grid;
     op->balanced = 0;
+    op->parts = op->x_parts = 1;
     (void)p;
     op->eps = 1e-6f;
 }
@@ -743,6 +744,13 @@ static int32_t fused_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev,
     a.debug_slot = env_int("QM_DEBUG_OP", 0);
 #endif
     a.wait_cycles = qm_wait_cycles();
+    // One op of up to four activation rows whose K fits whole: the lean body of the data-driven
+    // kernels (an op that reads the launch's input polls nothing).
+    if (p.slices == 1 && p.nt == 1 && p.consumers == 16 && p.depth >= 2 && p.depth <= 4 && env_int("QM_DD", 1) != 0) {
+        const int k = (p.cpm == 4 ? QM_K_FUSED_Q4K_DD_C4D2 : QM_K_FUSED_Q4K_DD_C2D2) + (p.depth - 2);
+        return qm_launch_ex(c, k, (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32, (unsigned)p.smem, &a,
+                            (flags & QM_FLAG_PDL) != 0, false);
+    }
     const bool coop = p.slices > 1;  // K slices meet at a grid barrier: all CTAs must be co-resident
     if (coop) DRV(c->drv->cuMemsetD32Async(c->gridbar_dev, 0, 1, c->stream));
     return qm_launch_ex(c, p.nt == 1 ? QM_K_FUSED_Q4K_NT1 : QM_K_FUSED_Q4K_NT2,

@@ -948,7 +948,6 @@ __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, 
     const int col0 = grp * nun * QM_K_UNIT;   // first column of this group's K part
     const int64_t xps = po->x_part_stride;
     {
-            constexpr int kRounds = 2;   // (row, unit) pairs of a warp in flight at once
             const int total = M * nun;
             const bool poll = po->barrier != 0;   // x is an earlier op's output
             float sq_run = 0.f;
@@ -1013,54 +1012,59 @@ __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, 
                         sq_run += sq;
                     }
                 }
-            } else
-            for (int base = warp; base < total; base += kRounds * C) {
-                float4 raw[kRounds][4];
-#pragma unroll
-                for (int r = 0; r < kRounds; r++)
-                    if (base + r * C < total) load_x(base + r * C, raw[r]);
-#pragma unroll
-                for (int r = 0; r < kRounds; r++) {
-                    const int idx = base + r * C;
-                    if (idx >= total) break;
-                    if (poll) {
-                        long long t0 = 0;
-                        for (;;) {
-                            bool ok = written4(raw[r][0]) & written4(raw[r][1]);
-                            if (xop >= 2) ok = ok & written4(raw[r][2]) & written4(raw[r][3]);
-                            if (__all_sync(0xffffffffu, ok || dead)) break;
-                            if (t0 == 0) t0 = clock64();
-                            else if (clock64() - t0 > a.wait_cycles) {
-                                if (lane == 0) atomicOr(a.status, QM_STATUS_TIMEOUT);
-                                dead = true;   // this and every later wait of the thread give up at once
-                            }
-                            load_x(idx, raw[r]);
+            } else {
+            // Two register sets alternate: while one (row, unit) pair is quantized the loads of the
+            // next pair but one are in flight, so only the first wait of an op is fully exposed.
+            auto consume = [&](int idx, float4 (&r)[4]) {
+                if (poll) {
+                    long long t0 = 0;
+                    for (;;) {
+                        bool ok = written4(r[0]) & written4(r[1]);
+                        if (xop >= 2) ok = ok & written4(r[2]) & written4(r[3]);
+                        if (__all_sync(0xffffffffu, ok || dead)) break;
+                        if (t0 == 0) t0 = clock64();
+                        else if (clock64() - t0 > a.wait_cycles) {
+                            if (lane == 0) atomicOr(a.status, QM_STATUS_TIMEOUT);
+                            dead = true;   // this and every later wait of the thread give up at once
                         }
-                    }
-                    const int j = idx / nun, ul = idx - j * nun;
-                    float v[8] = {raw[r][0].x, raw[r][0].y, raw[r][0].z, raw[r][0].w,
-                                  raw[r][1].x, raw[r][1].y, raw[r][1].z, raw[r][1].w};
-                    if (xop >= 2) {
-                        const float w[8] = {raw[r][2].x, raw[r][2].y, raw[r][2].z, raw[r][2].w,
-                                            raw[r][3].x, raw[r][3].y, raw[r][3].z, raw[r][3].w};
-#pragma unroll
-                        for (int e = 0; e < 8; e++)
-                            v[e] = xop == 2 ? v[e] + w[e] : v[e] / (1.f + __expf(-v[e])) * w[e];
-                    }
-                    const float sq = quantize_pair<NT>(v, j, ul, lane, NL, CPM, xs, plane_stride, xsum, sxw, 0.0625f);
-                    if (norm) {   // per-warp running sum of squares of activation row j
-                        if (j != sq_j) {
-                            if (sq_j >= 0) {
-#pragma unroll
-                                for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
-                                if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
-                            }
-                            sq_j = j;
-                            sq_run = 0.f;
-                        }
-                        sq_run += sq;
+                        load_x(idx, r);
                     }
                 }
+                const int j = idx / nun, ul = idx - j * nun;
+                float v[8] = {r[0].x, r[0].y, r[0].z, r[0].w, r[1].x, r[1].y, r[1].z, r[1].w};
+                if (xop >= 2) {
+                    const float w[8] = {r[2].x, r[2].y, r[2].z, r[2].w, r[3].x, r[3].y, r[3].z, r[3].w};
+#pragma unroll
+                    for (int e = 0; e < 8; e++)
+                        v[e] = xop == 2 ? v[e] + w[e] : v[e] / (1.f + __expf(-v[e])) * w[e];
+                }
+                const float sq = quantize_pair<NT>(v, j, ul, lane, NL, CPM, xs, plane_stride, xsum, sxw, 0.0625f);
+                if (norm) {   // per-warp running sum of squares of activation row j
+                    if (j != sq_j) {
+                        if (sq_j >= 0) {
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
+                            if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
+                        }
+                        sq_j = j;
+                        sq_run = 0.f;
+                    }
+                    sq_run += sq;
+                }
+            };
+            {
+                float4 rawA[4], rawB[4];
+                if (warp < total) load_x(warp, rawA);
+                if (warp + C < total) load_x(warp + C, rawB);
+                for (int idx = warp; idx < total; idx += 2 * C) {
+                    consume(idx, rawA);
+                    if (idx + 2 * C < total) load_x(idx + 2 * C, rawA);
+                    if (idx + C < total) {
+                        consume(idx + C, rawB);
+                        if (idx + 3 * C < total) load_x(idx + 3 * C, rawB);
+                    }
+                }
+            }
             }
             if (sq_j >= 0) {
 #pragma unroll

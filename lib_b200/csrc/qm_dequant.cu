@@ -221,3 +221,19 @@ extern "C" __global__ void __launch_bounds__(256) qm_repack_q80(const __grid_con
                 (uint32_t)s[1 + 2 * w] | ((uint32_t)s[2 + 2 * w] << 16);
     }
 }
+
+// Part-major copy of a tiled Q4_K store: item (tile, unit) of the [tiles][units] store goes to
+// [unit / ups][tile][unit % ups], so that the items of one K part of every tile are contiguous.
+// Sixteen bytes per thread.
+extern "C" __global__ void __launch_bounds__(256) qm_repack_parts(const __grid_constant__ QmPartsArgs a) {
+    const int64_t per_item = QM_Q4K_ITEM_BYTES / 16;
+    const int64_t total = (int64_t)a.tiles * a.units * per_item;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t item = idx / per_item, piece = idx - item * per_item;
+        const int64_t tile = item / a.units;
+        const int u = (int)(item - tile * a.units), part = u / a.ups, ul = u - part * a.ups;
+        const int64_t dst = (((int64_t)part * a.tiles + tile) * a.ups + ul) * per_item + piece;
+        reinterpret_cast<uint4 *>(a.dst)[dst] = reinterpret_cast<const uint4 *>(a.src)[idx];
+    }
+}

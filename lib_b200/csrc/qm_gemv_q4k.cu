@@ -932,7 +932,7 @@ __device__ __forceinline__ void cp_async_wait_n() {
 // adds the partial vectors of a producer that ran in K parts, applies the input transform and
 // quantizes into limb planes, sub-block sums and column weights; leaves each warp's part of the
 // sums of squares in ssq. Returns the thread's "gave up waiting" flag.
-template <int CPM, bool TP, bool PARTS>
+template <int CPM, bool TP>
 __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, uint8_t *xs, int plane_stride,
                                       uint32_t *xsum, float *sxw, float *ssq, bool dead) {
     const QmFusedArgs &a = *ap;
@@ -943,9 +943,8 @@ __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, 
     const float *opx = po->x, *opx2 = po->x2;
     const int64_t ldx = po->ldx;
     const bool norm = xop == 1 || xop == 2;
-    const int parts = PARTS ? po->parts : 1, x_parts = PARTS ? po->x_parts : 1;
-    const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G;
-    const int col0 = grp * nun * QM_K_UNIT;   // first column of this group's K part
+    const int x_parts = po->x_parts;
+    const int col0 = po->unit0 * QM_K_UNIT;   // first column of this op's K range
     const int64_t xps = po->x_part_stride;
     {
             const int total = M * nun;
@@ -1080,9 +1079,7 @@ __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, 
 // poll their own arena only, so no barrier crosses the GPUs inside a step. One barrier over the
 // GPUs ends the launch: when it returns, every slice of the step has arrived everywhere, which
 // is what lets the host refill the other arena half with the "not yet written" pattern.
-// PARTS: the op list may hold ops cut into K parts (QmOp::parts); compiled out otherwise, because
-// the streaming loop has no register to spare for it.
-template <int CPM, int D, bool TP, bool PARTS>
+template <int CPM, int D, bool TP>
 __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     constexpr int C = 16;                       // warps per CTA
     constexpr int NL = CPM == 4 ? 3 : 2;        // limbs per activation row
@@ -1112,15 +1109,18 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         for (int i = tid; i < a.nops * (int)(sizeof(QmOp) / 16); i += C * 32)
             reinterpret_cast<uint4 *>(sop)[i] = reinterpret_cast<const uint4 *>(a.inl)[i];
     __syncthreads();
-    const QmOp *ops = inl ? sop : a.ops;
+    // K parts: the CTAs form a.ngroups groups and each group runs its own copy of the op list (the
+    // copies differ only in the ops that are cut into parts)
+    const int ngroups = a.ngroups > 1 && !inl ? a.ngroups : 1;
+    const QmOp *ops = inl ? sop : a.ops + (size_t)((int)blockIdx.x / ((int)gridDim.x / ngroups)) * a.nops;
 
     // This warp's items of op `o`: the CTA owns a run of whole tiles, its items are dealt evenly to
     // the warps in order. Returns the first item and the count in CTA-local coordinates.
     // An op cut into K parts splits the CTAs into as many groups; `c` is then the CTA's index within
     // its group (q and rem are computed for the group's size).
-    auto warp_range = [&](int q, int rem, int units, int c, int &tile0, int &lo, int &n, int &wq, int &wrem) {
+    auto warp_range = [&](int q, int rem, int units, int c, int nctas, int &tile0, int &lo, int &n, int &wq, int &wrem) {
         tile0 = c * q + min(c, rem);
-        const int Ic = (q + (c < rem ? 1 : 0)) * units;
+        const int Ic = (c >= 0 && c < nctas) ? (q + (c < rem ? 1 : 0)) * units : 0;
         wq = Ic / C;
         wrem = Ic - wq * C;
         lo = warp * wq + min(warp, wrem);
@@ -1128,23 +1128,19 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     };
 
     // ---- producer side of the ring: a pointer and a count per op -------------------------------
-    // (the items of a tile's K part are contiguous in the store; the next tile's part follows
-    // p_skip bytes later)
-    int p_op = -1, p_n = 0, p_u = 0;
+    // (a warp's items of an op are one contiguous run of the store)
+    int p_op = -1, p_n = 0;
     const uint8_t *p_src = nullptr;
     auto p_next_op = [&]() {
         p_n = 0;
         for (p_op++; p_op < a.nops; p_op++) {
             const QmOp *po = ops + p_op;
             int tile0, lo, n, wq, wrem;
-            const int units = po->units, parts = PARTS ? po->parts : 1, total = po->units_total;
-            const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G;
-            warp_range(po->q, po->rem, units, (int)blockIdx.x - grp * G, tile0, lo, n, wq, wrem);
+            const int units = po->units;
+            warp_range(po->q, po->rem, units, (int)blockIdx.x - po->cta0, po->nctas, tile0, lo, n, wq, wrem);
             if (n > 0) {
-                const int tile = lo / units, u = lo - tile * units;
                 p_n = n;
-                p_u = units - u;
-                p_src = po->wq + ((int64_t)(tile0 + tile) * total + grp * units + u) * QM_Q4K_ITEM_BYTES + lane * 16;
+                p_src = po->wq + ((int64_t)tile0 * units + lo) * QM_Q4K_ITEM_BYTES + lane * 16;
                 break;
             }
         }
@@ -1159,11 +1155,6 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             cp_async16(p_dst + 1536, p_src + 1536);
             if (lane < 16) cp_async16(p_dst + 2048, p_src + 2048);
             p_src += QM_Q4K_ITEM_BYTES;
-            if (PARTS && --p_u == 0) {   // end of a tile's K part (the op's fields are re-read here, not kept in registers)
-                const QmOp *po = ops + p_op;
-                p_u = po->units;
-                p_src += (int64_t)(po->units_total - p_u) * QM_Q4K_ITEM_BYTES;
-            }
             if (--p_n == 0) p_next_op();
         }
         cp_async_commit();
@@ -1211,11 +1202,11 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         const int nun = po->units;
         const int xop = po->xop;
         const bool norm = xop == 1 || xop == 2;
-        const int parts = PARTS ? po->parts : 1, x_parts = PARTS ? po->x_parts : 1;
-        const int G = (int)gridDim.x / parts, grp = (int)blockIdx.x / G, cta_in_grp = (int)blockIdx.x - grp * G;
+        const int parts = po->parts, x_parts = po->x_parts;
+        const int cta_in_grp = (int)blockIdx.x - po->cta0;
 
         // ---- stage x: poll until written, quantize into limbs --------------------------------------
-        dead = dd_stage<CPM, TP, PARTS>(&a, po, xs, plane_stride, xsum, sxw, ssq, dead);
+        dead = dd_stage<CPM, TP>(&a, po, xs, plane_stride, xsum, sxw, ssq, dead);
         __syncthreads();
         QM_DD_MARK(1);
         if (!inl && warp == C - 1 && opi + 1 < a.nops && lane < (int)(sizeof(QmOp) / 16))
@@ -1234,7 +1225,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                 if (parts > 1) {
                     // a K part leaves its products unscaled; the consumer scales the sum. One CTA of the
                     // group publishes the part's sum of squares.
-                    if (cta_in_grp == 0 && tid == 0) st_relaxed_f32(ssq_out + grp * 8 + j, sq);
+                    if (cta_in_grp == 0 && tid == 0) st_relaxed_f32(ssq_out + po->part * 8 + j, sq);
                     continue;
                 }
                 float eps = po->eps;
@@ -1267,9 +1258,9 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         int tile0, lo, n;
         {
             int wq_, wrem_;
-            warp_range(po->q, po->rem, nun, cta_in_grp, tile0, lo, n, wq_, wrem_);
+            warp_range(po->q, po->rem, nun, cta_in_grp, po->nctas, tile0, lo, n, wq_, wrem_);
         }
-        float *opy = po->y + (int64_t)grp * po->y_part_stride;
+        float *opy = po->y;
         const int64_t ldy = po->ldy;
         const int rows = po->rows;
         const int hi = lo + n;
@@ -1399,10 +1390,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         if (fin_tile >= 0) {
             // partial sums of the warps that worked on the tile before this one, in warp order
             int t0_, lo_, n_, wq, wrem;
-            {
-                const int parts_ = PARTS ? po->parts : 1, G_ = (int)gridDim.x / parts_;
-                warp_range(po->q, po->rem, nun, (int)blockIdx.x % G_, t0_, lo_, n_, wq, wrem);
-            }
+            warp_range(po->q, po->rem, nun, (int)blockIdx.x - po->cta0, po->nctas, t0_, lo_, n_, wq, wrem);
             const unsigned int ts = (unsigned int)(fin_tile * nun), big = (unsigned int)wrem * (unsigned int)(wq + 1);
             const int wf = wq == 0 ? (int)ts : ts < big ? (int)(ts / (unsigned int)(wq + 1))
                                                          : wrem + (int)((ts - big) / (unsigned int)wq);
@@ -1468,31 +1456,24 @@ extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
 // Data-driven variants (no grid barrier between dependent ops): CPM = 4 mma columns per
 // activation row (up to two rows, three limbs) or 2 (up to four rows, two limbs), D ring stages
 // per warp as shared memory allows; _tp: tensor parallel, results stored into every GPU's arena
-// and one barrier over the GPUs at the end of the launch; _tpp: tensor parallel and op lists
-// with ops cut into K parts (each GPU holds few tiles of an op; the parts spread them over more CTAs).
-#define QM_DD_KERNEL(name, cpm, d, tp, parts)                                                \
+// and one barrier over the GPUs at the end of the launch.
+#define QM_DD_KERNEL(name, cpm, d, tp)                                                       \
     extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)                     \
         name(const __grid_constant__ QmFusedArgs a) {                                        \
-        dd_body<cpm, d, tp, parts>(a);                                                       \
+        dd_body<cpm, d, tp>(a);                                                              \
     }
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d2, 4, 2, false, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d3, 4, 3, false, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d4, 4, 4, false, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d2, 2, 2, false, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d3, 2, 3, false, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d4, 2, 4, false, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d2_tp, 4, 2, true, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d3_tp, 4, 3, true, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d4_tp, 4, 4, true, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d2_tp, 2, 2, true, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d3_tp, 2, 3, true, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d4_tp, 2, 4, true, false)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d2_tpp, 4, 2, true, true)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d3_tpp, 4, 3, true, true)
-QM_DD_KERNEL(qm_fused_q4k_dd_c4d4_tpp, 4, 4, true, true)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d2_tpp, 2, 2, true, true)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d3_tpp, 2, 3, true, true)
-QM_DD_KERNEL(qm_fused_q4k_dd_c2d4_tpp, 2, 4, true, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d2, 4, 2, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d3, 4, 3, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d4, 4, 4, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d2, 2, 2, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d3, 2, 3, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d4, 2, 4, false)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d2_tp, 4, 2, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d3_tp, 4, 3, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c4d4_tp, 4, 4, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d2_tp, 2, 2, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d3_tp, 2, 3, true)
+QM_DD_KERNEL(qm_fused_q4k_dd_c2d4_tp, 2, 4, true)
 
 // h = c * (sum of the K parts of the step's last matvec), see QmSumPartsArgs.
 extern "C" __global__ void __launch_bounds__(256) qm_sum_parts(const __grid_constant__ QmSumPartsArgs a) {

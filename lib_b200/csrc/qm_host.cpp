@@ -87,9 +87,7 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d2"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d3"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d4"},
     {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d2_tp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d3_tp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d4_tp"},
     {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d2_tp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d3_tp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d4_tp"},
-    {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d2_tpp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d3_tpp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d4_tpp"},
-    {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d2_tpp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d3_tpp"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c2d4_tpp"},
-    {QM_MOD_Q4K, "qm_sum_parts"},
+    {QM_MOD_Q4K, "qm_sum_parts"}, {QM_MOD_DEQUANT, "qm_repack_parts"},
     {QM_MOD_GEMM, "qm_gemm_q4k_bf16"}, {QM_MOD_GEMM, "qm_gemm_q4k_bf16_r256"},
     {QM_MOD_GEMM, "qm_gemm_q4k_bf16_k128"}, {QM_MOD_GEMM, "qm_gemm_q4k_bf16_r256_k128"},
     {QM_MOD_MOE, "qm_moe_route"},      {QM_MOD_MOE, "qm_moe_lists"},      {QM_MOD_MOE, "qm_moe_gather"},
@@ -177,7 +175,7 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             r = d->cuModuleGetFunction(&c->fn[k], c->modules[kKernels[k].module], kKernels[k].name);
             if (r != CUDA_SUCCESS) err = QM_ERR_NO_KERNEL;
         }
-        for (int k = QM_K_FUSED_Q4K_NT1; k <= QM_K_FUSED_Q4K_DD_C2D4_TPP && !err; k++) {
+        for (int k = QM_K_FUSED_Q4K_NT1; k <= QM_K_FUSED_Q4K_DD_C2D4_TP && !err; k++) {
             r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
@@ -716,6 +714,9 @@ void qm_fill_op(qm_ctx *c, const QmFusedPlan &p, const QmWeight *w, uint64_t x, 
     op->rem = op->tiles % grid;
     op->balanced = 0;
     op->parts = op->x_parts = 1;
+    op->part = 0;
+    op->cta0 = 0;
+    op->nctas = grid;
     (void)p;
     op->eps = 1e-6f;
 }

@@ -17,8 +17,7 @@ enum {
     QM_K_FUSED_Q4K_DD_C2D2, QM_K_FUSED_Q4K_DD_C2D3, QM_K_FUSED_Q4K_DD_C2D4,
     QM_K_FUSED_Q4K_DD_C4D2_TP, QM_K_FUSED_Q4K_DD_C4D3_TP, QM_K_FUSED_Q4K_DD_C4D4_TP,
     QM_K_FUSED_Q4K_DD_C2D2_TP, QM_K_FUSED_Q4K_DD_C2D3_TP, QM_K_FUSED_Q4K_DD_C2D4_TP,
-    QM_K_FUSED_Q4K_DD_C4D2_TPP, QM_K_FUSED_Q4K_DD_C4D3_TPP, QM_K_FUSED_Q4K_DD_C4D4_TPP,
-    QM_K_FUSED_Q4K_DD_C2D2_TPP, QM_K_FUSED_Q4K_DD_C2D3_TPP, QM_K_FUSED_Q4K_DD_C2D4_TPP, QM_K_SUM_PARTS,
+    QM_K_SUM_PARTS, QM_K_REPACK_PARTS,
     QM_K_GEMM_Q4K, QM_K_GEMM_Q4K_R256, QM_K_GEMM_Q4K_K128, QM_K_GEMM_Q4K_R256_K128, QM_K_MOE_ROUTE, QM_K_MOE_LISTS, QM_K_MOE_GATHER, QM_K_MOE_COMBINE,
     QM_K_DEQUANT_IQ2XXS, QM_K_GEMV_Q2K_M1, QM_K_GEMV_Q2K_M2, QM_K_GEMV_Q2K_M4, QM_K_GEMV_Q2K_M8,
     QM_K_GEMV_IQ2XXS_M1, QM_K_GEMV_IQ2XXS_M2, QM_K_GEMV_IQ2XXS_M4, QM_K_GEMV_IQ2XXS_M8, QM_K_COUNT

@@ -83,17 +83,20 @@ struct alignas(16) QmOp {   // a multiple of 16 bytes: the kernels copy descript
     unsigned int *q_cnt;      // producer side: one completion counter per unit of the next op's x, zero at launch
     int32_t q_half_tiles;     // 16-row tiles of y per operand of the next op (its cols / 16)
     int32_t q_halves;         // 1, or 2 when the next op's x is the sum of two halves of y
-    // K parts (data-driven kernels only). An op with parts = S > 1 is cut into S column ranges of
-    // `units` K units each; the CTAs form S groups, group s computes the partial products of range s
-    // over all tiles and stores them, WITHOUT the RMS scale of its input, to y + s*y_part_stride. A
-    // group stages only its range of x, and the tiles spread over S times as many (tile, range)
-    // pieces. The consumer (x_parts = S) adds the S partial vectors while it stages them; it
-    // normalises that sum itself, and to make the result equal to normalising the scaled sum it
-    // needs the producer's input mean square: group s leaves the sum of squares of its range per
-    // activation row in ssq_out[s*8 + row], the consumer reads all S from ssq_in.
-    int32_t parts;            // producer side: K parts of this op (1 = whole K per CTA)
+    // K parts (data-driven kernels only). An op can be cut into S column ranges ("parts") of
+    // `units` K units each. The CTAs of a launch then form groups (QmFusedArgs::ngroups), every
+    // group runs its own copy of the op list, and in the copy of group g the op IS part
+    // `part`: wq points at that part's items (the stack keeps a part-major copy of the matrix, so
+    // they are contiguous), unit0 is its first K unit of x, y its partial output vector, and only
+    // the CTAs [cta0, cta0 + nctas) work on it. A part leaves its products WITHOUT the RMS scale
+    // of its input. The consumer (x_parts = S) adds the S partial vectors while it stages them;
+    // it normalises that sum itself, and to make the result equal to normalising the scaled sum
+    // it needs the producer's input mean square: part s leaves the sum of squares of its range
+    // per activation row in ssq_out[s*8 + row], the consumer reads all S from ssq_in.
+    int32_t parts;            // producer side: K parts this op is one of (1 = the op is whole)
+    int32_t part;             // which part
+    int32_t cta0, nctas;      // the CTAs that work on this op: [cta0, cta0 + nctas)
     int32_t x_parts;          // consumer side: partial vectors that add up to x (1 = x is one vector)
-    int64_t y_part_stride;    // floats between the partial output vectors
     int64_t x_part_stride;    // floats between the partial input vectors
     float *ssq_out;           // producer side: [parts][8] sums of squares of x per K part and activation row
     const float *ssq_in;      // consumer side: the same words of the op that produced x
@@ -113,7 +116,7 @@ struct QmFusedArgs {
     int32_t debug;       // 0 in production
     int32_t debug_slot;
     int32_t img_units;   // K units an activation image has room for (>= units_total of every op that reads one)
-    int32_t pad0;
+    int32_t ngroups;     // CTA groups, each with its own copy of the op list (ops + g*nops); 0 or 1 = one list
     int64_t wait_cycles; // SM clock cycles after which a device-side wait gives up and sets QM_STATUS_TIMEOUT
     // Tensor-parallel launch (kernels *_tp): this GPU computes a row slice of every op and stores
     // it into the same place of every peer's activation arena (its own address + peer_delta[p]);
@@ -207,6 +210,13 @@ struct QmSumPartsArgs {
     int64_t part_stride, ld_in, ld_out;
     int32_t nparts, m, n;
     float inv_cols, eps;
+};
+
+// Part-major copy of a tiled Q4_K store (qm_repack_parts): ups = K units per part.
+struct QmPartsArgs {
+    const uint8_t *src;
+    uint8_t *dst;
+    int32_t tiles, units, ups, pad;
 };
 
 struct QmDequantArgs {

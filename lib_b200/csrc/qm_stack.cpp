@@ -17,6 +17,10 @@
 
 struct QmLayer {
     QmWeight *qkv, *o, *gu, *dn;
+    // part-major copies of the o / down weights for steps that run them in K parts ([part][tile][units/parts]
+    // items; same bytes in another order), made on first use and dropped when the layer is set again
+    CUdeviceptr o_parts, dn_parts;
+    int o_nparts, dn_nparts;
 };
 
 struct qm_stack {
@@ -50,6 +54,7 @@ struct qm_stack {
     int fused_dd_kernel[9];
     int fused_half0[9];         // tensor-parallel: arena half that the first copy of the op list addresses
     int fused_parts_o[9], fused_parts_dn[9];   // K parts of the o / down projections in the op list (1 = whole)
+    int fused_ngroups[9];       // CTA groups with a copy of the op list each (data-driven form with K parts)
     // tensor-parallel: one arena holds all activation buffers and the peers' arrival flags; the
     // peers map it through CUDA IPC and this GPU stores its row slices into all of them
     int tp_world, tp_rank;
@@ -265,6 +270,10 @@ extern "C" int32_t qm_stack_destroy(qm_ctx *c, qm_stack *s) {
     CtxGuard g(c);
     DRV(g.rc);
     c->drv->cuStreamSynchronize(c->stream);
+    for (QmLayer &ly : s->layer) {
+        if (ly.o_parts) c->drv->cuMemFree_v2(ly.o_parts);
+        if (ly.dn_parts) c->drv->cuMemFree_v2(ly.dn_parts);
+    }
     for (int i = 0; i < 9; i++) {
         if (s->graph[i]) c->drv->cuGraphExecDestroy(s->graph[i]);
         if (s->ops_dev[i]) c->drv->cuMemFree_v2(s->ops_dev[i]);
@@ -299,7 +308,14 @@ extern "C" int32_t qm_stack_set_layer(qm_ctx *c, qm_stack *s, int32_t layer, qm_
                                 {2 * s->ffn / W, s->hidden}, {s->hidden / W, s->ffn}};
     for (int i = 0; i < 4; i++)
         if (w[i]->rows != want[i][0] || w[i]->cols != want[i][1]) return QM_ERR_SHAPE;
-    s->layer[layer] = QmLayer{w[0], w[1], w[2], w[3]};
+    {
+        CtxGuard g(c);
+        QmLayer &old = s->layer[layer];
+        if (old.o_parts || old.dn_parts) c->drv->cuStreamSynchronize(c->stream);
+        if (old.o_parts) c->drv->cuMemFree_v2(old.o_parts);
+        if (old.dn_parts) c->drv->cuMemFree_v2(old.dn_parts);
+    }
+    s->layer[layer] = QmLayer{w[0], w[1], w[2], w[3], 0, 0, 0, 0};
     for (int i = 0; i < 9; i++) {
         CtxGuard g(c);
         if (s->graph[i]) c->drv->cuGraphExecDestroy(s->graph[i]);
@@ -399,25 +415,37 @@ static int32_t upload_ops(qm_ctx *c, qm_stack *s, int m, std::vector<QmOp> &ops)
 // each and spread over four times as many (tile, part) pieces; the consumer adds the parts up
 // while it stages them. QM_ERR_SHAPE when the step does not qualify (the caller then builds the
 // barrier form).
+static int32_t part_major_copy(qm_ctx *c, const QmWeight *w, int parts, CUdeviceptr *out, int *out_parts) {
+    if (*out && *out_parts == parts) return QM_OK;
+    if (*out) {
+        DRV(c->drv->cuStreamSynchronize(c->stream));
+        c->drv->cuMemFree_v2(*out);
+        *out = 0;
+    }
+    DRV(c->drv->cuMemAlloc_v2(out, (size_t)w->qbytes + 64));
+    QmPartsArgs a;
+    memset(&a, 0, sizeof a);
+    a.src = (const uint8_t *)(uintptr_t)w->wq;
+    a.dst = (uint8_t *)(uintptr_t)*out;
+    a.tiles = (int32_t)((w->rows + 15) / 16);
+    a.units = w->units;
+    a.ups = w->units / parts;
+    *out_parts = parts;
+    return qm_launch(c, QM_K_REPACK_PARTS, (unsigned)c->sm_count * 8, 1, 256, 0, &a, false);
+}
+
 static int32_t build_fused_dd(qm_ctx *c, qm_stack *s, int m) {
     if (m >= qm_env_int("QM_IMAGE_MIN_M", 4) || qm_env_int("QM_DD", 1) == 0) return QM_ERR_SHAPE;
     const int grid = qm_fused_grid(c);
-    // The down projection (long K: its CTAs would each stage all of x) runs in four K parts. The o
-    // projection stays whole by default: its x is short, and every part adds a vector that each CTA of
-    // the consumer polls and loads.
+    // The down projection (long K: its CTAs would each quantize all 2 x 14336 activations) runs in
+    // four K parts. The o projection stays whole by default: its x is short, and every part adds a
+    // vector that each CTA of the consumer polls and loads.
     auto parts_for = [&](const QmWeight *w, int want) {
         for (int k = QM_MAX_PARTS; k > 1; k >>= 1)
             if (k <= want && w->units % k == 0 && grid % k == 0) return k;
         return 1;
     };
-    // On one GPU every op stays whole: the kernels without K parts keep their streaming loop free of
-    // the extra state, which is worth more there than the shorter staging.
-    // With few GPUs the same holds (2 GPUs measured: 1.04 ms per step whole against 1.05 with the down
-    // projection in two parts); from four GPUs on a GPU's slice of the down projection is 64 tiles
-    // or fewer, which fills under half of the CTAs unless it is cut.
-    const bool tp_parts = s->tp_world > 1;
-    const int want_o = tp_parts ? qm_env_int("QM_PARTS_O", 1) : 1;
-    const int want_dn = tp_parts ? qm_env_int("QM_PARTS_DN", s->tp_world >= 4 ? QM_MAX_PARTS : 1) : 1;
+    const int want_o = qm_env_int("QM_PARTS_O", 1), want_dn = qm_env_int("QM_PARTS_DN", QM_MAX_PARTS);
     int max_units = 0, So = QM_MAX_PARTS, Sd = QM_MAX_PARTS;
     for (int L = 0; L < s->layers; L++) {
         const QmLayer &ly = s->layer[L];
@@ -438,47 +466,68 @@ static int32_t build_fused_dd(qm_ctx *c, qm_stack *s, int m) {
     if (p.nt == 1 && p.consumers == 16 && p.depth >= 2 && p.depth <= 4)
         kernel = (p.cpm == 4 ? QM_K_FUSED_Q4K_DD_C4D2 : QM_K_FUSED_Q4K_DD_C2D2) + (p.depth - 2);
     if (kernel < 0) return QM_ERR_SHAPE;
+    for (int L = 0; L < s->layers; L++) {
+        QmLayer &ly = s->layer[L];
+        int32_t rc = QM_OK;
+        if (So > 1) rc = part_major_copy(c, ly.o, So, &ly.o_parts, &ly.o_nparts);
+        if (!rc && Sd > 1) rc = part_major_copy(c, ly.dn, Sd, &ly.dn_parts, &ly.dn_nparts);
+        if (rc) return rc;
+    }
 
+    // One copy of the op list per CTA group; the copies differ in the ops that run in parts.
+    const int ngroups = std::max(So, Sd);
     std::vector<QmOp> ops;
     const int64_t qkv_ld = s->hidden + 2 * s->kv;
     const bool tp = s->tp_world > 1;
     const size_t R = (size_t)s->tp_rank * 4;
-    // Tensor-parallel: every matrix is sliced by rows (GPU r of g holds rows [r*N/g, (r+1)*N/g)); y points
-    // at this rank's rows of the full-width output and the results go to every GPU's arena.
-    auto add = [&](const QmWeight *w, CUdeviceptr x, CUdeviceptr x2, int64_t ldx, CUdeviceptr y, int64_t ldy, uint32_t xop,
-                   bool first, int parts, int64_t y_part_stride, CUdeviceptr ssq_out) -> QmOp & {
-        QmOp op;
-        qm_fill_op(c, p, w, x, x2, ldx, y + R * w->rows, ldy, xop, !first, 0, w->units / parts, 0, &op);
-        const int G = grid / parts;
-        op.q = op.tiles / G;
-        op.rem = op.tiles % G;
-        op.parts = parts;
-        op.y_part_stride = y_part_stride;
-        op.ssq_out = parts > 1 ? (float *)(uintptr_t)ssq_out : nullptr;
-        op.tp_shared = tp ? 1 : 0;
-        ops.push_back(op);
-        return ops.back();
-    };
-    auto consumes = [&](QmOp &op, int parts, int64_t stride, CUdeviceptr ssq, const QmWeight *producer) {
-        op.x_parts = parts;
-        op.x_part_stride = stride;
-        if (parts > 1) {
-            op.ssq_in = (const float *)(uintptr_t)ssq;
-            op.ssq_in_inv_cols = 1.f / (float)producer->cols;
-            op.ssq_in_eps = 1e-6f;
+    for (int g = 0; g < ngroups; g++) {
+        // Tensor-parallel: every matrix is sliced by rows (GPU r of g holds rows [r*N/g, (r+1)*N/g)); y
+        // points at this rank's rows of the full-width output and the results go to every GPU's arena.
+        auto add = [&](const QmWeight *w, CUdeviceptr parts_copy, CUdeviceptr x, CUdeviceptr x2, int64_t ldx, CUdeviceptr y,
+                       int64_t ldy, uint32_t xop, bool first, int parts, int64_t y_part_stride, CUdeviceptr ssq_out) -> QmOp & {
+            QmOp op;
+            const int ups = w->units / parts;
+            qm_fill_op(c, p, w, x, x2, ldx, y + R * w->rows, ldy, xop, !first, 0, ups, 0, &op);
+            if (parts > 1) {
+                const int per = ngroups / parts;          // CTA groups that share one part
+                const int part = g / per, G = grid / ngroups * per;
+                op.wq = (const uint8_t *)(uintptr_t)(parts_copy + (size_t)part * op.tiles * ups * QM_Q4K_ITEM_BYTES);
+                op.units_total = ups;                     // the part's items are contiguous in the copy
+                op.unit0 = part * ups;                    // ... and cover these K units of x
+                op.y = (float *)((uintptr_t)op.y + (size_t)part * y_part_stride * 4);
+                op.parts = parts;
+                op.part = part;
+                op.cta0 = part * G;
+                op.nctas = G;
+                op.q = op.tiles / G;
+                op.rem = op.tiles % G;
+                op.ssq_out = (float *)(uintptr_t)ssq_out;
+            }
+            op.tp_shared = tp ? 1 : 0;
+            ops.push_back(op);
+            return ops.back();
+        };
+        auto consumes = [&](QmOp &op, int parts, int64_t stride, CUdeviceptr ssq, const QmWeight *producer) {
+            op.x_parts = parts;
+            op.x_part_stride = stride;
+            if (parts > 1) {
+                op.ssq_in = (const float *)(uintptr_t)ssq;
+                op.ssq_in_inv_cols = 1.f / (float)producer->cols;
+                op.ssq_in_eps = 1e-6f;
+            }
+        };
+        for (int L = 0; L < s->layers; L++) {
+            const QmLayer &ly = s->layer[L];
+            const LayerBufs b = layer_bufs(s, L, m);
+            QmOp &qkv = add(ly.qkv, 0, L == 0 ? s->h0 : layer_bufs(s, L - 1, m).dn, 0, s->hidden, b.qkv, qkv_ld,
+                            QM_XOP_RMSNORM, L == 0, 1, 0, 0);
+            if (L > 0) consumes(qkv, Sd, b.part_stride, layer_bufs(s, L - 1, m).ssq_dn, s->layer[L - 1].dn);
+            add(ly.o, ly.o_parts, b.qkv, 0, qkv_ld, b.o, s->hidden, QM_XOP_RMSNORM, false, So, b.part_stride, b.ssq_o);
+            QmOp &gu = add(ly.gu, 0, b.o, 0, s->hidden, b.gu, 2 * s->ffn, QM_XOP_RMSNORM, false, 1, 0, 0);
+            consumes(gu, So, b.part_stride, b.ssq_o, ly.o);
+            add(ly.dn, ly.dn_parts, b.gu, b.gu + (size_t)s->ffn * 4, 2 * s->ffn, b.dn, s->hidden, QM_XOP_ADD_RMSNORM, false,
+                Sd, b.part_stride, b.ssq_dn);
         }
-    };
-    for (int L = 0; L < s->layers; L++) {
-        const QmLayer &ly = s->layer[L];
-        const LayerBufs b = layer_bufs(s, L, m);
-        QmOp &qkv = add(ly.qkv, L == 0 ? s->h0 : layer_bufs(s, L - 1, m).dn, 0, s->hidden, b.qkv, qkv_ld, QM_XOP_RMSNORM,
-                        L == 0, 1, 0, 0);
-        if (L > 0) consumes(qkv, Sd, b.part_stride, layer_bufs(s, L - 1, m).ssq_dn, s->layer[L - 1].dn);
-        add(ly.o, b.qkv, 0, qkv_ld, b.o, s->hidden, QM_XOP_RMSNORM, false, So, b.part_stride, b.ssq_o);
-        QmOp &gu = add(ly.gu, b.o, 0, s->hidden, b.gu, 2 * s->ffn, QM_XOP_RMSNORM, false, 1, 0, 0);
-        consumes(gu, So, b.part_stride, b.ssq_o, ly.o);
-        add(ly.dn, b.gu, b.gu + (size_t)s->ffn * 4, 2 * s->ffn, b.dn, s->hidden, QM_XOP_ADD_RMSNORM, false, Sd,
-            b.part_stride, b.ssq_dn);
     }
     for (const QmOp &op : ops)
         if ((int64_t)op.tiles * op.units >= (1ll << 31)) return QM_ERR_SHAPE;
@@ -489,6 +538,8 @@ static int32_t build_fused_dd(qm_ctx *c, qm_stack *s, int m) {
         c->drv->cuMemFree_v2(sync);
         return rc;
     }
+    s->fused_nops[m] = (int)(ops.size() / (size_t)ngroups / (tp ? 2 : 1));
+    s->fused_ngroups[m] = ngroups;
     s->img_dev[m] = 0;
     s->sync_dev[m] = sync;
     s->sync_bytes[m] = 256;
@@ -620,6 +671,7 @@ static int32_t build_fused(qm_ctx *c, qm_stack *s, int m) {
     s->fused_dd[m] = false;
     s->fused_dd_kernel[m] = -1;
     s->fused_parts_o[m] = s->fused_parts_dn[m] = 1;
+    s->fused_ngroups[m] = 1;
     s->fused_plan[m] = p;
     return QM_OK;
 }
@@ -659,6 +711,7 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
     a.status = (unsigned int *)(uintptr_t)c->status_dev;
     a.grid_bar = (unsigned int *)(uintptr_t)s->sync_dev[m];
     a.nops = s->fused_nops[m];
+    a.ngroups = s->fused_ngroups[m];
     a.img_units = s->img_units[m];
     a.m = m;
     a.consumers = p.consumers;
@@ -675,7 +728,7 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
     if (s->tp_world > 1) {
         if (!s->peers_open) return QM_ERR_STATE;
         const bool second = (s->act == s->act_half[0] ? 0 : 1) != s->fused_half0[m];
-        a.ops = (const QmOp *)(uintptr_t)(s->ops_dev[m] + (second ? (size_t)a.nops * sizeof(QmOp) : 0));
+        a.ops = (const QmOp *)(uintptr_t)(s->ops_dev[m] + (second ? (size_t)a.nops * a.ngroups * sizeof(QmOp) : 0));
         a.tp_world = s->tp_world;
         a.tp_rank = s->tp_rank;
         a.tp_epoch0 = s->tp_epoch;
@@ -695,8 +748,7 @@ static int32_t launch_fused(qm_ctx *c, qm_stack *s, int m) {
         if (s->fused_dd[m]) {
             a.tp_counter = 0;
             s->tp_epoch += 1;   // one barrier over the GPUs per launch
-            const bool with_parts = s->fused_parts_o[m] > 1 || s->fused_parts_dn[m] > 1;
-            int32_t rc = qm_launch_ex(c, s->fused_dd_kernel[m] + ((with_parts ? QM_K_FUSED_Q4K_DD_C4D2_TPP : QM_K_FUSED_Q4K_DD_C4D2_TP) - QM_K_FUSED_Q4K_DD_C4D2),
+            int32_t rc = qm_launch_ex(c, s->fused_dd_kernel[m] + (QM_K_FUSED_Q4K_DD_C4D2_TP - QM_K_FUSED_Q4K_DD_C4D2),
                                       (unsigned)qm_fused_grid(c), (unsigned)p.consumers * 32, (unsigned)p.smem, &a, false, true);
             return rc ? rc : sum_last_parts(c, s, m);
         }

@@ -274,6 +274,28 @@ QM_API int32_t qm_stack_set_peers(qm_ctx *ctx, qm_stack *stack, const void *hand
 QM_API int32_t qm_stack_arena(qm_ctx *ctx, qm_stack *stack, uint64_t *base, int64_t *bytes);
 QM_API int32_t qm_stack_set_peer_pointers(qm_ctx *ctx, qm_stack *stack, const uint64_t *bases);
 
+/* GGUF file -> weight store. qm_gguf_open parses header, metadata and tensor directory of a GGUF v3
+ * file by the rules of gguf.Read (gguf/gguf.go:116-250; QM_ERR_FORMAT for a malformed or
+ * unsupported file, QM_ERR_COUNT for a row that is not block aligned, QM_ERR_STATE if the file
+ * cannot be opened) and keeps what gguf.File.Tensors holds: name, TypeID, Dimensions, Offset.
+ * qm_gguf_tensor_info: info6 = {type id, ndims, dims[4]}, offs2 = {DataOffset + Offset, Bytes()}.
+ * qm_gguf_load_tensor / qm_gguf_load_rows stream rows [row_lo, row_hi) of a tensor (rows = product
+ * of Dimensions[1:], row length Dimensions[0]; row_hi = 0 means all) from the file through two
+ * pinned staging buffers into a store entry, reading the next chunk while the previous one is
+ * copied and permuted on the device; load_rows writes into an existing entry (q|k|v or gate|up
+ * stacked by rows). No GPU is needed to open and inspect a file. */
+typedef struct qm_gguf qm_gguf;
+QM_API int32_t qm_gguf_open(const char *path, qm_gguf **out);
+QM_API int32_t qm_gguf_close(qm_gguf *file);
+QM_API int32_t qm_gguf_tensor_count(qm_gguf *file);
+QM_API int32_t qm_gguf_tensor_info(qm_gguf *file, int32_t index, char *name, int32_t name_cap, int64_t *info6,
+                                   int64_t *offs2);
+QM_API int32_t qm_gguf_find(qm_gguf *file, const char *name);
+QM_API int32_t qm_gguf_load_tensor(qm_ctx *ctx, qm_gguf *file, int32_t index, int64_t row_lo, int64_t row_hi,
+                                   qm_weight *out);
+QM_API int32_t qm_gguf_load_rows(qm_ctx *ctx, qm_gguf *file, int32_t index, int64_t row_lo, int64_t row_hi,
+                                 qm_weight w, int64_t dst_row);
+
 /* Host-side residency manager for expert weight blobs, the behaviour of moe.ExpertCacheManager
  * (lm/moe/moe.go:143-287): at most max_hot experts stay in host memory, admitting one more
  * spills the least recently used one (never the one just touched) to <dir>/expert_<id>.bin, a

@@ -72,6 +72,13 @@ def _load():
         "qm_stack_set_peers": (i32, [p, p, p]),
         "qm_stack_arena": (i32, [p, p, ctypes.POINTER(u64), ctypes.POINTER(i64)]),
         "qm_stack_set_peer_pointers": (i32, [p, p, ctypes.POINTER(u64)]),
+        "qm_gguf_open": (i32, [ctypes.c_char_p, ctypes.POINTER(p)]),
+        "qm_gguf_close": (i32, [p]),
+        "qm_gguf_tensor_count": (i32, [p]),
+        "qm_gguf_tensor_info": (i32, [p, i32, ctypes.c_char_p, i32, ctypes.POINTER(i64), ctypes.POINTER(i64)]),
+        "qm_gguf_find": (i32, [p, ctypes.c_char_p]),
+        "qm_gguf_load_tensor": (i32, [p, p, i32, i64, i64, ctypes.POINTER(u64)]),
+        "qm_gguf_load_rows": (i32, [p, p, i32, i64, i64, u64, i64]),
         "qm_expert_cache_create": (i32, [ctypes.c_char_p, i32, ctypes.POINTER(p)]),
         "qm_expert_cache_register": (i32, [p, i64, p, i64]),
         "qm_expert_cache_get": (i32, [p, i64, p, i64, ctypes.POINTER(i64)]),
@@ -102,6 +109,44 @@ def _u8(data):
     if isinstance(data, np.ndarray):
         return np.ascontiguousarray(data.view(np.uint8).reshape(-1))
     return np.frombuffer(bytes(data), dtype=np.uint8)
+
+
+class GgufFile:
+    """qm_gguf: the tensor directory of a GGUF file, and its tensors streamed into the store."""
+
+    def __init__(self, path):
+        h = ctypes.c_void_p()
+        _check(lib.qm_gguf_open(os.fsencode(path), ctypes.byref(h)), "gguf_open")
+        self._h = h
+
+    def tensor_count(self):
+        return int(lib.qm_gguf_tensor_count(self._h))
+
+    def tensor_info(self, index):
+        """(name, type id, dimensions, file offset of the bytes, byte count)."""
+        name = ctypes.create_string_buffer(80)
+        info, offs = (ctypes.c_int64 * 6)(), (ctypes.c_int64 * 2)()
+        _check(lib.qm_gguf_tensor_info(self._h, index, name, 80, info, offs), "gguf_tensor_info")
+        return name.value.decode(), int(info[0]), [int(v) for v in info[2:2 + info[1]]], int(offs[0]), int(offs[1])
+
+    def find(self, name):
+        rc = lib.qm_gguf_find(self._h, name.encode())
+        if rc < 0:
+            raise QmError(rc, "gguf_find")
+        return rc
+
+    def load_tensor(self, ctx, index, row_lo=0, row_hi=0):
+        h = ctypes.c_uint64(0)
+        _check(lib.qm_gguf_load_tensor(ctx._h, self._h, index, row_lo, row_hi, ctypes.byref(h)), "gguf_load_tensor")
+        return Weight(ctx, h.value)
+
+    def load_rows(self, ctx, index, row_lo, row_hi, weight, dst_row):
+        _check(lib.qm_gguf_load_rows(ctx._h, self._h, index, row_lo, row_hi, weight.handle, dst_row), "gguf_load_rows")
+
+    def close(self):
+        if self._h:
+            lib.qm_gguf_close(self._h)
+            self._h = None
 
 
 class Weight:

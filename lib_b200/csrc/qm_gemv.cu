@@ -15,13 +15,10 @@
 //     lanes then read 16-byte pieces of their rows (4 lanes per row);
 //   * nibbles/bytes become exact small integers in fp16 with one LOP3/PRMT and
 //     one half2 FMA per pair (magic-number trick: 0x6400|q == 1024+q);
-//     for Q4_K the 6-bit sub-block scale is folded in exactly (sc*q <= 945);
 //   * activations are staged once per CTA in shared memory as fp16 hi+lo
 //     pairs (x = hi + lo to ~22 bits) in mma-fragment order;
 //   * mma.sync.m16n8k16 (A = weights, B = activations) accumulates in fp32;
-//     block/super-block scales are applied in fp32 on the accumulators;
-//   * the Q4_K minimum term sum_j m_j * sum(x in sub-block j) is one extra mma
-//     per super-block against pre-reduced activation sums.
+//     block scales are applied in fp32 on the accumulators.
 // The grid is one persistent CTA per SM. The (tile, K unit) item space is cut
 // into equal contiguous shares, one per warp of the whole grid, so there is no
 // tail wave and the activations are staged once per CTA. A tile whose K range
@@ -33,10 +30,12 @@
 #include <stdint.h>
 
 #include "qm_kernel_args.h"
+#include "qm_pipe.cuh"
 
 #define QM_FMT_Q4_0 2
 #define QM_FMT_Q8_0 8
-#define QM_FMT_Q4_K 12
+
+using namespace qm;
 
 namespace {
 
@@ -58,11 +57,6 @@ __device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
 __device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
     return d;
 }
 __device__ __forceinline__ float h2f_lo(uint32_t h2) {
@@ -87,15 +81,9 @@ constexpr uint32_t kH1032 = 0x64086408u;   // half2(1032)
 constexpr uint32_t kH1152 = 0x64806480u;   // half2(1152)
 constexpr uint32_t kHInv16 = 0x2C002C00u;  // half2(1/16)
 constexpr uint32_t kHNeg72 = 0xD480D480u;  // half2(-72)
-constexpr uint32_t kHNeg1024 = 0xE400E400u;
-constexpr uint32_t kHNeg64 = 0xD400D400u;
 
 // ---- per-format raw data of one K unit (256 columns) for a lane's two rows ----
 template <int FMT> struct UnitData;
-template <> struct UnitData<QM_FMT_Q4_K> {
-    uint4 hdr[2];   // d | dmin | 12 scale bytes
-    uint4 q[2][2];  // bytes 32t..32t+31 of the 128 quant bytes
-};
 template <> struct UnitData<QM_FMT_Q4_0> {
     uint4 d[2];     // 8 fp16 block scales
     uint4 q[2][2];  // two 4-block groups, word i = word t of block 4G+i
@@ -105,45 +93,8 @@ template <> struct UnitData<QM_FMT_Q8_0> {
     uint4 q[2][4];  // four 2-block groups, word 2*bi+hf = word 4*hf+t of block 2G+bi
 };
 
-// ---- bulk-copy pipeline primitives -------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(1000000u)  // the hardware may park the warp for up to ~1 ms per try
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after about two seconds of SM clock and reports it.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > 4000000000ll) return false;
-    }
-    return true;
-}
-
 // bytes of one row of one K unit in a stage, and the row strides of a stage
 template <int FMT> struct StageGeom;
-template <> struct StageGeom<QM_FMT_Q4_K> {
-    static constexpr int kQ = 144, kD = 0;
-};
 template <> struct StageGeom<QM_FMT_Q4_0> {
     static constexpr int kQ = 128, kD = 16;
 };
@@ -158,19 +109,13 @@ __device__ __forceinline__ void read_unit(UnitData<FMT> &ud, const uint8_t *stag
 #pragma unroll
     for (int rh = 0; rh < 2; rh++) {
         const uint8_t *row = stage + (g + 8 * rh) * rsq + un * StageGeom<FMT>::kQ;
-        if constexpr (FMT == QM_FMT_Q4_K) {
-            ud.hdr[rh] = *reinterpret_cast<const uint4 *>(row);
-            ud.q[rh][0] = *reinterpret_cast<const uint4 *>(row + 16 + 32 * t);
-            ud.q[rh][1] = *reinterpret_cast<const uint4 *>(row + 32 + 32 * t);
+        ud.d[rh] = *reinterpret_cast<const uint4 *>(stage + 16 * rsq + (g + 8 * rh) * rsd + un * 16);
+        if constexpr (FMT == QM_FMT_Q4_0) {
+            ud.q[rh][0] = *reinterpret_cast<const uint4 *>(row + 16 * t);
+            ud.q[rh][1] = *reinterpret_cast<const uint4 *>(row + 64 + 16 * t);
         } else {
-            ud.d[rh] = *reinterpret_cast<const uint4 *>(stage + 16 * rsq + (g + 8 * rh) * rsd + un * 16);
-            if constexpr (FMT == QM_FMT_Q4_0) {
-                ud.q[rh][0] = *reinterpret_cast<const uint4 *>(row + 16 * t);
-                ud.q[rh][1] = *reinterpret_cast<const uint4 *>(row + 64 + 16 * t);
-            } else {
 #pragma unroll
-                for (int G = 0; G < 4; G++) ud.q[rh][G] = *reinterpret_cast<const uint4 *>(row + 64 * G + 16 * t);
-            }
+            for (int G = 0; G < 4; G++) ud.q[rh][G] = *reinterpret_cast<const uint4 *>(row + 64 * G + 16 * t);
         }
     }
 }
@@ -193,119 +138,53 @@ __device__ __forceinline__ void compute_unit(const UnitData<FMT> &ud, float (&ac
         if (bact) b = *reinterpret_cast<const uint4 *>(plane + ((ul * 8 + jp) * 4 + t) * 16);
         return b;
     };
-    if constexpr (FMT == QM_FMT_Q4_K) {
-        uint32_t mulLo[2], addLo[2], mulHi[2], addHi[2], mAB[2];
-        float d[2], dmin[2];
+    // Q4_0 / Q8_0: every pair of mmas covers one 32-element block of each
+    // row, so the block scale is applied in fp32 on the pair's result.
 #pragma unroll
-        for (int rh = 0; rh < 2; rh++) {
-            d[rh] = h2f_lo(ud.hdr[rh].x);
-            dmin[rh] = h2f_hi(ud.hdr[rh].x);
-            const uint32_t S0 = ud.hdr[rh].y, S1 = ud.hdr[rh].z, S2 = ud.hdr[rh].w;
-            const uint32_t scv = (t < 2) ? (S0 & 0x3F3F3F3Fu)
-                                         : ((S2 & 0x0F0F0F0Fu) | ((S0 >> 2) & 0x30303030u));
-            const uint32_t mv = (t < 2) ? (S1 & 0x3F3F3F3Fu)
-                                        : (((S2 >> 4) & 0x0F0F0F0Fu) | ((S1 >> 2) & 0x30303030u));
-            const uint32_t scp = scv >> ((t & 1) * 16), mp = mv >> ((t & 1) * 16);
-            const uint32_t scA = hsub2(prmt(scp, 0x64646464u, 0x4040u), kMagic);  // (sc_2t, sc_2t)
-            const uint32_t scB = hsub2(prmt(scp, 0x64646464u, 0x4141u), kMagic);  // (sc_2t+1, ..)
-            mulLo[rh] = scA;
-            addLo[rh] = hmul2(scA, kHNeg1024);
-            mulHi[rh] = hmul2(scB, kHInv16);
-            addHi[rh] = hmul2(scB, kHNeg64);
-            mAB[rh] = hsub2(prmt(mp, 0x64646464u, 0x4140u), kMagic);  // (m_2t, m_2t+1)
+    for (int blk = 0; blk < 8; blk++) {
+        uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
+        if constexpr (FMT == QM_FMT_Q4_0) {
+            const uint32_t wA = u4w(ud.q[0][blk >> 2], blk & 3), wB = u4w(ud.q[1][blk >> 2], blk & 3);
+            const uint32_t wA8 = wA >> 8, wB8 = wB >> 8;
+            a0 = hsub2(lop_and_or(wA, 0x000F000Fu, kMagic), kH1032);
+            a1 = hsub2(lop_and_or(wB, 0x000F000Fu, kMagic), kH1032);
+            a2 = hsub2(lop_and_or(wA8, 0x000F000Fu, kMagic), kH1032);
+            a3 = hsub2(lop_and_or(wB8, 0x000F000Fu, kMagic), kH1032);
+            c0 = hfma2(lop_and_or(wA, 0x00F000F0u, kMagic), kHInv16, kHNeg72);
+            c1 = hfma2(lop_and_or(wB, 0x00F000F0u, kMagic), kHInv16, kHNeg72);
+            c2 = hfma2(lop_and_or(wA8, 0x00F000F0u, kMagic), kHInv16, kHNeg72);
+            c3 = hfma2(lop_and_or(wB8, 0x00F000F0u, kMagic), kHInv16, kHNeg72);
+        } else {
+            const int G = blk >> 1, bi = blk & 1;
+            const uint32_t wA0 = u4w(ud.q[0][G], 2 * bi) ^ 0x80808080u;
+            const uint32_t wB0 = u4w(ud.q[1][G], 2 * bi) ^ 0x80808080u;
+            const uint32_t wA1 = u4w(ud.q[0][G], 2 * bi + 1) ^ 0x80808080u;
+            const uint32_t wB1 = u4w(ud.q[1][G], 2 * bi + 1) ^ 0x80808080u;
+            a0 = hsub2(prmt(wA0, 0x64646464u, 0x4240u), kH1152);
+            a1 = hsub2(prmt(wB0, 0x64646464u, 0x4240u), kH1152);
+            a2 = hsub2(prmt(wA0, 0x64646464u, 0x4341u), kH1152);
+            a3 = hsub2(prmt(wB0, 0x64646464u, 0x4341u), kH1152);
+            c0 = hsub2(prmt(wA1, 0x64646464u, 0x4240u), kH1152);
+            c1 = hsub2(prmt(wB1, 0x64646464u, 0x4240u), kH1152);
+            c2 = hsub2(prmt(wA1, 0x64646464u, 0x4341u), kH1152);
+            c3 = hsub2(prmt(wB1, 0x64646464u, 0x4341u), kH1152);
         }
-        float accQ[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const uint32_t wA = u4w(ud.q[0][h], k), wB = u4w(ud.q[1][h], k);
-                const uint32_t wA8 = wA >> 8, wB8 = wB >> 8;
-                const int jp = h * 4 + k;
-                const uint4 b = load_b(xs_plane, jp);
-                uint32_t a0 = hfma2(lop_and_or(wA, 0x000F000Fu, kMagic), mulLo[0], addLo[0]);
-                uint32_t a1 = hfma2(lop_and_or(wB, 0x000F000Fu, kMagic), mulLo[1], addLo[1]);
-                uint32_t a2 = hfma2(lop_and_or(wA8, 0x000F000Fu, kMagic), mulLo[0], addLo[0]);
-                uint32_t a3 = hfma2(lop_and_or(wB8, 0x000F000Fu, kMagic), mulLo[1], addLo[1]);
-                mma16816(accQ, a0, a1, a2, a3, b.x, b.y, accQ);
-                uint32_t c0 = hfma2(lop_and_or(wA, 0x00F000F0u, kMagic), mulHi[0], addHi[0]);
-                uint32_t c1 = hfma2(lop_and_or(wB, 0x00F000F0u, kMagic), mulHi[1], addHi[1]);
-                uint32_t c2 = hfma2(lop_and_or(wA8, 0x00F000F0u, kMagic), mulHi[0], addHi[0]);
-                uint32_t c3 = hfma2(lop_and_or(wB8, 0x00F000F0u, kMagic), mulHi[1], addHi[1]);
-                mma16816(accQ, c0, c1, c2, c3, b.z, b.w, accQ);
-                if constexpr (MODE == 1) {
-                    const uint4 bl = load_b(xs_plane_lo, jp);
-                    mma16816(accQ, a0, a1, a2, a3, bl.x, bl.y, accQ);
-                    mma16816(accQ, c0, c1, c2, c3, bl.z, bl.w, accQ);
-                }
-            }
+        const uint4 b = load_b(xs_plane, blk);
+        float tmp[4];
+        mma16816(tmp, a0, a1, a2, a3, b.x, b.y, zero4);
+        mma16816(tmp, c0, c1, c2, c3, b.z, b.w, tmp);
+        if constexpr (MODE == 1) {
+            const uint4 bl = load_b(xs_plane_lo, blk);
+            mma16816(tmp, a0, a1, a2, a3, bl.x, bl.y, tmp);
+            mma16816(tmp, c0, c1, c2, c3, bl.z, bl.w, tmp);
         }
-        float accM[4];
-        {
-            const uint32_t bm = bact ? xsum_hi[t] : 0u;
-            mma16816(accM, mAB[0], mAB[1], 0u, 0u, bm, 0u, zero4);
-            if constexpr (MODE == 1) {
-                const uint32_t bml = bact ? xsum_lo[t] : 0u;
-                mma16816(accM, mAB[0], mAB[1], 0u, 0u, bml, 0u, accM);
-            }
-        }
-        acc[0] = fmaf(d[0], accQ[0], acc[0]);
-        acc[1] = fmaf(d[0], accQ[1], acc[1]);
-        acc[2] = fmaf(d[1], accQ[2], acc[2]);
-        acc[3] = fmaf(d[1], accQ[3], acc[3]);
-        acc[0] = fmaf(-dmin[0], accM[0], acc[0]);
-        acc[1] = fmaf(-dmin[0], accM[1], acc[1]);
-        acc[2] = fmaf(-dmin[1], accM[2], acc[2]);
-        acc[3] = fmaf(-dmin[1], accM[3], acc[3]);
-    } else {
-        // Q4_0 / Q8_0: every pair of mmas covers one 32-element block of each
-        // row, so the block scale is applied in fp32 on the pair's result.
-#pragma unroll
-        for (int blk = 0; blk < 8; blk++) {
-            uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
-            if constexpr (FMT == QM_FMT_Q4_0) {
-                const uint32_t wA = u4w(ud.q[0][blk >> 2], blk & 3), wB = u4w(ud.q[1][blk >> 2], blk & 3);
-                const uint32_t wA8 = wA >> 8, wB8 = wB >> 8;
-                a0 = hsub2(lop_and_or(wA, 0x000F000Fu, kMagic), kH1032);
-                a1 = hsub2(lop_and_or(wB, 0x000F000Fu, kMagic), kH1032);
-                a2 = hsub2(lop_and_or(wA8, 0x000F000Fu, kMagic), kH1032);
-                a3 = hsub2(lop_and_or(wB8, 0x000F000Fu, kMagic), kH1032);
-                c0 = hfma2(lop_and_or(wA, 0x00F000F0u, kMagic), kHInv16, kHNeg72);
-                c1 = hfma2(lop_and_or(wB, 0x00F000F0u, kMagic), kHInv16, kHNeg72);
-                c2 = hfma2(lop_and_or(wA8, 0x00F000F0u, kMagic), kHInv16, kHNeg72);
-                c3 = hfma2(lop_and_or(wB8, 0x00F000F0u, kMagic), kHInv16, kHNeg72);
-            } else {
-                const int G = blk >> 1, bi = blk & 1;
-                const uint32_t wA0 = u4w(ud.q[0][G], 2 * bi) ^ 0x80808080u;
-                const uint32_t wB0 = u4w(ud.q[1][G], 2 * bi) ^ 0x80808080u;
-                const uint32_t wA1 = u4w(ud.q[0][G], 2 * bi + 1) ^ 0x80808080u;
-                const uint32_t wB1 = u4w(ud.q[1][G], 2 * bi + 1) ^ 0x80808080u;
-                a0 = hsub2(prmt(wA0, 0x64646464u, 0x4240u), kH1152);
-                a1 = hsub2(prmt(wB0, 0x64646464u, 0x4240u), kH1152);
-                a2 = hsub2(prmt(wA0, 0x64646464u, 0x4341u), kH1152);
-                a3 = hsub2(prmt(wB0, 0x64646464u, 0x4341u), kH1152);
-                c0 = hsub2(prmt(wA1, 0x64646464u, 0x4240u), kH1152);
-                c1 = hsub2(prmt(wB1, 0x64646464u, 0x4240u), kH1152);
-                c2 = hsub2(prmt(wA1, 0x64646464u, 0x4341u), kH1152);
-                c3 = hsub2(prmt(wB1, 0x64646464u, 0x4341u), kH1152);
-            }
-            const uint4 b = load_b(xs_plane, blk);
-            float tmp[4];
-            mma16816(tmp, a0, a1, a2, a3, b.x, b.y, zero4);
-            mma16816(tmp, c0, c1, c2, c3, b.z, b.w, tmp);
-            if constexpr (MODE == 1) {
-                const uint4 bl = load_b(xs_plane_lo, blk);
-                mma16816(tmp, a0, a1, a2, a3, bl.x, bl.y, tmp);
-                mma16816(tmp, c0, c1, c2, c3, bl.z, bl.w, tmp);
-            }
-            const uint32_t dwA = u4w(ud.d[0], blk >> 1), dwB = u4w(ud.d[1], blk >> 1);
-            const float dA = (blk & 1) ? h2f_hi(dwA) : h2f_lo(dwA);
-            const float dB = (blk & 1) ? h2f_hi(dwB) : h2f_lo(dwB);
-            acc[0] = fmaf(dA, tmp[0], acc[0]);
-            acc[1] = fmaf(dA, tmp[1], acc[1]);
-            acc[2] = fmaf(dB, tmp[2], acc[2]);
-            acc[3] = fmaf(dB, tmp[3], acc[3]);
-        }
+        const uint32_t dwA = u4w(ud.d[0], blk >> 1), dwB = u4w(ud.d[1], blk >> 1);
+        const float dA = (blk & 1) ? h2f_hi(dwA) : h2f_lo(dwA);
+        const float dB = (blk & 1) ? h2f_hi(dwB) : h2f_lo(dwB);
+        acc[0] = fmaf(dA, tmp[0], acc[0]);
+        acc[1] = fmaf(dA, tmp[1], acc[1]);
+        acc[2] = fmaf(dB, tmp[2], acc[2]);
+        acc[3] = fmaf(dB, tmp[3], acc[3]);
     }
 }
 
@@ -442,32 +321,12 @@ __device__ __forceinline__ void gemv_body(const QmGemvArgs &a) {
             const uint32_t hA = pack_h2(v4.x, v4.z), hB = pack_h2(v4.y, v4.w);
             const uint32_t lA = pack_h2(v4.x - h2f_lo(hA), v4.z - h2f_hi(hA));
             const uint32_t lB = pack_h2(v4.y - h2f_lo(hB), v4.w - h2f_hi(hB));
-            int jp, tt, hs;
-            if constexpr (FMT == QM_FMT_Q4_K) {
-                // column bits inside the unit: t(2) | nibble(1) | h(1) | k(2) | e(2)
-                tt = cg >> 4; hs = (cg >> 3) & 1; jp = (cg & 7);
-            } else {
-                // column bits: block(3) | half(1) | t(2) | e(2)
-                tt = cg & 3; hs = (cg >> 2) & 1; jp = cg >> 3;
-            }
+            // column bits: block(3) | half(1) | t(2) | e(2)
+            const int tt = cg & 3, hs = (cg >> 2) & 1, jp = cg >> 3;
             const int off = ((ul * 8 + jp) * 4 + tt) * 16 + hs * 8;
             const int phi = MODE == 0 ? 2 * j : j, plo = MODE == 0 ? 2 * j + 1 : a.m + j;
             *reinterpret_cast<uint2 *>(xs + (size_t)phi * plane_stride + off) = make_uint2(hA, hB);
             *reinterpret_cast<uint2 *>(xs + (size_t)plo * plane_stride + off) = make_uint2(lA, lB);
-            if constexpr (FMT == QM_FMT_Q4_K) {
-                // sum of the 32 activations under each sub-block scale
-                float s = (v4.x + v4.y) + (v4.z + v4.w);
-                s += __shfl_xor_sync(0xffffffffu, s, 1);
-                s += __shfl_xor_sync(0xffffffffu, s, 2);
-                s += __shfl_xor_sync(0xffffffffu, s, 4);
-                if ((cg & 7) == 0) {
-                    const __half sh = __float2half_rn(s);
-                    const __half sl = __float2half_rn(s - __half2float(sh));
-                    __half *xh = reinterpret_cast<__half *>(xsum);
-                    xh[((size_t)ul * NPL + phi) * 8 + (cg >> 3)] = sh;
-                    xh[((size_t)ul * NPL + plo) * 8 + (cg >> 3)] = sl;
-                }
-            }
         }
     }
     __syncthreads();

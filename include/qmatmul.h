@@ -52,6 +52,8 @@ extern "C" {
 #define QM_ERR_NOMEM (-9)    /* host allocation failed                                              */
 #define QM_ERR_STATE (-10)   /* call not valid in the object's current state                        */
 #define QM_ERR_LIMIT (-11)   /* size beyond a documented fixed maximum                              */
+#define QM_ERR_DOMAIN (-12)  /* Q8_1 producer: nonfinite input/weight/value or zero denominator
+                                (the data refusals of cudaquant.RMSNormQ8_1, quant.go:56-68,76-90)  */
 
 /* Input transforms applied to the activation vector while it is staged
  * (qm_matvec flags, bits 0..3). */
@@ -61,6 +63,7 @@ extern "C" {
 #define QM_XOP_ADD_RMSNORM 2u /* rmsnorm(x + x2)                                               */
 #define QM_XOP_SWIGLU 3u      /* silu(x) * x2 (nvidia/x/egraph/codegen.go:328-374)             */
 #define QM_FLAG_PDL 0x100u    /* launch with programmatic stream serialization                 */
+#define QM_FLAG_X_Q8_1 0x200u /* qm_matvec_selected: x holds Q8_1 blocks, not float32          */
 
 typedef struct qm_ctx qm_ctx;
 typedef uint64_t qm_weight; /* opaque handle of one device-resident weight matrix */
@@ -137,6 +140,47 @@ QM_API int32_t qm_matvec(qm_ctx *ctx, qm_weight w, uint64_t x_dev, uint64_t x2_d
  * stream synchronized before the call returns. */
 QM_API int32_t qm_matvec_host(qm_ctx *ctx, qm_weight w, const float *x_host, int32_t m, int64_t ldx,
                        float *y_host, int64_t ldy, uint32_t flags);
+
+/* ---- Q8_1 activation ABI ----------------------------------------------------------------------
+ * An activation vector as blocks of 36 bytes per 32 elements: fp16 d, fp16 sum field, 32 signed
+ * quants; element i = d * q[i] (cudaquant.BlockQ8_1, nvidia/x/cudaquant/quant.go:35-40;
+ * block_q8_1 and q8_1_at of nvidia/x/egraph/codegen.go:114-128). Block pointers must be 4-byte
+ * aligned. All calls are asynchronous on the context's stream unless they take host buffers.
+ *
+ * qm_rmsnorm_q8_1: row r of x (rows ldx floats apart) -> blocks [r][cols/32] at out_dev, bytes as
+ * cudaquant.RMSNormQ8_1 produces them (quant.go:46-118; weight_dev = 0: unweighted). Replaces the
+ * one-thread-per-row kernel rms_quant_q8_1 (quant.go:129-155). What the reference refuses by
+ * looking at the data (nonfinite input or weight, zero denominator, nonfinite normalised value)
+ * sets a status bit: qm_last_status then returns QM_ERR_DOMAIN.
+ * qm_rmsnorm_q8_1_host: the reference's signature over host slices (lengths in elements), its
+ * refusals in its order: dimensions/epsilon -> QM_ERR_SHAPE, length mismatches -> QM_ERR_BUFFER,
+ * data refusals -> QM_ERR_DOMAIN with out_blocks left untouched. */
+QM_API int32_t qm_rmsnorm_q8_1(qm_ctx *ctx, uint64_t x_dev, int64_t ldx, uint64_t weight_dev, int64_t rows,
+                               int64_t cols, float eps, uint64_t out_dev);
+QM_API int32_t qm_rmsnorm_q8_1_host(qm_ctx *ctx, const float *input, int64_t n_input, const float *weight,
+                                    int64_t n_weight, int64_t rows, int64_t cols, float eps, int32_t weighted,
+                                    void *out_blocks);
+/* fused_swiglu_q8_1 (nvidia/x/egraph/codegen.go:513-552): `slots` vectors of `width` gate and up
+ * values laid end to end, v = silu(min(gate, 10)) * clamp(up, -10, 10) * weights[slot], into
+ * ceil(width*slots/32) blocks: d = fp16(max|v|/127), sum field = fp16(sum v), q = round(v/d). */
+QM_API int32_t qm_swiglu_q8_1(qm_ctx *ctx, uint64_t gate_dev, uint64_t up_dev, uint64_t weights_dev, int32_t width,
+                              int32_t slots, uint64_t out_dev);
+/* out[j][i] = d * q of row j's blocks (rows ldx_blocks blocks apart), float32, exact. */
+QM_API int32_t qm_q8_1_dequantize(qm_ctx *ctx, uint64_t xq_dev, int32_t m, int64_t ldx_blocks, int64_t cols,
+                                  uint64_t out_dev, int64_t ld_out);
+/* qm_matvec with Q8_1 activations (the *_matvec_q8_1 kernels, codegen.go:443-482 with ACT_LOAD =
+ * q8_1_at, :674-809): y[j][r] = sum_c (d*q)[j][c] * W[r][c]. flags: QM_FLAG_PDL only. */
+QM_API int32_t qm_matvec_q8_1(qm_ctx *ctx, qm_weight w, uint64_t xq_dev, int32_t m, int64_t ldx_blocks,
+                              uint64_t y_dev, int64_t ldy, uint32_t flags);
+/* Matvec over selected experts for decode-time MoE (q2_k_selected_matvec_q8_1, codegen.go:554-583;
+ * iq2_xxs_selected_matvec_q8_1, :585-616): `w` holds `experts` equally sized matrices stacked by
+ * rows (a GGUF 3-D expert tensor as it lies in the file), ids_dev[slot] (int32) names the expert of
+ * each of `slots` slots, y_dev = float32 [slot][rows of one expert]. x is one vector for all slots
+ * (x_slot_stride = 0, as in the reference) or one per slot, x_slot_stride floats (blocks) apart;
+ * float32, or Q8_1 blocks with QM_FLAG_X_Q8_1. An id outside [0, experts) fills that slot's
+ * outputs with the NaN 0x7fffffff. Formats: Q2_K, IQ2_XXS. */
+QM_API int32_t qm_matvec_selected(qm_ctx *ctx, qm_weight w, int32_t experts, uint64_t ids_dev, int32_t slots,
+                                  uint64_t x_dev, int64_t x_slot_stride, uint64_t y_dev, uint32_t flags);
 
 /* Batched / prefill product over a stored Q4_K matrix on the tcgen05 tensor cores:
  * c[j][r] = sum_k a[j][k] * W[r][k] for j < m, a bf16 [m][lda] (16-byte aligned, lda a multiple

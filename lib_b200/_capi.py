@@ -12,6 +12,7 @@ _HEADER = os.path.join(_HERE, "..", "include", "qmatmul.h")
 Q4_0, Q8_0, Q2_K, Q4_K, IQ2_XXS = 2, 8, 10, 12, 16
 XOP_NONE, XOP_RMSNORM, XOP_ADD_RMSNORM, XOP_SWIGLU = 0, 1, 2, 3
 FLAG_PDL = 0x100
+FLAG_X_Q8_1 = 0x200
 
 
 class QmError(RuntimeError):
@@ -58,6 +59,12 @@ def _load():
         "qm_moe_experts": (i32, [p, p, p, i32, u64, p, u64]),
         "qm_moe_combine": (i32, [p, u64, u64, u64, i32, i32, i32, u64, i64]),
         "qm_matvec_noalloc": (i32, [u64, u64, i32, i64, u64, i64, u64]),
+        "qm_rmsnorm_q8_1": (i32, [p, u64, i64, u64, i64, i64, ctypes.c_float, u64]),
+        "qm_rmsnorm_q8_1_host": (i32, [p, p, i64, p, i64, i64, i64, ctypes.c_float, i32, p]),
+        "qm_swiglu_q8_1": (i32, [p, u64, u64, u64, i32, i32, u64]),
+        "qm_q8_1_dequantize": (i32, [p, u64, i32, i64, i64, u64, i64]),
+        "qm_matvec_q8_1": (i32, [p, u64, u64, i32, i64, u64, i64, u32]),
+        "qm_matvec_selected": (i32, [p, u64, i32, u64, i32, u64, i64, u64, u32]),
         "qm_noalloc_status": (i32, [ctypes.POINTER(u32)]),
         "qm_stack_create": (i32, [p, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_stack_destroy": (i32, [p, p]),
@@ -288,6 +295,35 @@ class Context:
         s = ctypes.c_uint32(0)
         rc = lib.qm_noalloc_status(ctypes.byref(s))
         return rc, s.value
+
+    # ---- Q8_1 activation ABI -----------------------------------------------------------------
+    def rmsnorm_q8_1(self, x_dev, ldx, weight_dev, rows, cols, eps, out_dev):
+        _check(lib.qm_rmsnorm_q8_1(self._h, x_dev, ldx, weight_dev, rows, cols, eps, out_dev), "rmsnorm_q8_1")
+
+    def RMSNormQ8_1(self, input, weight, rows, cols, epsilon, weighted):
+        """cudaquant.RMSNormQ8_1 (nvidia/x/cudaquant/quant.go:46) on the GPU over host arrays -> block bytes;
+        raises QmError where the reference returns an error."""
+        x = np.ascontiguousarray(input, dtype=np.float32).reshape(-1)
+        w = None if weight is None else np.ascontiguousarray(weight, dtype=np.float32).reshape(-1)
+        ok = rows > 0 and cols > 0 and int(rows) * int(cols) == x.size
+        out = np.zeros((x.size // 32 if ok else 0) * 36 + 4, dtype=np.uint8)
+        _check(lib.qm_rmsnorm_q8_1_host(self._h, x.ctypes.data, x.size, None if w is None else w.ctypes.data,
+                                        0 if w is None else w.size, int(rows), int(cols), float(epsilon),
+                                        1 if weighted else 0, out.ctypes.data), "RMSNormQ8_1")
+        return out[:-4].tobytes()
+
+    def swiglu_q8_1(self, gate_dev, up_dev, weights_dev, width, slots, out_dev):
+        _check(lib.qm_swiglu_q8_1(self._h, gate_dev, up_dev, weights_dev, width, slots, out_dev), "swiglu_q8_1")
+
+    def q8_1_dequantize(self, xq_dev, m, ldx_blocks, cols, out_dev, ld_out):
+        _check(lib.qm_q8_1_dequantize(self._h, xq_dev, m, ldx_blocks, cols, out_dev, ld_out), "q8_1_dequantize")
+
+    def matvec_q8_1(self, w, xq_dev, m, ldx_blocks, y_dev, ldy, flags=0):
+        _check(lib.qm_matvec_q8_1(self._h, w.handle, xq_dev, m, ldx_blocks, y_dev, ldy, flags), "matvec_q8_1")
+
+    def matvec_selected(self, w, experts, ids_dev, slots, x_dev, x_slot_stride, y_dev, flags=0):
+        _check(lib.qm_matvec_selected(self._h, w.handle, experts, ids_dev, slots, x_dev, x_slot_stride, y_dev, flags),
+               "matvec_selected")
 
     def matvec_host(self, w, x, flags=0, out=None):
         x = np.ascontiguousarray(x, dtype=np.float32)

@@ -19,8 +19,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libqmatmul.so")
-KERNEL_SOURCES = ["qm_gemv.cu", "qm_dequant.cu", "qm_gemv_q4k.cu", "qm_gemm_q4k.cu", "qm_moe.cu", "qm_gemv_kq.cu"]
-HOST_SOURCES = ["qm_host.cpp", "qm_stack.cpp", "qm_moe.cpp", "qm_expert_cache.cpp", "qm_gguf.cpp"]
+KERNEL_SOURCES = ["qm_gemv.cu", "qm_dequant.cu", "qm_gemv_q4k.cu", "qm_gemm_q4k.cu", "qm_moe.cu", "qm_gemv_kq.cu", "qm_q8_1.cu"]
+HOST_SOURCES = ["qm_host.cpp", "qm_stack.cpp", "qm_moe.cpp", "qm_expert_cache.cpp", "qm_gguf.cpp", "qm_q8_1.cpp"]
 RUNTIME_SOURCES = ["qm_noalloc.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -46,7 +46,7 @@ def _run(cmd):
 def _describe(src, cubin, ptxas_log):
     """Kernel table for Go callers that load the cubin through nvidia/driver."""
     text = open(src).read()
-    names = re.findall(r'QM_(?:GEMV|DD)_KERNEL\((\w+),', text) + re.findall(
+    names = re.findall(r'QM_(?:GEMV|DD|KQ)_KERNEL\((\w+),', text) + re.findall(
         r'extern "C" __global__ void\s+(?:__launch_bounds__\([^)]*\)\s*)?(\w+)\(', text)
     res = {}
     cur = None

@@ -57,6 +57,7 @@ QM_INCBIN(qm_cubin_q4k, QM_STR(QM_CUBIN_DIR) "/qm_gemv_q4k.sm_100a.cubin")
 QM_INCBIN(qm_cubin_gemm, QM_STR(QM_CUBIN_DIR) "/qm_gemm_q4k.sm_100a.cubin")
 QM_INCBIN(qm_cubin_moe, QM_STR(QM_CUBIN_DIR) "/qm_moe.sm_100a.cubin")
 QM_INCBIN(qm_cubin_kq, QM_STR(QM_CUBIN_DIR) "/qm_gemv_kq.sm_100a.cubin")
+QM_INCBIN(qm_cubin_q81, QM_STR(QM_CUBIN_DIR) "/qm_q8_1.sm_100a.cubin")
 
 struct KernelImage {
     const unsigned char *begin;
@@ -69,6 +70,7 @@ static const KernelImage kImages[QM_MOD_COUNT] = {
     {qm_cubin_gemm, qm_cubin_gemm_end},
     {qm_cubin_moe, qm_cubin_moe_end},
     {qm_cubin_kq, qm_cubin_kq_end},
+    {qm_cubin_q81, qm_cubin_q81_end},
 };
 struct KernelName {
     int module;
@@ -96,6 +98,10 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_KQ, "qm_gemv_q2k_m1"},     {QM_MOD_KQ, "qm_gemv_q2k_m2"},     {QM_MOD_KQ, "qm_gemv_q2k_m4"},
     {QM_MOD_KQ, "qm_gemv_q2k_m8"},     {QM_MOD_KQ, "qm_gemv_iq2xxs_m1"},  {QM_MOD_KQ, "qm_gemv_iq2xxs_m2"},
     {QM_MOD_KQ, "qm_gemv_iq2xxs_m4"},  {QM_MOD_KQ, "qm_gemv_iq2xxs_m8"},
+    {QM_MOD_KQ, "qm_gemv_q2k_q81_m1"}, {QM_MOD_KQ, "qm_gemv_q2k_q81_m2"}, {QM_MOD_KQ, "qm_gemv_q2k_q81_m4"},
+    {QM_MOD_KQ, "qm_gemv_q2k_q81_m8"}, {QM_MOD_KQ, "qm_gemv_iq2xxs_q81_m1"}, {QM_MOD_KQ, "qm_gemv_iq2xxs_q81_m2"},
+    {QM_MOD_KQ, "qm_gemv_iq2xxs_q81_m4"}, {QM_MOD_KQ, "qm_gemv_iq2xxs_q81_m8"},
+    {QM_MOD_Q81, "qm_rmsnorm_q8_1"},   {QM_MOD_Q81, "qm_swiglu_q8_1"},    {QM_MOD_Q81, "qm_q8_1_expand"},
 };
 
 // ---- errors --------------------------------------------------------------------------
@@ -115,6 +121,7 @@ extern "C" const char *qm_error_string(int32_t code) {
     case QM_ERR_NOMEM: return "quant: host allocation failed";
     case QM_ERR_STATE: return "quant: call not valid in this state";
     case QM_ERR_LIMIT: return "quant: size beyond the fixed maximum of this entry point";
+    case QM_ERR_DOMAIN: return "cudaquant: nonfinite value or zero normalization denominator";
     }
     if (code > 0 && g_drv.loaded) {
         const char *s = nullptr;
@@ -230,6 +237,7 @@ extern "C" int32_t qm_destroy(qm_ctx *c) {
             if (c->moe_ws) d->cuMemFree_v2(c->moe_ws);
             if (c->moe_ws2) d->cuMemFree_v2(c->moe_ws2);
             if (c->moe_ws3) d->cuMemFree_v2(c->moe_ws3);
+            if (c->q81_ws) d->cuMemFree_v2(c->q81_ws);
             if (c->own_stream) d->cuStreamDestroy_v2(c->own_stream);
             for (int m = 0; m < QM_MOD_COUNT; m++)
                 if (c->modules[m]) d->cuModuleUnload(c->modules[m]);
@@ -263,7 +271,7 @@ extern "C" int32_t qm_last_status(qm_ctx *c, uint32_t *status) {
     DRV(c->drv->cuStreamSynchronize(c->stream));
     DRV(c->drv->cuMemcpyDtoH_v2(status, c->status_dev, 4));
     if (*status) DRV(c->drv->cuMemsetD8Async(c->status_dev, 0, 4, c->stream));
-    return (*status & QM_STATUS_TIMEOUT) ? QM_ERR_TIMEOUT : QM_OK;
+    return (*status & QM_STATUS_TIMEOUT) ? QM_ERR_TIMEOUT : (*status & QM_STATUS_DOMAIN) ? QM_ERR_DOMAIN : QM_OK;
 }
 
 #ifdef QM_DEBUG
@@ -324,13 +332,13 @@ extern "C" int32_t qm_memcpy_d2h(qm_ctx *c, void *dst, uint64_t src, int64_t byt
 }
 
 // ---- launch helper ----------------------------------------------------------------------
-int32_t qm_launch_ex(qm_ctx *c, int kernel, unsigned gx, unsigned block, unsigned smem, void *args, bool pdl,
-                     bool cooperative) {
+static int32_t launch_grid(qm_ctx *c, int kernel, unsigned gx, unsigned gy, unsigned block, unsigned smem, void *args,
+                           bool pdl, bool cooperative) {
     void *params[1] = {args};
     CUlaunchConfig cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDimX = gx;
-    cfg.gridDimY = 1;
+    cfg.gridDimY = gy;
     cfg.gridDimZ = 1;
     cfg.blockDimX = block;
     cfg.blockDimY = 1;
@@ -356,10 +364,14 @@ int32_t qm_launch_ex(qm_ctx *c, int kernel, unsigned gx, unsigned block, unsigne
     return QM_OK;
 }
 
+int32_t qm_launch_ex(qm_ctx *c, int kernel, unsigned gx, unsigned block, unsigned smem, void *args, bool pdl,
+                     bool cooperative) {
+    return launch_grid(c, kernel, gx, 1, block, smem, args, pdl, cooperative);
+}
+
 int32_t qm_launch(qm_ctx *c, int kernel, unsigned gx, unsigned gy, unsigned block, unsigned smem, void *args,
                   bool pdl) {
-    (void)gy;
-    return qm_launch_ex(c, kernel, gx, block, smem, args, pdl, false);
+    return launch_grid(c, kernel, gx, gy ? gy : 1, block, smem, args, pdl, false);
 }
 
 // ---- weight store -----------------------------------------------------------------------
@@ -761,6 +773,34 @@ static int32_t fused_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev,
                         (flags & QM_FLAG_PDL) != 0 && !coop, coop);
 }
 
+// Q2_K / IQ2_XXS: warp-per-row kernels over the GGUF bytes. x: float32 or (xq) Q8_1 blocks; ids_dev != 0: the
+// selected form over `experts` matrices stacked by rows in w, one grid row per slot, y = [slot][rows of one expert].
+int32_t qm_kq_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, bool xq, int32_t m, int64_t ldx, uint64_t y_dev,
+                     int64_t ldy, uint64_t ids_dev, int32_t experts, int32_t slots, int64_t x_slot_stride, bool pdl) {
+    QmKqArgs ka;
+    memset(&ka, 0, sizeof ka);
+    ka.wq = (const uint8_t *)(uintptr_t)w->wq;
+    ka.x = (const void *)(uintptr_t)x_dev;
+    ka.y = (float *)(uintptr_t)y_dev;
+    ka.ldx = ldx;
+    ka.ldy = ldy;
+    ka.rows = ids_dev ? w->rows / experts : w->rows;
+    ka.units = w->units;
+    ka.m = m;
+    ka.ids = (const int32_t *)(uintptr_t)ids_dev;
+    ka.experts = experts;
+    ka.x_slot_stride = x_slot_stride;
+    ka.y_slot_stride = ids_dev ? ka.rows : 0;
+    const int mi = m <= 1 ? 0 : m <= 2 ? 1 : m <= 4 ? 2 : 3;
+    const int k = (w->fmt == QM_FMT_Q2_K ? (xq ? QM_K_GEMV_Q2K_Q81_M1 : QM_K_GEMV_Q2K_M1)
+                                         : (xq ? QM_K_GEMV_IQ2XXS_Q81_M1 : QM_K_GEMV_IQ2XXS_M1)) + mi;
+    // eight warps per CTA, one row per warp at a time; enough CTAs to fill every SM eight deep
+    const int64_t want = (ka.rows + 7) / 8;
+    const int64_t cap = std::max<int64_t>(1, (int64_t)c->sm_count * 8 / std::max(1, slots));
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, cap));
+    return qm_launch(c, k, grid, (unsigned)std::max(1, slots), 256, 0, &ka, pdl);
+}
+
 int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,
                          uint64_t y_dev, int64_t ldy, uint32_t flags, CUdeviceptr partials, CUdeviceptr tickets) {
     if (w->fmt != QM_FMT_Q4_K && w->fmt != QM_FMT_Q4_0 && w->fmt != QM_FMT_Q8_0 && w->fmt != QM_FMT_Q2_K &&
@@ -774,22 +814,7 @@ int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t 
     if (w->fmt == QM_FMT_Q2_K || w->fmt == QM_FMT_IQ2_XXS) {
         // warp-per-row kernels over the GGUF bytes; plain products only (no fused input transform)
         if (xop != QM_XOP_NONE) return QM_ERR_ARG;
-        QmKqArgs ka;
-        memset(&ka, 0, sizeof ka);
-        ka.wq = (const uint8_t *)(uintptr_t)w->wq;
-        ka.x = (const float *)(uintptr_t)x_dev;
-        ka.y = (float *)(uintptr_t)y_dev;
-        ka.ldx = ldx;
-        ka.ldy = ldy;
-        ka.rows = w->rows;
-        ka.units = w->units;
-        ka.m = m;
-        const int mi = m <= 1 ? 0 : m <= 2 ? 1 : m <= 4 ? 2 : 3;
-        const int k = (w->fmt == QM_FMT_Q2_K ? QM_K_GEMV_Q2K_M1 : QM_K_GEMV_IQ2XXS_M1) + mi;
-        // eight warps per CTA, one row per warp at a time; enough CTAs to fill every SM eight deep
-        const int64_t want = (w->rows + 7) / 8;
-        const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)c->sm_count * 8));
-        return qm_launch(c, k, grid, 1, 256, 0, &ka, (flags & QM_FLAG_PDL) != 0);
+        return qm_kq_launch(c, w, x_dev, false, m, ldx, y_dev, ldy, 0, 0, 1, 0, (flags & QM_FLAG_PDL) != 0);
     }
     if (w->fmt == QM_FMT_Q4_K) {
         // integer tensor-core path; K is cut into slices when the activation planes of the

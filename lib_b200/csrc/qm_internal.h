@@ -9,7 +9,7 @@
 #define QM_CTX_MAGIC 0x514D4358u     // "QMCX"
 #define QM_WEIGHT_MAGIC 0x514D5754u  // "QMWT"
 
-enum { QM_MOD_GEMV = 0, QM_MOD_DEQUANT, QM_MOD_Q4K, QM_MOD_GEMM, QM_MOD_MOE, QM_MOD_KQ, QM_MOD_COUNT };
+enum { QM_MOD_GEMV = 0, QM_MOD_DEQUANT, QM_MOD_Q4K, QM_MOD_GEMM, QM_MOD_MOE, QM_MOD_KQ, QM_MOD_Q81, QM_MOD_COUNT };
 enum {
     QM_K_GEMV_Q40_M4 = 0, QM_K_GEMV_Q40_M8, QM_K_GEMV_Q80_M4,
     QM_K_GEMV_Q80_M8, QM_K_DEQUANT_Q4K, QM_K_DEQUANT_Q2K, QM_K_DEQUANT_Q40, QM_K_DEQUANT_Q80,
@@ -20,7 +20,10 @@ enum {
     QM_K_SUM_PARTS, QM_K_REPACK_PARTS,
     QM_K_GEMM_Q4K, QM_K_GEMM_Q4K_R256, QM_K_GEMM_Q4K_K128, QM_K_GEMM_Q4K_R256_K128, QM_K_MOE_ROUTE, QM_K_MOE_LISTS, QM_K_MOE_GATHER, QM_K_MOE_COMBINE,
     QM_K_DEQUANT_IQ2XXS, QM_K_GEMV_Q2K_M1, QM_K_GEMV_Q2K_M2, QM_K_GEMV_Q2K_M4, QM_K_GEMV_Q2K_M8,
-    QM_K_GEMV_IQ2XXS_M1, QM_K_GEMV_IQ2XXS_M2, QM_K_GEMV_IQ2XXS_M4, QM_K_GEMV_IQ2XXS_M8, QM_K_COUNT
+    QM_K_GEMV_IQ2XXS_M1, QM_K_GEMV_IQ2XXS_M2, QM_K_GEMV_IQ2XXS_M4, QM_K_GEMV_IQ2XXS_M8,
+    QM_K_GEMV_Q2K_Q81_M1, QM_K_GEMV_Q2K_Q81_M2, QM_K_GEMV_Q2K_Q81_M4, QM_K_GEMV_Q2K_Q81_M8,
+    QM_K_GEMV_IQ2XXS_Q81_M1, QM_K_GEMV_IQ2XXS_Q81_M2, QM_K_GEMV_IQ2XXS_Q81_M4, QM_K_GEMV_IQ2XXS_Q81_M8,
+    QM_K_RMSNORM_Q81, QM_K_SWIGLU_Q81, QM_K_Q81_EXPAND, QM_K_COUNT
 };
 
 #define QM_GEMV_SMEM_MAX (227 * 1024)
@@ -45,6 +48,8 @@ struct qm_ctx {
     CUdeviceptr upload_dev;
     CUdeviceptr moe_ws, moe_ws2, moe_ws3;   // scratch of the MoE stages (grown on demand)
     int64_t moe_ws_bytes, moe_ws2_bytes, moe_ws3_bytes;
+    CUdeviceptr q81_ws;                     // float32 copy of Q8_1 activations for the matvecs that quantize on their own
+    int64_t q81_ws_bytes;
     int64_t launches;
 };
 
@@ -116,3 +121,5 @@ int32_t qm_plan_gemv(qm_ctx *c, const QmWeight *w, int32_t m, QmGemvPlan *p);
 int32_t qm_plan_gemv_sms(int sm_count, const QmWeight *w, int32_t m, QmGemvPlan *p);
 int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,
                          uint64_t y_dev, int64_t ldy, uint32_t flags, CUdeviceptr partials, CUdeviceptr tickets);
+int32_t qm_kq_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, bool xq, int32_t m, int64_t ldx, uint64_t y_dev,
+                     int64_t ldy, uint64_t ids_dev, int32_t experts, int32_t slots, int64_t x_slot_stride, bool pdl);

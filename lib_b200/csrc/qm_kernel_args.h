@@ -12,6 +12,7 @@
 #define QM_GEMV_TILE_ROWS 16   // rows of one mma tile
 #define QM_STATUS_TIMEOUT 1u
 #define QM_STATUS_BOUNDS 2u
+#define QM_STATUS_DOMAIN 4u   // a Q8_1 producer met a zero denominator or a nonfinite value
 
 // Device layouts held by the weight store.
 //   Q4_K : the GGUF super-blocks regrouped so that one (16-row tile, K unit) item is 2304
@@ -193,12 +194,44 @@ struct QmCombineArgs {
 
 // GEMV over Q2_K / IQ2_XXS weights kept in their GGUF byte layout (qm_gemv_kq.cu).
 struct QmKqArgs {
-    const uint8_t *wq;       // [rows][units] super-blocks of 84 (Q2_K) or 66 (IQ2_XXS) bytes
-    const float *x;          // activations [m][ldx]
+    const uint8_t *wq;       // [rows][units] super-blocks of 84 (Q2_K) or 66 (IQ2_XXS) bytes; selected form: [experts][rows][units]
+    const void *x;           // activations [m][ldx] float32, or Q8_1 blocks (_q81 kernels; ldx in blocks)
     float *y;                // outputs [m][ldy]
     int64_t ldx, ldy;
-    int64_t rows;
+    int64_t rows;            // rows of the matrix (selected form: of one expert)
     int32_t units, m;
+    // selected form (ids != nullptr): blockIdx.y = slot, expert = ids[slot]
+    const int32_t *ids;
+    int32_t experts;
+    int32_t pad_;
+    int64_t x_slot_stride;   // floats (or blocks) between the activations of consecutive slots; 0: one x for all
+    int64_t y_slot_stride;   // floats between the outputs of consecutive slots
+};
+
+// RMSNorm -> Q8_1 (qm_q8_1.cu): row r of x (rows ldx floats apart) into cols/32 blocks of 36 bytes.
+struct QmNormQ81Args {
+    const float *x;
+    const float *weight;     // nullptr: unweighted
+    uint8_t *out;            // [rows][cols/32] blocks
+    unsigned int *status;
+    int64_t ldx;
+    int32_t cols;
+    float eps;
+};
+
+// SwiGLU -> Q8_1: `slots` vectors of `width` gate and up values laid end to end, one weight per slot.
+struct QmSwigluQ81Args {
+    const float *gate, *up, *weights;
+    uint8_t *out;            // ceil(width*slots/32) blocks
+    int32_t width, slots;
+};
+
+// Q8_1 -> float32.
+struct QmQ81ExpandArgs {
+    const uint8_t *xq;       // [m][ldx] blocks
+    float *out;              // [m][ld_out]
+    int64_t ldx, ld_out;
+    int32_t cols, m;
 };
 
 // h[j][r] = c_j * sum over parts of parts[k*part_stride + j*ld_in + r], c_j = rsqrt(mean square + eps)

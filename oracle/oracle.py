@@ -39,6 +39,13 @@ def _load():
     lib.qo_matvec_faithful.argtypes = [i32, p, i64, i64, i64, p, i32, i64, p, i64]
     lib.qo_rmsnorm.argtypes = [p, i64, ctypes.c_float, p]
     lib.qo_rmsnorm.restype = None
+    lib.qo_f32_to_f16.argtypes = [ctypes.c_float]
+    lib.qo_f32_to_f16.restype = ctypes.c_uint16
+    lib.qo_rmsnorm_q8_1.argtypes = [p, i64, p, i64, i64, i64, ctypes.c_float, i32, p]
+    lib.qo_swiglu_q8_1.argtypes = [p, p, p, i32, i32, p]
+    lib.qo_swiglu_q8_1.restype = None
+    lib.qo_q8_1_dequantize.argtypes = [p, i64, p]
+    lib.qo_q8_1_dequantize.restype = None
     return lib
 
 
@@ -47,7 +54,11 @@ _lib = _load()
 _MSG = {-1: "quant: element count is not a non-negative multiple of the block",
         -2: "quant: buffer length insufficient", -3: "quant: unknown format",
         -4: "gguf: unsupported tensor type", -5: "gguf: tensor row is not block aligned",
-        -6: "gguf: tensor byte count overflow"}
+        -6: "gguf: tensor byte count overflow",
+        -10: "cudaquant: invalid RMSNorm dimensions or epsilon", -11: "cudaquant: input length mismatch",
+        -12: "cudaquant: weight length mismatch", -13: "cudaquant: nonfinite input",
+        -14: "cudaquant: nonfinite weight", -15: "cudaquant: zero normalization denominator",
+        -16: "cudaquant: normalized value is nonfinite"}
 
 
 def _raise(rc):
@@ -155,3 +166,56 @@ def RMSNorm(x, eps=1e-6):
         for i in range(x.shape[0]):
             _lib.qo_rmsnorm(x[i].ctypes.data, x.shape[1], eps, out[i].ctypes.data)
     return out
+
+
+def Float32ToFloat16(f):
+    """nvidia/x/cudaquant/quant.go:325 float32ToFloat16 (bits)."""
+    return int(_lib.qo_f32_to_f16(float(np.float32(f))))
+
+
+def RMSNormQ8_1(input, weight, rows, cols, epsilon, weighted):
+    """nvidia/x/cudaquant/quant.go:46 RMSNormQ8_1 -> bytes of rows*cols/32 blocks (d, s, 32 quants)."""
+    x = np.ascontiguousarray(input, dtype=np.float32).reshape(-1)
+    w = np.zeros(0, dtype=np.float32) if weight is None else np.ascontiguousarray(weight, dtype=np.float32).reshape(-1)
+    # the output is sized by the input actually given: the length checks run before anything is written
+    nblk = x.size // 32 if rows > 0 and cols > 0 and int(rows) * int(cols) == x.size else 0
+    out = np.zeros(max(nblk, 1) * 36, dtype=np.uint8)
+    _raise(_lib.qo_rmsnorm_q8_1(x.ctypes.data, x.size, w.ctypes.data if w.size else None, w.size, int(rows), int(cols),
+                                float(epsilon), 1 if weighted else 0, out.ctypes.data))
+    return out[:nblk * 36].tobytes()
+
+
+def SwiGLUQ8_1(gate, up, weights, width, slots):
+    """fused_swiglu_q8_1 (nvidia/x/egraph/codegen.go:513-552) -> bytes of ceil(width*slots/32) blocks."""
+    g = np.ascontiguousarray(gate, dtype=np.float32).reshape(-1)
+    u = np.ascontiguousarray(up, dtype=np.float32).reshape(-1)
+    w = np.ascontiguousarray(weights, dtype=np.float32).reshape(-1)
+    assert g.size == u.size == width * slots and w.size == slots
+    nblk = (width * slots + 31) // 32
+    out = np.zeros(max(nblk, 1) * 36, dtype=np.uint8)
+    _lib.qo_swiglu_q8_1(g.ctypes.data, u.ctypes.data, w.ctypes.data, int(width), int(slots), out.ctypes.data)
+    return out[:nblk * 36].tobytes()
+
+
+def DequantizeQ8_1(blocks, n):
+    """q8_1_at (nvidia/x/egraph/codegen.go:125-128) for elements 0..n-1."""
+    b = _u8(blocks)
+    assert b.size >= (n + 31) // 32 * 36
+    out = np.empty(n, dtype=np.float32)
+    _lib.qo_q8_1_dequantize(b.ctypes.data, int(n), out.ctypes.data)
+    return out
+
+
+def SelectedMatVecQ8_1(fmt, data, experts, rows, cols, ids, xq):
+    """The *_selected_matvec_q8_1 kernels (nvidia/x/egraph/codegen.go:554-616): weights laid out
+    [expert][row][block], one Q8_1 vector x for all slots, y[slot][row]; a negative id gives NaN."""
+    a = _u8(data)
+    row_bytes = a.size // (experts * rows)
+    x = DequantizeQ8_1(xq, cols)
+    y = np.empty((len(ids), rows), dtype=np.float32)
+    for s, e in enumerate(ids):
+        if e < 0:
+            y[s] = np.nan
+        else:
+            y[s] = MatVec(fmt, a[e * rows * row_bytes:(e + 1) * rows * row_bytes], rows, cols, x)
+    return y

@@ -232,6 +232,25 @@ QM_API int32_t qm_moe_experts(qm_ctx *ctx, const qm_weight *gate_up, const qm_we
 QM_API int32_t qm_moe_combine(qm_ctx *ctx, uint64_t y_dev, uint64_t pos_dev, uint64_t weights_dev, int32_t tokens,
                               int32_t topk, int32_t hidden, uint64_t out_dev, int64_t ldo);
 
+/* Decode-time MoE over selected Q4_K experts (1..few tokens): for every (token, slot) pair the
+ * gate|up matvec of expert ids[t*topk+s] on the token's float32 x, then the down matvec on
+ * silu(gate) * up, then out[t] = sum_s weights[t*topk+s] * down output, slots in order. The whole
+ * batch is ONE persistent launch of the decode GEMV kernels plus a small combine; which expert a
+ * pair uses is read on the device, so ids and weights can come straight from qm_moe_route. The
+ * reference's counterparts are q2_k_selected_matvec_q8_1 / iq2_xxs_selected_matvec_q8_1
+ * (nvidia/x/egraph/codegen.go:554-616), one launch per projection. Experts must be Q4_K stores
+ * of one shape (gate|up: [2*ffn][hidden] rows stacked, down: [hidden][ffn]);
+ * max_tokens * topk <= 32. A token with an id outside [0, experts) gets NaN outputs. Pairs are
+ * independent matvecs: two tokens that choose the same expert each stream it — for larger
+ * batches use qm_moe_grouped. x_dev/ids_dev changes between runs rebuild a small device list
+ * (a synchronizing copy); steady-state callers keep their buffers. Asynchronous otherwise. */
+typedef struct qm_moe_decode qm_moe_decode;
+QM_API int32_t qm_moe_decode_create(qm_ctx *ctx, const qm_weight *gate_up, const qm_weight *down, int32_t experts,
+                                    int32_t topk, int32_t max_tokens, qm_moe_decode **out);
+QM_API int32_t qm_moe_decode_run(qm_ctx *ctx, qm_moe_decode *md, uint64_t x_dev, int32_t tokens, int64_t ldx,
+                                 uint64_t ids_dev, uint64_t weights_dev, uint64_t out_dev, int64_t ldo);
+QM_API int32_t qm_moe_decode_destroy(qm_ctx *ctx, qm_moe_decode *md);
+
 /* No counterpart in the reference. The Q4_0 / Q8_0 matvec of qm_matvec for callers that may
  * not allocate device memory at the point of the call: a server whose memory plan is frozen
  * once it starts serving, a latency-critical loop where an allocation would stall the device,

@@ -59,6 +59,9 @@ def _load():
         "qm_moe_experts": (i32, [p, p, p, i32, u64, p, u64]),
         "qm_moe_combine": (i32, [p, u64, u64, u64, i32, i32, i32, u64, i64]),
         "qm_matvec_noalloc": (i32, [u64, u64, i32, i64, u64, i64, u64]),
+        "qm_moe_decode_create": (i32, [p, p, p, i32, i32, i32, ctypes.POINTER(p)]),
+        "qm_moe_decode_run": (i32, [p, p, u64, i32, i64, u64, u64, u64, i64]),
+        "qm_moe_decode_destroy": (i32, [p, p]),
         "qm_rmsnorm_q8_1": (i32, [p, u64, i64, u64, i64, i64, ctypes.c_float, u64]),
         "qm_rmsnorm_q8_1_host": (i32, [p, p, i64, p, i64, i64, i64, ctypes.c_float, i32, p]),
         "qm_swiglu_q8_1": (i32, [p, u64, u64, u64, i32, i32, u64]),
@@ -285,6 +288,21 @@ class Context:
     def moe_combine(self, y_dev, pos_dev, weights_dev, tokens, topk, hidden, out_dev, ldo):
         _check(lib.qm_moe_combine(self._h, y_dev, pos_dev, weights_dev, tokens, topk, hidden, out_dev, ldo),
                "moe_combine")
+
+    def moe_decode_create(self, gate_up, down, topk, max_tokens):
+        """qm_moe_decode_create -> opaque handle for moe_decode_run / moe_decode_destroy."""
+        n = len(gate_up)
+        ga = (ctypes.c_uint64 * n)(*[w.handle for w in gate_up])
+        da = (ctypes.c_uint64 * n)(*[w.handle for w in down])
+        h = ctypes.c_void_p()
+        _check(lib.qm_moe_decode_create(self._h, ga, da, n, topk, max_tokens, ctypes.byref(h)), "moe_decode_create")
+        return h
+
+    def moe_decode_run(self, md, x_dev, tokens, ldx, ids_dev, weights_dev, out_dev, ldo):
+        _check(lib.qm_moe_decode_run(self._h, md, x_dev, tokens, ldx, ids_dev, weights_dev, out_dev, ldo), "moe_decode_run")
+
+    def moe_decode_destroy(self, md):
+        _check(lib.qm_moe_decode_destroy(self._h, md), "moe_decode_destroy")
 
     def matvec_noalloc(self, w, x_dev, m, ldx, y_dev, ldy, cu_stream=0):
         """qm_matvec_noalloc: Q4_0/Q8_0 matvec that allocates nothing (fixed scratch array)."""

@@ -1079,7 +1079,7 @@ __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, 
 // poll their own arena only, so no barrier crosses the GPUs inside a step. One barrier over the
 // GPUs ends the launch: when it returns, every slice of the step has arrived everywhere, which
 // is what lets the host refill the other arena half with the "not yet written" pattern.
-template <int CPM, int D, bool TP>
+template <int CPM, int D, bool TP, bool SEL = false>
 __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     constexpr int C = 16;                       // warps per CTA
     constexpr int NL = CPM == 4 ? 3 : 2;        // limbs per activation row
@@ -1140,7 +1140,12 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             warp_range(po->q, po->rem, units, (int)blockIdx.x - po->cta0, po->nctas, tile0, lo, n, wq, wrem);
             if (n > 0) {
                 p_n = n;
-                p_src = po->wq + ((int64_t)tile0 * units + lo) * QM_Q4K_ITEM_BYTES + lane * 16;
+                const uint8_t *wq = po->wq;
+                if (SEL && po->sel_table) {   // the slot's expert, known on the device only
+                    const int id = po->sel_ids[po->sel_index];
+                    wq = po->sel_table[min(max(id, 0), po->sel_count - 1)];
+                }
+                p_src = wq + ((int64_t)tile0 * units + lo) * QM_Q4K_ITEM_BYTES + lane * 16;
                 break;
             }
         }
@@ -1474,6 +1479,17 @@ QM_DD_KERNEL(qm_fused_q4k_dd_c4d4_tp, 4, 4, true)
 QM_DD_KERNEL(qm_fused_q4k_dd_c2d2_tp, 2, 2, true)
 QM_DD_KERNEL(qm_fused_q4k_dd_c2d3_tp, 2, 3, true)
 QM_DD_KERNEL(qm_fused_q4k_dd_c2d4_tp, 2, 4, true)
+
+// One activation row per op and ops whose matrix is chosen on the device from a table of experts
+// (QmOp::sel_table): decode-time MoE as a list of (token, slot) matvecs.
+#define QM_DD_SEL_KERNEL(name, d)                                                            \
+    extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)                     \
+        name(const __grid_constant__ QmFusedArgs a) {                                        \
+        dd_body<4, d, false, true>(a);                                                       \
+    }
+QM_DD_SEL_KERNEL(qm_fused_q4k_dd_c4d2_sel, 2)
+QM_DD_SEL_KERNEL(qm_fused_q4k_dd_c4d3_sel, 3)
+QM_DD_SEL_KERNEL(qm_fused_q4k_dd_c4d4_sel, 4)
 
 // h = c * (sum of the K parts of the step's last matvec), see QmSumPartsArgs.
 extern "C" __global__ void __launch_bounds__(256) qm_sum_parts(const __grid_constant__ QmSumPartsArgs a) {

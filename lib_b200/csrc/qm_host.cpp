@@ -102,6 +102,8 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_KQ, "qm_gemv_q2k_q81_m8"}, {QM_MOD_KQ, "qm_gemv_iq2xxs_q81_m1"}, {QM_MOD_KQ, "qm_gemv_iq2xxs_q81_m2"},
     {QM_MOD_KQ, "qm_gemv_iq2xxs_q81_m4"}, {QM_MOD_KQ, "qm_gemv_iq2xxs_q81_m8"},
     {QM_MOD_Q81, "qm_rmsnorm_q8_1"},   {QM_MOD_Q81, "qm_swiglu_q8_1"},    {QM_MOD_Q81, "qm_q8_1_expand"},
+    {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d2_sel"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d3_sel"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d4_sel"},
+    {QM_MOD_MOE, "qm_moe_decode_combine"},
 };
 
 // ---- errors --------------------------------------------------------------------------
@@ -190,6 +192,10 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             r = d->cuFuncSetAttribute(c->fn[QM_K_GEMM_Q4K], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             for (int k = QM_K_GEMM_Q4K_R256; k <= QM_K_GEMM_Q4K_R256_K128 && r == CUDA_SUCCESS; k++)
                 r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
+            if (r != CUDA_SUCCESS) err = (int32_t)r;
+        }
+        for (int k = QM_K_FUSED_Q4K_DD_C4D2_SEL; k <= QM_K_FUSED_Q4K_DD_C4D4_SEL && !err; k++) {
+            r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
         for (int k = QM_K_GEMV_Q40_M4; k <= QM_K_GEMV_Q80_M8 && !err; k++) {

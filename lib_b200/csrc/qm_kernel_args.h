@@ -103,6 +103,12 @@ struct alignas(16) QmOp {   // a multiple of 16 bytes: the kernels copy descript
     const float *ssq_in;      // consumer side: the same words of the op that produced x
     float ssq_in_inv_cols;    // 1 / K of the op that produced x
     float ssq_in_eps;         // its epsilon
+    // Selected expert (kernels *_sel only): when sel_table is set the op's matrix is not wq but
+    // sel_table[sel_ids[sel_index]] (an id outside [0, sel_count) is clamped into it), read on the
+    // device when the op's first copy is issued — all candidates have this op's shape.
+    const uint8_t *const *sel_table;
+    const int32_t *sel_ids;
+    int32_t sel_index, sel_count;
 };
 
 struct QmFusedArgs {
@@ -232,6 +238,17 @@ struct QmQ81ExpandArgs {
     float *out;              // [m][ld_out]
     int64_t ldx, ld_out;
     int32_t cols, m;
+};
+
+// out[t][c] = sum_k weights[t*topk+k] * y[t*topk+k][c] (decode-time MoE: one output vector per (token, slot)
+// pair); a token with an id outside [0, experts) gets the NaN 0x7fffffff.
+struct QmDecodeCombineArgs {
+    const float *y;          // [tokens*topk][hidden]
+    const int32_t *ids;
+    const float *weights;
+    float *out;
+    int64_t ldo;
+    int32_t tokens, topk, experts, hidden;
 };
 
 // h[j][r] = c_j * sum over parts of parts[k*part_stride + j*ld_in + r], c_j = rsqrt(mean square + eps)

@@ -284,3 +284,183 @@ extern "C" int32_t qm_moe_grouped(qm_ctx *c, const qm_weight *gate_up, const qm_
     }
     return qm_moe_combine(c, ws + o_y, ws + o_pos, weights_dev, tokens, topk, (int32_t)hidden, out_dev, ldo);
 }
+
+// ---- decode-time MoE over selected experts ----------------------------------------------------
+// One persistent launch of the data-driven decode kernel runs every (token, slot) pair of a small
+// batch as two dependent matvecs of one activation row: gate|up of the slot's expert on the token's
+// x, then down on silu(gate) * up. Which expert a pair uses is read on the device (QmOp::sel_*),
+// so the host never sees the router's output. The reference's counterpart is the pair of
+// *_selected_matvec_q8_1 kernels (nvidia/x/egraph/codegen.go:554-616), one launch per projection,
+// one warp per row.
+struct qm_moe_decode {
+    uint32_t magic;
+    int experts, topk, max_tokens;
+    int64_t hidden, ffn;
+    std::vector<const QmWeight *> gu, dn;
+    CUdeviceptr tables;      // [2][experts] device pointers: gate|up stores, then down stores
+    CUdeviceptr bufs;        // per pair: gate|up output [2*ffn], then per pair: down output [hidden]
+    CUdeviceptr ops_dev;
+    CUdeviceptr sync;
+    QmFusedPlan plan;
+    int kernel;
+    // what the device op list was built for
+    int built_tokens;
+    uint64_t built_x, built_ids;
+    int64_t built_ldx;
+};
+#define QM_MOE_DECODE_MAGIC 0x514D4D44u   // "QMMD"
+#define QM_MOE_DECODE_MAX_PAIRS 32
+
+extern "C" int32_t qm_moe_decode_destroy(qm_ctx *c, qm_moe_decode *d) {
+    CHECK_CTX(c);
+    if (!d || d->magic != QM_MOE_DECODE_MAGIC) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    c->drv->cuStreamSynchronize(c->stream);
+    if (d->tables) c->drv->cuMemFree_v2(d->tables);
+    if (d->bufs) c->drv->cuMemFree_v2(d->bufs);
+    if (d->ops_dev) c->drv->cuMemFree_v2(d->ops_dev);
+    if (d->sync) c->drv->cuMemFree_v2(d->sync);
+    d->magic = 0;
+    delete d;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_moe_decode_create(qm_ctx *c, const qm_weight *gate_up, const qm_weight *down, int32_t experts,
+                                        int32_t topk, int32_t max_tokens, qm_moe_decode **out) {
+    CHECK_CTX(c);
+    if (!gate_up || !down || !out) return QM_ERR_ARG;
+    *out = nullptr;
+    if (experts < 1 || experts > 4096 || topk < 1 || topk > experts || max_tokens < 1 ||
+        (int64_t)max_tokens * topk > QM_MOE_DECODE_MAX_PAIRS)
+        return QM_ERR_SHAPE;
+    qm_moe_decode *d = new (std::nothrow) qm_moe_decode();
+    if (!d) return QM_ERR_NOMEM;
+    d->magic = QM_MOE_DECODE_MAGIC;
+    d->experts = experts;
+    d->topk = topk;
+    d->max_tokens = max_tokens;
+    d->built_tokens = 0;
+    for (int e = 0; e < experts; e++) {
+        const QmWeight *g = qm_weight_from_handle(gate_up[e]), *dn = qm_weight_from_handle(down[e]);
+        int32_t bad = QM_OK;
+        if (!g || !dn) bad = QM_ERR_ARG;
+        else if (g->fmt != QM_FMT_Q4_K || dn->fmt != QM_FMT_Q4_K) bad = QM_ERR_FORMAT;
+        else if (g->device != c->device || dn->device != c->device) bad = QM_ERR_ARG;
+        else if (e == 0) {
+            d->hidden = g->cols;
+            d->ffn = dn->cols;
+        }
+        if (!bad && (g->cols != d->hidden || g->rows != 2 * d->ffn || dn->cols != d->ffn || dn->rows != d->hidden))
+            bad = QM_ERR_SHAPE;
+        if (bad) {
+            delete d;
+            return bad;
+        }
+        d->gu.push_back(g);
+        d->dn.push_back(dn);
+    }
+    const int max_units = (int)std::max(d->gu[0]->units, d->dn[0]->units);
+    if (qm_plan_fused(c, 1, max_units, false, &d->plan) != QM_OK || d->plan.consumers != 16 || d->plan.depth < 2 ||
+        d->plan.depth > 4) {
+        delete d;
+        return QM_ERR_SHAPE;
+    }
+    d->kernel = QM_K_FUSED_Q4K_DD_C4D2_SEL + (d->plan.depth - 2);
+    CtxGuard g(c);
+    if (g.rc != CUDA_SUCCESS) {
+        delete d;
+        return (int32_t)g.rc;
+    }
+    std::vector<uint64_t> tab((size_t)2 * experts);
+    for (int e = 0; e < experts; e++) {
+        tab[e] = (uint64_t)d->gu[e]->wq;
+        tab[experts + e] = (uint64_t)d->dn[e]->wq;
+    }
+    const int64_t pairs = (int64_t)max_tokens * topk;
+    CUresult r = c->drv->cuMemAlloc_v2(&d->tables, tab.size() * 8);
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemcpyHtoD_v2(d->tables, tab.data(), tab.size() * 8);
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&d->bufs, (size_t)(pairs * (2 * d->ffn + d->hidden) * 4));
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&d->ops_dev, (size_t)(2 * pairs) * sizeof(QmOp));
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&d->sync, 256);
+    if (r != CUDA_SUCCESS) {
+        qm_moe_decode_destroy(c, d);
+        return (int32_t)r;
+    }
+    *out = d;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_moe_decode_run(qm_ctx *c, qm_moe_decode *d, uint64_t x_dev, int32_t tokens, int64_t ldx,
+                                     uint64_t ids_dev, uint64_t weights_dev, uint64_t out_dev, int64_t ldo) {
+    CHECK_CTX(c);
+    if (!d || d->magic != QM_MOE_DECODE_MAGIC) return QM_ERR_ARG;
+    if (tokens < 0 || tokens > d->max_tokens || ldx < d->hidden || ldo < d->hidden || (ldx & 3)) return QM_ERR_SHAPE;
+    if (!x_dev || !ids_dev || !weights_dev || !out_dev || (x_dev & 15) || (ids_dev & 3) || (weights_dev & 3))
+        return QM_ERR_ARG;
+    if (tokens == 0) return QM_OK;
+    CtxGuard g(c);
+    DRV(g.rc);
+    const int pairs = tokens * d->topk;
+    const int64_t gu_floats = 2 * d->ffn;
+    const CUdeviceptr gu0 = d->bufs, dn0 = d->bufs + (size_t)((int64_t)d->max_tokens * d->topk * gu_floats * 4);
+    if (tokens != d->built_tokens || x_dev != d->built_x || ids_dev != d->built_ids || ldx != d->built_ldx) {
+        // all gate|up ops first: by the time a pair's down op stages its x, that x has long been written
+        std::vector<QmOp> ops((size_t)2 * pairs);
+        for (int pr = 0; pr < pairs; pr++) {
+            const int t = pr / d->topk;
+            QmOp &a = ops[pr], &b = ops[pairs + pr];
+            const CUdeviceptr gu = gu0 + (size_t)pr * gu_floats * 4, dn = dn0 + (size_t)pr * d->hidden * 4;
+            qm_fill_op(c, d->plan, d->gu[0], x_dev + (size_t)t * ldx * 4, 0, ldx, gu, gu_floats, QM_XOP_NONE, 0, 0,
+                       d->gu[0]->units, 0, &a);
+            qm_fill_op(c, d->plan, d->dn[0], gu, gu + (size_t)d->ffn * 4, gu_floats, dn, d->hidden, QM_XOP_SWIGLU, 1, 0,
+                       d->dn[0]->units, 0, &b);
+            a.sel_table = (const uint8_t *const *)(uintptr_t)d->tables;
+            b.sel_table = (const uint8_t *const *)(uintptr_t)(d->tables + (size_t)d->experts * 8);
+            a.sel_ids = b.sel_ids = (const int32_t *)(uintptr_t)ids_dev;
+            a.sel_index = b.sel_index = pr;
+            a.sel_count = b.sel_count = d->experts;
+        }
+        DRV(c->drv->cuStreamSynchronize(c->stream));   // the list in use may still be read
+        DRV(c->drv->cuMemcpyHtoD_v2(d->ops_dev, ops.data(), ops.size() * sizeof(QmOp)));
+        d->built_tokens = tokens;
+        d->built_x = x_dev;
+        d->built_ids = ids_dev;
+        d->built_ldx = ldx;
+    }
+    // every output word starts as "not yet written" (all ones)
+    DRV(c->drv->cuMemsetD32Async(gu0, 0xFFFFFFFFu, (size_t)pairs * gu_floats, c->stream));
+    DRV(c->drv->cuMemsetD32Async(dn0, 0xFFFFFFFFu, (size_t)pairs * d->hidden, c->stream));
+    DRV(c->drv->cuMemsetD32Async(d->sync, 0, 64, c->stream));
+    QmFusedArgs a;
+    memset(&a, 0, sizeof a);
+    a.ops = (const QmOp *)(uintptr_t)d->ops_dev;
+    a.status = (unsigned int *)(uintptr_t)c->status_dev;
+    a.grid_bar = (unsigned int *)(uintptr_t)d->sync;
+    a.nops = 2 * pairs;
+    a.ngroups = 1;
+    a.m = 1;
+    a.consumers = d->plan.consumers;
+    a.depth = d->plan.depth;
+    a.max_units = d->plan.max_units;
+    a.cpm = d->plan.cpm;
+    a.wait_cycles = qm_wait_cycles();
+    // no programmatic launch: the ids must be complete before the first copy is issued; cooperative: the CTAs
+    // poll one another's outputs and must all be resident
+    int32_t rc = qm_launch_ex(c, d->kernel, (unsigned)qm_fused_grid(c), (unsigned)d->plan.consumers * 32,
+                              (unsigned)d->plan.smem, &a, false, true);
+    if (rc) return rc;
+    QmDecodeCombineArgs ca;
+    memset(&ca, 0, sizeof ca);
+    ca.y = (const float *)(uintptr_t)dn0;
+    ca.ids = (const int32_t *)(uintptr_t)ids_dev;
+    ca.weights = (const float *)(uintptr_t)weights_dev;
+    ca.out = (float *)(uintptr_t)out_dev;
+    ca.ldo = ldo;
+    ca.tokens = tokens;
+    ca.topk = d->topk;
+    ca.experts = d->experts;
+    ca.hidden = (int32_t)d->hidden;
+    return qm_launch(c, QM_K_MOE_DECODE_COMBINE, grid_for((int64_t)tokens * d->hidden, 256, c->sm_count * 4), 1, 256, 0,
+                     &ca, false);
+}

@@ -112,3 +112,19 @@ extern "C" __global__ void __launch_bounds__(256) qm_moe_combine(const __grid_co
         a.out[(int64_t)tok * a.ldo + c] = s;
     }
 }
+
+// Decode-time MoE: the weighted sum of a token's slot outputs, in slot order.
+extern "C" __global__ void __launch_bounds__(256) qm_moe_decode_combine(const __grid_constant__ QmDecodeCombineArgs a) {
+    const int64_t total = (int64_t)a.tokens * a.hidden;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int tok = (int)(i / a.hidden), c = (int)(i - (int64_t)tok * a.hidden);
+        float s = 0.f;
+        bool bad = false;
+        for (int k = 0; k < a.topk; k++) {
+            const int id = a.ids[tok * a.topk + k];
+            bad |= id < 0 || id >= a.experts;
+            s = fmaf(a.weights[tok * a.topk + k], a.y[(int64_t)(tok * a.topk + k) * a.hidden + c], s);
+        }
+        a.out[(int64_t)tok * a.ldo + c] = bad ? __int_as_float(0x7fffffff) : s;
+    }
+}

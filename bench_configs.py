@@ -7,6 +7,9 @@
      (under `python -m torch.distributed.run --nproc-per-node N ...` the experts are sharded
      over the N GPUs and the tokens exchanged by NCCL all-to-all)
   7  Q4_K decode GEMV at the Llama-3-8B matrix shapes, one matrix at a time, batch 1 and 8
+  8  decode-time MoE: Mixtral-8x7B-shaped layer (8 Q4_K experts, top-2) at 1, 2 and 4 tokens through
+     qm_moe_decode (one launch for all (token, slot) matvecs); Q2_K / IQ2_XXS matvecs over selected
+     experts with Q8_1 activations; the Q8_1 producers
 
 Run as `python bench_configs.py --config 3 [--m 2048] [--copies 4] [--iters 10]`; bench.py runs
 short versions of the same cases for its `other_configs` block.
@@ -158,6 +161,99 @@ def moe_case(ctx, tokens, iters, hidden=4096, ffn=14336, experts=8, topk=2):
             "weight_bytes": sum(synth.gguf_bytes(Q4_K, 3 * ffn, hidden) for _ in range(experts))}
 
 
+def moe_decode_case(ctx, tokens, iters, hidden=4096, ffn=14336, experts=8, topk=2):
+    """Config 8: a decode step of an MoE layer. Bytes per step = the experts the pairs stream."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gu = [ctx.store_upload(Q4_K, 2 * ffn, hidden, synth.weights(Q4_K, 2 * ffn, hidden, 10 + e)) for e in range(experts)]
+    dn = [ctx.store_upload(Q4_K, hidden, ffn, synth.weights(Q4_K, hidden, ffn, 30 + e)) for e in range(experts)]
+    md = ctx.moe_decode_create(gu, dn, topk, tokens)
+    x = torch.randn(tokens, hidden, device=dev)
+    out = torch.empty(tokens, hidden, device=dev)
+    wts = torch.full((tokens, topk), 1.0 / topk, device=dev)
+    # eight id sets that walk over all experts, so that consecutive steps do not find their experts in L2
+    sets = [torch.tensor([[(2 * (t + r) + s * 3 + r) % experts for s in range(topk)] for t in range(tokens)],
+                         dtype=torch.int32, device=dev) for r in range(8)]
+    ids = torch.empty(tokens, topk, dtype=torch.int32, device=dev)
+
+    def enqueue():
+        for r in range(8):
+            ids.copy_(sets[r])
+            ctx.moe_decode_run(md, x.data_ptr(), tokens, hidden, ids.data_ptr(), wts.data_ptr(), out.data_ptr(), hidden)
+
+    ms = timed_eager_torch(ctx, enqueue, iters) / 8
+    rc, status = ctx.last_status()
+    ctx.moe_decode_destroy(md)
+    for w in gu + dn:
+        w.free()
+    hbm, _, which = peaks()
+    nbytes = tokens * topk * synth.gguf_bytes(Q4_K, 3 * ffn, hidden)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"op": "moe_decode", "format": "Q4_K", "experts": experts, "topk": topk, "tokens": tokens, "hidden": hidden,
+            "ffn": ffn, "us": round(ms * 1e3, 1), "weight_GBps": round(gbs, 1), "frac_hbm": round(gbs / hbm, 3),
+            "peak": which, "launches_per_step": 2, "status": [rc, status]}
+
+
+def timed_eager_torch(ctx, enqueue, iters):
+    """timed_eager for passes that also issue torch copies: everything on one torch stream."""
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        ctx.set_stream(s.cuda_stream)
+        for _ in range(3):
+            enqueue()
+        s.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for _ in range(iters):
+            enqueue()
+        e1.record(s)
+        s.synchronize()
+    ctx.set_stream(0)
+    return e0.elapsed_time(e1) / iters
+
+
+def selected_case(ctx, fmt, iters, rows=2048, cols=4096, experts=64, slots=6):
+    """Config 8: *_selected_matvec_q8_1 at a DeepSeek-style routed-expert shape: `slots` of `experts` small matrices."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    one = synth.weights(fmt, rows, cols, 3)
+    raw = np.concatenate([np.frombuffer(one, dtype=np.uint8)] * experts)
+    w = ctx.store_upload(fmt, experts * rows, cols, raw)
+    xf = synth.activations(1, cols, 9)
+    xq_host = np.zeros((cols // 32) * 36, dtype=np.uint8)
+    x = torch.from_numpy(xf).to(dev)
+    xq = torch.from_numpy(xq_host).to(dev)
+    ctx.rmsnorm_q8_1(x.data_ptr(), cols, 0, 1, cols, 1e-6, xq.data_ptr())
+    y = torch.empty(slots, rows, device=dev)
+    sets = [torch.tensor([(r * slots + s * 5) % experts for s in range(slots)], dtype=torch.int32, device=dev) for r in range(16)]
+
+    def enqueue():
+        for r in range(16):
+            ctx.matvec_selected(w, experts, sets[r].data_ptr(), slots, xq.data_ptr(), 0, y.data_ptr(), _capi.FLAG_X_Q8_1)
+
+    ms = timed_graph(ctx, enqueue, iters) / 16
+    w.free()
+    hbm, _, which = peaks()
+    nbytes = slots * synth.gguf_bytes(fmt, rows, cols)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"op": "selected_matvec_q8_1", "format": {10: "Q2_K", 16: "IQ2_XXS"}[fmt], "experts": experts, "slots": slots,
+            "rows": rows, "cols": cols, "us": round(ms * 1e3, 2), "weight_GBps": round(gbs, 1),
+            "frac_hbm": round(gbs / hbm, 3), "peak": which}
+
+
+def q8_1_producer_case(ctx, rows, cols, iters):
+    dev = torch.device("cuda", torch.cuda.current_device())
+    x = torch.randn(rows, cols, device=dev)
+    wt = torch.rand(cols, device=dev) + 0.5
+    out = torch.empty(rows * cols // 32 * 36, dtype=torch.uint8, device=dev)
+
+    def enqueue():
+        for _ in range(16):
+            ctx.rmsnorm_q8_1(x.data_ptr(), cols, wt.data_ptr(), rows, cols, 1e-6, out.data_ptr())
+
+    ms = timed_graph(ctx, enqueue, iters) / 16
+    return {"op": "rmsnorm_q8_1", "rows": rows, "cols": cols, "us": round(ms * 1e3, 2),
+            "note": "latency-bound: %d bytes in, %d out" % (rows * cols * 4, rows * cols // 32 * 36)}
+
+
 def moe_ep_case(tokens_total, iters, hidden=4096, ffn=14336, experts=8, topk=2):
     """Config 5 across the ranks of a torchrun launch: experts sharded by index, the batch of
     `tokens_total` tokens split evenly, rows exchanged by NCCL all-to-all (lib_b200.moe)."""
@@ -203,7 +299,7 @@ def moe_ep_case(tokens_total, iters, hidden=4096, ffn=14336, experts=8, topk=2):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, required=True, choices=(1, 2, 3, 5, 7))
+    ap.add_argument("--config", type=int, required=True, choices=(1, 2, 3, 5, 7, 8))
     ap.add_argument("--m", type=int, default=0, help="only this batch size")
     ap.add_argument("--copies", type=int, default=0, help="weight copies cycled through (default: > L2)")
     ap.add_argument("--iters", type=int, default=20)
@@ -230,6 +326,13 @@ def main():
     elif a.config == 3:
         for m in ((a.m,) if a.m else (64, 256, 2048)):
             out.append(gemm_case(ctx, m, a.copies, a.iters))
+    elif a.config == 8:
+        for t in ((a.m,) if a.m else (1, 2, 4)):
+            out.append(moe_decode_case(ctx, t, max(3, a.iters // 4)))
+        for fmt in (10, 16):
+            out.append(selected_case(ctx, fmt, a.iters))
+        for rows in (1, 8):
+            out.append(q8_1_producer_case(ctx, rows, 4096, a.iters))
     else:
         out.append(moe_case(ctx, a.tokens, max(3, a.iters // 4)))
     for line in out:

@@ -6,7 +6,8 @@
 // GGUF byte layout (84- and 66-byte super-blocks of 256 elements, rows contiguous): a warp
 // owns a row at a time and walks its super-blocks, the 32 lanes covering the 256 elements of
 // one super-block — 8 elements per lane, so every lane decodes whole bytes and the per-group
-// scales are read once per lane. Rows are dealt to the warps of a grid that fills the SMs.
+// scales are read once per lane. Rows are dealt to the warps of a grid that fills the SMs; a
+// warp streams its rows through a private shared-memory ring (cp.async, 2..4 rows in flight).
 // HBM-bound: algorithmic bytes per 256 weights = 84 (Q2_K) or 66 (IQ2_XXS) plus 4 bytes per
 // activation.
 //
@@ -32,6 +33,15 @@
 namespace {
 
 __device__ __forceinline__ float h2f(uint32_t bits) { return __half2float(__ushort_as_half((unsigned short)bits)); }
+// Exact float of an integer of magnitude below 2^22 with two full-rate instructions (the conversion
+// instruction runs at a quarter of that rate and was the busiest pipe of the Q8_1 kernels).
+__device__ __forceinline__ float small_int_to_float(int v) { return __int_as_float(v + 0x4B400000) - 12582912.f; }
+// Bytes 0..3 of `a`, each replaced by eight copies of its top bit (PRMT selector nibbles with bit 3 set).
+__device__ __forceinline__ uint32_t top_bits_to_bytes(uint32_t a) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %1, 0xBA98;" : "=r"(d) : "r"(a));
+    return d;
+}
 
 // Elements e, e+1 (e even) of activation row `row` (x: floats, or Q8_1 blocks when XQ; ldx in floats or blocks).
 template <bool XQ>
@@ -123,7 +133,74 @@ __device__ __forceinline__ void iq2xxs_block(const uint8_t *blk, const void *x, 
     }
 }
 
-template <int FMT, int M, bool XQ>
+// ---- Q8_1 activations: integer dot products ---------------------------------------------------
+// With the activations already in 8-bit quants the products run on dp4a: four 2-bit codes (or four
+// codebook magnitudes) times four quants per instruction, the block scales applied once per group
+// in float32 — a sixth of the instructions of the float form, which is bound by int-to-float
+// conversions.
+
+// Q2_K x Q8_1. Sixteen lanes cover a super-block, one 32-bit word of qs (16 elements of four groups)
+// each, so a warp takes two super-blocks per step; `blk` is this lane's super-block (or null past
+// the row's end), i = lane & 15, xb0 the index of the super-block's first Q8_1 block.
+template <int M>
+__device__ __forceinline__ void q2k_q81_block(const uint8_t *blk, const uint8_t *xq, int ldx, int m, int xb0, int i,
+                                              float (&acc)[M]) {
+    if (!blk) return;
+    const int h = i >> 3, li = i & 7;
+    const uint32_t word = *reinterpret_cast<const uint32_t *>(blk + 16 + 4 * i);
+    const uint32_t s_lo = *reinterpret_cast<const uint32_t *>(blk + 8 * h);
+    const uint32_t s_hi = *reinterpret_cast<const uint32_t *>(blk + 8 * h + 4);
+    const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk + 80);
+    const float d = h2f(dd & 0xFFFFu), dmin = h2f(dd >> 16);
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        // elements 128h + 32s + 4li .. +3: group 8h + 2s + (li >> 2), Q8_1 block xb0 + 4h + s
+        const uint32_t scb = ((s < 2 ? s_lo : s_hi) >> (8 * (((2 * s) & 3) + (li >> 2)))) & 0xFFu;
+        const int v = (int)((word >> (2 * s)) & 0x03030303u);
+        const int sc = (int)(scb & 0x0Fu), mn = (int)(scb >> 4);
+#pragma unroll
+        for (int j = 0; j < M; j++) {
+            const uint8_t *xb = xq + ((j < m ? j : 0) * ldx + xb0 + 4 * h + s) * 36;
+            const int xw = (int)*reinterpret_cast<const uint32_t *>(xb + 4 + 4 * li);
+            const float dx = h2f(*reinterpret_cast<const uint16_t *>(xb));
+            const int dot = __dp4a(v, xw, 0), sum = __dp4a(0x01010101, xw, 0);
+            acc[j] = fmaf(dx, d * small_int_to_float(sc * dot) - dmin * small_int_to_float(mn * sum), acc[j]);   // |.| <= 15*4*3*127
+        }
+    }
+}
+
+// IQ2_XXS x Q8_1: lane = 4*group + l owns codebook entry l of its group (eight elements); the signs go into
+// the sum as dot(all) - 2*dot(negated ones), which needs no per-byte negation.
+template <int M>
+__device__ __forceinline__ void iq2xxs_q81_block(const uint8_t *blk, const uint8_t *xq, int ldx, int m, int xb0, int lane,
+                                                 const unsigned long long *grid, float (&acc)[M]) {
+    const float d = h2f(*reinterpret_cast<const uint16_t *>(blk));
+    const int group = lane >> 2, l = lane & 3;
+    const uint16_t *g16 = reinterpret_cast<const uint16_t *>(blk + 2 + 8 * group);
+    const uint32_t indices = (uint32_t)g16[0] | ((uint32_t)g16[1] << 16);
+    const uint32_t aux = (uint32_t)g16[2] | ((uint32_t)g16[3] << 16);
+    const float scale = (0.125f * d) * (float)(2u * (aux >> 28) + 1u);
+    const unsigned long long code = grid[(indices >> (8 * l)) & 0xFFu];
+    const uint32_t si = (aux >> (7 * l)) & 127u;
+    const uint32_t signs = si | ((uint32_t)(__popc(si) & 1) << 7);
+    // byte k of a mask word = 0xFF where sign bit k is set: the bit goes to the byte's top, PRMT replicates it
+    const uint32_t t0 = ((signs & 0xFu) * 0x10204080u) & 0x80808080u, t1 = ((signs >> 4) * 0x10204080u) & 0x80808080u;
+    const int g0 = (int)(uint32_t)code, g1 = (int)(uint32_t)(code >> 32);
+    const int n0 = g0 & (int)top_bits_to_bytes(t0), n1 = g1 & (int)top_bits_to_bytes(t1);
+#pragma unroll
+    for (int j = 0; j < M; j++) {
+        const uint8_t *xb = xq + ((j < m ? j : 0) * ldx + xb0 + group) * 36;
+        const int x0 = (int)*reinterpret_cast<const uint32_t *>(xb + 4 + 8 * l);
+        const int x1 = (int)*reinterpret_cast<const uint32_t *>(xb + 8 + 8 * l);
+        const float dx = h2f(*reinterpret_cast<const uint16_t *>(xb));
+        const int all = __dp4a(g1, x1, __dp4a(g0, x0, 0)), neg = __dp4a(n1, x1, __dp4a(n0, x0, 0));
+        acc[j] = fmaf(scale * dx, small_int_to_float(all - 2 * neg), acc[j]);   // |.| <= 8*43*127
+    }
+}
+
+// SM: the rows go through the shared-memory rings and (Q8_1 kernels) the activations are staged in shared
+// memory — a compile-time property, so that those reads are shared-memory loads with 32-bit addresses.
+template <int FMT, int M, bool XQ, bool SM>
 __device__ __forceinline__ void gemv_kq_body(const QmKqArgs &a) {
     __shared__ unsigned long long grid[FMT == 16 ? 256 : 1];
     if (FMT == 16) {
@@ -150,16 +227,21 @@ __device__ __forceinline__ void gemv_kq_body(const QmKqArgs &a) {
         }
         wq += (int64_t)e * a.rows * a.units * kBlockBytes;
     }
-    for (int64_t row = wid; row < a.rows; row += warps) {
-        const uint8_t *wr = wq + row * (int64_t)a.units * kBlockBytes;
-        float acc[M];
-#pragma unroll
-        for (int j = 0; j < M; j++) acc[j] = 0.f;
-        const int64_t ldx = a.ldx;
-        for (int u = 0; u < a.units; u++) {
-            if (FMT == 10) q2k_block<M, XQ>(wr + (int64_t)u * kBlockBytes, x, ldx, m, u * 256, lane, acc);
-            else iq2xxs_block<M, XQ>(wr + (int64_t)u * kBlockBytes, x, ldx, m, u * 256, lane, grid, acc);
+    const int64_t row_bytes = (int64_t)a.units * kBlockBytes;
+    extern __shared__ __align__(16) uint8_t dyn_smem[];
+    int xld = (int)a.ldx;
+    if (XQ && SM) {
+        // the CTA's Q8_1 activations go to shared memory once: rows packed units*8 blocks apart
+        const int words = a.units * 8 * 9;
+        for (int idx = threadIdx.x; idx < m * words; idx += blockDim.x) {
+            const int j = idx / words, wd = idx - j * words;
+            reinterpret_cast<uint32_t *>(dyn_smem)[idx] =
+                __ldg(reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(x) + (int64_t)j * a.ldx * 36) + wd);
         }
+        __syncthreads();
+        xld = a.units * 8;
+    }
+    auto finish_row = [&](int64_t row, float (&acc)[M]) {
 #pragma unroll
         for (int j = 0; j < M; j++) {
             float s = acc[j];
@@ -167,6 +249,73 @@ __device__ __forceinline__ void gemv_kq_body(const QmKqArgs &a) {
             for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
             if (lane == 0 && j < m) y[(int64_t)j * a.ldy + row] = s;
         }
+    };
+    // one row's products: wr = the row's super-blocks (shared or global memory)
+    auto row_dot = [&](const uint8_t *wr, float (&acc)[M]) {
+        if (XQ && FMT == 10) {
+            const uint8_t *xq = SM ? dyn_smem : static_cast<const uint8_t *>(x);
+            for (int u = lane >> 4; u < a.units + (lane >> 4); u += 2)   // every lane makes the same number of steps
+                q2k_q81_block<M>(u < a.units ? wr + (int64_t)u * kBlockBytes : nullptr, xq, xld, m, u * 8, lane & 15, acc);
+        } else if (XQ) {
+            const uint8_t *xq = SM ? dyn_smem : static_cast<const uint8_t *>(x);
+            for (int u = 0; u < a.units; u++)
+                iq2xxs_q81_block<M>(wr + (int64_t)u * kBlockBytes, xq, xld, m, u * 8, lane, grid, acc);
+        } else {
+            for (int u = 0; u < a.units; u++) {
+                if (FMT == 10) q2k_block<M, false>(wr + (int64_t)u * kBlockBytes, x, a.ldx, m, u * 256, lane, acc);
+                else iq2xxs_block<M, false>(wr + (int64_t)u * kBlockBytes, x, a.ldx, m, u * 256, lane, grid, acc);
+            }
+        }
+    };
+    if (SM) {
+        // Staged form (rows are whole 16-byte pieces): every warp keeps `depth` rows in flight in a ring of its
+        // own in shared memory, filled by 16-byte cp.async copies, and decodes from there — the bytes in
+        // flight no longer depend on how many scattered loads a lane can have outstanding.
+        const int D = a.depth;
+        const uint32_t stage_bytes = (uint32_t)row_bytes;
+        uint8_t *ring = dyn_smem + (XQ ? a.xs_bytes : 0) + (threadIdx.x >> 5) * D * stage_bytes;
+        const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+        const int pieces = (int)(row_bytes >> 4);
+        int64_t p_row = wid;
+        int p_slot = 0;
+        auto issue = [&]() {
+            if (p_row < a.rows) {
+                const uint8_t *src = wq + p_row * row_bytes;
+                const uint32_t dst = ring_s + (uint32_t)p_slot * stage_bytes;
+                for (int i = lane; i < pieces; i += 32)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * i), "l"(src + 16 * i) : "memory");
+                p_row += warps;
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            p_slot = p_slot + 1 == D ? 0 : p_slot + 1;
+        };
+        for (int d = 0; d < D; d++) issue();
+        int c_slot = 0;
+        for (int64_t row = wid; row < a.rows; row += warps) {
+            // the oldest of the D groups in flight is this row
+            if (D == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else if (D == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
+            else asm volatile("cp.async.wait_group 3;" ::: "memory");
+            __syncwarp();
+            const uint8_t *wr = ring + (size_t)c_slot * stage_bytes;
+            float acc[M];
+#pragma unroll
+            for (int j = 0; j < M; j++) acc[j] = 0.f;
+            row_dot(wr, acc);
+            finish_row(row, acc);
+            __syncwarp();   // every lane has read the slot before the next copy overwrites it
+            issue();
+            c_slot = c_slot + 1 == D ? 0 : c_slot + 1;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    for (int64_t row = wid; !SM && row < a.rows; row += warps) {
+        const uint8_t *wr = wq + row * row_bytes;
+        float acc[M];
+#pragma unroll
+        for (int j = 0; j < M; j++) acc[j] = 0.f;
+        row_dot(wr, acc);
+        finish_row(row, acc);
     }
 }
 
@@ -176,7 +325,8 @@ __device__ __forceinline__ void gemv_kq_body(const QmKqArgs &a) {
 // and for Q8_1 activations.
 #define QM_KQ_KERNEL(name, fmt, mm, xq)                                                                        \
     extern "C" __global__ void __launch_bounds__(256) name(const __grid_constant__ QmKqArgs a) {               \
-        gemv_kq_body<fmt, mm, xq>(a);                                                                          \
+        if (a.depth >= 2) gemv_kq_body<fmt, mm, xq, true>(a);                                                  \
+        else gemv_kq_body<fmt, mm, xq, false>(a);                                                              \
     }
 QM_KQ_KERNEL(qm_gemv_q2k_m1, 10, 1, false)
 QM_KQ_KERNEL(qm_gemv_q2k_m2, 10, 2, false)

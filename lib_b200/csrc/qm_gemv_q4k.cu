@@ -1083,7 +1083,6 @@ template <int CPM, int D, bool TP, bool SEL = false>
 __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     constexpr int C = 16;                       // warps per CTA
     constexpr int NL = CPM == 4 ? 3 : 2;        // limbs per activation row
-    constexpr int NT = 1;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;

@@ -198,6 +198,10 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
+        for (int k = QM_K_GEMV_Q2K_M1; k <= QM_K_GEMV_IQ2XXS_Q81_M8 && !err; k++) {
+            r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_KQ_SMEM_MAX);
+            if (r != CUDA_SUCCESS) err = (int32_t)r;
+        }
         for (int k = QM_K_GEMV_Q40_M4; k <= QM_K_GEMV_Q80_M8 && !err; k++) {
             r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
@@ -800,11 +804,26 @@ int32_t qm_kq_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, bool xq, int3
     const int mi = m <= 1 ? 0 : m <= 2 ? 1 : m <= 4 ? 2 : 3;
     const int k = (w->fmt == QM_FMT_Q2_K ? (xq ? QM_K_GEMV_Q2K_Q81_M1 : QM_K_GEMV_Q2K_M1)
                                          : (xq ? QM_K_GEMV_IQ2XXS_Q81_M1 : QM_K_GEMV_IQ2XXS_M1)) + mi;
-    // eight warps per CTA, one row per warp at a time; enough CTAs to fill every SM eight deep
+    // eight warps per CTA, one row per warp at a time. Rows that are whole 16-byte pieces are streamed through
+    // per-warp rings in shared memory (2..4 rows in flight per warp, at most 96 KB per CTA); other shapes are
+    // read with direct loads.
+    const int64_t row_bytes = (int64_t)w->units * (w->fmt == QM_FMT_Q2_K ? 84 : 66);
+    unsigned smem = 0;
+    if (row_bytes % 16 == 0 && (w->wq & 15) == 0 && qm_env_int("QM_KQ_DIRECT", 0) == 0) {
+        // Q8_1 kernels also keep the activations of the CTA's slot in shared memory
+        const int64_t xs = xq ? ((int64_t)m * w->units * 8 * 36 + 15) & ~(int64_t)15 : 0;
+        const int64_t d = std::min<int64_t>(4, (QM_KQ_SMEM_MAX - xs) / (8 * row_bytes));
+        if (d >= 2) {
+            ka.depth = (int32_t)d;
+            ka.xs_bytes = (int32_t)xs;
+            smem = (unsigned)(xs + 8 * d * row_bytes);
+        }
+    }
+    const int per_sm = smem ? (int)std::max<int64_t>(1, std::min<int64_t>(8, (200 * 1024) / (smem + 3072))) : 8;
     const int64_t want = (ka.rows + 7) / 8;
-    const int64_t cap = std::max<int64_t>(1, (int64_t)c->sm_count * 8 / std::max(1, slots));
+    const int64_t cap = std::max<int64_t>(1, (int64_t)c->sm_count * per_sm / std::max(1, slots));
     const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(want, cap));
-    return qm_launch(c, k, grid, (unsigned)std::max(1, slots), 256, 0, &ka, pdl);
+    return qm_launch(c, k, grid, (unsigned)std::max(1, slots), 256, smem, &ka, pdl);
 }
 
 int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t x2_dev, int32_t m, int64_t ldx,

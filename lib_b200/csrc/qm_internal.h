@@ -28,6 +28,7 @@ enum {
 };
 
 #define QM_GEMV_SMEM_MAX (227 * 1024)
+#define QM_KQ_SMEM_MAX (96 * 1024)   // ring bytes per CTA of the Q2_K / IQ2_XXS GEMV
 #define QM_TICKETS 65536
 #define QM_PARTIALS_BYTES (64ll << 20)
 #define QM_UPLOAD_CHUNK (64ll << 20)

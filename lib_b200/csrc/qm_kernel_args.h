@@ -209,9 +209,11 @@ struct QmKqArgs {
     // selected form (ids != nullptr): blockIdx.y = slot, expert = ids[slot]
     const int32_t *ids;
     int32_t experts;
-    int32_t pad_;
+    int32_t depth;           // >= 2: rows go through a per-warp shared-memory ring of this many stages; 0: direct loads
     int64_t x_slot_stride;   // floats (or blocks) between the activations of consecutive slots; 0: one x for all
     int64_t y_slot_stride;   // floats between the outputs of consecutive slots
+    int32_t xs_bytes;        // _q81 kernels: > 0: shared-memory bytes (a multiple of 16) that hold the CTA's activations
+    int32_t pad_;
 };
 
 // RMSNorm -> Q8_1 (qm_q8_1.cu): row r of x (rows ldx floats apart) into cols/32 blocks of 36 bytes.

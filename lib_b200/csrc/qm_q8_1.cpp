@@ -20,7 +20,7 @@ static int32_t norm_launch(qm_ctx *c, uint64_t x_dev, int64_t ldx, uint64_t weig
     a.ldx = ldx;
     a.cols = (int32_t)cols;
     a.eps = eps;
-    return qm_launch(c, QM_K_RMSNORM_Q81, (unsigned)rows, 1, 256, 0, &a, false);
+    return qm_launch(c, QM_K_RMSNORM_Q81, (unsigned)rows, 1, 1024, 0, &a, false);
 }
 
 // The argument checks of cudaquant.RMSNormQ8_1 (quant.go:47-49) that need no data.
@@ -137,7 +137,8 @@ extern "C" int32_t qm_matvec_q8_1(qm_ctx *c, qm_weight h, uint64_t xq_dev, int32
     CHECK_CTX(c);
     QmWeight *w = qm_weight_from_handle(h);
     if (!w) return QM_ERR_ARG;
-    if (m < 1 || m > 8 || w->cols % 32 != 0 || ldx_blocks < w->cols / 32 || ldy < w->rows) return QM_ERR_SHAPE;
+    if (m < 1 || m > 8 || w->cols % 32 != 0 || ldx_blocks < w->cols / 32 || ldx_blocks > (1 << 22) || ldy < w->rows)
+        return QM_ERR_SHAPE;
     if (!xq_dev || !y_dev || (xq_dev & 3) || (flags & 0xFu) != QM_XOP_NONE) return QM_ERR_ARG;
     CtxGuard g(c);
     DRV(g.rc);
@@ -162,6 +163,7 @@ extern "C" int32_t qm_matvec_selected(qm_ctx *c, qm_weight h, int32_t experts, u
     if (experts < 1 || w->rows % experts != 0 || slots < 1 || slots > 65535 || x_slot_stride < 0) return QM_ERR_SHAPE;
     const bool xq = (flags & QM_FLAG_X_Q8_1) != 0;
     if (x_slot_stride != 0 && x_slot_stride < (xq ? w->cols / 32 : w->cols)) return QM_ERR_SHAPE;
+    if (x_slot_stride > (1ll << 40)) return QM_ERR_SHAPE;
     if (!ids_dev || !x_dev || !y_dev || (ids_dev & 3) || (x_dev & (xq ? 3 : 15)) || (!xq && (x_slot_stride & 3)))
         return QM_ERR_ARG;
     if ((flags & 0xFu) != QM_XOP_NONE) return QM_ERR_ARG;

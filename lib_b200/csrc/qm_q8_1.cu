@@ -5,9 +5,10 @@
 // Replaces the reference's "bounded correctness" producers, which run ONE thread per row
 // (rms_quant_q8_1, nvidia/x/cudaquant/quant.go:129-155) or one thread per block after a
 // 32-thread barrier (fused_swiglu_q8_1, nvidia/x/egraph/codegen.go:513-552):
-//   * qm_rmsnorm_q8_1: one CTA per row; the sum of squares is accumulated in float64 by all
-//     threads and reduced in a fixed order, then every warp turns 32-element blocks into Q8_1,
-//     a lane per element, maxima and quant sums by shuffles. Bytes follow
+//   * qm_rmsnorm_q8_1: one CTA of 1024 threads per row, four neighbouring elements per thread;
+//     the sum of squares is accumulated in float64 by all threads and reduced in a fixed order,
+//     then every group of eight lanes turns its 32-element block into Q8_1 (maxima and quant
+//     sums by shuffles), from registers when the row has at most 4096 columns. Bytes follow
 //     cudaquant.RMSNormQ8_1 (quant.go:46-118): inv = float32(1/sqrt(ss/cols + eps)),
 //     v = x*inv (*weight), qscale = max|v|/127, d = fp16(qscale), q = round-half-away(v/qscale)
 //     clamped to +-127, s = fp16(float32(sum q) * qscale). The float64 sum is added in a
@@ -41,20 +42,36 @@ __device__ __forceinline__ void store_block(uint8_t *dst, uint32_t head, int q, 
 
 }  // namespace
 
-extern "C" __global__ void __launch_bounds__(256) qm_rmsnorm_q8_1(const __grid_constant__ QmNormQ81Args a) {
-    __shared__ double part[8];
+// One CTA of 1024 threads per row: thread t owns elements 4t..4t+3 of every 4096-column chunk, so a block of 32
+// elements lies in eight neighbouring lanes and a row of up to 4096 columns is read from memory once.
+extern "C" __global__ void __launch_bounds__(1024) qm_rmsnorm_q8_1(const __grid_constant__ QmNormQ81Args a) {
+    __shared__ double part[32];
     __shared__ int bad;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t r = blockIdx.x;
     const float *in = a.x + r * a.ldx;
+    const bool vec = ((reinterpret_cast<uintptr_t>(in) | (a.weight ? reinterpret_cast<uintptr_t>(a.weight) : 0)) & 15) == 0;
+    auto load4 = [&](const float *p, int c) {
+        if (vec) return *reinterpret_cast<const float4 *>(p + c);
+        return make_float4(p[c], p[c + 1], p[c + 2], p[c + 3]);
+    };
     if (tid == 0) bad = 0;
     double ss = 0.0;
     bool nonfinite = false;
-    for (int c = tid; c < a.cols; c += 256) {
-        const float v = in[c];
-        nonfinite |= !isfinite(v);
-        if (a.weight && r == 0) nonfinite |= !isfinite(a.weight[c]);
-        ss = fma((double)v, (double)v, ss);   // the square is exact in float64: one rounding, as a separate add has
+    float4 keep = make_float4(0.f, 0.f, 0.f, 0.f);   // the row's first chunk stays in registers
+    for (int c = 4 * tid; c < a.cols; c += 4096) {
+        const float4 v = load4(in, c);
+        if (c < 4096) keep = v;
+        nonfinite |= !(isfinite(v.x) && isfinite(v.y) && isfinite(v.z) && isfinite(v.w));
+        if (a.weight && r == 0) {
+            const float4 w = load4(a.weight, c);
+            nonfinite |= !(isfinite(w.x) && isfinite(w.y) && isfinite(w.z) && isfinite(w.w));
+        }
+        // every square is exact in float64, so each fma rounds once, as a separate add would
+        ss = fma((double)v.x, (double)v.x, ss);
+        ss = fma((double)v.y, (double)v.y, ss);
+        ss = fma((double)v.z, (double)v.z, ss);
+        ss = fma((double)v.w, (double)v.w, ss);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -62,32 +79,43 @@ extern "C" __global__ void __launch_bounds__(256) qm_rmsnorm_q8_1(const __grid_c
     if (lane == 0) part[warp] = ss;
     if (nonfinite) bad = 1;
     __syncthreads();
-    double tot = 0.0;
+    double tot = part[lane];
 #pragma unroll
-    for (int w = 0; w < 8; w++) tot += part[w];
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     const double denom = tot / (double)a.cols + (double)a.eps;
     bool domain = bad != 0 || denom == 0.0;
     const float inv = (float)(1.0 / sqrt(denom));
     uint8_t *out = a.out + r * (int64_t)(a.cols / 32) * 36;
-    for (int b = warp; b < a.cols / 32; b += 8) {
-        const int c = b * 32 + lane;
-        float v = in[c] * inv;
-        if (a.weight) v *= a.weight[c];
-        domain |= !isfinite(v);
-        float mx = fabsf(v);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        const float qscale = mx / 127.f;
-        int q = 0;
-        if (qscale != 0.f) {
-            const float t = roundf(v / qscale);
-            q = t > 127.f ? 127 : t < -127.f ? -127 : (int)t;   // also maps a NaN to a definite value
+    for (int c = 4 * tid; c < a.cols; c += 4096) {
+        const float4 x = c < 4096 ? keep : load4(in, c);
+        float v[4] = {x.x * inv, x.y * inv, x.z * inv, x.w * inv};
+        if (a.weight) {
+            const float4 w = load4(a.weight, c);
+            v[0] *= w.x; v[1] *= w.y; v[2] *= w.z; v[3] *= w.w;
         }
-        int sum = q;
+        domain |= !(isfinite(v[0]) && isfinite(v[1]) && isfinite(v[2]) && isfinite(v[3]));
+        // the block's eight lanes are all here or all absent (cols is a multiple of 32); other lanes of the warp may be absent
+        const uint32_t grp = 0xFFu << (lane & 24);
+        float mx = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        const uint32_t head = f2h(qscale) | (qscale != 0.f ? f2h((float)sum * qscale) << 16 : 0u);
-        store_block(out + (int64_t)b * 36, head, q, lane);
+        for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(grp, mx, o));
+        const float qscale = mx / 127.f;
+        uint32_t word = 0;
+        int sum = 0;
+        if (qscale != 0.f) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float t = roundf(v[i] / qscale);
+                const int q = t > 127.f ? 127 : t < -127.f ? -127 : (int)t;   // also maps a NaN to a definite value
+                sum += q;
+                word |= ((uint32_t)q & 0xFFu) << (8 * i);
+            }
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(grp, sum, o);
+        uint32_t *dst = reinterpret_cast<uint32_t *>(out + (int64_t)(c >> 5) * 36);
+        if ((lane & 7) == 0) dst[0] = f2h(qscale) | (qscale != 0.f ? f2h((float)sum * qscale) << 16 : 0u);
+        dst[1 + (lane & 7)] = word;
     }
     if (domain) atomicOr(a.status, QM_STATUS_DOMAIN);
 }

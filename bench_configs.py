@@ -254,9 +254,10 @@ def q8_1_producer_case(ctx, rows, cols, iters):
             "note": "latency-bound: %d bytes in, %d out" % (rows * cols * 4, rows * cols // 32 * 36)}
 
 
-def moe_ep_case(tokens_total, iters, hidden=4096, ffn=14336, experts=8, topk=2):
+def moe_ep_case(tokens_total, iters, hidden=4096, ffn=14336, experts=8, topk=2, exchange="peer"):
     """Config 5 across the ranks of a torchrun launch: experts sharded by index, the batch of
-    `tokens_total` tokens split evenly, rows exchanged by NCCL all-to-all (lib_b200.moe)."""
+    `tokens_total` tokens split evenly, rows exchanged through peer memory behind the C ABI
+    (qm_ep_*, the default) or by NCCL all-to-all (lib_b200.moe, --exchange nccl)."""
     import torch.distributed as dist
     from lib_b200 import moe
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -265,21 +266,28 @@ def moe_ep_case(tokens_total, iters, hidden=4096, ffn=14336, experts=8, topk=2):
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     ctx = lib_b200.Context(local)
-    layer = moe.MoELayer(ctx, experts, topk, hidden, ffn, 5, rank, world)
     tokens = tokens_total // world
+    if exchange == "peer":
+        layer = moe.PeerExpertParallelLayer(ctx, experts, topk, hidden, ffn, 5, tokens, rank, world)
+    else:
+        layer = moe.MoELayer(ctx, experts, topk, hidden, ffn, 5, rank, world)
     x = torch.from_numpy(synth.activations(tokens, hidden, 40 + rank)).to(dev).to(torch.bfloat16)
     lg = torch.from_numpy(synth.activations(tokens, experts, 60 + rank)).to(dev)
-    for _ in range(3):
-        layer.forward(x, lg)
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        layer.forward(x, lg)
-    e1.record()
-    torch.cuda.synchronize()
+    # a stream of its own: the library takes stream handle 0 to mean its private stream, which the events
+    # of torch's default stream would not see
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for _ in range(3):
+            layer.forward(x, lg)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(iters):
+            layer.forward(x, lg)
+        e1.record(st)
+        torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
@@ -288,7 +296,8 @@ def moe_ep_case(tokens_total, iters, hidden=4096, ffn=14336, experts=8, topk=2):
             "tokens": tokens * world, "hidden": hidden, "ffn": ffn, "ms": round(ms, 3),
             "tokens_per_s": round(tokens * world / (ms * 1e-3)), "status": [rc, status],
             "TFLOPs": round(2.0 * tokens * world * topk * 3 * hidden * ffn / (ms * 1e-3) / 1e12, 1),
-            "exchange": "NCCL all_to_all_single (bf16 rows out, fp32 rows back)", "scaling": "strong"}
+            "exchange": "peer stores behind the C ABI (qm_ep_moe: bf16 rows out, fp32 rows back, flags)" if exchange == "peer"
+            else "NCCL all_to_all_single (bf16 rows out, fp32 rows back)", "scaling": "strong"}
     if rank == 0:
         print(json.dumps(line), flush=True)
     dist.barrier()
@@ -305,9 +314,10 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tokens", type=int, default=512)
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--exchange", choices=("peer", "nccl"), default="peer", help="config 5 on several GPUs")
     a = ap.parse_args()
     if a.config == 5 and int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        moe_ep_case(a.tokens, max(3, a.iters // 4))
+        moe_ep_case(a.tokens, max(3, a.iters // 4), exchange=a.exchange)
         return
     ctx = lib_b200.Context(0)
     torch.cuda.init()

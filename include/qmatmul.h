@@ -251,6 +251,40 @@ QM_API int32_t qm_moe_decode_run(qm_ctx *ctx, qm_moe_decode *md, uint64_t x_dev,
                                  uint64_t ids_dev, uint64_t weights_dev, uint64_t out_dev, int64_t ldo);
 QM_API int32_t qm_moe_decode_destroy(qm_ctx *ctx, qm_moe_decode *md);
 
+/* Expert-parallel MoE layer behind the C ABI: rank `rank` of `world` (<= 8, one rank per GPU) owns
+ * experts [rank*experts_local, (rank+1)*experts_local) of experts_total and calls qm_ep_moe with
+ * its own tokens; the routed rows travel to the ranks that own their experts and the results back
+ * through peer memory (plain stores into the peers' arenas, one flag per rank and direction, every
+ * wait bounded: QM_ERR_TIMEOUT from qm_last_status) — no collective library is involved. The
+ * reference's model for such an exchange is ncclGroupStart + ncclSend/ncclRecv pairs
+ * (nvidia/nccl/comm.gen.go:401,288; nvidia/x/nccltest/run.go:595-603).
+ * Set-up mirrors the tensor-parallel stack: qm_ep_create on every rank (max_tokens = the most
+ * tokens ANY rank passes in one step; it sizes the arena: world * max_tokens * topk rows in both
+ * directions), then either qm_ep_ipc_handle + exchange of the 64-byte handles + qm_ep_set_peers
+ * (one process per GPU) or qm_ep_arena + qm_ep_set_peer_pointers (one process, peer access
+ * enabled by the caller). world == 1 needs neither.
+ * A step: x bf16 [tokens][ldx], ids int32 and weights float32 [tokens][topk] as qm_moe_route
+ * writes them (ids outside [0, experts_total) contribute nothing), out float32 [tokens][ldo].
+ * Every rank must run the same number of steps, also with zero tokens. qm_ep_moe is
+ * qm_ep_begin (lists + push) + qm_ep_run (collect, grouped expert matmuls, return) + qm_ep_end
+ * (combine); a process that drives several ranks calls each phase for all its ranks before the
+ * next phase. Asynchronous on the context's stream. */
+typedef struct qm_ep qm_ep;
+QM_API int32_t qm_ep_create(qm_ctx *ctx, const qm_weight *gate_up, const qm_weight *down, int32_t experts_local,
+                            int32_t experts_total, int32_t topk, int32_t max_tokens, int32_t rank, int32_t world,
+                            qm_ep **out);
+QM_API int32_t qm_ep_arena(qm_ctx *ctx, qm_ep *ep, uint64_t *base, int64_t *bytes);
+QM_API int32_t qm_ep_ipc_handle(qm_ctx *ctx, qm_ep *ep, void *handle64);
+QM_API int32_t qm_ep_set_peers(qm_ctx *ctx, qm_ep *ep, const void *handles /* world x 64 bytes */);
+QM_API int32_t qm_ep_set_peer_pointers(qm_ctx *ctx, qm_ep *ep, const uint64_t *bases /* [world] */);
+QM_API int32_t qm_ep_moe(qm_ctx *ctx, qm_ep *ep, uint64_t x_bf16_dev, int32_t tokens, int64_t ldx, uint64_t ids_dev,
+                         uint64_t weights_dev, uint64_t out_dev, int64_t ldo);
+QM_API int32_t qm_ep_begin(qm_ctx *ctx, qm_ep *ep, uint64_t x_bf16_dev, int32_t tokens, int64_t ldx, uint64_t ids_dev,
+                           uint64_t weights_dev, uint64_t out_dev, int64_t ldo);
+QM_API int32_t qm_ep_run(qm_ctx *ctx, qm_ep *ep);
+QM_API int32_t qm_ep_end(qm_ctx *ctx, qm_ep *ep);
+QM_API int32_t qm_ep_destroy(qm_ctx *ctx, qm_ep *ep);
+
 /* No counterpart in the reference. The Q4_0 / Q8_0 matvec of qm_matvec for callers that may
  * not allocate device memory at the point of the call: a server whose memory plan is frozen
  * once it starts serving, a latency-critical loop where an allocation would stall the device,

@@ -59,6 +59,16 @@ def _load():
         "qm_moe_experts": (i32, [p, p, p, i32, u64, p, u64]),
         "qm_moe_combine": (i32, [p, u64, u64, u64, i32, i32, i32, u64, i64]),
         "qm_matvec_noalloc": (i32, [u64, u64, i32, i64, u64, i64, u64]),
+        "qm_ep_create": (i32, [p, p, p, i32, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
+        "qm_ep_arena": (i32, [p, p, ctypes.POINTER(u64), ctypes.POINTER(i64)]),
+        "qm_ep_ipc_handle": (i32, [p, p, p]),
+        "qm_ep_set_peers": (i32, [p, p, p]),
+        "qm_ep_set_peer_pointers": (i32, [p, p, ctypes.POINTER(u64)]),
+        "qm_ep_moe": (i32, [p, p, u64, i32, i64, u64, u64, u64, i64]),
+        "qm_ep_begin": (i32, [p, p, u64, i32, i64, u64, u64, u64, i64]),
+        "qm_ep_run": (i32, [p, p]),
+        "qm_ep_end": (i32, [p, p]),
+        "qm_ep_destroy": (i32, [p, p]),
         "qm_moe_decode_create": (i32, [p, p, p, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_moe_decode_run": (i32, [p, p, u64, i32, i64, u64, u64, u64, i64]),
         "qm_moe_decode_destroy": (i32, [p, p]),
@@ -351,6 +361,54 @@ class Context:
         _check(lib.qm_matvec_host(self._h, w.handle, x2.ctypes.data, m, x2.shape[1], y.ctypes.data,
                                   y.shape[-1], flags), "matvec")
         return y[0] if (x.ndim == 1 and out is None) else y
+
+
+class ExpertParallel:
+    """qm_ep: one rank's share of an expert-parallel MoE layer, the exchange over peer memory."""
+
+    def __init__(self, ctx, gate_up, down, experts_total, topk, max_tokens, rank=0, world=1):
+        self.ctx, self.rank, self.world = ctx, rank, world
+        n = len(gate_up)
+        ga = (ctypes.c_uint64 * n)(*[w.handle for w in gate_up])
+        da = (ctypes.c_uint64 * n)(*[w.handle for w in down])
+        h = ctypes.c_void_p()
+        _check(lib.qm_ep_create(ctx._h, ga, da, n, experts_total, topk, max_tokens, rank, world, ctypes.byref(h)), "ep_create")
+        self._h = h
+
+    def arena(self):
+        base, nbytes = ctypes.c_uint64(0), ctypes.c_int64(0)
+        _check(lib.qm_ep_arena(self.ctx._h, self._h, ctypes.byref(base), ctypes.byref(nbytes)), "ep_arena")
+        return base.value, nbytes.value
+
+    def ipc_handle(self):
+        buf = ctypes.create_string_buffer(64)
+        _check(lib.qm_ep_ipc_handle(self.ctx._h, self._h, buf), "ep_ipc_handle")
+        return buf.raw
+
+    def set_peers(self, handles):
+        blob = b"".join(handles)
+        _check(lib.qm_ep_set_peers(self.ctx._h, self._h, blob), "ep_set_peers")
+
+    def set_peer_pointers(self, bases):
+        arr = (ctypes.c_uint64 * len(bases))(*bases)
+        _check(lib.qm_ep_set_peer_pointers(self.ctx._h, self._h, arr), "ep_set_peer_pointers")
+
+    def moe(self, x_dev, tokens, ldx, ids_dev, weights_dev, out_dev, ldo):
+        _check(lib.qm_ep_moe(self.ctx._h, self._h, x_dev, tokens, ldx, ids_dev, weights_dev, out_dev, ldo), "ep_moe")
+
+    def begin(self, x_dev, tokens, ldx, ids_dev, weights_dev, out_dev, ldo):
+        _check(lib.qm_ep_begin(self.ctx._h, self._h, x_dev, tokens, ldx, ids_dev, weights_dev, out_dev, ldo), "ep_begin")
+
+    def run(self):
+        _check(lib.qm_ep_run(self.ctx._h, self._h), "ep_run")
+
+    def end(self):
+        _check(lib.qm_ep_end(self.ctx._h, self._h), "ep_end")
+
+    def close(self):
+        if self._h:
+            lib.qm_ep_destroy(self.ctx._h, self._h)
+            self._h = None
 
 
 class Stack:

@@ -104,6 +104,8 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_Q81, "qm_rmsnorm_q8_1"},   {QM_MOD_Q81, "qm_swiglu_q8_1"},    {QM_MOD_Q81, "qm_q8_1_expand"},
     {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d2_sel"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d3_sel"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_c4d4_sel"},
     {QM_MOD_MOE, "qm_moe_decode_combine"},
+    {QM_MOD_MOE, "qm_ep_push"},        {QM_MOD_MOE, "qm_ep_collect"},     {QM_MOD_MOE, "qm_ep_return"},
+    {QM_MOD_MOE, "qm_ep_combine"},
 };
 
 // ---- errors --------------------------------------------------------------------------

@@ -253,6 +253,38 @@ struct QmDecodeCombineArgs {
     int32_t tokens, topk, experts, hidden;
 };
 
+// Expert-parallel MoE over peer memory (qm_ep_* kernels in qm_moe.cu). Every rank owns `eloc` consecutive
+// experts and an arena of the same layout; a rank stores into the arenas of its peers (its own address plus
+// peer_delta[p]) and reads only its own.
+struct QmEpArgs {
+    // this rank's step
+    const uint16_t *x;        // bf16 tokens [tokens][ldx]
+    const int32_t *ids;       // [tokens*topk] global expert of every (token, slot) pair
+    const int32_t *list;      // pairs grouped by global expert (qm_moe_lists)
+    const int32_t *offsets;   // [experts + 1] starts of those groups
+    const int32_t *pos;       // [tokens*topk] place of every pair in the grouping, -1: none
+    const float *weights;     // [tokens*topk]
+    float *out;               // [tokens][ldo]
+    int64_t ldx, ldo;
+    // this rank as an owner of experts
+    uint16_t *compact;        // [world*cap][hidden] bf16: the rows received, grouped by local expert
+    int32_t *back;            // [world*cap] source rank << 24 | place in that rank's segment, per compact row
+    int32_t *loff;            // [eloc + 1] starts of the local experts' groups in `compact`
+    const float *y;           // [world*cap][hidden] outputs of the experts, in `compact` order
+    unsigned int *done;       // [2] CTA arrival counters (push, return), zero at the start of a step
+    unsigned int *status;
+    // the arena
+    unsigned int *flags;      // [2][QM_MAX_PEERS] epochs: [0][s] rank s has pushed its rows, [1][o] owner o has returned its results
+    int32_t *counts_in;       // [world][eloc] rows from rank s for local expert e
+    uint16_t *rows_in;        // [world][cap][hidden] bf16 rows from rank s, grouped by local expert
+    float *ret_in;            // [world][cap][hidden] results from owner o for the rows this rank sent it, in sending order
+    int64_t peer_delta[QM_MAX_PEERS];
+    int32_t tokens, topk, hidden, experts, eloc, world, rank, cap;
+    unsigned int epoch;
+    int32_t pad_;
+    int64_t wait_cycles;
+};
+
 // h[j][r] = c_j * sum over parts of parts[k*part_stride + j*ld_in + r], c_j = rsqrt(mean square + eps)
 // from the per-part sums of squares ssq[k*8 + j] (qm_sum_parts: the last matvec of a step that ran in K parts).
 struct QmSumPartsArgs {

@@ -464,3 +464,272 @@ extern "C" int32_t qm_moe_decode_run(qm_ctx *c, qm_moe_decode *d, uint64_t x_dev
     return qm_launch(c, QM_K_MOE_DECODE_COMBINE, grid_for((int64_t)tokens * d->hidden, 256, c->sm_count * 4), 1, 256, 0,
                      &ca, false);
 }
+
+// ---- expert parallelism behind the C ABI ------------------------------------------------------------
+// Rank r of `world` owns experts [r*eloc, (r+1)*eloc). A step moves the routed rows to their owners and the
+// results back through peer memory (the kernels of qm_moe.cu, qm_ep_*), so a caller needs no collective
+// library for it: the ranks exchange one 64-byte IPC handle each at set-up (or, in one process, plain
+// pointers), as for the tensor-parallel decode stack. Every rank must run the same number of steps.
+struct qm_ep {
+    uint32_t magic;
+    int eloc, experts, topk, max_tokens, cap, rank, world;
+    int64_t hidden, ffn;
+    std::vector<QmWeight *> wg, wd;
+    CUdeviceptr arena;          // flags | counts_in | rows_in | ret_in (the part the peers write)
+    int64_t arena_bytes, o_flags, o_counts, o_rows, o_ret;
+    CUdeviceptr local;          // lists | compact | back | loff | y | done
+    int64_t o_rankbuf, o_lcounts, o_offsets, o_list, o_pos, o_compact, o_back, o_loff, o_y, o_done;
+    CUdeviceptr peer_base[QM_MAX_PEERS];
+    bool peers_open, peers_ipc;
+    unsigned int epoch;
+    // the step in flight between begin and end
+    QmEpArgs step;
+    int phase;                  // 0: idle, 1: after begin, 2: after run
+};
+#define QM_EP_MAGIC 0x514D4550u   // "QMEP"
+
+static bool ep_check(qm_ep *e) { return e && e->magic == QM_EP_MAGIC; }
+
+extern "C" int32_t qm_ep_destroy(qm_ctx *c, qm_ep *e) {
+    CHECK_CTX(c);
+    if (!ep_check(e)) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    c->drv->cuStreamSynchronize(c->stream);
+    if (e->peers_open && e->peers_ipc)
+        for (int p = 0; p < e->world; p++)
+            if (p != e->rank && e->peer_base[p]) c->drv->cuIpcCloseMemHandle(e->peer_base[p]);
+    if (e->arena) c->drv->cuMemFree_v2(e->arena);
+    if (e->local) c->drv->cuMemFree_v2(e->local);
+    e->magic = 0;
+    delete e;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_ep_create(qm_ctx *c, const qm_weight *gate_up, const qm_weight *down, int32_t experts_local,
+                                int32_t experts_total, int32_t topk, int32_t max_tokens, int32_t rank, int32_t world,
+                                qm_ep **out) {
+    CHECK_CTX(c);
+    if (!out) return QM_ERR_ARG;
+    *out = nullptr;
+    if (world < 1 || world > QM_MAX_PEERS || rank < 0 || rank >= world || experts_local < 1 || experts_local > 64 ||
+        experts_total != experts_local * world || experts_total > 64 || topk < 1 || topk > experts_total ||
+        max_tokens < 1 || (int64_t)max_tokens * topk >= (1 << 20))
+        return QM_ERR_SHAPE;
+    qm_ep *e = new (std::nothrow) qm_ep();
+    if (!e) return QM_ERR_NOMEM;
+    int32_t rc = check_experts(gate_up, down, experts_local, e->wg, e->wd, &e->hidden, &e->ffn);
+    if (!rc && (e->ffn & 127)) rc = QM_ERR_SHAPE;   // the SwiGLU epilogue of the grouped matmul: whole 128-row tiles
+    if (rc) {
+        delete e;
+        return rc;
+    }
+    e->magic = QM_EP_MAGIC;
+    e->eloc = experts_local;
+    e->experts = experts_total;
+    e->topk = topk;
+    e->max_tokens = max_tokens;
+    e->cap = max_tokens * topk;
+    e->rank = rank;
+    e->world = world;
+    e->epoch = 0;
+    e->phase = 0;
+    e->peers_open = world == 1;
+    e->peers_ipc = false;
+    memset(e->peer_base, 0, sizeof e->peer_base);
+    const int64_t cap = e->cap, H = e->hidden, W = world;
+    e->o_flags = 0;
+    e->o_counts = 256;
+    e->o_rows = up256(e->o_counts + W * experts_local * 4);
+    e->o_ret = up256(e->o_rows + W * cap * H * 2);
+    e->arena_bytes = up256(e->o_ret + W * cap * H * 4);
+    int64_t o = 0;
+    auto take = [&](int64_t bytes) { const int64_t at = o; o = up256(o + bytes); return at; };
+    e->o_rankbuf = take(cap * 4);
+    e->o_lcounts = take(64 * 4);
+    e->o_offsets = take(65 * 4);
+    e->o_list = take(cap * 4);
+    e->o_pos = take(cap * 4);
+    e->o_compact = take(W * cap * H * 2);
+    e->o_back = take(W * cap * 4);
+    e->o_loff = take(65 * 4);
+    e->o_y = take(W * cap * H * 4);
+    e->o_done = take(256);
+    CtxGuard g(c);
+    CUresult r = g.rc;
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&e->arena, (size_t)e->arena_bytes);
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemsetD8Async(e->arena, 0, (size_t)e->o_rows, c->stream);   // flags and counts
+    if (r == CUDA_SUCCESS) r = c->drv->cuMemAlloc_v2(&e->local, (size_t)o);
+    if (r == CUDA_SUCCESS) r = c->drv->cuStreamSynchronize(c->stream);
+    if (r != CUDA_SUCCESS) {
+        if (e->arena) c->drv->cuMemFree_v2(e->arena);
+        if (e->local) c->drv->cuMemFree_v2(e->local);
+        delete e;
+        return (int32_t)r;
+    }
+    e->peer_base[rank] = e->arena;
+    *out = e;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_ep_arena(qm_ctx *c, qm_ep *e, uint64_t *base, int64_t *bytes) {
+    CHECK_CTX(c);
+    if (!ep_check(e) || !base || !bytes) return QM_ERR_ARG;
+    *base = (uint64_t)e->arena;
+    *bytes = e->arena_bytes;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_ep_ipc_handle(qm_ctx *c, qm_ep *e, void *handle64) {
+    CHECK_CTX(c);
+    if (!ep_check(e) || !handle64) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    CUipcMemHandle h;
+    DRV(c->drv->cuIpcGetMemHandle(&h, e->arena));
+    memcpy(handle64, &h, 64);
+    return QM_OK;
+}
+
+extern "C" int32_t qm_ep_set_peers(qm_ctx *c, qm_ep *e, const void *handles) {
+    CHECK_CTX(c);
+    if (!ep_check(e) || !handles || e->world < 2 || e->peers_open) return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    for (int p = 0; p < e->world; p++) {
+        if (p == e->rank) continue;
+        CUipcMemHandle h;
+        memcpy(&h, (const char *)handles + (size_t)p * 64, 64);
+        CUresult r = c->drv->cuIpcOpenMemHandle_v2(&e->peer_base[p], h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS);
+        if (r != CUDA_SUCCESS) {
+            for (int q = 0; q < p; q++)
+                if (q != e->rank && e->peer_base[q]) {
+                    c->drv->cuIpcCloseMemHandle(e->peer_base[q]);
+                    e->peer_base[q] = 0;
+                }
+            return (int32_t)r;
+        }
+    }
+    e->peers_open = true;
+    e->peers_ipc = true;
+    return QM_OK;
+}
+
+extern "C" int32_t qm_ep_set_peer_pointers(qm_ctx *c, qm_ep *e, const uint64_t *bases) {
+    CHECK_CTX(c);
+    if (!ep_check(e) || !bases || e->world < 2 || e->peers_open) return QM_ERR_ARG;
+    for (int p = 0; p < e->world; p++) {
+        if (p != e->rank && !bases[p]) return QM_ERR_ARG;
+        if (p != e->rank) e->peer_base[p] = (CUdeviceptr)bases[p];
+    }
+    e->peers_open = true;
+    e->peers_ipc = false;
+    return QM_OK;
+}
+
+static unsigned ep_grid(qm_ctx *c, int64_t rows) {
+    return (unsigned)std::max<int64_t>(1, std::min<int64_t>((rows + 7) / 8, (int64_t)c->sm_count * 4));
+}
+
+// begin: lists of this rank's pairs by global expert, rows pushed to their owners.
+extern "C" int32_t qm_ep_begin(qm_ctx *c, qm_ep *e, uint64_t x_bf16_dev, int32_t tokens, int64_t ldx, uint64_t ids_dev,
+                               uint64_t weights_dev, uint64_t out_dev, int64_t ldo) {
+    CHECK_CTX(c);
+    if (!ep_check(e)) return QM_ERR_ARG;
+    if (!e->peers_open || e->phase != 0) return QM_ERR_STATE;
+    if (tokens < 0 || tokens > e->max_tokens || ldx < e->hidden || ldo < e->hidden || ((ldx * 2) & 15)) return QM_ERR_SHAPE;
+    if (tokens > 0 && (!x_bf16_dev || !ids_dev || !weights_dev || !out_dev || (x_bf16_dev & 15) || (ids_dev & 3)))
+        return QM_ERR_ARG;
+    CtxGuard g(c);
+    DRV(g.rc);
+    e->epoch += 1;
+    QmEpArgs &a = e->step;
+    memset(&a, 0, sizeof a);
+    const CUdeviceptr L = e->local, A = e->arena;
+    a.x = (const uint16_t *)(uintptr_t)x_bf16_dev;
+    a.ids = (const int32_t *)(uintptr_t)ids_dev;
+    a.list = (const int32_t *)(uintptr_t)(L + e->o_list);
+    a.offsets = (const int32_t *)(uintptr_t)(L + e->o_offsets);
+    a.pos = (const int32_t *)(uintptr_t)(L + e->o_pos);
+    a.weights = (const float *)(uintptr_t)weights_dev;
+    a.out = (float *)(uintptr_t)out_dev;
+    a.ldx = ldx;
+    a.ldo = ldo;
+    a.compact = (uint16_t *)(uintptr_t)(L + e->o_compact);
+    a.back = (int32_t *)(uintptr_t)(L + e->o_back);
+    a.loff = (int32_t *)(uintptr_t)(L + e->o_loff);
+    a.y = (const float *)(uintptr_t)(L + e->o_y);
+    a.done = (unsigned int *)(uintptr_t)(L + e->o_done);
+    a.status = (unsigned int *)(uintptr_t)c->status_dev;
+    a.flags = (unsigned int *)(uintptr_t)(A + e->o_flags);
+    a.counts_in = (int32_t *)(uintptr_t)(A + e->o_counts);
+    a.rows_in = (uint16_t *)(uintptr_t)(A + e->o_rows);
+    a.ret_in = (float *)(uintptr_t)(A + e->o_ret);
+    for (int p = 0; p < e->world; p++) a.peer_delta[p] = (int64_t)e->peer_base[p] - (int64_t)A;
+    a.tokens = tokens;
+    a.topk = e->topk;
+    a.hidden = (int32_t)e->hidden;
+    a.experts = e->experts;
+    a.eloc = e->eloc;
+    a.world = e->world;
+    a.rank = e->rank;
+    a.cap = e->cap;
+    a.epoch = e->epoch;
+    a.wait_cycles = qm_wait_cycles();
+    DRV(c->drv->cuMemsetD32Async(L + e->o_done, 0, 2, c->stream));
+    QmListArgs la;
+    memset(&la, 0, sizeof la);
+    la.ids = a.ids;
+    la.rank = (int32_t *)(uintptr_t)(L + e->o_rankbuf);
+    la.counts = (int32_t *)(uintptr_t)(L + e->o_lcounts);
+    la.offsets = (int32_t *)(uintptr_t)(L + e->o_offsets);
+    la.list = (int32_t *)(uintptr_t)(L + e->o_list);
+    la.pos = (int32_t *)(uintptr_t)(L + e->o_pos);
+    la.tokens = tokens;
+    la.experts = e->experts;
+    la.topk = e->topk;
+    int32_t rc = qm_launch(c, QM_K_MOE_LISTS, 1, 1, 1024, 0, &la, false);
+    if (!rc) rc = qm_launch(c, QM_K_EP_PUSH, ep_grid(c, (int64_t)tokens * e->topk), 1, 256, 0, &a, false);
+    if (!rc) e->phase = 1;
+    return rc;
+}
+
+// run: what the other ranks pushed is regrouped by local expert, multiplied, and sent back.
+extern "C" int32_t qm_ep_run(qm_ctx *c, qm_ep *e) {
+    CHECK_CTX(c);
+    if (!ep_check(e)) return QM_ERR_ARG;
+    if (e->phase != 1) return QM_ERR_STATE;
+    CtxGuard g(c);
+    DRV(g.rc);
+    QmEpArgs &a = e->step;
+    const int64_t bound = (int64_t)e->world * e->cap;   // rows this rank can receive
+    int32_t rc = qm_launch(c, QM_K_EP_COLLECT, ep_grid(c, bound), 1, 256, 0, &a, false);
+    if (rc) return rc;
+    const int typical = (int)std::max<int64_t>(1, bound / e->experts);
+    rc = experts_launch(c, e->wg, e->wd, e->eloc, e->local + e->o_compact, bound, (int32_t)bound, typical,
+                        e->local + e->o_loff, e->local + e->o_y, e->hidden, e->ffn);
+    if (rc) return rc;
+    rc = qm_launch(c, QM_K_EP_RETURN, ep_grid(c, bound), 1, 256, 0, &a, false);
+    if (!rc) e->phase = 2;
+    return rc;
+}
+
+// end: the results that came back are combined with the routing weights.
+extern "C" int32_t qm_ep_end(qm_ctx *c, qm_ep *e) {
+    CHECK_CTX(c);
+    if (!ep_check(e)) return QM_ERR_ARG;
+    if (e->phase != 2) return QM_ERR_STATE;
+    CtxGuard g(c);
+    DRV(g.rc);
+    e->phase = 0;
+    return qm_launch(c, QM_K_EP_COMBINE, grid_for((int64_t)std::max(1, e->step.tokens) * e->hidden, 256, c->sm_count * 8),
+                     1, 256, 0, &e->step, false);
+}
+
+extern "C" int32_t qm_ep_moe(qm_ctx *c, qm_ep *e, uint64_t x_bf16_dev, int32_t tokens, int64_t ldx, uint64_t ids_dev,
+                             uint64_t weights_dev, uint64_t out_dev, int64_t ldo) {
+    int32_t rc = qm_ep_begin(c, e, x_bf16_dev, tokens, ldx, ids_dev, weights_dev, out_dev, ldo);
+    if (!rc) rc = qm_ep_run(c, e);
+    if (!rc) rc = qm_ep_end(c, e);
+    return rc;
+}

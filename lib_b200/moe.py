@@ -152,6 +152,36 @@ class MoELayer:
         self.gate_up, self.down = [], []
 
 
+class PeerExpertParallelLayer(MoELayer):
+    """The same layer with the exchange behind the C ABI (qm_ep_*): routed rows and results travel through
+    peer memory, no collective library on the data path. `group` (any torch.distributed backend) is used
+    once, at set-up, to hand the 64-byte IPC handles of the arenas around."""
+
+    def __init__(self, ctx, experts, topk, hidden, ffn, seed, max_tokens, rank=0, world=1, group=None):
+        super().__init__(ctx, experts, topk, hidden, ffn, seed, rank, world, group)
+        from ._capi import ExpertParallel
+        self.ep = ExpertParallel(ctx, self.gate_up, self.down, experts, topk, max_tokens, rank, world)
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, self.ep.ipc_handle(), group=group)
+            self.ep.set_peers(handles)
+            dist.barrier(group=group)       # every rank has mapped its peers before any rank runs a step
+
+    def forward(self, x, logits):
+        self.ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        ids, w = self.route(logits)
+        tokens = x.shape[0]
+        out = torch.empty((max(tokens, 1), self.hidden), dtype=torch.float32, device=x.device)
+        self.ep.moe(x.data_ptr(), tokens, x.stride(0) if tokens else self.hidden, ids.data_ptr(), w.data_ptr(),
+                    out.data_ptr(), self.hidden)
+        self._keep = (ids, w)               # the step reads them asynchronously
+        return out[:tokens]
+
+    def close(self):
+        self.ep.close()
+        super().close()
+
+
 class ExpertCacheManager:
     """moe.ExpertCacheManager (lm/moe/moe.go:143-287) over the library's host-side cache: at most
     max_hot expert blobs in memory, least recently used spilled to <dir>/expert_<id>.bin, cold

@@ -346,20 +346,15 @@ QM_API int32_t qm_stack_parts(qm_ctx *ctx, qm_stack *stack, int64_t *info2);
 QM_API int32_t qm_stack_use_graph(qm_ctx *ctx, qm_stack *stack, int32_t on);
 
 /* Tensor-parallel decode stack over the GPUs of one box, one process per GPU (config "row
- * sharding at 1/2/4/8 GPUs"). The two large matrices of a layer are shared: rank `rank` of
- * `world` (<= 8) holds rows [rank*R/world, (rank+1)*R/world) of gate|up and of down (R/world a
- * multiple of 16) and hands those slices to qm_stack_set_layer; q|k|v and o (19 % of the
- * bytes) are handed over whole and computed by every GPU for itself, which costs less than the
- * barrier over the GPUs that sharing them would add. The whole step is one persistent launch
- * per GPU: a GPU's slice of a shared output is stored straight into every peer's activation
- * buffers over NVLink (peer memory mapped through CUDA IPC) and the barrier after a shared
- * matvec spans the GPUs (arrival counters or flags in peer memory, every wait bounded:
- * QM_STATUS timeout in qm_last_status) — the all-gather of the reference's plan
- * (nvidia/nccl AllGather, nvidia/nccl/nccl.gen.go) fused into the matvec kernel. Set-up:
- * every rank creates its stack, exports qm_stack_ipc_handle (64 bytes), the handles are
- * exchanged by the caller (any transport) and given to qm_stack_set_peers as world x 64 bytes
- * in rank order. Steps must be issued by all ranks, the same number of times with the same m.
- * qm_stack_step_host returns the full h and all k|v rows on every rank. */
+ * sharding at 1/2/4/8 GPUs"). Rank `rank` of `world` (<= 8) holds rows [rank*R/world,
+ * (rank+1)*R/world) of EVERY matrix — q|k|v, o, gate|up, down — (R/world a multiple of 16)
+ * and hands those slices to qm_stack_set_layer. The whole step is one persistent launch per
+ * GPU: a GPU's slice of an output is stored straight into every peer's activation arena over
+ * NVLink (peer memory mapped through CUDA IPC, or plain pointers in a one-process caller) and
+ * consumers poll their own arena for the words they read; one barrier over the GPUs ends the
+ * launch (flags in peer memory, every wait bounded: QM_ERR_TIMEOUT from qm_last_status) — the
+ * all-gather of the reference's plan (nvidia/x/nccltest/run.go:375-391,584) fused into the
+ * matvec kernel. */
 QM_API int32_t qm_stack_create_tp(qm_ctx *ctx, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
                                   int32_t m_max, int32_t rank, int32_t world, qm_stack **out);
 QM_API int32_t qm_stack_ipc_handle(qm_ctx *ctx, qm_stack *stack, void *handle64);

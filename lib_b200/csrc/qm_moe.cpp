@@ -705,10 +705,24 @@ extern "C" int32_t qm_ep_run(qm_ctx *c, qm_ep *e) {
     const int64_t bound = (int64_t)e->world * e->cap;   // rows this rank can receive
     int32_t rc = qm_launch(c, QM_K_EP_COLLECT, ep_grid(c, bound), 1, 256, 0, &a, false);
     if (rc) return rc;
-    const int typical = (int)std::max<int64_t>(1, bound / e->experts);
-    rc = experts_launch(c, e->wg, e->wd, e->eloc, e->local + e->o_compact, bound, (int32_t)bound, typical,
-                        e->local + e->o_loff, e->local + e->o_y, e->hidden, e->ffn);
-    if (rc) return rc;
+    // As in qm_moe_grouped, the list lengths are read back once so that the grouped launches have exactly the
+    // token tiles that hold rows; QM_MOE_NOSYNC=1 sizes them for the longest possible list instead (no
+    // synchronization; the empty CTAs cost more than the read-back on the shapes measured).
+    int32_t longest = (int32_t)bound, typical = (int32_t)std::max<int64_t>(1, bound / e->experts);
+    if (!qm_env_int("QM_MOE_NOSYNC", 0)) {
+        int32_t loff[65];
+        DRV(c->drv->cuMemcpyDtoHAsync_v2(loff, e->local + e->o_loff, (size_t)(e->eloc + 1) * 4, c->stream));
+        DRV(c->drv->cuStreamSynchronize(c->stream));
+        longest = 0;
+        for (int k = 0; k < e->eloc; k++) longest = std::max(longest, loff[k + 1] - loff[k]);
+        if (longest < 0 || longest > bound) return QM_ERR_STATE;
+        typical = longest;
+    }
+    if (longest > 0) {
+        rc = experts_launch(c, e->wg, e->wd, e->eloc, e->local + e->o_compact, bound, longest, typical,
+                            e->local + e->o_loff, e->local + e->o_y, e->hidden, e->ffn);
+        if (rc) return rc;
+    }
     rc = qm_launch(c, QM_K_EP_RETURN, ep_grid(c, bound), 1, 256, 0, &a, false);
     if (!rc) e->phase = 2;
     return rc;

@@ -132,7 +132,10 @@ struct Cursor {   // walks the items of this warp, op after op
 // Quantizes the 256 activations of row j, unit ul (eight per lane, v) into limbs and writes
 // them, their sub-block sums and the column weights in the layout the main loop reads; the
 // destination is shared memory or an activation image. Returns this lane's sum of squares.
-template <int NT>
+// NAT: the weights keep the order of the GGUF block (mma k index i <-> element i of the sub-block), as
+// the Q4_0 / Q8_0 stores do; otherwise k index 4t+i <-> element 8t+i, 16+4t+i <-> element 8t+4+i, the
+// order of the tiled Q4_K store.
+template <int NT, bool NAT = false>
 __device__ __forceinline__ float quantize_pair(const float (&v)[8], int j, int ul, int lane, int NL, int CPM,
                                                uint8_t *xs_b, int pstride, uint32_t *xsum_b, float *sxw_b,
                                                float wmul = 1.f) {
@@ -171,9 +174,19 @@ __device__ __forceinline__ float quantize_pair(const float (&v)[8], int j, int u
     // lane = 4*sub-block + t': this lane's 8 columns are the B fragment of lane t' for
     // sub-block sb; the fragments of sub-blocks 2p and 2p+1 sit side by side
     const int sb = lane >> 2, tq = lane & 3;
-    const int off = ((ul * 4 + (sb >> 1)) * 4 + tq) * 16 + (sb & 1) * 8;
-    for (int l = 0; l < NL; l++)
-        *reinterpret_cast<uint2 *>(xs_b + (size_t)(j * NL + l) * pstride + off) = make_uint2(w0[l], w1[l]);
+    if (NAT) {
+        // elements 8tq..8tq+3 are register b[tq >> 1] of lane t' = 2*(tq & 1), the next four that of lane t' + 1
+        const int off = ((ul * 4 + (sb >> 1)) * 4 + 2 * (tq & 1)) * 16 + (sb & 1) * 8 + (tq >> 1) * 4;
+        for (int l = 0; l < NL; l++) {
+            uint8_t *pl = xs_b + (size_t)(j * NL + l) * pstride + off;
+            *reinterpret_cast<uint32_t *>(pl) = w0[l];
+            *reinterpret_cast<uint32_t *>(pl + 16) = w1[l];
+        }
+    } else {
+        const int off = ((ul * 4 + (sb >> 1)) * 4 + tq) * 16 + (sb & 1) * 8;
+        for (int l = 0; l < NL; l++)
+            *reinterpret_cast<uint2 *>(xs_b + (size_t)(j * NL + l) * pstride + off) = make_uint2(w0[l], w1[l]);
+    }
     const int n0 = j * CPM;   // first mma column of this activation row
     if (tq == 0) {
         // sub-block sums in units of the unit's maximum (|.| <= 32): safe in fp16 whatever
@@ -1438,6 +1451,308 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Q4_0 / Q8_0 on the same integer path (kernels qm_gemv_q40_lean_*, qm_gemv_q80_lean_*): one matvec of up
+// to four activation rows. The stores of these formats are row-major planes (quants and fp16 scales), laid
+// out so that one 16-byte piece holds a lane's mma operands of four (Q4_0) or two (Q8_0) blocks; an item
+// (16 rows x 256 columns) is gathered into a stage by 16-byte cp.async copies, row by row (every row of an
+// item is a whole 128- or 256-byte line), with the pieces of odd rows swapped between the two halves of
+// each 128 bytes so that the 16-byte reads of a quarter warp touch all banks.
+// Arithmetic: Q8_0 value = d_b*q (s8 x s8 mma), Q4_0 value = d_b*(q - 8): u8 x s8 mma on the codes, the
+// -8*d_b*sum(x) term as one f16 mma per unit of the block scales (fp16 as stored) against the sub-block
+// sums of the activations. The block scale multiplies the exact integer sum of its sub-block in fp32.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// FMT: 2 = Q4_0, 8 = Q8_0. CPM mma columns per activation row (4: up to two rows, three limbs; 2: two
+// limbs), NT column tiles of eight (NT = 2 with CPM = 2: up to eight rows), D ring stages per warp.
+// K parts (a.parts > 1): the CTAs form a.parts groups, group p multiplies K units [p*units, (p+1)*units) of
+// every tile — it stages only that range of x — and leaves its products, without the RMS scale, in partial
+// vector p (a.y + p*a.part_stride) and its sums of squares in a.ssq[p*8 + row]; qm_lean_sum adds them up.
+template <int FMT, int CPM, int D, int NT>
+__device__ __forceinline__ void lean_body(const QmLeanArgs &a) {
+    constexpr int C = 16;
+    constexpr int NL = CPM == 4 ? 3 : 2;
+    constexpr int ROWB = FMT == 2 ? 128 : 256;            // quant bytes of one row of an item
+    constexpr int QB = 16 * ROWB;                         // quant bytes of an item
+    constexpr int STAGE = QB + 256;                       // + 16 rows of 8 fp16 scales
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int M = a.m, P = M * NL, nun = a.units;
+
+    const int plane_stride = nun * 256 + 64;
+    uint8_t *xs = smem;                                                             // [P][plane_stride]
+    uint32_t *xsum = reinterpret_cast<uint32_t *>(xs + (size_t)P * plane_stride);    // [units][8*NT][4] f16 pairs
+    float *sxw = reinterpret_cast<float *>(xsum + (size_t)nun * 8 * NT * 4);         // [units][8*NT] column weights
+    float *ssq = sxw + (size_t)nun * 8 * NT;                                         // [8][16]
+    float *slots = ssq + 8 * 16;                                                     // [C][2][M*16]
+    uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(slots + (size_t)C * 2 * M * 16) + 127) & ~(uintptr_t)127);
+    uint8_t *my_stages = stages + (size_t)warp * D * STAGE;
+
+    asm volatile("griddepcontrol.launch_dependents;");
+    for (int i = tid; i < nun * 8 * NT * 5; i += C * 32) xsum[i] = 0u;   // xsum and sxw are adjacent: absent columns read zero
+
+    // ---- this warp's items: the CTA owns a run of whole tiles of its K part, its items go evenly to the warps
+    const int G = (int)gridDim.x / a.parts;               // CTAs per K part
+    const int part = (int)blockIdx.x / G, c = (int)blockIdx.x - part * G;
+    const int unit0 = part * nun;
+    const int tile0 = c * a.q + min(c, a.rem);
+    const int Ic = (a.q + (c < a.rem ? 1 : 0)) * nun;
+    const int wq_ = Ic / C, wrem = Ic - wq_ * C;
+    const int lo = warp * wq_ + min(warp, wrem), n = wq_ + (warp < wrem ? 1 : 0), hi = lo + n;
+    float *const yout = a.y + (int64_t)part * a.part_stride;
+
+    // ---- producer: gathers one item per call into the next stage ------------------------------------
+    const int64_t rs = (int64_t)a.units_total * ROWB, srs = (int64_t)a.units_total * 16;   // bytes between rows: quants, scales
+    constexpr int RPP = 32 / (ROWB / 16);                 // rows covered by one pass of the warp's 32 pieces
+    constexpr int PASSES = 16 / RPP;
+    const int prow = lane / (ROWB / 16), pcol = lane % (ROWB / 16);   // this lane's row within a pass and piece
+    const uint32_t ring0 = smem_u32(my_stages);
+    const uint32_t dst_q = prow * ROWB + ((pcol ^ (4 * (prow & 1))) * 16), dst_s = QB + lane * 16;
+    int p_left = n, p_tile = lo / nun, p_u = lo - p_tile * nun;
+    uint32_t p_dst = ring0;
+    auto issue = [&]() {
+        if (p_left > 0) {
+            const int row0 = (tile0 + p_tile) * 16;
+            const uint8_t *qsrc = a.wq + (int64_t)(unit0 + p_u) * ROWB + pcol * 16;
+#pragma unroll
+            for (int j = 0; j < PASSES; j++) {
+                const int r = min(row0 + prow + j * RPP, a.rows - 1);   // rows past the last one repeat it; never stored
+                cp_async16(p_dst + dst_q + j * RPP * ROWB, qsrc + r * rs);
+            }
+            if (lane < 16)
+                cp_async16(p_dst + dst_s, reinterpret_cast<const uint8_t *>(a.wd) + min(row0 + lane, a.rows - 1) * srs + (unit0 + p_u) * 16);
+            p_left--;
+            if (++p_u == nun) { p_u = 0; p_tile++; }
+        }
+        cp_async_commit();
+        p_dst = p_dst + STAGE == ring0 + D * STAGE ? ring0 : p_dst + STAGE;
+    };
+#pragma unroll
+    for (int d = 0; d < D; d++) issue();
+
+    // ---- stage x (the launch's input: no polling), quantize into limb planes --------------------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __syncthreads();
+    const int xop = a.xop;
+    const bool norm = xop == 1 || xop == 2;
+    {
+        float sq_run = 0.f;
+        int sq_j = -1;
+        if (norm && lane < 8) ssq[lane * 16 + warp] = 0.f;
+        __syncwarp();
+        for (int idx = warp; idx < M * nun; idx += C) {
+            const int j = idx / nun, ul = idx - j * nun;
+            const int col = (unit0 + ul) * QM_K_UNIT + lane * 8;
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = 0.f;
+            if (col < a.cols) {   // cols is a multiple of 32: a lane's eight columns are all inside or all outside
+                const float *xp = a.x + (int64_t)j * a.ldx + col;
+                const float4 r0 = *reinterpret_cast<const float4 *>(xp), r1 = *reinterpret_cast<const float4 *>(xp + 4);
+                v[0] = r0.x; v[1] = r0.y; v[2] = r0.z; v[3] = r0.w; v[4] = r1.x; v[5] = r1.y; v[6] = r1.z; v[7] = r1.w;
+                if (xop >= 2) {
+                    const float *x2p = a.x2 + (int64_t)j * a.ldx + col;
+                    const float4 s0 = *reinterpret_cast<const float4 *>(x2p), s1 = *reinterpret_cast<const float4 *>(x2p + 4);
+                    const float w[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                    for (int e = 0; e < 8; e++) v[e] = xop == 2 ? v[e] + w[e] : v[e] / (1.f + __expf(-v[e])) * w[e];
+                }
+            }
+            const float sq = quantize_pair<NT, true>(v, j, ul, lane, NL, CPM, xs, plane_stride, xsum, sxw, 1.f);
+            if (norm) {
+                if (j != sq_j) {
+                    if (sq_j >= 0) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
+                        if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
+                    }
+                    sq_j = j;
+                    sq_run = 0.f;
+                }
+                sq_run += sq;
+            }
+        }
+        if (sq_j >= 0) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq_run += __shfl_xor_sync(0xffffffffu, sq_run, o);
+            if (lane == 0) ssq[sq_j * 16 + warp] = sq_run;
+        }
+    }
+    __syncthreads();
+    float myscale[NT];
+#pragma unroll
+    for (int ct = 0; ct < NT; ct++) myscale[ct] = 1.f;
+    if (norm) {
+        const float inv_cols = 1.f / (float)a.cols;
+        for (int j = 0; j < M; j++) {
+            float sq = ssq[j * 16 + (lane & 15)];
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (a.parts > 1) {   // a part leaves its products unscaled and publishes its share of the sum of squares
+                if (c == 0 && tid == 0) a.ssq[part * 8 + j] = sq;
+                continue;
+            }
+            const float sc = rsqrtf(sq * inv_cols + a.eps);
+#pragma unroll
+            for (int ct = 0; ct < NT; ct++)
+                if ((CPM == 4 ? (t >> 1) : ct * 4 + t) == j) myscale[ct] = sc;
+        }
+    }
+
+    // ---- stream --------------------------------------------------------------------------------------
+    const uint8_t *bplane[NT];
+#pragma unroll
+    for (int ct = 0; ct < NT; ct++) {
+        const int ncol = ct * 8 + g, col_row = ncol / CPM, col_limb = ncol - col_row * CPM;
+        const bool col_on = col_row < M && col_limb < NL;
+        bplane[ct] = xs + (size_t)(col_on ? col_row * NL + col_limb : 0) * plane_stride + t * 16;
+    }
+    const uint32_t swz = 4u * (g & 1);
+    const uint8_t *c_stage = my_stages;
+    int fin_tile = -1;
+    auto flush = [&](int tile, int s0, int s1, const float (&accF)[NT][4]) {
+        const bool from_start = s0 == tile * nun, to_end = s1 == tile * nun + nun;
+        if (!(from_start && to_end) && to_end) fin_tile = tile;
+#pragma unroll
+        for (int ct = 0; ct < NT; ct++) {
+            float vA = accF[ct][0] + accF[ct][1], vB = accF[ct][2] + accF[ct][3];
+            int jrow;
+            bool valid;
+            if (CPM == 4) {
+                vA += __shfl_xor_sync(0xffffffffu, vA, 1);
+                vB += __shfl_xor_sync(0xffffffffu, vB, 1);
+                jrow = t >> 1;
+                valid = (t & 1) == 0 && jrow < M;
+            } else {
+                jrow = ct * 4 + t;
+                valid = jrow < M;
+            }
+            vA *= myscale[ct];
+            vB *= myscale[ct];
+            if (from_start && to_end) {
+                const int rA = (tile0 + tile) * 16 + g, rB = rA + 8;
+                if (valid) {
+                    float *yA = yout + (int64_t)jrow * a.ldy + rA;
+                    if (rA < a.rows) yA[0] = vA;
+                    if (rB < a.rows) yA[8] = vB;
+                }
+            } else {
+                // slot 1: the segment ends inside the tile; slot 0: it joined the tile late and reaches its end
+                float *p = slots + ((size_t)warp * 2 + (to_end ? 0 : 1)) * M * 16;
+                if (valid) { p[jrow * 16 + g] = vA; p[jrow * 16 + g + 8] = vB; }
+            }
+        }
+    };
+    for (int i = lo; i < hi;) {
+        const int tile = i / nun, u0 = i - tile * nun;
+        const int seg_end = min(hi, (tile + 1) * nun);
+        float accF[NT][4];
+#pragma unroll
+        for (int ct = 0; ct < NT; ct++) accF[ct][0] = accF[ct][1] = accF[ct][2] = accF[ct][3] = 0.f;
+        int boff = u0 * 256;                                            // byte offset of the unit in a plane
+        const float *cwp = sxw + (size_t)u0 * 8 * NT + 2 * t;
+        const uint32_t *bmp = xsum + (size_t)u0 * 32 * NT + g * 4 + t;
+        for (int k = i; k < seg_end; k++) {
+            cp_async_wait_n<D - 1>();
+            __syncwarp();
+            const uint8_t *stage = c_stage;
+            const uint4 hA = *reinterpret_cast<const uint4 *>(stage + QB + 16 * g);        // eight fp16 block scales of row g
+            const uint4 hB = *reinterpret_cast<const uint4 *>(stage + QB + 16 * g + 128);   // ... of row g + 8
+            const uint32_t hAw[4] = {hA.x, hA.y, hA.z, hA.w}, hBw[4] = {hB.x, hB.y, hB.z, hB.w};
+            float accU[NT][4];
+#pragma unroll
+            for (int ct = 0; ct < NT; ct++) accU[ct][0] = accU[ct][1] = accU[ct][2] = accU[ct][3] = 0.f;
+            const uint8_t *rowA = stage + g * ROWB, *rowB = rowA + 8 * ROWB;
+            constexpr int GROUPS = ROWB / 64;   // 64-byte groups per row: four blocks (Q4_0) or two (Q8_0) each
+#pragma unroll
+            for (int q = 0; q < GROUPS; q++) {
+                const uint32_t piece = (((uint32_t)(q * 4 + t)) ^ swz) * 16;
+                const uint4 wA = *reinterpret_cast<const uint4 *>(rowA + piece);
+                const uint4 wB = *reinterpret_cast<const uint4 *>(rowB + piece);
+                const uint32_t wAw[4] = {wA.x, wA.y, wA.z, wA.w}, wBw[4] = {wB.x, wB.y, wB.z, wB.w};
+                constexpr int BPG = FMT == 2 ? 4 : 2;   // blocks per group
+#pragma unroll
+                for (int s = 0; s < BPG; s++) {
+                    const int sb = q * BPG + s;   // sub-block of the unit
+                    uint32_t a0, a1, a2, a3;
+                    if (FMT == 2) {
+                        a0 = wAw[s] & 0x0F0F0F0Fu; a1 = wBw[s] & 0x0F0F0F0Fu;
+                        a2 = (wAw[s] >> 4) & 0x0F0F0F0Fu; a3 = (wBw[s] >> 4) & 0x0F0F0F0Fu;
+                    } else {
+                        a0 = wAw[2 * s]; a1 = wBw[2 * s]; a2 = wAw[2 * s + 1]; a3 = wBw[2 * s + 1];
+                    }
+                    const uint32_t pa = hAw[sb >> 1], pb = hBw[sb >> 1];
+                    const float dA = __half2float(__ushort_as_half((unsigned short)((sb & 1) ? pa >> 16 : pa & 0xFFFFu)));
+                    const float dB = __half2float(__ushort_as_half((unsigned short)((sb & 1) ? pb >> 16 : pb & 0xFFFFu)));
+#pragma unroll
+                    for (int ct = 0; ct < NT; ct++) {
+                        const uint2 b = *reinterpret_cast<const uint2 *>(bplane[ct] + boff + 64 * (sb >> 1) + 8 * (sb & 1));
+                        int S[4];
+                        if (FMT == 2) mma_u8s8(S, a0, a1, a2, a3, b.x, b.y);
+                        else mma_s8s8(S, a0, a1, a2, a3, b.x, b.y);
+                        accU[ct][0] = fmaf(dA, (float)S[0], accU[ct][0]);
+                        accU[ct][1] = fmaf(dA, (float)S[1], accU[ct][1]);
+                        accU[ct][2] = fmaf(dB, (float)S[2], accU[ct][2]);
+                        accU[ct][3] = fmaf(dB, (float)S[3], accU[ct][3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int ct = 0; ct < NT; ct++) {
+                const float2 cw = *reinterpret_cast<const float2 *>(cwp + 8 * ct);
+                if (FMT == 2) {
+                    // - 8 * sum_b d_b * sum(x in block b): the scales as they are stored (fp16 pairs 2t, 2t+1) times the sums
+                    float accM[4];
+                    mma_f16(accM, *reinterpret_cast<const uint32_t *>(stage + QB + 16 * g + 4 * t),
+                            *reinterpret_cast<const uint32_t *>(stage + QB + 16 * g + 128 + 4 * t), bmp[32 * ct]);
+                    const float mx = -8.f * 127.f * cw.x, my = -8.f * 16256.f * cw.y;
+                    accF[ct][0] = fmaf(cw.x, accU[ct][0], fmaf(mx, accM[0], accF[ct][0]));
+                    accF[ct][1] = fmaf(cw.y, accU[ct][1], fmaf(my, accM[1], accF[ct][1]));
+                    accF[ct][2] = fmaf(cw.x, accU[ct][2], fmaf(mx, accM[2], accF[ct][2]));
+                    accF[ct][3] = fmaf(cw.y, accU[ct][3], fmaf(my, accM[3], accF[ct][3]));
+                } else {
+                    accF[ct][0] = fmaf(cw.x, accU[ct][0], accF[ct][0]);
+                    accF[ct][1] = fmaf(cw.y, accU[ct][1], accF[ct][1]);
+                    accF[ct][2] = fmaf(cw.x, accU[ct][2], accF[ct][2]);
+                    accF[ct][3] = fmaf(cw.y, accU[ct][3], accF[ct][3]);
+                }
+            }
+            boff += 256;
+            cwp += 8 * NT;
+            bmp += 32 * NT;
+            c_stage = c_stage + STAGE == my_stages + D * STAGE ? my_stages : c_stage + STAGE;
+            __syncwarp();
+            issue();
+        }
+        flush(tile, i, seg_end, accF);
+        i = seg_end;
+    }
+    __syncthreads();
+    if (fin_tile >= 0) {
+        // partial sums of the warps that worked on the tile before this one, in warp order
+        const unsigned int ts = (unsigned int)(fin_tile * nun), big = (unsigned int)wrem * (unsigned int)(wq_ + 1);
+        const int wf = wq_ == 0 ? (int)ts : ts < big ? (int)(ts / (unsigned int)(wq_ + 1))
+                                                      : wrem + (int)((ts - big) / (unsigned int)wq_);
+        for (int o = lane; o < 16 * M; o += 32) {
+            float sum = 0.f;
+            for (int x = wf; x < warp; x++) sum += slots[((size_t)x * 2 + 1) * M * 16 + o];
+            sum += slots[(size_t)warp * 2 * M * 16 + o];
+            const int j = o >> 4, r = (tile0 + fin_tile) * 16 + (o & 15);
+            if (r < a.rows) yout[(int64_t)j * a.ldy + r] = sum;
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
@@ -1512,4 +1827,41 @@ extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
 extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)
     qm_fused_q4k_nt2_tp(const __grid_constant__ QmFusedArgs a) {
     fused_body<2, false, true>(a);
+}
+
+// Q4_0 / Q8_0 matvec on the integer path (see lean_body): c4 = up to two activation rows (three limbs), c2 = up
+// to four, c2n2 = up to eight (two column tiles); d = ring stages per warp.
+#define QM_LEAN_KERNEL(name, fmt, cpm, d, nt)                                                \
+    extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)                     \
+        name(const __grid_constant__ QmLeanArgs a) {                                         \
+        lean_body<fmt, cpm, d, nt>(a);                                                       \
+    }
+QM_LEAN_KERNEL(qm_gemv_q40_lean_c4d4, 2, 4, 4, 1)
+QM_LEAN_KERNEL(qm_gemv_q40_lean_c4d2, 2, 4, 2, 1)
+QM_LEAN_KERNEL(qm_gemv_q40_lean_c2d4, 2, 2, 4, 1)
+QM_LEAN_KERNEL(qm_gemv_q40_lean_c2d2, 2, 2, 2, 1)
+QM_LEAN_KERNEL(qm_gemv_q40_lean_c2n2d4, 2, 2, 4, 2)
+QM_LEAN_KERNEL(qm_gemv_q40_lean_c2n2d2, 2, 2, 2, 2)
+QM_LEAN_KERNEL(qm_gemv_q80_lean_c4d3, 8, 4, 3, 1)
+QM_LEAN_KERNEL(qm_gemv_q80_lean_c4d2, 8, 4, 2, 1)
+QM_LEAN_KERNEL(qm_gemv_q80_lean_c2d3, 8, 2, 3, 1)
+QM_LEAN_KERNEL(qm_gemv_q80_lean_c2d2, 8, 2, 2, 1)
+QM_LEAN_KERNEL(qm_gemv_q80_lean_c2n2d3, 8, 2, 3, 2)
+QM_LEAN_KERNEL(qm_gemv_q80_lean_c2n2d2, 8, 2, 2, 2)
+
+// out[j][r] = c_j * sum over the K parts of a lean matvec, c_j = rsqrt(mean square + eps) from the parts' sums of
+// squares when the matvec normalises its input, else 1.
+extern "C" __global__ void __launch_bounds__(256) qm_lean_sum(const __grid_constant__ QmSumPartsArgs a) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int total = a.m * a.n;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const int j = idx / a.n, r = idx - j * a.n;
+        float sum = 0.f, sq = 0.f;
+        for (int k = 0; k < a.nparts; k++) {
+            sum += a.parts[k * a.part_stride + (int64_t)j * a.ld_in + r];
+            if (a.ssq) sq += a.ssq[k * 8 + j];
+        }
+        a.out[(int64_t)j * a.ld_out + r] = a.ssq ? sum * rsqrtf(sq * a.inv_cols + a.eps) : sum;
+    }
 }

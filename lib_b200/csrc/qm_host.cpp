@@ -106,6 +106,11 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_MOE, "qm_moe_decode_combine"},
     {QM_MOD_MOE, "qm_ep_push"},        {QM_MOD_MOE, "qm_ep_collect"},     {QM_MOD_MOE, "qm_ep_return"},
     {QM_MOD_MOE, "qm_ep_combine"},
+    {QM_MOD_Q4K, "qm_gemv_q40_lean_c4d4"}, {QM_MOD_Q4K, "qm_gemv_q40_lean_c4d2"}, {QM_MOD_Q4K, "qm_gemv_q40_lean_c2d4"},
+    {QM_MOD_Q4K, "qm_gemv_q40_lean_c2d2"}, {QM_MOD_Q4K, "qm_gemv_q40_lean_c2n2d4"}, {QM_MOD_Q4K, "qm_gemv_q40_lean_c2n2d2"},
+    {QM_MOD_Q4K, "qm_gemv_q80_lean_c4d3"}, {QM_MOD_Q4K, "qm_gemv_q80_lean_c4d2"}, {QM_MOD_Q4K, "qm_gemv_q80_lean_c2d3"},
+    {QM_MOD_Q4K, "qm_gemv_q80_lean_c2d2"}, {QM_MOD_Q4K, "qm_gemv_q80_lean_c2n2d3"}, {QM_MOD_Q4K, "qm_gemv_q80_lean_c2n2d2"},
+    {QM_MOD_Q4K, "qm_lean_sum"},
 };
 
 // ---- errors --------------------------------------------------------------------------
@@ -194,6 +199,10 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             r = d->cuFuncSetAttribute(c->fn[QM_K_GEMM_Q4K], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             for (int k = QM_K_GEMM_Q4K_R256; k <= QM_K_GEMM_Q4K_R256_K128 && r == CUDA_SUCCESS; k++)
                 r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
+            if (r != CUDA_SUCCESS) err = (int32_t)r;
+        }
+        for (int k = QM_K_Q40_LEAN_C4D4; k <= QM_K_Q80_LEAN_C2N2D2 && !err; k++) {
+            r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
         for (int k = QM_K_FUSED_Q4K_DD_C4D2_SEL; k <= QM_K_FUSED_Q4K_DD_C4D4_SEL && !err; k++) {
@@ -850,6 +859,78 @@ int32_t qm_matvec_launch(qm_ctx *c, const QmWeight *w, uint64_t x_dev, uint64_t 
         int32_t frc = qm_plan_fused(c, m, w->units, true, &fp);
         if (frc) return frc;
         return fused_matvec_launch(c, w, x_dev, x2_dev, m, ldx, y_dev, ldy, flags, fp);
+    }
+    if (env_int("QM_LEAN", 1) != 0) {
+        // The integer tensor-core body: one persistent CTA of 16 warps per SM, whole tiles per CTA, per-warp
+        // cp.async rings. A long K is cut into parts (CTA groups that each stage only their range of x and
+        // leave partial vectors which a small second launch adds up); the deepest ring that fits is taken.
+        // The older kernel takes what fits in no form.
+        const bool q40 = w->fmt == QM_FMT_Q4_0;
+        const int cpm = m <= 2 ? 4 : 2, nt = m <= 4 ? 1 : 2, planes = m * (cpm == 4 ? 3 : 2);
+        const int stage = (q40 ? 2048 : 4096) + 256;
+        const int grid = qm_fused_grid(c), tiles = (int)((w->rows + 15) / 16);
+        const int64_t ldp = (w->rows + 3) & ~(int64_t)3;
+        const int want = env_int("QM_LEAN_PARTS", w->units >= 32 ? 4 : 1);
+        const int order[3] = {want, want == 4 ? 2 : want == 2 ? 4 : 2, want == 1 ? 4 : 1};
+        const int depths[2] = {q40 ? 4 : 3, 2};
+        for (int oi = 0; oi < 3; oi++) {
+            const int S = order[oi];
+            if (S < 1 || w->units % S != 0 || grid % S != 0) continue;
+            if (S > 1 && (!partials || 256 + (int64_t)S * m * ldp * 4 > QM_PARTIALS_BYTES)) continue;
+            const int ups = w->units / S;
+            const int64_t fixed = (int64_t)planes * (ups * 256 + 64) + (int64_t)ups * nt * 160 + 512 + 16 * 2 * m * 64 + 128;
+            for (int di = 0; di < 2; di++) {
+                const int64_t smem = fixed + (int64_t)16 * depths[di] * stage;
+                if (smem > QM_GEMV_SMEM_MAX) continue;
+                QmLeanArgs la;
+                memset(&la, 0, sizeof la);
+                la.wq = (const uint8_t *)(uintptr_t)w->wq;
+                la.wd = (const uint16_t *)(uintptr_t)w->wd;
+                la.x = (const float *)(uintptr_t)x_dev;
+                la.x2 = (const float *)(uintptr_t)x2_dev;
+                la.ldx = ldx;
+                la.rows = (int32_t)w->rows;
+                la.cols = (int32_t)w->cols;
+                la.units = ups;
+                la.units_total = w->units;
+                la.m = m;
+                la.xop = (int32_t)xop;
+                la.eps = 1e-6f;
+                la.parts = S;
+                const int G = grid / S;
+                la.q = tiles / G;
+                la.rem = tiles % G;
+                const bool norm = xop == QM_XOP_RMSNORM || xop == QM_XOP_ADD_RMSNORM;
+                if (S == 1) {
+                    la.y = (float *)(uintptr_t)y_dev;
+                    la.ldy = ldy;
+                } else {
+                    la.ssq = (float *)(uintptr_t)partials;
+                    la.y = (float *)(uintptr_t)(partials + 256);
+                    la.ldy = ldp;
+                    la.part_stride = (int64_t)m * ldp;
+                }
+                const int k = (q40 ? QM_K_Q40_LEAN_C4D4 : QM_K_Q80_LEAN_C4D3) + (cpm == 4 ? 0 : nt == 1 ? 2 : 4) + di;
+                const bool pdl = (flags & QM_FLAG_PDL) != 0;
+                int32_t lrc = qm_launch_ex(c, k, (unsigned)grid, 512, (unsigned)smem, &la, pdl, false);
+                if (lrc || S == 1) return lrc;
+                QmSumPartsArgs sa;
+                memset(&sa, 0, sizeof sa);
+                sa.parts = la.y;
+                sa.ssq = norm ? la.ssq : nullptr;
+                sa.out = (float *)(uintptr_t)y_dev;
+                sa.part_stride = la.part_stride;
+                sa.ld_in = ldp;
+                sa.ld_out = ldy;
+                sa.nparts = S;
+                sa.m = m;
+                sa.n = (int32_t)w->rows;
+                sa.inv_cols = 1.f / (float)w->cols;
+                sa.eps = 1e-6f;
+                const unsigned sgrid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(((int64_t)m * w->rows + 255) / 256, c->sm_count));
+                return qm_launch(c, QM_K_LEAN_SUM, sgrid, 1, 256, 0, &sa, true);
+            }
+        }
     }
     QmGemvPlan p;
     int32_t rc = qm_plan_gemv(c, w, m, &p);

@@ -25,7 +25,10 @@ enum {
     QM_K_GEMV_IQ2XXS_Q81_M1, QM_K_GEMV_IQ2XXS_Q81_M2, QM_K_GEMV_IQ2XXS_Q81_M4, QM_K_GEMV_IQ2XXS_Q81_M8,
     QM_K_RMSNORM_Q81, QM_K_SWIGLU_Q81, QM_K_Q81_EXPAND,
     QM_K_FUSED_Q4K_DD_C4D2_SEL, QM_K_FUSED_Q4K_DD_C4D3_SEL, QM_K_FUSED_Q4K_DD_C4D4_SEL, QM_K_MOE_DECODE_COMBINE,
-    QM_K_EP_PUSH, QM_K_EP_COLLECT, QM_K_EP_RETURN, QM_K_EP_COMBINE, QM_K_COUNT
+    QM_K_EP_PUSH, QM_K_EP_COLLECT, QM_K_EP_RETURN, QM_K_EP_COMBINE,
+    QM_K_Q40_LEAN_C4D4, QM_K_Q40_LEAN_C4D2, QM_K_Q40_LEAN_C2D4, QM_K_Q40_LEAN_C2D2, QM_K_Q40_LEAN_C2N2D4, QM_K_Q40_LEAN_C2N2D2,
+    QM_K_Q80_LEAN_C4D3, QM_K_Q80_LEAN_C4D2, QM_K_Q80_LEAN_C2D3, QM_K_Q80_LEAN_C2D2, QM_K_Q80_LEAN_C2N2D3, QM_K_Q80_LEAN_C2N2D2,
+    QM_K_LEAN_SUM, QM_K_COUNT
 };
 
 #define QM_GEMV_SMEM_MAX (227 * 1024)

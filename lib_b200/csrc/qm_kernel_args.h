@@ -49,6 +49,25 @@ struct QmGemvArgs {
     float eps;
 };
 
+// One Q4_0 / Q8_0 matvec of up to four activation rows on the integer tensor-core path (lean_body).
+struct QmLeanArgs {
+    const uint8_t *wq;       // quant plane [rows][units*8][16 or 32 B] (layouts above)
+    const uint16_t *wd;      // fp16 scale plane [rows][units*8]
+    const float *x, *x2;     // activations [m][ldx]; x2: second operand of QM_XOP_ADD_RMSNORM / QM_XOP_SWIGLU
+    float *y;                // outputs [m][ldy]
+    int64_t ldx, ldy;
+    int32_t rows, cols, m;
+    int32_t units;           // K units of one part (all of a row's when parts == 1)
+    int32_t units_total;     // K units of a whole row of the store
+    int32_t xop;
+    float eps;
+    int32_t q, rem;          // 16-row tiles per CTA of a part: q, the first rem CTAs one more
+    int32_t parts;           // K parts (CTA groups); > 1: y holds `parts` partial vectors, part_stride floats apart
+    int32_t pad_;
+    int64_t part_stride;
+    float *ssq;              // parts > 1 with a normalising xop: [parts][8] sums of squares of x per part and row
+};
+
 // One matvec of a fused sequence (Q4_K weights, integer tensor-core path).
 #define QM_Q4K_ITEM_BYTES 2304
 #define QM_MAX_INLINE_OPS 8

@@ -2,10 +2,11 @@
 oracle's dequantize + float64 dot on the same seeded inputs.
 
 Tolerance: normwise relative error ||y - y_ref|| / ||y_ref|| <= 1e-3 (float32
-activations), the bound the benchmark specification states. The kernels keep
-activations to 21-22 bits (three 7-bit integer limbs, or fp16 hi+lo) for up to
-two activation rows and to 14 bits of each 256-column unit's maximum (two
-limbs) beyond, so the tests also hold them to 2e-5 and 3e-4 respectively."""
+activations), the bound the benchmark specification states. The integer
+tensor-core kernels (Q4_K, Q4_0, Q8_0) keep activations to 21 bits (three 7-bit
+limbs) for up to two activation rows and to 14 bits of each 256-column unit's
+maximum (two limbs) beyond; the Q2_K / IQ2_XXS kernels multiply in float32. So
+the tests also hold them to 2e-5 and 3e-4 respectively."""
 import numpy as np
 import pytest
 
@@ -18,7 +19,7 @@ TIGHT_TOL = 2e-5
 
 
 def tight(fmt, m):
-    return 3e-4 if (fmt == 12 and m > 2) else TIGHT_TOL
+    return 3e-4 if (fmt in (2, 8, 12) and m > 2) else TIGHT_TOL
 
 
 def nre(got, want):

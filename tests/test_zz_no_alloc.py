@@ -12,7 +12,10 @@ import lib_b200
 from lib_b200 import synth
 
 pytestmark = pytest.mark.gpu
-TOL = 2e-5  # normwise; same bound the other matvec tests hold these formats to
+# normwise; the bounds the other matvec tests hold these formats to: qm_matvec quantizes three and more
+# activation rows into two 7-bit limbs, qm_matvec_noalloc keeps fp16 pairs for every batch
+def tol(m):
+    return 3e-4 if m > 2 else 2e-5
 
 
 def nre(got, want):
@@ -44,7 +47,7 @@ def test_noalloc_matches_matvec_twice(ctx, devbuf, fmt, rows, cols, m):
         assert ctx.noalloc_status() == (0, 0)   # no bounded wait of the kernel ran out
         want, got = y_ref.get((m, rows)), y_new.get((m, rows))
         assert np.isfinite(got).all()
-        assert nre(got, want) <= TOL
+        assert nre(got, want) <= tol(m)
     w.free()
 
 

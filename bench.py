@@ -242,6 +242,11 @@ def other_configs(ctx):
         ("config 3: Q4_K matmul 4096x4096, M=256", lambda: bc.gemm_case(ctx, 256, 0, 10)),
         ("config 3: Q4_K matmul 4096x4096, M=2048", lambda: bc.gemm_case(ctx, 2048, 0, 10)),
         ("config 5: MoE layer 8 experts top-2, 512 tokens", lambda: bc.moe_case(ctx, 512, 5)),
+        ("decode-time MoE (qm_moe_decode): 8 Q4_K experts top-2, 1 token", lambda: bc.moe_decode_case(ctx, 1, 5)),
+        ("decode-time MoE (qm_moe_decode): 8 Q4_K experts top-2, 4 tokens", lambda: bc.moe_decode_case(ctx, 4, 5)),
+        ("selected-expert matvec, Q2_K, Q8_1 activations, 6 of 64 experts of 2048x4096", lambda: bc.selected_case(ctx, 10, 10)),
+        ("selected-expert matvec, IQ2_XXS, Q8_1 activations, 6 of 64 experts of 2048x4096", lambda: bc.selected_case(ctx, 16, 10)),
+        ("RMSNorm -> Q8_1, 8 rows of 4096", lambda: bc.q8_1_producer_case(ctx, 8, 4096, 10)),
     ]:
         try:
             r = fn()

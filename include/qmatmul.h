@@ -405,6 +405,23 @@ QM_API int32_t qm_expert_cache_hot(qm_expert_cache *cache);                     
 QM_API int32_t qm_expert_cache_evict(qm_expert_cache *cache, int64_t expert);                    /* EvictColdExpert */
 QM_API int32_t qm_expert_cache_close(qm_expert_cache *cache);                                    /* Close */
 
+/* Device-side residency over such a host cache, for models whose experts do not all fit in HBM:
+ * `max_resident` store entries of one shape (fmt, rows, cols) are allocated once;
+ * qm_expert_pool_get returns the entry that holds `expert`, first overwriting the least recently
+ * used entry (never the one just touched) with the expert's bytes from the host cache (memory or
+ * spill file) when it is not resident. A returned handle names an ENTRY: it stays valid, but a
+ * later get that misses may give the entry to another expert — fetch the handles of all experts
+ * of a step (max_resident >= their number) before launching it. No counterpart in the
+ * reference, whose ExpertCacheManager stops at host memory (lm/moe/moe.go:143-287).
+ * qm_expert_pool_info: [0] experts resident, [1] entries, [2] hits, [3] misses. */
+typedef struct qm_expert_pool qm_expert_pool;
+QM_API int32_t qm_expert_pool_create(qm_ctx *ctx, qm_expert_cache *host, int32_t fmt, int64_t rows, int64_t cols,
+                                     int32_t max_resident, qm_expert_pool **out);
+QM_API int32_t qm_expert_pool_get(qm_ctx *ctx, qm_expert_pool *pool, int64_t expert, qm_weight *out);
+QM_API int32_t qm_expert_pool_info(qm_expert_pool *pool, int64_t *info4);
+QM_API int32_t qm_expert_pool_evict(qm_expert_pool *pool, int64_t expert);
+QM_API int32_t qm_expert_pool_close(qm_ctx *ctx, qm_expert_pool *pool);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,6 +59,11 @@ def _load():
         "qm_moe_experts": (i32, [p, p, p, i32, u64, p, u64]),
         "qm_moe_combine": (i32, [p, u64, u64, u64, i32, i32, i32, u64, i64]),
         "qm_matvec_noalloc": (i32, [u64, u64, i32, i64, u64, i64, u64]),
+        "qm_expert_pool_create": (i32, [p, p, i32, i64, i64, i32, ctypes.POINTER(p)]),
+        "qm_expert_pool_get": (i32, [p, p, i64, ctypes.POINTER(u64)]),
+        "qm_expert_pool_info": (i32, [p, ctypes.POINTER(i64)]),
+        "qm_expert_pool_evict": (i32, [p, i64]),
+        "qm_expert_pool_close": (i32, [p, p]),
         "qm_ep_create": (i32, [p, p, p, i32, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_ep_arena": (i32, [p, p, ctypes.POINTER(u64), ctypes.POINTER(i64)]),
         "qm_ep_ipc_handle": (i32, [p, p, p]),

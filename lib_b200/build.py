@@ -20,7 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libqmatmul.so")
 KERNEL_SOURCES = ["qm_gemv.cu", "qm_dequant.cu", "qm_gemv_q4k.cu", "qm_gemm_q4k.cu", "qm_moe.cu", "qm_gemv_kq.cu", "qm_q8_1.cu"]
-HOST_SOURCES = ["qm_host.cpp", "qm_stack.cpp", "qm_moe.cpp", "qm_expert_cache.cpp", "qm_gguf.cpp", "qm_q8_1.cpp"]
+HOST_SOURCES = ["qm_host.cpp", "qm_stack.cpp", "qm_moe.cpp", "qm_expert_cache.cpp", "qm_gguf.cpp", "qm_q8_1.cpp", "qm_expert_pool.cpp"]
 RUNTIME_SOURCES = ["qm_noalloc.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

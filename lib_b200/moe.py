@@ -218,3 +218,37 @@ class ExpertCacheManager:
         if self._h:
             self._lib.qm_expert_cache_close(self._h)
             self._h = None
+
+
+class ExpertPool:
+    """qm_expert_pool: device-side residency over an ExpertCacheManager — at most max_resident experts of
+    one shape hold a device store entry; `get` pages an expert in over the least recently used entry."""
+
+    def __init__(self, ctx, cache, fmt, rows, cols, max_resident):
+        import ctypes
+        from ._capi import lib, _check, Weight
+        self._lib, self._check, self._ct, self._Weight, self.ctx, self.cache = lib, _check, ctypes, Weight, ctx, cache
+        h = ctypes.c_void_p()
+        _check(lib.qm_expert_pool_create(ctx._h, cache._h, fmt, rows, cols, int(max_resident), ctypes.byref(h)),
+               "expert_pool_create")
+        self._h = h
+
+    def get(self, expert_id):
+        """The store entry (Weight) that holds the expert now; do not free it."""
+        w = self._ct.c_uint64(0)
+        self._check(self._lib.qm_expert_pool_get(self.ctx._h, self._h, int(expert_id), self._ct.byref(w)), "expert_pool_get")
+        return self._Weight(self.ctx, w.value)
+
+    def info(self):
+        """(experts resident, entries, hits, misses)"""
+        v = (self._ct.c_int64 * 4)()
+        self._check(self._lib.qm_expert_pool_info(self._h, v), "expert_pool_info")
+        return tuple(int(x) for x in v)
+
+    def evict(self, expert_id):
+        self._check(self._lib.qm_expert_pool_evict(self._h, int(expert_id)), "expert_pool_evict")
+
+    def close(self):
+        if self._h:
+            self._lib.qm_expert_pool_close(self.ctx._h, self._h)
+            self._h = None

@@ -343,14 +343,13 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                         tmem_ld32(quarter_base + (uint32_t)(sub * BN + c0), v);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         if (n < a.n) {
+                            // split K: this CTA's share of the tile goes to its own plane of the scratch
+                            float *base = a.splitk == 1 ? a.c : a.partials + (int64_t)blockIdx.z * a.m * a.n;
+                            const int64_t ld = a.splitk == 1 ? a.ldc : a.n;
 #pragma unroll
                             for (int j = 0; j < 32; j++) {
                                 const int m = m0 + c0 + j;
-                                if (m < m_cnt) {
-                                    float *cp = a.c + (int64_t)(row_off + m) * a.ldc + n;
-                                    if (a.splitk == 1) *cp = __uint_as_float(v[j]);
-                                    else atomicAdd(cp, __uint_as_float(v[j]));
-                                }
+                                if (m < m_cnt) base[(int64_t)(row_off + m) * ld + n] = __uint_as_float(v[j]);
                             }
                         }
                     }
@@ -365,6 +364,71 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(NSUB * BN)) : "memory");
+    }
+    if (a.splitk > 1) {
+        // Every CTA of the tile adds one band of it, in order of z, once all splitk shares are in the scratch:
+        // the launch is cooperative (all CTAs resident), the wait for the others is bounded. (The barrier
+        // above ordered every thread's stores before thread 0's fence and arrival.)
+        volatile uint32_t *s_ok = tmem_slot + 1;   // a free word of the dynamic shared memory's tail
+        unsigned int *ticket = a.tickets + 2 * (blockIdx.y * gridDim.x + blockIdx.x);
+        if (tid == 0) {
+            __threadfence();
+            atomicAdd(ticket, 1u);
+            const long long t0 = clock64();
+            bool ok = true;
+            while (ld_acquire(ticket) < (unsigned int)a.splitk) {
+                if (clock64() - t0 > a.wait_cycles) { atomicOr(a.status, QM_STATUS_TIMEOUT); ok = false; break; }
+            }
+            *s_ok = ok ? 1u : 0u;
+        }
+        __syncthreads();
+        if (*s_ok) {
+            const int rows = min(NSUB * kBM, a.n - n0), toks = min(BN, a.m - m0);
+            const int t_lo = (int)((int64_t)toks * blockIdx.z / a.splitk), t_hi = (int)((int64_t)toks * (blockIdx.z + 1) / a.splitk);
+            const int64_t plane = (int64_t)a.m * a.n;
+            if ((rows & 3) == 0 && (a.n & 3) == 0 && (a.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(a.c) & 15) == 0) {
+                // 16 bytes per thread and four of them in flight: the loop is bound by the latency of its loads
+                const int r4 = rows >> 2, total = r4 * (t_hi - t_lo), step = (int)blockDim.x;
+                for (int i0 = tid; i0 < total; i0 += 4 * step) {
+                    float4 acc[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int i = i0 + u * step;
+                        acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (i < total) {
+                            const int mm = t_lo + i / r4, nn = (i % r4) << 2;
+                            const float *src = a.partials + (int64_t)(m0 + mm) * a.n + n0 + nn;
+                            for (int z = 0; z < a.splitk; z++) {
+                                const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + z * plane));
+                                acc[u].x += v.x; acc[u].y += v.y; acc[u].z += v.z; acc[u].w += v.w;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int i = i0 + u * step;
+                        if (i < total) {
+                            const int mm = t_lo + i / r4, nn = (i % r4) << 2;
+                            *reinterpret_cast<float4 *>(a.c + (int64_t)(m0 + mm) * a.ldc + n0 + nn) = acc[u];
+                        }
+                    }
+                }
+            } else {
+                for (int i = tid; i < rows * (t_hi - t_lo); i += blockDim.x) {
+                    const int mm = t_lo + i / rows, nn = i % rows;
+                    const int64_t at = (int64_t)(m0 + mm) * a.n + n0 + nn;
+                    float sum = 0.f;
+                    for (int z = 0; z < a.splitk; z++) sum += __ldcg(a.partials + z * plane + at);
+                    a.c[(int64_t)(m0 + mm) * a.ldc + n0 + nn] = sum;
+                }
+            }
+        }
+        // the last CTA to finish its band zeroes the tile's two words for the next launch
+        __syncthreads();
+        if (tid == 0 && atomicAdd(ticket + 1, 1u) + 1u == (unsigned int)a.splitk) {
+            ticket[0] = 0u;
+            ticket[1] = 0u;
+        }
     }
 }
 

@@ -199,6 +199,7 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             r = d->cuFuncSetAttribute(c->fn[QM_K_GEMM_Q4K], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             for (int k = QM_K_GEMM_Q4K_R256; k <= QM_K_GEMM_Q4K_R256_K128 && r == CUDA_SUCCESS; k++)
                 r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
+
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
         for (int k = QM_K_Q40_LEAN_C4D4; k <= QM_K_Q80_LEAN_C2N2D2 && !err; k++) {
@@ -1072,26 +1073,38 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     const int rows_per_cta = g.swiglu ? 128 : 128 * nsub;
     cfg.gridDimX = (unsigned)((out_cols + rows_per_cta - 1) / rows_per_cta);
     cfg.gridDimY = (unsigned)((m + bn - 1) / bn);
-    // few tokens: split K over CTAs until the SMs are covered; partial tiles are added into a
-    // zeroed C (float adds in arrival order: results may differ in the last bits between runs)
+    // few tokens: split K over CTAs until the SMs are covered; the last CTA of a tile adds the shares in a
+    // fixed order (no atomics on C: the same bits every run)
     int splitk = 1;
     if (!grouped) {
         while (splitk < 8 && (int)(cfg.gridDimX * cfg.gridDimY) * splitk * 2 <= c->sm_count && w->units * 4 / (splitk * 2) >= 8)
             splitk *= 2;
         splitk = env_int("QM_GEMM_SPLITK", splitk);
     }
+    // the shares go through the context's scratch (one plane of m x n floats per share) and a ticket per tile
+    while (splitk > 1 && ((int64_t)splitk * m * out_cols * 4 > QM_PARTIALS_BYTES || (int64_t)cfg.gridDimX * cfg.gridDimY * 2 > QM_TICKETS))
+        splitk /= 2;
     a.splitk = splitk;
+    a.partials = (float *)(uintptr_t)c->partials_dev;
+    a.tickets = (unsigned int *)(uintptr_t)c->tickets_dev;
+    a.wait_cycles = qm_wait_cycles();
     cfg.gridDimZ = (unsigned)splitk;
     if (grouped) {   // expert in y, token tile in z (see the kernel)
         cfg.gridDimZ = cfg.gridDimY;
         cfg.gridDimY = (unsigned)g.experts;
     }
-    if (splitk > 1) DRV(c->drv->cuMemsetD2D32Async((CUdeviceptr)c_dev, (size_t)ldc * 4, 0, (size_t)w->rows, (size_t)m, c->stream));
     cfg.blockDimX = 576;   // TMA warp, MMA warp, sixteen dequantizing warps
     cfg.blockDimY = cfg.blockDimZ = 1;
     cfg.sharedMemBytes = smem;
     cfg.hStream = c->stream;
     const int kern = ks == 2 ? (r256 ? QM_K_GEMM_Q4K_R256_K128 : QM_K_GEMM_Q4K_K128) : (r256 ? QM_K_GEMM_Q4K_R256 : QM_K_GEMM_Q4K);
+    CUlaunchAttribute coop;
+    if (splitk > 1) {   // the CTAs of a tile wait for one another before they add the shares: all must be resident
+        coop.id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE;
+        coop.value.cooperative = 1;
+        cfg.attrs = &coop;
+        cfg.numAttrs = 1;
+    }
     DRV(c->drv->cuLaunchKernelEx(&cfg, c->fn[kern], params, nullptr));
     c->launches++;
     return QM_OK;

@@ -181,6 +181,12 @@ struct QmGemmArgs {
     uint16_t *h;           // bf16 [rows][ldh]
     int64_t ldh;
     int32_t debug, pad;    // 0 in production; bits switch off pipeline roles for timing experiments (results are wrong)
+    // Split K: share z of an output tile goes to partials[z][m][n] (plain stores); when all splitk CTAs of
+    // the tile have arrived (tickets[2*tile], zero between launches) each adds one band of the tile in order
+    // of z and writes C — no atomics on C, the same bits every run. The launch is cooperative.
+    float *partials;
+    unsigned int *tickets;
+    int64_t wait_cycles;
 };
 
 // Mixture-of-experts helpers (qm_moe.cu).

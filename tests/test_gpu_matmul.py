@@ -42,7 +42,9 @@ def run(ctx, devbuf, n, k, m, seed, check_rows=None):
     be = k // 256 * 144
     want = oracle.MatVec(12, raw[r0 * be:r1 * be], r1 - r0, k, bf16_to_f32(a16))
     assert np.isfinite(c).all()
-    return nre(c[:, r0:r1], want)
+    err = nre(c[:, r0:r1], want)
+    print("matmul_bf16 %dx%d, M=%d: nre %.3g (bound %.0e)" % (n, k, m, err, TOL))
+    return err
 
 
 @pytest.mark.parametrize("n,k,m", [(256, 512, 64), (128, 256, 1), (384, 1024, 100), (200, 768, 130),
@@ -58,3 +60,27 @@ def test_config3_shapes(ctx, devbuf, m):
 
 def test_config3_m2048_sampled_rows(ctx, devbuf):
     assert run(ctx, devbuf, 4096, 4096, 2048, seed=77, check_rows=(1920, 2048)) <= TOL
+
+
+def test_split_k_gives_the_same_bits_every_run(ctx, devbuf):
+    """Few tokens: K is split over CTAs and the shares are added in a fixed order, not by atomics."""
+    n, k, m = 1024, 4096, 48
+    raw = synth.weights(12, n, k, 5)
+    a16 = to_bf16_bits(synth.activations(m, k, 6))
+    w = ctx.store_upload(12, n, k, raw)
+    ad = devbuf(a16)
+    outs = []
+    for rep in range(4):
+        cd = devbuf(np.full((m, n), np.nan, np.float32))
+        ctx.matmul_bf16(w, ad.ptr, m, k, cd.ptr, n)
+        ctx.sync()
+        outs.append(cd.get((m, n)).view(np.uint32).copy())
+    assert ctx.last_status() == (0, 0)
+    assert all(np.array_equal(outs[0], o) for o in outs[1:])
+    # an unaligned output pitch takes the scalar form of the reduction
+    cd = devbuf(np.full((m, n + 3), np.nan, np.float32))
+    ctx.matmul_bf16(w, ad.ptr, m, k, cd.ptr, n + 3)
+    ctx.sync()
+    got = cd.get((m, n + 3))[:, :n]
+    assert np.array_equal(got.view(np.uint32), outs[0])
+    w.free()

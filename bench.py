@@ -205,6 +205,15 @@ def parity_check(ctx, runner, synth, m, layers, x_host, dist, rank, world):
     ptrs = runner.stack.buffers()
     gu = np.empty((m, 2 * FFN), np.float32)
     ctx.d2h(gu, ptrs[3])
+    if world > 1 and getattr(runner, "paired", False):
+        # every rank holds only its own gate and up slices (its down part needs no others): put them together
+        f = FFN // world
+        own = np.zeros_like(gu)
+        own[:, rank * f:(rank + 1) * f] = gu[:, rank * f:(rank + 1) * f]
+        own[:, FFN + rank * f:FFN + (rank + 1) * f] = gu[:, FFN + rank * f:FFN + (rank + 1) * f]
+        t = torch.from_numpy(own).cuda()
+        dist.all_reduce(t)
+        gu = t.cpu().numpy()
     down_raw = decode.layer_tensors(FMT, HIDDEN, KV, FFN, SEED, layers - 1)[6][3]
     want = oracle.MatVec(FMT, down_raw, HIDDEN, FFN, oracle.RMSNorm(gu[:, :FFN] + gu[:, FFN:]))
     out["nre"] = float(np.linalg.norm(h.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30))
@@ -268,6 +277,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-batch", action="store_true", help="skip the short run at the other batch size (8 or 1)")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the short runs of the other configurations")
+    ap.add_argument("--tp", choices=("paired", "rows"), default="paired",
+                    help="sharding on several GPUs: paired (q|k|v, gate|up by rows; o, down by K; up to batch 4) or every matrix by rows")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -298,9 +309,14 @@ def main():
         runner = decode.SingleGpuDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED)
         tp_mode = None
     else:
-        runner = decode.PeerTensorParallelDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED, rank, world, barrier=False)
-        tp_mode = ("every matrix sliced by rows; slices stored into all peers' arenas over NVLink and polled "
-                   "there; one persistent launch per GPU and step")
+        paired = args.tp == "paired" and m <= 4
+        runner = decode.PeerTensorParallelDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED, rank, world, m_max=4 if paired else 8,
+                                                 barrier=False, paired=paired)
+        tp_mode = ("paired: q|k|v and gate|up sliced by rows, o and down by the K columns of the rank's own slices; partial "
+                   "outputs stored into all peers' arenas over NVLink, polled there and added in rank order by the consumer "
+                   "(two exchanges per layer); one persistent launch per GPU and step" if paired else
+                   "every matrix sliced by rows; slices stored into all peers' arenas over NVLink and polled "
+                   "there (four exchanges per layer); one persistent launch per GPU and step")
 
     x_host = torch.from_numpy(synth.activations(m, HIDDEN, SEED + 999)).pin_memory()
     x_dev = x_host.to("cuda", non_blocking=False)
@@ -350,7 +366,7 @@ def main():
         # ---- the other batch size the workload is quoted at (reported beside the metric) ----
         m2 = 8 if m == 1 else 1
         ms_other = None
-        if not args.no_other_batch:
+        if not args.no_other_batch and not (getattr(runner, "paired", False) and m2 > 4):   # the paired form holds up to four rows
             x2_dev = torch.from_numpy(synth.activations(m2, HIDDEN, SEED + 998)).to("cuda")
             h2_dev = torch.empty(m2, HIDDEN, device="cuda")
             n2 = max(3, min(args.steps, 50))

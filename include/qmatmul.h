@@ -357,6 +357,18 @@ QM_API int32_t qm_stack_use_graph(qm_ctx *ctx, qm_stack *stack, int32_t on);
  * matvec kernel. */
 QM_API int32_t qm_stack_create_tp(qm_ctx *ctx, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
                                   int32_t m_max, int32_t rank, int32_t world, qm_stack **out);
+/* The paired form of the same step, the usual pairing of transformer matrices: q|k|v and gate|up sliced by
+ * rows, o and down by K over the rank's OWN slice of their inputs, so that only two of a layer's four
+ * hand-overs cross the GPUs. Rank r holds: of q|k|v the rows of q slice r followed by the rows of k|v slice r;
+ * of gate|up the rows of gate slice r followed by those of up slice r (slice r of N rows = [r*N/world,
+ * (r+1)*N/world)); of o and of down ALL rows of the K columns [r*K/world, (r+1)*K/world) — a column shard
+ * is, for every row, the blocks of that column range, in row order. An o or down part leaves a partial
+ * output vector per GPU in every arena; the consumer adds them in rank order (the same bits on every GPU).
+ * This departs from "rows of every matrix": it is the same product, summed over K in `world` pieces
+ * instead of one. hidden and ffn must be multiples of 256*world, 2*kv_dim of 16*world; m_max <= 4.
+ * Everything else (handles, peers, steps, results, bounded waits) is as for qm_stack_create_tp. */
+QM_API int32_t qm_stack_create_tp_paired(qm_ctx *ctx, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
+                                         int32_t m_max, int32_t rank, int32_t world, qm_stack **out);
 QM_API int32_t qm_stack_ipc_handle(qm_ctx *ctx, qm_stack *stack, void *handle64);
 QM_API int32_t qm_stack_set_peers(qm_ctx *ctx, qm_stack *stack, const void *handles);
 /* The same for a caller that drives all GPUs from one process (the reference's nccltest model,

@@ -93,6 +93,7 @@ def _load():
         "qm_stack_parts": (i32, [p, p, ctypes.POINTER(i64)]),
         "qm_stack_use_graph": (i32, [p, p, i32]),
         "qm_stack_create_tp": (i32, [p, i32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
+        "qm_stack_create_tp_paired": (i32, [p, i32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(p)]),
         "qm_stack_ipc_handle": (i32, [p, p, p]),
         "qm_stack_set_peers": (i32, [p, p, p]),
         "qm_stack_arena": (i32, [p, p, ctypes.POINTER(u64), ctypes.POINTER(i64)]),
@@ -419,12 +420,15 @@ class ExpertParallel:
 class Stack:
     """qm_stack: a decode step over `layers` quantized transformer-shaped layers."""
 
-    def __init__(self, ctx, layers, hidden, kv_dim, ffn, m_max=8, rank=0, world=1):
+    def __init__(self, ctx, layers, hidden, kv_dim, ffn, m_max=8, rank=0, world=1, paired=False):
         self.ctx, self.layers, self.hidden, self.kv_dim, self.ffn, self.m_max = ctx, layers, hidden, kv_dim, ffn, m_max
-        self.rank, self.world = rank, world
+        self.rank, self.world, self.paired = rank, world, paired
         h = ctypes.c_void_p()
         if world == 1:
             _check(lib.qm_stack_create(ctx._h, layers, hidden, kv_dim, ffn, m_max, ctypes.byref(h)), "stack_create")
+        elif paired:
+            _check(lib.qm_stack_create_tp_paired(ctx._h, layers, hidden, kv_dim, ffn, m_max, rank, world, ctypes.byref(h)),
+                   "stack_create_tp_paired")
         else:
             _check(lib.qm_stack_create_tp(ctx._h, layers, hidden, kv_dim, ffn, m_max, rank, world, ctypes.byref(h)),
                    "stack_create_tp")

@@ -1010,6 +1010,33 @@ __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, 
                             v[0] += r[2 * k].x; v[1] += r[2 * k].y; v[2] += r[2 * k].z; v[3] += r[2 * k].w;
                             v[4] += r[2 * k + 1].x; v[5] += r[2 * k + 1].y; v[6] += r[2 * k + 1].z; v[7] += r[2 * k + 1].w;
                         }
+                    if (TP && x_parts > 4) {
+                        // tensor-parallel lists have up to eight partial vectors (one per GPU): the second four
+                        for (;;) {
+                            bool ok = true;
+#pragma unroll
+                            for (int k = 0; k < 4; k++)
+                                if (4 + k < x_parts) {
+                                    r[2 * k] = ld_relaxed_sys_v4(xp + (4 + k) * xps);
+                                    r[2 * k + 1] = ld_relaxed_sys_v4(xp + (4 + k) * xps + 4);
+                                }
+#pragma unroll
+                            for (int k = 0; k < 4; k++)
+                                if (4 + k < x_parts) ok = ok & written4(r[2 * k]) & written4(r[2 * k + 1]);
+                            if (__all_sync(0xffffffffu, ok || dead)) break;
+                            if (t0 == 0) t0 = clock64();
+                            else if (clock64() - t0 > a.wait_cycles) {
+                                if (lane == 0) atomicOr(a.status, QM_STATUS_TIMEOUT);
+                                dead = true;
+                            }
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            if (4 + k < x_parts) {
+                                v[0] += r[2 * k].x; v[1] += r[2 * k].y; v[2] += r[2 * k].z; v[3] += r[2 * k].w;
+                                v[4] += r[2 * k + 1].x; v[5] += r[2 * k + 1].y; v[6] += r[2 * k + 1].z; v[7] += r[2 * k + 1].w;
+                            }
+                    }
                     const float sq = quantize_pair<NT>(v, j, ul, lane, NL, CPM, xs, plane_stride, xsum, sxw, 0.0625f);
                     if (norm) {
                         if (j != sq_j) {
@@ -1242,7 +1269,15 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                 if (parts > 1) {
                     // a K part leaves its products unscaled; the consumer scales the sum. One CTA of the
                     // group publishes the part's sum of squares.
-                    if (cta_in_grp == 0 && tid == 0) st_relaxed_f32(ssq_out + po->part * 8 + j, sq);
+                    if (cta_in_grp == 0 && tid == 0) {
+                        float *word = ssq_out + po->part * 8 + j;
+                        if (TP && (po->tp_shared & 1)) {   // a GPU's K part: every GPU's consumers read the word
+                            for (int p = 0; p < a.tp_world; p++)
+                                st_relaxed_sys_f32(reinterpret_cast<float *>(reinterpret_cast<char *>(word) + a.peer_delta[p]), sq);
+                        } else {
+                            st_relaxed_f32(word, sq);
+                        }
+                    }
                     continue;
                 }
                 float eps = po->eps;
@@ -1254,7 +1289,8 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                     for (int k = 0; k < x_parts; k++) {
                         float part;
                         for (;;) {
-                            asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + j) : "memory");
+                            if (TP) asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + j) : "memory");
+                            else asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + j) : "memory");
                             if (__float_as_uint(part) != kUnwritten || dead) break;
                             if (t0 == 0) t0 = clock64();
                             else if (clock64() - t0 > a.wait_cycles) {
@@ -1283,11 +1319,17 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         const int hi = lo + n;
         int fin_tile = -1;   // CTA-local tile this warp adds up after the CTA barrier
 
-        auto store_y = [&](float *yp, float val) {   // a result must never look like "not yet written"
+        // Tensor-parallel lists: rows from split_row on go to a second output (q|k|v and gate|up slices that are
+        // two row ranges of the full vector); tp_shared bit 0 / bit 1 = the first / second output goes to every
+        // GPU's arena, otherwise to this GPU's only.
+        // (read from the descriptor in shared memory where they are used: the streaming loop has no register to spare)
+        auto store_y = [&](float *yp, float val, bool share) {   // a result must never look like "not yet written"
             if (__float_as_uint(val) == kUnwritten) val = __uint_as_float(0x7FC00000u);
-            if (TP) {
+            if (TP && share) {
                 for (int p = 0; p < a.tp_world; p++)   // the same place of every GPU's arena, this one included
                     st_relaxed_sys_f32(reinterpret_cast<float *>(reinterpret_cast<char *>(yp) + a.peer_delta[p]), val);
+            } else if (TP) {
+                st_relaxed_sys_f32(yp, val);
             } else {
                 st_relaxed_f32(yp, val);
             }
@@ -1313,9 +1355,12 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             if (from_start && to_end) {
                 const int rA = (tile0 + tile) * 16 + g, rB = rA + 8;
                 if (valid) {
-                    float *yA = opy + (int64_t)jrow * ldy + rA;
-                    if (rA < rows) store_y(yA, vA);
-                    if (rB < rows) store_y(yA + 8, vB);
+                    const int split = TP ? po->split_row : 0;
+                    const bool second = TP && split > 0 && (tile0 + tile) * 16 >= split;   // whole tiles on either side
+                    float *yA = (second ? po->y2 - split : opy) + (int64_t)jrow * ldy + rA;
+                    const bool share = TP && (po->tp_shared & (second ? 2 : 1)) != 0;
+                    if (rA < rows) store_y(yA, vA, share);
+                    if (rB < rows) store_y(yA + 8, vB, share);
                 }
                 return;
             }
@@ -1416,7 +1461,10 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                 for (int x = wf; x < warp; x++) sum += slots[((size_t)x * 2 + 1) * M * 16 + o];
                 sum += slots[(size_t)warp * 2 * M * 16 + o];
                 const int j = o >> 4, r = (tile0 + fin_tile) * 16 + (o & 15);
-                if (r < rows) store_y(opy + (int64_t)j * ldy + r, sum);
+                const int split = TP ? po->split_row : 0;
+                const bool second = TP && split > 0 && (tile0 + fin_tile) * 16 >= split;
+                if (r < rows)
+                    store_y((second ? po->y2 - split : opy) + (int64_t)j * ldy + r, sum, TP && (po->tp_shared & (second ? 2 : 1)) != 0);
             }
         }
         QM_DD_MARK(3);

@@ -92,8 +92,8 @@ struct alignas(16) QmOp {   // a multiple of 16 bytes: the kernels copy descript
     // addends on a zero: order-independent), and y's shared tiles are zeroed during the op before
     int32_t q, rem;
     int32_t balanced;
-    int32_t tp_shared;   // tensor-parallel launch: 1 = this op computes a row slice and stores it into every GPU's arena
-                         // (a barrier over all GPUs follows); 0 = every GPU computes the whole op for itself
+    int32_t tp_shared;   // tensor-parallel launch: bit 0 = the op's results (and the words of its K part) go into every
+                         // GPU's arena, else into this GPU's only; bit 1 = the same for the second output (y2)
     // Activation image: the quantized form of an op's x (limb planes, sub-block sums, column
     // weights, sums of squares per unit) in global memory. An op whose x is the previous op's y
     // can read it ready-made instead of every CTA quantizing all of x: the previous op builds
@@ -128,6 +128,12 @@ struct alignas(16) QmOp {   // a multiple of 16 bytes: the kernels copy descript
     const uint8_t *const *sel_table;
     const int32_t *sel_ids;
     int32_t sel_index, sel_count;
+    // Second output (tensor-parallel kernels only): rows [split_row, rows) of the op go to y2 instead of y
+    // (split_row a multiple of 16; 0 = one output). tp_shared bit 0 / bit 1 then say which of the two goes
+    // to every GPU's arena.
+    float *y2;
+    int32_t split_row;
+    int32_t pad3_;
 };
 
 struct QmFusedArgs {

@@ -58,6 +58,11 @@ struct qm_stack {
     // tensor-parallel: one arena holds all activation buffers and the peers' arrival flags; the
     // peers map it through CUDA IPC and this GPU stores its row slices into all of them
     int tp_world, tp_rank;
+    // Tensor-parallel sharding. Rows (false): every matrix sliced by output rows, four exchanges per layer.
+    // Paired (true): q|k|v and gate|up by rows, o and down by K over the rank's own slice of their inputs —
+    // their partial outputs (one vector per GPU) are added by the consumer, two exchanges per layer.
+    bool tp_paired;
+    int parts_cap;              // partial vectors the o / down buffers of a layer have room for
     CUdeviceptr arena;
     size_t arena_bytes, flags_off;
     CUdeviceptr peer_base[QM_MAX_PEERS];
@@ -73,15 +78,15 @@ struct qm_stack {
 // Device addresses of layer L's output buffers in a step of batch m. The o and down projections
 // have room for QM_MAX_PARTS partial output vectors each (see QmOp::parts; steps that do not cut
 // them into K parts use the first), followed by the words their K parts publish.
-#define QM_MAX_PARTS 4
+#define QM_MAX_PARTS 4           // K parts of one GPU's op (CTA groups); a paired tensor-parallel stack has one part per GPU
 struct LayerBufs {
     CUdeviceptr qkv, o, gu, dn;
-    CUdeviceptr ssq_o, ssq_dn;   // [QM_MAX_PARTS][8] floats each
+    CUdeviceptr ssq_o, ssq_dn;   // [parts_cap][8] floats each
     int64_t part_stride;         // floats between the partial vectors of o (and of dn)
 };
 static size_t layer_floats(const qm_stack *s, int m) {
     const size_t qkv_ld = (size_t)s->hidden + 2 * s->kv;
-    return (size_t)m * (qkv_ld + 2 * (size_t)s->ffn + 2 * QM_MAX_PARTS * (size_t)s->hidden) + 2 * QM_MAX_PARTS * 8;
+    return (size_t)m * (qkv_ld + 2 * (size_t)s->ffn + 2 * s->parts_cap * (size_t)s->hidden) + 2 * s->parts_cap * 8;
 }
 static LayerBufs layer_bufs(const qm_stack *s, int L, int m) {
     const size_t qkv_ld = (size_t)s->hidden + 2 * s->kv;
@@ -89,10 +94,10 @@ static LayerBufs layer_bufs(const qm_stack *s, int L, int m) {
     b.part_stride = (int64_t)m * s->hidden;
     b.qkv = s->act + (size_t)L * layer_floats(s, m) * 4;
     b.o = b.qkv + (size_t)m * qkv_ld * 4;
-    b.gu = b.o + (size_t)QM_MAX_PARTS * m * s->hidden * 4;
+    b.gu = b.o + (size_t)s->parts_cap * m * s->hidden * 4;
     b.dn = b.gu + (size_t)m * 2 * s->ffn * 4;
-    b.ssq_o = b.dn + (size_t)QM_MAX_PARTS * m * s->hidden * 4;
-    b.ssq_dn = b.ssq_o + QM_MAX_PARTS * 8 * 4;
+    b.ssq_o = b.dn + (size_t)s->parts_cap * m * s->hidden * 4;
+    b.ssq_dn = b.ssq_o + s->parts_cap * 8 * 4;
     return b;
 }
 
@@ -100,7 +105,7 @@ static qm_stack *stack_check(qm_stack *s) { return (s && s->magic == QM_STACK_MA
 static CUdeviceptr h_source(const qm_stack *s, int m);
 
 static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn, int32_t m_max,
-                            int32_t rank, int32_t world, qm_stack **out) {
+                            int32_t rank, int32_t world, bool paired, qm_stack **out) {
     CHECK_CTX(c);
     if (!out) return QM_ERR_ARG;
     *out = nullptr;
@@ -110,6 +115,9 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
     if (world < 1 || world > QM_MAX_PEERS || rank < 0 || rank >= world) return QM_ERR_ARG;
     if (world > 1 && ((hidden % (16 * world)) || ((2 * ffn) % (16 * world)) || ((hidden + 2 * kv_dim) % (16 * world))))
         return QM_ERR_SHAPE;   // every GPU's row slice must be whole 16-row tiles
+    // paired: the row slices of q, of k|v, of gate and of up are whole tiles, the K slices of o and down whole units
+    if (paired && (world < 2 || (hidden % (256 * world)) || (ffn % (256 * world)) || ((2 * kv_dim) % (16 * world)) || m_max > 4))
+        return QM_ERR_SHAPE;
     qm_stack *s = new (std::nothrow) qm_stack();
     if (!s) return QM_ERR_NOMEM;
     s->magic = QM_STACK_MAGIC;
@@ -120,6 +128,8 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
     s->m_max = m_max;
     s->tp_world = world;
     s->tp_rank = rank;
+    s->tp_paired = paired;
+    s->parts_cap = paired ? 8 : QM_MAX_PARTS;   // paired: one part per GPU, or several per GPU while the total stays at eight
     s->arena = 0;
     s->peers_open = false;
     s->peers_ipc = false;
@@ -173,7 +183,7 @@ static int32_t stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t k
 
 extern "C" int32_t qm_stack_create(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
                                    int32_t m_max, qm_stack **out) {
-    return stack_create(c, layers, hidden, kv_dim, ffn, m_max, 0, 1, out);
+    return stack_create(c, layers, hidden, kv_dim, ffn, m_max, 0, 1, false, out);
 }
 
 // Tensor-parallel stack: rank `rank` of `world` GPUs of one box. The gate|up and down matrices
@@ -181,7 +191,16 @@ extern "C" int32_t qm_stack_create(qm_ctx *c, int32_t layers, int32_t hidden, in
 // [rank*R/world, (rank+1)*R/world); q|k|v and o are whole on every rank.
 extern "C" int32_t qm_stack_create_tp(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
                                       int32_t m_max, int32_t rank, int32_t world, qm_stack **out) {
-    return stack_create(c, layers, hidden, kv_dim, ffn, m_max, rank, world, out);
+    return stack_create(c, layers, hidden, kv_dim, ffn, m_max, rank, world, false, out);
+}
+
+// The paired form: rank r holds of q|k|v the rows of q slice r followed by the rows of k|v slice r, of gate|up the
+// rows of gate slice r followed by those of up slice r (slice r of N rows = [r*N/world, (r+1)*N/world)), and of
+// o and down ALL rows of the K columns [r*K/world, (r+1)*K/world) — the columns that multiply the rank's own
+// slice of q, respectively of gate and up. Up to four activation rows.
+extern "C" int32_t qm_stack_create_tp_paired(qm_ctx *c, int32_t layers, int32_t hidden, int32_t kv_dim, int32_t ffn,
+                                             int32_t m_max, int32_t rank, int32_t world, qm_stack **out) {
+    return stack_create(c, layers, hidden, kv_dim, ffn, m_max, rank, world, true, out);
 }
 
 // The CUDA IPC handle (64 bytes) of this stack's activation arena, for the peers.
@@ -304,8 +323,12 @@ extern "C" int32_t qm_stack_set_layer(qm_ctx *c, qm_stack *s, int32_t layer, qm_
         if (!p) return QM_ERR_ARG;
     // tensor-parallel: every matrix is this rank's slice of the rows
     const int64_t W = s->tp_world;
-    const int64_t want[4][2] = {{(s->hidden + 2 * s->kv) / W, s->hidden}, {s->hidden / W, s->hidden},
-                                {2 * s->ffn / W, s->hidden}, {s->hidden / W, s->ffn}};
+    int64_t want[4][2] = {{(s->hidden + 2 * s->kv) / W, s->hidden}, {s->hidden / W, s->hidden},
+                          {2 * s->ffn / W, s->hidden}, {s->hidden / W, s->ffn}};
+    if (s->tp_paired) {   // o and down: all rows of the rank's K columns
+        want[1][0] = s->hidden; want[1][1] = s->hidden / W;
+        want[3][0] = s->hidden; want[3][1] = s->ffn / W;
+    }
     for (int i = 0; i < 4; i++)
         if (w[i]->rows != want[i][0] || w[i]->cols != want[i][1]) return QM_ERR_SHAPE;
     {
@@ -389,6 +412,7 @@ static int32_t upload_ops(qm_ctx *c, qm_stack *s, int m, std::vector<QmOp> &ops)
             op.x = (const float *)moved(op.x);
             op.x2 = (const float *)moved(op.x2);
             op.y = (float *)moved(op.y);
+            op.y2 = (float *)moved(op.y2);
             op.ssq_out = (float *)moved(op.ssq_out);
             op.ssq_in = (const float *)moved(op.ssq_in);
             ops.push_back(op);
@@ -550,6 +574,128 @@ static int32_t build_fused_dd(qm_ctx *c, qm_stack *s, int m) {
     s->fused_dd_kernel[m] = kernel;
     s->fused_parts_o[m] = So;
     s->fused_parts_dn[m] = Sd;
+    s->fused_plan[m] = p;
+    return QM_OK;
+}
+
+// The op list of a paired tensor-parallel step (see qm_stack_create_tp_paired), data-driven form. Per layer:
+//   q|k|v  rows of this rank   x = the W partial vectors of the previous down projection   -> q slice (own arena),
+//                                                                                              k|v slice (all arenas)
+//   o      K part of this rank x = the rank's own q slice (no exchange)                     -> partial vector r (all)
+//   gate|up rows of this rank  x = the W partial vectors of o                               -> own arena only
+//   down   K part of this rank x = the rank's own gate and up slices (no exchange)          -> partial vector r (all)
+// A K part leaves its products without the RMS scale of its input and publishes its sum of squares; the consumer
+// adds the W vectors in rank order and corrects its epsilon (QmOp::parts).
+static int32_t build_fused_paired(qm_ctx *c, qm_stack *s, int m) {
+    if (m > 4) return QM_ERR_SHAPE;
+    const int W = s->tp_world, r = s->tp_rank, grid = qm_fused_grid(c);
+    for (int L = 0; L < s->layers; L++) {
+        const QmLayer &ly = s->layer[L];
+        if (!ly.qkv) return QM_ERR_STATE;
+        const QmWeight *ws[4] = {ly.qkv, ly.o, ly.gu, ly.dn};
+        for (const QmWeight *w : ws)
+            if (w->fmt != QM_FMT_Q4_K) return QM_ERR_FORMAT;
+    }
+    // A rank's down part can be cut further into S parts run by S groups of its CTAs (a CTA then stages a 1/(W*S)
+    // of gate and up, not 1/W), as long as the consumer has at most parts_cap vectors to add. Off by default:
+    // on 2 GPUs one part per GPU measured 0.97 ms per step, two 0.98, four 1.07 — every further vector costs the
+    // consumers more than the shorter staging saves (QM_PAIRED_PARTS_DN).
+    const int dn_units = (s->ffn / W) / 256;
+    int S = 1;
+    for (int k = QM_MAX_PARTS; k > 1; k >>= 1)
+        if (k <= qm_env_int("QM_PAIRED_PARTS_DN", 1) && W * k <= s->parts_cap && dn_units % k == 0 && grid % k == 0) {
+            S = k;
+            break;
+        }
+    const int max_units = std::max(s->hidden / 256, dn_units / S);
+    QmFusedPlan p;
+    if (qm_plan_fused(c, m, max_units, false, &p) != QM_OK || p.nt != 1 || p.consumers != 16 || p.depth < 2 || p.depth > 4)
+        return QM_ERR_SHAPE;
+    const int kernel = (p.cpm == 4 ? QM_K_FUSED_Q4K_DD_C4D2 : QM_K_FUSED_Q4K_DD_C2D2) + (p.depth - 2);
+    if (S > 1)
+        for (int L = 0; L < s->layers; L++) {
+            QmLayer &ly = s->layer[L];
+            const int32_t rc = part_major_copy(c, ly.dn, S, &ly.dn_parts, &ly.dn_nparts);
+            if (rc) return rc;
+        }
+    std::vector<QmOp> ops;
+    const int64_t qkv_ld = s->hidden + 2 * s->kv;
+    const int64_t q_rows = s->hidden / W, kv_rows = 2 * s->kv / W, f_rows = s->ffn / W;
+    auto add = [&](const QmWeight *w, CUdeviceptr x, CUdeviceptr x2, int64_t ldx, CUdeviceptr y, int64_t ldy, uint32_t xop,
+                   bool first, int unit0, int units) -> QmOp & {
+        QmOp op;
+        qm_fill_op(c, p, w, x, x2, ldx, y, ldy, xop, !first, unit0, units, 0, &op);
+        ops.push_back(op);
+        return ops.back();
+    };
+    auto consumes = [&](QmOp &op, int parts, int64_t stride, CUdeviceptr ssq, int64_t producer_cols) {
+        op.x_parts = parts;
+        op.x_part_stride = stride;
+        op.ssq_in = (const float *)(uintptr_t)ssq;
+        op.ssq_in_inv_cols = 1.f / (float)producer_cols;
+        op.ssq_in_eps = 1e-6f;
+    };
+    for (int g = 0; g < S; g++)   // one copy of the list per CTA group; the copies differ in the down op only
+        for (int L = 0; L < s->layers; L++) {
+            const QmLayer &ly = s->layer[L];
+            const LayerBufs b = layer_bufs(s, L, m);
+            // q|k|v: q rows into this arena only (the rank's own o part reads them), k|v rows into every arena
+            QmOp &qkv = add(ly.qkv, L == 0 ? s->h0 : layer_bufs(s, L - 1, m).dn, 0, s->hidden, b.qkv + (size_t)r * q_rows * 4,
+                            qkv_ld, QM_XOP_RMSNORM, L == 0, 0, ly.qkv->units);
+            qkv.split_row = (int32_t)q_rows;
+            qkv.y2 = (float *)(uintptr_t)(b.qkv + (size_t)(s->hidden + r * kv_rows) * 4);
+            qkv.tp_shared = 2;
+            if (L > 0) consumes(qkv, W * S, b.part_stride, layer_bufs(s, L - 1, m).ssq_dn, s->ffn);
+            // o: the K columns that multiply this rank's q slice; one part per GPU
+            QmOp &o = add(ly.o, b.qkv, 0, qkv_ld, b.o + (size_t)r * b.part_stride * 4, s->hidden, QM_XOP_RMSNORM, false,
+                          (int)(r * q_rows / 256), ly.o->units);
+            o.parts = W;
+            o.part = r;
+            o.ssq_out = (float *)(uintptr_t)b.ssq_o;
+            o.tp_shared = 1;
+            // gate|up: gate rows then up rows of this rank, for its own down parts only
+            QmOp &gu = add(ly.gu, b.o, 0, s->hidden, b.gu + (size_t)r * f_rows * 4, 2 * s->ffn, QM_XOP_RMSNORM, false, 0,
+                           ly.gu->units);
+            gu.split_row = (int32_t)f_rows;
+            gu.y2 = (float *)(uintptr_t)(b.gu + (size_t)(s->ffn + r * f_rows) * 4);
+            gu.tp_shared = 0;
+            consumes(gu, W, b.part_stride, b.ssq_o, s->hidden);
+            // down: the K columns that multiply this rank's gate and up slices, part r*S + g of W*S by CTA group g
+            const int ups = dn_units / S, part = r * S + g, G = grid / S;
+            QmOp &dn = add(ly.dn, b.gu, b.gu + (size_t)s->ffn * 4, 2 * s->ffn, b.dn + (size_t)part * b.part_stride * 4,
+                           s->hidden, QM_XOP_ADD_RMSNORM, false, (int)(r * f_rows / 256) + g * ups, ups);
+            if (S > 1) dn.wq = (const uint8_t *)(uintptr_t)(ly.dn_parts + (size_t)g * dn.tiles * ups * QM_Q4K_ITEM_BYTES);
+            dn.units_total = ups;
+            dn.parts = W * S;
+            dn.part = part;
+            dn.cta0 = g * G;
+            dn.nctas = G;
+            dn.q = dn.tiles / G;
+            dn.rem = dn.tiles % G;
+            dn.ssq_out = (float *)(uintptr_t)b.ssq_dn;
+            dn.tp_shared = 1;
+        }
+    for (const QmOp &op : ops)
+        if ((int64_t)op.tiles * op.units >= (1ll << 31)) return QM_ERR_SHAPE;
+    CUdeviceptr sync = 0;
+    DRV(c->drv->cuMemAlloc_v2(&sync, 256));
+    int32_t rc = upload_ops(c, s, m, ops);
+    if (rc) {
+        c->drv->cuMemFree_v2(sync);
+        return rc;
+    }
+    s->fused_nops[m] = (int)(ops.size() / (size_t)S / 2);   // per list; upload_ops appended the copies for the other arena half
+    s->fused_ngroups[m] = S;
+    s->img_dev[m] = 0;
+    s->sync_dev[m] = sync;
+    s->sync_bytes[m] = 256;
+    s->img_units[m] = max_units;
+    s->fused_ncross[m] = 1;
+    s->fused_img[m] = false;
+    s->fused_dd[m] = true;
+    s->fused_dd_kernel[m] = kernel;
+    s->fused_parts_o[m] = W;
+    s->fused_parts_dn[m] = W * S;
     s->fused_plan[m] = p;
     return QM_OK;
 }
@@ -797,6 +943,7 @@ static int32_t enqueue_layers(qm_ctx *c, qm_stack *s, int m, int upto_layers) {
 
 // The data-driven form where the step qualifies, else the form with grid barriers.
 static int32_t build_any(qm_ctx *c, qm_stack *s, int m) {
+    if (s->tp_paired) return build_fused_paired(c, s, m);
     int32_t rc = build_fused_dd(c, s, m);
     if (rc == QM_ERR_SHAPE) rc = build_fused(c, s, m);
     return rc;

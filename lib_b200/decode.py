@@ -1,7 +1,6 @@
 """Runners of the decode step used by the benchmark and the tests: a single-GPU
-runner over `qm_stack`, and a tensor-parallel runner that shards every matrix by
-output rows over the ranks of a torch.distributed (NCCL) group and all-gathers
-the output slices.
+runner over `qm_stack`, the tensor-parallel runner over peer memory (row-sharded or
+paired), and an older runner that all-gathers row slices with NCCL (kept as a comparison).
 
 Weights are seeded synthetic tensors (lib_b200.synth); q, k, v and gate, up are
 generated as separate tensors and written into one store entry by rows, the way
@@ -93,20 +92,53 @@ class SingleGpuDecode:
             w.free()
 
 
-class PeerTensorParallelDecode:
-    """Row-sharded decode step as ONE persistent launch per GPU (qm_stack_create_tp): rank r
-    holds rows [r*N/g, (r+1)*N/g) of every matrix and stores its slice of each matvec straight
-    into all peers' activation buffers over NVLink; consumers poll their own arena for the words
-    they read, so no barrier crosses the GPUs inside a step (one ends it). torch.distributed only
-    carries the 64-byte IPC handles at set-up."""
+def column_shard(fmt, rows, cols, data, col_lo, col_hi):
+    """GGUF bytes of the columns [col_lo, col_hi) of a rows x cols tensor: for every row the blocks of that range."""
+    be, bb = synth.BLOCK[fmt]
+    a = np.asarray(data, dtype=np.uint8).reshape(rows, cols // be * bb)
+    return np.ascontiguousarray(a[:, col_lo // be * bb:col_hi // be * bb]).reshape(-1)
 
-    def __init__(self, ctx, layers, hidden, kv, ffn, fmt, seed, rank, world, m_max=8, barrier=True):
+
+def upload_row_slices(ctx, fmt, cols, tensors, rank, world):
+    """One store entry: slice `rank` of the rows of every tensor in `tensors` [(rows, bytes)], stacked in order."""
+    be, bb = synth.BLOCK[fmt]
+    row_bytes = cols // be * bb
+    w = ctx.store_create(fmt, sum(r for r, _ in tensors) // world, cols)
+    off = 0
+    for rows, data in tensors:
+        lo, hi = shard_range(rows, rank, world)
+        w.write_rows(off, hi - lo, data[lo * row_bytes:hi * row_bytes])
+        off += hi - lo
+    return w
+
+
+class PeerTensorParallelDecode:
+    """Tensor-parallel decode step as ONE persistent launch per GPU. Every rank stores its results straight
+    into the peers' activation buffers over NVLink; consumers poll their own arena for the words they read,
+    so no barrier crosses the GPUs inside a step (one ends it). torch.distributed only carries the 64-byte
+    IPC handles at set-up.
+    paired=False (qm_stack_create_tp): rank r holds rows [r*N/g, (r+1)*N/g) of every matrix; four exchanges
+    per layer. paired=True (qm_stack_create_tp_paired, up to four activation rows): q|k|v and gate|up by rows,
+    o and down by the K columns of the rank's own slices; two exchanges per layer."""
+
+    def __init__(self, ctx, layers, hidden, kv, ffn, fmt, seed, rank, world, m_max=8, barrier=True, paired=False):
         """barrier=False: the caller runs a collective of its own on all ranks before the first
         step (every rank must have mapped every arena before any rank stores into one)."""
         import torch.distributed as dist
-        self.ctx, self.hidden, self.rank, self.world = ctx, hidden, rank, world
-        self.stack = _capi.Stack(ctx, layers, hidden, kv, ffn, m_max, rank, world)
+        self.ctx, self.hidden, self.rank, self.world, self.paired = ctx, hidden, rank, world, paired
+        self.stack = _capi.Stack(ctx, layers, hidden, kv, ffn, m_max, rank, world, paired=paired)
         for L in range(layers):
+            if paired:
+                t = {n: (r, c, b) for n, r, c, b in layer_tensors(fmt, hidden, kv, ffn, seed, L)}
+                kvt = (2 * kv, np.concatenate([np.asarray(t["k"][2]), np.asarray(t["v"][2])]))   # k|v as one tensor of 2*kv rows
+                klo, khi = shard_range(hidden, rank, world)
+                flo, fhi = shard_range(ffn, rank, world)
+                ws = [upload_row_slices(ctx, fmt, hidden, [(hidden, t["q"][2]), kvt], rank, world),
+                      ctx.store_upload(fmt, hidden, khi - klo, column_shard(fmt, hidden, hidden, t["o"][2], klo, khi)),
+                      upload_row_slices(ctx, fmt, hidden, [(ffn, t["gate"][2]), (ffn, t["up"][2])], rank, world),
+                      ctx.store_upload(fmt, hidden, fhi - flo, column_shard(fmt, hidden, ffn, t["down"][2], flo, fhi))]
+                self.stack.set_layer(L, *ws)
+                continue
             ws = []
             for i, (rows, cols, parts) in enumerate(stacked(layer_tensors(fmt, hidden, kv, ffn, seed, L))):
                 lo, hi = shard_range(rows, rank, world)   # every matrix sliced by rows

@@ -1,6 +1,6 @@
-"""Tensor-parallel decode stack on two GPUs (every matrix sliced by rows, one persistent launch
-per GPU, output slices stored into the peer's buffers over NVLink and polled there) against the
-same stack on one GPU. Needs two visible GPUs; skipped otherwise. The ranks run as child processes and
+"""Tensor-parallel decode stack on two GPUs (one persistent launch per GPU, results stored into the
+peer's buffers over NVLink and polled there), in both shardings — every matrix by rows, and the paired
+form (q|k|v and gate|up by rows, o and down by K) — against the same stack on one GPU. Needs two visible GPUs; skipped otherwise. The ranks run as child processes and
 exchange the 64-byte IPC handles over a gloo group."""
 import os
 import socket
@@ -25,10 +25,13 @@ torch.cuda.set_device(rank)
 dist.init_process_group("gloo", rank=rank, world_size=world)
 ctx = lib_b200.Context(rank)
 layers, hidden, kv, ffn, fmt, seed = 3, 512, 128, 768, 12, 77
-tp = decode.PeerTensorParallelDecode(ctx, layers, hidden, kv, ffn, fmt, seed, rank, world)
+paired = os.environ.get("QM_TEST_PAIRED") == "1"
+if paired:
+    hidden, ffn = 512, 1024                    # K slices of o and down must be whole 256-column units
+tp = decode.PeerTensorParallelDecode(ctx, layers, hidden, kv, ffn, fmt, seed, rank, world, m_max=4 if paired else 8, paired=paired)
 one = decode.SingleGpuDecode(ctx, layers, hidden, kv, ffn, fmt, seed)
 ok = True
-for m in (1, 3, 8):
+for m in ((1, 3, 4) if paired else (1, 3, 8)):
     x = synth.activations(m, hidden, 300 + m)
     for rep in range(3):                       # several steps: the arena halves alternate, the epochs grow
         h = np.full((m, hidden), np.nan, np.float32)
@@ -48,7 +51,8 @@ os._exit(0 if ok else 1)
 '''
 
 
-def test_two_gpu_tensor_parallel_matches_single_gpu():
+@pytest.mark.parametrize("paired", [False, True], ids=["rows", "paired"])
+def test_two_gpu_tensor_parallel_matches_single_gpu(paired):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -58,7 +62,8 @@ def test_two_gpu_tensor_parallel_matches_single_gpu():
     s.close()
     procs = []
     for r in range(2):
-        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), QM_ROOT=ROOT)
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), QM_ROOT=ROOT,
+                   QM_TEST_PAIRED="1" if paired else "0")
         procs.append(subprocess.Popen([sys.executable, "-c", CHILD], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))
     outs = []

@@ -1225,6 +1225,9 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     do {                                                                                                          \
         if (a.debug == 9 && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && opi < 480)            \
             reinterpret_cast<unsigned long long *>(a.status + 16)[(opi * 2 + (blockIdx.x != 0)) * 4 + (k)] = gtime(); \
+        /* a.debug == 10: every CTA's stamps of the four ops of layer a.debug_slot */                             \
+        if (a.debug == 10 && tid == 0 && (opi >> 2) == a.debug_slot && gridDim.x <= 200)                          \
+            reinterpret_cast<unsigned long long *>(a.status + 16)[(((opi & 3) * gridDim.x) + blockIdx.x) * 4 + (k)] = gtime(); \
     } while (0)
 #else
 #define QM_DD_MARK(k) do { } while (0)

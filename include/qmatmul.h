@@ -194,7 +194,8 @@ QM_API int32_t qm_matmul_bf16(qm_ctx *ctx, qm_weight w, uint64_t a_dev, int32_t 
  * logit + bias (descending, ties to the lower index), weights = softmax over the selected
  * experts' UNBIASED logits (exp in double, rounded to float32, float32 sum in selection order).
  * logits float32 [tokens][ld], bias float32 [experts] or 0, ids int32 [tokens][topk],
- * weights float32 [tokens][topk]; experts <= 64. Device pointers, asynchronous. */
+ * weights float32 [tokens][topk]; experts <= 256 (the 256 routed experts of the reference's
+ * MoEConfig, lm/moe/moe.go). Device pointers, asynchronous. */
 QM_API int32_t qm_moe_route(qm_ctx *ctx, uint64_t logits_dev, int32_t tokens, int64_t ld, int32_t experts,
                             int32_t topk, uint64_t bias_dev, uint64_t ids_dev, uint64_t weights_dev);
 /* Grouped expert matmul over routed token lists (SwiGLU experts, Q4_K weights):

@@ -195,6 +195,8 @@ struct QmGemmArgs {
     int64_t wait_cycles;
 };
 
+#define QM_MAX_EXPERTS 256    // experts of a layer (router, dispatch lists, grouped matmuls); 64 per GPU in expert-parallel runs
+
 // Mixture-of-experts helpers (qm_moe.cu).
 struct QmRouteArgs {
     const float *logits;   // [tokens][ld]

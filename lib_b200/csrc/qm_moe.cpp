@@ -17,7 +17,7 @@ extern "C" int32_t qm_moe_route(qm_ctx *c, uint64_t logits_dev, int32_t tokens, 
                                 int32_t topk, uint64_t bias_dev, uint64_t ids_dev, uint64_t weights_dev) {
     CHECK_CTX(c);
     if (!logits_dev || !ids_dev || !weights_dev) return QM_ERR_ARG;
-    if (tokens < 0 || experts < 1 || experts > 64 || topk < 0 || topk > experts || ld < experts) return QM_ERR_SHAPE;
+    if (tokens < 0 || experts < 1 || experts > QM_MAX_EXPERTS || topk < 0 || topk > experts || ld < experts) return QM_ERR_SHAPE;
     if (tokens == 0 || topk == 0) return QM_OK;
     CtxGuard g(c);
     DRV(g.rc);
@@ -53,7 +53,7 @@ static int32_t ensure_ws3(qm_ctx *c, int64_t bytes) { return grow(c, &c->moe_ws3
 static int32_t check_experts(const qm_weight *gate_up, const qm_weight *down, int32_t experts,
                              std::vector<QmWeight *> &wg, std::vector<QmWeight *> &wd, int64_t *hidden, int64_t *ffn) {
     if (!gate_up || !down) return QM_ERR_ARG;
-    if (experts < 1 || experts > 64) return QM_ERR_SHAPE;
+    if (experts < 1 || experts > QM_MAX_EXPERTS) return QM_ERR_SHAPE;
     wg.resize(experts);
     wd.resize(experts);
     for (int e = 0; e < experts; e++) {
@@ -83,7 +83,7 @@ static int32_t dispatch_impl(qm_ctx *c, uint64_t ids_dev, int32_t tokens, int32_
                              int32_t *counts_host, CUdeviceptr *offsets_dev_out) {
     CHECK_CTX(c);
     if (!ids_dev || !x_bf16_dev || !rows_dev || !pos_dev) return QM_ERR_ARG;
-    if (experts < 1 || experts > 64 || tokens < 0 || topk < 1 || hidden < 8 || (hidden & 7) || ldx < hidden ||
+    if (experts < 1 || experts > QM_MAX_EXPERTS || tokens < 0 || topk < 1 || hidden < 8 || (hidden & 7) || ldx < hidden ||
         (x_bf16_dev & 15) || (rows_dev & 15) || ((ldx * 2) & 15))
         return QM_ERR_SHAPE;
     for (int e = 0; e < experts && counts_host; e++) counts_host[e] = 0;
@@ -91,8 +91,8 @@ static int32_t dispatch_impl(qm_ctx *c, uint64_t ids_dev, int32_t tokens, int32_
     CtxGuard g(c);
     DRV(g.rc);
     const int64_t pairs = (int64_t)tokens * topk;
-    const int64_t o_rank = 0, o_counts = up256(pairs * 4), o_offsets = o_counts + 256, o_list = o_offsets + 512,
-                  total = o_list + up256(pairs * 4);
+    const int64_t o_rank = 0, o_counts = up256(pairs * 4), o_offsets = o_counts + up256(QM_MAX_EXPERTS * 4),
+                  o_list = o_offsets + up256((QM_MAX_EXPERTS + 1) * 4), total = o_list + up256(pairs * 4);
     int32_t rc = ensure_ws(c, total);
     if (rc) return rc;
     const CUdeviceptr ws = c->moe_ws;
@@ -112,7 +112,7 @@ static int32_t dispatch_impl(qm_ctx *c, uint64_t ids_dev, int32_t tokens, int32_
     if (offsets_dev_out) *offsets_dev_out = ws + o_offsets;
     int rows = (int)pairs;   // every pair names an expert, so the lists hold all pairs
     if (counts_host) {
-        int32_t offsets[65];
+        int32_t offsets[QM_MAX_EXPERTS + 1];
         DRV(c->drv->cuMemcpyDtoHAsync_v2(offsets, ws + o_offsets, (size_t)(experts + 1) * 4, c->stream));
         DRV(c->drv->cuStreamSynchronize(c->stream));
         rows = offsets[experts];
@@ -146,11 +146,12 @@ extern "C" int32_t qm_moe_dispatch(qm_ctx *c, uint64_t ids_dev, int32_t tokens, 
 static int32_t experts_launch(qm_ctx *c, const std::vector<QmWeight *> &wg, const std::vector<QmWeight *> &wd,
                               int32_t experts, uint64_t rows_bf16_dev, int64_t rows, int32_t longest, int32_t typical,
                               CUdeviceptr offsets_dev, uint64_t y_dev, int64_t hidden, int64_t ffn) {
-    const int64_t o_h = 0, o_gl = up256(rows * ffn * 2) + 512, o_dl = o_gl + 512, total = o_dl + 512;
+    const int64_t o_h = 0, o_gl = up256(rows * ffn * 2) + up256((QM_MAX_EXPERTS + 1) * 4), o_dl = o_gl + QM_MAX_EXPERTS * 8,
+                  total = o_dl + QM_MAX_EXPERTS * 8;
     int32_t rc = ensure_ws2(c, total);
     if (rc) return rc;
     const CUdeviceptr ws = c->moe_ws2;
-    uint64_t lists[2][64];
+    uint64_t lists[2][QM_MAX_EXPERTS];
     for (int e = 0; e < experts; e++) {
         lists[0][e] = (uint64_t)wg[e]->wq;
         lists[1][e] = (uint64_t)wd[e]->wq;
@@ -188,7 +189,7 @@ extern "C" int32_t qm_moe_experts(qm_ctx *c, const qm_weight *gate_up, const qm_
     if ((rows_bf16_dev & 15) || (ffn & 127)) return QM_ERR_SHAPE;   // SwiGLU epilogue: whole 128-row tiles of gate rows
     int64_t rows = 0;
     int32_t longest = 0;
-    int32_t offsets[65];
+    int32_t offsets[QM_MAX_EXPERTS + 1];
     for (int e = 0; e < experts; e++) {
         if (counts_host[e] < 0) return QM_ERR_COUNT;
         offsets[e] = (int32_t)rows;
@@ -201,7 +202,7 @@ extern "C" int32_t qm_moe_experts(qm_ctx *c, const qm_weight *gate_up, const qm_
     CtxGuard g(c);
     DRV(g.rc);
     // workspace: the bf16 hidden activations, the offsets, then the two lists of weight stores
-    const int64_t o_off = up256(rows * ffn * 2), total = o_off + 3 * 512;
+    const int64_t o_off = up256(rows * ffn * 2), total = o_off + up256((QM_MAX_EXPERTS + 1) * 4) + 2 * QM_MAX_EXPERTS * 8;
     rc = ensure_ws2(c, total);
     if (rc) return rc;
     const CUdeviceptr ws = c->moe_ws2;
@@ -262,7 +263,7 @@ extern "C" int32_t qm_moe_grouped(qm_ctx *c, const qm_weight *gate_up, const qm_
     // (all pairs) and the CTAs beyond an expert's rows leave at once — no synchronization, but
     // those thousands of empty CTAs each hold an SM's shared memory for a moment (0.95 ms).
     if (!qm_env_int("QM_MOE_NOSYNC", 0)) {
-        int32_t counts[64];
+        int32_t counts[QM_MAX_EXPERTS];
         rc = qm_moe_dispatch(c, ids_dev, tokens, topk, experts, x_bf16_dev, ldx, (int32_t)hidden, ws + o_rows, ws + o_pos,
                              counts);
         if (rc) return rc;
@@ -513,7 +514,7 @@ extern "C" int32_t qm_ep_create(qm_ctx *c, const qm_weight *gate_up, const qm_we
     if (!out) return QM_ERR_ARG;
     *out = nullptr;
     if (world < 1 || world > QM_MAX_PEERS || rank < 0 || rank >= world || experts_local < 1 || experts_local > 64 ||
-        experts_total != experts_local * world || experts_total > 64 || topk < 1 || topk > experts_total ||
+        experts_total != experts_local * world || experts_total > QM_MAX_EXPERTS || topk < 1 || topk > experts_total ||
         max_tokens < 1 || (int64_t)max_tokens * topk >= (1 << 20))
         return QM_ERR_SHAPE;
     qm_ep *e = new (std::nothrow) qm_ep();
@@ -546,8 +547,8 @@ extern "C" int32_t qm_ep_create(qm_ctx *c, const qm_weight *gate_up, const qm_we
     int64_t o = 0;
     auto take = [&](int64_t bytes) { const int64_t at = o; o = up256(o + bytes); return at; };
     e->o_rankbuf = take(cap * 4);
-    e->o_lcounts = take(64 * 4);
-    e->o_offsets = take(65 * 4);
+    e->o_lcounts = take(QM_MAX_EXPERTS * 4);
+    e->o_offsets = take((QM_MAX_EXPERTS + 1) * 4);
     e->o_list = take(cap * 4);
     e->o_pos = take(cap * 4);
     e->o_compact = take(W * cap * H * 2);

@@ -20,17 +20,17 @@ extern "C" __global__ void __launch_bounds__(128) qm_moe_route(const __grid_cons
     const int n = a.experts, k = min(a.topk, n);
     int32_t *ids = a.ids + (int64_t)tok * a.topk;
     float *wts = a.weights + (int64_t)tok * a.topk;
-    unsigned long long taken = 0ull;   // experts <= 64
+    unsigned long long taken[QM_MAX_EXPERTS / 64] = {};   // one bit per expert
     float max_logit = 0.f;
     for (int s = 0; s < k; s++) {
         int best = -1;
         float best_score = 0.f;
         for (int e = 0; e < n; e++) {
-            if (taken >> e & 1ull) continue;
+            if (taken[e >> 6] >> (e & 63) & 1ull) continue;
             const float sc = __fadd_rn(lg[e], a.bias ? a.bias[e] : 0.f);
             if (best < 0 || sc > best_score) { best = e; best_score = sc; }   // strict: ties keep the lower index
         }
-        taken |= 1ull << best;
+        taken[best >> 6] |= 1ull << (best & 63);
         ids[s] = best;
         const float l = lg[best];
         if (s == 0 || l > max_logit) max_logit = l;
@@ -50,7 +50,7 @@ extern "C" __global__ void __launch_bounds__(128) qm_moe_route(const __grid_cons
 // pairs with ballots. counts[e], offsets[e] (exclusive prefix, written by warp 0 at the end),
 // list[] = pair index (token*topk + slot) grouped by expert, pos[pair] = row in that grouping.
 extern "C" __global__ void __launch_bounds__(1024) qm_moe_lists(const __grid_constant__ QmListArgs a) {
-    __shared__ int s_count[64];
+    __shared__ int s_count[QM_MAX_EXPERTS], s_off[QM_MAX_EXPERTS + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int npairs = a.tokens * a.topk;
     for (int e = warp; e < a.experts; e += blockDim.x >> 5) {
@@ -70,6 +70,7 @@ extern "C" __global__ void __launch_bounds__(1024) qm_moe_lists(const __grid_con
         for (int e = 0; e < a.experts; e++) {
             a.counts[e] = s_count[e];
             a.offsets[e] = off;
+            s_off[e] = off;
             off += s_count[e];
         }
         a.offsets[a.experts] = off;
@@ -78,9 +79,7 @@ extern "C" __global__ void __launch_bounds__(1024) qm_moe_lists(const __grid_con
     for (int pr = threadIdx.x; pr < npairs; pr += blockDim.x) {
         const int e = a.ids[pr];
         if (e < 0 || e >= a.experts) { a.pos[pr] = -1; continue; }   // names no expert: in no list
-        int off = 0;
-        for (int x = 0; x < e; x++) off += s_count[x];
-        const int p = off + a.rank[pr];
+        const int p = s_off[e] + a.rank[pr];
         a.pos[pr] = p;
         a.list[p] = pr;
     }

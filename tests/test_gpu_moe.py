@@ -128,3 +128,28 @@ def test_layer_stages_match_oracle(ctx):
     got = out.cpu().numpy().astype(np.float64)
     assert float(np.linalg.norm(got - want) / np.linalg.norm(want)) <= TOL
     layer.close()
+
+
+def test_router_and_dispatch_with_256_experts(ctx, devbuf):
+    """The reference's MoEConfig names 256 routed experts with 8 active: routing bit for bit against the oracle,
+    the per-expert lists against a stable sort of the pairs."""
+    g = np.random.Generator(np.random.Philox(key=11))
+    tokens, experts, topk, hidden = 96, 256, 8, 64
+    lg = g.standard_normal((tokens, experts), dtype=np.float32)
+    lg[::5, 200] = lg[::5, 17]          # exact ties across the 64-expert words of the taken mask
+    bias = (g.standard_normal(experts) * 0.3).astype(np.float32)
+    ids, w, ids_d, wts_d = route_gpu(ctx, devbuf, lg, experts, topk, bias=bias)
+    for t in range(tokens):
+        oi, ow = oracle.Route(lg[t], experts, topk, bias)
+        assert list(ids[t]) == list(oi)
+        assert np.array_equal(w[t].view(np.uint32), ow.view(np.uint32))
+    x = to_bf16_bits(synth.activations(tokens, hidden, 3))
+    rows_d, pos_d = devbuf(nbytes=tokens * topk * hidden * 2), devbuf(nbytes=tokens * topk * 4)
+    counts = ctx.moe_dispatch(ids_d.ptr, tokens, topk, experts, devbuf(x).ptr, hidden, hidden, rows_d.ptr, pos_d.ptr)
+    flat = ids.reshape(-1)
+    assert counts == [int((flat == e).sum()) for e in range(experts)]
+    order = np.argsort(flat, kind="stable")               # pairs grouped by expert, token order inside a group
+    rows = rows_d.get((tokens * topk, hidden), np.uint16)
+    assert np.array_equal(rows, x[order // topk])
+    pos = pos_d.get((tokens * topk,), np.int32)
+    assert np.array_equal(pos[order], np.arange(tokens * topk))

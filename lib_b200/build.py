@@ -46,7 +46,7 @@ def _run(cmd):
 def _describe(src, cubin, ptxas_log):
     """Kernel table for Go callers that load the cubin through nvidia/driver."""
     text = open(src).read()
-    names = re.findall(r'QM_(?:GEMV|DD|KQ|DD_SEL|LEAN)_KERNEL\((\w+),', text) + re.findall(
+    names = re.findall(r'QM_(?:GEMV|DD|KQ|DD_SEL|LEAN|DD8)_KERNEL\((\w+),', text) + re.findall(
         r'extern "C" __global__ void\s+(?:__launch_bounds__\([^)]*\)\s*)?(\w+)\(', text)
     res = {}
     cur = None

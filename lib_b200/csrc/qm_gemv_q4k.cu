@@ -945,11 +945,11 @@ __device__ __forceinline__ void cp_async_wait_n() {
 // adds the partial vectors of a producer that ran in K parts, applies the input transform and
 // quantizes into limb planes, sub-block sums and column weights; leaves each warp's part of the
 // sums of squares in ssq. Returns the thread's "gave up waiting" flag.
-template <int CPM, bool TP>
+template <int CPM, bool TP, int NT = 1>
 __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, uint8_t *xs, int plane_stride,
                                       uint32_t *xsum, float *sxw, float *ssq, bool dead) {
     const QmFusedArgs &a = *ap;
-    constexpr int C = 16, NL = CPM == 4 ? 3 : 2, NT = 1;
+    constexpr int C = 16, NL = CPM == 4 ? 3 : 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int M = a.m;
     const int nun = po->units, xop = po->xop;
@@ -1119,7 +1119,9 @@ __device__ __forceinline__ bool dd_stage(const QmFusedArgs *ap, const QmOp *po, 
 // poll their own arena only, so no barrier crosses the GPUs inside a step. One barrier over the
 // GPUs ends the launch: when it returns, every slice of the step has arrived everywhere, which
 // is what lets the host refill the other arena half with the "not yet written" pattern.
-template <int CPM, int D, bool TP, bool SEL = false>
+// NT = column tiles of eight mma columns: 1, or 2 with CPM = 2 for five to eight activation rows (each weight
+// fragment then feeds two mma, one per tile; the low- and high-nibble sums share one accumulator).
+template <int CPM, int D, bool TP, bool SEL = false, int NT = 1>
 __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     constexpr int C = 16;                       // warps per CTA
     constexpr int NL = CPM == 4 ? 3 : 2;        // limbs per activation row
@@ -1132,9 +1134,9 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     // ---- shared memory (qm_plan_fused computes an upper bound of this) -------------------------
     const int plane_stride = a.max_units * 256 + 64;
     uint8_t *xs = smem;                                                            // [P][plane_stride]
-    uint32_t *xsum = reinterpret_cast<uint32_t *>(xs + (size_t)P * plane_stride);   // [units][8][4] f16 pairs
-    float *sxw = reinterpret_cast<float *>(xsum + (size_t)a.max_units * 8 * 4);     // [units][8] column weights
-    float *ssq = sxw + (size_t)a.max_units * 8;                                     // [8][16]
+    uint32_t *xsum = reinterpret_cast<uint32_t *>(xs + (size_t)P * plane_stride);   // [units][8*NT][4] f16 pairs
+    float *sxw = reinterpret_cast<float *>(xsum + (size_t)a.max_units * 8 * NT * 4);   // [units][8*NT] column weights
+    float *ssq = sxw + (size_t)a.max_units * 8 * NT;                                // [8][16]
     float *slots = ssq + 8 * 16;                                                    // [C][2][M*16]
     QmOp *sop = reinterpret_cast<QmOp *>(((uintptr_t)(slots + (size_t)C * 2 * M * 16) + 15) & ~(uintptr_t)15);   // [2], or [nops] inline
     uint8_t *stages = reinterpret_cast<uint8_t *>(((uintptr_t)(sop + (inl ? QM_MAX_INLINE_OPS : 2)) + 127) & ~(uintptr_t)127);
@@ -1142,7 +1144,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
 
     asm volatile("griddepcontrol.launch_dependents;");
     // columns of absent activation rows and pad columns must read as zero weights and sums
-    for (int i = tid; i < a.max_units * 8 * 5; i += C * 32) xsum[i] = 0u;   // xsum and sxw are adjacent
+    for (int i = tid; i < a.max_units * 8 * NT * 5; i += C * 32) xsum[i] = 0u;   // xsum and sxw are adjacent
     // inline ops: all of them into shared memory, where the producer side reads ahead too
     if (inl)
         for (int i = tid; i < a.nops * (int)(sizeof(QmOp) / 16); i += C * 32)
@@ -1213,6 +1215,9 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
     const int col_row = g / CPM, col_limb = g - col_row * CPM;
     const bool col_on = col_row < M && col_limb < NL;
     const uint8_t *bplane = xs + (size_t)(col_on ? col_row * NL + col_limb : 0) * plane_stride + t * 16;
+    // second column tile (NT == 2): mma column 8 + g = limb (g % 2) of activation row 4 + g / 2
+    const bool col2_on = NT == 2 && 4 + g / 2 < M;
+    const uint8_t *bplane2 = xs + (size_t)(col2_on ? (4 + g / 2) * NL + (g & 1) : 0) * plane_stride + t * 16;
     // byte selector that brings the minima of sub-blocks 2t and 2t+1 (of the eight in two words)
     // to the low half of a word
     const uint32_t min_sel = (uint32_t)(2 * t) | ((uint32_t)(2 * t + 1) << 4) | 0x4400u;
@@ -1253,18 +1258,42 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         const int cta_in_grp = (int)blockIdx.x - po->cta0;
 
         // ---- stage x: poll until written, quantize into limbs --------------------------------------
-        dead = dd_stage<CPM, TP>(&a, po, xs, plane_stride, xsum, sxw, ssq, dead);
+        dead = dd_stage<CPM, TP, NT>(&a, po, xs, plane_stride, xsum, sxw, ssq, dead);
         __syncthreads();
         QM_DD_MARK(1);
         if (!inl && warp == C - 1 && opi + 1 < a.nops && lane < (int)(sizeof(QmOp) / 16))
             reinterpret_cast<uint4 *>(&sop[(opi + 1) & 1])[lane] = __ldg(reinterpret_cast<const uint4 *>(ops + opi + 1) + lane);
 
         // RMS normalisation is a scalar per activation row: it multiplies the finished sums
-        float myscale = 1.f;
+        float myscale = 1.f, myscale2 = 1.f;   // myscale2: the row of the second column tile
         if (norm) {
             const float inv_cols = 1.f / (float)po->cols;
             const float *ssq_in = po->ssq_in;
             float *ssq_out = po->ssq_out;
+            // The words of a producer that ran in K parts (its sums of squares per part and row): every lane
+            // polls ONE word — part lane / 8 (and that plus four, with more than four parts), row lane % 8 —
+            // so that all of them cost one trip to L2, not one each.
+            float ssq_w0 = 0.f, ssq_w1 = 0.f;
+            if (ssq_in && parts == 1) {
+                auto poll_word = [&](int k) -> float {
+                    float part;
+                    long long t0 = 0;
+                    for (;;) {
+                        if (TP) asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + (lane & 7)) : "memory");
+                        else asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + (lane & 7)) : "memory");
+                        if (__float_as_uint(part) != kUnwritten || dead) break;
+                        if (t0 == 0) t0 = clock64();
+                        else if (clock64() - t0 > a.wait_cycles) {
+                            atomicOr(a.status, QM_STATUS_TIMEOUT);
+                            dead = true;
+                        }
+                    }
+                    return part;
+                };
+                if ((lane >> 3) < x_parts && (lane & 7) < M) ssq_w0 = poll_word(lane >> 3);
+                if (TP && (lane >> 3) + 4 < x_parts && (lane & 7) < M) ssq_w1 = poll_word((lane >> 3) + 4);
+                __syncwarp();
+            }
             for (int j = 0; j < M; j++) {
                 float sq = ssq[j * 16 + (lane & 15)];   // the warps' parts, added as a fixed tree
 #pragma unroll
@@ -1287,26 +1316,15 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                 if (ssq_in) {
                     // x is c times the sum that was staged, c = rsqrt(ms + eps') of the producer's input:
                     // normalising c*v with eps equals normalising v with eps / c^2
-                    float ms = 0.f;
-                    long long t0 = 0;
-                    for (int k = 0; k < x_parts; k++) {
-                        float part;
-                        for (;;) {
-                            if (TP) asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + j) : "memory");
-                            else asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + j) : "memory");
-                            if (__float_as_uint(part) != kUnwritten || dead) break;
-                            if (t0 == 0) t0 = clock64();
-                            else if (clock64() - t0 > a.wait_cycles) {
-                                atomicOr(a.status, QM_STATUS_TIMEOUT);
-                                dead = true;
-                            }
-                        }
-                        ms += part;
-                    }
+                    float ms = 0.f;   // the parts in order: the same sum on every CTA and GPU
+                    for (int k = 0; k < x_parts && k < 4; k++) ms += __shfl_sync(0xffffffffu, ssq_w0, k * 8 + j);
+                    if (TP)
+                        for (int k = 4; k < x_parts; k++) ms += __shfl_sync(0xffffffffu, ssq_w1, (k - 4) * 8 + j);
                     eps *= ms * po->ssq_in_inv_cols + po->ssq_in_eps;
                 }
                 const float sc = rsqrtf(sq * inv_cols + eps);
                 if ((CPM == 4 ? (t >> 1) : t) == j) myscale = sc;
+                if (NT == 2 && 4 + t == j) myscale2 = sc;
             }
         }
 
@@ -1339,7 +1357,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         };
         // Ends a tile's segment [s0, s1) of this warp: stores the outputs if the warp had the whole
         // tile, else leaves its partial sums for the warp that reaches the tile's end.
-        auto flush = [&](int tile, int s0, int s1, const float (&accF)[4]) {
+        auto flush = [&](int tile, int s0, int s1, const float (&accF)[4], const float (&accF2)[4]) {
             float vA = accF[0] + accF[1], vB = accF[2] + accF[3];
             int jrow;
             bool valid;
@@ -1354,16 +1372,31 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             }
             vA *= myscale;
             vB *= myscale;
+            // second column tile: activation row 4 + t
+            float vA2 = 0.f, vB2 = 0.f;
+            const bool valid2 = NT == 2 && 4 + t < M;
+            if (NT == 2) {
+                vA2 = (accF2[0] + accF2[1]) * myscale2;
+                vB2 = (accF2[2] + accF2[3]) * myscale2;
+            }
             const bool from_start = s0 == tile * nun, to_end = s1 == tile * nun + nun;
             if (from_start && to_end) {
                 const int rA = (tile0 + tile) * 16 + g, rB = rA + 8;
-                if (valid) {
+                if (valid || valid2) {
                     const int split = TP ? po->split_row : 0;
                     const bool second = TP && split > 0 && (tile0 + tile) * 16 >= split;   // whole tiles on either side
-                    float *yA = (second ? po->y2 - split : opy) + (int64_t)jrow * ldy + rA;
+                    float *y0 = (second ? po->y2 - split : opy) + rA;
                     const bool share = TP && (po->tp_shared & (second ? 2 : 1)) != 0;
-                    if (rA < rows) store_y(yA, vA, share);
-                    if (rB < rows) store_y(yA + 8, vB, share);
+                    if (valid) {
+                        float *yA = y0 + (int64_t)jrow * ldy;
+                        if (rA < rows) store_y(yA, vA, share);
+                        if (rB < rows) store_y(yA + 8, vB, share);
+                    }
+                    if (valid2) {
+                        float *yA = y0 + (int64_t)(4 + t) * ldy;
+                        if (rA < rows) store_y(yA, vA2, share);
+                        if (rB < rows) store_y(yA + 8, vB2, share);
+                    }
                 }
                 return;
             }
@@ -1371,6 +1404,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
             // its end, so this warp adds the tile up after the barrier
             float *p = slots + ((size_t)warp * 2 + (to_end ? 0 : 1)) * M * 16;
             if (valid) { p[jrow * 16 + g] = vA; p[jrow * 16 + g + 8] = vB; }
+            if (valid2) { p[(4 + t) * 16 + g] = vA2; p[(4 + t) * 16 + g + 8] = vB2; }
             if (to_end) fin_tile = tile;
         };
 
@@ -1380,10 +1414,10 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         for (int i = lo; i < hi;) {
             const int tile = i / nun, u0 = i - tile * nun;
             const int seg_end = min(hi, (tile + 1) * nun);
-            float accF[4] = {0.f, 0.f, 0.f, 0.f};
+            float accF[4] = {0.f, 0.f, 0.f, 0.f}, accF2[4] = {0.f, 0.f, 0.f, 0.f};
             bp = bplane + (size_t)u0 * 256;
-            cwp = sxw + (size_t)u0 * 8 + 2 * t;
-            bmp = xsum + (size_t)u0 * 32 + g * 4 + t;
+            cwp = sxw + (size_t)u0 * 8 * NT + 2 * t;
+            bmp = xsum + (size_t)u0 * 32 * NT + g * 4 + t;
             for (int k = i; k < seg_end; k++) {
                 cp_async_wait_n<D - 1>();   // the oldest of the D groups in flight is this item
                 __syncwarp();               // ... and every lane's copies of it have landed
@@ -1395,59 +1429,109 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
                 const uint32_t scB0 = hB.y & 0x3F3F3F3Fu, scB1 = (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u);
                 const uint32_t mnA0 = hA.z & 0x3F3F3F3Fu, mnA1 = ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u);
                 const uint32_t mnB0 = hB.z & 0x3F3F3F3Fu, mnB1 = ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u);
-                int accL[4] = {0, 0, 0, 0}, accH[4] = {0, 0, 0, 0};   // low-nibble / high-nibble sub-blocks
-                const uint8_t *rowA = stage + 256 + 32 * g + 8 * t;
+                if constexpr (NT == 1) {
+                    int accL[4] = {0, 0, 0, 0}, accH[4] = {0, 0, 0, 0};   // low-nibble / high-nibble sub-blocks
+                    const uint8_t *rowA = stage + 256 + 32 * g + 8 * t;
+    #pragma unroll
+                    for (int p = 0; p < 4; p++) {
+                        const uint2 wA = *reinterpret_cast<const uint2 *>(rowA + 512 * p);
+                        const uint2 wB = *reinterpret_cast<const uint2 *>(rowA + 512 * p + 256);
+                        const uint4 b = *reinterpret_cast<const uint4 *>(bp + 64 * p);
+                        // sub-block 2p in the low nibbles, 2p+1 in the high ones (left in place: x16)
+                        const int sAl = (int)__byte_perm(p < 2 ? scA0 : scA1, 0, 0x4440 + ((2 * p) & 3));
+                        const int sAh = (int)__byte_perm(p < 2 ? scA0 : scA1, 0, 0x4440 + ((2 * p + 1) & 3));
+                        const int sBl = (int)__byte_perm(p < 2 ? scB0 : scB1, 0, 0x4440 + ((2 * p) & 3));
+                        const int sBh = (int)__byte_perm(p < 2 ? scB0 : scB1, 0, 0x4440 + ((2 * p + 1) & 3));
+                        int S[4];
+                        mma_u8s8(S, wA.x & 0x0F0F0F0Fu, wB.x & 0x0F0F0F0Fu, wA.y & 0x0F0F0F0Fu, wB.y & 0x0F0F0F0Fu, b.x, b.y);
+                        accL[0] += sAl * S[0];
+                        accL[1] += sAl * S[1];
+                        accL[2] += sBl * S[2];
+                        accL[3] += sBl * S[3];
+                        mma_u8s8(S, wA.x & 0xF0F0F0F0u, wB.x & 0xF0F0F0F0u, wA.y & 0xF0F0F0F0u, wB.y & 0xF0F0F0F0u, b.z, b.w);
+                        accH[0] += sAh * S[0];
+                        accH[1] += sAh * S[1];
+                        accH[2] += sBh * S[2];
+                        accH[3] += sBh * S[3];
+                    }
+                    // ---- minima: one f16 mma against the sub-block sums of the activations -----------------
+                    const uint32_t mpA = hsub2(__byte_perm(__byte_perm(mnA0, mnA1, min_sel), 0x64646464u, 0x4140), 0x64006400u);
+                    const uint32_t mpB = hsub2(__byte_perm(__byte_perm(mnB0, mnB1, min_sel), 0x64646464u, 0x4140), 0x64006400u);
+                    float accM[4];
+                    mma_f16(accM, mpA, mpB, *bmp);
+                    // ---- per-unit float32 scaling -------------------------------------------------------
+                    const float2 ddA = __half22float2(*reinterpret_cast<const __half2 *>(&hA.x));   // d, dmin of row g
+                    const float2 ddB = __half22float2(*reinterpret_cast<const __half2 *>(&hB.x));
+                    const float2 cw = *reinterpret_cast<const float2 *>(cwp);
+                    // even column: first limb / high half of the sums, weight sx; odd column: second limb /
+                    // low half, weight sx/128; the sums are in units of 127*sx. The column weights come
+                    // divided by 16: the integer sums are taken as 16*low + high (below 2^29).
+                    const float mx = 2032.f * cw.x, my = 260096.f * cw.y;
+                    const float f0 = (float)(accL[0] * 16 + accH[0]), f1 = (float)(accL[1] * 16 + accH[1]);
+                    const float f2 = (float)(accL[2] * 16 + accH[2]), f3 = (float)(accL[3] * 16 + accH[3]);
+                    accF[0] = fmaf(ddA.x * cw.x, f0, fmaf(-ddA.y * mx, accM[0], accF[0]));
+                    accF[1] = fmaf(ddA.x * cw.y, f1, fmaf(-ddA.y * my, accM[1], accF[1]));
+                    accF[2] = fmaf(ddB.x * cw.x, f2, fmaf(-ddB.y * mx, accM[2], accF[2]));
+                    accF[3] = fmaf(ddB.x * cw.y, f3, fmaf(-ddB.y * my, accM[3], accF[3]));
+                } else {
+                    // Two column tiles: every weight fragment feeds two mma. One integer accumulator per output:
+                    // the low-nibble sums enter with their scale times 16 (the high nibbles stay in place, x16).
+                    int acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+                    const uint8_t *rowA = stage + 256 + 32 * g + 8 * t;
+                    const uint8_t *bp2 = bplane2 + (bp - bplane);
 #pragma unroll
-                for (int p = 0; p < 4; p++) {
-                    const uint2 wA = *reinterpret_cast<const uint2 *>(rowA + 512 * p);
-                    const uint2 wB = *reinterpret_cast<const uint2 *>(rowA + 512 * p + 256);
-                    const uint4 b = *reinterpret_cast<const uint4 *>(bp + 64 * p);
-                    // sub-block 2p in the low nibbles, 2p+1 in the high ones (left in place: x16)
-                    const int sAl = (int)__byte_perm(p < 2 ? scA0 : scA1, 0, 0x4440 + ((2 * p) & 3));
-                    const int sAh = (int)__byte_perm(p < 2 ? scA0 : scA1, 0, 0x4440 + ((2 * p + 1) & 3));
-                    const int sBl = (int)__byte_perm(p < 2 ? scB0 : scB1, 0, 0x4440 + ((2 * p) & 3));
-                    const int sBh = (int)__byte_perm(p < 2 ? scB0 : scB1, 0, 0x4440 + ((2 * p + 1) & 3));
-                    int S[4];
-                    mma_u8s8(S, wA.x & 0x0F0F0F0Fu, wB.x & 0x0F0F0F0Fu, wA.y & 0x0F0F0F0Fu, wB.y & 0x0F0F0F0Fu, b.x, b.y);
-                    accL[0] += sAl * S[0];
-                    accL[1] += sAl * S[1];
-                    accL[2] += sBl * S[2];
-                    accL[3] += sBl * S[3];
-                    mma_u8s8(S, wA.x & 0xF0F0F0F0u, wB.x & 0xF0F0F0F0u, wA.y & 0xF0F0F0F0u, wB.y & 0xF0F0F0F0u, b.z, b.w);
-                    accH[0] += sAh * S[0];
-                    accH[1] += sAh * S[1];
-                    accH[2] += sBh * S[2];
-                    accH[3] += sBh * S[3];
+                    for (int p = 0; p < 4; p++) {
+                        const uint2 wA = *reinterpret_cast<const uint2 *>(rowA + 512 * p);
+                        const uint2 wB = *reinterpret_cast<const uint2 *>(rowA + 512 * p + 256);
+                        const int sAl = (int)__byte_perm(p < 2 ? scA0 : scA1, 0, 0x4440 + ((2 * p) & 3)) << 4;
+                        const int sAh = (int)__byte_perm(p < 2 ? scA0 : scA1, 0, 0x4440 + ((2 * p + 1) & 3));
+                        const int sBl = (int)__byte_perm(p < 2 ? scB0 : scB1, 0, 0x4440 + ((2 * p) & 3)) << 4;
+                        const int sBh = (int)__byte_perm(p < 2 ? scB0 : scB1, 0, 0x4440 + ((2 * p + 1) & 3));
+                        const uint32_t a0l = wA.x & 0x0F0F0F0Fu, a1l = wB.x & 0x0F0F0F0Fu, a2l = wA.y & 0x0F0F0F0Fu, a3l = wB.y & 0x0F0F0F0Fu;
+                        const uint32_t a0h = wA.x & 0xF0F0F0F0u, a1h = wB.x & 0xF0F0F0F0u, a2h = wA.y & 0xF0F0F0F0u, a3h = wB.y & 0xF0F0F0F0u;
+#pragma unroll
+                        for (int ct = 0; ct < 2; ct++) {
+                            const uint4 b = *reinterpret_cast<const uint4 *>((ct ? bp2 : bp) + 64 * p);
+                            int S[4];
+                            mma_u8s8(S, a0l, a1l, a2l, a3l, b.x, b.y);
+                            acc[ct][0] += sAl * S[0];
+                            acc[ct][1] += sAl * S[1];
+                            acc[ct][2] += sBl * S[2];
+                            acc[ct][3] += sBl * S[3];
+                            mma_u8s8(S, a0h, a1h, a2h, a3h, b.z, b.w);
+                            acc[ct][0] += sAh * S[0];
+                            acc[ct][1] += sAh * S[1];
+                            acc[ct][2] += sBh * S[2];
+                            acc[ct][3] += sBh * S[3];
+                        }
+                    }
+                    const uint32_t mpA = hsub2(__byte_perm(__byte_perm(mnA0, mnA1, min_sel), 0x64646464u, 0x4140), 0x64006400u);
+                    const uint32_t mpB = hsub2(__byte_perm(__byte_perm(mnB0, mnB1, min_sel), 0x64646464u, 0x4140), 0x64006400u);
+                    const float2 ddA = __half22float2(*reinterpret_cast<const __half2 *>(&hA.x));   // d, dmin of row g
+                    const float2 ddB = __half22float2(*reinterpret_cast<const __half2 *>(&hB.x));
+#pragma unroll
+                    for (int ct = 0; ct < 2; ct++) {
+                        float accM[4];
+                        mma_f16(accM, mpA, mpB, bmp[32 * ct]);
+                        const float2 cw = *reinterpret_cast<const float2 *>(cwp + 8 * ct);
+                        const float mx = 2032.f * cw.x, my = 260096.f * cw.y;
+                        float (&out)[4] = ct ? accF2 : accF;
+                        out[0] = fmaf(ddA.x * cw.x, (float)acc[ct][0], fmaf(-ddA.y * mx, accM[0], out[0]));
+                        out[1] = fmaf(ddA.x * cw.y, (float)acc[ct][1], fmaf(-ddA.y * my, accM[1], out[1]));
+                        out[2] = fmaf(ddB.x * cw.x, (float)acc[ct][2], fmaf(-ddB.y * mx, accM[2], out[2]));
+                        out[3] = fmaf(ddB.x * cw.y, (float)acc[ct][3], fmaf(-ddB.y * my, accM[3], out[3]));
+                    }
                 }
-                // ---- minima: one f16 mma against the sub-block sums of the activations -----------------
-                const uint32_t mpA = hsub2(__byte_perm(__byte_perm(mnA0, mnA1, min_sel), 0x64646464u, 0x4140), 0x64006400u);
-                const uint32_t mpB = hsub2(__byte_perm(__byte_perm(mnB0, mnB1, min_sel), 0x64646464u, 0x4140), 0x64006400u);
-                float accM[4];
-                mma_f16(accM, mpA, mpB, *bmp);
-                // ---- per-unit float32 scaling -------------------------------------------------------
-                const float2 ddA = __half22float2(*reinterpret_cast<const __half2 *>(&hA.x));   // d, dmin of row g
-                const float2 ddB = __half22float2(*reinterpret_cast<const __half2 *>(&hB.x));
-                const float2 cw = *reinterpret_cast<const float2 *>(cwp);
-                // even column: first limb / high half of the sums, weight sx; odd column: second limb /
-                // low half, weight sx/128; the sums are in units of 127*sx. The column weights come
-                // divided by 16: the integer sums are taken as 16*low + high (below 2^29).
-                const float mx = 2032.f * cw.x, my = 260096.f * cw.y;
-                const float f0 = (float)(accL[0] * 16 + accH[0]), f1 = (float)(accL[1] * 16 + accH[1]);
-                const float f2 = (float)(accL[2] * 16 + accH[2]), f3 = (float)(accL[3] * 16 + accH[3]);
-                accF[0] = fmaf(ddA.x * cw.x, f0, fmaf(-ddA.y * mx, accM[0], accF[0]));
-                accF[1] = fmaf(ddA.x * cw.y, f1, fmaf(-ddA.y * my, accM[1], accF[1]));
-                accF[2] = fmaf(ddB.x * cw.x, f2, fmaf(-ddB.y * mx, accM[2], accF[2]));
-                accF[3] = fmaf(ddB.x * cw.y, f3, fmaf(-ddB.y * my, accM[3], accF[3]));
                 bp += 256;
-                cwp += 8;
-                bmp += 32;
+                cwp += 8 * NT;
+                bmp += 32 * NT;
                 c_stage = c_stage + kStageBytes == my_stages + D * kStageBytes ? my_stages : c_stage + kStageBytes;
                 // every lane's reads of the slot have returned (their values were consumed above):
                 // after the warp converges the next copy may overwrite it
                 __syncwarp();
                 issue();
             }
-            flush(tile, i, seg_end, accF);
+            flush(tile, i, seg_end, accF, accF2);
             i = seg_end;
         }
         QM_DD_MARK(2);
@@ -1844,6 +1928,15 @@ QM_DD_KERNEL(qm_fused_q4k_dd_c4d4_tp, 4, 4, true)
 QM_DD_KERNEL(qm_fused_q4k_dd_c2d2_tp, 2, 2, true)
 QM_DD_KERNEL(qm_fused_q4k_dd_c2d3_tp, 2, 3, true)
 QM_DD_KERNEL(qm_fused_q4k_dd_c2d4_tp, 2, 4, true)
+
+// Five to eight activation rows: two column tiles (D = 2 or 3 stages: sixteen limb planes take the room of the fourth).
+#define QM_DD8_KERNEL(name, d)                                                               \
+    extern "C" __global__ void __launch_bounds__(QM_GEMV_MAX_THREADS, 1)                     \
+        name(const __grid_constant__ QmFusedArgs a) {                                        \
+        dd_body<2, d, false, false, 2>(a);                                                   \
+    }
+QM_DD8_KERNEL(qm_fused_q4k_dd_n2d2, 2)
+QM_DD8_KERNEL(qm_fused_q4k_dd_n2d3, 3)
 
 // One activation row per op and ops whose matrix is chosen on the device from a table of experts
 // (QmOp::sel_table): decode-time MoE as a list of (token, slot) matvecs.

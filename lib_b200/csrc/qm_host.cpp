@@ -111,6 +111,7 @@ static const KernelName kKernels[QM_K_COUNT] = {
     {QM_MOD_Q4K, "qm_gemv_q80_lean_c4d3"}, {QM_MOD_Q4K, "qm_gemv_q80_lean_c4d2"}, {QM_MOD_Q4K, "qm_gemv_q80_lean_c2d3"},
     {QM_MOD_Q4K, "qm_gemv_q80_lean_c2d2"}, {QM_MOD_Q4K, "qm_gemv_q80_lean_c2n2d3"}, {QM_MOD_Q4K, "qm_gemv_q80_lean_c2n2d2"},
     {QM_MOD_Q4K, "qm_lean_sum"},
+    {QM_MOD_Q4K, "qm_fused_q4k_dd_n2d2"}, {QM_MOD_Q4K, "qm_fused_q4k_dd_n2d3"},
 };
 
 // ---- errors --------------------------------------------------------------------------
@@ -200,6 +201,10 @@ extern "C" int32_t qm_init(int32_t device, qm_ctx **out) {
             for (int k = QM_K_GEMM_Q4K_R256; k <= QM_K_GEMM_Q4K_R256_K128 && r == CUDA_SUCCESS; k++)
                 r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
 
+            if (r != CUDA_SUCCESS) err = (int32_t)r;
+        }
+        for (int k = QM_K_FUSED_Q4K_DD_N2D2; k <= QM_K_FUSED_Q4K_DD_N2D3 && !err; k++) {
+            r = d->cuFuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, QM_GEMV_SMEM_MAX);
             if (r != CUDA_SUCCESS) err = (int32_t)r;
         }
         for (int k = QM_K_Q40_LEAN_C4D4; k <= QM_K_Q80_LEAN_C2N2D2 && !err; k++) {

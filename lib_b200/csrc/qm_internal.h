@@ -28,7 +28,7 @@ enum {
     QM_K_EP_PUSH, QM_K_EP_COLLECT, QM_K_EP_RETURN, QM_K_EP_COMBINE,
     QM_K_Q40_LEAN_C4D4, QM_K_Q40_LEAN_C4D2, QM_K_Q40_LEAN_C2D4, QM_K_Q40_LEAN_C2D2, QM_K_Q40_LEAN_C2N2D4, QM_K_Q40_LEAN_C2N2D2,
     QM_K_Q80_LEAN_C4D3, QM_K_Q80_LEAN_C4D2, QM_K_Q80_LEAN_C2D3, QM_K_Q80_LEAN_C2D2, QM_K_Q80_LEAN_C2N2D3, QM_K_Q80_LEAN_C2N2D2,
-    QM_K_LEAN_SUM, QM_K_COUNT
+    QM_K_LEAN_SUM, QM_K_FUSED_Q4K_DD_N2D2, QM_K_FUSED_Q4K_DD_N2D3, QM_K_COUNT
 };
 
 #define QM_GEMV_SMEM_MAX (227 * 1024)

@@ -459,7 +459,9 @@ static int32_t part_major_copy(qm_ctx *c, const QmWeight *w, int parts, CUdevice
 }
 
 static int32_t build_fused_dd(qm_ctx *c, qm_stack *s, int m) {
-    if (m >= qm_env_int("QM_IMAGE_MIN_M", 4) || qm_env_int("QM_DD", 1) == 0) return QM_ERR_SHAPE;
+    // up to three rows, and five to eight (two column tiles; single GPU); four rows run with activation images
+    const bool two_tiles = m > 4 && s->tp_world == 1 && qm_env_int("QM_DD8", 1) != 0;
+    if ((m >= qm_env_int("QM_IMAGE_MIN_M", 4) && !two_tiles) || qm_env_int("QM_DD", 1) == 0) return QM_ERR_SHAPE;
     const int grid = qm_fused_grid(c);
     // The down projection (long K: its CTAs would each quantize all 2 x 14336 activations) runs in
     // four K parts. The o projection stays whole by default: its x is short, and every part adds a
@@ -489,6 +491,13 @@ static int32_t build_fused_dd(qm_ctx *c, qm_stack *s, int m) {
     int kernel = -1;
     if (p.nt == 1 && p.consumers == 16 && p.depth >= 2 && p.depth <= 4)
         kernel = (p.cpm == 4 ? QM_K_FUSED_Q4K_DD_C4D2 : QM_K_FUSED_Q4K_DD_C2D2) + (p.depth - 2);
+    if (p.nt == 2 && p.consumers == 16 && p.depth >= 2) {
+        if (p.depth > 3) {   // the two-tile kernels exist with two and three stages
+            p.smem -= (p.depth - 3) * 16 * QM_Q4K_ITEM_BYTES;
+            p.depth = 3;
+        }
+        kernel = QM_K_FUSED_Q4K_DD_N2D2 + (p.depth - 2);
+    }
     if (kernel < 0) return QM_ERR_SHAPE;
     for (int L = 0; L < s->layers; L++) {
         QmLayer &ly = s->layer[L];

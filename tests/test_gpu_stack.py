@@ -43,7 +43,7 @@ def oracle_chain(fmt, raws, x, hidden, kv, ffn):
 
 
 @pytest.mark.parametrize("fmt", [12, 2, 8])
-@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("m", [1, 3, 5, 8])
 def test_small_stack_matches_oracle(ctx, fmt, m):
     layers, hidden, kv, ffn = 3, 512, 128, 1536
     st, raws = build_stack(ctx, layers, hidden, kv, ffn, fmt, seed=200)

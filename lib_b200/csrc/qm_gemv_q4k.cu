@@ -1257,8 +1257,39 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         const int parts = po->parts, x_parts = po->x_parts;
         const int cta_in_grp = (int)blockIdx.x - po->cta0;
 
+        const float *ssq_in = po->ssq_in;
+        // The words of a producer that ran in K parts (its sums of squares per part and row): every lane reads
+        // ONE word — part lane / 8 (and that plus four, with more than four parts), row lane % 8 — so that all of
+        // them cost one trip to L2, not one each; the loads are issued here and their values looked at after x has
+        // been staged (the producer published them when it started, long before its outputs).
+        float ssq_w0 = 0.f, ssq_w1 = 0.f;
+        const bool want_w0 = norm && ssq_in && parts == 1 && (lane >> 3) < x_parts && (lane & 7) < M;
+        const bool want_w1 = TP && norm && ssq_in && parts == 1 && (lane >> 3) + 4 < x_parts && (lane & 7) < M;
+        auto load_word = [&](int k) -> float {
+            float part;
+            if (TP) asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + (lane & 7)) : "memory");
+            else asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + (lane & 7)) : "memory");
+            return part;
+        };
+        if (want_w0) ssq_w0 = load_word(lane >> 3);
+        if (want_w1) ssq_w1 = load_word((lane >> 3) + 4);
         // ---- stage x: poll until written, quantize into limbs --------------------------------------
         dead = dd_stage<CPM, TP, NT>(&a, po, xs, plane_stride, xsum, sxw, ssq, dead);
+        {   // a word that had not been written yet: wait for it (bounded)
+            auto settle = [&](float &w, int k) {
+                long long t0 = 0;
+                while (__float_as_uint(w) == kUnwritten && !dead) {
+                    if (t0 == 0) t0 = clock64();
+                    else if (clock64() - t0 > a.wait_cycles) {
+                        atomicOr(a.status, QM_STATUS_TIMEOUT);
+                        dead = true;
+                    }
+                    w = load_word(k);
+                }
+            };
+            if (want_w0) settle(ssq_w0, lane >> 3);
+            if (want_w1) settle(ssq_w1, (lane >> 3) + 4);
+        }
         __syncthreads();
         QM_DD_MARK(1);
         if (!inl && warp == C - 1 && opi + 1 < a.nops && lane < (int)(sizeof(QmOp) / 16))
@@ -1268,32 +1299,7 @@ __device__ __forceinline__ void dd_body(const QmFusedArgs &a) {
         float myscale = 1.f, myscale2 = 1.f;   // myscale2: the row of the second column tile
         if (norm) {
             const float inv_cols = 1.f / (float)po->cols;
-            const float *ssq_in = po->ssq_in;
             float *ssq_out = po->ssq_out;
-            // The words of a producer that ran in K parts (its sums of squares per part and row): every lane
-            // polls ONE word — part lane / 8 (and that plus four, with more than four parts), row lane % 8 —
-            // so that all of them cost one trip to L2, not one each.
-            float ssq_w0 = 0.f, ssq_w1 = 0.f;
-            if (ssq_in && parts == 1) {
-                auto poll_word = [&](int k) -> float {
-                    float part;
-                    long long t0 = 0;
-                    for (;;) {
-                        if (TP) asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + (lane & 7)) : "memory");
-                        else asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(part) : "l"(ssq_in + k * 8 + (lane & 7)) : "memory");
-                        if (__float_as_uint(part) != kUnwritten || dead) break;
-                        if (t0 == 0) t0 = clock64();
-                        else if (clock64() - t0 > a.wait_cycles) {
-                            atomicOr(a.status, QM_STATUS_TIMEOUT);
-                            dead = true;
-                        }
-                    }
-                    return part;
-                };
-                if ((lane >> 3) < x_parts && (lane & 7) < M) ssq_w0 = poll_word(lane >> 3);
-                if (TP && (lane >> 3) + 4 < x_parts && (lane & 7) < M) ssq_w1 = poll_word((lane >> 3) + 4);
-                __syncwarp();
-            }
             for (int j = 0; j < M; j++) {
                 float sq = ssq[j * 16 + (lane & 15)];   // the warps' parts, added as a fixed tree
 #pragma unroll

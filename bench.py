@@ -279,8 +279,8 @@ def main():
     ap.add_argument("--no-other-configs", action="store_true", help="skip the short runs of the other configurations")
     ap.add_argument("--tp", choices=("auto", "paired", "rows"), default="auto",
                     help="sharding on several GPUs: paired (q|k|v, gate|up by rows; o, down by K; up to batch 4), every matrix "
-                         "by rows, or auto = paired up to four GPUs (measured 0.97 / 0.92 ms against 1.01 / 0.94 by rows on 2 / 4 "
-                         "GPUs) and rows beyond (8 GPUs: 0.92 against 1.10 ms: the consumers add one vector per GPU)")
+                         "by rows, or auto = paired where the batch allows (measured 0.96 / 0.85 / 0.87 ms against 0.98 / 0.92 / "
+                         "0.89 by rows on 2 / 4 / 8 GPUs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -311,7 +311,7 @@ def main():
         runner = decode.SingleGpuDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED)
         tp_mode = None
     else:
-        paired = (args.tp == "paired" or (args.tp == "auto" and world <= 4)) and m <= 4
+        paired = args.tp in ("paired", "auto") and m <= 4
         runner = decode.PeerTensorParallelDecode(ctx, layers, HIDDEN, KV, FFN, FMT, SEED, rank, world, m_max=4 if paired else 8,
                                                  barrier=False, paired=paired)
         tp_mode = ("paired: q|k|v and gate|up sliced by rows, o and down by the K columns of the rank's own slices; partial "

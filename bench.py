@@ -397,12 +397,13 @@ def main():
 
     pk, pk_kind = peaks()
     step_bytes = step_algorithmic_bytes(synth, m, layers)
-    gpu_bytes = step_bytes / world            # every matrix is sliced by rows: each GPU streams 1/N of the weights
+    gpu_bytes = step_bytes / world            # every matrix is sliced (by rows or by K): each GPU streams 1/N of the weights
     achieved = gpu_bytes / (ms * 1e-3) / 1e9  # per GPU
     kernel = ("qm_fused_q4k_dd_c4d4" if m == 1 else "qm_fused_q4k_dd_c4d3" if m == 2 else "qm_fused_q4k_dd_c2d3" if m == 3
-              else "qm_fused_q4k_nt1_img" if m == 4 else "qm_fused_q4k_nt2_img")
+              else "qm_fused_q4k_nt1_img" if m == 4 else "qm_fused_q4k_dd_n2d3")
     if world > 1:
-        kernel = kernel + "_tp" if m <= 3 else ("qm_fused_q4k_nt1_tp" if m == 4 else "qm_fused_q4k_nt2_tp")
+        kernel = kernel + "_tp" if m <= 3 else ("qm_fused_q4k_dd_c2d3_tp" if (m == 4 and getattr(runner, "paired", False))
+                                                else "qm_fused_q4k_nt1_tp" if m == 4 else "qm_fused_q4k_nt2_tp")
     line = {
         "metric": "decode_tokens_per_s", "value": m / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,

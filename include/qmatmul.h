@@ -209,7 +209,10 @@ QM_API int32_t qm_moe_route(qm_ctx *ctx, uint64_t logits_dev, int32_t tokens, in
  * down); ffn must be a multiple of 128. The list lengths are read back to the host once (one
  * stream synchronization inside the call) to size those launches; with QM_MOE_NOSYNC=1 in the
  * environment nothing is read back and the call is fully asynchronous (slower: the launches
- * then cover the longest possible lists). */
+ * then cover the longest possible lists). With QM_MOE_FOLD=1 the gate|up matmul gathers the
+ * tokens' rows itself (tile::gather4 copies that follow the dispatch list; needs x 16-byte aligned
+ * and ldx a multiple of 8) and no gathered copy is written: the same bits, no 2*pairs*hidden bytes
+ * of scratch traffic, but slower on large token tiles. */
 QM_API int32_t qm_moe_grouped(qm_ctx *ctx, const qm_weight *gate_up, const qm_weight *down, int32_t experts,
                               uint64_t x_bf16_dev, int32_t tokens, int64_t ldx, uint64_t ids_dev,
                               uint64_t weights_dev, int32_t topk, uint64_t out_dev, int64_t ldo);

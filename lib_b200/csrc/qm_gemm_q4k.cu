@@ -73,6 +73,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int 
         : "memory");
 }
 // K-major, 128-byte swizzle, 8-row groups 1024 bytes apart (sm_100 descriptor version 1)
+// Four rows (y0..y3) of a 2-D tensor, box columns starting at x, into four consecutive rows at dst.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void *tmap, int x, int y0, int y1, int y2, int y3,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
+        "l"(tmap), "r"(bar), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3)
+        : "memory");
+}
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
@@ -152,7 +160,33 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
+    if (warp == 0 && a.gather_list) {
+        // ---- activation chunks gathered by the rows' token numbers ----------------------------
+        // One tile::gather4 copy brings the 64-column chunk of four rows named by their row numbers
+        // in the tokens' own matrix (a tensor map with a one-row box) into four consecutive
+        // 128-byte rows of the swizzled tile; lane l issues the copies of row groups l, l+32, ...
+        int *tok = reinterpret_cast<int *>(tmem_slot + 6);   // 16-byte aligned
+        for (int r = lane; r < BN; r += 32)   // rows past the list read its last row; the epilogue drops them
+            tok[r] = a.gather_list[row_off + min(m0 + r, m_cnt - 1)] / a.gather_topk;
+        __syncwarp();
+        for (int kc = 0; kc < nk; kc++) {
+            const int s = kc % kStages;
+            const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
+            if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) {
+                if (lane == 0) atomicOr(a.status, QM_STATUS_TIMEOUT);
+                break;
+            }
+            if (lane == 0) mbar_expect_tx(full_b + 8 * s, (uint32_t)(KS * b_tile));
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < KS; j++)
+                for (int g4 = lane; g4 < BN / 4; g4 += 32) {
+                    const int4 t = *reinterpret_cast<const int4 *>(tok + 4 * g4);
+                    tma_gather4(smem_base + s * stage_bytes + a_bytes + j * b_tile + g4 * 512, &a.tmap_gather,
+                                ((kc_lo + kc) * KS + j) * kBK, t.x, t.y, t.z, t.w, full_b + 8 * s);
+                }
+        }
+    } else if (warp == 0) {
         // ---- activation chunks by TMA ---------------------------------------------------------
         if (lane == 0) {
             for (int kc = 0; kc < nk; kc++) {

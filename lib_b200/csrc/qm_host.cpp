@@ -1071,7 +1071,19 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
 #ifdef QM_DEBUG
     a.debug = env_int("QM_GEMM_DEBUG", 0);
 #endif
-    const unsigned smem = 1024 + stages * stage_bytes + 256;
+    unsigned smem = 1024 + stages * stage_bytes + 256;
+    if (g.gather_list_dev) {   // the loader warp's table of token numbers sits behind the barriers
+        if (!grouped || bn > 256 || g.gather_topk < 1) return QM_ERR_SHAPE;
+        a.gather_list = (const int32_t *)(uintptr_t)g.gather_list_dev;
+        a.gather_topk = g.gather_topk;
+        const cuuint32_t row_box[2] = {64, 1};   // tile::gather4 names the four rows itself
+        DRV(c->drv->cuTensorMapEncodeTiled(&a.tmap_gather, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)(uintptr_t)a_dev,
+                                           dims, strides, row_box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+        smem += 1024;
+        if (smem > QM_GEMV_SMEM_MAX) return QM_ERR_SHAPE;
+    }
     void *params[1] = {&a};
     CUlaunchConfig cfg;
     memset(&cfg, 0, sizeof cfg);

@@ -115,6 +115,10 @@ struct QmGemmGroup {
     bool swiglu;               // gate|up weights, output bf16 silu(gate)*up to h_dev
     CUdeviceptr h_dev;
     int64_t ldh;
+    // gather folded into the activation load: grouped row p is row list[p] / topk of a_dev
+    // [rows_total][lda] (the tokens as the caller holds them); 0: a_dev is already grouped
+    CUdeviceptr gather_list_dev;
+    int gather_topk;
 };
 int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, int64_t rows_total, int64_t lda,
                        uint64_t c_dev, int64_t ldc, const QmGemmGroup &g);

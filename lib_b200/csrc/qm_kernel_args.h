@@ -193,6 +193,12 @@ struct QmGemmArgs {
     float *partials;
     unsigned int *tickets;
     int64_t wait_cycles;
+    // Gather folded into the activation load (grouped launches): row p of the grouped order is row
+    // gather_list[p] / gather_topk of the tokens' own matrix, which tmap_gather describes with a box of
+    // 64 columns x 1 row; the loader warp fetches four rows per tile::gather4 copy.
+    const int32_t *gather_list;   // null: the activations are already grouped (tmap_act, tiled loads)
+    int32_t gather_topk, pad2;
+    alignas(64) CUtensorMap tmap_gather;
 };
 
 #define QM_MAX_EXPERTS 256    // experts of a layer (router, dispatch lists, grouped matmuls); 64 per GPU in expert-parallel runs

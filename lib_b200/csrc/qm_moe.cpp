@@ -80,9 +80,10 @@ static inline int64_t up256(int64_t v) { return (v + 255) & ~(int64_t)255; }
 // pairs and *offsets_dev_out names the device array [experts + 1] of list starts.
 static int32_t dispatch_impl(qm_ctx *c, uint64_t ids_dev, int32_t tokens, int32_t topk, int32_t experts,
                              uint64_t x_bf16_dev, int64_t ldx, int32_t hidden, uint64_t rows_dev, uint64_t pos_dev,
-                             int32_t *counts_host, CUdeviceptr *offsets_dev_out) {
+                             int32_t *counts_host, CUdeviceptr *offsets_dev_out, CUdeviceptr *list_dev_out = nullptr) {
     CHECK_CTX(c);
-    if (!ids_dev || !x_bf16_dev || !rows_dev || !pos_dev) return QM_ERR_ARG;
+    // list_dev_out: the caller's matmul fetches the rows by the list itself; nothing is copied here
+    if (!ids_dev || !x_bf16_dev || (!rows_dev && !list_dev_out) || !pos_dev) return QM_ERR_ARG;
     if (experts < 1 || experts > QM_MAX_EXPERTS || tokens < 0 || topk < 1 || hidden < 8 || (hidden & 7) || ldx < hidden ||
         (x_bf16_dev & 15) || (rows_dev & 15) || ((ldx * 2) & 15))
         return QM_ERR_SHAPE;
@@ -110,6 +111,7 @@ static int32_t dispatch_impl(qm_ctx *c, uint64_t ids_dev, int32_t tokens, int32_
     rc = qm_launch(c, QM_K_MOE_LISTS, 1, 1, 1024, 0, &la, false);
     if (rc) return rc;
     if (offsets_dev_out) *offsets_dev_out = ws + o_offsets;
+    if (list_dev_out) *list_dev_out = ws + o_list;
     int rows = (int)pairs;   // every pair names an expert, so the lists hold all pairs
     if (counts_host) {
         int32_t offsets[QM_MAX_EXPERTS + 1];
@@ -120,6 +122,7 @@ static int32_t dispatch_impl(qm_ctx *c, uint64_t ids_dev, int32_t tokens, int32_
         for (int e = 0; e < experts; e++) counts_host[e] = offsets[e + 1] - offsets[e];
         if (rows == 0) return QM_OK;
     }
+    if (list_dev_out) return QM_OK;
     QmGatherArgs ga;
     memset(&ga, 0, sizeof ga);
     ga.x = (const uint16_t *)(uintptr_t)x_bf16_dev;
@@ -145,7 +148,8 @@ extern "C" int32_t qm_moe_dispatch(qm_ctx *c, uint64_t ids_dev, int32_t tokens, 
 // bounds the list lengths (sizes the grid), `typical` chooses the token tile.
 static int32_t experts_launch(qm_ctx *c, const std::vector<QmWeight *> &wg, const std::vector<QmWeight *> &wd,
                               int32_t experts, uint64_t rows_bf16_dev, int64_t rows, int32_t longest, int32_t typical,
-                              CUdeviceptr offsets_dev, uint64_t y_dev, int64_t hidden, int64_t ffn) {
+                              CUdeviceptr offsets_dev, uint64_t y_dev, int64_t hidden, int64_t ffn,
+                              CUdeviceptr gather_list_dev = 0, int gather_topk = 0, int64_t x_rows = 0, int64_t ldx = 0) {
     const int64_t o_h = 0, o_gl = up256(rows * ffn * 2) + up256((QM_MAX_EXPERTS + 1) * 4), o_dl = o_gl + QM_MAX_EXPERTS * 8,
                   total = o_dl + QM_MAX_EXPERTS * 8;
     int32_t rc = ensure_ws2(c, total);
@@ -167,7 +171,14 @@ static int32_t experts_launch(qm_ctx *c, const std::vector<QmWeight *> &wg, cons
     grp.swiglu = true;
     grp.h_dev = ws + o_h;
     grp.ldh = ffn;
-    rc = qm_gemm_launch(c, wg[0], rows_bf16_dev, longest, rows, hidden, 0, 0, grp);
+    if (gather_list_dev) {   // rows_bf16_dev holds the tokens' rows as the caller has them; the matmul gathers
+        grp.gather_list_dev = gather_list_dev;
+        grp.gather_topk = gather_topk;
+        rc = qm_gemm_launch(c, wg[0], rows_bf16_dev, longest, x_rows, ldx, 0, 0, grp);
+        grp.gather_list_dev = 0;
+    } else {
+        rc = qm_gemm_launch(c, wg[0], rows_bf16_dev, longest, rows, hidden, 0, 0, grp);
+    }
     if (rc) return rc;
     grp.wq_list_dev = ws + o_dl;
     grp.swiglu = false;
@@ -262,7 +273,37 @@ extern "C" int32_t qm_moe_grouped(qm_ctx *c, const qm_weight *gate_up, const qm_
     // keeps everything on the device instead: the launches then cover the longest possible list
     // (all pairs) and the CTAs beyond an expert's rows leave at once — no synchronization, but
     // those thousands of empty CTAs each hold an SM's shared memory for a moment (0.95 ms).
-    if (!qm_env_int("QM_MOE_NOSYNC", 0)) {
+    // QM_MOE_FOLD=1: the gate|up matmul fetches each grouped row from the token's own row of x (its
+    // loader warp follows the dispatch list with tile::gather4 copies), so no gathered copy is written.
+    // Same bits as the separate gather pass (the matmul sees the same rows in the same order), but
+    // slower at the Mixtral shape: a gather4 copy moves 512 bytes and one SM completes one every ~26 ns,
+    // which is 20 GB/s per SM where the 256-token tiles want 51 GB/s (1.62 ms per layer against
+    // 0.82 ms; the same loader with 16-byte cp.async from one warp: 1.32 ms), while the pass it
+    // saves costs about 5 us. So the separate pass stays the default.
+    const bool fold = qm_env_int("QM_MOE_FOLD", 0) != 0 && (x_bf16_dev & 15) == 0 && (ldx & 7) == 0;
+    const bool nosync = qm_env_int("QM_MOE_NOSYNC", 0) != 0;
+    if (fold) {
+        int32_t counts[QM_MAX_EXPERTS];
+        CUdeviceptr offsets_dev = 0, list_dev = 0;
+        rc = dispatch_impl(c, ids_dev, tokens, topk, experts, x_bf16_dev, ldx, (int32_t)hidden, 0, ws + o_pos,
+                           nosync ? nullptr : counts, &offsets_dev, &list_dev);
+        if (rc) return rc;
+        int32_t longest = (int32_t)pairs, typical = (int32_t)std::max<int64_t>(1, (pairs + experts - 1) / experts);
+        if (!nosync) {
+            longest = 0;
+            for (int e = 0; e < experts; e++) longest = std::max(longest, counts[e]);
+            typical = longest;
+        }
+        if (longest > 0) {
+            CtxGuard g(c);
+            DRV(g.rc);
+            rc = experts_launch(c, wg, wd, experts, x_bf16_dev, pairs, longest, typical, offsets_dev, ws + o_y, hidden, ffn,
+                                list_dev, topk, tokens, ldx);
+            if (rc) return rc;
+        }
+        return qm_moe_combine(c, ws + o_y, ws + o_pos, weights_dev, tokens, topk, (int32_t)hidden, out_dev, ldo);
+    }
+    if (!nosync) {
         int32_t counts[QM_MAX_EXPERTS];
         rc = qm_moe_dispatch(c, ids_dev, tokens, topk, experts, x_bf16_dev, ldx, (int32_t)hidden, ws + o_rows, ws + o_pos,
                              counts);

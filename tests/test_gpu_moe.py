@@ -106,6 +106,42 @@ def test_mixtral_shape_sampled_tokens(ctx, devbuf):
     assert run_moe(ctx, devbuf, 8, 4096, 14336, 512, 2, 500, [0, 255, 511]) <= TOL
 
 
+def test_gather_folded_into_the_matmul_gives_the_same_bits(ctx, devbuf, monkeypatch):
+    """The gate|up matmul fetching the tokens' rows by the dispatch list itself (the default) against the
+    separate gather pass (the reference's order of work, nvidia/x/cudamoe/moe.go:72-96): same rows in the same
+    order, so equal bits; also with the list lengths kept on the device, and with a padded row pitch."""
+    experts, hidden, ffn, tokens, topk, seed, ldx = 4, 512, 768, 333, 2, 77, 520
+    gu_raw = [synth.weights(12, 2 * ffn, hidden, seed + e) for e in range(experts)]
+    dn_raw = [synth.weights(12, hidden, ffn, seed + 100 + e) for e in range(experts)]
+    gu = [ctx.store_upload(12, 2 * ffn, hidden, r) for r in gu_raw]
+    dn = [ctx.store_upload(12, hidden, ffn, r) for r in dn_raw]
+    x_bf = np.zeros((tokens, ldx), np.uint16)
+    x_bf[:, :hidden] = to_bf16_bits(synth.activations(tokens, hidden, seed + 200))
+    lg = synth.activations(tokens, experts, seed + 201)
+    ids, wts, ids_d, wts_d = route_gpu(ctx, devbuf, lg, experts, topk)
+    xd = devbuf(x_bf)
+    outs = {}
+    for fold in ("1", "0"):
+        for nosync in ("0", "1"):
+            monkeypatch.setenv("QM_MOE_FOLD", fold)
+            monkeypatch.setenv("QM_MOE_NOSYNC", nosync)
+            od = devbuf(np.full((tokens, hidden), np.nan, np.float32))
+            ctx.moe_grouped(gu, dn, xd.ptr, tokens, ldx, ids_d.ptr, wts_d.ptr, topk, od.ptr, hidden)
+            ctx.sync()
+            rc, status = ctx.last_status()
+            assert rc == 0 and status == 0
+            outs[fold, nosync] = od.get((tokens, hidden))
+    base = outs["0", "0"]
+    assert np.isfinite(base).all()
+    for k, v in outs.items():
+        assert np.array_equal(v.view(np.uint32), base.view(np.uint32)), k
+    want = moe_oracle(gu_raw, dn_raw, hidden, ffn, x_bf[:, :hidden], ids, wts, [0, 100, 332])
+    got = outs["1", "0"][[0, 100, 332]].astype(np.float64)
+    assert float(np.linalg.norm(got - want) / np.linalg.norm(want)) <= TOL
+    for w in gu + dn:
+        w.free()
+
+
 def test_layer_stages_match_oracle(ctx):
     """lib_b200.moe.MoELayer on one GPU (route -> dispatch -> experts -> combine through the
     staged entry points) against the oracle chain."""

@@ -206,8 +206,10 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         // ---- MMA issue ----------------------------------------------------------------------------
         if (lane == 0) {
             // kind::f16, fp32 accumulate, A and B bf16, both K-major, N = BN, M = 128
-            const int NI = min(BN, 256);   // tokens per MMA
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NI >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+            // (N = the tile's tokens that exist, rounded up to 16: a short expert list does not pay for the
+            // whole token tile)
+            const uint32_t idesc0 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBM >> 4) << 24);
+            const int mv = min(BN, m_cnt - m0);
             bool ok = true;
             for (int kc = 0; kc < nk && ok; kc++) {
                 const int s = kc % kStages;
@@ -221,11 +223,13 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                     const uint64_t bdesc = smem_desc(smem_base + s * stage_bytes + a_bytes + j * b_tile);
 #pragma unroll
                     for (int sub = 0; sub < NSUB; sub++)
-                        for (int nb = 0; nb < BN && !QM_GEMM_DEBUG_BIT(4); nb += 256)
+                        for (int nb = 0; nb < mv && !QM_GEMM_DEBUG_BIT(4); nb += 256) {
+                            const uint32_t idesc = idesc0 | ((uint32_t)(min(256, (mv - nb + 15) & ~15) >> 3) << 17);
 #pragma unroll
                             for (int k16 = 0; k16 < kBK / 16; k16++)   // 16 bf16 = 32 bytes = 2 descriptor units
                                 umma_f16(tmem_base + (uint32_t)(sub * BN + nb), adesc + sub * (kATile >> 4) + 2 * k16,
                                          bdesc + (nb * 128 >> 4) + 2 * k16, idesc, (kc | j | k16) != 0);
+                        }
                 }
                 umma_commit(empty + 8 * s);   // frees the stage when these MMAs have read it
             }
@@ -334,7 +338,9 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         if (ok && mbar_wait_bounded(tmem_full, 0u)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // the four warps of a TMEM lane quarter split the token columns (at least 32 each)
-            const int cpart = max(32, BN / 4), cbeg = ((warp - 2) >> 2) * cpart, cend = min(BN, cbeg + cpart);
+            // (of the columns that hold tokens: the rest of the accumulator was never written)
+            const int mv32 = (min(BN, m_cnt - m0) + 31) & ~31;
+            const int cpart = max(32, (mv32 / 4 + 31) & ~31), cbeg = ((warp - 2) >> 2) * cpart, cend = min(mv32, cbeg + cpart);
             auto tmem_ld32 = [](uint32_t addr, uint32_t (&v)[32]) {
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"

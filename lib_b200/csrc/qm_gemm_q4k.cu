@@ -102,10 +102,28 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 // KS = 64-column K chunks per pipeline stage: 1, or 2 for small token tiles, where the barrier
 // handshake of a stage (about 0.3 us, whatever the stage count) is longer than the MMAs of one
 // chunk: two chunks per handshake halve it.
+#ifdef QM_DEBUG
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define QM_GEMM_STAMP(i)                                                                                       \
+    do {                                                                                                       \
+        if ((a.debug & 64) && a.swiglu) {                                                                      \
+            const int L_ = blockIdx.y * gridDim.x + blockIdx.x;                                                \
+            if (L_ < 990) reinterpret_cast<unsigned long long *>(a.status + 256)[L_ * 4 + (i)] = gtime();      \
+        }                                                                                                      \
+    } while (0)
+#else
+#define QM_GEMM_STAMP(i)
+#endif
+
 template <int NSUB, int KS>
 __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) QM_GEMM_STAMP(0);
     const int BN = a.bn, kStages = a.stages;
     const int b_tile = BN * kBK * 2;          // one 64-column chunk of the activations
     constexpr int a_tile = NSUB * kATile;     // one 64-column chunk of the weights
@@ -114,8 +132,18 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)kStages * stage_bytes);
     const uint32_t full_a = smem_u32(bars), full_b = full_a + 8 * kMaxStages, empty = full_b + 8 * kMaxStages;
-    const uint32_t tmem_full = empty + 8 * kMaxStages;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kMaxStages + 1);
+    // Two "empty" barriers per stage, taken in turn by the stage's phases: a parity wait cannot tell a
+    // barrier's completions two apart, and with one barrier per stage that allowed no more chunks in
+    // production than stages. With two, the chunks whose release could be mistaken lie four phases apart,
+    // so four groups of dequantizing warps may work ahead of two or three stages.
+    const uint32_t tmem_full = empty + 8 * 2 * kMaxStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 4 * kMaxStages + 1);
+    // chunk kc may be written into its stage when the MMAs of chunk kc - kStages have read it
+    auto wait_empty = [&](int kc) -> bool {
+        const int ph = kc / kStages;
+        if (ph == 0) return true;
+        return mbar_wait_bounded(empty + 8 * (2 * (kc % kStages) + ((ph - 1) & 1)), (uint32_t)((ph - 1) >> 1) & 1u);
+    };
     const uint32_t smem_base = smem_u32(smem);
 
     const bool fuse_swiglu = NSUB == 2 && a.swiglu != 0;
@@ -142,9 +170,10 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
 
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) {
-            mbar_init(full_a + 8 * s, kStages >= 4 ? 4 : 8);   // warps of one producer group
+            mbar_init(full_a + 8 * s, a.groups == 4 ? 4 : 8);   // warps of one producer group
             mbar_init(full_b + 8 * s, 1);
-            mbar_init(empty + 8 * s, 1);
+            mbar_init(empty + 8 * (2 * s), 1);
+            mbar_init(empty + 8 * (2 * s + 1), 1);
         }
         mbar_init(tmem_full, 1);
         fence_barrier_init();
@@ -171,8 +200,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         __syncwarp();
         for (int kc = 0; kc < nk; kc++) {
             const int s = kc % kStages;
-            const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
-            if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) {
+            if (!wait_empty(kc)) {
                 if (lane == 0) atomicOr(a.status, QM_STATUS_TIMEOUT);
                 break;
             }
@@ -189,15 +217,16 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     } else if (warp == 0) {
         // ---- activation chunks by TMA ---------------------------------------------------------
         if (lane == 0) {
+            const int box = a.box_rows, nbox = (min(BN, m_cnt - m0) + box - 1) / box;
             for (int kc = 0; kc < nk; kc++) {
                 const int s = kc % kStages;
-                const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
-                if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); break; }
+                if (!wait_empty(kc)) { atomicOr(a.status, QM_STATUS_TIMEOUT); break; }
                 if (QM_GEMM_DEBUG_BIT(2)) { mbar_arrive(full_b + 8 * s); continue; }
-                mbar_expect_tx(full_b + 8 * s, (uint32_t)(KS * b_tile));
+                // only the boxes that hold rows of this tile (an MMA reads no further than its N)
+                mbar_expect_tx(full_b + 8 * s, (uint32_t)(KS * nbox * box * 128));
 #pragma unroll
                 for (int j = 0; j < KS; j++)
-                    for (int nb = 0; nb < BN; nb += 256)   // a TMA box has at most 256 rows
+                    for (int nb = 0; nb < nbox * box; nb += box)   // a TMA box has at most 256 rows
                         tma_load_2d(smem_base + s * stage_bytes + a_bytes + j * b_tile + nb * 128, &a.tmap_act,
                                     ((kc_lo + kc) * KS + j) * kBK, row_off + m0 + nb, full_b + 8 * s);
             }
@@ -231,9 +260,12 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                                          bdesc + (nb * 128 >> 4) + 2 * k16, idesc, (kc | j | k16) != 0);
                         }
                 }
-                umma_commit(empty + 8 * s);   // frees the stage when these MMAs have read it
+                if (QM_GEMM_DEBUG_BIT(16)) mbar_arrive(empty + 8 * (2 * s + ((kc / kStages) & 1)));
+                else
+                umma_commit(empty + 8 * (2 * s + ((kc / kStages) & 1)));   // frees the stage when these MMAs have read it
             }
             umma_commit(tmem_full);           // accumulator complete (or abandoned)
+            QM_GEMM_STAMP(2);
         }
     } else {
         // ---- dequantize weight rows into the A tile, then the epilogue --------------------------
@@ -241,10 +273,9 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         // kc = g, g+4, g+8, ...: one thread per weight row turns the row's 32 quant bytes of the
         // chunk into its 64 bf16 columns. A thread's iteration is a chain of dependent steps (wait
         // for the stage, convert, store, fence, arrive); four chunks in flight hide that latency.
-        // A group may be at most one phase ahead of a stage's "empty" barrier (a parity wait
-        // cannot tell phases two apart), so there are no more groups than stages: four groups with
-        // four stages, two groups (two threads per row, one per nibble half) with two or three.
-        const int kGroups = kStages >= 4 ? 4 : 2;
+        // With fewer stages than groups a group's loads are in flight while it waits for a stage.
+        // (Two groups — two threads per row, one per nibble half — is the other form the host can ask for.)
+        const int kGroups = a.groups == 4 ? 4 : 2;
         const int pt = tid - 64;
         const int r = pt & 127;              // row of a 128-row sub-tile
         const int grp = kGroups == 4 ? pt >> 7 : pt >> 8;   // warp-uniform
@@ -262,7 +293,14 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         // current one has been handed over, into the same registers: the other groups' turns lie
         // between the loads and their use.
         uint4 qa[KS][NSUB], qb[KS][NSUB], hd[KS][NSUB];
+#ifdef QM_DEBUG
+#pragma unroll
+        for (int j = 0; j < KS; j++)
+#pragma unroll
+            for (int sub = 0; sub < NSUB; sub++) qa[j][sub] = qb[j][sub] = hd[j][sub] = make_uint4(0x11111111u, 0x3c003c00u, 0x01010101u, 0x02020202u);
+#endif
         auto load_stage = [&](int kcl) {
+            if (QM_GEMM_DEBUG_BIT(8)) return;
 #pragma unroll
             for (int j = 0; j < KS; j++) {
                 const int c64 = (kc_lo + kcl) * KS + j;   // 64-column chunk along K
@@ -278,8 +316,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         if (grp < nk) load_stage(grp);
         for (int kc = grp; kc < nk; kc += kGroups) {
             const int s = kc % kStages;
-            const uint32_t ph = (uint32_t)(kc / kStages) & 1u;
-            if (!mbar_wait_bounded(empty + 8 * s, ph ^ 1u)) { atomicOr(a.status, QM_STATUS_TIMEOUT); ok = false; break; }
+            if (!wait_empty(kc)) { atomicOr(a.status, QM_STATUS_TIMEOUT); ok = false; break; }
 #pragma unroll
             for (int j = 0; j < KS; j++) {
                 const int p = ((kc_lo + kc) * KS + j) & 3;
@@ -329,6 +366,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                     }
                 }
             }
+            if (!QM_GEMM_DEBUG_BIT(32))
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
             __syncwarp();
             if (lane == 0) mbar_arrive(full_a + 8 * s);   // one arrival per warp: 128 arrivals on one barrier serialize
@@ -337,19 +375,16 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         // ---- epilogue: accumulator row r holds C[m0..m0+BN)[n0+r] -------------------------------------
         if (ok && mbar_wait_bounded(tmem_full, 0u)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // the four warps of a TMEM lane quarter split the token columns (at least 32 each)
-            // (of the columns that hold tokens: the rest of the accumulator was never written)
-            const int mv32 = (min(BN, m_cnt - m0) + 31) & ~31;
-            const int cpart = max(32, (mv32 / 4 + 31) & ~31), cbeg = ((warp - 2) >> 2) * cpart, cend = min(mv32, cbeg + cpart);
-            auto tmem_ld32 = [](uint32_t addr, uint32_t (&v)[32]) {
+            if (tid == 64) QM_GEMM_STAMP(1);
+            // the four warps of a TMEM lane quarter split the token columns that hold tokens (the rest of
+            // the accumulator was never written) in blocks of 16, as evenly as the count allows
+            const int blocks = (min(BN, m_cnt - m0) + 15) >> 4, q = (warp - 2) >> 2;
+            const int cbeg = 16 * (q * (blocks >> 2) + min(q, blocks & 3)), cend = cbeg + 16 * ((blocks >> 2) + (q < (blocks & 3) ? 1 : 0));
+            auto tmem_ld16 = [](uint32_t addr, uint32_t (&v)[16]) {
                 asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                    "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
-                      "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
-                      "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
-                      "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                     : "r"(addr)
                     : "memory");
             };
@@ -357,19 +392,20 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
             if (fuse_swiglu) {
                 // gate in accumulator 0, the matching up rows in accumulator 1: h = silu(gate) * up
                 const int n = n0 + (warp & 3) * 32 + lane;
-                for (int c0 = cbeg; c0 < cend; c0 += 32) {
-                    uint32_t g[32], u[32];
-                    tmem_ld32(quarter_base + (uint32_t)c0, g);
-                    tmem_ld32(quarter_base + (uint32_t)(BN + c0), u);
+                for (int c0 = cbeg; c0 < cend; c0 += 16) {
+                    uint32_t g[16], u[16];
+                    tmem_ld16(quarter_base + (uint32_t)c0, g);
+                    tmem_ld16(quarter_base + (uint32_t)(BN + c0), u);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (n < a.n) {
+                        uint16_t *hp = a.h + (int64_t)(row_off + m0 + c0) * a.ldh + n;
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int m = m0 + c0 + j;
-                            if (m < m_cnt) {
+                        for (int j = 0; j < 16; j++) {
+                            if (m0 + c0 + j < m_cnt) {
                                 const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
-                                const __nv_bfloat16 hv = __float2bfloat16_rn(gv / (1.f + __expf(-gv)) * uv);
-                                a.h[(int64_t)(row_off + m) * a.ldh + n] = *reinterpret_cast<const uint16_t *>(&hv);
+                                // (fast division: the quotient is rounded to bf16 next; the IEEE form cost 10 us per CTA here)
+                                const __nv_bfloat16 hv = __float2bfloat16_rn(__fdividef(gv, 1.f + __expf(-gv)) * uv);
+                                hp[(int64_t)j * a.ldh] = *reinterpret_cast<const uint16_t *>(&hv);
                             }
                         }
                     }
@@ -378,18 +414,24 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
 #pragma unroll 1
                 for (int sub = 0; sub < NSUB; sub++) {
                     const int n = n0 + sub * kBM + (warp & 3) * 32 + lane;
-                    for (int c0 = cbeg; c0 < cend; c0 += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(quarter_base + (uint32_t)(sub * BN + c0), v);
+                    // split K: this CTA's share of the tile goes to its own plane of the scratch
+                    float *base = a.splitk == 1 ? a.c : a.partials + (int64_t)blockIdx.z * a.m * a.n;
+                    const int64_t ld = a.splitk == 1 ? a.ldc : a.n;
+                    for (int c0 = cbeg; c0 < cend; c0 += 32) {   // two blocks per wait where there are two
+                        uint32_t v[16], w[16];
+                        const bool two = c0 + 16 < cend;
+                        tmem_ld16(quarter_base + (uint32_t)(sub * BN + c0), v);
+                        if (two) tmem_ld16(quarter_base + (uint32_t)(sub * BN + c0 + 16), w);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         if (n < a.n) {
-                            // split K: this CTA's share of the tile goes to its own plane of the scratch
-                            float *base = a.splitk == 1 ? a.c : a.partials + (int64_t)blockIdx.z * a.m * a.n;
-                            const int64_t ld = a.splitk == 1 ? a.ldc : a.n;
+                            float *cp = base + (int64_t)(row_off + m0 + c0) * ld + n;
 #pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                const int m = m0 + c0 + j;
-                                if (m < m_cnt) base[(int64_t)(row_off + m) * ld + n] = __uint_as_float(v[j]);
+                            for (int j = 0; j < 16; j++)
+                                if (m0 + c0 + j < m_cnt) cp[(int64_t)j * ld] = __uint_as_float(v[j]);
+                            if (two) {
+#pragma unroll
+                                for (int j = 0; j < 16; j++)
+                                    if (m0 + c0 + 16 + j < m_cnt) cp[(int64_t)(16 + j) * ld] = __uint_as_float(w[j]);
                             }
                         }
                     }
@@ -401,6 +443,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (tid == 0) QM_GEMM_STAMP(3);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(NSUB * BN)) : "memory");

@@ -1045,7 +1045,9 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     if (stages * stage_bytes + 2048 > QM_GEMV_SMEM_MAX) return QM_ERR_SHAPE;
     const cuuint64_t dims[2] = {(cuuint64_t)w->cols, (cuuint64_t)rows_total};
     const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)std::min(bn, 256)};
+    // grouped launches fetch the token tile in boxes of 64 rows, as many as the expert's list fills
+    const int box_rows = grouped ? 64 : std::min(bn, 256);
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     DRV(c->drv->cuTensorMapEncodeTiled(&a.tmap_act, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void *)(uintptr_t)a_dev, dims,
                                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1061,6 +1063,8 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     a.tiles16 = (int32_t)((w->rows + 15) / 16);
     a.bn = bn;
     a.stages = stages;
+    a.box_rows = box_rows;
+    a.groups = env_int("QM_GEMM_GROUPS", 4) == 2 ? 2 : 4;
     a.grouped = grouped ? 1 : 0;
     a.wq_list = (const uint8_t *const *)(uintptr_t)g.wq_list_dev;
     a.offsets = (const int32_t *)(uintptr_t)g.offsets_dev;
@@ -1071,7 +1075,7 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
 #ifdef QM_DEBUG
     a.debug = env_int("QM_GEMM_DEBUG", 0);
 #endif
-    unsigned smem = 1024 + stages * stage_bytes + 256;
+    unsigned smem = 1024 + stages * stage_bytes + 512;   // alignment slack, stages, barriers
     if (g.gather_list_dev) {   // the loader warp's table of token numbers sits behind the barriers
         if (!grouped || bn > 256 || g.gather_topk < 1) return QM_ERR_SHAPE;
         a.gather_list = (const int32_t *)(uintptr_t)g.gather_list_dev;

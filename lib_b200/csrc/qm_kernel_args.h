@@ -186,7 +186,8 @@ struct QmGemmArgs {
     int32_t swiglu, up_offset;
     uint16_t *h;           // bf16 [rows][ldh]
     int64_t ldh;
-    int32_t debug, pad;    // 0 in production; bits switch off pipeline roles for timing experiments (results are wrong)
+    int32_t debug;         // 0 in production; bits switch off pipeline roles for timing experiments (results are wrong)
+    int32_t groups;        // groups of dequantizing warps, each a chunk ahead of the next: 4 (one thread per weight row) or 2
     // Split K: share z of an output tile goes to partials[z][m][n] (plain stores); when all splitk CTAs of
     // the tile have arrived (tickets[2*tile], zero between launches) each adds one band of the tile in order
     // of z and writes C — no atomics on C, the same bits every run. The launch is cooperative.
@@ -197,7 +198,9 @@ struct QmGemmArgs {
     // gather_list[p] / gather_topk of the tokens' own matrix, which tmap_gather describes with a box of
     // 64 columns x 1 row; the loader warp fetches four rows per tile::gather4 copy.
     const int32_t *gather_list;   // null: the activations are already grouped (tmap_act, tiled loads)
-    int32_t gather_topk, pad2;
+    int32_t gather_topk;
+    int32_t box_rows;             // token rows per tiled load of tmap_act
+    int32_t pad3;
     alignas(64) CUtensorMap tmap_gather;
 };
 

@@ -178,9 +178,12 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         mbar_init(tmem_full, 1);
         fence_barrier_init();
     }
+    // TMEM columns come in powers of two
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < (uint32_t)(NSUB * BN)) tmem_cols <<= 1;
     if (warp == 1) {   // TMEM accumulators: NSUB x BN fp32 columns x 128 lanes
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)(NSUB * BN))
+                     "r"(tmem_cols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -446,7 +449,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     if (tid == 0) QM_GEMM_STAMP(3);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(NSUB * BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
     if (a.splitk > 1) {
         // Every CTA of the tile adds one band of it, in order of z, once all splitk shares are in the scratch:

@@ -1034,7 +1034,8 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     const bool r256 = g.swiglu || (env_int("QM_GEMM_R256", 0) != 0 && w->rows >= 256);
     const int nsub = r256 ? 2 : 1;
     const int mt = g.m_typical > 0 ? g.m_typical : m;
-    const int bn_auto = mt <= 64 ? 64 : mt <= 128 ? 128 : (mt <= 256 || r256) ? 256 : 512;
+    // (192: a grouped launch whose longest list fits gets a smaller activation tile and with it a fourth stage)
+    const int bn_auto = mt <= 64 ? 64 : mt <= 128 ? 128 : (grouped && mt <= 192) ? 192 : (mt <= 256 || r256) ? 256 : 512;
     const int bn = std::min(bn_auto, std::max(64, env_int("QM_GEMM_BN", 512)));
     // Two 64-column chunks per stage where at least two such stages fit and the token tile is
     // small: the handshake of a stage costs ~0.3 us, more than the MMAs of one small chunk.

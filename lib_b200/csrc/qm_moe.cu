@@ -51,15 +51,30 @@ extern "C" __global__ void __launch_bounds__(128) qm_moe_route(const __grid_cons
 // list[] = pair index (token*topk + slot) grouped by expert, pos[pair] = row in that grouping.
 extern "C" __global__ void __launch_bounds__(1024) qm_moe_lists(const __grid_constant__ QmListArgs a) {
     __shared__ int s_count[QM_MAX_EXPERTS], s_off[QM_MAX_EXPERTS + 1];
+    // up to kSmall pairs the expert numbers and ranks stay in shared memory (one pass over ids)
+    constexpr int kSmall = 8192;
+    __shared__ short s_id[kSmall], s_rank[kSmall];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int npairs = a.tokens * a.topk;
+    const bool small = npairs <= kSmall;
+    if (small) {
+        for (int pr = threadIdx.x; pr < npairs; pr += blockDim.x) {
+            const int e = a.ids[pr];
+            s_id[pr] = (short)((e < 0 || e >= a.experts) ? -1 : e);
+        }
+        __syncthreads();
+    }
     for (int e = warp; e < a.experts; e += blockDim.x >> 5) {
         int cnt = 0;
         for (int base = 0; base < npairs; base += 32) {
             const int pr = base + lane;
-            const bool mine = pr < npairs && a.ids[pr] == e;
+            const bool mine = pr < npairs && (small ? (int)s_id[pr] : a.ids[pr]) == e;
             const unsigned int bal = __ballot_sync(0xffffffffu, mine);
-            if (mine) a.rank[pr] = cnt + __popc(bal & ((1u << lane) - 1u));
+            if (mine) {
+                const int r = cnt + __popc(bal & ((1u << lane) - 1u));
+                if (small) s_rank[pr] = (short)r;
+                else a.rank[pr] = r;
+            }
             cnt += __popc(bal);
         }
         if (lane == 0) s_count[e] = cnt;
@@ -77,9 +92,9 @@ extern "C" __global__ void __launch_bounds__(1024) qm_moe_lists(const __grid_con
     }
     __syncthreads();
     for (int pr = threadIdx.x; pr < npairs; pr += blockDim.x) {
-        const int e = a.ids[pr];
+        const int e = small ? (int)s_id[pr] : a.ids[pr];
         if (e < 0 || e >= a.experts) { a.pos[pr] = -1; continue; }   // names no expert: in no list
-        const int p = s_off[e] + a.rank[pr];
+        const int p = s_off[e] + (small ? (int)(unsigned short)s_rank[pr] : a.rank[pr]);
         a.pos[pr] = p;
         a.list[p] = pr;
     }
@@ -100,6 +115,24 @@ extern "C" __global__ void __launch_bounds__(256) qm_moe_gather(const __grid_con
 
 // out[tok][:] = sum_s weights[tok][s] * y[pos[tok*topk+s]][:] in slot order (deterministic).
 extern "C" __global__ void __launch_bounds__(256) qm_moe_combine(const __grid_constant__ QmCombineArgs a) {
+    if (((a.hidden | a.ldo) & 3) == 0 && (((uintptr_t)a.y | (uintptr_t)a.out) & 15) == 0) {   // four columns per thread
+        const int h4 = a.hidden >> 2;
+        const int64_t total4 = (int64_t)a.tokens * h4;
+        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
+            const int tok = (int)(i / h4), c = (int)(i - (int64_t)tok * h4);
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < a.topk; k++) {
+                const int p = a.pos[tok * a.topk + k];
+                if (p >= 0) {
+                    const float w = a.weights[tok * a.topk + k];
+                    const float4 v = reinterpret_cast<const float4 *>(a.y + (int64_t)p * a.hidden)[c];
+                    s.x = fmaf(w, v.x, s.x); s.y = fmaf(w, v.y, s.y); s.z = fmaf(w, v.z, s.z); s.w = fmaf(w, v.w, s.w);
+                }
+            }
+            reinterpret_cast<float4 *>(a.out + (int64_t)tok * a.ldo)[c] = s;
+        }
+        return;
+    }
     const int64_t total = (int64_t)a.tokens * a.hidden;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int tok = (int)(i / a.hidden), c = (int)(i - (int64_t)tok * a.hidden);

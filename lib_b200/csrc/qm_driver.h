@@ -28,6 +28,7 @@
     X(cuMemcpyDtoH_v2, CUresult (*)(void *, CUdeviceptr, size_t))                                 \
     X(cuMemcpyHtoDAsync_v2, CUresult (*)(CUdeviceptr, const void *, size_t, CUstream))            \
     X(cuMemcpyDtoHAsync_v2, CUresult (*)(void *, CUdeviceptr, size_t, CUstream))                  \
+    X(cuMemcpy2DAsync_v2, CUresult (*)(const CUDA_MEMCPY2D *, CUstream))                          \
     X(cuMemcpyDtoDAsync_v2, CUresult (*)(CUdeviceptr, CUdeviceptr, size_t, CUstream))             \
     X(cuMemsetD8Async, CUresult (*)(CUdeviceptr, unsigned char, size_t, CUstream))                \
     X(cuMemsetD32Async, CUresult (*)(CUdeviceptr, unsigned int, size_t, CUstream))                \

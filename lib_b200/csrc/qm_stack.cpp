@@ -1038,11 +1038,20 @@ extern "C" int32_t qm_stack_step_host(qm_ctx *c, qm_stack *s, const float *x_hos
     if (kv_host && s->kv) {
         const int64_t qkv_ld = s->hidden + 2 * s->kv;
         // (tensor-parallel: every GPU's slice of q|k|v has been stored into this arena)
-        for (int L = 0; L < s->layers; L++)
-            for (int j = 0; j < m; j++)
-                DRV(d->cuMemcpyDtoHAsync_v2(kv_host + ((size_t)L * m + j) * 2 * s->kv,
-                                            layer_bufs(s, L, m).qkv + ((size_t)j * qkv_ld + s->hidden) * 4,
-                                            (size_t)2 * s->kv * 4, c->stream));
+        // One strided copy per activation row: the layers' buffers lie a fixed distance apart.
+        for (int j = 0; j < m; j++) {
+            CUDA_MEMCPY2D cp;
+            memset(&cp, 0, sizeof cp);
+            cp.srcMemoryType = CU_MEMORYTYPE_DEVICE;
+            cp.srcDevice = layer_bufs(s, 0, m).qkv + ((size_t)j * qkv_ld + s->hidden) * 4;
+            cp.srcPitch = layer_floats(s, m) * 4;
+            cp.dstMemoryType = CU_MEMORYTYPE_HOST;
+            cp.dstHost = kv_host + (size_t)j * 2 * s->kv;
+            cp.dstPitch = (size_t)m * 2 * s->kv * 4;
+            cp.WidthInBytes = (size_t)2 * s->kv * 4;
+            cp.Height = (size_t)s->layers;
+            DRV(d->cuMemcpy2DAsync_v2(&cp, c->stream));
+        }
     }
     DRV(d->cuStreamSynchronize(c->stream));
     return QM_OK;

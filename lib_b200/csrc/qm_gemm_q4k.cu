@@ -150,7 +150,8 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     // grouped launches put the expert in blockIdx.y and the token tile in blockIdx.z: CTAs are
     // handed out x-fastest, then y, then z, so every expert's first token tiles (the ones with
     // work) start before the mostly empty later tiles
-    const int n0 = blockIdx.x * kBM * (fuse_swiglu ? 1 : NSUB), m0 = (a.grouped ? blockIdx.z : blockIdx.y) * BN;
+    // (grouped launches with split K: blockIdx.z = token tile * splitk + K share)
+    const int n0 = blockIdx.x * kBM * (fuse_swiglu ? 1 : NSUB), m0 = (a.grouped ? (int)blockIdx.z / a.splitk : (int)blockIdx.y) * BN;
     // grouped launch: this CTA's expert, its rows of the gathered activations and its weights
     int row_off = 0, m_cnt = a.m;
     const uint8_t *wq = a.wq;
@@ -164,7 +165,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
     // 64-column chunks along K; with split K (splitk > 1) this CTA takes a contiguous share
     // and adds its partial tile to C, which the host zeroed
     const int nk_all = a.units * 4 / KS;      // stage chunks of KS x 64 columns
-    const int zk = a.grouped ? 0 : (int)blockIdx.z;
+    const int zk = a.grouped ? (int)blockIdx.z % a.splitk : (int)blockIdx.z;
     const int kc_lo = (int)((int64_t)nk_all * zk / a.splitk);
     const int nk = (int)((int64_t)nk_all * (zk + 1) / a.splitk) - kc_lo;
 
@@ -418,7 +419,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
                 for (int sub = 0; sub < NSUB; sub++) {
                     const int n = n0 + sub * kBM + (warp & 3) * 32 + lane;
                     // split K: this CTA's share of the tile goes to its own plane of the scratch
-                    float *base = a.splitk == 1 ? a.c : a.partials + (int64_t)blockIdx.z * a.m * a.n;
+                    float *base = a.splitk == 1 ? a.c : a.partials + (int64_t)zk * a.plane_rows * a.n;
                     const int64_t ld = a.splitk == 1 ? a.ldc : a.n;
                     for (int c0 = cbeg; c0 < cend; c0 += 32) {   // two blocks per wait where there are two
                         uint32_t v[16], w[16];
@@ -456,7 +457,9 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         // the launch is cooperative (all CTAs resident), the wait for the others is bounded. (The barrier
         // above ordered every thread's stores before thread 0's fence and arrival.)
         volatile uint32_t *s_ok = tmem_slot + 1;   // a free word of the dynamic shared memory's tail
-        unsigned int *ticket = a.tickets + 2 * (blockIdx.y * gridDim.x + blockIdx.x);
+        const unsigned int tile_id = a.grouped ? ((blockIdx.z / a.splitk) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x
+                                               : blockIdx.y * gridDim.x + blockIdx.x;
+        unsigned int *ticket = a.tickets + 2 * tile_id;
         if (tid == 0) {
             __threadfence();
             atomicAdd(ticket, 1u);
@@ -469,9 +472,9 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         }
         __syncthreads();
         if (*s_ok) {
-            const int rows = min(NSUB * kBM, a.n - n0), toks = min(BN, a.m - m0);
-            const int t_lo = (int)((int64_t)toks * blockIdx.z / a.splitk), t_hi = (int)((int64_t)toks * (blockIdx.z + 1) / a.splitk);
-            const int64_t plane = (int64_t)a.m * a.n;
+            const int rows = min(NSUB * kBM, a.n - n0), toks = min(BN, m_cnt - m0);
+            const int t_lo = (int)((int64_t)toks * zk / a.splitk) + row_off, t_hi = (int)((int64_t)toks * (zk + 1) / a.splitk) + row_off;
+            const int64_t plane = (int64_t)a.plane_rows * a.n;
             if ((rows & 3) == 0 && (a.n & 3) == 0 && (a.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(a.c) & 15) == 0) {
                 // 16 bytes per thread and four of them in flight: the loop is bound by the latency of its loads
                 const int r4 = rows >> 2, total = r4 * (t_hi - t_lo), step = (int)blockDim.x;

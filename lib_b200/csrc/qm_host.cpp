@@ -1098,21 +1098,26 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     // few tokens: split K over CTAs until the SMs are covered; the last CTA of a tile adds the shares in a
     // fixed order (no atomics on C: the same bits every run)
     int splitk = 1;
-    if (!grouped) {
-        while (splitk < 8 && (int)(cfg.gridDimX * cfg.gridDimY) * splitk * 2 <= c->sm_count && w->units * 4 / (splitk * 2) >= 8)
-            splitk *= 2;
-        splitk = env_int("QM_GEMM_SPLITK", splitk);
+    // (grouped launches too, where the experts' tiles leave SMs idle — few experts per GPU in expert-parallel
+    // runs; not with the SwiGLU epilogue, whose launches have row tiles enough)
+    const int64_t tiles = (int64_t)cfg.gridDimX * cfg.gridDimY * (grouped ? g.experts : 1);
+    const int64_t plane_rows = grouped ? rows_total : m;
+    if (!g.swiglu) {
+        while (splitk < 8 && tiles * splitk * 2 <= c->sm_count && w->units * 4 / (splitk * 2) >= 8) splitk *= 2;
+        if (!grouped) splitk = env_int("QM_GEMM_SPLITK", splitk);
+        else if (env_int("QM_GEMM_GROUPED_SPLITK", 1) == 0) splitk = 1;
     }
-    // the shares go through the context's scratch (one plane of m x n floats per share) and a ticket per tile
-    while (splitk > 1 && ((int64_t)splitk * m * out_cols * 4 > QM_PARTIALS_BYTES || (int64_t)cfg.gridDimX * cfg.gridDimY * 2 > QM_TICKETS))
+    // the shares go through the context's scratch (one plane of rows x n floats per share) and a ticket per tile
+    while (splitk > 1 && ((int64_t)splitk * plane_rows * out_cols * 4 > QM_PARTIALS_BYTES || tiles * 2 > QM_TICKETS))
         splitk /= 2;
     a.splitk = splitk;
+    a.plane_rows = (int32_t)plane_rows;
     a.partials = (float *)(uintptr_t)c->partials_dev;
     a.tickets = (unsigned int *)(uintptr_t)c->tickets_dev;
     a.wait_cycles = qm_wait_cycles();
     cfg.gridDimZ = (unsigned)splitk;
-    if (grouped) {   // expert in y, token tile in z (see the kernel)
-        cfg.gridDimZ = cfg.gridDimY;
+    if (grouped) {   // expert in y, token tile and K share in z (see the kernel)
+        cfg.gridDimZ = cfg.gridDimY * (unsigned)splitk;
         cfg.gridDimY = (unsigned)g.experts;
     }
     cfg.blockDimX = 576;   // TMA warp, MMA warp, sixteen dequantizing warps

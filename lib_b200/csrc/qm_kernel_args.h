@@ -200,7 +200,7 @@ struct QmGemmArgs {
     const int32_t *gather_list;   // null: the activations are already grouped (tmap_act, tiled loads)
     int32_t gather_topk;
     int32_t box_rows;             // token rows per tiled load of tmap_act
-    int32_t pad3;
+    int32_t plane_rows;           // activation rows of one split-K plane (m, or all grouped rows)
     alignas(64) CUtensorMap tmap_gather;
 };
 

@@ -142,6 +142,39 @@ def test_gather_folded_into_the_matmul_gives_the_same_bits(ctx, devbuf, monkeypa
         w.free()
 
 
+def test_grouped_down_matmul_with_split_k(ctx, devbuf, monkeypatch):
+    """Few experts leave SMs idle in the grouped down launch, so it splits K over CTAs (shares through
+    the scratch, added in a fixed order): same bits run after run, the oracle's values within the layer's
+    tolerance, and the unsplit launch's values to rounding."""
+    experts, hidden, ffn, tokens, topk, seed = 2, 512, 2048, 150, 2, 91
+    gu_raw = [synth.weights(12, 2 * ffn, hidden, seed + e) for e in range(experts)]
+    dn_raw = [synth.weights(12, hidden, ffn, seed + 100 + e) for e in range(experts)]
+    gu = [ctx.store_upload(12, 2 * ffn, hidden, r) for r in gu_raw]
+    dn = [ctx.store_upload(12, hidden, ffn, r) for r in dn_raw]
+    x_bf = to_bf16_bits(synth.activations(tokens, hidden, seed + 200))
+    lg = synth.activations(tokens, experts, seed + 201)
+    ids, wts, ids_d, wts_d = route_gpu(ctx, devbuf, lg, experts, topk)
+    xd = devbuf(x_bf)
+    outs = []
+    for split in ("1", "1", "0"):
+        monkeypatch.setenv("QM_GEMM_GROUPED_SPLITK", split)
+        od = devbuf(np.full((tokens, hidden), np.nan, np.float32))
+        ctx.moe_grouped(gu, dn, xd.ptr, tokens, hidden, ids_d.ptr, wts_d.ptr, topk, od.ptr, hidden)
+        ctx.sync()
+        rc, status = ctx.last_status()
+        assert rc == 0 and status == 0
+        outs.append(od.get((tokens, hidden)))
+    assert np.isfinite(outs[0]).all()
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    ref = outs[2].astype(np.float64)
+    assert float(np.linalg.norm(outs[0] - ref) / np.linalg.norm(ref)) <= 1e-5   # another order of float32 additions
+    want = moe_oracle(gu_raw, dn_raw, hidden, ffn, x_bf, ids, wts, [0, 77, 149])
+    got = outs[0][[0, 77, 149]].astype(np.float64)
+    assert float(np.linalg.norm(got - want) / np.linalg.norm(want)) <= TOL
+    for w in gu + dn:
+        w.free()
+
+
 def test_layer_stages_match_oracle(ctx):
     """lib_b200.moe.MoELayer on one GPU (route -> dispatch -> experts -> combine through the
     staged entry points) against the oracle chain."""

@@ -10,13 +10,18 @@
 //     weight store, turns the nibbles into exact bf16 integers with the magic-number trick (byte
 //     0x43 beside the code = 128+q), applies the sub-block scale and minimum with one bf16x2 FMA
 //     per pair, and writes the row into shared memory in the canonical K-major 128-byte-swizzled
-//     layout of tcgen05 (A operand); four chunks in flight hide the latency of that chain;
-//   * warp 0 streams the matching 64 x BN activation chunk with a 2-D TMA tile copy
-//     (SWIZZLE_128B, no multicast) that completes on an mbarrier (B operand);
+//     layout of tcgen05 (A operand); four chunks in flight hide the latency of that chain
+//     (each stage has two release barriers, so four groups may run ahead of two or three stages);
+//   * warp 0 streams the matching 64 x BN activation chunk with 2-D TMA tile copies
+//     (SWIZZLE_128B, no multicast; only the boxes that hold rows of the tile) that complete on an
+//     mbarrier (B operand) — or, for a grouped launch given the dispatch list instead of gathered
+//     rows, with tile::gather4 copies of four token rows each;
 //   * one elected thread of warp 1 issues four tcgen05.mma.kind::f16 (K = 16 each) per chunk
 //     and per 256 tokens into a TMEM accumulator of BN fp32 columns (BN = 512 uses the whole
-//     tensor memory: the dequantized tile then feeds two MMAs), tcgen05.commit frees the stage;
-//   * after the last chunk warps 2..17 read the accumulator back with tcgen05.ld and store C.
+//     tensor memory: the dequantized tile then feeds two MMAs; N = the tile's tokens rounded up to
+//     16), tcgen05.commit frees the stage;
+//   * after the last chunk warps 2..17 read the accumulator back with tcgen05.ld (16 columns at a
+//     time, dealt evenly to the four warps of a lane quarter) and store C.
 // A ring of 2..8 shared-memory stages decouples the three roles. Every mbarrier wait is
 // bounded (qm_pipe.cuh); on expiry the status word gets QM_STATUS_TIMEOUT, the roles leave
 // their loops, TMEM is freed and the kernel returns.

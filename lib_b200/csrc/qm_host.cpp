@@ -1031,9 +1031,13 @@ int32_t qm_gemm_launch(qm_ctx *c, const QmWeight *w, uint64_t a_dev, int32_t m, 
     // (gate rows in one accumulator, the matching up rows in the other); for plain matmuls it is
     // kept behind QM_GEMM_R256=1: measured equal within noise (76.6 us against 74.0 us at
     // 4096 x 4096 x 2048), so neither the stage count nor the activation traffic is the limit.
-    const bool r256 = g.swiglu || (env_int("QM_GEMM_R256", 0) != 0 && w->rows >= 256);
-    const int nsub = r256 ? 2 : 1;
     const int mt = g.m_typical > 0 ? g.m_typical : m;
+    // ... and the grouped down launch where 128-row tiles would not fit one wave of the SMs (eight experts
+    // of 4096 rows: 256 tiles are 1.73 waves, 128 tiles of 256 rows are one; MoE layer 0.647 -> 0.612 ms)
+    const bool r256_wave = grouped && !g.swiglu && mt <= 256 && w->rows >= 256 &&
+                           ((w->rows + 127) / 128) * (int64_t)g.experts > c->sm_count;
+    const bool r256 = g.swiglu || (env_int("QM_GEMM_R256", r256_wave ? 1 : 0) != 0 && w->rows >= 256);
+    const int nsub = r256 ? 2 : 1;
     // (192: a grouped launch whose longest list fits gets a smaller activation tile and with it a fourth stage)
     const int bn_auto = mt <= 64 ? 64 : mt <= 128 ? 128 : (grouped && mt <= 192) ? 192 : (mt <= 256 || r256) ? 256 : 512;
     const int bn = std::min(bn_auto, std::max(64, env_int("QM_GEMM_BN", 512)));

@@ -100,6 +100,23 @@ def test_llama_shaped_layer_per_matvec(ctx):
     st.close()
 
 
+def test_full_llama_shaped_stack_end_to_end(ctx):
+    """All 32 layers at the Llama-3-8B shapes of the benchmark (3.9 GB of Q4_K weights), batch 1: the final
+    hidden state and every layer's k|v against the oracle chain run from the same input — 128 dependent
+    matvecs with their normalisations, nothing re-fed from the device on the way."""
+    layers, hidden, kv, ffn, fmt = 32, 4096, 1024, 14336, 12
+    st, raws = build_stack(ctx, layers, hidden, kv, ffn, fmt, seed=20240229)
+    x = synth.activations(1, hidden, 13)
+    h, kvs = st.step_host(x, want_kv=True)
+    rc, status = ctx.last_status()
+    assert rc == 0 and status == 0
+    want_h, want_kv, _ = oracle_chain(fmt, raws, x, hidden, kv, ffn)
+    err_h, err_kv = nre(h, want_h), nre(kvs, want_kv)
+    print("32-layer stack: nre(h) = %.3g, nre(k|v) = %.3g" % (err_h, err_kv))
+    assert err_h <= TOL and err_kv <= TOL
+    st.close()
+
+
 def test_stack_argument_errors(ctx):
     st = _capi.Stack(ctx, 1, 512, 128, 1536, 4)
     w = ctx.store_upload(12, 512, 512, synth.weights(12, 512, 512, 1))

@@ -168,7 +168,7 @@ __device__ __forceinline__ void gemm_body(const QmGemmArgs &a) {
         wq = a.wq_list[e];
     }
     // 64-column chunks along K; with split K (splitk > 1) this CTA takes a contiguous share
-    // and adds its partial tile to C, which the host zeroed
+    // and stores its partial tile to its own plane of the scratch (added up in a fixed order at the end)
     const int nk_all = a.units * 4 / KS;      // stage chunks of KS x 64 columns
     const int zk = a.grouped ? (int)blockIdx.z % a.splitk : (int)blockIdx.z;
     const int kc_lo = (int)((int64_t)nk_all * zk / a.splitk);

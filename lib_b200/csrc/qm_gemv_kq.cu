@@ -139,62 +139,79 @@ __device__ __forceinline__ void iq2xxs_block(const uint8_t *blk, const void *x, 
 // in float32 — a sixth of the instructions of the float form, which is bound by int-to-float
 // conversions.
 
-// Q2_K x Q8_1. Sixteen lanes cover a super-block, one 32-bit word of qs (16 elements of four groups)
-// each, so a warp takes two super-blocks per step; `blk` is this lane's super-block (or null past
-// the row's end), i = lane & 15, xb0 the index of the super-block's first Q8_1 block.
+// Q2_K x Q8_1. Sixteen lanes cover a super-block, one group of sixteen elements each (sixteen bytes of qs at
+// one shift, against half a Q8_1 block: four words times four words on dp4a, the group's scale and minimum
+// applied once), so a warp takes two super-blocks per step; `blk` is this lane's super-block (or null past
+// the row's end), i = lane & 15 = the group, xb0 the index of the super-block's first Q8_1 block.
 template <int M>
 __device__ __forceinline__ void q2k_q81_block(const uint8_t *blk, const uint8_t *xq, int ldx, int m, int xb0, int i,
                                               float (&acc)[M]) {
     if (!blk) return;
-    const int h = i >> 3, li = i & 7;
-    const uint32_t word = *reinterpret_cast<const uint32_t *>(blk + 16 + 4 * i);
-    const uint32_t s_lo = *reinterpret_cast<const uint32_t *>(blk + 8 * h);
-    const uint32_t s_hi = *reinterpret_cast<const uint32_t *>(blk + 8 * h + 4);
+    // elements 16i .. 16i+15: bytes 16*(i&1) .. +15 of half i>>3, bit pair (i>>1)&3; Q8_1 block xb0 + (i>>1)
+    const int sh = 2 * ((i >> 1) & 3), l0 = 16 * (i & 1);
+    const uint32_t *qw = reinterpret_cast<const uint32_t *>(blk + 16 + 32 * (i >> 3) + l0);
+    const uint32_t scb = blk[i];
     const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk + 80);
-    const float d = h2f(dd & 0xFFFFu), dmin = h2f(dd >> 16);
+    // (an fp16 times an integer below 16 is exact in float32)
+    const float dsc = h2f(dd & 0xFFFFu) * (float)(scb & 0x0Fu), dmn = h2f(dd >> 16) * (float)(scb >> 4);
+    int v[4];
 #pragma unroll
-    for (int s = 0; s < 4; s++) {
-        // elements 128h + 32s + 4li .. +3: group 8h + 2s + (li >> 2), Q8_1 block xb0 + 4h + s
-        const uint32_t scb = ((s < 2 ? s_lo : s_hi) >> (8 * (((2 * s) & 3) + (li >> 2)))) & 0xFFu;
-        const int v = (int)((word >> (2 * s)) & 0x03030303u);
-        const int sc = (int)(scb & 0x0Fu), mn = (int)(scb >> 4);
+    for (int w = 0; w < 4; w++) v[w] = (int)((qw[w] >> sh) & 0x03030303u);
 #pragma unroll
-        for (int j = 0; j < M; j++) {
-            const uint8_t *xb = xq + ((j < m ? j : 0) * ldx + xb0 + 4 * h + s) * 36;
-            const int xw = (int)*reinterpret_cast<const uint32_t *>(xb + 4 + 4 * li);
-            const float dx = h2f(*reinterpret_cast<const uint16_t *>(xb));
-            const int dot = __dp4a(v, xw, 0), sum = __dp4a(0x01010101, xw, 0);
-            acc[j] = fmaf(dx, d * small_int_to_float(sc * dot) - dmin * small_int_to_float(mn * sum), acc[j]);   // |.| <= 15*4*3*127
+    for (int j = 0; j < M; j++) {
+        const uint8_t *xb = xq + ((j < m ? j : 0) * ldx + xb0 + (i >> 1)) * 36;
+        const uint32_t *xw = reinterpret_cast<const uint32_t *>(xb + 4 + l0);
+        int dot = 0, sum = 0;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const int xv = (int)xw[w];
+            dot = __dp4a(v[w], xv, dot);
+            sum = __dp4a(0x01010101, xv, sum);
         }
+        const float dx = h2f(*reinterpret_cast<const uint16_t *>(xb));
+        acc[j] = fmaf(dx, dsc * small_int_to_float(dot) - dmn * small_int_to_float(sum), acc[j]);   // |.| <= 16*3*127
     }
 }
 
-// IQ2_XXS x Q8_1: lane = 4*group + l owns codebook entry l of its group (eight elements); the signs go into
-// the sum as dot(all) - 2*dot(negated ones), which needs no per-byte negation.
+// IQ2_XXS x Q8_1: eight lanes cover a super-block, one group of 32 elements (four codebook entries, one Q8_1
+// block) each, so a warp takes four super-blocks per step; `blk` is this lane's super-block (or null past the
+// row's end). The signs go into the sum as dot(all) - 2*dot(negated ones), which needs no per-byte negation;
+// the group's scale is applied once to the integer sum.
 template <int M>
-__device__ __forceinline__ void iq2xxs_q81_block(const uint8_t *blk, const uint8_t *xq, int ldx, int m, int xb0, int lane,
+__device__ __forceinline__ void iq2xxs_q81_block(const uint8_t *blk, const uint8_t *xq, int ldx, int m, int xb0, int group,
                                                  const unsigned long long *grid, float (&acc)[M]) {
+    if (!blk) return;
     const float d = h2f(*reinterpret_cast<const uint16_t *>(blk));
-    const int group = lane >> 2, l = lane & 3;
     const uint16_t *g16 = reinterpret_cast<const uint16_t *>(blk + 2 + 8 * group);
     const uint32_t indices = (uint32_t)g16[0] | ((uint32_t)g16[1] << 16);
     const uint32_t aux = (uint32_t)g16[2] | ((uint32_t)g16[3] << 16);
     const float scale = (0.125f * d) * (float)(2u * (aux >> 28) + 1u);
-    const unsigned long long code = grid[(indices >> (8 * l)) & 0xFFu];
-    const uint32_t si = (aux >> (7 * l)) & 127u;
-    const uint32_t signs = si | ((uint32_t)(__popc(si) & 1) << 7);
-    // byte k of a mask word = 0xFF where sign bit k is set: the bit goes to the byte's top, PRMT replicates it
-    const uint32_t t0 = ((signs & 0xFu) * 0x10204080u) & 0x80808080u, t1 = ((signs >> 4) * 0x10204080u) & 0x80808080u;
-    const int g0 = (int)(uint32_t)code, g1 = (int)(uint32_t)(code >> 32);
-    const int n0 = g0 & (int)top_bits_to_bytes(t0), n1 = g1 & (int)top_bits_to_bytes(t1);
+    int gw[8], nw[8];
+#pragma unroll
+    for (int l = 0; l < 4; l++) {
+        const unsigned long long code = grid[(indices >> (8 * l)) & 0xFFu];
+        const uint32_t si = (aux >> (7 * l)) & 127u;
+        const uint32_t signs = si | ((uint32_t)(__popc(si) & 1) << 7);
+        // byte k of a mask word = 0xFF where sign bit k is set: the bit goes to the byte's top, PRMT replicates it
+        const uint32_t t0 = ((signs & 0xFu) * 0x10204080u) & 0x80808080u, t1 = ((signs >> 4) * 0x10204080u) & 0x80808080u;
+        gw[2 * l] = (int)(uint32_t)code;
+        gw[2 * l + 1] = (int)(uint32_t)(code >> 32);
+        nw[2 * l] = gw[2 * l] & (int)top_bits_to_bytes(t0);
+        nw[2 * l + 1] = gw[2 * l + 1] & (int)top_bits_to_bytes(t1);
+    }
 #pragma unroll
     for (int j = 0; j < M; j++) {
         const uint8_t *xb = xq + ((j < m ? j : 0) * ldx + xb0 + group) * 36;
-        const int x0 = (int)*reinterpret_cast<const uint32_t *>(xb + 4 + 8 * l);
-        const int x1 = (int)*reinterpret_cast<const uint32_t *>(xb + 8 + 8 * l);
+        const uint32_t *xw = reinterpret_cast<const uint32_t *>(xb + 4);
+        int all = 0, neg = 0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int xv = (int)xw[k];
+            all = __dp4a(gw[k], xv, all);
+            neg = __dp4a(nw[k], xv, neg);
+        }
         const float dx = h2f(*reinterpret_cast<const uint16_t *>(xb));
-        const int all = __dp4a(g1, x1, __dp4a(g0, x0, 0)), neg = __dp4a(n1, x1, __dp4a(n0, x0, 0));
-        acc[j] = fmaf(scale * dx, small_int_to_float(all - 2 * neg), acc[j]);   // |.| <= 8*43*127
+        acc[j] = fmaf(scale * dx, small_int_to_float(all - 2 * neg), acc[j]);   // |.| <= 32*43*127
     }
 }
 
@@ -258,8 +275,8 @@ __device__ __forceinline__ void gemv_kq_body(const QmKqArgs &a) {
                 q2k_q81_block<M>(u < a.units ? wr + (int64_t)u * kBlockBytes : nullptr, xq, xld, m, u * 8, lane & 15, acc);
         } else if (XQ) {
             const uint8_t *xq = SM ? dyn_smem : static_cast<const uint8_t *>(x);
-            for (int u = 0; u < a.units; u++)
-                iq2xxs_q81_block<M>(wr + (int64_t)u * kBlockBytes, xq, xld, m, u * 8, lane, grid, acc);
+            for (int u = lane >> 3; u < a.units + (lane >> 3); u += 4)   // every lane makes the same number of steps
+                iq2xxs_q81_block<M>(u < a.units ? wr + (int64_t)u * kBlockBytes : nullptr, xq, xld, m, u * 8, lane & 7, grid, acc);
         } else {
             for (int u = 0; u < a.units; u++) {
                 if (FMT == 10) q2k_block<M, false>(wr + (int64_t)u * kBlockBytes, x, a.ldx, m, u * 256, lane, acc);

@@ -139,37 +139,43 @@ __device__ __forceinline__ void iq2xxs_block(const uint8_t *blk, const void *x, 
 // in float32 — a sixth of the instructions of the float form, which is bound by int-to-float
 // conversions.
 
-// Q2_K x Q8_1. Sixteen lanes cover a super-block, one group of sixteen elements each (sixteen bytes of qs at
-// one shift, against half a Q8_1 block: four words times four words on dp4a, the group's scale and minimum
-// applied once), so a warp takes two super-blocks per step; `blk` is this lane's super-block (or null past
-// the row's end), i = lane & 15 = the group, xb0 the index of the super-block's first Q8_1 block.
+// Q2_K x Q8_1. Eight lanes cover a super-block, one Q8_1 block each (32 elements = two scale groups: 32 bytes
+// of qs at one bit position, eight words times eight words on dp4a, each group's scale and minimum applied
+// once to its integer sums), so a warp takes four super-blocks per step; `blk` is this lane's super-block (or
+// null past the row's end), i = lane & 7 = the Q8_1 block within it, xb0 the index of its first Q8_1 block.
 template <int M>
 __device__ __forceinline__ void q2k_q81_block(const uint8_t *blk, const uint8_t *xq, int ldx, int m, int xb0, int i,
                                               float (&acc)[M]) {
     if (!blk) return;
-    // elements 16i .. 16i+15: bytes 16*(i&1) .. +15 of half i>>3, bit pair (i>>1)&3; Q8_1 block xb0 + (i>>1)
-    const int sh = 2 * ((i >> 1) & 3), l0 = 16 * (i & 1);
-    const uint32_t *qw = reinterpret_cast<const uint32_t *>(blk + 16 + 32 * (i >> 3) + l0);
-    const uint32_t scb = blk[i];
+    // elements 32i .. 32i+31: the 32 bytes of half i>>2, bit pair i&3; scale groups 2i and 2i+1
+    const int sh = 2 * (i & 3);
+    const uint32_t *qw = reinterpret_cast<const uint32_t *>(blk + 16 + 32 * (i >> 2));
+    const uint32_t sc2 = *reinterpret_cast<const uint16_t *>(blk + 2 * i);
     const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk + 80);
+    const float d = h2f(dd & 0xFFFFu), dmin = h2f(dd >> 16);
     // (an fp16 times an integer below 16 is exact in float32)
-    const float dsc = h2f(dd & 0xFFFFu) * (float)(scb & 0x0Fu), dmn = h2f(dd >> 16) * (float)(scb >> 4);
-    int v[4];
+    const float dsc0 = d * (float)(sc2 & 0x0Fu), dmn0 = dmin * (float)((sc2 >> 4) & 0x0Fu);
+    const float dsc1 = d * (float)((sc2 >> 8) & 0x0Fu), dmn1 = dmin * (float)(sc2 >> 12);
+    int v[8];
 #pragma unroll
-    for (int w = 0; w < 4; w++) v[w] = (int)((qw[w] >> sh) & 0x03030303u);
+    for (int w = 0; w < 8; w++) v[w] = (int)((qw[w] >> sh) & 0x03030303u);
 #pragma unroll
     for (int j = 0; j < M; j++) {
-        const uint8_t *xb = xq + ((j < m ? j : 0) * ldx + xb0 + (i >> 1)) * 36;
-        const uint32_t *xw = reinterpret_cast<const uint32_t *>(xb + 4 + l0);
-        int dot = 0, sum = 0;
+        const uint8_t *xb = xq + ((j < m ? j : 0) * ldx + xb0 + i) * 36;
+        const uint32_t *xw = reinterpret_cast<const uint32_t *>(xb + 4);
+        int dot0 = 0, sum0 = 0, dot1 = 0, sum1 = 0;
 #pragma unroll
         for (int w = 0; w < 4; w++) {
-            const int xv = (int)xw[w];
-            dot = __dp4a(v[w], xv, dot);
-            sum = __dp4a(0x01010101, xv, sum);
+            const int x0 = (int)xw[w], x1 = (int)xw[4 + w];
+            dot0 = __dp4a(v[w], x0, dot0);
+            sum0 = __dp4a(0x01010101, x0, sum0);
+            dot1 = __dp4a(v[4 + w], x1, dot1);
+            sum1 = __dp4a(0x01010101, x1, sum1);
         }
         const float dx = h2f(*reinterpret_cast<const uint16_t *>(xb));
-        acc[j] = fmaf(dx, dsc * small_int_to_float(dot) - dmn * small_int_to_float(sum), acc[j]);   // |.| <= 16*3*127
+        const float g0 = dsc0 * small_int_to_float(dot0) - dmn0 * small_int_to_float(sum0);   // |.| <= 16*3*127
+        const float g1 = dsc1 * small_int_to_float(dot1) - dmn1 * small_int_to_float(sum1);
+        acc[j] = fmaf(dx, g0 + g1, acc[j]);
     }
 }
 
@@ -271,8 +277,8 @@ __device__ __forceinline__ void gemv_kq_body(const QmKqArgs &a) {
     auto row_dot = [&](const uint8_t *wr, float (&acc)[M]) {
         if (XQ && FMT == 10) {
             const uint8_t *xq = SM ? dyn_smem : static_cast<const uint8_t *>(x);
-            for (int u = lane >> 4; u < a.units + (lane >> 4); u += 2)   // every lane makes the same number of steps
-                q2k_q81_block<M>(u < a.units ? wr + (int64_t)u * kBlockBytes : nullptr, xq, xld, m, u * 8, lane & 15, acc);
+            for (int u = lane >> 3; u < a.units + (lane >> 3); u += 4)   // every lane makes the same number of steps
+                q2k_q81_block<M>(u < a.units ? wr + (int64_t)u * kBlockBytes : nullptr, xq, xld, m, u * 8, lane & 7, acc);
         } else if (XQ) {
             const uint8_t *xq = SM ? dyn_smem : static_cast<const uint8_t *>(x);
             for (int u = lane >> 3; u < a.units + (lane >> 3); u += 4)   // every lane makes the same number of steps
